@@ -1,0 +1,382 @@
+"""Operator interface of the runtime.
+
+Every operator has two implementations with identical semantics:
+
+* CUDA tensors -> the hand-written sm_100a kernels in csrc/kernels (via skein_b200.ops._lib). There
+  is no PyTorch fallback on this path: a missing or failing kernel raises.
+* CPU tensors  -> the fp32 PyTorch reference in skein_b200.ops.reference (tests, planner-side
+  tooling, parity oracle).
+
+Conventions: activations are row-major [tokens, features] bf16; weights are [out_features,
+in_features] bf16 (the HuggingFace layout), experts stacked on a leading dim.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib, reference as ref
+
+_WORKSPACES: dict = {}
+
+
+class Workspace:
+    """Per-device scratch shared by kernels that run one after another on a stream.
+
+    Holds the stream-K partial-tile buffer and arrival counters of the GEMM, the split-KV buffers
+    of decode attention, and the two-int status word that kernels write an error code into when a
+    bounded wait runs out or a debug bounds check trips.
+    """
+
+    GEMM_WS_BYTES = 148 * 2 * 128 * 256 * 4 + (1 << 20)
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        L = _lib.lib()
+        self.sm_count = L.skein_sm_count()
+        self.gemm_ws = torch.empty(max(self.GEMM_WS_BYTES, self.sm_count * 2 * 128 * 256 * 4), dtype=torch.uint8,
+                                   device=device)
+        self.gemm_counters = torch.zeros(max(self.sm_count, 256), dtype=torch.int32, device=device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.attn_ws = None
+        self.attn_counters = None
+
+    def attn_scratch(self, B, Hq, Hkv, splits):
+        n = _lib.lib().skein_attn_decode_workspace_floats(B, Hq, splits)
+        if self.attn_ws is None or self.attn_ws.numel() < n:
+            self.attn_ws = torch.empty(int(n), dtype=torch.float32, device=self.device)
+        if self.attn_counters is None or self.attn_counters.numel() < B * Hkv:
+            self.attn_counters = torch.zeros(B * Hkv, dtype=torch.int32, device=self.device)
+        return self.attn_ws, self.attn_counters
+
+    def check_status(self):
+        """Host read of the status word (synchronises). Raises on a recorded device-side error."""
+        code, detail = self.status.tolist()
+        if code != 0:
+            self.status.zero_()
+            names = {1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
+                     3: "timeout waiting for an accumulator", 4: "timeout waiting for a drained accumulator",
+                     5: "timeout waiting for a peer flag", 7: "index out of range"}
+            raise RuntimeError(f"device status {code} ({names.get(code, 'unknown')}), detail {detail}")
+
+
+def workspace(device=None) -> Workspace:
+    device = torch.device(device if device is not None else torch.cuda.current_device())
+    if device.type != "cuda":
+        raise ValueError("workspaces exist for CUDA devices only")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ws = _WORKSPACES.get(device)
+    if ws is None:
+        ws = _WORKSPACES[device] = Workspace(device)
+    return ws
+
+
+def _round_up(x, m):
+    return (x + m - 1) // m * m
+
+
+def pick_n_tile(rows_hint: int, dual: bool) -> int:
+    cap = 128 if dual else 256
+    return max(16, min(cap, _round_up(max(rows_hint, 1), 16)))
+
+
+def _gemm_launch(p: "_lib.GemmParams", what: str):
+    ws = workspace()
+    p.workspace = ws.gemm_ws.data_ptr()
+    p.counters = ws.gemm_counters.data_ptr()
+    p.status = ws.status.data_ptr()
+    _lib.check(_lib.lib().skein_gemm_ws(C.byref(p), _lib.stream_ptr()), what)
+    _lib.count_launch()
+
+
+def _base_params(x, w2d, out, F, K, n_tile, mode) -> "_lib.GemmParams":
+    p = _lib.GemmParams()
+    p.W = w2d.data_ptr()
+    p.X = x.data_ptr()
+    p.out = out.data_ptr() if out is not None else None
+    p.G, p.F, p.K = 1, F, K
+    p.w_rows_per_group = w2d.shape[0]
+    p.up_row_off = 0
+    p.x_rows = x.shape[0]
+    p.t_static = x.shape[0]
+    p.n_tile = n_tile
+    p.ldo = out.stride(0) if out is not None else 0
+    p.mode = mode
+    return p
+
+
+def _check_act(x):
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("activations must be contiguous bf16")
+
+
+def linear(x, w, out=None, residual=None, n_tile=None):
+    """y[t, f] = sum_k x[t, k] w[f, k] (+ residual[t, f])."""
+    if not x.is_cuda:
+        y = ref.linear(x, w, residual)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _check_act(x)
+    T, K = x.shape
+    F = w.shape[0]
+    if out is None:
+        out = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    p = _base_params(x, w, out, F, K, n_tile or pick_n_tile(T, False), 0)
+    if residual is not None:
+        p.residual = residual.data_ptr()
+    _gemm_launch(p, "linear")
+    return out
+
+
+def swiglu_linear(x, w13, out=None, n_tile=None):
+    """silu(x @ w13[:I].T) * (x @ w13[I:].T) with both products from one pass over x."""
+    if not x.is_cuda:
+        return ref.swiglu_linear(x, w13)
+    _check_act(x)
+    T, K = x.shape
+    inter = w13.shape[0] // 2
+    if out is None:
+        out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    p = _base_params(x, w13, out, inter, K, n_tile or pick_n_tile(T, True), 1)
+    p.up_row_off = inter
+    _gemm_launch(p, "swiglu_linear")
+    return out
+
+
+def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, rows_hint=None):
+    """Per-expert linear over an expert-sorted activation matrix.
+
+    xs [rows, K]; w [E, F, K] (or [E, 2I, K] with gate rows first when swiglu); counts / offsets are
+    int32 device tensors of E (offsets may have E+1) entries: rows of expert e are
+    offsets[e] : offsets[e] + counts[e]. Rows not covered by any expert are left untouched.
+    """
+    if not xs.is_cuda:
+        return ref.grouped_linear(xs, w, counts, offsets, swiglu)
+    _check_act(xs)
+    rows, K = xs.shape
+    E = w.shape[0]
+    F = w.shape[1] // 2 if swiglu else w.shape[1]
+    if out is None:
+        out = torch.empty(rows, F, dtype=torch.bfloat16, device=xs.device)
+    if rows == 0:
+        return out
+    if n_tile is None:
+        avg = (rows_hint if rows_hint is not None else rows) / E
+        n_tile = pick_n_tile(int(math.ceil(avg * 1.5)), swiglu)
+    p = _base_params(xs, w.view(E * w.shape[1], K), out, F, K, n_tile, 1 if swiglu else 0)
+    p.G = E
+    p.w_rows_per_group = w.shape[1]
+    p.up_row_off = F if swiglu else 0
+    p.group_off = offsets.data_ptr()
+    p.group_cnt = counts.data_ptr()
+    _gemm_launch(p, "grouped_linear")
+    return out
+
+
+def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None, residual_out=None,
+                            normed_out=None, flags=None, epoch=None, wait_budget_ms=0):
+    """See csrc/kernels/norm.cu. partial: [n_src, rows, H] or None. Returns (residual_out, normed_out)."""
+    src = residual if residual is not None else partial
+    if not src.is_cuda:
+        return ref.reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx, row_w)
+    H = src.shape[-1]
+    B = residual.shape[0] if residual is not None else (row_idx.shape[0] if row_idx is not None else partial.shape[1])
+    if residual_out is None:
+        residual_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
+    if normed_out is None and gamma is not None:
+        normed_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
+    n_src = partial.shape[0] if partial is not None else 0
+    src_stride = partial.stride(0) if partial is not None else 0
+    topk = row_idx.shape[1] if row_idx is not None else 0
+    ws = workspace()
+    rc = _lib.lib().skein_reduce_residual_rmsnorm(
+        _lib.ptr(residual), _lib.ptr(partial), _lib.ptr(row_idx), _lib.ptr(row_w), _lib.ptr(gamma),
+        _lib.ptr(residual_out), _lib.ptr(normed_out), _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(),
+        src_stride, B, H, n_src, topk, float(eps), wait_budget_ms, _lib.stream_ptr())
+    _lib.check(rc, "reduce_residual_rmsnorm")
+    _lib.count_launch()
+    return residual_out, normed_out
+
+
+def rmsnorm(x, gamma, eps):
+    return reduce_residual_rmsnorm(x, None, gamma, eps)[1]
+
+
+def rope_kv_append(qkv, positions, seq_of_token, block_table, cos_sin, kv_cache, Hq, Hkv, D):
+    """Rotate q (in place) and k, append k/v of every token into the paged cache."""
+    if not qkv.is_cuda:
+        return ref.rope_kv_append(qkv, positions, seq_of_token, block_table, cos_sin, kv_cache, Hq, Hkv, D)
+    T = qkv.shape[0]
+    ws = workspace()
+    rc = _lib.lib().skein_rope_kv_append(
+        qkv.data_ptr(), positions.data_ptr(), _lib.ptr(seq_of_token), block_table.data_ptr(), block_table.stride(0),
+        cos_sin.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[3], T, Hq, Hkv, D, cos_sin.shape[0],
+        kv_cache.shape[0], ws.status.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "rope_kv_append")
+    _lib.count_launch()
+
+
+def pick_splits(B, Hkv, ctx_hint, sm_count=148):
+    ctas = max(B * Hkv, 1)
+    s = max(1, (2 * sm_count) // ctas)
+    s = min(s, max(1, ctx_hint // 256), 16)
+    return s
+
+
+def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=None, splits=None, ctx_hint=1024):
+    """q: [B, row_stride] whose first Hq*D columns are the (rotated) query heads -> [B, Hq*D]."""
+    if not q.is_cuda:
+        return ref.attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale)
+    B = q.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(B, Hq * D, dtype=torch.bfloat16, device=q.device)
+    ws = workspace()
+    if splits is None:
+        splits = pick_splits(B, Hkv, ctx_hint, ws.sm_count)
+    wsf, ctr = (None, None)
+    if splits > 1:
+        wsf, ctr = ws.attn_scratch(B, Hq, Hkv, splits)
+    rc = _lib.lib().skein_attn_decode(
+        q.data_ptr(), q.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+        _lib.ptr(wsf), _lib.ptr(ctr), ws.status.data_ptr(), B, Hq, Hkv, D, kv_cache.shape[3], block_table.stride(0),
+        kv_cache.shape[0], splits, float(scale), _lib.stream_ptr())
+    _lib.check(rc, "attn_decode")
+    _lib.count_launch()
+    return out
+
+
+def attn_prefill(q, kv_cache, block_table, q_start, q_len, kv_len, max_q_len, Hq, Hkv, D, scale=None, out=None):
+    if not q.is_cuda:
+        return ref.attn_prefill(q, kv_cache, block_table, q_start, q_len, kv_len, Hq, Hkv, D, scale)
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
+    ws = workspace()
+    rc = _lib.lib().skein_attn_prefill(
+        q.data_ptr(), q.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), q_start.data_ptr(), q_len.data_ptr(),
+        kv_len.data_ptr(), out.data_ptr(), ws.status.data_ptr(), q_len.shape[0], int(max_q_len), Hq, Hkv, D,
+        kv_cache.shape[3], block_table.stride(0), kv_cache.shape[0], float(scale), _lib.stream_ptr())
+    _lib.check(rc, "attn_prefill")
+    _lib.count_launch()
+    return out
+
+
+def router_topk(x, wg, topk, want_logits=False):
+    """Returns (expert_ids int32 [T, k], weights fp32 [T, k], logits fp32 [T, E] or None)."""
+    if not x.is_cuda:
+        ids, w, lg = ref.router_topk(x, wg, topk)
+        return ids, w, (lg if want_logits else None)
+    T, H = x.shape
+    E = wg.shape[0]
+    ids = torch.empty(T, topk, dtype=torch.int32, device=x.device)
+    w = torch.empty(T, topk, dtype=torch.float32, device=x.device)
+    lg = torch.empty(T, E, dtype=torch.float32, device=x.device) if want_logits else None
+    rc = _lib.lib().skein_router_topk(x.data_ptr(), wg.data_ptr(), T, H, E, topk, ids.data_ptr(), w.data_ptr(),
+                                      _lib.ptr(lg), _lib.stream_ptr())
+    _lib.check(rc, "router_topk")
+    _lib.count_launch()
+    return ids, w, lg
+
+
+def router_plan(expert_ids, E, e_first=0, e_count=None, bufs=None):
+    """Expert-sorted layout of the (token, slot) pairs. Returns (counts[E], offsets[E+1], row_of[T*k], src_token[T*k])."""
+    if not expert_ids.is_cuda:
+        return ref.router_plan(expert_ids, E, e_first, e_count)
+    T, topk = expert_ids.shape
+    n = T * topk
+    dev = expert_ids.device
+    if bufs is None:
+        counts = torch.empty(E, dtype=torch.int32, device=dev)
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        row_of = torch.empty(n, dtype=torch.int32, device=dev)
+        src_token = torch.zeros(max(n, 1), dtype=torch.int32, device=dev)
+    else:
+        counts, offsets, row_of, src_token = bufs
+    rc = _lib.lib().skein_router_plan(expert_ids.data_ptr(), n, E, topk, counts.data_ptr(), offsets.data_ptr(),
+                                      row_of.data_ptr(), src_token.data_ptr(), e_first,
+                                      E if e_count is None else e_count, _lib.stream_ptr())
+    _lib.check(rc, "router_plan")
+    _lib.count_launch()
+    return counts, offsets, row_of, src_token
+
+
+def gather_rows(x, src_row, n_rows_dev=None, out=None):
+    """out[r] = x[src_row[r]] for r < n_rows (a device int, or all rows of src_row)."""
+    if not x.is_cuda:
+        return x[src_row.long()]
+    n = src_row.shape[0]
+    H = x.shape[1]
+    if out is None:
+        out = torch.zeros(n, H, dtype=x.dtype, device=x.device)
+    rc = _lib.lib().skein_gather_rows(x.data_ptr(), src_row.data_ptr(), out.data_ptr(), n, H, _lib.ptr(n_rows_dev),
+                                      _lib.stream_ptr())
+    _lib.check(rc, "gather_rows")
+    _lib.count_launch()
+    return out
+
+
+def embed(ids, table, vocab_start=0, out=None):
+    if not table.is_cuda:
+        return ref.embed(ids, table, vocab_start)
+    T = ids.shape[0]
+    H = table.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    rc = _lib.lib().skein_embed_gather(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, H, vocab_start,
+                                       table.shape[0], _lib.stream_ptr())
+    _lib.check(rc, "embed")
+    _lib.count_launch()
+    return out
+
+
+def sample_argmax(logits, idx_offset=0, out=None, out_val=None):
+    """Greedy token per row (ties -> lowest index). logits [B, V] bf16, row stride arbitrary."""
+    if not logits.is_cuda:
+        r = ref.sample_argmax(logits) + idx_offset
+        return r
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    rc = _lib.lib().skein_sample_argmax(logits.data_ptr(), logits.stride(0), B, V, idx_offset, out.data_ptr(),
+                                        _lib.ptr(out_val), _lib.stream_ptr())
+    _lib.check(rc, "sample_argmax")
+    _lib.count_launch()
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, seeds, step, out=None):
+    """Temperature / top-k / top-p sampling; per-row parameters are device tensors."""
+    if not logits.is_cuda:
+        raise NotImplementedError("stochastic sampling runs on the GPU; use sample_argmax on CPU")
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    rc = _lib.lib().skein_sample_topk_topp(logits.data_ptr(), logits.stride(0), B, V, _lib.ptr(temperature),
+                                           _lib.ptr(top_k), _lib.ptr(top_p), _lib.ptr(seeds), _lib.ptr(step),
+                                           out.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "sample")
+    _lib.count_launch()
+    return out
+
+
+def quant_fp8_block128(x):
+    """bf16 [rows, K] -> (e4m3 [rows, K], fp32 scales [rows, K/128])."""
+    if not x.is_cuda:
+        return ref.quant_fp8_block128(x)
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(rows, K // 128, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().skein_quant_fp8_block128(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, K, _lib.stream_ptr())
+    _lib.check(rc, "quant_fp8_block128")
+    _lib.count_launch()
+    return q, s
