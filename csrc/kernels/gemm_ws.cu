@@ -111,8 +111,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     sched.KB = p.K / (p.fp8 ? 128 : 64);
     sched.U = acc;
     sched.TK = (long long)acc * sched.KB;
+    // equal share per CTA, but never so small that a tile is cut into more than 8 pieces
     long long per = (sched.TK + gridDim.x - 1) / gridDim.x;
-    if (per < 4) per = 4;
+    const long long min_per = sched.KB >= 32 ? sched.KB / 8 : 4;
+    if (per < min_per) per = min_per;
     sched.per = (int)per;
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
@@ -324,14 +326,29 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) { g16[j] = 0.f; u16[j] = 0.f; }
-              for (int c = c_first; c <= c_last; ++c) {
-                const int slot = ((long long)c * sched.per) / KB == u ? 0 : 1;
-                const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems;
+              // contributors are read four at a time so that 64+ loads are in flight per thread
+              for (int cb = c_first; cb <= c_last; cb += 4) {
+                float tg[4][16], tu[4][16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  g16[j] += __ldcg(&ws[(size_t)(c0 + j) * TILE_F + r]);
-                  if (DUAL) u16[j] += __ldcg(&ws[(size_t)(n_tile + c0 + j) * TILE_F + r]);
+                for (int ci = 0; ci < 4; ++ci) {
+                  const int c = cb + ci;
+                  if (c <= c_last) {
+                    const int slot = ((long long)c * sched.per) / KB == u ? 0 : 1;
+                    const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                      tg[ci][j] = __ldcg(&ws[(size_t)(c0 + j) * TILE_F + r]);
+                      if (DUAL) tu[ci][j] = __ldcg(&ws[(size_t)(n_tile + c0 + j) * TILE_F + r]);
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { tg[ci][j] = 0.f; if (DUAL) tu[ci][j] = 0.f; }
+                  }
                 }
+#pragma unroll
+                for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) { g16[j] += tg[ci][j]; if (DUAL) u16[j] += tu[ci][j]; }
               }
             }
             if (f_ok) {

@@ -153,7 +153,28 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const __nv_bfloa
   }
 }
 
+// Feeds a decode step's sampled tokens back as the next step's inputs without a host round trip:
+// live rows (seq_len > 0) take the new token and move one position forward.
+__global__ void advance_decode_state_kernel(const int* __restrict__ sampled, int* __restrict__ tokens,
+                                            int* __restrict__ positions, int* __restrict__ seq_lens, int B,
+                                            int* step_counter) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b == 0 && step_counter) *step_counter += 1;
+  if (b >= B || seq_lens[b] <= 0) return;
+  tokens[b] = sampled[b];
+  positions[b] += 1;
+  seq_lens[b] += 1;
+}
+
 }  // namespace skein
+
+extern "C" int skein_advance_decode_state(const int* sampled, int* tokens, int* positions, int* seq_lens, int B,
+                                          int* step_counter, void* stream) {
+  if (B == 0) return 0;
+  skein::advance_decode_state_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sampled, tokens, positions,
+                                                                                        seq_lens, B, step_counter);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int skein_sample_argmax(const void* logits, long long ld, int B, int V, int idx_offset, int* out_idx,
                                    float* out_val, void* stream) {

@@ -1,0 +1,169 @@
+"""Model and parallel-layout descriptions used by the decoder graph.
+
+ModelConfig is read from a HuggingFace ``config.json`` (MixtralForCausalLM, LlamaForCausalLM and
+the Llama-shaped Mistral / Qwen2 families). The reference imports Mixtral only
+(crates/skein_ir/src/model/mod.rs:33-47, model/mixtral.rs:74-372) and rejects the rest; here the
+dense Llama-style block is a Mixtral block with a plain SwiGLU MLP instead of routed experts.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+
+MOE_ARCHS = {"MixtralForCausalLM"}
+DENSE_ARCHS = {"LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM"}
+
+
+class ImportError_(ValueError):
+    """A config.json that cannot be turned into a consistent model."""
+
+
+@dataclass
+class ModelConfig:
+    architecture: str = "MixtralForCausalLM"
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 32000
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 1e6
+    num_experts: int = 8          # 0 = dense MLP
+    top_k: int = 2
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    name: str = "mixtral-8x7b"
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def validate(self) -> None:
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ImportError_("num_attention_heads must be a multiple of num_key_value_heads")
+        if self.is_moe and not (1 <= self.top_k <= self.num_experts):
+            raise ImportError_("num_experts_per_tok must be in [1, num_local_experts]")
+        if self.head_dim % 2 != 0:
+            raise ImportError_("head_dim must be even (RoPE rotates pairs)")
+
+    def param_count(self) -> int:
+        H, I, D = self.hidden_size, self.intermediate_size, self.head_dim
+        attn = H * (self.num_heads * D) * 2 + H * (self.num_kv_heads * D) * 2
+        ffn = 3 * H * I * max(self.num_experts, 1) + (H * self.num_experts if self.is_moe else 0)
+        per_block = attn + ffn + 2 * H
+        emb = self.vocab_size * H
+        return self.num_layers * per_block + emb + H + (0 if self.tie_word_embeddings else emb)
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    @staticmethod
+    def from_hf_dict(d: dict, name: str | None = None) -> "ModelConfig":
+        archs = d.get("architectures") or []
+        if not archs:
+            raise ImportError_("config.json has no `architectures`")
+        arch = archs[0]
+        if arch not in MOE_ARCHS | DENSE_ARCHS:
+            raise ImportError_(f"architecture {arch} is not supported")
+        act = d.get("hidden_act", "silu")
+        if act != "silu":
+            raise ImportError_(f"hidden_act {act!r} is not supported (only silu)")
+        H = int(d["hidden_size"])
+        nh = int(d["num_attention_heads"])
+        hd = d.get("head_dim") or (H // nh)
+        if d.get("head_dim") is None and H % nh != 0:
+            raise ImportError_("hidden_size is not divisible by num_attention_heads and head_dim is absent")
+        cfg = ModelConfig(
+            architecture=arch, hidden_size=H, intermediate_size=int(d["intermediate_size"]),
+            num_layers=int(d["num_hidden_layers"]), num_heads=nh,
+            num_kv_heads=int(d.get("num_key_value_heads", nh)), head_dim=int(hd), vocab_size=int(d["vocab_size"]),
+            rms_norm_eps=float(d.get("rms_norm_eps", 1e-5)), rope_theta=float(d.get("rope_theta", 1e4)),
+            num_experts=int(d.get("num_local_experts", 0)) if arch in MOE_ARCHS else 0,
+            top_k=int(d.get("num_experts_per_tok", 0)) if arch in MOE_ARCHS else 0,
+            max_position_embeddings=int(d.get("max_position_embeddings", 8192)),
+            tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
+            name=name or d.get("_name_or_path") or d.get("model_type", "model"))
+        cfg.validate()
+        return cfg
+
+    @staticmethod
+    def from_file(path) -> "ModelConfig":
+        p = Path(path)
+        return ModelConfig.from_hf_dict(json.loads(p.read_text()), name=p.stem.replace("_config", ""))
+
+
+def mixtral_8x7b() -> ModelConfig:
+    return ModelConfig()
+
+
+def mixtral_8x22b() -> ModelConfig:
+    return ModelConfig(hidden_size=6144, intermediate_size=16384, num_layers=56, num_heads=48, num_kv_heads=8,
+                       head_dim=128, vocab_size=32768, rope_theta=1e6, num_experts=8, top_k=2,
+                       max_position_embeddings=65536, name="mixtral-8x22b")
+
+
+def llama3_70b() -> ModelConfig:
+    return ModelConfig(architecture="LlamaForCausalLM", hidden_size=8192, intermediate_size=28672, num_layers=80,
+                       num_heads=64, num_kv_heads=8, head_dim=128, vocab_size=128256, rms_norm_eps=1e-5,
+                       rope_theta=5e5, num_experts=0, top_k=0, max_position_embeddings=8192, name="llama3-70b")
+
+
+def tiny_mixtral(layers=2, hidden=256, inter=512, heads=4, kv_heads=2, experts=4, vocab=512) -> ModelConfig:
+    """A small Mixtral-shaped model for tests (head_dim stays 128: the attention kernels require it)."""
+    return ModelConfig(hidden_size=hidden, intermediate_size=inter, num_layers=layers, num_heads=heads,
+                       num_kv_heads=kv_heads, head_dim=128, vocab_size=vocab, num_experts=experts, top_k=2,
+                       max_position_embeddings=4096, name="tiny-mixtral")
+
+
+def tiny_llama(layers=2, hidden=256, inter=512, heads=4, kv_heads=2, vocab=512) -> ModelConfig:
+    return ModelConfig(architecture="LlamaForCausalLM", hidden_size=hidden, intermediate_size=inter,
+                       num_layers=layers, num_heads=heads, num_kv_heads=kv_heads, head_dim=128, vocab_size=vocab,
+                       rope_theta=5e5, num_experts=0, top_k=0, max_position_embeddings=4096, name="tiny-llama")
+
+
+@dataclass
+class ParallelLayout:
+    """Where this rank sits in the TP x PP x EP grid (device coordinates are lexicographic in
+    (pp, ep, tp), tp fastest, as in the reference's Placement: crates/skein_cost/src/cluster.rs:100-169)."""
+    tp: int = 1
+    pp: int = 1
+    ep: int = 1
+    rank: int = 0
+
+    @property
+    def world(self) -> int:
+        return self.tp * self.pp * self.ep
+
+    @property
+    def tp_rank(self) -> int:
+        return self.rank % self.tp
+
+    @property
+    def ep_rank(self) -> int:
+        return (self.rank // self.tp) % self.ep
+
+    @property
+    def pp_rank(self) -> int:
+        return self.rank // (self.tp * self.ep)
+
+    def tp_group(self) -> list[int]:
+        base = self.rank - self.tp_rank
+        return [base + i for i in range(self.tp)]
+
+    def ep_group(self) -> list[int]:
+        base = self.pp_rank * self.tp * self.ep + self.tp_rank
+        return [base + i * self.tp for i in range(self.ep)]
+
+    def pp_group(self) -> list[int]:
+        inner = self.rank % (self.tp * self.ep)
+        return [inner + s * self.tp * self.ep for s in range(self.pp)]
+
+    def stage_layers(self, num_layers: int) -> range:
+        """Blocks of this pipeline stage; the remainder is spread over the first stages."""
+        base, rem = divmod(num_layers, self.pp)
+        s = self.pp_rank
+        start = s * base + min(s, rem)
+        return range(start, start + base + (1 if s < rem else 0))

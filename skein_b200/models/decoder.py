@@ -1,0 +1,208 @@
+"""Decoder-only transformer (Mixtral MoE blocks or Llama dense blocks) over the operator interface.
+
+The graph is the same for prefill and decode; only the attention operator differs. Per block:
+
+    normed -> fused q/k/v projection -> RoPE + paged-KV append -> attention -> o_proj
+           -> [sum partials + residual + RMSNorm]                      (one fused kernel)
+           -> MoE: router top-k -> expert-sorted gather -> grouped gate/up GEMM with SwiGLU epilogue
+                   -> grouped down GEMM            | dense: gate/up GEMM with SwiGLU -> down GEMM
+           -> [top-k weighted combine + sum partials + residual + next block's RMSNorm] (one kernel)
+
+Under tensor parallelism the two row-parallel projections (o_proj, down) store their partial output
+straight into every peer's buffer from the GEMM epilogue and the fused reduce kernel that follows
+waits on the peers' flags, so a block has no stand-alone collective launch.
+
+This is the role of the reference's op wiring (crates/skein_emit/src/op_wiring.rs:740-902 wire_block,
+:904 attention, :1153-1304 MoE variants, :1787 rms_norm, :2431-2472 RoPE), with PyTorch holding
+the graph instead of luminal and hand-written kernels instead of searched ones.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from .config import ModelConfig, ParallelLayout
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor            # [H]
+    wqkv: torch.Tensor                 # [(Hq + 2 Hkv) / tp * D, H]   q rows, then k rows, then v rows
+    wo: torch.Tensor                   # [H, Hq / tp * D]
+    ffn_norm: torch.Tensor             # [H]
+    router: torch.Tensor | None        # [E, H]
+    w13: torch.Tensor                  # MoE: [E_local, 2 I / tp, H] (gate rows first); dense: [2 I / tp, H]
+    w2: torch.Tensor                   # MoE: [E_local, H, I / tp];                     dense: [H, I / tp]
+    # block-scaled fp8 copies (present when the plan's dtype map selects fp8 for this block)
+    fp8: dict = field(default_factory=dict)
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor | None         # [V, H] (first pipeline stage)
+    layers: list                       # LayerWeights of this stage's blocks
+    final_norm: torch.Tensor | None    # [H] (last stage)
+    lm_head: torch.Tensor | None       # [V / tp, H] (last stage)
+
+
+def shard_shapes(cfg: ModelConfig, lay: ParallelLayout):
+    if cfg.num_heads % lay.tp or cfg.num_kv_heads % lay.tp:
+        raise ValueError(f"tp={lay.tp} must divide the query heads ({cfg.num_heads}) and kv heads ({cfg.num_kv_heads})")
+    if cfg.intermediate_size % lay.tp:
+        raise ValueError("tp must divide intermediate_size")
+    if cfg.is_moe and cfg.num_experts % lay.ep:
+        raise ValueError("ep must divide the number of experts")
+    if not cfg.is_moe and lay.ep != 1:
+        raise ValueError("expert parallelism needs a MoE model")
+    return dict(Hq=cfg.num_heads // lay.tp, Hkv=cfg.num_kv_heads // lay.tp, I=cfg.intermediate_size // lay.tp,
+                E_local=(cfg.num_experts // lay.ep) if cfg.is_moe else 0,
+                V_local=(cfg.vocab_size + lay.tp - 1) // lay.tp)
+
+
+def random_weights(cfg: ModelConfig, lay: ParallelLayout, device, seed: int = 0, std: float = 0.02,
+                   dtype=torch.bfloat16) -> ModelWeights:
+    """Random-init weights N(0, std) of this rank's shard shapes (norm gains are 1, as HF initialises them)."""
+    sh = shard_shapes(cfg, lay)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed * 1000003 + lay.rank)
+    H, D = cfg.hidden_size, cfg.head_dim
+
+    def rnd(*shape):
+        t = torch.empty(*shape, dtype=dtype, device=device)
+        t.normal_(0.0, std, generator=g)
+        return t
+
+    layers = []
+    for _ in lay.stage_layers(cfg.num_layers):
+        if cfg.is_moe:
+            router, w13, w2 = rnd(cfg.num_experts, H), rnd(sh["E_local"], 2 * sh["I"], H), rnd(sh["E_local"], H, sh["I"])
+        else:
+            router, w13, w2 = None, rnd(2 * sh["I"], H), rnd(H, sh["I"])
+        layers.append(LayerWeights(
+            attn_norm=torch.ones(H, dtype=dtype, device=device), wqkv=rnd((sh["Hq"] + 2 * sh["Hkv"]) * D, H),
+            wo=rnd(H, sh["Hq"] * D), ffn_norm=torch.ones(H, dtype=dtype, device=device), router=router, w13=w13, w2=w2))
+    first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
+    return ModelWeights(
+        embed=rnd(cfg.vocab_size, H) if first else None, layers=layers,
+        final_norm=torch.ones(H, dtype=dtype, device=device) if last else None,
+        lm_head=rnd(sh["V_local"], H) if last else None)
+
+
+@dataclass
+class BatchInputs:
+    """Device-side description of one step (prefill chunk or decode step)."""
+    token_ids: torch.Tensor            # [T] int32
+    positions: torch.Tensor            # [T] int32, -1 marks a padding row
+    block_table: torch.Tensor          # [S, max_blocks] int32
+    seq_lens: torch.Tensor             # [S] int32: cache length of each sequence after this step
+    is_prefill: bool = False
+    seq_of_token: torch.Tensor | None = None   # [T] int32 (prefill); decode: token t belongs to sequence t
+    q_start: torch.Tensor | None = None        # [S] int32 (prefill)
+    q_len: torch.Tensor | None = None          # [S] int32 (prefill)
+    max_q_len: int = 0                         # host int (prefill)
+    logit_rows: torch.Tensor | None = None     # [S] int64 rows of the hidden state that produce logits (prefill)
+    ctx_hint: int = 1024                       # host-side typical context length (chooses split-KV)
+
+
+class Decoder:
+    """One rank's share of the model: weights, KV cache and the step function."""
+
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
+                 num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None):
+        self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
+        self.comm = comm  # tensor-parallel communicator (skein_b200.parallel.tp.TPComm) or None
+        self.sh = shard_shapes(cfg, self.layout)
+        self.page_size = page_size
+        dev = (weights.embed if weights.embed is not None else weights.layers[0].wqkv).device
+        self.device = dev
+        self.max_pos = max_pos or cfg.max_position_embeddings
+        self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev)
+        self.num_pages = num_pages
+        self.kv = [torch.zeros(num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+                   for _ in weights.layers] if num_pages > 0 else []
+        self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
+
+    # ---- pieces ---------------------------------------------------------------------------------
+    def _attention(self, li: int, normed, inp: BatchInputs):
+        cfg, sh, lw = self.cfg, self.sh, self.w.layers[li]
+        qkv = ops.linear(normed, lw.wqkv)
+        ops.rope_kv_append(qkv, inp.positions, inp.seq_of_token, inp.block_table, self.cos_sin, self.kv[li],
+                           sh["Hq"], sh["Hkv"], cfg.head_dim)
+        if inp.is_prefill:
+            return ops.attn_prefill(qkv, self.kv[li], inp.block_table, inp.q_start, inp.q_len, inp.seq_lens,
+                                    inp.max_q_len, sh["Hq"], sh["Hkv"], cfg.head_dim)
+        return ops.attn_decode(qkv, self.kv[li], inp.block_table, inp.seq_lens, sh["Hq"], sh["Hkv"], cfg.head_dim,
+                               ctx_hint=inp.ctx_hint)
+
+    def _row_parallel(self, x, w, grouped=None):
+        """Row-parallel projection. Returns (partial [n_src, rows, H], flags, epoch) for the fused reduce."""
+        if self.comm is None or self.comm.size == 1:
+            y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
+            return y.unsqueeze(0), None, None
+        return self.comm.linear_push(x, w, grouped)
+
+    def _ffn(self, li: int, normed):
+        """Returns (partial, flags, epoch, row_idx, row_w) feeding the fused combine/reduce."""
+        cfg, lw = self.cfg, self.w.layers[li]
+        if not cfg.is_moe:
+            h = ops.swiglu_linear(normed, lw.w13)
+            part, flags, epoch = self._row_parallel(h, lw.w2)
+            return part, flags, epoch, None, None
+        T = normed.shape[0]
+        ids, wts, _ = ops.router_topk(normed, lw.router, cfg.top_k)
+        e_local = self.sh["E_local"]
+        counts, offsets, row_of, src_token = ops.router_plan(ids, cfg.num_experts,
+                                                             self.layout.ep_rank * e_local, e_local)
+        xs = ops.gather_rows(normed, src_token)
+        first = self.layout.ep_rank * e_local
+        cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
+        h = ops.grouped_linear(xs, lw.w13, cnt_l, off_l, swiglu=True, rows_hint=T * cfg.top_k)
+        part, flags, epoch = self._row_parallel(h, lw.w2, (cnt_l, off_l))
+        return part, flags, epoch, row_of.view(T, cfg.top_k), wts
+
+    # ---- the step ---------------------------------------------------------------------------------
+    def forward_hidden(self, inp: BatchInputs, hidden_in: torch.Tensor | None = None):
+        """Runs this stage's blocks. Returns (residual stream [T, H], normed [T, H]) where `normed` is the final
+        norm on the last stage and the next stage's first attn_norm input otherwise (None)."""
+        cfg = self.cfg
+        if hidden_in is None:
+            residual = ops.embed(inp.token_ids, self.w.embed)
+        else:
+            residual = hidden_in
+        layers = self.w.layers
+        normed = ops.rmsnorm(residual, layers[0].attn_norm, cfg.rms_norm_eps)
+        last_stage = self.w.final_norm is not None
+        for li, lw in enumerate(layers):
+            attn = self._attention(li, normed, inp)
+            part, flags, epoch = self._row_parallel(attn, lw.wo)
+            residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
+                                                           flags=flags, epoch=epoch)
+            part, flags, epoch, row_idx, row_w = self._ffn(li, normed)
+            if li + 1 < len(layers):
+                next_gamma = layers[li + 1].attn_norm
+            else:
+                next_gamma = self.w.final_norm if last_stage else None
+            residual, normed = ops.reduce_residual_rmsnorm(residual, part, next_gamma, cfg.rms_norm_eps, row_idx,
+                                                           row_w, flags=flags, epoch=epoch)
+            if self.capture_hidden is not None:
+                self.capture_hidden.append(residual.detach().float().cpu())
+        return residual, normed
+
+    def logits(self, normed, inp: BatchInputs):
+        """Logits of this rank's vocabulary shard for the rows that need them."""
+        if inp.is_prefill and inp.logit_rows is not None:
+            normed = normed.index_select(0, inp.logit_rows).contiguous()
+        return ops.linear(normed, self.w.lm_head)
+
+    def forward(self, inp: BatchInputs, hidden_in=None):
+        """Full step on a single stage: returns (greedy tokens int32 [rows], logits shard)."""
+        _, normed = self.forward_hidden(inp, hidden_in)
+        lg = self.logits(normed, inp)
+        if self.comm is not None and self.comm.size > 1:
+            tok = self.comm.vocab_parallel_argmax(lg, self.sh["V_local"])
+        else:
+            tok = ops.sample_argmax(lg)
+        return tok, lg

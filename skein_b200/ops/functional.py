@@ -380,3 +380,20 @@ def quant_fp8_block128(x):
     _lib.check(rc, "quant_fp8_block128")
     _lib.count_launch()
     return q, s
+
+
+def advance_decode_state(sampled, tokens, positions, seq_lens, step_counter=None):
+    """tokens <- sampled, positions += 1, seq_lens += 1 for live rows (device-side token feedback)."""
+    if not sampled.is_cuda:
+        live = seq_lens > 0
+        tokens[live] = sampled[live]
+        positions[live] += 1
+        seq_lens[live] += 1
+        if step_counter is not None:
+            step_counter += 1
+        return
+    rc = _lib.lib().skein_advance_decode_state(sampled.data_ptr(), tokens.data_ptr(), positions.data_ptr(),
+                                               seq_lens.data_ptr(), sampled.shape[0], _lib.ptr(step_counter),
+                                               _lib.stream_ptr())
+    _lib.check(rc, "advance_decode_state")
+    _lib.count_launch()

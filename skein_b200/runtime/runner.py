@@ -1,0 +1,160 @@
+"""ModelRunner: static step buffers, CUDA-graph capture per batch bucket, prefill chunks.
+
+The decode step of one batch bucket is captured once into a CUDA graph (every kernel of the step,
+sampling included) and replayed. A step's host inputs travel in ONE pinned buffer and ONE
+host-to-device copy:
+
+    [ token ids B | positions B | seq_lens B | block table B x max_blocks ]      (int32)
+
+and its result in one device-to-host copy: [ sampled tokens B | device status word 2 ].
+
+Capture classes are padded batch sizes (the reference keys its full-step captures per micro-batch:
+crates/skein_runtime/src/distributed/gpu_rank.rs:466-555; its dispatcher for capture classes is a
+stub: crates/skein_runtime/src/dispatch/mod.rs:48-58). Padding rows carry position -1 / seq_len 0
+and are skipped by the kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..models.decoder import BatchInputs, Decoder
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def bucket_for(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    raise ValueError(f"batch {n} exceeds the largest capture class {BUCKETS[-1]}")
+
+
+class _Bucket:
+    def __init__(self, B: int, max_blocks: int, device):
+        self.B, self.max_blocks = B, max_blocks
+        n_in = 3 * B + B * max_blocks
+        pin = device.type == "cuda"
+        self.host_in = torch.zeros(n_in, dtype=torch.int32, pin_memory=pin)
+        self.dev_in = torch.zeros(n_in, dtype=torch.int32, device=device)
+        self.host_out = torch.zeros(B + 2, dtype=torch.int32, pin_memory=pin)
+        self.dev_out = torch.zeros(B + 2, dtype=torch.int32, device=device)
+        self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.graph = None          # one step, host-fed
+        self.graph_loop = None     # one step + device-side token feedback
+        self.host_in[B:2 * B] = -1
+
+    def views(self, buf):
+        B, mb = self.B, self.max_blocks
+        return buf[:B], buf[B:2 * B], buf[2 * B:3 * B], buf[3 * B:].view(B, mb)
+
+    @property
+    def h2d_bytes(self):
+        return self.host_in.numel() * 4
+
+    @property
+    def d2h_bytes(self):
+        return self.host_out.numel() * 4
+
+
+class ModelRunner:
+    def __init__(self, decoder: Decoder, max_blocks_per_seq: int, use_graphs: bool = True, ctx_hint: int = 1024):
+        self.dec = decoder
+        self.device = decoder.device
+        self.max_blocks = max_blocks_per_seq
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.ctx_hint = ctx_hint
+        self.buckets: dict[int, _Bucket] = {}
+        self.graph_captures = 0
+        self.graph_replays = 0
+
+    # ---- decode -----------------------------------------------------------------------------------
+    def bucket(self, n: int) -> _Bucket:
+        B = bucket_for(n)
+        bk = self.buckets.get(B)
+        if bk is None:
+            bk = self.buckets[B] = _Bucket(B, self.max_blocks, self.device)
+        return bk
+
+    def _decode_body(self, bk: _Bucket, feedback: bool):
+        tok, pos, lens, bt = bk.views(bk.dev_in)
+        inp = BatchInputs(token_ids=tok, positions=pos, block_table=bt, seq_lens=lens, ctx_hint=self.ctx_hint)
+        sampled, _ = self.dec.forward(inp)
+        bk.dev_out[:bk.B].copy_(sampled)
+        if self.device.type == "cuda":
+            bk.dev_out[bk.B:].copy_(ops.workspace().status)
+        if feedback:
+            ops.advance_decode_state(sampled, tok, pos, lens, bk.step_counter)
+
+    def _ensure_graph(self, bk: _Bucket, feedback: bool):
+        attr = "graph_loop" if feedback else "graph"
+        if getattr(bk, attr) is not None:
+            return getattr(bk, attr)
+        # eager warm-up allocates workspaces and descriptor caches outside the capture
+        saved = bk.dev_in.clone()
+        self._decode_body(bk, False)
+        torch.cuda.synchronize()
+        bk.dev_in.copy_(saved)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._decode_body(bk, feedback)
+        torch.cuda.synchronize()
+        bk.dev_in.copy_(saved)  # the capture itself does not run, but keep the inputs pristine
+        self.graph_captures += 1
+        setattr(bk, attr, g)
+        return g
+
+    def load_decode_inputs(self, bk: _Bucket, tokens, positions, seq_lens, block_tables):
+        """Fill the pinned staging buffer from host lists (rows beyond len(tokens) are padding)."""
+        n = len(tokens)
+        t, p, l, bt = bk.views(bk.host_in)
+        t.zero_(); p.fill_(-1); l.zero_()
+        t[:n] = torch.as_tensor(tokens, dtype=torch.int32)
+        p[:n] = torch.as_tensor(positions, dtype=torch.int32)
+        l[:n] = torch.as_tensor(seq_lens, dtype=torch.int32)
+        for i, row in enumerate(block_tables):
+            bt[i, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+
+    def decode_step(self, bk: _Bucket, sync: bool = True):
+        """H2D of the staged inputs, one step, D2H of the result. Returns the host result view."""
+        bk.dev_in.copy_(bk.host_in, non_blocking=True)
+        if self.use_graphs:
+            self._ensure_graph(bk, False).replay()
+            self.graph_replays += 1
+        else:
+            self._decode_body(bk, False)
+        bk.host_out.copy_(bk.dev_out, non_blocking=True)
+        if sync and self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+            if int(bk.host_out[bk.B]) != 0:
+                ops.workspace().check_status()
+        return bk.host_out[:bk.B]
+
+    def decode_loop_step(self, bk: _Bucket):
+        """One step with device-side token feedback (no host traffic). Inputs must already be on the device."""
+        if self.use_graphs:
+            self._ensure_graph(bk, True).replay()
+            self.graph_replays += 1
+        else:
+            self._decode_body(bk, True)
+
+    # ---- prefill ----------------------------------------------------------------------------------
+    def prefill(self, seqs, want_logits: bool = False):
+        """seqs: list of (new_token_ids, block_table_row, cached_len). Runs one eager chunk holding every new
+        token of every listed sequence. Returns greedy next tokens (host list) [and logits]."""
+        dev = self.device
+        toks, pos, sot, qs, ql, kl, rows = [], [], [], [], [], [], []
+        S = len(seqs)
+        bt = torch.zeros(S, self.max_blocks, dtype=torch.int32)
+        for s, (ids, table, cached) in enumerate(seqs):
+            qs.append(len(toks)); ql.append(len(ids)); kl.append(cached + len(ids))
+            toks.extend(ids); pos.extend(range(cached, cached + len(ids))); sot.extend([s] * len(ids))
+            rows.append(len(toks) - 1)
+            bt[s, :len(table)] = torch.as_tensor(table, dtype=torch.int32)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        inp = BatchInputs(token_ids=i32(toks), positions=i32(pos), block_table=bt.to(dev), seq_lens=i32(kl),
+                          is_prefill=True, seq_of_token=i32(sot), q_start=i32(qs), q_len=i32(ql), max_q_len=max(ql),
+                          logit_rows=torch.tensor(rows, dtype=torch.int64, device=dev))
+        tok, lg = self.dec.forward(inp)
+        out = tok.cpu().tolist()
+        return (out, lg) if want_logits else out
