@@ -175,8 +175,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t full = smem_u32(&bar_full[s]);
             const uint32_t st = smem_base + s * a.stage_bytes;
             mbar_expect_tx(full, tx_bytes);
-            tma_load_2d(st, &tmW, full, kb * k_elems, w_row, pol_w);
-            if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, full, kb * k_elems, w_row + p.up_row_off, pol_w);
+            if (p.w_packed) {
+              // tile-packed weights: tile (row tile, kb) is one contiguous 16 KB block
+              tma_load_2d(st, &tmW, full, 0, ((w_row / TILE_F) * KB + kb) * TILE_F, pol_w);
+              if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, full, 0, (((w_row + p.up_row_off) / TILE_F) * KB + kb) * TILE_F, pol_w);
+            } else {
+              tma_load_2d(st, &tmW, full, kb * k_elems, w_row, pol_w);
+              if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, full, kb * k_elems, w_row + p.up_row_off, pol_w);
+            }
             tma_load_2d(st + (DUAL ? 2 : 1) * W_TILE_BYTES, &tmX, full, kb * k_elems, x_row, pol_x);
           }
           pos = (long long)u * KB + kb1;
@@ -540,7 +546,13 @@ extern "C" int skein_gemm_ws(const SkeinGemmParams* p, void* stream) {
   if (!p->workspace || !p->counters) return -8;
   CUtensorMap tmW, tmX;
   const int eb = p->fp8 ? 1 : 2;
-  rc = cached_tmap_2d(&tmW, p->W, (uint64_t)p->G * p->w_rows_per_group, p->K, eb, TILE_F);
+  if (p->w_packed) {
+    if (p->w_rows_per_group % TILE_F != 0 || (p->mode == 1 && p->up_row_off % TILE_F != 0)) return -9;
+    const uint64_t tiles = (uint64_t)p->G * (p->w_rows_per_group / TILE_F) * (p->K / (p->fp8 ? 128 : 64));
+    rc = cached_tmap_2d(&tmW, p->W, tiles * TILE_F, p->fp8 ? 128 : 64, eb, TILE_F);
+  } else {
+    rc = cached_tmap_2d(&tmW, p->W, (uint64_t)p->G * p->w_rows_per_group, p->K, eb, TILE_F);
+  }
   if (rc) return rc;
   rc = cached_tmap_2d(&tmX, p->X, p->x_rows, p->K, eb, p->n_tile);
   if (rc) return rc;

@@ -42,6 +42,7 @@ typedef struct SkeinGemmParams {
   int32_t stages;           // 0 -> as many as fit
   int32_t grid;             // 0 -> number of SMs
   int32_t wait_budget_ms;   // 0 -> 2000
+  int32_t w_packed;         // W is stored tile by tile: [rows/128][K/64 (or /128 fp8)][128][128 bytes]
 } SkeinGemmParams;
 
 // Returns 0 or a cudaError_t / negative argument-error code.

@@ -82,7 +82,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const __nv_bfloat16* _
       ids[j] = best; vals[j] = bv;
     }
     float den = 0.f;
-    for (int j = 0; j < topk; ++j) { vals[j] = __expf(vals[j] - vals[0]); den += vals[j]; }
+    const float vmax = vals[0];  // selections come out in descending order
+    for (int j = 0; j < topk; ++j) { vals[j] = __expf(vals[j] - vmax); den += vals[j]; }
     for (int j = 0; j < topk; ++j) {
       expert_ids[t * topk + j] = ids[j];
       expert_w[t * topk + j] = vals[j] / den;

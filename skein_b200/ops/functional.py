@@ -108,6 +108,47 @@ def _base_params(x, w2d, out, F, K, n_tile, mode) -> "_lib.GemmParams":
     return p
 
 
+class PackedWeight:
+    """A weight matrix re-laid for streaming: [groups, rows/128, K/64, 128, 64] bf16, so that each
+    128 x 64 tile the GEMM loads is one contiguous 16 KB block and a CTA's K loop walks consecutive
+    memory. `shape` keeps the logical [groups?, rows, K]."""
+
+    def __init__(self, data: torch.Tensor, shape):
+        self.data, self.shape = data, tuple(shape)
+        self.device, self.dtype = data.device, data.dtype
+
+    @property
+    def is_cuda(self):
+        return self.data.is_cuda
+
+    def data_ptr(self):
+        return self.data.data_ptr()
+
+    def unpack(self) -> torch.Tensor:
+        *g, R, K = self.shape
+        G = g[0] if g else 1
+        t = self.data.view(G, R // 128, K // 64, 128, 64).permute(0, 1, 3, 2, 4).reshape(G, R, K)
+        return t if g else t[0]
+
+
+def pack_weight(w: torch.Tensor) -> PackedWeight:
+    """[rows, K] or [G, rows, K] (rows % 128 == 0, K % 64 == 0) -> PackedWeight."""
+    shape = tuple(w.shape)
+    R, K = shape[-2], shape[-1]
+    if R % 128 or K % 64:
+        raise ValueError("pack_weight needs rows % 128 == 0 and K % 64 == 0")
+    G = shape[0] if w.dim() == 3 else 1
+    t = w.reshape(G, R // 128, 128, K // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
+    return PackedWeight(t, shape)
+
+
+def _wview(w):
+    """(2-D view or packed data, rows per group, packed flag)."""
+    if isinstance(w, PackedWeight):
+        return w.data, w.shape[-2], 1
+    return (w.view(-1, w.shape[-1]) if w.dim() == 3 else w), w.shape[-2], 0
+
+
 def _check_act(x):
     if x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("activations must be contiguous bf16")
@@ -116,7 +157,7 @@ def _check_act(x):
 def linear(x, w, out=None, residual=None, n_tile=None):
     """y[t, f] = sum_k x[t, k] w[f, k] (+ residual[t, f])."""
     if not x.is_cuda:
-        y = ref.linear(x, w, residual)
+        y = ref.linear(x, w.unpack() if isinstance(w, PackedWeight) else w, residual)
         if out is not None:
             out.copy_(y)
             return out
@@ -128,7 +169,9 @@ def linear(x, w, out=None, residual=None, n_tile=None):
         out = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    p = _base_params(x, w, out, F, K, n_tile or pick_n_tile(T, False), 0)
+    wv, _, packed = _wview(w)
+    p = _base_params(x, wv, out, F, K, n_tile or pick_n_tile(T, False), 0)
+    p.w_rows_per_group, p.w_packed = F, packed
     if residual is not None:
         p.residual = residual.data_ptr()
     _gemm_launch(p, "linear")
@@ -138,7 +181,7 @@ def linear(x, w, out=None, residual=None, n_tile=None):
 def swiglu_linear(x, w13, out=None, n_tile=None):
     """silu(x @ w13[:I].T) * (x @ w13[I:].T) with both products from one pass over x."""
     if not x.is_cuda:
-        return ref.swiglu_linear(x, w13)
+        return ref.swiglu_linear(x, w13.unpack() if isinstance(w13, PackedWeight) else w13)
     _check_act(x)
     T, K = x.shape
     inter = w13.shape[0] // 2
@@ -146,7 +189,9 @@ def swiglu_linear(x, w13, out=None, n_tile=None):
         out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    p = _base_params(x, w13, out, inter, K, n_tile or pick_n_tile(T, True), 1)
+    wv, rows_pg, packed = _wview(w13)
+    p = _base_params(x, wv, out, inter, K, n_tile or pick_n_tile(T, True), 1)
+    p.w_rows_per_group, p.w_packed = rows_pg, packed
     p.up_row_off = inter
     _gemm_launch(p, "swiglu_linear")
     return out
@@ -160,7 +205,7 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
     offsets[e] : offsets[e] + counts[e]. Rows not covered by any expert are left untouched.
     """
     if not xs.is_cuda:
-        return ref.grouped_linear(xs, w, counts, offsets, swiglu)
+        return ref.grouped_linear(xs, w.unpack() if isinstance(w, PackedWeight) else w, counts, offsets, swiglu)
     _check_act(xs)
     rows, K = xs.shape
     E = w.shape[0]
@@ -172,9 +217,10 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
     if n_tile is None:
         avg = (rows_hint if rows_hint is not None else rows) / E
         n_tile = pick_n_tile(int(math.ceil(avg * 1.5)), swiglu)
-    p = _base_params(xs, w.view(E * w.shape[1], K), out, F, K, n_tile, 1 if swiglu else 0)
+    wv, rows_pg, packed = _wview(w)
+    p = _base_params(xs, wv, out, F, K, n_tile, 1 if swiglu else 0)
     p.G = E
-    p.w_rows_per_group = w.shape[1]
+    p.w_rows_per_group, p.w_packed = rows_pg, packed
     p.up_row_off = F if swiglu else 0
     p.group_off = offsets.data_ptr()
     p.group_cnt = counts.data_ptr()
