@@ -133,20 +133,35 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
 #pragma unroll
       for (int i = 0; i < 8; ++i) o_acc[g][i] *= alpha[g];
     const int n_valid = min(AD_CHUNK, t_end - c0);
-    for (int t = tph; t < n_valid; t += 8) {
-      const int tk2 = c0 + t;
-      const __nv_bfloat16* vp = p.kv + (((size_t)page_s[t] * 2 + 1) * p.Hkv + kvh) * head_stride +
-                                (size_t)(tk2 % ps) * AD_D + dgrp * 8;
-      const uint4 raw = *reinterpret_cast<const uint4*>(vp);
-      const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      float vf[8];
+    // 8 V rows are requested before any is used, so 8 x 16 bytes are in flight per thread
+#pragma unroll 1
+    for (int tb = tph; tb < n_valid; tb += 64) {
+      uint4 raw[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(vb[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y; }
+      for (int u = 0; u < 8; ++u) {
+        const int t = tb + u * 8;
+        raw[u] = make_uint4(0, 0, 0, 0);
+        if (t < n_valid) {
+          const __nv_bfloat16* vp = p.kv + (((size_t)page_s[t] * 2 + 1) * p.Hkv + kvh) * head_stride +
+                                    (size_t)((c0 + t) % ps) * AD_D + dgrp * 8;
+          raw[u] = *reinterpret_cast<const uint4*>(vp);
+        }
+      }
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pr = s_s[g][t];
+      for (int u = 0; u < 8; ++u) {
+        const int t = tb + u * 8;
+        if (t < n_valid) {
+          const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+          float vf[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o_acc[g][i] += pr * vf[i];
+          for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(vb[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y; }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pr = s_s[g][t];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o_acc[g][i] += pr * vf[i];
+          }
+        }
       }
     }
     __syncthreads();

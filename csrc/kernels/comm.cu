@@ -1,0 +1,184 @@
+// Peer-memory plumbing and the small stand-alone collectives.
+//
+//   * symmetric heap: every rank cudaMallocs one heap and exports a CUDA IPC handle; peers map it,
+//     so kernels address a peer's buffer with plain loads/stores that travel over NVLink.
+//   * push_rows: one-shot "all-gather of partials": copy a local buffer into this rank's slot of every
+//     peer's buffer and publish this rank's flag there. Followed by reduce_residual_rmsnorm (norm.cu)
+//     it is a one-shot all-reduce; the fused path does the same push from the GEMM epilogue.
+//   * argmax_push: vocabulary-parallel greedy sampling. Each rank reduces its logit shard to one
+//     (value, global index) pair per row and pushes 8 bytes per row to every peer
+//     (merge_candidates in sample.cu picks the winner).
+//   * copy_pages: KV pages to (or from) a peer's cache, for prefill/decode disaggregation.
+// Flags carry monotonically increasing epochs kept in device memory, so the same launches replay
+// inside a CUDA graph. Every wait on a flag is bounded (ptx.cuh: wait_flag_ge).
+//
+// Replaces the reference's NCCL all-reduce + copy-back (crates/skein_runtime/src/cuda/nccl.rs:196-245),
+// its 2-rank host-shared-memory all-reduce with an unbounded spin (crates/skein_runtime/src/cuda/
+// shm_allreduce.rs:24-69), the logits all-gather (nccl.rs:251-298) and the host-staged KV block
+// transport (nccl.rs:504-588).
+#include "ptx.cuh"
+#include <cuda_bf16.h>
+#include <math.h>
+#include <string.h>
+
+namespace skein {
+
+constexpr int MAXP = 8;
+
+struct PeerPtrs {
+  void* dst[MAXP];
+  int* flag[MAXP];
+  int n;
+};
+
+// Publishes epoch+1 on every peer once all CTAs of the launch have finished their stores.
+__device__ __forceinline__ void publish_when_all_done(const PeerPtrs& pp, int* epoch, int* done_counter) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y * gridDim.z;
+    const int old = atomicAdd(done_counter, 1);
+    if (old == total - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      const int e = *epoch + 1;
+      for (int i = 0; i < pp.n; ++i) st_release_sys(pp.flag[i], e);
+      *epoch = e;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) push_rows_kernel(const uint4* __restrict__ src, long long n_vec, PeerPtrs pp,
+                                                         int* epoch, int* done_counter) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int p = 0; p < pp.n; ++p) reinterpret_cast<uint4*>(pp.dst[p])[i] = v;
+  }
+  publish_when_all_done(pp, epoch, done_counter);
+}
+
+struct ValIdx { float v; int i; };
+__device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+// grid = B rows, 1024 threads. val_dst[p] / idx_dst[p] point at this rank's [B] slot on peer p.
+struct CandPtrs {
+  float* val[MAXP];
+  int* idx[MAXP];
+};
+__global__ void __launch_bounds__(1024) argmax_push_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int V,
+                                                            int idx_offset, CandPtrs cp, PeerPtrs pp, int* epoch,
+                                                            int* done_counter) {
+  __shared__ ValIdx sh[32];
+  const int b = blockIdx.x;
+  const __nv_bfloat16* row = logits + (size_t)b * ld;
+  ValIdx best{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = __bfloat162float(row[i]);
+    if (v > best.v) { best.v = v; best.i = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    ValIdx y{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, y);
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) sh[w] = best;
+  __syncthreads();
+  if (w == 0) {
+    ValIdx r = sh[l];
+    for (int o = 16; o > 0; o >>= 1) {
+      ValIdx y{__shfl_xor_sync(0xffffffffu, r.v, o), __shfl_xor_sync(0xffffffffu, r.i, o)};
+      r = better(r, y);
+    }
+    if (l == 0) {
+      for (int p = 0; p < pp.n; ++p) { cp.val[p][b] = r.v; cp.idx[p][b] = r.i + idx_offset; }
+    }
+  }
+  publish_when_all_done(pp, epoch, done_counter);
+}
+
+// One CTA per page: dst_cache[dst_page[i]] = src_cache[src_page[i]] (either side may be peer memory).
+__global__ void __launch_bounds__(256) copy_pages_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                          const int* __restrict__ src_page, const int* __restrict__ dst_page,
+                                                          long long vec_per_page) {
+  const uint4* s = src + (long long)src_page[blockIdx.x] * vec_per_page;
+  uint4* d = dst + (long long)dst_page[blockIdx.x] * vec_per_page;
+  for (long long i = threadIdx.x; i < vec_per_page; i += blockDim.x) d[i] = s[i];
+}
+
+// A wait that nothing satisfies within its budget: used to test the timeout path without a fault.
+__global__ void wait_flag_kernel(const int* flag, int epoch, unsigned long long budget_ns, int* status) {
+  if (!wait_flag_ge(flag, epoch, budget_ns)) report_status(status, ST_TIMEOUT_PEER_FLAG, 0);
+}
+
+}  // namespace skein
+
+// ---- IPC heap -----------------------------------------------------------------------------------
+extern "C" int skein_ipc_alloc(void** ptr, long long bytes) {
+  cudaError_t e = cudaMalloc(ptr, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(*ptr, 0, (size_t)bytes);
+}
+extern "C" int skein_ipc_free(void* ptr) { return (int)cudaFree(ptr); }
+extern "C" int skein_ipc_get_handle(void* ptr, void* handle_out_64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle_out_64, &h, sizeof(h));
+  return 0;
+}
+extern "C" int skein_ipc_open(const void* handle_64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+extern "C" int skein_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
+extern "C" int skein_ipc_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+// ---- collectives ----------------------------------------------------------------------------------
+extern "C" int skein_push_rows(const void* src, long long bytes, void* const* peer_dst, int* const* peer_flag,
+                               int n_peers, int* epoch, int* done_counter, void* stream) {
+  using namespace skein;
+  if (bytes % 16 != 0 || n_peers < 1 || n_peers > MAXP) return -1;
+  PeerPtrs pp;
+  pp.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) { pp.dst[i] = peer_dst[i]; pp.flag[i] = peer_flag[i]; }
+  const long long n_vec = bytes / 16;
+  int grid = (int)((n_vec + 255) / 256);
+  if (grid > 296) grid = 296;
+  if (grid < 1) grid = 1;
+  push_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, n_vec, pp, epoch, done_counter);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int skein_argmax_push(const void* logits, long long ld, int B, int V, int idx_offset, float* const* peer_val,
+                                 int* const* peer_idx, int* const* peer_flag, int n_peers, int* epoch,
+                                 int* done_counter, void* stream) {
+  using namespace skein;
+  if (B == 0) return 0;
+  if (n_peers < 1 || n_peers > MAXP) return -1;
+  CandPtrs cp;
+  PeerPtrs pp;
+  pp.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) { cp.val[i] = peer_val[i]; cp.idx[i] = peer_idx[i]; pp.flag[i] = peer_flag[i]; pp.dst[i] = nullptr; }
+  argmax_push_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V, idx_offset, cp, pp,
+                                                           epoch, done_counter);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int skein_copy_pages(const void* src_cache, void* dst_cache, const int* src_page, const int* dst_page,
+                                int n_pages, long long page_bytes, void* stream) {
+  if (n_pages == 0) return 0;
+  if (page_bytes % 16 != 0) return -1;
+  skein::copy_pages_kernel<<<n_pages, 256, 0, (cudaStream_t)stream>>>((const uint4*)src_cache, (uint4*)dst_cache,
+                                                                      src_page, dst_page, page_bytes / 16);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int skein_wait_flag(const int* flag, int epoch, int budget_ms, int* status, void* stream) {
+  skein::wait_flag_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag, epoch, (unsigned long long)budget_ms * 1000000ull,
+                                                             status);
+  return (int)cudaGetLastError();
+}

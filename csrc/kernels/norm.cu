@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(512) reduce_residual_rmsnorm_kernel(const Norm
       const int nk = p.topk > 0 ? p.topk : 1;
       for (int j = 0; j < nk; ++j) {
         const int row = p.row_idx ? p.row_idx[b * p.topk + j] : b;
+        if (row < 0) continue;  // pair routed to an expert that lives on another rank
         const float w = p.row_w ? p.row_w[b * p.topk + j] : 1.f;
         for (int s = 0; s < p.n_src; ++s) {
           const __nv_bfloat16* src = p.partial + (size_t)s * p.src_stride + (size_t)row * p.H + h;

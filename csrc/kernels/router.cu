@@ -23,33 +23,44 @@ namespace skein {
 constexpr int RT_MAX_E = 64;
 constexpr int RT_MAX_K = 8;
 
-// grid = T tokens, 128 threads.
-__global__ void __launch_bounds__(128) router_topk_kernel(const __nv_bfloat16* __restrict__ x,
+__device__ void router_plan_body(const int* __restrict__ expert_ids, int n_pairs, int E, int topk,
+                                 int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
+                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s);
+
+// grid = T tokens, 512 threads: thread i owns 8 consecutive elements of the hidden vector per pass, so
+// every load of a pass is issued before the first is consumed. The last CTA to finish also lays out
+// the expert-sorted order (router_plan_body), which saves a launch on the decode path.
+__global__ void __launch_bounds__(512) router_topk_kernel(const __nv_bfloat16* __restrict__ x,
                                                            const __nv_bfloat16* __restrict__ wg, int T, int H, int E,
                                                            int topk, int* __restrict__ expert_ids,
-                                                           float* __restrict__ expert_w, float* __restrict__ logits_out) {
-  __shared__ float part[4][RT_MAX_E];
+                                                           float* __restrict__ expert_w, float* __restrict__ logits_out,
+                                                           int* counts, int* offsets, int* row_of, int* src_token,
+                                                           int e_first, int e_count, int* done_counter) {
+  __shared__ float part[16][RT_MAX_E];
   __shared__ float logit[RT_MAX_E];
+  __shared__ int cnt_s[RT_MAX_E];
+  __shared__ int off_s[RT_MAX_E + 1];
+  __shared__ int is_last;
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float acc[RT_MAX_E / 8];  // experts are processed 8 at a time to bound registers
   for (int e0 = 0; e0 < E; e0 += 8) {
     float a[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) a[i] = 0.f;
-    for (int h = tid * 8; h < H; h += 128 * 8) {
+    for (int h = tid * 8; h < H; h += 512 * 8) {
       const uint4 xr = *reinterpret_cast<const uint4*>(x + (size_t)t * H + h);
+      uint4 wr[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        wr[i] = (e0 + i < E) ? *reinterpret_cast<const uint4*>(wg + (size_t)(e0 + i) * H + h) : make_uint4(0, 0, 0, 0);
       const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xr);
       float xf[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(xb[i]); xf[2 * i] = f.x; xf[2 * i + 1] = f.y; }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        if (e0 + i < E) {
-          const uint4 wr = *reinterpret_cast<const uint4*>(wg + (size_t)(e0 + i) * H + h);
-          const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wr);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wr[i]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wb[j]); a[i] += xf[2 * j] * f.x + xf[2 * j + 1] * f.y; }
-        }
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wb[j]); a[i] += xf[2 * j] * f.x + xf[2 * j + 1] * f.y; }
       }
     }
 #pragma unroll
@@ -59,11 +70,12 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const __nv_bfloat16* _
       if (lane == 0 && e0 + i < E) part[warp][e0 + i] = v;
     }
   }
-  (void)acc;
   __syncthreads();
   if (tid < E) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) v += part[w][tid];
     // the router projection is a bf16 linear layer: round like one
-    const float v = part[0][tid] + part[1][tid] + part[2][tid] + part[3][tid];
     logit[tid] = __bfloat162float(__float2bfloat16(v));
     if (logits_out) logits_out[(size_t)t * E + tid] = logit[tid];
   }
@@ -88,23 +100,32 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const __nv_bfloat16* _
       expert_ids[t * topk + j] = ids[j];
       expert_w[t * topk + j] = vals[j] / den;
     }
+    int last = 0;
+    if (done_counter != nullptr) {
+      __threadfence();
+      const int old = atomicAdd(done_counter, 1);
+      last = (old == (int)gridDim.x - 1);
+      if (last) *done_counter = 0;
+    }
+    is_last = last;
   }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  router_plan_body(expert_ids, T * topk, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s);
 }
 
-// One CTA, E warps (E <= 32). n_pairs = T * topk.
-__global__ void __launch_bounds__(1024) router_plan_kernel(const int* __restrict__ expert_ids, int n_pairs, int E,
-                                                            int topk, int* __restrict__ counts, int* __restrict__ offsets,
-                                                            int* __restrict__ row_of, int* __restrict__ src_token,
-                                                            int e_first, int e_count) {
-  // Experts outside [e_first, e_first + e_count) get count 0 (expert parallelism: not ours).
-  __shared__ int cnt_s[RT_MAX_E];
-  __shared__ int off_s[RT_MAX_E + 1];
+// One CTA; one warp per expert walks the (token, slot) pairs in order. n_pairs = T * topk.
+// Experts outside [e_first, e_first + e_count) get count 0 (expert parallelism: not ours).
+__device__ void router_plan_body(const int* __restrict__ expert_ids, int n_pairs, int E, int topk,
+                                 int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
+                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarps) {
     int c = 0;
     for (int i0 = 0; i0 < n_pairs; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < n_pairs && expert_ids[i] == e;
+      const bool hit = i < n_pairs && __ldcg(expert_ids + i) == e;
       c += __popc(__ballot_sync(0xffffffffu, hit));
     }
     if (lane == 0) cnt_s[e] = (e >= e_first && e < e_first + e_count) ? c : 0;
@@ -123,7 +144,7 @@ __global__ void __launch_bounds__(1024) router_plan_kernel(const int* __restrict
     int base = off_s[e];
     for (int i0 = 0; i0 < n_pairs; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < n_pairs && expert_ids[i] == e;
+      const bool hit = i < n_pairs && __ldcg(expert_ids + i) == e;
       const unsigned bal = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         if (mine) {
@@ -139,15 +160,28 @@ __global__ void __launch_bounds__(1024) router_plan_kernel(const int* __restrict
   }
 }
 
+__global__ void __launch_bounds__(1024) router_plan_kernel(const int* __restrict__ expert_ids, int n_pairs, int E,
+                                                            int topk, int* __restrict__ counts, int* __restrict__ offsets,
+                                                            int* __restrict__ row_of, int* __restrict__ src_token,
+                                                            int e_first, int e_count) {
+  __shared__ int cnt_s[RT_MAX_E];
+  __shared__ int off_s[RT_MAX_E + 1];
+  router_plan_body(expert_ids, n_pairs, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s);
+}
+
 }  // namespace skein
 
+// With done_counter (a zeroed device int) the same launch also produces the expert-sorted layout
+// (counts[E], offsets[E+1], row_of[T*topk], src_token[T*topk]); without it only ids and weights.
 extern "C" int skein_router_topk(const void* x, const void* wg, int T, int H, int E, int topk, int* expert_ids,
-                                 float* expert_w, float* logits_out, void* stream) {
+                                 float* expert_w, float* logits_out, int* counts, int* offsets, int* row_of,
+                                 int* src_token, int e_first, int e_count, int* done_counter, void* stream) {
   using namespace skein;
   if (T == 0) return 0;
   if (E > RT_MAX_E || topk > RT_MAX_K || topk > E || H % 8 != 0) return -1;
-  router_topk_kernel<<<T, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, T, H, E,
-                                                          topk, expert_ids, expert_w, logits_out);
+  router_topk_kernel<<<T, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, T, H, E,
+                                                          topk, expert_ids, expert_w, logits_out, counts, offsets,
+                                                          row_of, src_token, e_first, e_count, done_counter);
   return (int)cudaGetLastError();
 }
 

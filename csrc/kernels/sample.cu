@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(1024) sample_argmax_kernel(const __nv_bfloat16
   }
 }
 
-// cand_val / cand_idx: [n_src][B]; the winner is the largest value, ties -> lowest global index.
-__global__ void merge_candidates_kernel(const float* cand_val, const int* cand_idx, int n_src, int B,
+// cand_val / cand_idx: [n_src][stride] (first B of each row used); the winner is the largest value, ties -> lowest global index.
+__global__ void merge_candidates_kernel(const float* cand_val, const int* cand_idx, int n_src, int B, int stride,
                                         const int* flags, const int* epoch, int* status, unsigned long long budget_ns,
                                         int* __restrict__ out_idx) {
   __shared__ int failed;
@@ -83,8 +83,8 @@ __global__ void merge_candidates_kernel(const float* cand_val, const int* cand_i
     ValIdx best{-INFINITY, 0x7fffffff};
     for (int s = 0; s < n_src; ++s) {
       ValIdx c;
-      c.v = __ldcg(cand_val + (size_t)s * B + b);
-      c.i = __ldcg(cand_idx + (size_t)s * B + b);
+      c.v = __ldcg(cand_val + (size_t)s * stride + b);
+      c.i = __ldcg(cand_idx + (size_t)s * stride + b);
       best = better(best, c);
     }
     out_idx[b] = best.i;
@@ -184,11 +184,11 @@ extern "C" int skein_sample_argmax(const void* logits, long long ld, int B, int 
   return (int)cudaGetLastError();
 }
 
-extern "C" int skein_merge_candidates(const float* cand_val, const int* cand_idx, int n_src, int B, const int* flags,
+extern "C" int skein_merge_candidates(const float* cand_val, const int* cand_idx, int n_src, int B, int stride, const int* flags,
                                       const int* epoch, int* status, int wait_budget_ms, int* out_idx, void* stream) {
   if (B == 0) return 0;
   const unsigned long long budget = (unsigned long long)(wait_budget_ms > 0 ? wait_budget_ms : 10000) * 1000000ull;
-  skein::merge_candidates_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cand_val, cand_idx, n_src, B, flags, epoch, status,
+  skein::merge_candidates_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cand_val, cand_idx, n_src, B, stride, flags, epoch, status,
                                                                       budget, out_idx);
   return (int)cudaGetLastError();
 }

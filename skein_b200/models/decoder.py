@@ -152,12 +152,10 @@ class Decoder:
             part, flags, epoch = self._row_parallel(h, lw.w2)
             return part, flags, epoch, None, None
         T = normed.shape[0]
-        ids, wts, _ = ops.router_topk(normed, lw.router, cfg.top_k)
         e_local = self.sh["E_local"]
-        counts, offsets, row_of, src_token = ops.router_plan(ids, cfg.num_experts,
-                                                             self.layout.ep_rank * e_local, e_local)
-        xs = ops.gather_rows(normed, src_token)
         first = self.layout.ep_rank * e_local
+        ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
+        xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
         cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
         h = ops.grouped_linear(xs, lw.w13, cnt_l, off_l, swiglu=True, rows_hint=T * cfg.top_k)
         part, flags, epoch = self._row_parallel(h, lw.w2, (cnt_l, off_l))

@@ -77,13 +77,24 @@ def lib():
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_prefill", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
-    _sig(L, "skein_router_topk", i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp])
+    _sig(L, "skein_router_topk", i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp])
     _sig(L, "skein_router_plan", i32, [vp, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp])
     _sig(L, "skein_sample_argmax", i32, [vp, i64, i32, i32, i32, vp, vp, vp])
-    _sig(L, "skein_merge_candidates", i32, [vp, vp, i32, i32, vp, vp, vp, i32, vp, vp])
+    _sig(L, "skein_merge_candidates", i32, [vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, vp])
     _sig(L, "skein_sample_topk_topp", i32, [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp])
     _sig(L, "skein_quant_fp8_block128", i32, [vp, vp, vp, i64, i32, vp])
     _sig(L, "skein_advance_decode_state", i32, [vp, vp, vp, vp, i32, vp, vp])
+    pvp = C.POINTER(C.c_void_p)
+    _sig(L, "skein_ipc_alloc", i32, [pvp, i64])
+    _sig(L, "skein_ipc_free", i32, [vp])
+    _sig(L, "skein_ipc_get_handle", i32, [vp, C.c_char_p])
+    _sig(L, "skein_ipc_open", i32, [C.c_char_p, pvp])
+    _sig(L, "skein_ipc_close", i32, [vp])
+    _sig(L, "skein_ipc_handle_bytes", i32, [])
+    _sig(L, "skein_push_rows", i32, [vp, i64, pvp, pvp, i32, vp, vp, vp])
+    _sig(L, "skein_argmax_push", i32, [vp, i64, i32, i32, i32, pvp, pvp, pvp, i32, vp, vp, vp])
+    _sig(L, "skein_copy_pages", i32, [vp, vp, vp, vp, i32, i64, vp])
+    _sig(L, "skein_wait_flag", i32, [vp, i32, i32, vp, vp])
     for name, rt, at in _OPTIONAL:
         if hasattr(L, name):
             _sig(L, name, rt, at)

@@ -40,6 +40,7 @@ class Workspace:
                                    device=device)
         self.gemm_counters = torch.zeros(max(self.sm_count, 256), dtype=torch.int32, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.router_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.attn_ws = None
         self.attn_counters = None
 
@@ -328,10 +329,37 @@ def router_topk(x, wg, topk, want_logits=False):
     w = torch.empty(T, topk, dtype=torch.float32, device=x.device)
     lg = torch.empty(T, E, dtype=torch.float32, device=x.device) if want_logits else None
     rc = _lib.lib().skein_router_topk(x.data_ptr(), wg.data_ptr(), T, H, E, topk, ids.data_ptr(), w.data_ptr(),
-                                      _lib.ptr(lg), _lib.stream_ptr())
+                                      _lib.ptr(lg), None, None, None, None, 0, E, None, _lib.stream_ptr())
     _lib.check(rc, "router_topk")
     _lib.count_launch()
     return ids, w, lg
+
+
+def route(x, wg, topk, e_first=0, e_count=None):
+    """Router and expert-sorted layout in one launch.
+
+    Returns (expert_ids [T, k], weights [T, k], counts [E], offsets [E+1], row_of [T*k], src_token [T*k]);
+    offsets[E] is the number of rows routed to this rank's experts, rows of src_token beyond it are unset.
+    """
+    E = wg.shape[0]
+    if not x.is_cuda:
+        ids, w, _ = ref.router_topk(x, wg, topk)
+        return (ids, w) + tuple(ref.router_plan(ids, E, e_first, e_count))
+    T, H = x.shape
+    dev = x.device
+    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    w = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    meta = torch.empty(2 * E + 1 + 2 * T * topk, dtype=torch.int32, device=dev)
+    counts, offsets = meta[:E], meta[E:2 * E + 1]
+    row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
+    ws = workspace()
+    rc = _lib.lib().skein_router_topk(x.data_ptr(), wg.data_ptr(), T, H, E, topk, ids.data_ptr(), w.data_ptr(), None,
+                                      counts.data_ptr(), offsets.data_ptr(), row_of.data_ptr(), src_token.data_ptr(),
+                                      e_first, E if e_count is None else e_count, ws.router_counter.data_ptr(),
+                                      _lib.stream_ptr())
+    _lib.check(rc, "route")
+    _lib.count_launch()
+    return ids, w, counts, offsets, row_of, src_token
 
 
 def router_plan(expert_ids, E, e_first=0, e_count=None, bufs=None):
@@ -363,7 +391,7 @@ def gather_rows(x, src_row, n_rows_dev=None, out=None):
     n = src_row.shape[0]
     H = x.shape[1]
     if out is None:
-        out = torch.zeros(n, H, dtype=x.dtype, device=x.device)
+        out = torch.empty(n, H, dtype=x.dtype, device=x.device)
     rc = _lib.lib().skein_gather_rows(x.data_ptr(), src_row.data_ptr(), out.data_ptr(), n, H, _lib.ptr(n_rows_dev),
                                       _lib.stream_ptr())
     _lib.check(rc, "gather_rows")
@@ -443,3 +471,39 @@ def advance_decode_state(sampled, tokens, positions, seq_lens, step_counter=None
                                                _lib.stream_ptr())
     _lib.check(rc, "advance_decode_state")
     _lib.count_launch()
+
+
+def linear_push(x, w, peer_out, peer_flag, epoch, done_counter, ldo, grouped=None, n_tile=None, rows_hint=None,
+                wait_budget_ms=0):
+    """Row-parallel projection whose epilogue stores the partial result into every peer's buffer.
+
+    peer_out[i] / peer_flag[i] are raw addresses valid in this process (peer-mapped memory): the bf16
+    destination of this rank's partial on peer i, and the flag word this rank owns there. `epoch` and
+    `done_counter` are local int32 device tensors. grouped = (counts, offsets) selects the per-expert form.
+    """
+    _check_act(x)
+    rows, K = x.shape
+    wv, rows_pg, packed = _wview(w)
+    if grouped is None:
+        F = w.shape[0]
+        p = _base_params(x, wv, None, F, K, n_tile or pick_n_tile(rows, False), 2)
+        p.w_rows_per_group = F
+    else:
+        counts, offsets = grouped
+        E, F = w.shape[0], w.shape[1]
+        if n_tile is None:
+            avg = (rows_hint if rows_hint is not None else rows) / E
+            n_tile = pick_n_tile(int(math.ceil(avg * 1.5)), False)
+        p = _base_params(x, wv, None, F, K, n_tile, 2)
+        p.G, p.w_rows_per_group = E, rows_pg
+        p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
+    p.w_packed = packed
+    p.ldo = ldo
+    p.n_peers = len(peer_out)
+    for i, (po, pf) in enumerate(zip(peer_out, peer_flag)):
+        p.peer_out[i] = po
+        p.peer_flag[i] = pf
+    p.epoch = epoch.data_ptr()
+    p.done_counter = done_counter.data_ptr()
+    p.wait_budget_ms = wait_budget_ms
+    _gemm_launch(p, "linear_push")

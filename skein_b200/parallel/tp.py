@@ -1,0 +1,142 @@
+"""Tensor-parallel communicator: the collectives of a decoder block, fused into its kernels.
+
+Fused mode (decode and small prefill chunks). A row-parallel projection (o_proj, expert down)
+stores its partial output from the GEMM epilogue straight into every rank's receive buffer (slot =
+source rank) over NVLink peer stores and then releases a per-source flag on each peer; the kernel
+that consumes the sum (residual + RMSNorm, csrc/kernels/norm.cu) waits on the flags and adds the
+slots. A block therefore launches no collective. Two receive buffers alternate: a rank can only be
+one all-reduce ahead of the slowest peer, because it cannot finish all-reduce k+1 without that peer's
+contribution, which the peer sends only after it has consumed all-reduce k.
+
+NCCL mode (large prefill chunks, or SKEIN_COMM=nccl as the un-fused baseline): the same math with
+a library all-reduce between the local GEMM and the reduce kernel.
+
+Greedy sampling is vocabulary-parallel: each rank reduces its logit shard to one candidate per row
+and pushes 8 bytes per row to every peer.
+
+The reference does these with ncclAllReduce + a device copy back (crates/skein_runtime/src/cuda/
+nccl.rs:196-245), a 2-rank host-memory kernel under capture (cuda/shm_allreduce.rs:24-69) and an
+all-gather of logits (nccl.rs:251-298).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _lib
+from .symm import SymmetricHeap
+
+
+class TPComm:
+    def __init__(self, group, device, hidden: int, fused_rows: int = 512, max_batch: int = 256, mode: str | None = None,
+                 wait_budget_ms: int = 10000):
+        self.group, self.device = group, device
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        self.hidden, self.fused_rows, self.max_batch = hidden, fused_rows, max_batch
+        self.mode = mode or os.environ.get("SKEIN_COMM", "fused")
+        self.wait_budget_ms = wait_budget_ms
+        N = self.size
+        slot_bytes = fused_rows * hidden * 2
+        heap_bytes = 2 * N * slot_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
+        self.heap = SymmetricHeap(group, device, heap_bytes)
+        h = self.heap
+        self.buf_off = [h.alloc(N * slot_bytes) for _ in range(2)]
+        self.flag_off = [h.alloc(256) for _ in range(2)]
+        self.cand_val_off = h.alloc(N * max_batch * 4)
+        self.cand_idx_off = h.alloc(N * max_batch * 4)
+        self.cand_flag_off = h.alloc(256)
+        self.slot_bytes = slot_bytes
+        self.bufs = [h.view(o, (N, fused_rows, hidden), torch.bfloat16) for o in self.buf_off]
+        self.flags = [h.view(o, (N,), torch.int32) for o in self.flag_off]
+        self.cand_val = h.view(self.cand_val_off, (N, max_batch), torch.float32)
+        self.cand_idx = h.view(self.cand_idx_off, (N, max_batch), torch.int32)
+        self.cand_flags = h.view(self.cand_flag_off, (N,), torch.int32)
+        # local, not shared: epochs and "all CTAs done" counters of buffers 0/1 and of the candidate exchange
+        self.epochs = torch.zeros(3, dtype=torch.int32, device=device)
+        self.done = torch.zeros(3, dtype=torch.int32, device=device)
+        self.cur = 0
+        r = self.rank
+        self._peer_out = [[h.peer_ptr(p, self.buf_off[b] + r * slot_bytes) for p in range(N)] for b in range(2)]
+        self._peer_flag = [[h.peer_ptr(p, self.flag_off[b] + 4 * r) for p in range(N)] for b in range(2)]
+        VP = C.c_void_p * N
+        self._cand_val_ptrs = VP(*[h.peer_ptr(p, self.cand_val_off + 4 * r * max_batch) for p in range(N)])
+        self._cand_idx_ptrs = VP(*[h.peer_ptr(p, self.cand_idx_off + 4 * r * max_batch) for p in range(N)])
+        self._cand_flag_ptrs = VP(*[h.peer_ptr(p, self.cand_flag_off + 4 * r) for p in range(N)])
+        self._push_dst = [VP(*self._peer_out[b]) for b in range(2)]
+        self._push_flag = [VP(*self._peer_flag[b]) for b in range(2)]
+
+    @staticmethod
+    def create(group, device, max_rows: int, hidden: int, **kw) -> "TPComm":
+        return TPComm(group, device, hidden, **kw)
+
+    # ---- row-parallel projection + all-reduce ------------------------------------------------------
+    def _fused_ok(self, rows: int) -> bool:
+        return self.mode == "fused" and rows <= self.fused_rows
+
+    def linear_push(self, x, w, grouped=None):
+        """Returns (partial [n_src, rows, H], flags or None, epoch or None) for ops.reduce_residual_rmsnorm."""
+        rows = x.shape[0]
+        if not self._fused_ok(rows):
+            y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
+            dist.all_reduce(y, group=self.group)
+            return y.unsqueeze(0), None, None
+        b = self.cur
+        self.cur ^= 1
+        ops.linear_push(x, w, self._peer_out[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+                        self.hidden, grouped=grouped, wait_budget_ms=0)
+        return self.bufs[b], self.flags[b], self.epochs[b:b + 1]
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Stand-alone sum all-reduce of a [rows, H] bf16 tensor (one-shot push + local reduce)."""
+        rows = x.shape[0]
+        if not self._fused_ok(rows) or x.shape[1] != self.hidden:
+            y = x.clone()
+            dist.all_reduce(y, group=self.group)
+            return y
+        b = self.cur
+        self.cur ^= 1
+        rc = _lib.lib().skein_push_rows(x.data_ptr(), x.numel() * 2, self._push_dst[b], self._push_flag[b], self.size,
+                                        self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
+                                        _lib.stream_ptr())
+        _lib.check(rc, "push_rows")
+        _lib.count_launch()
+        out, _ = ops.reduce_residual_rmsnorm(None, self.bufs[b][:, :rows], None, 0.0, flags=self.flags[b],
+                                             epoch=self.epochs[b:b + 1], wait_budget_ms=self.wait_budget_ms)
+        return out
+
+    # ---- vocabulary-parallel greedy sampling ----------------------------------------------------------
+    def vocab_parallel_argmax(self, logits: torch.Tensor, v_local: int) -> torch.Tensor:
+        B, V = logits.shape
+        if B > self.max_batch:
+            # large prefill batches: gather (value, index) pairs with the library instead
+            val = torch.empty(B, dtype=torch.float32, device=logits.device)
+            idx = ops.sample_argmax(logits, idx_offset=self.rank * v_local, out_val=val)
+            vals = [torch.empty_like(val) for _ in range(self.size)]
+            idxs = [torch.empty_like(idx) for _ in range(self.size)]
+            dist.all_gather(vals, val, group=self.group)
+            dist.all_gather(idxs, idx, group=self.group)
+            v = torch.stack(vals)
+            i = torch.stack(idxs)
+            best = v.max(dim=0, keepdim=True).values
+            cand = torch.where(v == best, i, torch.full_like(i, 2 ** 31 - 1))
+            return cand.min(dim=0).values
+        rc = _lib.lib().skein_argmax_push(logits.data_ptr(), logits.stride(0), B, V, self.rank * v_local,
+                                          self._cand_val_ptrs, self._cand_idx_ptrs, self._cand_flag_ptrs, self.size,
+                                          self.epochs[2:3].data_ptr(), self.done[2:3].data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "argmax_push")
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+        ws = ops.workspace()
+        rc = _lib.lib().skein_merge_candidates(self.cand_val.data_ptr(), self.cand_idx.data_ptr(), self.size, B, self.max_batch,
+                                               self.cand_flags.data_ptr(), self.epochs[2:3].data_ptr(),
+                                               ws.status.data_ptr(), self.wait_budget_ms, out.data_ptr(),
+                                               _lib.stream_ptr())
+        _lib.check(rc, "merge_candidates")
+        _lib.count_launch(2)
+        return out
+
+    def close(self):
+        self.heap.close()

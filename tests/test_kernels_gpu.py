@@ -180,6 +180,22 @@ def test_router_topk_and_plan():
     assert torch.equal(counts.cpu(), c2) and torch.equal(row_of.cpu(), r2) and torch.equal(src.cpu()[:n], s2[:n])
 
 
+@pytest.mark.parametrize("T,H,E", [(64, 4096, 8), (5, 256, 4), (300, 8192, 16)])
+def test_fused_route_equals_two_step(T, H, E):
+    torch.manual_seed(11)
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    wg = (torch.randn(E, H, device=DEV) / 32).bfloat16()
+    for e_first, e_count in ((0, E), (E // 2, E // 2)):
+        ids, w, counts, offsets, row_of, src = ops.route(x, wg, 2, e_first, e_count)
+        ids2, w2, _ = ops.router_topk(x, wg, 2)
+        c2, o2, r2, s2 = ops.router_plan(ids2, E, e_first, e_count)
+        torch.cuda.synchronize()
+        n = int(o2[-1])
+        assert torch.equal(ids, ids2) and torch.equal(w, w2)
+        assert torch.equal(counts, c2) and torch.equal(offsets, o2) and torch.equal(row_of, r2)
+        assert torch.equal(src[:n], s2[:n])
+
+
 def test_sampling():
     torch.manual_seed(9)
     B, V = 5, 32000

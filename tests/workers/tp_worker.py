@@ -1,0 +1,127 @@
+"""Multi-GPU worker (one process per GPU, launched by torch.distributed.run from test_tp_gpu.py).
+
+Checks, on every rank:
+  1. stand-alone push all-reduce equals the sum of the ranks' inputs
+  2. fused GEMM -> push -> reduce+residual+RMSNorm equals the fp32 reference of the unsharded op
+     (dense and grouped / MoE-combine forms): "TP shards summed equal the full op", the property the
+     reference tests on CPU in crates/skein_emit/tests/op_numerics.rs:299,371
+  3. vocabulary-parallel argmax equals argmax of the gathered logits (vocab_parallel.rs:56)
+  4. a tiny Mixtral served TP=N (CUDA-graph decode, fused collectives) produces the same tokens as the
+     unsharded CPU reference graph
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from skein_b200 import ops  # noqa: E402
+from skein_b200.models import config as mc  # noqa: E402
+from skein_b200.models.decoder import Decoder, random_weights  # noqa: E402
+from skein_b200.models.sharding import shard_model  # noqa: E402
+from skein_b200.ops import reference as ref  # noqa: E402
+from skein_b200.parallel.tp import TPComm  # noqa: E402
+from skein_b200.runtime.runner import ModelRunner  # noqa: E402
+
+
+def rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / (b.norm() + 1e-9))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    H = 1024
+    comm = TPComm(dist.group.WORLD, dev, hidden=H, fused_rows=256, max_batch=64,
+                  mode=os.environ.get("SKEIN_COMM", "fused"))
+    g = torch.Generator().manual_seed(7)
+
+    # 1. stand-alone all-reduce (several rounds so both buffers and epochs cycle)
+    for it in range(5):
+        xs = [torch.randn(40, H, generator=g).bfloat16() for _ in range(world)]
+        y = comm.all_reduce(xs[rank].to(dev))
+        want = torch.stack([x.float() for x in xs]).sum(0)
+        assert rel(y, want) < 1e-2, ("all_reduce", it, rel(y, want))
+
+    # 2a. dense row-parallel projection
+    T, K = 48, 512 * world
+    x_full = torch.randn(T, K, generator=g).bfloat16()
+    w_full = (torch.randn(H, K, generator=g) / 32).bfloat16()
+    res = torch.randn(T, H, generator=g).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    ks = slice(rank * 512, (rank + 1) * 512)
+    for it in range(3):
+        part, flags, epoch = comm.linear_push(x_full[:, ks].contiguous().to(dev), w_full[:, ks].contiguous().to(dev))
+        r1, n1 = ops.reduce_residual_rmsnorm(res.to(dev), part, gamma.to(dev), 1e-5, flags=flags, epoch=epoch)
+        r2, n2 = ref.reduce_residual_rmsnorm(res, ref.linear(x_full, w_full).unsqueeze(0), gamma, 1e-5)
+        assert rel(r1, r2) < 2e-2 and rel(n1, n2) < 2e-2, ("dense", it, rel(r1, r2), rel(n1, n2))
+
+    # 2b. grouped (MoE down projection + top-2 combine)
+    E, topk, Kp = 4, 2, 256
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, topk, generator=g)
+    counts, offsets, row_of, src = ref.router_plan(ids, E)
+    rows = T * topk
+    h_full = torch.randn(rows, Kp * world, generator=g).bfloat16()
+    w2_full = (torch.randn(E, H, Kp * world, generator=g) / 32).bfloat16()
+    kp = slice(rank * Kp, (rank + 1) * Kp)
+    part, flags, epoch = comm.linear_push(h_full[:, kp].contiguous().to(dev), w2_full[:, :, kp].contiguous().to(dev),
+                                          (counts.to(dev), offsets.to(dev)))
+    r1, n1 = ops.reduce_residual_rmsnorm(res.to(dev), part, gamma.to(dev), 1e-5, row_of.view(T, topk).to(dev),
+                                         wts.to(dev), flags=flags, epoch=epoch)
+    y_full = ref.grouped_linear(h_full, w2_full, counts, offsets)
+    r2, n2 = ref.reduce_residual_rmsnorm(res, y_full.unsqueeze(0), gamma, 1e-5, row_of.view(T, topk), wts)
+    assert rel(r1, r2) < 2e-2 and rel(n1, n2) < 2e-2, ("grouped", rel(r1, r2), rel(n1, n2))
+
+    # 3. vocabulary-parallel argmax
+    V_local = 1000
+    logits = torch.randn(world, 16, V_local, generator=g).bfloat16()
+    tok = comm.vocab_parallel_argmax(logits[rank].to(dev), V_local)
+    want = ref.sample_argmax(torch.cat(list(logits), dim=1))
+    assert torch.equal(tok.cpu(), want), "vocab-parallel argmax"
+
+    # 4. tiny Mixtral, TP = world, graph decode with fused collectives vs the CPU reference graph
+    cfg = mc.tiny_mixtral(layers=2, hidden=H, inter=512 * world, heads=4 * world if world <= 2 else 8,
+                          kv_heads=world if world <= 2 else 8, experts=4, vocab=1024)
+    if world > 2:
+        cfg.num_heads, cfg.num_kv_heads = 8, 8
+    full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=11, std=0.05)
+    lay = mc.ParallelLayout(tp=world, rank=rank)
+    dec = Decoder(cfg, shard_model(full, cfg, lay, dev), lay, num_pages=32, page_size=16, max_pos=256, comm=comm)
+    dec_ref = Decoder(cfg, full, num_pages=32, page_size=16, max_pos=256)
+    B = 3
+    prompts = torch.randint(0, cfg.vocab_size, (B, 21), generator=g).tolist()
+    tables = [[1 + 4 * s + i for i in range(4)] for s in range(B)]
+
+    def generate(decoder, use_graphs, n=6):
+        runner = ModelRunner(decoder, max_blocks_per_seq=4, use_graphs=use_graphs)
+        toks = runner.prefill([(prompts[s], tables[s], 0) for s in range(B)])
+        outs, cached = [toks], 21
+        bk = runner.bucket(B)
+        for _ in range(n):
+            runner.load_decode_inputs(bk, outs[-1], [cached] * B, [cached + 1] * B, tables)
+            outs.append(runner.decode_step(bk)[:B].tolist())
+            cached += 1
+        return outs
+
+    got = generate(dec, True)
+    torch.cuda.synchronize()
+    ops.workspace().check_status()
+    if rank == 0:
+        want = generate(dec_ref, False)
+        assert got == want, (got, want)
+    dist.barrier()
+    if rank == 0:
+        print("TP_WORKER_OK world", world, "mode", comm.mode)
+    comm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
