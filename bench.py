@@ -141,7 +141,8 @@ def main():
     t0 = time.time()
     weights = random_weights(cfg, lay, dev, seed=0, std=0.02)
     dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm)
-    runner = ModelRunner(dec, max_blocks_per_seq=blocks_per_seq, use_graphs=True, ctx_hint=P + Gn // 2)
+    use_graphs = comm is None or comm.mode == "fused"   # the NCCL baseline mode launches eagerly
+    runner = ModelRunner(dec, max_blocks_per_seq=blocks_per_seq, use_graphs=use_graphs, ctx_hint=P + Gn // 2)
     torch.cuda.synchronize()
     t_init = time.time() - t0
 
@@ -181,7 +182,8 @@ def main():
     # ---- device-timed loop ---------------------------------------------------------------------------
     reset_state()
     l0 = _lib.launches()
-    runner._ensure_graph(bk, True)
+    if use_graphs:
+        runner._ensure_graph(bk, True)
     launches_per_step = None
     for _ in range(W):
         runner.decode_loop_step(bk)
@@ -249,7 +251,7 @@ def main():
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
                        "global_batch": B, "seq_len": P, "gen_len": Gn, "parallelism": f"tp{world}",
                        "kv": "paged, block 16", "l2": "inputs (weights) larger than L2, no flush",
-                       "cuda_graph": True},
+                       "cuda_graph": use_graphs, "comm": (comm.mode if comm else "none")},
             "ttft_p50_ms": round(ttft[len(ttft) // 2], 2),
             "tpot_p99_ms": e2e["tpot_p99_ms"] if e2e else None,
             "e2e": e2e, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,

@@ -36,7 +36,8 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
-    dist.init_process_group("nccl", device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     H = 1024
     comm = TPComm(dist.group.WORLD, dev, hidden=H, fused_rows=256, max_batch=64,
                   mode=os.environ.get("SKEIN_COMM", "fused"))
@@ -99,23 +100,55 @@ def main():
     prompts = torch.randint(0, cfg.vocab_size, (B, 21), generator=g).tolist()
     tables = [[1 + 4 * s + i for i in range(4)] for s in range(B)]
 
-    def generate(decoder, use_graphs, n=6):
-        runner = ModelRunner(decoder, max_blocks_per_seq=4, use_graphs=use_graphs)
-        toks = runner.prefill([(prompts[s], tables[s], 0) for s in range(B)])
-        outs, cached = [toks], 21
-        bk = runner.bucket(B)
-        for _ in range(n):
-            runner.load_decode_inputs(bk, outs[-1], [cached] * B, [cached + 1] * B, tables)
-            outs.append(runner.decode_step(bk)[:B].tolist())
+    # reference run on CPU (rank 0 decides, everyone follows): tokens plus the top-1/top-2 logit gap per step
+    from skein_b200.models.decoder import BatchInputs
+    steps = 6
+    if rank == 0:
+        runner_ref = ModelRunner(dec_ref, max_blocks_per_seq=4, use_graphs=False)
+        toks, lg = runner_ref.prefill([(prompts[s], tables[s], 0) for s in range(B)], want_logits=True)
+        ref_toks, gaps = [toks], []
+        top2 = lg.float().topk(2, dim=-1).values
+        gaps.append((top2[:, 0] - top2[:, 1]).tolist())
+        cached = 21
+        for _ in range(steps):
+            i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+            bt = torch.zeros(B, 4, dtype=torch.int32)
+            for s_ in range(B):
+                bt[s_] = torch.tensor(tables[s_], dtype=torch.int32)
+            inp = BatchInputs(token_ids=i32(ref_toks[-1]), positions=i32([cached] * B), block_table=bt,
+                              seq_lens=i32([cached + 1] * B))
+            tok, lg = dec_ref.forward(inp)
+            top2 = lg.float().topk(2, dim=-1).values
+            gaps.append((top2[:, 0] - top2[:, 1]).tolist())
+            ref_toks.append(tok.tolist())
             cached += 1
-        return outs
+        payload = [ref_toks, gaps]
+    else:
+        payload = [None, None]
+    dist.broadcast_object_list(payload, src=0)
+    ref_toks, gaps = payload
 
-    got = generate(dec, True)
+    # teacher-forced TP run through CUDA graphs: every step is fed the reference's previous tokens
+    use_graphs = comm.mode == "fused"   # library collectives are launched eagerly, not captured
+    runner = ModelRunner(dec, max_blocks_per_seq=4, use_graphs=use_graphs)
+    got = [runner.prefill([(prompts[s], tables[s], 0) for s in range(B)])]
+    bk = runner.bucket(B)
+    cached = 21
+    for t in range(steps):
+        runner.load_decode_inputs(bk, ref_toks[t], [cached] * B, [cached + 1] * B, tables)
+        got.append(runner.decode_step(bk)[:B].tolist())
+        cached += 1
     torch.cuda.synchronize()
     ops.workspace().check_status()
-    if rank == 0:
-        want = generate(dec_ref, False)
-        assert got == want, (got, want)
+    assert runner.graph_replays == (steps if use_graphs else 0)
+    mism = 0
+    for t in range(steps + 1):
+        for s_ in range(B):
+            if got[t][s_] != ref_toks[t][s_]:
+                mism += 1
+                # a different greedy token is only acceptable at a near-tie of the reference logits
+                assert gaps[t][s_] < 0.08, (t, s_, got[t][s_], ref_toks[t][s_], gaps[t][s_])
+    assert mism <= 3, mism
     dist.barrier()
     if rank == 0:
         print("TP_WORKER_OK world", world, "mode", comm.mode)
