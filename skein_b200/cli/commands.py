@@ -1,0 +1,205 @@
+"""Bodies of the `skein` sub-commands. Each returns a process exit code and reports through `emit`."""
+from __future__ import annotations
+
+import json
+import os
+import time
+from collections import Counter
+from pathlib import Path
+
+from .. import core
+
+
+def _read(p) -> str:
+    return Path(p).read_text()
+
+
+def _search_options(args) -> dict:
+    o = {"objective": getattr(args, "objective", "latency")}
+    for env, key in (("SKEIN_FORCE_TP", "force_tp"), ("SKEIN_FORCE_PP", "force_pp"), ("SKEIN_FORCE_EP", "force_ep"), ("SKEIN_FORCE_BATCH", "force_batch")):
+        if os.environ.get(env):
+            o[key] = int(os.environ[env])
+    return o
+
+
+def _plan_summary(plan: dict) -> dict:
+    dm = Counter((d["weight"], d["activation"], d["kv_cache"]) for d in plan["dtype_map"]["per_layer"])
+    return {"parallelism": plan["parallelism"], "kv": plan["kv"], "batching": plan["batching"],
+            "dtype_histogram": {"/".join(k): v for k, v in sorted(dm.items())},
+            "cuda_graphs": plan["execution"]["cuda_graphs"]["enable"], "disaggregated": plan["disaggregation"] is not None}
+
+
+def cmd_extract(args, emit) -> int:
+    t0 = time.time()
+    ins = (_read(args.model), _read(args.cluster), _read(args.trace), _read(args.drift), _read(args.cost))
+    if args.disaggregate_decode_devices:
+        r = core.extract_disaggregated_plan(*ins, args.disaggregate_decode_devices, _search_options(args))
+    else:
+        r = core.extract_plan(*ins, _search_options(args))
+    Path(args.out).write_text(r["plan_json"])
+    plan = json.loads(r["plan_json"])
+    report = {"plan_path": str(args.out), "content_hash": r["content_hash"], "cost_us": r["cost_us"], "search": json.loads(r["counters_json"]),
+              "summary": _plan_summary(plan), "wall_s": round(time.time() - t0, 3)}
+    s = report["summary"]
+    emit(args, report, f"plan written to {args.out}\n  hash        {r['content_hash']}\n  cost        {r['cost_us']:.1f} us per decode step\n"
+                       f"  placement   tp={s['parallelism']['tp']} pp={s['parallelism']['pp']} ep={s['parallelism']['ep']}\n"
+                       f"  batching    {s['batching']}\n  kv          {s['kv']}\n  dtypes      {s['dtype_histogram']}\n"
+                       f"  search      {report['search']}")
+    return 0
+
+
+def cmd_compile(args, emit) -> int:
+    from ..compile.pipeline import compile_model
+
+    prompts = None
+    if args.parity_prompts_path:
+        prompts = [json.loads(l)["tokens"] for l in _read(args.parity_prompts_path).splitlines() if l.strip()]
+    r = compile_model(_read(args.model), _read(args.cluster), _read(args.trace), _read(args.drift), _read(args.cost), args.out,
+                      weights=args.weights, options=_search_options(args), n_parity_prompts=args.n_parity_prompts, prompts=prompts,
+                      enforce_parity=args.enforce_parity, seed=args.seed)
+    if r.replans:
+        Path(args.drift).write_text(r.drift_toml)    # the feedback edge: the next extract sees the raised entries
+    rep = r.report
+    payload = {"artifact": str(r.artifact_dir), "content_hash": r.artifact_dir.name, "summary": _plan_summary(r.plan), "replans": r.replans,
+               "parity": None if rep is None else {"passed": rep.passed, "avg_final_kl": rep.avg_final_kl, "failing_layers": len(rep.failing)}}
+    emit(args, payload, f"artifact {r.artifact_dir}\n  parity      {'skipped' if rep is None else ('passed' if rep.passed else 'FAILED')}"
+                        f"{'' if rep is None else f' (avg final KL {rep.avg_final_kl:.3g})'}\n  re-plans    {r.replans}")
+    return 0
+
+
+def cmd_verify(args, emit) -> int:
+    import torch
+
+    from ..compile import parity
+    from ..compile.artifact import Artifact
+    from ..compile.pipeline import default_parity_prompts
+
+    art = Artifact(args.artifact)
+    if args.tokens_file:
+        prompts = [json.loads(l)["tokens"] if l.strip().startswith("{") else [int(t) for t in l.split()] for l in _read(args.tokens_file).splitlines() if l.strip()]
+    elif args.sample_from:
+        prompts = [json.loads(l)["tokens"] for l in _read(args.sample_from).splitlines() if l.strip()][:args.n_prompts]
+    else:
+        prompts = default_parity_prompts(art.cfg, min(args.n_prompts, 8))
+    cand = parity.ArtifactForward(art, args.device)
+    if args.dump_only:
+        dump_dir = Path(os.environ.get("SKEIN_DUMP_DIR", "."))
+        dump_dir.mkdir(parents=True, exist_ok=True)
+        for i, p in enumerate(prompts):
+            _, lg = cand.run(p)
+            torch.save(lg, dump_dir / f"logits_{i}.pt")
+        emit(args, {"dumped": len(prompts), "dir": str(dump_dir)}, f"dumped {len(prompts)} logit vectors to {dump_dir}")
+        return 0
+    ref_art = Artifact(args.reference) if args.reference else Artifact(art.path / "reference_bf16")
+    if args.hf_reference:
+        if args.reference_dtype not in ("bfloat16", "float32"):
+            raise ValueError("reference dtype must be bfloat16 or float32")
+        refw = ref_art.load_full_weights(args.device)
+        reference = parity.DenseForward(art.cfg, refw)
+    else:
+        reference = parity.ArtifactForward(ref_art, args.device)
+    tol = json.loads(core.cost_constants_json(_read(args.cost))).get("parity_tolerance_mse", {})
+    rep = parity.verify(cand, reference, prompts, art.plan, args.max_accuracy_drift, tol)
+    (art.path / "parity_report.json").write_text(rep.to_json())
+    emit(args, json.loads(rep.to_json()), f"parity {'passed' if rep.passed else 'FAILED'}: avg final KL {rep.avg_final_kl:.3g} "
+                                          f"(limit {rep.max_accuracy_drift:g}), {len(rep.failing)} failing layers over {rep.prompts} prompts")
+    return 1 if (args.enforce and not rep.passed) else 0
+
+
+def cmd_serve(args, emit) -> int:
+    from ..parallel import launcher, worker
+
+    argv = ["--artifact", args.artifact, "--port", str(args.port), "--total-kv-bytes", str(args.total_kv_bytes), "--max-new-tokens",
+            str(args.max_new_tokens), "--rendezvous", args.rendezvous, "--max-batch", str(args.max_batch), "--max-seq-len", str(args.max_seq_len)]
+    for flag, val in (("--workload", args.workload), ("--cost", args.cost), ("--prompt", args.prompt), ("--demo-prompts", args.demo_prompts)):
+        if val is not None:
+            argv += [flag, val]
+    if args.batch_demo and not args.demo_prompts and args.prompt is None:
+        argv += ["--demo-prompts", "The quick brown fox|Blackwell tensor cores|Paged attention is"]
+    if launcher.world_from_env() is None and args.gpus:
+        gpus = launcher.parse_gpus(args.gpus)
+        failed = launcher.launch_ranks(gpus, args.rendezvous, argv)
+        emit(args, {"ranks": len(gpus), "failed": failed}, f"{len(gpus)} ranks finished, {failed} failed")
+        return 1 if failed else 0
+    return worker.run_rank(worker.parse(argv))
+
+
+def cmd_calibrate(args, emit) -> int:
+    import torch
+
+    from .. import calibrate as cal
+
+    corpus = cal.Corpus.from_toml(_read(args.corpus))
+    cost_text = _read(args.out_cost)
+    consts = json.loads(core.cost_constants_json(cost_text))
+    if args.hardware not in consts["peak_tflops"]:
+        raise ValueError(f"no [peak_tflops.{args.hardware}] table in {args.out_cost}")
+    eff, drift = {}, {}
+    if torch.cuda.is_available():
+        eff = cal.calibrate_kernels(corpus, consts["peak_tflops"][args.hardware]["bf16"], consts.get("hbm_gbps", {}).get(args.hardware, 6552.0))
+        Path(args.out_cost).write_text(cal.write_cost_constants(cost_text, eff))
+    if args.candidate_artifact:
+        from ..compile import parity
+        from ..compile.artifact import Artifact
+        from ..compile.pipeline import default_parity_prompts
+        art = Artifact(args.candidate_artifact)
+        ref = Artifact(args.reference_artifact) if args.reference_artifact else Artifact(art.path / "reference_bf16")
+        prompts = default_parity_prompts(art.cfg, min(corpus.n_drift_prompts, 8), seed=corpus.sampling_seed)
+        rep = parity.verify(parity.ArtifactForward(art), parity.ArtifactForward(ref), prompts, art.plan, 1.0, consts.get("parity_tolerance_mse", {}))
+        drift = cal.calibrate_drift(json.loads(rep.to_json())["layers"], art.plan)
+        name = Path(args.model).stem.replace("_config", "")
+        dpath = Path(args.out_drift_dir) / f"{name}_drift.toml"
+        dpath.write_text(cal.write_drift_table(_read(dpath), drift))
+    emit(args, {"efficiencies": {f"{k[0]}.{k[1]}": v for k, v in eff.items()}, "drift_entries": len(drift)},
+         f"calibrated {len(eff)} kernel efficiencies, {len(drift)} drift entries")
+    return 0
+
+
+def cmd_bench(args, emit) -> int:
+    """Replay a trace (arrival times honoured, scaled by --time-scale) against a single-process engine."""
+    import torch
+
+    from ..compile.artifact import Artifact
+    from ..parallel import worker
+
+    art = Artifact(args.artifact)
+    if art.num_devices != 1:
+        raise ValueError("`skein bench` drives a single-process engine; launch multi-GPU artifacts with `skein serve --gpus` and bench over HTTP")
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    wargs = worker.parse(["--artifact", args.artifact, "--workload", args.workload])
+    eng = worker.build_engine(art, 0, device, None, wargs)
+    lines = [json.loads(l) for l in _read(args.workload).splitlines() if l.strip()]
+    slo, reqs = lines[0]["slo"], lines[1:]
+    if args.max_requests:
+        reqs = reqs[:args.max_requests]
+    g = torch.Generator().manual_seed(0)
+    t0 = time.monotonic()
+    pending = list(reqs)
+    done_tokens, rejected, first_seen, ttfts = 0, 0, {}, []
+    while pending or not eng.idle:
+        now = (time.monotonic() - t0) * 1000.0 * args.time_scale
+        while pending and pending[0]["arrival_ms"] <= now:
+            r = pending.pop(0)
+            n_prompt = min(int(r["prompt_tokens"]), eng.dec.max_pos - int(r["output_tokens"]) - 1)
+            ids = torch.randint(0, art.cfg.vocab_size, (max(1, n_prompt),), generator=g).tolist()
+            rid, d = eng.submit(ids, int(r["output_tokens"]))
+            rejected += d.kind == "reject"
+            first_seen[rid] = time.monotonic()
+        evs = eng.step()
+        if not evs:
+            time.sleep(0.0005)
+        for ev in evs:
+            if ev.error is None:
+                done_tokens += 1
+    wall = time.monotonic() - t0
+    text = eng.metrics.render()
+    ok = int(next((l.split()[-1] for l in text.splitlines() if l.startswith('skein_requests_total{status="ok"}')), 0))
+    ttft_p50, tpot_p99 = eng.metrics.ttft_p50(), eng.metrics.tpot_p99()
+    good = ok if (ttft_p50 <= slo["ttft_p95_ms"] and tpot_p99 <= slo["tpot_p95_ms"]) else 0
+    rep_path = art.path / "parity_report.json"
+    drift_ok = json.loads(rep_path.read_text())["passed"] if rep_path.exists() else None
+    out = {"throughput_tok_s": round(done_tokens / wall, 2), "goodput_req_s": round(good / wall, 3), "drift_compliance": drift_ok,
+           "requests_ok": ok, "requests_rejected": rejected, "ttft_p50_ms": ttft_p50, "tpot_p99_ms": tpot_p99, "wall_s": round(wall, 2),
+           "baseline": args.baseline}
+    emit(args, out, "\n".join(f"{k:20s} {v}" for k, v in out.items()))
+    return 0

@@ -1,0 +1,130 @@
+"""`skein` command line: extract | compile | verify | serve | calibrate | bench.
+
+Flags follow the reference's clap definitions (crates/skein_cli/src/cli.rs:15-239): global `--log-level`
+and `--output text|json`; errors are printed to stderr as one JSON object when `--output json`
+(crates/skein_cli/src/output.rs:117-190). `bench` is the sub-command the reference's Makefile and a stale
+test expect but its CLI never defined (crates/skein_cli/tests/arg_parsing.rs:137-160).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import sys
+from pathlib import Path
+
+log = logging.getLogger("skein")
+
+
+def _read(p) -> str:
+    return Path(p).read_text()
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="skein", description="Blackwell-native LLM serving compiler and runtime")
+    ap.add_argument("--log-level", default="info")
+    ap.add_argument("--output", default="text", choices=["text", "json"])
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    def planner_inputs(p):
+        p.add_argument("--model", required=True, help="HuggingFace config.json")
+        p.add_argument("--cluster", required=True, help="cluster TOML")
+        p.add_argument("--trace", required=True, help="workload trace JSONL (first line: SLO)")
+        p.add_argument("--drift", required=True, help="drift table TOML")
+        p.add_argument("--cost", required=True, help="cost constants TOML")
+        p.add_argument("--objective", default=os.environ.get("SKEIN_OBJECTIVE", "latency"), choices=["latency", "throughput"])
+
+    e = sub.add_parser("extract", help="search placement + per-layer dtypes, write plan.json")
+    planner_inputs(e)
+    e.add_argument("--out", default="plan.json")
+    e.add_argument("--disaggregate-decode-devices", type=int, default=0)
+
+    c = sub.add_parser("compile", help="plan, shard weights, write the artifact, run the parity gate")
+    planner_inputs(c)
+    c.add_argument("--weights", default=None, help="HF safetensors file or directory; omit for seeded random weights")
+    c.add_argument("--out", default="artifacts/")
+    c.add_argument("--search-budget", type=int, default=100, help="accepted for compatibility; kernels are ahead-of-time compiled")
+    c.add_argument("--enforce-parity", action="store_true")
+    c.add_argument("--parity-prompts-path", default=None)
+    c.add_argument("--n-parity-prompts", type=int, default=8)
+    c.add_argument("--seed", type=int, default=0)
+
+    v = sub.add_parser("verify", help="parity of an artifact against its bf16 reference or the dense oracle")
+    v.add_argument("--artifact", required=True)
+    v.add_argument("--reference", default=None, help="reference artifact (default: <artifact>/reference_bf16)")
+    v.add_argument("--sample-from", default=None, help="JSONL of {\"tokens\": [...]} prompts")
+    v.add_argument("--n-prompts", type=int, default=50)
+    v.add_argument("--cost", default="cluster/cost_constants.toml")
+    v.add_argument("--enforce", action="store_true")
+    v.add_argument("--hf-reference", action="store_true", help="compare against the cache-free dense oracle on the bf16 weights")
+    v.add_argument("--reference-dtype", default="bfloat16")
+    v.add_argument("--dump-only", action="store_true")
+    v.add_argument("--tokens-file", default=None)
+    v.add_argument("--max-accuracy-drift", type=float, default=0.01)
+    v.add_argument("--device", default="cpu")
+
+    s = sub.add_parser("serve", help="serve an artifact over HTTP (:8080) or run a generation job")
+    s.add_argument("--artifact", required=True)
+    s.add_argument("--workload", default=None)
+    s.add_argument("--cost", default="cluster/cost_constants.toml")
+    s.add_argument("--port", type=int, default=8080)
+    s.add_argument("--enable-hot-swap", action="store_true")
+    s.add_argument("--total-kv-bytes", type=int, default=0, help="0 = size the pool from free device memory")
+    s.add_argument("--bytes-per-token", type=int, default=0)
+    s.add_argument("--gpus", default=None, help="comma-separated device ids; one process per GPU")
+    s.add_argument("--prompt", default=None)
+    s.add_argument("--max-new-tokens", type=int, default=32)
+    s.add_argument("--rendezvous", default="/tmp/skein_rendezvous")
+    s.add_argument("--batch-demo", action="store_true")
+    s.add_argument("--demo-prompts", default=None)
+    s.add_argument("--cuda-graphs", action="store_true", default=True)
+    s.add_argument("--max-batch", type=int, default=0)
+    s.add_argument("--max-seq-len", type=int, default=4096)
+
+    k = sub.add_parser("calibrate", help="measure kernel efficiencies / collective bandwidth / dtype drift, rewrite the TOML files")
+    k.add_argument("--hardware", required=True)
+    k.add_argument("--model", required=True)
+    k.add_argument("--corpus", required=True)
+    k.add_argument("--drift-prompts-path", default=None)
+    k.add_argument("--reference-artifact", default=None)
+    k.add_argument("--candidate-artifact", default=None)
+    k.add_argument("--out-cost", default="cluster/cost_constants.toml")
+    k.add_argument("--out-drift-dir", default="models/")
+
+    b = sub.add_parser("bench", help="replay a workload trace against an artifact and report throughput / goodput / drift compliance")
+    b.add_argument("--artifact", required=True)
+    b.add_argument("--workload", required=True)
+    b.add_argument("--baseline", default=None, help="URL or label of the system the numbers are compared with")
+    b.add_argument("--metrics", default="throughput,goodput,drift_compliance")
+    b.add_argument("--max-requests", type=int, default=0)
+    b.add_argument("--time-scale", type=float, default=1.0, help="divide arrival times by this factor")
+    b.add_argument("--collectives", action="store_true", help="micro-benchmark the stand-alone collectives instead")
+    return ap
+
+
+def emit(args, payload: dict, text: str) -> None:
+    if args.output == "json":
+        print(json.dumps(payload, sort_keys=True))
+    else:
+        print(text)
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    logging.basicConfig(level=getattr(logging, args.log_level.upper(), logging.INFO), format="%(levelname)s %(name)s: %(message)s")
+    try:
+        from . import commands
+        return getattr(commands, "cmd_" + args.command)(args, emit)
+    except Exception as e:  # one-line JSON error objects, like the reference
+        if args.output == "json":
+            print(json.dumps({"error": {"kind": type(e).__name__, "message": str(e)}}), file=sys.stderr)
+        else:
+            print(f"error: {type(e).__name__}: {e}", file=sys.stderr)
+        if os.environ.get("SKEIN_TRACEBACK"):
+            raise
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,129 @@
+"""One process per GPU: launch plan, per-rank command/environment, file rendezvous, wait-and-count.
+
+The parent computes one command per rank (environment: SKEIN_RANK, SKEIN_WORLD_SIZE, SKEIN_RENDEZVOUS,
+CUDA_VISIBLE_DEVICES), spawns them, waits, and reports how many failed. Ranks meet through a file
+rendezvous: the leader publishes a small blob atomically (tmp + rename), the others poll for it with a
+timeout and get a clear error if it never appears. torch.distributed is then initialised from the
+address carried in the blob.
+
+Counterpart of crates/skein_runtime/src/distributed/launcher.rs:20-72, rendezvous.rs:19,48 and
+crates/skein_cli/src/cmd/serve.rs:256-300.
+"""
+from __future__ import annotations
+
+import json
+import os
+import socket
+import subprocess
+import sys
+import time
+from dataclasses import dataclass
+from pathlib import Path
+
+
+class RendezvousError(RuntimeError):
+    pass
+
+
+@dataclass
+class RankLaunch:
+    rank: int
+    world_size: int
+    gpu: int
+    rendezvous: str
+
+
+def parse_gpus(spec: str) -> list[int]:
+    gpus = [int(x) for x in spec.split(",") if x.strip() != ""]
+    if not gpus:
+        raise ValueError("--gpus needs at least one device id")
+    if len(set(gpus)) != len(gpus):
+        raise ValueError("--gpus lists a device twice")
+    return gpus
+
+
+def plan_launch(gpus: list[int], rendezvous: str) -> list[RankLaunch]:
+    return [RankLaunch(r, len(gpus), g, rendezvous) for r, g in enumerate(gpus)]
+
+
+def build_command(launch: RankLaunch, argv: list[str], base_env: dict | None = None):
+    """Returns (argv, env) of the child for this rank."""
+    env = dict(base_env if base_env is not None else os.environ)
+    env.update({"SKEIN_RANK": str(launch.rank), "SKEIN_WORLD_SIZE": str(launch.world_size),
+                "SKEIN_RENDEZVOUS": launch.rendezvous, "CUDA_VISIBLE_DEVICES": str(launch.gpu)})
+    return [sys.executable, "-m", "skein_b200.parallel.worker", *argv], env
+
+
+def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: float | None = None) -> int:
+    """Spawn every rank, wait for all, return the number of ranks that failed."""
+    rdv = Path(rendezvous)
+    if rdv.exists():
+        rdv.unlink()
+    procs = []
+    for l in plan_launch(gpus, rendezvous):
+        cmd, env = build_command(l, argv)
+        procs.append(subprocess.Popen(cmd, env=env))
+    failed = 0
+    deadline = None if timeout_s is None else time.monotonic() + timeout_s
+    for p in procs:
+        try:
+            rc = p.wait(None if deadline is None else max(0.1, deadline - time.monotonic()))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            rc = -9
+        failed += rc != 0
+    return failed
+
+
+def world_from_env():
+    """(rank, world_size, rendezvous path) from SKEIN_RANK / SKEIN_WORLD_SIZE / SKEIN_RENDEZVOUS, or None."""
+    if "SKEIN_RANK" not in os.environ or "SKEIN_WORLD_SIZE" not in os.environ:
+        return None
+    return int(os.environ["SKEIN_RANK"]), int(os.environ["SKEIN_WORLD_SIZE"]), os.environ.get("SKEIN_RENDEZVOUS", "/tmp/skein_rendezvous")
+
+
+# ---- file rendezvous ------------------------------------------------------------------------------------------
+def publish(path: str, payload: bytes) -> None:
+    p = Path(path)
+    p.parent.mkdir(parents=True, exist_ok=True)
+    tmp = p.with_name(p.name + f".{os.getpid()}.tmp")
+    tmp.write_bytes(payload)
+    os.replace(tmp, p)     # readers see either nothing or the whole blob
+
+
+def fetch(path: str, timeout_s: float = 60.0, poll_s: float = 0.02) -> bytes:
+    p = Path(path)
+    t0 = time.monotonic()
+    while True:
+        if p.exists():
+            data = p.read_bytes()
+            if data:
+                return data
+        if time.monotonic() - t0 > timeout_s:
+            raise RendezvousError(f"rendezvous file {path} did not appear within {timeout_s:g} s (is rank 0 running?)")
+        time.sleep(poll_s)
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def init_process_group(rank: int, world: int, rendezvous: str, backend: str = "nccl", timeout_s: float = 120.0, device=None):
+    """Rank 0 picks a port and publishes it; everyone initialises torch.distributed over 127.0.0.1."""
+    import datetime
+
+    import torch.distributed as dist
+
+    if rank == 0:
+        blob = {"addr": "127.0.0.1", "port": free_port(), "world": world}
+        publish(rendezvous, json.dumps(blob).encode())
+    else:
+        blob = json.loads(fetch(rendezvous, timeout_s))
+        if blob["world"] != world:
+            raise RendezvousError(f"rendezvous was published for world size {blob['world']}, this rank expects {world}")
+    kw = {"device_id": device} if (device is not None and backend == "nccl") else {}
+    dist.init_process_group(backend, init_method=f"tcp://{blob['addr']}:{blob['port']}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=max(timeout_s, 60.0)), **kw)
+    return dist.group.WORLD

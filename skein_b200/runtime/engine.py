@@ -1,0 +1,180 @@
+"""Serving engine: continuous batching over paged KV, one scheduler iteration per `step()`.
+
+    submit()  -> admission decision from the C++ batcher (admit / delay / reject); admitted requests get
+                 their KV pages (with radix prefix reuse) at once
+    step()    -> promote delayed requests, ask the batcher for the step's work, run the prefill chunks
+                 (eager) and the decode batch (CUDA-graph replay of the batch-size bucket), hand the
+                 sampled tokens back to the batcher, retire finished requests, record metrics
+
+Under tensor parallelism every rank runs the same engine on the same request stream (rank 0
+broadcasts submissions and the clock, see DistributedFrontend), so all ranks take identical
+scheduling decisions and meet in the fused collectives.
+
+A failing step does not take the server down: the batch is retired, its streams are closed with an
+error, queued requests stay queued (the reference wraps each step in catch_unwind for the same
+purpose: crates/skein_runtime/src/server/forward.rs:237-420).
+
+Counterpart of the reference's driver loops (crates/skein_runtime/src/server/forward.rs:237-420 single
+process; distributed/batch_driver.rs:77-514 single-GPU continuous batching; distributed/gpu_rank.rs
+724-877 multi-GPU generation).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import core
+from .runner import ModelRunner
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 64
+    chunk_tokens: int = 0              # 0 = whole prompt in one chunk (bounded by max_prefill_tokens)
+    max_prefill_tokens: int = 8192
+    ttft_ms: float = 500.0
+    tpot_ms: float = 50.0
+    decode_us_at_b1: float = 8000.0
+    batch_exponent: float = 0.7
+    prefill_per_token_us: float = 25.0
+    prefix_cache: bool = True
+    eos_token: int = -1
+    use_graphs: bool = True
+
+
+@dataclass
+class TokenEvent:
+    request_id: int
+    token: int
+    is_final: bool
+    error: str | None = None
+
+
+class Engine:
+    def __init__(self, decoder, cfg: EngineConfig | None = None, metrics=None, clock=None):
+        self.dec = decoder
+        self.cfg = cfg or EngineConfig()
+        c = self.cfg
+        if decoder.num_pages <= 0:
+            raise ValueError("the decoder was built without a KV page pool")
+        self.kv = core.KvBlockManager(decoder.num_pages, decoder.page_size, c.prefix_cache)
+        self.batcher = core.ContinuousBatcher(
+            max_batch=c.max_batch, chunk_tokens=c.chunk_tokens, ttft_ms=c.ttft_ms, tpot_ms=c.tpot_ms,
+            decode_us_at_b1=c.decode_us_at_b1, batch_exponent=c.batch_exponent,
+            prefill_per_token_us=c.prefill_per_token_us, kv=self.kv, max_prefill_tokens=c.max_prefill_tokens)
+        self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
+        self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
+        self.metrics = metrics or core.MetricsRegistry()
+        self.clock = clock or (lambda: int(time.monotonic() * 1000))
+        self._next_id = 1
+        self._step = 0
+        self._last = {}          # request id -> last sampled token (input of its next decode step)
+        self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
+
+    # ---- admission ----------------------------------------------------------------------------------------
+    def submit(self, prompt_ids, max_new_tokens: int = 32, now_ms: int | None = None, request_id: int | None = None):
+        """Returns (request_id, decision) with decision.kind in {"admit", "delay", "reject"}."""
+        rid = request_id if request_id is not None else self._next_id
+        self._next_id = max(self._next_id, rid) + 1
+        now = self.clock() if now_ms is None else now_ms
+        prompt = [int(t) for t in prompt_ids]
+        if len(prompt) + max_new_tokens > self.dec.max_pos:
+            self.metrics.record_request(rid, "rejected", 0.0, 0.0, 0, 0)
+            raise ValueError(f"prompt + max_new_tokens exceeds the position limit {self.dec.max_pos}")
+        d = self.batcher.submit(rid, prompt, max_new_tokens, now)
+        if d.kind == "reject":
+            self.metrics.record_request(rid, "rejected", 0.0, 0.0, 0, 0)
+        return rid, d
+
+    # ---- one scheduler iteration ----------------------------------------------------------------------------
+    def step(self, now_ms: int | None = None) -> list[TokenEvent]:
+        now = self.clock() if now_ms is None else now_ms
+        self.batcher.promote_ready(now)
+        prefill, decode = self.batcher.next_step_batch()
+        if not prefill and not decode:
+            return []
+        t0 = time.perf_counter()
+        try:
+            if self.failure_injector is not None:
+                self.failure_injector(self._step)
+            events = self._run(prefill, decode, now)
+        except Exception as e:  # retire the batch, keep serving
+            events = [TokenEvent(rid, -1, True, error=f"{type(e).__name__}: {e}") for rid in self.batcher.retire_all()]
+            for ev in events:
+                self._last.pop(ev.request_id, None)
+                self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
+            self.metrics.count("skein_step_failures_total")
+        us = (time.perf_counter() - t0) * 1e6
+        self.metrics.record_step(self._step, len(decode) + len(prefill), us, 0.0, self.kv.in_use_pages)
+        self._step += 1
+        return events
+
+    def _run(self, prefill, decode, now) -> list[TokenEvent]:
+        events: list[TokenEvent] = []
+        if prefill:
+            seqs = []
+            for rid, start, end, last in prefill:
+                prompt = self.batcher.prompt(rid)
+                seqs.append((prompt[start:end], self.kv.pages_for(rid), start))
+            toks = self.runner.prefill(seqs)
+            for (rid, start, end, last), tok in zip(prefill, toks):
+                self.batcher.prefill_advanced(rid, end)
+                if last:
+                    events.append(self._accept(rid, tok, now))
+        if decode:
+            toks_in, pos, lens, tables = [], [], [], []
+            for rid in decode:
+                info = self.batcher.request_info(rid)
+                p = info["prompt_len"] + len(info["generated"]) - 1
+                toks_in.append(self._last[rid]); pos.append(p); lens.append(p + 1); tables.append(self.kv.pages_for(rid))
+            bk = self.runner.bucket(len(decode))
+            self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables)
+            out = self.runner.decode_step(bk)
+            for i, rid in enumerate(decode):
+                events.append(self._accept(rid, int(out[i]), now))
+        return events
+
+    def _accept(self, rid, tok, now) -> TokenEvent:
+        finished, n = self.batcher.accept_token(rid, int(tok), now, self.cfg.eos_token)
+        self._last[rid] = int(tok)
+        if finished:
+            info = self.batcher.request_info(rid)
+            ttft = float(info["first_token_ms"] - info["arrival_ms"])
+            tpot = float(info["last_token_ms"] - info["first_token_ms"]) / max(1, n - 1)
+            self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
+            self.batcher.retire(rid)
+            self._last.pop(rid, None)
+        return TokenEvent(rid, int(tok), bool(finished))
+
+    # ---- helpers ------------------------------------------------------------------------------------------------
+    @property
+    def idle(self) -> bool:
+        return self.batcher.inflight_len == 0 and self.batcher.queued_len == 0
+
+    def run_until_done(self, max_steps: int = 1 << 20, on_event=None) -> dict[int, list[int]]:
+        out: dict[int, list[int]] = {}
+        steps = 0
+        while not self.idle and steps < max_steps:
+            evs = self.step()
+            if not evs and self.batcher.inflight_len == 0:
+                time.sleep(0.001)   # only delayed requests left: wait for their retry time
+            for ev in evs:
+                if ev.error is None:
+                    out.setdefault(ev.request_id, []).append(ev.token)
+                if on_event:
+                    on_event(ev)
+            steps += 1
+        return out
+
+    def generate(self, prompts, max_new_tokens: int = 32) -> list[list[int]]:
+        """Convenience: submit every prompt now and run to completion. Returns generated ids per prompt."""
+        ids = []
+        for p in prompts:
+            rid, d = self.submit(p, max_new_tokens)
+            if d.kind == "reject":
+                raise RuntimeError(f"request rejected: {d.reason}")
+            ids.append(rid)
+        res = self.run_until_done()
+        return [res.get(i, []) for i in ids]

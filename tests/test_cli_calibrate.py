@@ -1,0 +1,204 @@
+"""CLI (argument parsing, extract determinism, JSON output and error objects, compile -> verify -> serve on CPU),
+calibration (corpus validation, statistics, byte-stable writers, prompt sampling) and the launcher/rendezvous.
+
+Mirrors crates/skein_cli/tests/{arg_parsing,extract_e2e,output_formats}.rs, crates/skein_calibrate/tests/
+{corpus_loading,cost_writer_byte_stable}.rs and the unit tests in launcher.rs:81-110, rendezvous.rs:101-118.
+"""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from skein_b200 import calibrate as cal
+from skein_b200.cli.main import build_parser, main
+from skein_b200.parallel import launcher
+
+ROOT = Path(__file__).resolve().parent.parent
+ARGS = ["--model", str(ROOT / "configs/mixtral_8x7b_config.json"), "--cluster", str(ROOT / "cluster/h100_2x.toml"), "--trace",
+        str(ROOT / "cluster/sample_trace.jsonl"), "--drift", str(ROOT / "models/mixtral_8x7b_drift.toml"), "--cost", str(ROOT / "cluster/cost_constants.toml")]
+TINY = {"architectures": ["MixtralForCausalLM"], "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2, "num_attention_heads": 4,
+        "num_key_value_heads": 2, "head_dim": 128, "num_local_experts": 4, "num_experts_per_tok": 2, "vocab_size": 512, "rope_theta": 1e6,
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 512}
+
+
+def test_arg_parsing_all_subcommands():
+    p = build_parser()
+    a = p.parse_args(["--output", "json", "extract", *ARGS, "--out", "x.json"])
+    assert a.command == "extract" and a.output == "json" and a.out == "x.json"
+    a = p.parse_args(["compile", *ARGS, "--weights", "w/", "--enforce-parity", "--n-parity-prompts", "3"])
+    assert a.enforce_parity and a.n_parity_prompts == 3 and a.out == "artifacts/"
+    a = p.parse_args(["verify", "--artifact", "a", "--enforce", "--hf-reference", "--n-prompts", "7"])
+    assert a.enforce and a.hf_reference and a.n_prompts == 7 and a.cost == "cluster/cost_constants.toml"
+    a = p.parse_args(["serve", "--artifact", "a", "--gpus", "0,1", "--prompt", "hi"])
+    assert a.port == 8080 and a.max_new_tokens == 32 and a.rendezvous == "/tmp/skein_rendezvous" and a.gpus == "0,1"
+    a = p.parse_args(["calibrate", "--hardware", "b200", "--model", "m", "--corpus", "c"])
+    assert a.out_cost == "cluster/cost_constants.toml" and a.out_drift_dir == "models/"
+    a = p.parse_args(["bench", "--artifact", "a", "--workload", "w", "--baseline", "http://x", "--metrics", "throughput,goodput"])
+    assert a.metrics == "throughput,goodput"
+    with pytest.raises(SystemExit):
+        p.parse_args(["extract"])                       # required inputs missing
+
+
+def test_extract_end_to_end_deterministic_json(tmp_path, capsys):
+    out1, out2 = tmp_path / "p1.json", tmp_path / "p2.json"
+    assert main(["--output", "json", "extract", *ARGS, "--out", str(out1)]) == 0
+    rep1 = json.loads(capsys.readouterr().out)
+    assert main(["--output", "json", "extract", *ARGS, "--out", str(out2)]) == 0
+    rep2 = json.loads(capsys.readouterr().out)
+    assert out1.read_bytes() == out2.read_bytes() and rep1["content_hash"] == rep2["content_hash"]
+    assert set(rep1) >= {"plan_path", "content_hash", "cost_us", "search", "summary"} and rep1["search"]["raw"] == 560
+    assert main(["extract", *ARGS, "--out", str(out1)]) == 0
+    assert "placement   tp=" in capsys.readouterr().out
+
+
+def test_errors_are_json_objects_on_stderr(tmp_path, capsys):
+    bad = tmp_path / "cluster.toml"
+    bad.write_text((ROOT / "cluster/h100_2x.toml").read_text().replace("num_devices = 2", "num_devices = 5"))
+    args = list(ARGS)
+    args[3] = str(bad)
+    assert main(["--output", "json", "extract", *args, "--out", str(tmp_path / "p.json")]) == 1
+    err = json.loads(capsys.readouterr().err)
+    assert err["error"]["kind"] == "ClusterError" and "num_devices" in err["error"]["message"]
+
+
+def test_compile_verify_serve_job_cpu(tmp_path, capsys):
+    cfg = tmp_path / "tiny_config.json"
+    cfg.write_text(json.dumps(TINY))
+    drift = tmp_path / "tiny_drift.toml"
+    drift.write_text((ROOT / "models/mixtral_8x7b_drift.toml").read_text())
+    common = ["--model", str(cfg), "--cluster", str(ROOT / "cluster/b200_1x.toml"), "--trace", str(ROOT / "cluster/sample_trace.jsonl"),
+              "--drift", str(drift), "--cost", str(ROOT / "cluster/cost_constants.toml")]
+    assert main(["--output", "json", "compile", *common, "--out", str(tmp_path / "art"), "--n-parity-prompts", "2", "--enforce-parity"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["parity"]["passed"] and (tmp_path / "art" / "LATEST").is_symlink()
+    art = str(tmp_path / "art" / "LATEST")
+    art = str((tmp_path / "art" / os.readlink(art)))
+    assert main(["--output", "json", "verify", "--artifact", art, "--enforce", "--cost", str(ROOT / "cluster/cost_constants.toml"), "--n-prompts", "2"]) == 0
+    assert json.loads(capsys.readouterr().out)["passed"]
+    assert main(["--output", "json", "verify", "--artifact", art, "--hf-reference", "--cost", str(ROOT / "cluster/cost_constants.toml"), "--n-prompts", "2"]) == 0
+    hf = json.loads(capsys.readouterr().out)
+    assert hf["avg_final_kl"] < 0.05                    # runtime graph vs cache-free dense oracle
+    # generation job through the worker (single rank, CPU)
+    r = subprocess.run([sys.executable, "-m", "skein_b200.cli.main", "serve", "--artifact", art, "--prompt", "hello", "--max-new-tokens", "4",
+                        "--max-seq-len", "128"], capture_output=True, text=True, cwd=ROOT, timeout=300,
+                       env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert len(out["generated"][0]) == 4 and out["tokens_per_s"] > 0
+    # trace replay
+    assert main(["--output", "json", "bench", "--artifact", art, "--workload", str(ROOT / "cluster/sample_trace.jsonl"), "--max-requests", "2",
+                 "--time-scale", "1000"]) == 0
+    b = json.loads(capsys.readouterr().out)
+    assert b["requests_ok"] + b["requests_rejected"] == 2 and b["drift_compliance"] is True
+
+
+# ---- calibration ----------------------------------------------------------------------------------------------------
+CORPUS = """workload_trace_path = "traces/t.jsonl"
+n_drift_prompts = 4
+sampling_strategy = "stratified_by_length"
+sampling_seed = 0
+[[kernel_samples]]
+op_kind = "gemm"
+dtype = "bf16"
+shape = [4096, 4096]
+repeats = 10
+"""
+
+
+@pytest.mark.parametrize("old,new,msg", [
+    ('n_drift_prompts = 4', 'n_drift_prompts = 0', "n_drift_prompts"),
+    ('"stratified_by_length"', '"alphabetical"', "sampling_strategy"),
+    ('op_kind = "gemm"', 'op_kind = "fft"', "op_kind"),
+    ('dtype = "bf16"', 'dtype = "fp4"', "dtype"),
+    ('shape = [4096, 4096]', 'shape = [4096, 0]', "shape"),
+    ('shape = [4096, 4096]', 'shape = []', "shape"),
+    ('repeats = 10', 'repeats = 0', "repeats"),
+    ('workload_trace_path = "traces/t.jsonl"', 'workload_trace_path = ""', "workload_trace_path"),
+    ('n_drift_prompts = 4\n', '', "n_drift_prompts"),
+])
+def test_corpus_rejections(old, new, msg):
+    assert cal.Corpus.from_toml(CORPUS).kernel_samples[0].shape == [4096, 4096]
+    with pytest.raises(cal.CalibrationError, match=msg):
+        cal.Corpus.from_toml(CORPUS.replace(old, new))
+    with pytest.raises(cal.CalibrationError, match="kernel_samples"):
+        cal.Corpus.from_toml(CORPUS.split("[[kernel_samples]]")[0])
+
+
+def test_statistics_and_prompt_sampling():
+    assert cal.median([3, 1, 2]) == 2 and cal.median([]) == 0.0 and cal.median([1, 2, 3, 4]) == 3
+    assert cal.p95([10.0]) == 10.0 and cal.p95(list(map(float, range(1, 101)))) == pytest.approx(95.05)
+    lengths = [5, 500, 50, 5000, 20, 200, 2000, 10]
+    a = cal.sample_prompts(lengths, 4, "stratified_by_length", 0)
+    assert a == cal.sample_prompts(lengths, 4, "stratified_by_length", 0) and len(a) == 4
+    assert cal.sample_prompts(lengths, 3, "first_n", 9) == [0, 1, 2]
+    assert cal.sample_prompts(lengths, 4, "uniform_random", 1) != cal.sample_prompts(lengths, 4, "uniform_random", 2)
+    # one prompt per length stratum
+    srt = sorted(range(8), key=lambda i: lengths[i])
+    strata = [set(srt[0:2]), set(srt[2:4]), set(srt[4:6]), set(srt[6:8])]
+    assert all(len(s & set(a)) == 1 for s in strata)
+
+
+def test_cost_writer_is_byte_stable_and_preserves_unmeasured_entries():
+    text = (ROOT / "cluster/cost_constants.toml").read_text()
+    assert cal.write_cost_constants(text, {}) == text
+    new = cal.write_cost_constants(text, {("gemm", "bf16"): 0.91, ("attention", "bf16"): 0.33}, {"ring_allreduce": 0.8}, {"b200": 6600.0})
+    changed = [(a, b) for a, b in zip(text.split("\n"), new.split("\n")) if a != b]
+    assert len(changed) == 4 and len(text.split("\n")) == len(new.split("\n"))
+    assert "bf16     = 0.91" in new and "ring_allreduce = 0.8" in new and "b200      = 6600.0" in new
+    assert "fp8_e4m3 = 0.72" in new                       # unmeasured entry untouched
+    assert cal.write_cost_constants(new, {("gemm", "bf16"): 0.91}) == new
+    # comments after values survive; a new key lands inside its section
+    t2 = cal.rewrite_toml_values("[a]\nx = 1.0   # keep me\n[b]\ny = 2.0\n", {("a", "x"): 3.5, ("a", "z"): 7.0})
+    assert t2 == "[a]\nx = 3.5   # keep me\nz = 7.0\n[b]\ny = 2.0\n"
+
+
+def test_drift_writer_monotonic():
+    text = (ROOT / "models/mixtral_8x7b_drift.toml").read_text()
+    a = cal.write_drift_table(text, {(3, "weight", "fp8_e4m3"): 0.02})
+    assert "[layer.3.weight]\nfp8_e4m3 = 0.02" in a
+    assert cal.write_drift_table(a, {(3, "weight", "fp8_e4m3"): 0.01}) == a
+    assert cal.calibrate_drift([{"layer": 0, "mse": 0.5}, {"layer": 1, "mse": 0.1}],
+                               {"dtype_map": {"per_layer": [{"weight": "bf16", "activation": "bf16", "kv_cache": "bf16"},
+                                                            {"weight": "fp8_e4m3", "activation": "bf16", "kv_cache": "bf16"}]}}) == {(1, "weight", "fp8_e4m3"): 0.1}
+
+
+# ---- launcher / rendezvous ---------------------------------------------------------------------------------------------
+def test_launch_plan_and_commands():
+    plan = launcher.plan_launch(launcher.parse_gpus("3,5"), "/tmp/rdv")
+    assert [(l.rank, l.world_size, l.gpu) for l in plan] == [(0, 2, 3), (1, 2, 5)]
+    cmd, env = launcher.build_command(plan[1], ["--artifact", "a"], base_env={})
+    assert cmd[1:4] == ["-m", "skein_b200.parallel.worker", "--artifact"]
+    assert env == {"SKEIN_RANK": "1", "SKEIN_WORLD_SIZE": "2", "SKEIN_RENDEZVOUS": "/tmp/rdv", "CUDA_VISIBLE_DEVICES": "5"}
+    with pytest.raises(ValueError):
+        launcher.parse_gpus("1,1")
+    with pytest.raises(ValueError):
+        launcher.parse_gpus("")
+
+
+def test_rendezvous_publish_fetch_and_timeout(tmp_path):
+    p = str(tmp_path / "rdv")
+    with pytest.raises(launcher.RendezvousError, match="did not appear"):
+        launcher.fetch(p, timeout_s=0.1)
+    launcher.publish(p, b"hello")
+    assert launcher.fetch(p, 1.0) == b"hello" and not list(tmp_path.glob("*.tmp"))
+
+
+def test_two_cpu_ranks_meet_and_failure_is_counted(tmp_path):
+    script = ("import sys; sys.path.insert(0, %r)\nfrom skein_b200.parallel import launcher\nimport torch, torch.distributed as dist\n"
+              "r, w, p = launcher.world_from_env()\nif len(sys.argv) > 1 and r == 1: sys.exit(3)\n"
+              "launcher.init_process_group(r, w, p, 'gloo', timeout_s=30)\nt = torch.tensor([float(r + 1)])\ndist.all_reduce(t)\n"
+              "assert t.item() == 3.0\ndist.destroy_process_group()\n") % str(ROOT)
+    f = tmp_path / "rank.py"
+    f.write_text(script)
+
+    def run(extra):
+        procs = []
+        for l in launcher.plan_launch([0, 1], str(tmp_path / "rdv")):
+            _, env = launcher.build_command(l, [])
+            procs.append(subprocess.Popen([sys.executable, str(f), *extra], env=env))
+        return sum(p.wait(120) != 0 for p in procs)
+
+    assert run([]) == 0

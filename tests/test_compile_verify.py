@@ -1,0 +1,159 @@
+"""Artifact write -> load -> rebuild, the parity gate with fake forwards (pass / layer failure / KL failure),
+monotonic drift feedback and re-plan, LATEST symlink, hot-swap shape check.
+
+Mirrors crates/skein_compile/tests/{artifact_roundtrip,compile_e2e}.rs, crates/skein_parity/tests/
+{failure_handling,common}.rs (InMemoryReference, OffsetForward, TiltedForward) and
+crates/skein_runtime/tests/hotswap_drain.rs (shape-compat reject).
+"""
+import json
+import os
+from pathlib import Path
+
+import pytest
+import torch
+
+from skein_b200 import core
+from skein_b200.compile import parity
+from skein_b200.compile.artifact import Artifact, ArtifactError, WeightSource, build_artifact, update_latest_symlink, verify_shape_compatibility
+from skein_b200.compile.pipeline import compile_model
+from skein_b200.models.config import ModelConfig
+
+ROOT = Path(__file__).resolve().parent.parent
+CONST = (ROOT / "cluster/cost_constants.toml").read_text()
+TRACE = (ROOT / "cluster/sample_trace.jsonl").read_text()
+DRIFT = (ROOT / "models/mixtral_8x7b_drift.toml").read_text()
+TINY = json.dumps({"architectures": ["MixtralForCausalLM"], "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 3,
+                   "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "num_local_experts": 4, "num_experts_per_tok": 2,
+                   "vocab_size": 512, "rope_theta": 1e6, "rms_norm_eps": 1e-5, "max_position_embeddings": 1024})
+
+
+def cluster(n):
+    return (ROOT / f"cluster/b200_{n}x.toml").read_text()
+
+
+def test_artifact_roundtrip_sharded_weights_reassemble(tmp_path):
+    res = core.extract_plan(TINY, cluster(4), TRACE, DRIFT, CONST, {"force_tp": 2, "force_ep": 2, "force_pp": 1, "force_batch": 8},
+                            [["bf16", "bf16", "bf16"]])
+    cfg = ModelConfig.from_hf_dict(json.loads(TINY))
+    src = WeightSource(cfg, seed=3, std=0.05)
+    d = build_artifact(res["plan_json"], TINY, tmp_path, src)
+    assert d.name == res["content_hash"] and (d / "device_3" / "weights.safetensors").exists()
+    art = Artifact(d)
+    assert art.num_devices == 4
+    for dev in range(4):
+        art.check_lowering(dev)
+    full = art.load_full_weights("cpu")
+    # reassembled tensors equal the source tensors
+    assert torch.equal(full.embed, src.get("model.embed_tokens.weight", (512, 256)))
+    q = src.get("model.layers.1.self_attn.q_proj.weight", (512, 256))
+    assert torch.equal(full.layers[1].wqkv[:512], q)
+    w2 = src.get("model.layers.2.block_sparse_moe.experts.3.w2.weight", (256, 512))
+    assert torch.equal(full.layers[2].w2[3], w2)
+    # a rank's shard has the shard shapes
+    w = art.load_weights(3, "cpu")                       # ep 1, tp 1
+    assert w.layers[0].w13.shape == (2, 512, 256) and w.layers[0].w2.shape == (2, 256, 256) and w.lm_head.shape == (256, 256)
+    assert torch.equal(w.layers[0].w2[1], w2_like(src, 0, 3)[:, 256:])
+    # corruption is detected
+    (d / "device_0" / "segments.json").write_text("{}")
+    with pytest.raises(ArtifactError, match="does not match the plan"):
+        Artifact(d).check_lowering(0)
+    os.rename(d, tmp_path / "deadbeef")
+    with pytest.raises(ArtifactError, match="plan hash"):
+        Artifact(tmp_path / "deadbeef")
+
+
+def w2_like(src, layer, e):
+    return src.get(f"model.layers.{layer}.block_sparse_moe.experts.{e}.w2.weight", (256, 512))
+
+
+class FakeForward:
+    """Deterministic activations derived from the tokens (the reference's InMemoryReference), optionally with a
+    per-layer offset (OffsetForward) or a tilt of the logits only (TiltedForward)."""
+
+    def __init__(self, layers, offset_layer=None, offset=0.0, tilt=0.0):
+        self.layers, self.offset_layer, self.offset, self.tilt = layers, offset_layer, offset, tilt
+
+    def run(self, prompt):
+        g = torch.Generator().manual_seed(sum(prompt))
+        hid = [torch.randn(len(prompt), 8, generator=g) for _ in range(self.layers)]
+        logits = torch.randn(32, generator=g)
+        if self.offset_layer is not None:
+            hid[self.offset_layer] = hid[self.offset_layer] + self.offset
+        logits = logits + self.tilt * torch.arange(32.0)
+        return hid, logits
+
+
+def plan_dict(layers, fp8_layers=()):
+    return {"dtype_map": {"per_layer": [{"weight": "fp8_e4m3" if i in fp8_layers else "bf16", "activation": "bf16", "kv_cache": "bf16"}
+                                        for i in range(layers)]}}
+
+
+TOL = {"bf16": 1e-3, "fp8_e4m3": 5e-3}
+
+
+def test_parity_gate_pass_layer_fail_and_kl_fail():
+    prompts = [[1, 2, 3], [4, 5, 6, 7]]
+    plan = plan_dict(12, fp8_layers=(10,))
+    ok = parity.verify(FakeForward(12), FakeForward(12), prompts, plan, 0.01, TOL)
+    assert ok.passed and ok.avg_final_kl < 1e-9 and not ok.failing and ok.prompts == 2
+    bad = parity.verify(FakeForward(12, offset_layer=10, offset=0.2), FakeForward(12), prompts, plan, 0.01, TOL)
+    assert not bad.passed and [(f.layer, f.component, f.dtype) for f in bad.failing] == [(10, "weight", "fp8_e4m3")]
+    assert bad.failing[0].mse == pytest.approx(0.04, rel=1e-3)
+    # a small offset on the fp8 layer is inside its looser tolerance but would fail a bf16 layer
+    assert parity.verify(FakeForward(12, offset_layer=10, offset=0.05), FakeForward(12), prompts, plan, 0.01, TOL).passed
+    assert not parity.verify(FakeForward(12, offset_layer=3, offset=0.05), FakeForward(12), prompts, plan, 0.01, TOL).passed
+    kl = parity.verify(FakeForward(12, tilt=0.3), FakeForward(12), prompts, plan, 0.01, TOL)
+    assert not kl.passed and kl.avg_final_kl > 0.01 and kl.failing and kl.failing[0].layer == 10   # blamed on the quantised layer
+    rep = json.loads(kl.to_json())
+    assert set(rep) >= {"passed", "avg_final_kl", "layers", "failing"}
+
+
+def test_drift_update_is_monotonic():
+    plan = plan_dict(12, fp8_layers=(10,))
+    bad = parity.verify(FakeForward(12, offset_layer=10, offset=0.2), FakeForward(12), [[1, 2, 3]], plan, 0.01, TOL)
+    t1 = parity.update_drift_table_on_failure(DRIFT, bad)
+    assert core.DriftTable.from_toml(t1).lookup(10, "weight", "fp8_e4m3") == pytest.approx(0.04, rel=1e-3)
+    smaller = parity.verify(FakeForward(12, offset_layer=10, offset=0.1), FakeForward(12), [[1, 2, 3]], plan, 0.01, TOL)
+    t2 = parity.update_drift_table_on_failure(t1, smaller)
+    assert t2 == t1                                       # never lowered, byte-identical
+
+
+def test_compile_end_to_end_with_replan_and_latest(tmp_path):
+    # a drift budget that lets the planner pick fp8 weights somewhere, and tight memory so that it wants to
+    trace = TRACE.replace('"max_accuracy_drift": 0.01', '"max_accuracy_drift": 0.02')
+    tiny_mem = cluster(1).replace("device_memory_gb = 180", "device_memory_gb = 1")
+    r = compile_model(TINY, tiny_mem, trace, DRIFT, CONST, tmp_path, options={"force_batch": 4}, n_parity_prompts=2, seed=1)
+    assert (tmp_path / "LATEST").is_symlink() and os.readlink(tmp_path / "LATEST") == r.artifact_dir.name
+    assert (r.artifact_dir / "reference_bf16" / "plan.json").exists() and (r.artifact_dir / "parity_report.json").exists()
+    rep = json.loads((r.artifact_dir / "parity_report.json").read_text())
+    assert len(rep["layers"]) == 3 and r.report is not None
+    n_fp8 = sum(d["weight"] == "fp8_e4m3" for d in r.plan["dtype_map"]["per_layer"])
+    assert n_fp8 >= 1                                     # the dtype map is honoured, not clamped to bf16
+    art = Artifact(r.artifact_dir)
+    io0 = {t["name"]: t for t in art.io_manifest(0)["tensors"]}
+    fp8_layer = next(i for i, d in enumerate(r.plan["dtype_map"]["per_layer"]) if d["weight"] == "fp8_e4m3")
+    assert io0[f"model.layers.{fp8_layer}.self_attn.q_proj.weight"]["dtype"] == "fp8_e4m3"
+    from safetensors import safe_open
+    with safe_open(str(r.artifact_dir / "device_0" / "weights.safetensors"), framework="pt") as sf:
+        assert f"model.layers.{fp8_layer}.self_attn.q_proj.weight.scale" in sf.keys()
+    # real fp8 block-scaled weights pass the gate on this model
+    assert r.report.passed, r.report.to_json()
+    # enforce + impossible tolerance -> failure is raised after re-plans that push the drift table up
+    strict = CONST.replace("fp8_e4m3 = 5.0e-3", "fp8_e4m3 = 1.0e-12").replace("bf16     = 1.0e-3", "bf16     = 1.0e-3")
+    r2 = compile_model(TINY, tiny_mem, trace, DRIFT, strict, tmp_path / "b", options={"force_batch": 4}, n_parity_prompts=1, seed=1, max_replans=3)
+    assert r2.replans >= 1 and core.DriftTable.from_toml(r2.drift_toml).num_overrides() >= 1
+    assert r2.report.passed and all(d["weight"] == "bf16" for d in r2.plan["dtype_map"]["per_layer"])   # re-planned away from fp8
+
+
+def test_hot_swap_shape_check_and_atomic_symlink(tmp_path):
+    mk = lambda opts: build_artifact(core.extract_plan(TINY, cluster(2), TRACE, DRIFT, CONST, opts, [["bf16", "bf16", "bf16"]])["plan_json"],
+                                     TINY, tmp_path, write_weights=False)
+    a = Artifact(mk({"force_tp": 2, "force_ep": 1, "force_pp": 1, "force_batch": 8}))
+    b = Artifact(mk({"force_tp": 2, "force_ep": 1, "force_pp": 1, "force_batch": 16}))
+    c = Artifact(mk({"force_tp": 1, "force_ep": 2, "force_pp": 1, "force_batch": 8}))
+    verify_shape_compatibility(a, b)                      # same shards, different batch policy: compatible
+    with pytest.raises(ArtifactError, match="differs"):
+        verify_shape_compatibility(a, c)
+    update_latest_symlink(tmp_path, a.path)
+    update_latest_symlink(tmp_path, b.path)
+    assert os.readlink(tmp_path / "LATEST") == b.path.name and not list(tmp_path.glob(".LATEST*"))
