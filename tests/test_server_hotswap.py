@@ -1,0 +1,123 @@
+"""HTTP front end and hot swap on CPU: JSON and SSE completions, /metrics, 429 on rejection, 400 on bad bodies,
+a step failure closes the stream with an error while the server keeps serving; hot swap rejects incompatible
+artifacts, drains under load, and leaves the old artifact mounted when the drain times out.
+
+Mirrors crates/skein_runtime/tests/{serve_driver.rs:43-239, hotswap_drain.rs:55-142, observability_metrics.rs:14}.
+"""
+import asyncio
+import json
+import threading
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+from skein_b200 import core
+from skein_b200.compile.artifact import Artifact, build_artifact
+from skein_b200.models.decoder import Decoder
+from skein_b200.runtime.engine import Engine, EngineConfig
+from skein_b200.runtime.hotswap import HotSwap, HotSwapError
+from skein_b200.runtime.server import EngineDriver, build_app
+from skein_b200.runtime.tokenizer import Tokenizer
+
+ROOT = Path(__file__).resolve().parent.parent
+TINY = json.dumps({"architectures": ["LlamaForCausalLM"], "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2,
+                   "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 300, "rope_theta": 5e5,
+                   "rms_norm_eps": 1e-5, "max_position_embeddings": 256})
+INPUTS = ((ROOT / "cluster/b200_1x.toml").read_text(), (ROOT / "cluster/sample_trace.jsonl").read_text(),
+          (ROOT / "models/llama3_70b_drift.toml").read_text(), (ROOT / "cluster/cost_constants.toml").read_text())
+
+
+def make_artifact(tmp_path, seed=0, batch=4, cfg=TINY):
+    from skein_b200.compile.artifact import WeightSource
+    from skein_b200.models.config import ModelConfig
+    plan = core.extract_plan(cfg, *INPUTS, {"force_batch": batch}, [["bf16", "bf16", "bf16"]])["plan_json"]
+    c = ModelConfig.from_hf_dict(json.loads(cfg))
+    return Artifact(build_artifact(plan, cfg, tmp_path, WeightSource(c, seed=seed, std=0.05)))
+
+
+def make_engine(art, **kw):
+    dec = Decoder(art.cfg, art.load_weights(0, "cpu"), art.layout(0), num_pages=64, page_size=16, max_pos=256)
+    return Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, **kw))
+
+
+def test_tokenizer_fallback():
+    t = Tokenizer(300)
+    assert t.is_fallback and t.encode("hi") == [104, 105] and t.decode([104, 105]) == "hi"
+    assert Tokenizer(50).encode("hi") == [104 % 50, 105 % 50]
+
+
+def test_http_completions_stream_metrics_and_errors(tmp_path):
+    from aiohttp.test_utils import TestClient, TestServer
+
+    art = make_artifact(tmp_path)
+    eng = make_engine(art)
+    driver = EngineDriver(eng).start()
+
+    async def scenario():
+        async with TestClient(TestServer(build_app(driver, Tokenizer(300)))) as c:
+            r = await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 3})
+            assert r.status == 200
+            body = await r.json()
+            assert len(body["tokens"]) == 3 and isinstance(body["text"], str)
+            r = await c.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 4, "stream": True})
+            assert r.status == 200 and r.headers["Content-Type"].startswith("text/event-stream")
+            events = [json.loads(l[6:]) for l in (await r.text()).splitlines() if l.startswith("data: ")]
+            assert len(events) == 4 and events[-1]["is_final"] and not events[0]["is_final"] and all("token" in e for e in events)
+            assert (await c.post("/v1/completions", json={"max_tokens": 3})).status == 400
+            assert (await c.post("/v1/completions", data=b"not json")).status == 400
+            r = await c.post("/v1/completions", json={"prompt": [1] * 250, "max_tokens": 100})
+            assert r.status == 429                               # prompt + max_tokens beyond the position limit
+            m = await (await c.get("/metrics")).text()
+            assert 'skein_requests_total{status="ok"} 2' in m and "skein_steps_total" in m and "skein_kv_pages_in_use" in m
+            assert (await (await c.get("/healthz")).json())["ok"]
+            # a failing step: the stream ends with an error event, the next request is served
+            eng.failure_injector = lambda step: (_ for _ in ()).throw(RuntimeError("boom"))
+            r = await c.post("/v1/completions", json={"prompt": [1, 2], "max_tokens": 3})
+            assert r.status == 503 and "boom" in (await r.json())["error"]["message"]
+            eng.failure_injector = None
+            assert (await c.post("/v1/completions", json={"prompt": [1, 2], "max_tokens": 2})).status == 200
+
+    try:
+        asyncio.run(asyncio.wait_for(scenario(), 120))
+    finally:
+        driver.stop()
+
+
+def test_hot_swap_reject_drain_and_timeout(tmp_path):
+    a = make_artifact(tmp_path / "a", seed=0)
+    b = make_artifact(tmp_path / "b", seed=1, batch=8)           # same shapes, other weights and batch policy
+    wide = json.loads(TINY); wide["intermediate_size"] = 1024
+    c = make_artifact(tmp_path / "c", cfg=json.dumps(wide))
+    eng = make_engine(a)
+    driver = EngineDriver(eng).start()
+    try:
+        hs = HotSwap(driver, a, drain_timeout_s=30.0)
+        with pytest.raises(HotSwapError, match="rejected"):
+            hs.swap(c.path)
+        # drain under load: requests in flight finish, then the weights change
+        subs = [driver.submit([3, 4, 5], 6) for _ in range(3)]
+        t = threading.Thread(target=lambda: hs.swap(b.path, tmp_path))
+        t.start()
+        done = []
+        for rid, kind, reason, q in subs:
+            while True:
+                ev = q.get(timeout=60)
+                if ev.is_final:
+                    done.append(ev.error)
+                    break
+        t.join(60)
+        assert done == [None, None, None] and hs.mounted.path == b.path and not driver.draining
+        assert (tmp_path / "LATEST").is_symlink()
+        w_new = b.load_weights(0, "cpu")
+        assert torch.equal(eng.dec.w.layers[0].wqkv, w_new.layers[0].wqkv)
+        # drain timeout: a long request keeps the old artifact mounted and admission resumes
+        hs2 = HotSwap(driver, b, drain_timeout_s=0.01)
+        rid, kind, reason, q = driver.submit([1, 2, 3], 200)
+        with pytest.raises(HotSwapError, match="timed out"):
+            hs2.swap(a.path)
+        assert hs2.mounted.path == b.path and not driver.draining
+        assert driver.submit([9], 1)[1] in ("admit", "delay")
+    finally:
+        driver.stop()
