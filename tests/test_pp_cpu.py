@@ -1,0 +1,20 @@
+"""Pipeline parallelism with two CPU ranks (gloo): see workers/pp_worker.py."""
+import os
+import subprocess
+import sys
+
+from skein_b200.parallel import launcher
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_two_stage_pipeline_matches_single_stage(tmp_path):
+    procs = []
+    for l in launcher.plan_launch([0, 1], str(tmp_path / "rdv")):
+        _, env = launcher.build_command(l, [])
+        env["CUDA_VISIBLE_DEVICES"] = ""
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "workers", "pp_worker.py")], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=300) for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[1][-2000:] for o in outs)
+    assert "PP_WORKER_OK" in outs[0][0]

@@ -1,0 +1,89 @@
+"""Pipeline-parallel worker (gloo on CPU, or nccl on GPUs): pp stages reproduce the single-stage model, both
+through the plain stage-by-stage step and through the micro-batched pipelined decode."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from skein_b200.models import config as mc  # noqa: E402
+from skein_b200.models.decoder import BatchInputs, Decoder, random_weights  # noqa: E402
+from skein_b200.models.sharding import shard_model  # noqa: E402
+from skein_b200.parallel import launcher, pp  # noqa: E402
+from skein_b200.runtime.runner import ModelRunner  # noqa: E402
+
+
+def main():
+    rank, world, rdv = launcher.world_from_env()
+    use_cuda = os.environ.get("PP_WORKER_DEVICE", "cpu") == "cuda"
+    dev = torch.device("cuda", 0) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(dev)
+    launcher.init_process_group(rank, world, rdv, "nccl" if use_cuda else "gloo", timeout_s=60, device=dev if use_cuda else None)
+    cfg = mc.tiny_mixtral(layers=5)                      # 5 blocks over 2 stages: 3 + 2
+    full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=21, std=0.05)
+    lay = mc.ParallelLayout(pp=world, rank=rank)
+    _, pp_ranks, pp_group = pp.make_groups((1, world, 1), rank)
+    fb_group = dist.new_group(list(range(world)))
+    dec = Decoder(cfg, shard_model(full, cfg, lay, dev), lay, num_pages=32, page_size=16, max_pos=128)
+    stage = pp.PipelineStage(dec, lay, pp_ranks, pp_group)
+    assert len(dec.w.layers) == (3 if rank == 0 else 2)
+    g = torch.Generator().manual_seed(3)
+    B = 4
+    prompts = torch.randint(0, cfg.vocab_size, (B, 18), generator=g).tolist()
+    tables = [[1 + 4 * s + i for i in range(4)] for s in range(B)]
+
+    def gen(model, steps=4):
+        runner = ModelRunner(model, max_blocks_per_seq=4, use_graphs=False)
+        outs = [runner.prefill([(prompts[s], tables[s], 0) for s in range(B)])]
+        bk, cached = runner.bucket(B), 18
+        for _ in range(steps):
+            runner.load_decode_inputs(bk, outs[-1], [cached] * B, [cached + 1] * B, tables)
+            outs.append(runner.decode_step(bk)[:B].tolist())
+            cached += 1
+        return outs
+
+    got = gen(stage)
+    want = gen(Decoder(cfg, full, num_pages=32, page_size=16, max_pos=128)) if rank == 0 else None
+    if rank == 0:
+        assert got == want, (got, want)
+
+    # micro-batched pipelined decode: 2 micro-batches of 2 sequences, continuing from a fresh prefill
+    for kv in dec.kv:
+        kv.zero_()
+    runner = ModelRunner(stage, max_blocks_per_seq=4, use_graphs=False)
+    first = runner.prefill([(prompts[s], tables[s], 0) for s in range(B)])
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    micro = []
+    for m in range(2):
+        rows = [2 * m, 2 * m + 1]
+        bt = torch.zeros(2, 4, dtype=torch.int32, device=dev)
+        for i, r in enumerate(rows):
+            bt[i] = i32(tables[r])
+        micro.append(BatchInputs(token_ids=i32([first[r] for r in rows]), positions=i32([18, 18]), block_table=bt, seq_lens=i32([19, 19])))
+
+    def advance(inp, toks):
+        if toks is not None:
+            inp.token_ids.copy_(toks)
+        inp.positions.add_(1)
+        inp.seq_lens.add_(1)
+
+    out = pp.pipelined_decode(stage, micro, 4, advance, fb_group)
+    if rank == world - 1:
+        piped = [[int(x) for m in range(2) for x in out[t][m].tolist()] for t in range(4)]
+    else:
+        piped = None
+    box = [piped]
+    dist.broadcast_object_list(box, src=world - 1)
+    if rank == 0:
+        assert box[0] == want[1:], (box[0], want[1:])
+        print("PP_WORKER_OK world", world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
