@@ -1,0 +1,70 @@
+"""Host-side failure detection: heartbeats in a shared directory and a monitor that declares a rank dead.
+
+Each rank touches `<dir>/rank_<r>.hb` with a monotonically increasing counter from a daemon thread. The
+monitor (any rank, or the launcher) reads the files; a rank whose counter has not moved for
+`missed_beats x interval` is reported dead, after which the caller aborts its communicator / stops launching
+fused steps and fails in-flight requests with a retriable status. Nothing here touches a GPU: device-side
+waits are bounded on their own (status word), this layer catches ranks that died on the host.
+
+The reference has no heartbeat (its launcher only counts failed children at exit:
+crates/skein_cli/src/cmd/serve.rs:256-298); its shared-memory all-reduce spins forever on a dead peer
+(crates/skein_runtime/src/cuda/shm_allreduce.rs:53).
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from pathlib import Path
+
+
+class Heartbeat:
+    def __init__(self, directory: str, rank: int, interval_s: float = 0.2):
+        self.path = Path(directory) / f"rank_{rank}.hb"
+        self.interval_s = interval_s
+        self._stop = threading.Event()
+        self._n = 0
+        self._t = threading.Thread(target=self._run, daemon=True)
+        Path(directory).mkdir(parents=True, exist_ok=True)
+
+    def start(self):
+        self._beat()
+        self._t.start()
+        return self
+
+    def stop(self):
+        self._stop.set()
+        self._t.join(2.0)
+
+    def _beat(self):
+        self._n += 1
+        tmp = self.path.with_suffix(".tmp")
+        tmp.write_text(str(self._n))
+        os.replace(tmp, self.path)
+
+    def _run(self):
+        while not self._stop.wait(self.interval_s):
+            self._beat()
+
+
+class Monitor:
+    def __init__(self, directory: str, world: int, interval_s: float = 0.2, missed_beats: int = 5):
+        self.dir, self.world = Path(directory), world
+        self.limit_s = interval_s * missed_beats
+        self._last = {}     # rank -> (counter, time it last changed)
+
+    def dead_ranks(self, now: float | None = None) -> list[int]:
+        now = time.monotonic() if now is None else now
+        dead = []
+        for r in range(self.world):
+            p = self.dir / f"rank_{r}.hb"
+            try:
+                n = int(p.read_text() or 0)
+            except (FileNotFoundError, ValueError):
+                n = -1
+            prev = self._last.get(r)
+            if prev is None or prev[0] != n:
+                self._last[r] = (n, now)
+            elif now - prev[1] > self.limit_s:
+                dead.append(r)
+        return dead
