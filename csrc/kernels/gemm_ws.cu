@@ -21,6 +21,7 @@
 // host/cublaslt/mod.rs:888-1130), its fp8 GEMV (same file :797-886) and the GLUMoE GEMV kernels
 // (host/moe/mod.rs:229-381) with one tensor-core kernel.
 #include "gemm_ws.cuh"
+#include "gemm_sched.cuh"
 #include "ptx.cuh"
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -46,30 +47,6 @@ struct KernelArgs {
   uint64_t budget_ns;
 };
 
-struct Sched {
-  int pre[SKEIN_MAX_GROUPS + 1];  // first unit of each group
-  int cnt[SKEIN_MAX_GROUPS];
-  int off[SKEIN_MAX_GROUPS];
-  int ntile[SKEIN_MAX_GROUPS];
-  int MT, KB, U, per;
-  long long TK;
-};
-
-struct Unit { int g, m, n; };
-
-__device__ __forceinline__ Unit decode_unit(const Sched& s, int G, int u) {
-  int g = 0;
-  while (g + 1 < G && u >= s.pre[g + 1]) ++g;
-  int r = u - s.pre[g];
-  Unit x;
-  x.g = g;
-  x.m = r / s.ntile[g];
-  x.n = r - x.m * s.ntile[g];
-  return x;
-}
-
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-
 template <bool DUAL>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -93,29 +70,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // ---- set-up ---------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    const int G = p.G;
-    const int MT = (p.F + TILE_F - 1) / TILE_F;
-    int acc = 0;
-    for (int g = 0; g < G; ++g) {
-      const int c = p.group_cnt ? p.group_cnt[g] : p.t_static;
-      const int o = p.group_off ? p.group_off[g] : 0;
-      const int nt = (c + p.n_tile - 1) / p.n_tile;
-      sched.cnt[g] = c;
-      sched.off[g] = o;
-      sched.ntile[g] = nt > 0 ? nt : 1;  // never divide by zero; such a group has no units
-      sched.pre[g] = acc;
-      acc += MT * nt;
-    }
-    sched.pre[G] = acc;
-    sched.MT = MT;
-    sched.KB = p.K / (p.fp8 ? 128 : 64);
-    sched.U = acc;
-    sched.TK = (long long)acc * sched.KB;
-    // equal share per CTA, but never so small that a tile is cut into more than 8 pieces
-    long long per = (sched.TK + gridDim.x - 1) / gridDim.x;
-    const long long min_per = sched.KB >= 32 ? sched.KB / 8 : 4;
-    if (per < min_per) per = min_per;
-    sched.per = (int)per;
+    build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x);
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);

@@ -23,6 +23,7 @@ from dataclasses import dataclass, field
 import torch
 
 from .. import ops
+from ..ops import fp8
 from ..ops import reference as ref
 from .config import ModelConfig, ParallelLayout
 
@@ -91,6 +92,20 @@ def random_weights(cfg: ModelConfig, lay: ParallelLayout, device, seed: int = 0,
         lm_head=rnd(sh["V_local"], H) if last else None)
 
 
+def quantize_blocks(weights: ModelWeights, blocks, names=("wqkv", "wo", "w13", "w2"), drop_bf16: bool = True) -> None:
+    """Replace the named projections of the listed blocks (indices into weights.layers) by block-scaled e4m3
+    copies, as the plan's per-layer dtype map asks. With drop_bf16 the bf16 tensors are released."""
+    for b in blocks:
+        lw = weights.layers[b]
+        for name in names:
+            w = getattr(lw, name)
+            if w is None or name in lw.fp8 or w.shape[-1] % 128 != 0:
+                continue
+            lw.fp8[name] = fp8.quantize_weight(w)
+            if drop_bf16:
+                setattr(lw, name, None)
+
+
 @dataclass
 class BatchInputs:
     """Device-side description of one step (prefill chunk or decode step)."""
@@ -116,7 +131,7 @@ class Decoder:
         self.comm = comm  # tensor-parallel communicator (skein_b200.parallel.tp.TPComm) or None
         self.sh = shard_shapes(cfg, self.layout)
         self.page_size = page_size
-        dev = (weights.embed if weights.embed is not None else weights.layers[0].wqkv).device
+        dev = (weights.embed if weights.embed is not None else weights.layers[0].attn_norm).device
         self.device = dev
         self.max_pos = max_pos or cfg.max_position_embeddings
         self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev)
@@ -128,7 +143,7 @@ class Decoder:
     # ---- pieces ---------------------------------------------------------------------------------
     def _attention(self, li: int, normed, inp: BatchInputs):
         cfg, sh, lw = self.cfg, self.sh, self.w.layers[li]
-        qkv = ops.linear(normed, lw.wqkv)
+        qkv = self._col_linear(normed, lw, "wqkv")
         ops.rope_kv_append(qkv, inp.positions, inp.seq_of_token, inp.block_table, self.cos_sin, self.kv[li],
                            sh["Hq"], sh["Hkv"], cfg.head_dim)
         if inp.is_prefill:
@@ -137,9 +152,30 @@ class Decoder:
         return ops.attn_decode(qkv, self.kv[li], inp.block_table, inp.seq_lens, sh["Hq"], sh["Hkv"], cfg.head_dim,
                                ctx_hint=inp.ctx_hint)
 
-    def _row_parallel(self, x, w, grouped=None):
+    def _col_linear(self, x, lw, name, swiglu=False, grouped=None, rows_hint=None):
+        """Column-parallel (local) projection through the block's bf16 weight or, when the plan's dtype map
+        selected fp8 for this block, its block-scaled e4m3 copy (activations quantised on the fly)."""
+        w8 = lw.fp8.get(name)
+        if w8 is not None:
+            xq, xs = ops.quant_fp8_block128(x)
+            if grouped is not None:
+                return fp8.grouped_linear(xq, xs, w8, *grouped, swiglu=swiglu, rows_hint=rows_hint)
+            return fp8.linear(xq, xs, w8, swiglu=swiglu)
+        w = getattr(lw, name)
+        if grouped is not None:
+            return ops.grouped_linear(x, w, *grouped, swiglu=swiglu, rows_hint=rows_hint)
+        return ops.swiglu_linear(x, w) if swiglu else ops.linear(x, w)
+
+    def _row_parallel(self, x, lw, name, grouped=None):
         """Row-parallel projection. Returns (partial [n_src, rows, H], flags, epoch) for the fused reduce."""
-        if self.comm is None or self.comm.size == 1:
+        single = self.comm is None or self.comm.size == 1
+        w8 = lw.fp8.get(name)
+        if w8 is not None and single:
+            return self._col_linear(x, lw, name, grouped=grouped).unsqueeze(0), None, None
+        w = getattr(lw, name)
+        if w is None:
+            w = w8.dequant()      # fp8 row-parallel projections under TP run W8A16 until the fp8 push epilogue lands
+        if single:
             y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
             return y.unsqueeze(0), None, None
         return self.comm.linear_push(x, w, grouped)
@@ -148,8 +184,8 @@ class Decoder:
         """Returns (partial, flags, epoch, row_idx, row_w) feeding the fused combine/reduce."""
         cfg, lw = self.cfg, self.w.layers[li]
         if not cfg.is_moe:
-            h = ops.swiglu_linear(normed, lw.w13)
-            part, flags, epoch = self._row_parallel(h, lw.w2)
+            h = self._col_linear(normed, lw, "w13", swiglu=True)
+            part, flags, epoch = self._row_parallel(h, lw, "w2")
             return part, flags, epoch, None, None
         T = normed.shape[0]
         e_local = self.sh["E_local"]
@@ -157,8 +193,8 @@ class Decoder:
         ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
         xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
         cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
-        h = ops.grouped_linear(xs, lw.w13, cnt_l, off_l, swiglu=True, rows_hint=T * cfg.top_k)
-        part, flags, epoch = self._row_parallel(h, lw.w2, (cnt_l, off_l))
+        h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k)
+        part, flags, epoch = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
         return part, flags, epoch, row_of.view(T, cfg.top_k), wts
 
     # ---- the step ---------------------------------------------------------------------------------
@@ -175,7 +211,7 @@ class Decoder:
         last_stage = self.w.final_norm is not None
         for li, lw in enumerate(layers):
             attn = self._attention(li, normed, inp)
-            part, flags, epoch = self._row_parallel(attn, lw.wo)
+            part, flags, epoch = self._row_parallel(attn, lw, "wo")
             residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
                                                            flags=flags, epoch=epoch)
             part, flags, epoch, row_idx, row_w = self._ffn(li, normed)

@@ -1,0 +1,123 @@
+"""Block-scaled fp8 (e4m3, one fp32 scale per 1 x 128 block along K) linear operators.
+
+Weights are quantised once (`quantize_weight`), activations on the fly (`ops.quant_fp8_block128`); the GEMM
+(csrc/kernels/gemm_ws_fp8.cu) multiplies e4m3 x e4m3 on the tensor cores and applies both scales per
+K-block. On CPU the same math runs through the fp32 reference (dequantise, matmul).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib, functional as F, reference as ref
+
+_lib.register_optional("skein_gemm_ws_fp8", C.c_int, [C.POINTER(_lib.GemmParams), C.c_void_p])
+
+
+class Fp8Weight:
+    """q: e4m3 [rows, K] (or [G, rows, K]); scale_t: fp32 [K/128, rows_total] (K-block major, the layout the
+    kernel reads with coalesced loads). `shape` is the logical shape."""
+
+    def __init__(self, q: torch.Tensor, scale_t: torch.Tensor, shape):
+        self.q, self.scale_t, self.shape = q, scale_t, tuple(shape)
+        self.device = q.device
+
+    @property
+    def is_cuda(self):
+        return self.q.is_cuda
+
+    def dequant(self) -> torch.Tensor:
+        rows_total = self.scale_t.shape[1]
+        K = self.shape[-1]
+        w = ref.dequant_fp8_block128(self.q.reshape(rows_total, K), self.scale_t.t().contiguous())
+        return w.view(*self.shape).to(torch.bfloat16)
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.scale_t.numel() * 4
+
+
+def quantize_weight(w: torch.Tensor) -> Fp8Weight:
+    shape = tuple(w.shape)
+    K = shape[-1]
+    w2 = w.reshape(-1, K).contiguous()
+    q, s = F.quant_fp8_block128(w2) if w2.is_cuda else ref.quant_fp8_block128(w2)
+    return Fp8Weight(q.view(*shape), s.t().contiguous(), shape)
+
+
+def _launch(p, what):
+    ws = F.workspace()
+    p.workspace = ws.gemm_ws.data_ptr()
+    p.counters = ws.gemm_counters.data_ptr()
+    p.status = ws.status.data_ptr()
+    L = _lib.lib()
+    if not hasattr(L, "skein_gemm_ws_fp8"):
+        raise RuntimeError("libskein_kernels.so was built without the fp8 GEMM; rebuild with `python -m skein_b200._build`")
+    _lib.check(L.skein_gemm_ws_fp8(C.byref(p), _lib.stream_ptr()), what)
+    _lib.count_launch()
+
+
+def _n_tile(rows_hint: int, dual: bool) -> int:
+    cap = 32 if dual else 64
+    return max(16, min(cap, (max(rows_hint, 1) + 15) // 16 * 16 if rows_hint <= cap else cap))
+
+
+def _ref_linear(xq, xs, w: Fp8Weight, swiglu):
+    x = ref.dequant_fp8_block128(xq, xs)
+    wd = w.dequant().float()
+    if swiglu:
+        I = wd.shape[-2] // 2
+        return (torch.nn.functional.silu(x @ wd[:I].t()) * (x @ wd[I:].t())).to(torch.bfloat16)
+    return (x @ wd.t()).to(torch.bfloat16)
+
+
+def linear(xq, xs, w: Fp8Weight, swiglu: bool = False, out=None, n_tile=None):
+    """xq e4m3 [T, K], xs fp32 [T, K/128] -> bf16 [T, F] (F = rows, or rows/2 with the SwiGLU pair epilogue)."""
+    if not xq.is_cuda:
+        return _ref_linear(xq, xs, w, swiglu)
+    T, K = xq.shape
+    rows = w.shape[-2]
+    Fo = rows // 2 if swiglu else rows
+    if out is None:
+        out = torch.empty(T, Fo, dtype=torch.bfloat16, device=xq.device)
+    if T == 0:
+        return out
+    p = _lib.GemmParams()
+    p.W, p.X, p.out = w.q.data_ptr(), xq.data_ptr(), out.data_ptr()
+    p.w_scale, p.x_scale = w.scale_t.data_ptr(), xs.data_ptr()
+    p.G, p.F, p.K = 1, Fo, K
+    p.w_rows_per_group, p.up_row_off = rows, (Fo if swiglu else 0)
+    p.x_rows, p.t_static = T, T
+    p.n_tile = n_tile or _n_tile(T, swiglu)
+    p.ldo, p.mode, p.fp8 = out.stride(0), (1 if swiglu else 0), 1
+    _launch(p, "fp8 linear")
+    return out
+
+
+def grouped_linear(xq, xs, w: Fp8Weight, counts, offsets, swiglu: bool = False, out=None, n_tile=None, rows_hint=None):
+    """Per-expert fp8 linear over expert-sorted rows. w.shape = [E, rows, K]."""
+    if not xq.is_cuda:
+        x = ref.dequant_fp8_block128(xq, xs).to(torch.bfloat16)
+        return ref.grouped_linear(x, w.dequant(), counts, offsets, swiglu)
+    R, K = xq.shape
+    E, rows = w.shape[0], w.shape[1]
+    Fo = rows // 2 if swiglu else rows
+    if out is None:
+        out = torch.empty(R, Fo, dtype=torch.bfloat16, device=xq.device)
+    if R == 0:
+        return out
+    if n_tile is None:
+        avg = (rows_hint if rows_hint is not None else R) / E
+        n_tile = _n_tile(int(math.ceil(avg * 1.5)), swiglu)
+    p = _lib.GemmParams()
+    p.W, p.X, p.out = w.q.data_ptr(), xq.data_ptr(), out.data_ptr()
+    p.w_scale, p.x_scale = w.scale_t.data_ptr(), xs.data_ptr()
+    p.G, p.F, p.K = E, Fo, K
+    p.w_rows_per_group, p.up_row_off = rows, (Fo if swiglu else 0)
+    p.x_rows, p.t_static = R, R
+    p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
+    p.n_tile = n_tile
+    p.ldo, p.mode, p.fp8 = out.stride(0), (1 if swiglu else 0), 1
+    _launch(p, "fp8 grouped_linear")
+    return out

@@ -128,3 +128,19 @@ def test_cuda_graph_decode_equals_eager():
         runner.decode_loop_step(bk)
         loop.append(bk.dev_out[:3].tolist())
     assert loop == eager
+
+
+def test_fp8_blocks_track_the_bf16_model_cpu():
+    """Blocks switched to block-scaled e4m3 weights (and on-the-fly quantised activations) stay close to bf16."""
+    from skein_b200.models.decoder import quantize_blocks
+    cfg = mc.tiny_mixtral(layers=3)
+    torch.manual_seed(4)
+    w, dec = _build(cfg, "cpu", seed=8)
+    ids = torch.randint(0, cfg.vocab_size, (30,)).tolist()
+    lg_bf16, _ = _run_sequence(dec, ids, [30], 0)
+    w8, dec8 = _build(cfg, "cpu", seed=8)
+    quantize_blocks(w8, [1, 2])
+    assert w8.layers[1].w13 is None and "w13" in w8.layers[1].fp8 and not w8.layers[0].fp8
+    lg_fp8, _ = _run_sequence(dec8, ids, [30], 0)
+    a, b = lg_fp8.float(), lg_bf16.float()
+    assert 0 < float((a - b).norm() / b.norm()) < 0.15
