@@ -27,6 +27,8 @@ struct NormParams {
   const __nv_bfloat16* partial;    // [n_src][rows][H] or null
   const int* row_idx;              // [B, topk] rows into partial, or null (row = b)
   const float* row_w;              // [B, topk] weights, or null
+  const int* owner_ids;            // [B, topk] expert id of each pair, or null: with it only the sources that own the
+                                   // expert are read: ranks (id / experts_per_owner) * owner_span .. + owner_span - 1
   const __nv_bfloat16* gamma;      // [H] or null (no normalisation, normed_out unused)
   __nv_bfloat16* residual_out;     // [B, H] or null
   __nv_bfloat16* normed_out;       // [B, H] or null
@@ -35,6 +37,7 @@ struct NormParams {
   int* status;
   long long src_stride;            // elements between sources in `partial`
   int B, H, n_src, topk;
+  int experts_per_owner, owner_span;
   float eps;
   unsigned long long budget_ns;
 };
@@ -92,7 +95,13 @@ __global__ void __launch_bounds__(512) reduce_residual_rmsnorm_kernel(const Norm
         const int row = p.row_idx ? p.row_idx[b * p.topk + j] : b;
         if (row < 0) continue;  // pair routed to an expert that lives on another rank
         const float w = p.row_w ? p.row_w[b * p.topk + j] : 1.f;
-        for (int s = 0; s < p.n_src; ++s) {
+        int s_lo = 0, s_hi = p.n_src;
+        if (p.owner_ids) {
+          s_lo = (p.owner_ids[b * p.topk + j] / p.experts_per_owner) * p.owner_span;
+          s_hi = s_lo + p.owner_span;
+          if (s_lo < 0 || s_hi > p.n_src) continue;
+        }
+        for (int s = s_lo; s < s_hi; ++s) {
           const __nv_bfloat16* src = p.partial + (size_t)s * p.src_stride + (size_t)row * p.H + h;
           uint4 r;
           // data written by other GPUs: bypass L1
@@ -143,13 +152,15 @@ __global__ void __launch_bounds__(512) reduce_residual_rmsnorm_kernel(const Norm
 extern "C" int skein_reduce_residual_rmsnorm(
     const void* residual, const void* partial, const int* row_idx, const float* row_w, const void* gamma,
     void* residual_out, void* normed_out, const int* flags, const int* epoch, int* status,
-    long long src_stride, int B, int H, int n_src, int topk, float eps, int wait_budget_ms, void* stream) {
+    long long src_stride, int B, int H, int n_src, int topk, float eps, int wait_budget_ms, const int* owner_ids,
+    int experts_per_owner, int owner_span, void* stream) {
   using namespace skein;
   if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0) return -1;
   if (B == 0) return 0;
   NormParams p;
   p.residual = (const __nv_bfloat16*)residual; p.partial = (const __nv_bfloat16*)partial;
   p.row_idx = row_idx; p.row_w = row_w; p.gamma = (const __nv_bfloat16*)gamma;
+  p.owner_ids = owner_ids; p.experts_per_owner = experts_per_owner > 0 ? experts_per_owner : 1; p.owner_span = owner_span > 0 ? owner_span : 1;
   p.residual_out = (__nv_bfloat16*)residual_out; p.normed_out = (__nv_bfloat16*)normed_out;
   p.flags = flags; p.epoch = epoch; p.status = status; p.src_stride = src_stride;
   p.B = B; p.H = H; p.n_src = n_src; p.topk = topk; p.eps = eps;

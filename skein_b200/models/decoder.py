@@ -126,9 +126,13 @@ class Decoder:
     """One rank's share of the model: weights, KV cache and the step function."""
 
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
-                 num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None):
+                 num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None):
         self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
-        self.comm = comm  # tensor-parallel communicator (skein_b200.parallel.tp.TPComm) or None
+        self.comm = comm          # tensor-parallel communicator over this rank's TP group, or None
+        self.comm_moe = comm_moe  # communicator over all tp x ep ranks of the stage (expert parallelism), or None
+        self._owner = None
+        if self.layout.ep > 1 and comm_moe is None:
+            raise ValueError("expert parallelism needs a communicator over the stage's tp x ep ranks (comm_moe)")
         self.sh = shard_shapes(cfg, self.layout)
         self.page_size = page_size
         dev = (weights.embed if weights.embed is not None else weights.layers[0].attn_norm).device
@@ -190,6 +194,19 @@ class Decoder:
         T = normed.shape[0]
         e_local = self.sh["E_local"]
         first = self.layout.ep_rank * e_local
+        if self.layout.ep > 1:
+            # Expert parallel: every rank of the stage routes all tokens the same way (global expert-sorted
+            # layout), computes only the rows of the experts it owns, and its down projection stores those rows
+            # into every rank's receive slot; the combine then reads each (token, slot) pair from the ranks that
+            # own its expert. Row positions are global, so no index exchange is needed.
+            ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k)
+            xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+            cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
+            h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep)
+            w2 = lw.w2 if lw.w2 is not None else lw.fp8["w2"].dequant()
+            part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
+            self._owner = (ids, e_local, self.layout.tp)
+            return part, flags, epoch, row_of.view(T, cfg.top_k), wts
         ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
         xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
         cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
@@ -214,13 +231,16 @@ class Decoder:
             part, flags, epoch = self._row_parallel(attn, lw, "wo")
             residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
                                                            flags=flags, epoch=epoch)
+            self._owner = None
             part, flags, epoch, row_idx, row_w = self._ffn(li, normed)
             if li + 1 < len(layers):
                 next_gamma = layers[li + 1].attn_norm
             else:
                 next_gamma = self.w.final_norm if last_stage else None
+            own = {} if self._owner is None else dict(owner_ids=self._owner[0], experts_per_owner=self._owner[1],
+                                                      owner_span=self._owner[2])
             residual, normed = ops.reduce_residual_rmsnorm(residual, part, next_gamma, cfg.rms_norm_eps, row_idx,
-                                                           row_w, flags=flags, epoch=epoch)
+                                                           row_w, flags=flags, epoch=epoch, **own)
             if self.capture_hidden is not None:
                 self.capture_hidden.append(residual.detach().float().cpu())
         return residual, normed

@@ -244,11 +244,12 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
 
 
 def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None, residual_out=None,
-                            normed_out=None, flags=None, epoch=None, wait_budget_ms=0):
+                            normed_out=None, flags=None, epoch=None, wait_budget_ms=0, owner_ids=None, experts_per_owner=1,
+                            owner_span=1):
     """See csrc/kernels/norm.cu. partial: [n_src, rows, H] or None. Returns (residual_out, normed_out)."""
     src = residual if residual is not None else partial
     if not src.is_cuda:
-        return ref.reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx, row_w)
+        return ref.reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx, row_w, owner_ids, experts_per_owner, owner_span)
     H = src.shape[-1]
     B = residual.shape[0] if residual is not None else (row_idx.shape[0] if row_idx is not None else partial.shape[1])
     if residual_out is None:
@@ -262,7 +263,8 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
     rc = _lib.lib().skein_reduce_residual_rmsnorm(
         _lib.ptr(residual), _lib.ptr(partial), _lib.ptr(row_idx), _lib.ptr(row_w), _lib.ptr(gamma),
         _lib.ptr(residual_out), _lib.ptr(normed_out), _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(),
-        src_stride, B, H, n_src, topk, float(eps), wait_budget_ms, _lib.stream_ptr())
+        src_stride, B, H, n_src, topk, float(eps), wait_budget_ms, _lib.ptr(owner_ids), experts_per_owner, owner_span,
+        _lib.stream_ptr())
     _lib.check(rc, "reduce_residual_rmsnorm")
     _lib.count_launch()
     return residual_out, normed_out

@@ -41,7 +41,8 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False):
     return out
 
 
-def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None):
+def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None, owner_ids=None, experts_per_owner=1,
+                            owner_span=1):
     """partial: [n_src, rows, H] or None. Returns (residual_out bf16-rounded, normed_out or None)."""
     acc = residual.float() if residual is not None else None
     if partial is not None:
@@ -56,7 +57,11 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
                 wj = row_w[:, j].float().unsqueeze(1)
                 valid = (row_idx[:, j] >= 0).float().unsqueeze(1)
                 for s in range(p.shape[0]):
-                    contrib = contrib + valid * wj * p[s][idx]
+                    mine = 1.0
+                    if owner_ids is not None:
+                        lo = (owner_ids[:, j].long() // experts_per_owner) * owner_span
+                        mine = ((s >= lo) & (s < lo + owner_span)).float().unsqueeze(1)
+                    contrib = contrib + mine * valid * wj * p[s][idx]
         acc = contrib if acc is None else acc + contrib
     dt = residual.dtype if residual is not None else partial.dtype
     res_out = acc.to(dt)

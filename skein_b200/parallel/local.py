@@ -63,6 +63,22 @@ class BarrierComm:
     def abort(self):
         self.sh.barrier.abort()
 
+    def subgroup(self, ranks) -> "BarrierComm":
+        """Communicator over a subset of the world's ranks (every member must ask for the same tuple)."""
+        ranks = tuple(ranks)
+        world = self.world_shared if hasattr(self, "world_shared") else self.sh
+        with world_lock:
+            groups = world.__dict__.setdefault("groups", {})
+            if ranks not in groups:
+                groups[ranks] = _Shared(len(ranks), world.timeout_s)
+        my_world_rank = self.world_rank if hasattr(self, "world_rank") else self.rank
+        c = BarrierComm(groups[ranks], ranks.index(my_world_rank))
+        c.world_shared, c.world_rank = world, my_world_rank
+        return c
+
+
+world_lock = threading.Lock()
+
 
 def run_ranks(n: int, fn, timeout_s: float = 60.0):
     """Run fn(rank, comm) on n threads. Returns the list of results; re-raises the first rank exception after

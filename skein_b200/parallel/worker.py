@@ -42,18 +42,23 @@ def size_kv_pool(art: Artifact, lay, device, total_kv_bytes: int, page_size: int
     return max(8, int((free - reserve_frac * total) // page_bytes))
 
 
-def build_engine(art: Artifact, rank: int, device, comm, args) -> Engine:
+def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp_info=None) -> Engine:
     lay = art.layout(rank)
     art.check_lowering(rank)
     weights = art.load_weights(rank, device)
     pages = size_kv_pool(art, lay, device, args.total_kv_bytes)
     pages = min(pages, max(8, (args.max_seq_len // 16 + 1) * max(1, args.max_batch or art.plan["batching"]["max_batch"]) * 2))
     dec = Decoder(art.cfg, weights, lay, num_pages=pages, page_size=art.plan["kv"]["layout"].get("page_size", 16),
-                  max_pos=min(args.max_seq_len, art.cfg.max_position_embeddings), comm=comm)
+                  max_pos=min(args.max_seq_len, art.cfg.max_position_embeddings), comm=comm, comm_moe=comm_moe)
+    if pp_info is not None:
+        from .pp import PipelineStage
+        dec = PipelineStage(dec, lay, *pp_info)
     batching = art.plan["batching"]
+    fused = all(c is None or c.mode == "fused" for c in (comm, comm_moe))
     ecfg = EngineConfig(max_batch=args.max_batch or batching["max_batch"], chunk_tokens=batching.get("chunk_tokens", 0),
                         prefix_cache=art.plan["execution"]["prefix_cache"]["enable"],
-                        use_graphs=device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and (comm is None or comm.mode == "fused"))
+                        # stage-to-stage NCCL p2p and library collectives are launched eagerly, never captured
+                        use_graphs=device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused and pp_info is None)
     if args.workload:
         from .. import core
         w = core.workload_parse(open(args.workload).read())
@@ -182,17 +187,32 @@ def run_rank(args) -> int:
     art = Artifact(args.artifact)
     if art.num_devices != world:
         raise SystemExit(f"artifact was compiled for {art.num_devices} devices, launched with {world}")
-    comm, control_group = None, None
+    comm, comm_moe, pp_info, control_group = None, None, None, None
     if world > 1:
+        from . import pp as pp_mod
         launcher.init_process_group(rank, world, rdv, "nccl" if use_cuda else "gloo", device=device if use_cuda else None)
         control_group = dist.new_group(backend="gloo")
         tp, pp, ep = art.layout_dims
-        if pp > 1 or ep > 1:
-            raise SystemExit("this worker serves tensor-parallel placements; pipeline/expert-parallel stages run through their own drivers")
+        lay = art.layout(rank)
+        tp_group, pp_ranks, pp_group = pp_mod.make_groups(art.layout_dims, rank)
+        # one group per pipeline stage (its tp x ep ranks): the expert-parallel combine runs over it
+        stage_group = None
+        for s in range(pp):
+            ranks = list(range(s * tp * ep, (s + 1) * tp * ep))
+            g = dist.new_group(ranks) if (ep > 1 and len(ranks) > 1) else None
+            if rank in ranks:
+                stage_group = g
         if use_cuda:
             from .tp import TPComm
-            comm = TPComm(dist.group.WORLD, device, hidden=art.cfg.hidden_size)
-    engine = build_engine(art, rank, device, comm, args)
+            if tp > 1:
+                comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size)
+            if ep > 1:
+                comm_moe = TPComm(stage_group, device, hidden=art.cfg.hidden_size)
+        elif tp > 1 or ep > 1:
+            raise SystemExit("tensor/expert-parallel serving needs GPUs (CPU ranks are covered by skein_b200.parallel.local)")
+        if pp > 1:
+            pp_info = (pp_ranks, pp_group)
+    engine = build_engine(art, rank, device, comm, args, comm_moe, pp_info)
     control = ControlPlane(control_group, rank)
     tok = Tokenizer(art.cfg.vocab_size, art.tokenizer_path())
     rc = 0
@@ -230,8 +250,9 @@ def run_rank(args) -> int:
             driver.stop()
     if world > 1:
         dist.barrier()
-        if comm is not None:
-            comm.close()
+        for c in (comm, comm_moe):
+            if c is not None:
+                c.close()
         dist.destroy_process_group()
     return rc
 

@@ -91,3 +91,27 @@ def test_a_rank_that_never_arrives_times_out():
     with pytest.raises(CommError):
         run_ranks(2, rank_fn, timeout_s=0.2)
     assert time.time() - t0 < 5
+
+
+@pytest.mark.parametrize("tp,ep", [(1, 2), (1, 4), (2, 2)], ids=["ep2", "ep4", "tp2xep2"])
+def test_expert_parallel_ranks_reproduce_the_unsharded_model(tp, ep):
+    """Experts owned in blocks by the EP ranks, attention tensor-parallel inside each TP group: the owner-aware
+    combine reproduces the single-device model (the reference only tests its dense EP scheme on CPU:
+    crates/skein_emit/tests/ep_routing.rs:14,68, topology_emission.rs:57)."""
+    cfg = mc.tiny_mixtral(heads=4, kv_heads=2, experts=4)
+    torch.manual_seed(0)
+    full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=9, std=0.05)
+    prompts = torch.randint(0, cfg.vocab_size, (2, 19)).tolist()
+    tables = [[1, 2, 3, 4], [5, 6, 7, 8]]
+    want, _ = _generate(Decoder(cfg, full, num_pages=16, page_size=16, max_pos=128), prompts, tables)
+
+    def rank_fn(r, world):
+        lay = mc.ParallelLayout(tp=tp, ep=ep, rank=r)
+        comm_tp = world.subgroup(lay.tp_group()) if tp > 1 else None
+        dec = Decoder(cfg, shard_model(full, cfg, lay), lay, num_pages=16, page_size=16, max_pos=128, comm=comm_tp, comm_moe=world)
+        assert dec.w.layers[0].w13.shape[0] == cfg.num_experts // ep
+        return _generate(dec, prompts, tables)[0]
+
+    results, errors = run_ranks(tp * ep, rank_fn)
+    assert not any(errors)
+    assert all(r == want for r in results)
