@@ -246,7 +246,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tmem_ld16(t_acc + c0, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_F + r] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; j += 4)   // row-major partials: 16-byte accesses, few instructions on the fix-up path
+              *reinterpret_cast<uint4*>(&ws[(size_t)r * acc_cols + c0 + j]) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
           }
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_tempty[b]));
@@ -297,9 +298,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     const int slot = ((long long)c * sched.per) / KB == u ? 0 : 1;
                     const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                      tg[ci][j] = __ldcg(&ws[(size_t)(c0 + j) * TILE_F + r]);
-                      if (DUAL) tu[ci][j] = __ldcg(&ws[(size_t)(n_tile + c0 + j) * TILE_F + r]);
+                    for (int j = 0; j < 16; j += 4) {
+                      const float4 a4 = __ldcg(reinterpret_cast<const float4*>(&ws[(size_t)r * acc_cols + c0 + j]));
+                      tg[ci][j] = a4.x; tg[ci][j + 1] = a4.y; tg[ci][j + 2] = a4.z; tg[ci][j + 3] = a4.w;
+                      if (DUAL) {
+                        const float4 b4 = __ldcg(reinterpret_cast<const float4*>(&ws[(size_t)r * acc_cols + n_tile + c0 + j]));
+                        tu[ci][j] = b4.x; tu[ci][j + 1] = b4.y; tu[ci][j + 2] = b4.z; tu[ci][j + 3] = b4.w;
+                      }
                     }
                   } else {
 #pragma unroll

@@ -22,10 +22,12 @@ namespace skein {
 
 constexpr int RT_MAX_E = 64;
 constexpr int RT_MAX_K = 8;
+constexpr int RT_STAGE_IDS = 2048;
 
 __device__ void router_plan_body(const int* __restrict__ expert_ids, int n_pairs, int E, int topk,
                                  int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
-                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s);
+                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s,
+                                 const int* ids_s);
 
 // grid = T tokens, 512 threads: thread i owns 8 consecutive elements of the hidden vector per pass, so
 // every load of a pass is issued before the first is consumed. The last CTA to finish also lays out
@@ -41,6 +43,7 @@ __global__ void __launch_bounds__(512) router_topk_kernel(const __nv_bfloat16* _
   __shared__ int cnt_s[RT_MAX_E];
   __shared__ int off_s[RT_MAX_E + 1];
   __shared__ int is_last;
+  __shared__ int ids_stage[RT_STAGE_IDS];
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int e0 = 0; e0 < E; e0 += 8) {
     float a[8];
@@ -112,20 +115,29 @@ __global__ void __launch_bounds__(512) router_topk_kernel(const __nv_bfloat16* _
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  router_plan_body(expert_ids, T * topk, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s);
+  const int n_pairs = T * topk;
+  const int* staged = nullptr;
+  if (n_pairs <= RT_STAGE_IDS) {
+    for (int i = tid; i < n_pairs; i += blockDim.x) ids_stage[i] = __ldcg(expert_ids + i);
+    __syncthreads();
+    staged = ids_stage;
+  }
+  router_plan_body(expert_ids, n_pairs, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s, staged);
 }
 
 // One CTA; one warp per expert walks the (token, slot) pairs in order. n_pairs = T * topk.
 // Experts outside [e_first, e_first + e_count) get count 0 (expert parallelism: not ours).
 __device__ void router_plan_body(const int* __restrict__ expert_ids, int n_pairs, int E, int topk,
                                  int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
-                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s) {
+                                 int* __restrict__ src_token, int e_first, int e_count, int* cnt_s, int* off_s,
+                                 const int* ids_s) {
+  // ids_s: optional copy of expert_ids in shared memory (the two passes below then never wait on L2)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarps) {
     int c = 0;
     for (int i0 = 0; i0 < n_pairs; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < n_pairs && __ldcg(expert_ids + i) == e;
+      const bool hit = i < n_pairs && (ids_s ? ids_s[i] : __ldcg(expert_ids + i)) == e;
       c += __popc(__ballot_sync(0xffffffffu, hit));
     }
     if (lane == 0) cnt_s[e] = (e >= e_first && e < e_first + e_count) ? c : 0;
@@ -144,7 +156,7 @@ __device__ void router_plan_body(const int* __restrict__ expert_ids, int n_pairs
     int base = off_s[e];
     for (int i0 = 0; i0 < n_pairs; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < n_pairs && __ldcg(expert_ids + i) == e;
+      const bool hit = i < n_pairs && (ids_s ? ids_s[i] : __ldcg(expert_ids + i)) == e;
       const unsigned bal = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         if (mine) {
@@ -166,7 +178,7 @@ __global__ void __launch_bounds__(1024) router_plan_kernel(const int* __restrict
                                                             int e_first, int e_count) {
   __shared__ int cnt_s[RT_MAX_E];
   __shared__ int off_s[RT_MAX_E + 1];
-  router_plan_body(expert_ids, n_pairs, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s);
+  router_plan_body(expert_ids, n_pairs, E, topk, counts, offsets, row_of, src_token, e_first, e_count, cnt_s, off_s, nullptr);
 }
 
 }  // namespace skein
