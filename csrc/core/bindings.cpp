@@ -313,6 +313,16 @@ PYBIND11_MODULE(_skein_core, m) {
         return d;
       })
       .def("prompt", [](const ContinuousBatcher& b, uint64_t id) { auto* r = b.get(id); return r ? r->req.prompt : std::vector<int32_t>{}; })
+      // position of the token each listed request feeds into its next decode step (-1 for unknown ids)
+      .def("decode_positions", [](const ContinuousBatcher& b, const std::vector<uint64_t>& ids) {
+        std::vector<int32_t> out;
+        out.reserve(ids.size());
+        for (uint64_t id : ids) {
+          auto* r = b.get(id);
+          out.push_back(r ? (int32_t)(r->req.prompt.size() + r->generated.size()) - 1 : -1);
+        }
+        return out;
+      })
       .def_property_readonly("inflight_len", &ContinuousBatcher::inflight_len).def_property_readonly("queued_len", &ContinuousBatcher::queued_len)
       .def_property_readonly("rejected", &ContinuousBatcher::rejected).def_property_readonly("retired", &ContinuousBatcher::retired)
       .def_property_readonly("max_batch", &ContinuousBatcher::max_batch).def("inflight_ids", &ContinuousBatcher::inflight_ids);

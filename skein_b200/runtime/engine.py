@@ -124,11 +124,10 @@ class Engine:
                 if last:
                     events.append(self._accept(rid, tok, now))
         if decode:
-            toks_in, pos, lens, tables = [], [], [], []
-            for rid in decode:
-                info = self.batcher.request_info(rid)
-                p = info["prompt_len"] + len(info["generated"]) - 1
-                toks_in.append(self._last[rid]); pos.append(p); lens.append(p + 1); tables.append(self.kv.pages_for(rid))
+            pos = self.batcher.decode_positions(decode)
+            toks_in = [self._last[rid] for rid in decode]
+            lens = [p + 1 for p in pos]
+            tables = [self.kv.pages_for(rid) for rid in decode]
             bk = self.runner.bucket(len(decode))
             self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables)
             out = self.runner.decode_step(bk)

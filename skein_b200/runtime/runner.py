@@ -42,6 +42,7 @@ class _Bucket:
         self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.graph = None          # one step, host-fed
         self.graph_loop = None     # one step + device-side token feedback
+        self.np_views = None
         self.host_in[B:2 * B] = -1
 
     def views(self, buf):
@@ -107,13 +108,17 @@ class ModelRunner:
     def load_decode_inputs(self, bk: _Bucket, tokens, positions, seq_lens, block_tables):
         """Fill the pinned staging buffer from host lists (rows beyond len(tokens) are padding)."""
         n = len(tokens)
-        t, p, l, bt = bk.views(bk.host_in)
-        t.zero_(); p.fill_(-1); l.zero_()
-        t[:n] = torch.as_tensor(tokens, dtype=torch.int32)
-        p[:n] = torch.as_tensor(positions, dtype=torch.int32)
-        l[:n] = torch.as_tensor(seq_lens, dtype=torch.int32)
+        if bk.np_views is None:   # numpy views share the pinned buffer: no tensor objects per row on the hot path
+            bk.np_views = tuple(v.numpy() for v in bk.views(bk.host_in))
+        t, p, l, bt = bk.np_views
+        t[:n] = tokens
+        p[:n] = positions
+        l[:n] = seq_lens
+        t[n:] = 0
+        p[n:] = -1
+        l[n:] = 0
         for i, row in enumerate(block_tables):
-            bt[i, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+            bt[i, :len(row)] = row
 
     def decode_step(self, bk: _Bucket, sync: bool = True):
         """H2D of the staged inputs, one step, D2H of the result. Returns the host result view."""
