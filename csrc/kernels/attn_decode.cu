@@ -24,6 +24,7 @@ namespace skein {
 constexpr int AD_THREADS = 128;
 constexpr int AD_CHUNK = 128;
 constexpr int AD_D = 128;
+constexpr int AD_MAX_SPLITS = 16;
 
 struct AttnDecodeParams {
   const __nv_bfloat16* q;   // [B, q_stride] with head h at h * D
@@ -215,17 +216,29 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnDecod
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // Merge: (m, l) of every head and split are staged in shared memory with one parallel load, then each
+  // thread fetches its output dim of all splits at once (independent loads, all in flight together).
+  float* ml_s = &o_s[0][0][0];   // the P*V scratch is free by now: [G][AD_MAX_SPLITS][2] floats
+  const size_t base0 = ((size_t)b * p.Hq + kvh * G) * p.splits;
+  for (int i = tid; i < G * p.splits * 2; i += AD_THREADS) ml_s[i] = __ldcg(&p.ws_ml[base0 * 2 + i]);
+  __syncthreads();
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const size_t base = ((size_t)b * p.Hq + kvh * G + g) * p.splits;
+    const size_t base = base0 + (size_t)g * p.splits;
+    float ov[AD_MAX_SPLITS];
+#pragma unroll
+    for (int s2 = 0; s2 < AD_MAX_SPLITS; ++s2) ov[s2] = (s2 < p.splits) ? __ldcg(&p.ws_o[(base + s2) * AD_D + d]) : 0.f;
     float M = -INFINITY;
-    for (int s2 = 0; s2 < p.splits; ++s2) M = fmaxf(M, __ldcg(&p.ws_ml[(base + s2) * 2]));
+    for (int s2 = 0; s2 < p.splits; ++s2) M = fmaxf(M, ml_s[(g * p.splits + s2) * 2]);
     float L = 0.f, O = 0.f;
-    for (int s2 = 0; s2 < p.splits; ++s2) {
-      const float mi = __ldcg(&p.ws_ml[(base + s2) * 2]);
-      const float w = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
-      L += w * __ldcg(&p.ws_ml[(base + s2) * 2 + 1]);
-      O += w * __ldcg(&p.ws_o[(base + s2) * AD_D + d]);
+#pragma unroll
+    for (int s2 = 0; s2 < AD_MAX_SPLITS; ++s2) {
+      if (s2 < p.splits) {
+        const float mi = ml_s[(g * p.splits + s2) * 2];
+        const float w = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
+        L += w * ml_s[(g * p.splits + s2) * 2 + 1];
+        O += w * ov[s2];
+      }
     }
     p.out[((size_t)b * p.Hq + kvh * G + g) * AD_D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
   }
@@ -243,7 +256,7 @@ extern "C" int skein_attn_decode(const void* q, long long q_stride, const void* 
                                  float scale, void* stream) {
   using namespace skein;
   if (B == 0) return 0;
-  if (D != AD_D || Hq % Hkv != 0 || splits < 1) return -1;
+  if (D != AD_D || Hq % Hkv != 0 || splits < 1 || splits > AD_MAX_SPLITS) return -1;
   AttnDecodeParams p;
   p.q = (const __nv_bfloat16*)q; p.kv = (const __nv_bfloat16*)kv; p.block_table = block_table; p.seq_lens = seq_lens;
   p.out = (__nv_bfloat16*)out;
