@@ -278,3 +278,84 @@ extern "C" int skein_attn_decode(const void* q, long long q_stride, const void* 
   }
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in attn_decode_noalloc.h).
+// The split-KV scratch is part of the library image. In host code the names below are host-side
+// stand-ins for the device arrays, not device addresses: the addresses a kernel can use come from
+// cudaGetSymbolAddress, looked up once per device and cached.
+// ---------------------------------------------------------------------------------------------
+#include "attn_decode_noalloc.h"
+
+namespace skein {
+static __device__ __align__(256) float g_noalloc_scratch[(size_t)SKEIN_ATTN_NOALLOC_MAX_ROWS * (AD_D + 2)];
+static __device__ __align__(256) int g_noalloc_counters[SKEIN_ATTN_NOALLOC_MAX_COUNTERS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoAllocDevice { float* scratch; int* counters; bool ready; };
+static NoAllocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
+}  // namespace skein
+
+extern "C" const char* skein_attn_decode_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case SKEIN_NOALLOC_ERR_BAD_ARGS: return "bad arguments (D must be 128, splits >= 1, Hq a multiple of Hkv, B >= 0)";
+    case SKEIN_NOALLOC_ERR_TOO_LARGE:
+      return "problem exceeds the built-in scratch: need B*Hq*splits <= 8192, B*Hkv <= 4096 and splits <= 16";
+    case SKEIN_NOALLOC_ERR_UNSUPPORTED_GROUP: return "Hq / Hkv must be 1, 2, 4 or 8";
+    case SKEIN_NOALLOC_ERR_DEVICE: return "could not identify the current device or its index is out of range";
+    default: return "CUDA runtime error (positive values are cudaError_t)";
+  }
+}
+
+extern "C" int skein_attn_decode_noalloc(const void* q, long long q_stride, const void* kv, const int* block_table,
+                                         const int* seq_lens, void* out, int* status, int B, int Hq, int Hkv, int D,
+                                         int page_size, int max_blocks, int num_pages, int splits, float scale,
+                                         void* stream) {
+  using namespace skein;
+  if (B == 0) return 0;
+  if (B < 0 || D != AD_D || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || splits < 1 || page_size <= 0) return SKEIN_NOALLOC_ERR_BAD_ARGS;
+  const int G = Hq / Hkv;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return SKEIN_NOALLOC_ERR_UNSUPPORTED_GROUP;
+  if ((long long)B * Hq * splits > SKEIN_ATTN_NOALLOC_MAX_ROWS || (long long)B * Hkv > SKEIN_ATTN_NOALLOC_MAX_COUNTERS)
+    return SKEIN_NOALLOC_ERR_TOO_LARGE;
+  if (splits > AD_MAX_SPLITS) return SKEIN_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SKEIN_NOALLOC_ERR_DEVICE;
+  NoAllocDevice& nd = g_noalloc_dev[dev];
+  if (!nd.ready) {
+    // set-up, once per device, with that device current
+    void* ps = nullptr;
+    void* pc = nullptr;
+    e = cudaGetSymbolAddress(&ps, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
+    if (e != cudaSuccess) return (int)e;
+    nd.scratch = static_cast<float*>(ps);
+    nd.counters = static_cast<int*>(pc);
+    nd.ready = true;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  // the scratch keeps the previous call's contents: the arrival counters must start at zero
+  e = cudaMemsetAsync(nd.counters, 0, sizeof(int) * (size_t)B * Hkv, s);
+  if (e != cudaSuccess) return (int)e;
+  AttnDecodeParams p;
+  p.q = (const __nv_bfloat16*)q; p.kv = (const __nv_bfloat16*)kv; p.block_table = block_table; p.seq_lens = seq_lens;
+  p.out = (__nv_bfloat16*)out;
+  p.ws_o = nd.scratch;
+  p.ws_ml = nd.scratch + (size_t)B * Hq * splits * AD_D;
+  p.counters = nd.counters; p.status = status; p.q_stride = q_stride;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
+  p.splits = splits;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  dim3 grid(splits, Hkv, B);
+  switch (G) {
+    case 1: attn_decode_kernel<1><<<grid, AD_THREADS, 0, s>>>(p); break;
+    case 2: attn_decode_kernel<2><<<grid, AD_THREADS, 0, s>>>(p); break;
+    case 4: attn_decode_kernel<4><<<grid, AD_THREADS, 0, s>>>(p); break;
+    default: attn_decode_kernel<8><<<grid, AD_THREADS, 0, s>>>(p); break;
+  }
+  return (int)cudaGetLastError();
+}
