@@ -1,0 +1,163 @@
+"""Per-kernel micro-benchmarks with roofline fractions against the measured peaks of the machine.
+
+    python -m skein_b200.utils.microbench --op moe_gate_up --tp 1
+    python -m skein_b200.utils.microbench --op all --tp 8
+    python -m skein_b200.utils.microbench --op moe_gate_up --tp 4 --iters 1 --warmup 1     # a profiler-sized run
+
+Shapes are the decode step of Mixtral-8x7B (64 sequences, top-2 of 8 experts, hidden 4096, ffn 14336,
+32/8 heads of 128) divided by --tp the way the tensor-parallel shards divide them. Every op is timed
+with CUDA events after warm-up, with a 256 MiB write between iterations so that nothing is served from
+L2, and reported as the median. The denominators are the machine's measured copy bandwidth and bf16
+GEMM rate when a MEASURED_PEAKS.json sits at the repository root, else the stated fallback.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import ops
+
+_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "kind": "measured"}
+    return dict(_FALLBACK, kind="fallback")
+
+
+def timeit(fn, iters, warmup, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    scr = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    ts = []
+    for _ in range(iters):
+        if scr is not None:
+            scr.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _report(name, us, bytes_, flops, pk):
+    gbs = bytes_ / us * 1e-3
+    tfs = flops / us * 1e-6
+    fb, ff = gbs / pk["hbm_gbs"], tfs / pk["bf16_tflops"]
+    bound = "memory" if fb >= ff else "compute"
+    print(json.dumps({"op": name, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tfs, 2),
+                      "frac_of_%s_hbm" % pk["kind"]: round(fb, 3), "frac_of_%s_bf16" % pk["kind"]: round(ff, 3),
+                      "bound": bound, "MB": round(bytes_ / 1e6, 2)}))
+
+
+def _bf(*shape, std=0.02):
+    return torch.empty(*shape, device="cuda", dtype=torch.bfloat16).normal_(0, std)
+
+
+def op_moe(which, tp, a):
+    E, H, F, per = 8, 4096, 14336 // tp, a.tokens * 2 // 8
+    rows = E * per
+    cnt = torch.full((E,), per, dtype=torch.int32, device="cuda")
+    off = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    off[1:] = torch.cumsum(cnt, 0)
+    if which == "gate_up":
+        xs, w = _bf(rows, H, std=1.0), _bf(E, 2 * F, H)
+        out = torch.empty(rows, F, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops.grouped_linear(xs, w, cnt, off, swiglu=True, out=out)
+        fl = 2 * rows * 2 * F * H
+    else:
+        xs, w = _bf(rows, F, std=1.0), _bf(E, H, F)
+        out = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops.grouped_linear(xs, w, cnt, off, swiglu=False, out=out)
+        fl = 2 * rows * H * F
+    by = w.numel() * 2 + xs.numel() * 2 + out.numel() * 2
+    return fn, by, fl
+
+
+def op_dense(F, K, a):
+    x, w = _bf(a.tokens, K, std=1.0), _bf(F, K)
+    out = torch.empty(a.tokens, F, dtype=torch.bfloat16, device="cuda")
+    return (lambda: ops.linear(x, w, out=out)), (w.numel() + x.numel() + out.numel()) * 2, 2 * a.tokens * F * K
+
+
+def op_attn(tp, a):
+    B, Hq, Hkv, D, ctx = a.tokens, 32 // tp, max(1, 8 // tp), 128, a.ctx
+    nb = (ctx + 15) // 16
+    kv = _bf(B * nb + 1, 2, Hkv, 16, D, std=1.0)
+    bt = torch.arange(B * nb, dtype=torch.int32, device="cuda").view(B, nb) + 1
+    lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = _bf(B, Hq * D, std=1.0)
+    out = torch.empty(B, Hq * D, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: ops.attn_decode(q, kv, bt, lens, Hq, Hkv, D, out=out, ctx_hint=ctx)
+    return fn, B * ctx * 2 * Hkv * D * 2, 4 * B * Hq * ctx * D
+
+
+def op_reduce(a):
+    B, H = a.tokens, 4096
+    res, part, g = _bf(B, H, std=1.0), _bf(1, B, H, std=1.0), _bf(H, std=1.0)
+    fn = lambda: ops.reduce_residual_rmsnorm(res, part, g, 1e-5)
+    return fn, 4 * B * H * 2, 6 * B * H
+
+
+def op_router(a):
+    x, wg = _bf(a.tokens, 4096, std=1.0), _bf(8, 4096)
+    fn = lambda: ops.route(x, wg, 2)
+    return fn, (x.numel() + wg.numel()) * 2, 2 * a.tokens * 8 * 4096
+
+
+def build(name, a):
+    tp = a.tp
+    if name == "moe_gate_up":
+        return op_moe("gate_up", tp, a)
+    if name == "moe_down":
+        return op_moe("down", tp, a)
+    if name == "qkv":
+        return op_dense((32 + 16) * 128 // tp, 4096, a)
+    if name == "o_proj":
+        return op_dense(4096, 32 * 128 // tp, a)
+    if name == "lm_head":
+        return op_dense(32000 // tp, 4096, a)
+    if name == "attn_decode":
+        return op_attn(tp, a)
+    if name == "reduce_norm":
+        return op_reduce(a)
+    if name == "router":
+        return op_router(a)
+    raise SystemExit(f"unknown op {name}")
+
+
+OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "router")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--op", default="all", help="one of: all, " + ", ".join(OPS))
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree whose shard shapes are timed")
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=640)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    pk = peaks()
+    for name in (OPS if a.op == "all" else a.op.split(",")):
+        fn, by, fl = build(name, a)
+        us = timeit(fn, a.iters, a.warmup, flush=not a.no_flush)
+        _report(f"{name}/tp{a.tp}", us, by, fl, pk)
+    ops.workspace().check_status()
+
+
+if __name__ == "__main__":
+    main()
