@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--eager", action="store_true",
+                    help="launch the step's kernels one by one instead of replaying the captured graph "
+                         "(for a per-kernel launch list; the timed loop sits in an NVTX range named 'timed')")
     return ap.parse_args()
 
 
@@ -127,7 +130,8 @@ def main():
     comm = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         from skein_b200.parallel.tp import TPComm
         comm = TPComm.create(dist.group.WORLD, dev, max_rows=max(8192, 2 * args.batch), hidden=4096)
 
@@ -141,7 +145,7 @@ def main():
     t0 = time.time()
     weights = random_weights(cfg, lay, dev, seed=0, std=0.02)
     dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm)
-    use_graphs = comm is None or comm.mode == "fused"   # the NCCL baseline mode launches eagerly
+    use_graphs = (comm is None or comm.mode == "fused") and not args.eager   # the NCCL baseline mode launches eagerly
     runner = ModelRunner(dec, max_blocks_per_seq=blocks_per_seq, use_graphs=use_graphs, ctx_hint=P + Gn // 2)
     torch.cuda.synchronize()
     t_init = time.time() - t0
@@ -156,6 +160,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def check_all(where):
+        # every rank learns of a device-side error (a peer wait that ran out, a bad index) on any rank
+        code = ops.workspace().status[:1].clone()
+        if world > 1:
+            dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if int(code[0]) != 0:
+            if rank == 0:
+                print(json.dumps({"error": f"device status {int(code[0])} after {where}", "n_gpus": world}))
+            if world > 1:
+                dist.destroy_process_group()
+            sys.exit(3)
+
     # ---- prefill (chunks of up to 8192 tokens); TTFT of a sequence = time until its chunk finished ----
     per_chunk = max(1, 8192 // P)
     barrier()
@@ -166,7 +182,7 @@ def main():
         torch.cuda.synchronize()
         first_tokens.extend(toks)
         ttft.extend([(time.perf_counter() - t_start) * 1e3] * len(toks))
-    ops.workspace().check_status()
+    check_all("prefill")
 
     bk = runner.bucket(B)
 
@@ -185,8 +201,10 @@ def main():
     if use_graphs:
         runner._ensure_graph(bk, True)
     launches_per_step = None
-    for _ in range(W):
+    for i in range(W):
         runner.decode_loop_step(bk)
+        if i == 0:
+            check_all("the first decode step")
     # kernels per step: count one eager step's launches on a scratch copy of the state
     saved = bk.dev_in.clone()
     torch.cuda.synchronize()
@@ -200,13 +218,15 @@ def main():
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    torch.cuda.nvtx.range_push("timed")
     for _ in range(K):
         runner.decode_loop_step(bk)
+    torch.cuda.nvtx.range_pop()
     ev1.record()
     barrier()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
-    ops.workspace().check_status()
+    check_all("the timed loop")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -23,6 +23,7 @@ enum : int {
   ST_TIMEOUT_PEER_FLAG = 5,   // a flag written by another rank never reached its epoch
   ST_TIMEOUT_SPLITK = 6,      // (unused: split-K uses last-arriver, no waits)
   ST_BAD_INDEX = 7,           // debug bounds check tripped
+  ST_TIMEOUT_GRID_BARRIER = 8,  // a grid-wide arrival counter never filled (a CTA of the launch was not resident)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -72,7 +72,8 @@ __global__ void merge_candidates_kernel(const float* cand_val, const int* cand_i
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
   if (flags != nullptr && (int)threadIdx.x < n_src) {
-    if (!wait_flag_ge(flags + threadIdx.x, *epoch, budget_ns)) {
+    const bool poisoned = status != nullptr && *(volatile int*)status == ST_TIMEOUT_PEER_FLAG;
+    if (poisoned || !wait_flag_ge(flags + threadIdx.x, *epoch, budget_ns)) {
       report_status(status, ST_TIMEOUT_PEER_FLAG, threadIdx.x);
       failed = 1;
     }

@@ -184,8 +184,9 @@ class Decoder:
             return y.unsqueeze(0), None, None
         return self.comm.linear_push(x, w, grouped)
 
-    def _ffn(self, li: int, normed):
-        """Returns (partial, flags, epoch, row_idx, row_w) feeding the fused combine/reduce."""
+    def _ffn(self, li: int, normed, routed=None):
+        """Returns (partial, flags, epoch, row_idx, row_w) feeding the fused combine/reduce. `routed` carries the
+        router's outputs and the expert-sorted activations when the preceding reduce kernel already made them."""
         cfg, lw = self.cfg, self.w.layers[li]
         if not cfg.is_moe:
             h = self._col_linear(normed, lw, "w13", swiglu=True)
@@ -199,16 +200,22 @@ class Decoder:
             # layout), computes only the rows of the experts it owns, and its down projection stores those rows
             # into every rank's receive slot; the combine then reads each (token, slot) pair from the ranks that
             # own its expert. Row positions are global, so no index exchange is needed.
-            ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k)
-            xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+            if routed is None:
+                ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k)
+                xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+            else:
+                ids, wts, counts, offsets, row_of, src_token, xs = routed
             cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
             h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep)
             w2 = lw.w2 if lw.w2 is not None else lw.fp8["w2"].dequant()
             part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
             self._owner = (ids, e_local, self.layout.tp)
             return part, flags, epoch, row_of.view(T, cfg.top_k), wts
-        ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
-        xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+        if routed is None:
+            ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
+            xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+        else:
+            ids, wts, counts, offsets, row_of, src_token, xs = routed
         cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
         h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k)
         part, flags, epoch = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
@@ -229,10 +236,20 @@ class Decoder:
         for li, lw in enumerate(layers):
             attn = self._attention(li, normed, inp)
             part, flags, epoch = self._row_parallel(attn, lw, "wo")
-            residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
-                                                           flags=flags, epoch=epoch)
+            routed = None
+            if cfg.is_moe and residual.is_cuda and ops.can_fuse_route(residual.shape[0], cfg.top_k, residual.device):
+                # decode-sized batches: the router and the expert-sorted scatter ride in the reduce kernel
+                ep = self.layout.ep > 1
+                e_first = 0 if ep else self.layout.ep_rank * self.sh["E_local"]
+                e_cnt = cfg.num_experts if ep else self.sh["E_local"]
+                out = ops.reduce_norm_route(residual, part, lw.ffn_norm, cfg.rms_norm_eps, lw.router, cfg.top_k,
+                                            e_first, e_cnt, flags=flags, epoch=epoch)
+                residual, normed, routed = out[0], out[1], out[2:]
+            else:
+                residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
+                                                               flags=flags, epoch=epoch)
             self._owner = None
-            part, flags, epoch, row_idx, row_w = self._ffn(li, normed)
+            part, flags, epoch, row_idx, row_w = self._ffn(li, normed, routed)
             if li + 1 < len(layers):
                 next_gamma = layers[li + 1].attn_norm
             else:

@@ -68,12 +68,17 @@ def lib():
     _sig(L, "skein_sm_count", i32, [])
     _sig(L, "skein_reduce_residual_rmsnorm", i32,
          [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, i32, vp, i32, i32, vp])
+    _sig(L, "skein_reduce_norm_route", i32,
+         [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, f32, i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
+          vp, vp, i32, vp])
     _sig(L, "skein_rope_kv_append", i32,
          [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp])
     _sig(L, "skein_embed_gather", i32, [vp, vp, vp, i32, i32, i32, i32, vp])
     _sig(L, "skein_gather_rows", i32, [vp, vp, vp, i32, i32, vp, vp])
     _sig(L, "skein_attn_decode_workspace_floats", i64, [i32, i32, i32])
     _sig(L, "skein_attn_decode", i32,
+         [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
+    _sig(L, "skein_attn_decode_mma", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_prefill", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])

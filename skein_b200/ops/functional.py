@@ -42,6 +42,7 @@ class Workspace:
         self.gemm_counters = torch.zeros(max(self.sm_count, 256), dtype=torch.int32, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
         self.router_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.route_barrier = torch.zeros(2, dtype=torch.int32, device=device)
         self.attn_ws = None
         self.attn_counters = None
 
@@ -58,9 +59,11 @@ class Workspace:
         code, detail = self.status.tolist()
         if code != 0:
             self.status.zero_()
+            self.route_barrier.zero_()   # a grid barrier that gave up leaves its counters dirty
             names = {1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
                      3: "timeout waiting for an accumulator", 4: "timeout waiting for a drained accumulator",
-                     5: "timeout waiting for a peer flag", 7: "index out of range"}
+                     5: "timeout waiting for a peer flag", 7: "index out of range",
+                     8: "timeout at a grid-wide arrival counter"}
             raise RuntimeError(f"device status {code} ({names.get(code, 'unknown')}), detail {detail}")
 
 
@@ -270,6 +273,52 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
     return residual_out, normed_out
 
 
+def can_fuse_route(T, topk, device=None) -> bool:
+    """True when reduce_norm_route may be used: every token's CTA must be resident at once."""
+    return 0 < T <= workspace(device).sm_count and T * topk <= 2048 and os.environ.get("SKEIN_FUSE_ROUTE", "1") != "0"
+
+
+def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_count=None, flags=None, epoch=None,
+                      wait_budget_ms=0):
+    """Residual add + (all-reduce consumer) + RMSNorm + MoE router + scatter into expert-sorted order, one launch.
+
+    Equals reduce_residual_rmsnorm followed by route and gather_rows (csrc/kernels/norm.cu). Returns
+    (residual_out, normed_out, expert_ids [T,k], weights [T,k], counts [E], offsets [E+1], row_of [T*k],
+    src_token [T*k], xs [T*k, H]).
+    """
+    src = residual if residual is not None else partial
+    E = wg.shape[0]
+    e_count = E if e_count is None else e_count
+    if not src.is_cuda:
+        res, normed = ref.reduce_residual_rmsnorm(residual, partial, gamma, eps, None, None, None, 1, 1)
+        ids, w, _ = ref.router_topk(normed, wg, topk)
+        counts, offsets, row_of, src_token = ref.router_plan(ids, E, e_first, e_count)
+        return res, normed, ids, w, counts, offsets, row_of, src_token, normed[src_token.long()]
+    H = src.shape[-1]
+    T = residual.shape[0] if residual is not None else partial.shape[1]
+    dev = src.device
+    residual_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    normed_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    w = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    meta = torch.empty(2 * E + 1 + 2 * T * topk, dtype=torch.int32, device=dev)
+    counts, offsets = meta[:E], meta[E:2 * E + 1]
+    row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
+    xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev)
+    n_src = partial.shape[0] if partial is not None else 0
+    src_stride = partial.stride(0) if partial is not None else 0
+    ws = workspace()
+    rc = _lib.lib().skein_reduce_norm_route(
+        _lib.ptr(residual), _lib.ptr(partial), gamma.data_ptr(), residual_out.data_ptr(), normed_out.data_ptr(),
+        _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(), src_stride, T, H, n_src, float(eps), wait_budget_ms,
+        wg.data_ptr(), E, topk, e_first, e_count, ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
+        row_of.data_ptr(), src_token.data_ptr(), xs.data_ptr(), ws.route_barrier.data_ptr(), ws.sm_count,
+        _lib.stream_ptr())
+    _lib.check(rc, "reduce_norm_route")
+    _lib.count_launch()
+    return residual_out, normed_out, ids, w, counts, offsets, row_of, src_token, xs
+
+
 def rmsnorm(x, gamma, eps):
     return reduce_residual_rmsnorm(x, None, gamma, eps)[1]
 
@@ -298,8 +347,12 @@ def pick_splits(B, Hkv, ctx_hint, sm_count=148):
     return s
 
 
-def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=None, splits=None, ctx_hint=1024):
-    """q: [B, row_stride] whose first Hq*D columns are the (rotated) query heads -> [B, Hq*D]."""
+def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=None, splits=None, ctx_hint=1024,
+                impl=None):
+    """q: [B, row_stride] whose first Hq*D columns are the (rotated) query heads -> [B, Hq*D].
+
+    impl "mma" (default where it applies: page size a multiple of 16, at most 16 query heads per kv head) is the
+    tensor-core kernel with the asynchronous copy pipeline, "scalar" the FMA kernel; SKEIN_ATTN_DECODE overrides."""
     if not q.is_cuda:
         return ref.attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale)
     B = q.shape[0]
@@ -312,7 +365,11 @@ def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=
     wsf, ctr = (None, None)
     if splits > 1:
         wsf, ctr = ws.attn_scratch(B, Hq, Hkv, splits)
-    rc = _lib.lib().skein_attn_decode(
+    impl = impl or os.environ.get("SKEIN_ATTN_DECODE", "mma")
+    if kv_cache.shape[3] % 16 != 0 or Hq // Hkv > 16:
+        impl = "scalar"
+    fn = _lib.lib().skein_attn_decode_mma if impl == "mma" else _lib.lib().skein_attn_decode
+    rc = fn(
         q.data_ptr(), q.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
         _lib.ptr(wsf), _lib.ptr(ctr), ws.status.data_ptr(), B, Hq, Hkv, D, kv_cache.shape[3], block_table.stride(0),
         kv_cache.shape[0], splits, float(scale), _lib.stream_ptr())

@@ -106,19 +106,41 @@ def _make_cache(B, ctx_lens, Hkv, D, page_size, extra_pages=3):
     return kv, perm.contiguous(), max_blocks
 
 
+@pytest.mark.parametrize("impl", ["mma", "scalar"])
 @pytest.mark.parametrize("Hq,Hkv,splits", [(32, 8, 1), (32, 8, 4), (4, 1, 8), (8, 8, 2), (16, 2, 3)])
-def test_attn_decode(Hq, Hkv, splits):
+def test_attn_decode(Hq, Hkv, splits, impl):
     torch.manual_seed(5)
     B, D, ps = 9, 128, 16
     lens = [1, 15, 16, 17, 130, 512, 700, 33, 0]
     kv, bt, _ = _make_cache(B, lens, Hkv, D, ps)
     q = torch.randn(B, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
     sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    o = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits)
-    o2 = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits)
+    o = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits, impl=impl)
+    o2 = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits, impl=impl)
     _check_status()
     assert torch.equal(o, o2)
     assert _rel_err(o, ref.attn_decode(q, kv, bt, sl, Hq, Hkv, D)) < 1e-2
+
+
+@pytest.mark.parametrize("Hq,Hkv,ps,splits", [(16, 1, 16, 2), (8, 2, 32, 1), (8, 2, 32, 3), (4, 1, 64, 5)])
+def test_attn_decode_mma_pages_and_unwritten_slots(Hq, Hkv, ps, splits):
+    """Larger pages, 16 heads per kv head, many tiles per warp, and cache slots past each context's end holding
+    NaN (never-written memory): they must not reach the output."""
+    torch.manual_seed(6)
+    B, D = 6, 128
+    lens = [3, 40, 2500, 1, 1023, 97]
+    kv, bt, _ = _make_cache(B, lens, Hkv, D, ps)
+    for b, l in enumerate(lens):                       # poison every slot at or past the end of the context
+        for blk in range(l // ps, bt.shape[1]):
+            lo = l % ps if blk == l // ps else 0
+            kv[int(bt[b, blk]), :, :, lo:, :] = float("nan")
+    q = torch.randn(B, Hq * D, device=DEV).bfloat16()
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    o = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits, impl="mma")
+    _check_status()
+    assert torch.isfinite(o.float()).all()
+    kv_clean = torch.nan_to_num(kv.float(), nan=0.0).bfloat16()
+    assert _rel_err(o, ref.attn_decode(q, kv_clean, bt, sl, Hq, Hkv, D)) < 1e-2
 
 
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
@@ -194,6 +216,30 @@ def test_fused_route_equals_two_step(T, H, E):
         assert torch.equal(ids, ids2) and torch.equal(w, w2)
         assert torch.equal(counts, c2) and torch.equal(offsets, o2) and torch.equal(row_of, r2)
         assert torch.equal(src[:n], s2[:n])
+
+
+@pytest.mark.parametrize("T,H,E,n_src", [(64, 4096, 8, 1), (5, 256, 4, 0), (128, 6144, 16, 2), (1, 4096, 8, 1)])
+def test_reduce_norm_route_equals_separate_kernels(T, H, E, n_src):
+    """The one-launch reduce + norm + router + scatter gives exactly what the three separate kernels give,
+    on repeated launches (its grid-wide counter re-arms itself)."""
+    torch.manual_seed(12)
+    res = torch.randn(T, H, device=DEV).bfloat16()
+    part = torch.randn(n_src, T, H, device=DEV).bfloat16() if n_src else None
+    gamma = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    wg = (torch.randn(E, H, device=DEV) / 32).bfloat16()
+    assert ops.can_fuse_route(T, 2)
+    for e_first, e_count in ((0, E), (E // 2, E // 2), (0, E)):
+        r1, n1 = ops.reduce_residual_rmsnorm(res, part, gamma, 1e-5)
+        ids1, w1, c1, o1, row1, src1 = ops.route(n1, wg, 2, e_first, e_count)
+        xs1 = ops.gather_rows(n1, src1, n_rows_dev=o1[E:])
+        r2, n2, ids2, w2, c2, o2, row2, src2, xs2 = ops.reduce_norm_route(res, part, gamma, 1e-5, wg, 2, e_first, e_count)
+        _check_status()
+        n = int(o1[-1])
+        assert torch.equal(r1, r2) and torch.equal(n1, n2)
+        assert torch.equal(ids1, ids2) and torch.equal(w1, w2)
+        assert torch.equal(c1, c2) and torch.equal(o1, o2) and torch.equal(row1, row2)
+        assert torch.equal(src1[:n], src2[:n]) and torch.equal(xs1[:n], xs2[:n])
+    assert ops.workspace().route_barrier.tolist() == [0, 0]
 
 
 def test_sampling():

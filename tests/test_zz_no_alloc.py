@@ -51,7 +51,8 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row():
     stream = torch.cuda.current_stream().cuda_stream
     for seed, (B, Hq, Hkv, lens, splits) in enumerate([(6, 32, 8, [700, 33, 512, 1, 130, 257], 4), (5, 8, 8, [90, 600, 17, 300, 45], 3)]):
         q, kv, bt, sl, D, ps, max_blocks, num_pages = _case(seed, B, Hq, Hkv, lens, splits)
-        want = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits)
+        # the entry point it is a variant of: the scalar split-KV kernel with caller-provided scratch
+        want = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=splits, impl="scalar")
         out = torch.empty(B, Hq * D, dtype=torch.bfloat16, device="cuda")
         rc = fn(q.data_ptr(), q.stride(0), kv.data_ptr(), bt.data_ptr(), sl.data_ptr(), out.data_ptr(), status.data_ptr(), B, Hq, Hkv, D,
                 ps, max_blocks, num_pages, splits, 1.0 / D ** 0.5, stream)
