@@ -38,6 +38,7 @@ constexpr int AM_MAX_SPLITS = 16;
 struct AttnMmaParams {
   const __nv_bfloat16* q;   // [B, q_stride] with head h at h * D
   const __nv_bfloat16* kv;  // paged cache
+  __nv_bfloat16* kv_rw;     // the same cache, writable (RoPE + append fusion)
   const int* block_table;   // [B, max_blocks]
   const int* seq_lens;      // [B] context length including the new token; 0 = padding row
   __nv_bfloat16* out;       // [B, Hq * D]
@@ -48,6 +49,12 @@ struct AttnMmaParams {
   long long q_stride;
   int B, Hq, Hkv, G, page_size, max_blocks, num_pages, splits;
   float scale_log2e;
+  // optional fusion of RoPE and the KV append of the new token (cos_sin == nullptr: q is already rotated and
+  // the cache already holds the token). q then points at the raw fused q/k/v projection rows
+  // [B, q_stride >= (Hq + 2 * Hkv) * D]: q heads, k heads, v heads.
+  const float* cos_sin;     // [max_pos, D/2, 2] fp32
+  const int* positions;     // [B] position of the new token, -1 = padding row
+  int max_pos;
 };
 
 __device__ __forceinline__ uint32_t am_swz(int row, int chunk) {  // byte offset in a [16][128] bf16 tile
@@ -101,11 +108,63 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnM
   const uint32_t st_base = smem_u32(am_smem) + warp * AM_WARP_BYTES;
 
   // ---- Q rows (G heads, zero padded to 16) -> shared -> A fragments for all 8 k-steps ----
-  for (int c = tid; c < AM_TILE * 16; c += AM_THREADS) {
-    const int r = c >> 4, ch = c & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (size_t)b * p.q_stride + (size_t)(kvh * G + r) * AM_D + ch * 8);
-    *reinterpret_cast<uint4*>(q_s + am_swz(r, ch)) = v;
+  const bool rope = p.cos_sin != nullptr;
+  int pos = rope ? p.positions[b] : -1;
+  if (rope && pos >= p.max_pos) { report_status(p.status, ST_BAD_INDEX, pos); pos = -1; }
+  if (!rope) {
+    for (int c = tid; c < AM_TILE * 16; c += AM_THREADS) {
+      const int r = c >> 4, ch = c & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (size_t)b * p.q_stride + (size_t)(kvh * G + r) * AM_D + ch * 8);
+      *reinterpret_cast<uint4*>(q_s + am_swz(r, ch)) = v;
+    }
+  } else {
+    // rotate-half RoPE: dim i pairs with dim i + 64, i.e. chunk ch with chunk ch + 8; one pair of chunks per thread
+    const int r = tid >> 3, ch = tid & 7;
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+    if (r < G && pos >= 0) {
+      const __nv_bfloat16* qp = p.q + (size_t)b * p.q_stride + (size_t)(kvh * G + r) * AM_D;
+      lo = *reinterpret_cast<const uint4*>(qp + ch * 8);
+      hi = *reinterpret_cast<const uint4*>(qp + 64 + ch * 8);
+      const float4* cs = reinterpret_cast<const float4*>(p.cos_sin + ((size_t)pos * 64 + ch * 8) * 2);
+      __nv_bfloat162* lb = reinterpret_cast<__nv_bfloat162*>(&lo);
+      __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 c2 = cs[i];   // (cos, sin) of dims 2i and 2i + 1 of this chunk
+        const float2 x0 = __bfloat1622float2(lb[i]), x1 = __bfloat1622float2(hb[i]);
+        lb[i] = __floats2bfloat162_rn(x0.x * c2.x - x1.x * c2.y, x0.y * c2.z - x1.y * c2.w);
+        hb[i] = __floats2bfloat162_rn(x1.x * c2.x + x0.x * c2.y, x1.y * c2.z + x0.y * c2.w);
+      }
+    }
+    *reinterpret_cast<uint4*>(q_s + am_swz(r, ch)) = lo;
+    *reinterpret_cast<uint4*>(q_s + am_swz(r, ch + 8)) = hi;
+    // the CTA whose token range holds the new token rotates its K row and appends K and V to the cache;
+    // the barrier below orders these stores before the asynchronous copies that read them back
+    if (pos >= 0) {
+      int s_app = per > 0 ? pos / per : 0;
+      if (s_app > p.splits - 1) s_app = p.splits - 1;
+      if (s_app == split) {
+        int pg = p.block_table[(size_t)b * p.max_blocks + pos / ps];
+        if (pg < 0 || pg >= p.num_pages) {
+          report_status(p.status, ST_BAD_INDEX, pg);
+        } else {
+          const __nv_bfloat16* kr = p.q + (size_t)b * p.q_stride + (size_t)(p.Hq + kvh) * AM_D;
+          const __nv_bfloat16* vr = kr + (size_t)p.Hkv * AM_D;
+          __nv_bfloat16* kd = p.kv_rw + (((size_t)pg * 2) * p.Hkv + kvh) * (size_t)ps * AM_D + (size_t)(pos % ps) * AM_D;
+          __nv_bfloat16* vd = kd + (size_t)p.Hkv * ps * AM_D;
+          if (tid < 64) {
+            const float2 cs = reinterpret_cast<const float2*>(p.cos_sin)[(size_t)pos * 64 + tid];
+            const float x0 = __bfloat162float(kr[tid]), x1 = __bfloat162float(kr[tid + 64]);
+            kd[tid] = __float2bfloat16(x0 * cs.x - x1 * cs.y);
+            kd[tid + 64] = __float2bfloat16(x1 * cs.x + x0 * cs.y);
+          } else {
+            const int j = tid - 64;
+            reinterpret_cast<__nv_bfloat162*>(vd)[j] = reinterpret_cast<const __nv_bfloat162*>(vr)[j];
+          }
+        }
+      }
+    }
   }
   __syncthreads();
   uint32_t qf[8][4];
@@ -322,10 +381,10 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnM
 
 // Same contract as skein_attn_decode (ws / counters from skein_attn_decode_workspace_floats; counters zero at
 // first use). Requires D = 128, page_size a multiple of 16, at most 16 query heads per kv head.
-extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const void* kv, const int* block_table,
-                                     const int* seq_lens, void* out, float* ws, int* counters, int* status, int B,
-                                     int Hq, int Hkv, int D, int page_size, int max_blocks, int num_pages, int splits,
-                                     float scale, void* stream) {
+static int attn_decode_mma_launch(const void* q, long long q_stride, void* kv, const int* block_table,
+                                  const int* seq_lens, void* out, float* ws, int* counters, int* status, int B,
+                                  int Hq, int Hkv, int D, int page_size, int max_blocks, int num_pages, int splits,
+                                  float scale, const float* cos_sin, const int* positions, int max_pos, void* stream) {
   using namespace skein;
   if (B == 0) return 0;
   if (D != AM_D || Hq % Hkv != 0 || page_size % AM_TILE != 0) return -1;
@@ -343,7 +402,9 @@ extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const vo
     attr_set[dev] = true;
   }
   AttnMmaParams p;
-  p.q = (const __nv_bfloat16*)q; p.kv = (const __nv_bfloat16*)kv; p.block_table = block_table; p.seq_lens = seq_lens;
+  p.q = (const __nv_bfloat16*)q; p.kv = (const __nv_bfloat16*)kv; p.kv_rw = (__nv_bfloat16*)kv;
+  p.block_table = block_table; p.seq_lens = seq_lens;
+  p.cos_sin = cos_sin; p.positions = positions; p.max_pos = max_pos;
   p.out = (__nv_bfloat16*)out; p.ws_o = ws; p.ws_ml = ws ? ws + (size_t)B * Hq * splits * AM_D : nullptr;
   p.counters = counters; p.status = status; p.q_stride = q_stride;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
@@ -351,4 +412,26 @@ extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const vo
   dim3 grid(splits, Hkv, B);
   attn_decode_mma_kernel<<<grid, AM_THREADS, AM_SMEM_BYTES, (cudaStream_t)stream>>>(p);
   return (int)cudaGetLastError();
+}
+
+extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const void* kv, const int* block_table,
+                                     const int* seq_lens, void* out, float* ws, int* counters, int* status, int B,
+                                     int Hq, int Hkv, int D, int page_size, int max_blocks, int num_pages, int splits,
+                                     float scale, void* stream) {
+  return attn_decode_mma_launch(q, q_stride, const_cast<void*>(kv), block_table, seq_lens, out, ws, counters, status, B,
+                                Hq, Hkv, D, page_size, max_blocks, num_pages, splits, scale, nullptr, nullptr, 0, stream);
+}
+
+// Decode attention straight from the fused q/k/v projection: rotates q and k (rotate-half RoPE from the fp32
+// cos/sin table), appends the new token's k and v rows to the paged cache and attends, in one launch.
+// qkv rows: [q heads | k heads | v heads] x D; positions[b] = position of the new token (-1: padding row, whose
+// seq_lens entry must be 0); seq_lens[b] = positions[b] + 1.
+extern "C" int skein_attn_decode_rope_mma(const void* qkv, long long qkv_stride, void* kv, const int* block_table,
+                                          const int* seq_lens, const int* positions, const float* cos_sin,
+                                          int max_pos, void* out, float* ws, int* counters, int* status, int B, int Hq,
+                                          int Hkv, int D, int page_size, int max_blocks, int num_pages, int splits,
+                                          float scale, void* stream) {
+  if (cos_sin == nullptr || positions == nullptr) return -1;
+  return attn_decode_mma_launch(qkv, qkv_stride, kv, block_table, seq_lens, out, ws, counters, status, B, Hq, Hkv, D,
+                                page_size, max_blocks, num_pages, splits, scale, cos_sin, positions, max_pos, stream);
 }

@@ -2,8 +2,12 @@
 //
 // A "unit" is one output tile: (group g, feature tile m of 128 rows, token tile n of n_tile rows). Units are
 // ordered group-major, then m, then n, and each owns KB consecutive K-blocks of one long line of K-blocks.
-// CTA c processes K-blocks [c * per, (c + 1) * per) of that line (stream-K). Group sizes are read from
-// device memory, so every CTA rebuilds the same table at start-up.
+// Two ways to deal the line to the CTAs:
+//   * line cut (stream-K): CTA c processes K-blocks [c * per, (c + 1) * per). Balanced for any tile count, but
+//     a CTA's range usually straddles a tile boundary, so it parks and reduces two partial tiles.
+//   * tile-aligned (only when there are no more tiles than CTAs): each tile is cut into `split` near-equal
+//     pieces owned by `split` consecutive CTAs, so every CTA has exactly one piece of one tile.
+// Group sizes are read from device memory, so every CTA rebuilds the same table at start-up.
 #pragma once
 #include "gemm_ws.cuh"
 #include <cuda.h>
@@ -16,6 +20,7 @@ struct Sched {
   int off[SKEIN_MAX_GROUPS];
   int ntile[SKEIN_MAX_GROUPS];
   int MT, KB, U, per;
+  int split;   // > 0: tile-aligned with this many CTAs per tile; 0: line cut with `per` K-blocks per CTA
   long long TK;
 };
 
@@ -32,8 +37,37 @@ __device__ __forceinline__ Unit decode_unit(const Sched& s, int G, int u) {
   return x;
 }
 
+// K-block range of CTA c on the line, the CTAs that share tile u, and which of its two workspace slots CTA c
+// uses for tile u (slot 0: the tile its range begins in).
+__device__ __forceinline__ long long cta_begin(const Sched& s, int c) {
+  if (s.split > 0) {
+    const int u = c / s.split, pc = c - u * s.split;
+    if (u >= s.U) return s.TK;
+    return (long long)u * s.KB + (long long)pc * s.KB / s.split;
+  }
+  const long long b = (long long)c * s.per;
+  return b < s.TK ? b : s.TK;
+}
+__device__ __forceinline__ long long cta_end(const Sched& s, int c) {
+  if (s.split > 0) {
+    const int u = c / s.split, pc = c - u * s.split;
+    if (u >= s.U) return s.TK;
+    return (long long)u * s.KB + (long long)(pc + 1) * s.KB / s.split;
+  }
+  const long long e = (long long)(c + 1) * s.per;
+  return e < s.TK ? e : s.TK;
+}
+__device__ __forceinline__ void tile_ctas(const Sched& s, int u, int& c_first, int& c_last) {
+  if (s.split > 0) { c_first = u * s.split; c_last = c_first + s.split - 1; return; }
+  const long long ub = (long long)u * s.KB;
+  c_first = (int)(ub / s.per);
+  c_last = (int)((ub + s.KB - 1) / s.per);
+}
+__device__ __forceinline__ int cta_slot(const Sched& s, int c, int u) { return cta_begin(s, c) / s.KB == u ? 0 : 1; }
+
 // Fills the table (one thread). k_elems_per_block: 64 for bf16, 128 for e4m3.
-__device__ __forceinline__ void build_sched(Sched& sched, const SkeinGemmParams& p, int k_elems_per_block, int grid) {
+__device__ __forceinline__ void build_sched(Sched& sched, const SkeinGemmParams& p, int k_elems_per_block, int grid,
+                                            bool allow_aligned = false) {
   const int G = p.G;
   const int MT = (p.F + 127) / 128;
   int acc = 0;
@@ -57,6 +91,16 @@ __device__ __forceinline__ void build_sched(Sched& sched, const SkeinGemmParams&
   const long long min_per = sched.KB >= 32 ? sched.KB / 8 : 4;
   if (per < min_per) per = min_per;
   sched.per = (int)per;
+  sched.split = 0;
+  if (allow_aligned && acc > 0 && acc <= grid) {
+    int sp = grid / acc;
+    if (sp > 8) sp = 8;
+    const int by_k = sched.KB / 4 > 0 ? sched.KB / 4 : 1;   // at least 4 K-blocks per piece
+    if (sp > by_k) sp = by_k;
+    // with fewer than two CTAs per tile, whole tiles on `acc` CTAs beat the line cut while the longer
+    // K loop costs less than the second partial tile that the line cut's straddling brings
+    if (sp >= 2 || (long long)sched.KB * (grid - acc) < 30ll * grid) sched.split = sp;
+  }
 }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }

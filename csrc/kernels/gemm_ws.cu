@@ -70,7 +70,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // ---- set-up ---------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x);
+    build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x, p.line_cut_only == 0);
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -91,10 +91,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const uint32_t tmem_base = tmem_base_smem;
 
   const int KB = sched.KB;
-  const long long kb_begin = (long long)blockIdx.x * sched.per;
-  long long kb_end = kb_begin + sched.per;
-  if (kb_end > sched.TK) kb_end = sched.TK;
-  const bool has_work = kb_begin < sched.TK;
+  const long long kb_begin = cta_begin(sched, blockIdx.x);
+  const long long kb_end = cta_end(sched, blockIdx.x);
+  const bool has_work = kb_begin < kb_end;
   const int n_tile = p.n_tile;
   const int k_elems = p.fp8 ? 128 : 64;
 
@@ -204,6 +203,27 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int et = threadIdx.x - 64;        // 0..127
       const int acc_cols = (DUAL ? 2 : 1) * n_tile;
       const size_t slot_elems = (size_t)TILE_F * acc_cols;
+      // final value of one output element: activation pair, residual, store (locally or into every peer)
+      auto emit = [&](float g, float u, long long row, int f) {
+        float y = g;
+        if (DUAL) y = silu(g) * u;
+        const size_t idx = (size_t)row * p.ldo + p.out_col0 + f;
+        if (p.residual) y += __bfloat162float(((const __nv_bfloat16*)p.residual)[idx]);
+        const __nv_bfloat16 yb = __float2bfloat16(y);
+        if (p.mode == 2) {
+          for (int pe = 0; pe < p.n_peers; ++pe) ((__nv_bfloat16*)p.peer_out[pe])[idx] = yb;
+        } else {
+          ((__nv_bfloat16*)p.out)[idx] = yb;
+        }
+      };
+      // Stream-K tiles that several CTAs share: every contributor parks its fp32 partial and counts itself
+      // in (phase 1, inside the loop); once its own work is done it waits for the tile's other
+      // contributors and reduces ITS slice of the tile's rows from all partials, in contributor order
+      // (phase 2). The reduction is spread over the contributors instead of falling on the last to arrive,
+      // and the result does not depend on timing. All CTAs of the grid are resident (one per SM), so
+      // the wait cannot starve; it is bounded all the same.
+      int ps_u[2] = {0, 0};
+      int n_pseg = 0;
       uint32_t seg = 0;
       long long pos = kb_begin;
       bool ok = true;
@@ -219,6 +239,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (!mbar_wait(smem_u32(&bar_tfull[b]), bph, &abort_flag, a.budget_ns)) {
           report_status(p.status, ST_TIMEOUT_TMEM_FULL, blockIdx.x);
           abort_flag = 1;
+          ok = false;
           break;
         }
         tc_fence_after();
@@ -229,14 +250,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const bool f_ok = f < p.F;
         const long long row0 = (long long)sched.off[un.g] + (long long)un.n * n_tile;
 
-        bool do_final = full_seg;
-        int c_first = 0, c_last = 0;
         if (!full_seg) {
-          // ---- stream-K partial: park the fp32 tile, count arrivals, last one finishes ----
-          const long long ub = (long long)u * KB;
-          c_first = (int)(ub / sched.per);
-          c_last = (int)((ub + KB - 1) / sched.per);
-          const int my_slot = ((long long)blockIdx.x * sched.per) / KB == u ? 0 : 1;
+          // ---- phase 1: park the fp32 partial, count this CTA in ----
+          int c_first, c_last_unused;
+          tile_ctas(sched, u, c_first, c_last_unused);
+          const int my_slot = cta_slot(sched, blockIdx.x, u);
           float* ws = p.workspace + ((size_t)blockIdx.x * 2 + my_slot) * slot_elems;
           for (int c0 = 0; c0 < acc_cols; c0 += 16) {
             // skip column chunks that hold only padding tokens
@@ -246,101 +264,143 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tmem_ld16(t_acc + c0, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)   // row-major partials: 16-byte accesses, few instructions on the fix-up path
-              *reinterpret_cast<uint4*>(&ws[(size_t)r * acc_cols + c0 + j]) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            for (int j = 0; j < 16; ++j)   // column-major partials [col][feature]: a warp writes 128 contiguous bytes
+              ws[(size_t)(c0 + j) * TILE_F + r] = __uint_as_float(v[j]);
           }
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_tempty[b]));
           __threadfence();
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) {
-            const int nc = c_last - c_first + 1;
-            const int old = atomicAdd(&p.counters[c_first], 1);
-            const int last = (old == nc - 1);
-            if (last) p.counters[c_first] = 0;
-            epi_last = last;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          do_final = epi_last != 0;
-          if (do_final) __threadfence();
-          // all 128 threads must have read epi_last before a later segment overwrites it
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-
-        if (do_final) {
+          if (et == 0) atomicAdd(&p.counters[c_first], 1);
+          if (n_pseg < 2) ps_u[n_pseg] = u;
+          ++n_pseg;
+        } else {
           for (int c0 = 0; c0 < n_tile; c0 += 16) {
             if (c0 >= valid) break;
-            float g16[16], u16[16];
-            if (full_seg) {
-              uint32_t v[16];
-              tmem_ld16(t_acc + c0, v);
-              if (DUAL) {
-                uint32_t w[16];
-                tmem_ld16(t_acc + n_tile + c0, w);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) u16[j] = __uint_as_float(w[j]);
-              } else {
-                tmem_ld_wait();
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) g16[j] = __uint_as_float(v[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) { g16[j] = 0.f; u16[j] = 0.f; }
-              // contributors are read four at a time so that 64+ loads are in flight per thread
-              for (int cb = c_first; cb <= c_last; cb += 4) {
-                float tg[4][16], tu[4][16];
-#pragma unroll
-                for (int ci = 0; ci < 4; ++ci) {
-                  const int c = cb + ci;
-                  if (c <= c_last) {
-                    const int slot = ((long long)c * sched.per) / KB == u ? 0 : 1;
-                    const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4) {
-                      const float4 a4 = __ldcg(reinterpret_cast<const float4*>(&ws[(size_t)r * acc_cols + c0 + j]));
-                      tg[ci][j] = a4.x; tg[ci][j + 1] = a4.y; tg[ci][j + 2] = a4.z; tg[ci][j + 3] = a4.w;
-                      if (DUAL) {
-                        const float4 b4 = __ldcg(reinterpret_cast<const float4*>(&ws[(size_t)r * acc_cols + n_tile + c0 + j]));
-                        tu[ci][j] = b4.x; tu[ci][j + 1] = b4.y; tu[ci][j + 2] = b4.z; tu[ci][j + 3] = b4.w;
-                      }
-                    }
-                  } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) { tg[ci][j] = 0.f; if (DUAL) tu[ci][j] = 0.f; }
-                  }
-                }
-#pragma unroll
-                for (int ci = 0; ci < 4; ++ci)
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) { g16[j] += tg[ci][j]; if (DUAL) u16[j] += tu[ci][j]; }
-              }
-            }
+            uint32_t v[16], w[16];
+            tmem_ld16(t_acc + c0, v);
+            if (DUAL) tmem_ld16(t_acc + n_tile + c0, w);
+            tmem_ld_wait();
             if (f_ok) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 if (c0 + j >= valid) break;
-                float y = g16[j];
-                if (DUAL) y = silu(y) * u16[j];
-                const size_t idx = (size_t)(row0 + c0 + j) * p.ldo + p.out_col0 + f;
-                if (p.residual) y += __bfloat162float(((const __nv_bfloat16*)p.residual)[idx]);
-                const __nv_bfloat16 yb = __float2bfloat16(y);
-                if (p.mode == 2) {
-                  for (int pe = 0; pe < p.n_peers; ++pe) ((__nv_bfloat16*)p.peer_out[pe])[idx] = yb;
-                } else {
-                  ((__nv_bfloat16*)p.out)[idx] = yb;
-                }
+                emit(__uint_as_float(v[j]), DUAL ? __uint_as_float(w[j]) : 0.f, row0 + c0 + j, f);
               }
             }
           }
-        }
-        if (full_seg) {
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_tempty[b]));
         }
         ++seg;
         pos = (long long)u * KB + kb1;
+      }
+
+      // ---- phase 2: reduce this CTA's slice of every tile it shares ----
+      for (int si = 0; si < n_pseg && si < 2 && ok; ++si) {
+        const int u = ps_u[si];
+        const Unit un = decode_unit(sched, p.G, u);
+        int c_first, c_last;
+        tile_ctas(sched, u, c_first, c_last);
+        const int nc = c_last - c_first + 1;
+        int valid = sched.cnt[un.g] - un.n * n_tile;
+        if (valid > n_tile) valid = n_tile;
+        const long long row0 = (long long)sched.off[un.g] + (long long)un.n * n_tile;
+        if (et == 0) {
+          // the low half of the counter holds arrivals, the high half departures
+          int arrived = 0;
+          const uint64_t t0 = global_timer_ns();
+          for (;;) {
+            arrived = ld_acquire_sys(&p.counters[c_first]) & 0xffff;
+            if (arrived >= nc || abort_flag) break;
+            if (global_timer_ns() - t0 > a.budget_ns) break;
+          }
+          if (arrived < nc) {
+            report_status(p.status, ST_TIMEOUT_SPLITK, blockIdx.x);
+            abort_flag = 1;
+          }
+          epi_last = arrived >= nc;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool go = epi_last != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // epi_last is rewritten for the next tile
+        if (!go) { ok = false; break; }
+        // slices are whole groups of 8 features, so that a thread sums 8 consecutive features of one token
+        // (two 16-byte loads per contributor) and stores them with one 16-byte access
+        const int rows_per = ((TILE_F + nc - 1) / nc + 7) & ~7;
+        const int r_lo = ((int)blockIdx.x - c_first) * rows_per;
+        int r_hi = r_lo + rows_per;
+        if (r_hi > TILE_F) r_hi = TILE_F;
+        const int n_grp = r_hi > r_lo ? (r_hi - r_lo) / 8 : 0;
+        const int n_items = n_grp * valid;
+        const bool wide_ok = (p.ldo % 8 == 0) && (p.out_col0 % 8 == 0);
+        for (int i = et; i < n_items; i += EPI_THREADS) {
+          const int rr = r_lo + (i % n_grp) * 8;     // consecutive threads -> consecutive feature groups
+          const int col = i / n_grp;                 // token column (< valid)
+          float g8[8], u8[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { g8[j] = 0.f; u8[j] = 0.f; }
+          for (int cb = c_first; cb <= c_last; cb += 4) {
+            float4 tg[4][2], tu[4][2];
+#pragma unroll
+            for (int ci = 0; ci < 4; ++ci) {   // four contributors' loads in flight together
+              const int c = cb + ci;
+              tg[ci][0] = tg[ci][1] = tu[ci][0] = tu[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (c <= c_last) {
+                const int slot = cta_slot(sched, c, u);
+                const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems + (size_t)col * TILE_F + rr;
+                tg[ci][0] = __ldcg(reinterpret_cast<const float4*>(ws));
+                tg[ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + 4));
+                if (DUAL) {
+                  tu[ci][0] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F));
+                  tu[ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F + 4));
+                }
+              }
+            }
+#pragma unroll
+            for (int ci = 0; ci < 4; ++ci) {   // fixed summation order
+              g8[0] += tg[ci][0].x; g8[1] += tg[ci][0].y; g8[2] += tg[ci][0].z; g8[3] += tg[ci][0].w;
+              g8[4] += tg[ci][1].x; g8[5] += tg[ci][1].y; g8[6] += tg[ci][1].z; g8[7] += tg[ci][1].w;
+              if (DUAL) {
+                u8[0] += tu[ci][0].x; u8[1] += tu[ci][0].y; u8[2] += tu[ci][0].z; u8[3] += tu[ci][0].w;
+                u8[4] += tu[ci][1].x; u8[5] += tu[ci][1].y; u8[6] += tu[ci][1].z; u8[7] += tu[ci][1].w;
+              }
+            }
+          }
+          const int f0 = un.m * TILE_F + rr;
+          const long long row = row0 + col;
+          if (wide_ok && f0 + 8 <= p.F) {
+            const size_t idx = (size_t)row * p.ldo + p.out_col0 + f0;
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = DUAL ? silu(g8[j]) * u8[j] : g8[j];
+            if (p.residual) {
+              const uint4 rv = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.residual + idx);
+              const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { const float2 t = __bfloat1622float2(rb[j]); y[2 * j] += t.x; y[2 * j + 1] += t.y; }
+            }
+            uint4 o;
+            __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+            if (p.mode == 2) {
+              for (int pe = 0; pe < p.n_peers; ++pe) *reinterpret_cast<uint4*>((__nv_bfloat16*)p.peer_out[pe] + idx) = o;
+            } else {
+              *reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + idx) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (f0 + j < p.F) emit(g8[j], u8[j], row, f0 + j);
+          }
+        }
+        // count this CTA out; the last one out re-arms the counter for the next launch
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          const int old = atomicAdd(&p.counters[c_first], 0x10000);
+          if ((old >> 16) == nc - 1) p.counters[c_first] = 0;
+        }
       }
     }
   }
@@ -482,6 +542,7 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   ka->stages = st;
   ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : 2000) * 1000000ull;
   *grid = p->grid > 0 ? p->grid : sm_count_cached();
+  if (*grid > sm_count_cached()) *grid = sm_count_cached();   // the split-K reduction needs every CTA resident
   *smem = (size_t)st * ka->stage_bytes + 1024;
   return 0;
 }

@@ -43,6 +43,7 @@ typedef struct SkeinGemmParams {
   int32_t grid;             // 0 -> number of SMs
   int32_t wait_budget_ms;   // 0 -> 2000
   int32_t w_packed;         // W is stored tile by tile: [rows/128][K/64 (or /128 fp8)][128][128 bytes]
+  int32_t line_cut_only;    // 1: never use the tile-aligned split (see gemm_sched.cuh), for comparison runs
 } SkeinGemmParams;
 
 // Returns 0 or a cudaError_t / negative argument-error code.

@@ -148,6 +148,10 @@ class Decoder:
     def _attention(self, li: int, normed, inp: BatchInputs):
         cfg, sh, lw = self.cfg, self.sh, self.w.layers[li]
         qkv = self._col_linear(normed, lw, "wqkv")
+        if not inp.is_prefill and inp.seq_of_token is None and ops.can_fuse_rope(self.kv[li], sh["Hq"], sh["Hkv"]):
+            # decode: RoPE and the cache append ride in the attention kernel
+            return ops.attn_decode_rope(qkv, inp.positions, inp.block_table, self.cos_sin, self.kv[li], inp.seq_lens,
+                                        sh["Hq"], sh["Hkv"], cfg.head_dim, ctx_hint=inp.ctx_hint)
         ops.rope_kv_append(qkv, inp.positions, inp.seq_of_token, inp.block_table, self.cos_sin, self.kv[li],
                            sh["Hq"], sh["Hkv"], cfg.head_dim)
         if inp.is_prefill:

@@ -33,7 +33,7 @@ class GemmParams(C.Structure):
         ("w_rows_per_group", C.c_int32), ("up_row_off", C.c_int32), ("x_rows", C.c_int32),
         ("t_static", C.c_int32), ("n_tile", C.c_int32), ("ldo", C.c_int32), ("out_col0", C.c_int32),
         ("mode", C.c_int32), ("fp8", C.c_int32), ("stages", C.c_int32), ("grid", C.c_int32),
-        ("wait_budget_ms", C.c_int32), ("w_packed", C.c_int32),
+        ("wait_budget_ms", C.c_int32), ("w_packed", C.c_int32), ("line_cut_only", C.c_int32),
     ]
 
 
@@ -80,6 +80,8 @@ def lib():
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_decode_mma", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
+    _sig(L, "skein_attn_decode_rope_mma", i32,
+         [vp, i64, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_prefill", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_router_topk", i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp])

@@ -93,16 +93,16 @@ def _gemm_launch(p: "_lib.GemmParams", what: str):
     p.workspace = ws.gemm_ws.data_ptr()
     p.counters = ws.gemm_counters.data_ptr()
     p.status = ws.status.data_ptr()
+    p.line_cut_only = 1 if os.environ.get("SKEIN_GEMM_ALIGNED", "1") == "0" else 0
     if p.grid == 0 and os.environ.get("SKEIN_GEMM_AUTOGRID", "1") == "1":
-        # With at least ~0.6 tiles per SM, give every CTA a whole number of tiles: no tile is split, so the
-        # stream-K fix-up (partial store, counter, re-read) disappears; measured 3-12 % faster than equal
-        # K-shares on 148 CTAs. The estimate assumes one token tile per group (decode); a wrong guess only
-        # brings the fix-up back, never a wrong result.
+        # With between one and two tiles per SM, give every CTA a whole number of tiles: no tile is split, so
+        # the stream-K partial store / reduce disappears; measured 3-12 % faster than equal K-shares on all
+        # CTAs. (With fewer tiles than SMs the kernel itself cuts each tile into aligned pieces; with many
+        # tiles per SM the equal-share split measured ~2 % faster end to end, so it stays the default there.)
+        # The estimate assumes one token tile per group (decode); a wrong guess only changes the split.
         rows = p.t_static if not p.group_cnt else p.n_tile
         units = p.G * ((p.F + 127) // 128) * max(1, (rows + p.n_tile - 1) // p.n_tile)
-        # (in a full decode step the gain only shows while tiles are scarce: with many tiles per SM the
-        # equal-share split measured ~2 % faster end to end, so it keeps the default there)
-        if 0.6 * ws.sm_count <= units <= 2 * ws.sm_count:
+        if ws.sm_count < units <= 2 * ws.sm_count:
             per_cta = (units + ws.sm_count - 1) // ws.sm_count
             p.grid = (units + per_cta - 1) // per_cta
     _lib.check(_lib.lib().skein_gemm_ws(C.byref(p), _lib.stream_ptr()), what)
@@ -374,6 +374,39 @@ def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=
         _lib.ptr(wsf), _lib.ptr(ctr), ws.status.data_ptr(), B, Hq, Hkv, D, kv_cache.shape[3], block_table.stride(0),
         kv_cache.shape[0], splits, float(scale), _lib.stream_ptr())
     _lib.check(rc, "attn_decode")
+    _lib.count_launch()
+    return out
+
+
+def can_fuse_rope(kv_cache, Hq, Hkv) -> bool:
+    """True when attn_decode_rope runs as one kernel (else it falls back to rope_kv_append + attn_decode)."""
+    return (kv_cache.is_cuda and kv_cache.shape[3] % 16 == 0 and Hq // Hkv <= 16 and kv_cache.shape[4] == 128
+            and os.environ.get("SKEIN_ATTN_DECODE", "mma") == "mma" and os.environ.get("SKEIN_FUSE_ROPE", "1") != "0")
+
+
+def attn_decode_rope(qkv, positions, block_table, cos_sin, kv_cache, seq_lens, Hq, Hkv, D, scale=None, out=None,
+                     splits=None, ctx_hint=1024):
+    """Decode attention straight from the fused q/k/v projection: RoPE of q and k, append of the new token's k/v
+    to the paged cache, attention; one launch (csrc/kernels/attn_decode_mma.cu). qkv: [B, (Hq + 2 Hkv) * D]."""
+    if not can_fuse_rope(kv_cache, Hq, Hkv):
+        rope_kv_append(qkv, positions, None, block_table, cos_sin, kv_cache, Hq, Hkv, D)
+        return attn_decode(qkv, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale, out, splits, ctx_hint)
+    B = qkv.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(B, Hq * D, dtype=torch.bfloat16, device=qkv.device)
+    ws = workspace()
+    if splits is None:
+        splits = pick_splits(B, Hkv, ctx_hint, ws.sm_count)
+    wsf, ctr = (None, None)
+    if splits > 1:
+        wsf, ctr = ws.attn_scratch(B, Hq, Hkv, splits)
+    rc = _lib.lib().skein_attn_decode_rope_mma(
+        qkv.data_ptr(), qkv.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
+        positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[0], out.data_ptr(), _lib.ptr(wsf), _lib.ptr(ctr),
+        ws.status.data_ptr(), B, Hq, Hkv, D, kv_cache.shape[3], block_table.stride(0), kv_cache.shape[0], splits,
+        float(scale), _lib.stream_ptr())
+    _lib.check(rc, "attn_decode_rope")
     _lib.count_launch()
     return out
 

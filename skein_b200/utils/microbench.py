@@ -52,6 +52,34 @@ def timeit(fn, iters, warmup, flush=True):
     return ts[len(ts) // 2]
 
 
+def timeit_graph(make, bytes_per_launch, iters, warmup):
+    """In-graph timing: enough independent copies of the op's operands that their total exceeds twice the L2,
+    one launch per copy captured into a CUDA graph, launches back to back as in a decode step. Returns the mean
+    time per launch (the event timer's ~2 us resolution is amortised over the whole graph)."""
+    copies = max(2, min(64, -(-(256 << 20) // max(int(bytes_per_launch), 1))))
+    fns = [make()[0] for _ in range(copies)]
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) * 1e3 / copies)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def _report(name, us, bytes_, flops, pk):
     gbs = bytes_ / us * 1e-3
     tfs = flops / us * 1e-6
@@ -150,12 +178,18 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="time launches back to back inside a CUDA graph over rotating operand copies (cold L2, "
+                         "no per-launch event overhead) instead of one launch per event pair")
     a = ap.parse_args(argv)
     pk = peaks()
     for name in (OPS if a.op == "all" else a.op.split(",")):
         fn, by, fl = build(name, a)
-        us = timeit(fn, a.iters, a.warmup, flush=not a.no_flush)
-        _report(f"{name}/tp{a.tp}", us, by, fl, pk)
+        if a.graph:
+            us = timeit_graph(lambda: build(name, a), by, a.iters, a.warmup)
+        else:
+            us = timeit(fn, a.iters, a.warmup, flush=not a.no_flush)
+        _report(f"{name}/tp{a.tp}" + ("/graph" if a.graph else ""), us, by, fl, pk)
     ops.workspace().check_status()
 
 

@@ -143,6 +143,29 @@ def test_attn_decode_mma_pages_and_unwritten_slots(Hq, Hkv, ps, splits):
     assert _rel_err(o, ref.attn_decode(q, kv_clean, bt, sl, Hq, Hkv, D)) < 1e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv,splits", [(32, 8, 1), (4, 1, 5), (16, 2, 3)])
+def test_attn_decode_rope_fusion_equals_separate_kernels(Hq, Hkv, splits):
+    """RoPE + KV append + attention in one launch against rope_kv_append followed by attn_decode."""
+    torch.manual_seed(9)
+    B, D, ps = 8, 128, 16
+    lens = [1, 16, 17, 130, 640, 33, 0, 48]
+    kv, bt, _ = _make_cache(B, [l + 1 for l in lens], Hkv, D, ps)
+    kv2 = kv.clone()
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qkv2 = qkv.clone()
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)     # -1 for the padding row
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tab = ref.rope_cos_sin_table(1024, D, 1e6, DEV)
+    assert ops.can_fuse_rope(kv, Hq, Hkv)
+    o1 = ops.attn_decode_rope(qkv, pos, bt, tab, kv, sl, Hq, Hkv, D, splits=splits)
+    ops.rope_kv_append(qkv2, pos, None, bt, tab, kv2, Hq, Hkv, D)
+    o2 = ops.attn_decode(qkv2, kv2, bt, sl, Hq, Hkv, D, splits=splits, impl="mma")
+    _check_status()
+    assert torch.equal(qkv[:, Hq * D:], qkv2[:, Hq * D:])          # the fused kernel leaves the projection untouched
+    assert _rel_err(kv, kv2) < 1e-3
+    assert _rel_err(o1, o2) < 5e-3
+
+
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
 def test_attn_prefill(Hq, Hkv):
     torch.manual_seed(6)
