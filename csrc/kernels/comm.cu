@@ -2,9 +2,9 @@
 //
 //   * symmetric heap: every rank cudaMallocs one heap and exports a CUDA IPC handle; peers map it,
 //     so kernels address a peer's buffer with plain loads/stores that travel over NVLink.
-//   * push_rows: one-shot "all-gather of partials": copy a local buffer into this rank's slot of every
-//     peer's buffer and publish this rank's flag there. Followed by reduce_residual_rmsnorm (norm.cu)
-//     it is a one-shot all-reduce; the fused path does the same push from the GEMM epilogue.
+//   * publish_rows: copy a local tensor into this rank's peer-mapped buffer and set this rank's flag on
+//     every peer. Followed by reduce_residual_rmsnorm (norm.cu), which pulls every rank's buffer over
+//     NVLink and sums, it is a one-shot all-reduce; the fused path publishes from the GEMM epilogue.
 //   * argmax_push: vocabulary-parallel greedy sampling. Each rank reduces its logit shard to one
 //     (value, global index) pair per row and pushes 8 bytes per row to every peer
 //     (merge_candidates in sample.cu picks the winner).
@@ -33,7 +33,7 @@ struct PeerPtrs {
 
 // Publishes epoch+1 on every peer once all CTAs of the launch have finished their stores.
 __device__ __forceinline__ void publish_when_all_done(const PeerPtrs& pp, int* epoch, int* done_counter) {
-  __threadfence_system();
+  __threadfence_system();   // this launch may have written into peers' memory (argmax candidates)
   __syncthreads();
   if (threadIdx.x == 0) {
     const int total = gridDim.x * gridDim.y * gridDim.z;
@@ -42,18 +42,16 @@ __device__ __forceinline__ void publish_when_all_done(const PeerPtrs& pp, int* e
       *done_counter = 0;
       __threadfence_system();
       const int e = *epoch + 1;
-      for (int i = 0; i < pp.n; ++i) st_release_sys(pp.flag[i], e);
+      for (int i = 0; i < pp.n; ++i) st_relaxed_sys(pp.flag[i], e);   // ordered by the fence above
       *epoch = e;
     }
   }
 }
 
-__global__ void __launch_bounds__(256) push_rows_kernel(const uint4* __restrict__ src, long long n_vec, PeerPtrs pp,
-                                                         int* epoch, int* done_counter) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
-    const uint4 v = src[i];
-    for (int p = 0; p < pp.n; ++p) reinterpret_cast<uint4*>(pp.dst[p])[i] = v;
-  }
+__global__ void __launch_bounds__(256) publish_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst_local,
+                                                            long long n_vec, PeerPtrs pp, int* epoch, int* done_counter) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x)
+    dst_local[i] = src[i];
   publish_when_all_done(pp, epoch, done_counter);
 }
 
@@ -138,18 +136,19 @@ extern "C" int skein_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(pt
 extern "C" int skein_ipc_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
 
 // ---- collectives ----------------------------------------------------------------------------------
-extern "C" int skein_push_rows(const void* src, long long bytes, void* const* peer_dst, int* const* peer_flag,
-                               int n_peers, int* epoch, int* done_counter, void* stream) {
+extern "C" int skein_publish_rows(const void* src, long long bytes, void* dst_local, int* const* peer_flag, int n_peers,
+                                  int* epoch, int* done_counter, void* stream) {
   using namespace skein;
   if (bytes % 16 != 0 || n_peers < 1 || n_peers > MAXP) return -1;
   PeerPtrs pp;
   pp.n = n_peers;
-  for (int i = 0; i < n_peers; ++i) { pp.dst[i] = peer_dst[i]; pp.flag[i] = peer_flag[i]; }
+  for (int i = 0; i < n_peers; ++i) { pp.dst[i] = nullptr; pp.flag[i] = peer_flag[i]; }
   const long long n_vec = bytes / 16;
   int grid = (int)((n_vec + 255) / 256);
   if (grid > 296) grid = 296;
   if (grid < 1) grid = 1;
-  push_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, n_vec, pp, epoch, done_counter);
+  publish_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst_local, n_vec, pp, epoch,
+                                                             done_counter);
   return (int)cudaGetLastError();
 }
 

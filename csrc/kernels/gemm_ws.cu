@@ -13,9 +13,9 @@
 //     tcgen05.mma into one of two TMEM accumulators, warps 2-5 drain the other accumulator
 //     (tcgen05.ld), apply the epilogue and store.
 //   * epilogues: plain store (+ residual), SwiGLU of a gate/up pair of weight tiles that share the
-//     token tile, or a store of the partial result into every tensor-parallel peer's buffer
-//     followed by a release of that peer's flag (the all-reduce is finished by the consumer,
-//     see norm.cu: reduce_residual_rmsnorm).
+//     token tile, or a store of the partial result into a peer-mapped local buffer followed by a
+//     release of this rank's flag on every tensor-parallel peer (the all-reduce is finished by the
+//     consumer, which pulls the partials over NVLink: see norm.cu, reduce_residual_rmsnorm).
 //
 // Replaces the reference's cuBLASLt matmul host op (vendor/luminal/crates/luminal_cuda_lite/src/
 // host/cublaslt/mod.rs:888-1130), its fp8 GEMV (same file :797-886) and the GLUMoE GEMV kernels
@@ -210,11 +210,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const size_t idx = (size_t)row * p.ldo + p.out_col0 + f;
         if (p.residual) y += __bfloat162float(((const __nv_bfloat16*)p.residual)[idx]);
         const __nv_bfloat16 yb = __float2bfloat16(y);
-        if (p.mode == 2) {
-          for (int pe = 0; pe < p.n_peers; ++pe) ((__nv_bfloat16*)p.peer_out[pe])[idx] = yb;
-        } else {
-          ((__nv_bfloat16*)p.out)[idx] = yb;
-        }
+        ((__nv_bfloat16*)p.out)[idx] = yb;
       };
       // Stream-K tiles that several CTAs share: every contributor parks its fp32 partial and counts itself
       // in (phase 1, inside the loop); once its own work is done it waits for the tile's other
@@ -384,11 +380,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
-            if (p.mode == 2) {
-              for (int pe = 0; pe < p.n_peers; ++pe) *reinterpret_cast<uint4*>((__nv_bfloat16*)p.peer_out[pe] + idx) = o;
-            } else {
-              *reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + idx) = o;
-            }
+            *reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + idx) = o;
           } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -405,20 +397,23 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
   }
 
-  // ---- tensor-parallel push: the last CTA to finish publishes this rank's flag on every peer ---
+  // ---- tensor-parallel publish: the last CTA to finish sets this rank's flag on every peer -------
+  // The result sits in local memory that the peers have mapped; they pull it once they see the flag. Every
+  // epilogue thread orders its stores device-wide, the CTAs count themselves in, and the last one issues the
+  // single system-scope fence that orders all of those stores before the flag words it then writes.
   if (p.mode == 2) {
     if (warp >= 2) {
-      __threadfence_system();
+      __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
         const int old = atomicAdd(p.done_counter, 1);
         if (old == (int)gridDim.x - 1) {
           *p.done_counter = 0;
-          __threadfence_system();
+          __threadfence_system();   // orders every CTA's stores (observed through the counter) before the flags
           const int e = *p.epoch + 1;
           // a failed launch publishes nothing: the consumers' bounded waits then report it
           if (p.status == nullptr || p.status[0] == 0) {
-            for (int pe = 0; pe < p.n_peers; ++pe) st_release_sys(p.peer_flag[pe], e);
+            for (int pe = 0; pe < p.n_peers; ++pe) st_relaxed_sys(p.peer_flag[pe], e);
           }
           *p.epoch = e;
         }

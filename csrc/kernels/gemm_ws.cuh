@@ -23,9 +23,9 @@ typedef struct SkeinGemmParams {
   // fp8 block scales (fp8 != 0): one float per 128 K-elements.
   const float* w_scale;     // [G * w_rows_per_group, K / 128]
   const float* x_scale;     // [x_rows, K / 128]
-  // one-shot push to peers (mode 2): the tile is stored into every peer's buffer.
-  void* peer_out[SKEIN_MAX_PEERS];      // bf16 bases (already offset to this rank's slot)
-  int32_t* peer_flag[SKEIN_MAX_PEERS];  // flag word on each peer that this rank sets
+  // publish (mode 2): the result is stored locally (out, a buffer that the peers have mapped) and, once every
+  // CTA is done, this rank's flag word on each peer is set; the consumers pull the partials over NVLink.
+  int32_t* peer_flag[SKEIN_MAX_PEERS];  // flag word on each peer (this rank included) that this rank sets
   int32_t* epoch;           // device int: last epoch published through peer_flag
   int32_t* done_counter;    // device int, zero at first use
   int32_t n_peers;
@@ -37,7 +37,7 @@ typedef struct SkeinGemmParams {
   int32_t n_tile;           // tokens per tile: multiple of 16, <= 256 (<= 128 when dual)
   int32_t ldo;
   int32_t out_col0;
-  int32_t mode;             // 0 store, 1 SwiGLU(gate, up) store (dual), 2 push to peers
+  int32_t mode;             // 0 store, 1 SwiGLU(gate, up) store (dual), 2 store + publish flags to peers
   int32_t fp8;
   int32_t stages;           // 0 -> as many as fit
   int32_t grid;             // 0 -> number of SMs

@@ -254,11 +254,7 @@ gemm_ws_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               const size_t idx = (size_t)(row0 + j) * p.ldo + p.out_col0 + f;
               if (p.residual) y += __bfloat162float(((const __nv_bfloat16*)p.residual)[idx]);
               const __nv_bfloat16 yb = __float2bfloat16(y);
-              if (p.mode == 2) {
-                for (int pe = 0; pe < p.n_peers; ++pe) ((__nv_bfloat16*)p.peer_out[pe])[idx] = yb;
-              } else {
-                ((__nv_bfloat16*)p.out)[idx] = yb;
-              }
+              ((__nv_bfloat16*)p.out)[idx] = yb;
             }
           }
         }
@@ -267,8 +263,9 @@ gemm_ws_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   }
 
+  // publish: local stores ordered device-wide, then one system-scope fence by the last CTA (see gemm_ws.cu)
   if (p.mode == 2 && warp >= 2) {
-    __threadfence_system();
+    __threadfence();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) {
       const int old = atomicAdd(p.done_counter, 1);
@@ -277,7 +274,7 @@ gemm_ws_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __threadfence_system();
         const int e = *p.epoch + 1;
         if (p.status == nullptr || p.status[0] == 0)
-          for (int pe = 0; pe < p.n_peers; ++pe) st_release_sys(p.peer_flag[pe], e);
+          for (int pe = 0; pe < p.n_peers; ++pe) st_relaxed_sys(p.peer_flag[pe], e);
         *p.epoch = e;
       }
     }

@@ -26,6 +26,9 @@ namespace skein {
 struct NormParams {
   const __nv_bfloat16* residual;   // [B, H] or null (treated as zero)
   const __nv_bfloat16* partial;    // [n_src][rows][H] or null
+  const __nv_bfloat16* src_base[8];  // with use_ptrs: source s is the [rows][H] buffer at src_base[s] (a peer's memory,
+                                   // read over NVLink) instead of partial + s * src_stride
+  int use_ptrs;
   const int* row_idx;              // [B, topk] rows into partial, or null (row = b)
   const float* row_w;              // [B, topk] weights, or null
   const int* owner_ids;            // [B, topk] expert id of each pair, or null: with it only the sources that own the
@@ -93,26 +96,52 @@ __device__ __forceinline__ bool reduce_norm_row(const NormParams& p, const int b
 #pragma unroll
       for (int i = 0; i < 8; ++i) a[i] = 0.f;
     }
-    if (p.partial) {
+    if (p.partial || p.use_ptrs) {
       const int nk = p.topk > 0 ? p.topk : 1;
-      for (int j = 0; j < nk; ++j) {
-        const int row = p.row_idx ? p.row_idx[b * p.topk + j] : b;
+      // the (row, weight, owner) triples of up to 8 slots are fetched together, ahead of the data loads
+      int rows8[8], own8[8];
+      float w8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        rows8[j] = (j < nk) ? (p.row_idx ? p.row_idx[b * p.topk + j] : b) : -1;
+        w8[j] = (j < nk && p.row_w) ? p.row_w[b * p.topk + j] : 1.f;
+        own8[j] = (j < nk && p.owner_ids) ? p.owner_ids[b * p.topk + j] : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {   // top-k is at most 8 (host-checked)
+        if (j >= nk) break;
+        const int row = rows8[j];
         if (row < 0) continue;  // pair routed to an expert that lives on another rank
-        const float w = p.row_w ? p.row_w[b * p.topk + j] : 1.f;
+        const float w = w8[j];
         int s_lo = 0, s_hi = p.n_src;
         if (p.owner_ids) {
-          s_lo = (p.owner_ids[b * p.topk + j] / p.experts_per_owner) * p.owner_span;
+          s_lo = (own8[j] / p.experts_per_owner) * p.owner_span;
           s_hi = s_lo + p.owner_span;
           if (s_lo < 0 || s_hi > p.n_src) continue;
         }
-        for (int s = s_lo; s < s_hi; ++s) {
-          const __nv_bfloat16* src = p.partial + (size_t)s * p.src_stride + (size_t)row * p.H + h;
-          uint4 r;
-          // data written by other GPUs: bypass L1
-          asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(src));
-          const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
+        // sources in batches of 8: every load of a batch is issued before the first is consumed (the partials of
+        // 8 tensor-parallel ranks would otherwise cost 8 dependent round trips); the sum order stays s_lo..s_hi
+        for (int s0 = s_lo; s0 < s_hi; s0 += 8) {
+          uint4 r8[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(rb[i]); a[2 * i] += w * f.x; a[2 * i + 1] += w * f.y; }
+          for (int u = 0; u < 8; ++u) {
+            r8[u] = make_uint4(0, 0, 0, 0);
+            if (s0 + u < s_hi) {
+              const __nv_bfloat16* src = (p.use_ptrs ? p.src_base[s0 + u] : p.partial + (size_t)(s0 + u) * p.src_stride) +
+                                         (size_t)row * p.H + h;
+              // data written by other GPUs: bypass L1
+              asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(r8[u].x), "=r"(r8[u].y), "=r"(r8[u].z), "=r"(r8[u].w) : "l"(src));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (s0 + u < s_hi) {
+              const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r8[u]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(rb[i]); a[2 * i] += w * f.x; a[2 * i + 1] += w * f.y; }
+            }
+          }
         }
       }
     }
@@ -336,11 +365,14 @@ extern "C" int skein_reduce_residual_rmsnorm(
     const void* residual, const void* partial, const int* row_idx, const float* row_w, const void* gamma,
     void* residual_out, void* normed_out, const int* flags, const int* epoch, int* status,
     long long src_stride, int B, int H, int n_src, int topk, float eps, int wait_budget_ms, const int* owner_ids,
-    int experts_per_owner, int owner_span, void* stream) {
+    int experts_per_owner, int owner_span, const void* const* src_ptrs, void* stream) {
   using namespace skein;
-  if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0) return -1;
+  if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0 || topk > 8) return -1;
+  if (src_ptrs != nullptr && (n_src < 1 || n_src > 8)) return -1;
   if (B == 0) return 0;
   NormParams p;
+  p.use_ptrs = src_ptrs != nullptr;
+  for (int i = 0; i < 8; ++i) p.src_base[i] = (p.use_ptrs && i < n_src) ? (const __nv_bfloat16*)src_ptrs[i] : nullptr;
   p.residual = (const __nv_bfloat16*)residual; p.partial = (const __nv_bfloat16*)partial;
   p.row_idx = row_idx; p.row_w = row_w; p.gamma = (const __nv_bfloat16*)gamma;
   p.owner_ids = owner_ids; p.experts_per_owner = experts_per_owner > 0 ? experts_per_owner : 1; p.owner_span = owner_span > 0 ? owner_span : 1;
@@ -366,14 +398,17 @@ extern "C" int skein_reduce_norm_route(
     const int* flags, const int* epoch, int* status, long long src_stride, int B, int H, int n_src, float eps,
     int wait_budget_ms, const void* wg, int E, int topk, int e_first, int e_count, int* expert_ids, float* expert_w,
     int* counts, int* offsets, int* row_of, int* src_token, void* xs, int* barrier, int max_resident_ctas,
-    void* stream) {
+    const void* const* src_ptrs, void* stream) {
   using namespace skein;
   if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0) return -1;
   if (B == 0) return 0;
   if (E > NR_MAX_E || topk > NR_MAX_K || topk > E || B * topk > NR_MAX_PAIRS) return -1;
   if (B > max_resident_ctas) return -2;
   if (gamma == nullptr || normed_out == nullptr || wg == nullptr || barrier == nullptr) return -1;
+  if (src_ptrs != nullptr && (n_src < 1 || n_src > 8)) return -1;
   NormParams p;
+  p.use_ptrs = src_ptrs != nullptr;
+  for (int i = 0; i < 8; ++i) p.src_base[i] = (p.use_ptrs && i < n_src) ? (const __nv_bfloat16*)src_ptrs[i] : nullptr;
   p.residual = (const __nv_bfloat16*)residual; p.partial = (const __nv_bfloat16*)partial;
   p.row_idx = nullptr; p.row_w = nullptr; p.gamma = (const __nv_bfloat16*)gamma;
   p.owner_ids = nullptr; p.experts_per_owner = 1; p.owner_span = 1;

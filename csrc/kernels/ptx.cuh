@@ -202,6 +202,11 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t fmt_a, uint32_t fmt_b, u
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Plain system-scope store: used for the per-peer flag words AFTER one system-scope fence has ordered the
+// data before them (a release store per peer would repeat that fence once per peer).
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -27,7 +27,7 @@ class GemmParams(C.Structure):
         ("group_off", C.c_void_p), ("group_cnt", C.c_void_p),
         ("workspace", C.c_void_p), ("counters", C.c_void_p), ("status", C.c_void_p),
         ("w_scale", C.c_void_p), ("x_scale", C.c_void_p),
-        ("peer_out", C.c_void_p * MAX_PEERS), ("peer_flag", C.c_void_p * MAX_PEERS),
+        ("peer_flag", C.c_void_p * MAX_PEERS),
         ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
         ("n_peers", C.c_int32), ("G", C.c_int32), ("F", C.c_int32), ("K", C.c_int32),
         ("w_rows_per_group", C.c_int32), ("up_row_off", C.c_int32), ("x_rows", C.c_int32),
@@ -67,10 +67,10 @@ def lib():
     _sig(L, "skein_gemm_ws_workspace_bytes", i64, [C.POINTER(GemmParams)])
     _sig(L, "skein_sm_count", i32, [])
     _sig(L, "skein_reduce_residual_rmsnorm", i32,
-         [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, i32, vp, i32, i32, vp])
+         [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, i32, vp, i32, i32, vp, vp])
     _sig(L, "skein_reduce_norm_route", i32,
          [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, f32, i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
-          vp, vp, i32, vp])
+          vp, vp, i32, vp, vp])
     _sig(L, "skein_rope_kv_append", i32,
          [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp])
     _sig(L, "skein_embed_gather", i32, [vp, vp, vp, i32, i32, i32, i32, vp])
@@ -98,7 +98,7 @@ def lib():
     _sig(L, "skein_ipc_open", i32, [C.c_char_p, pvp])
     _sig(L, "skein_ipc_close", i32, [vp])
     _sig(L, "skein_ipc_handle_bytes", i32, [])
-    _sig(L, "skein_push_rows", i32, [vp, i64, pvp, pvp, i32, vp, vp, vp])
+    _sig(L, "skein_publish_rows", i32, [vp, i64, vp, pvp, i32, vp, vp, vp])
     _sig(L, "skein_argmax_push", i32, [vp, i64, i32, i32, i32, pvp, pvp, pvp, i32, vp, vp, vp])
     _sig(L, "skein_copy_pages", i32, [vp, vp, vp, vp, i32, i64, vp])
     _sig(L, "skein_wait_flag", i32, [vp, i32, i32, vp, vp])

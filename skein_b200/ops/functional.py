@@ -246,28 +246,40 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
     return out
 
 
+def _partial_args(partial, flags, epoch):
+    """(data pointer, source stride, n_src, per-source pointer array or None, flags, epoch) of a partial-sum operand:
+    a [n_src, rows, H] tensor, or peer partials (parallel/tp.py: one peer-mapped [rows, H] buffer per rank, pulled
+    over NVLink by the kernel)."""
+    if partial is None:
+        return None, 0, 0, None, flags, epoch
+    if hasattr(partial, "ptrs"):
+        return partial.local.data_ptr(), 0, partial.n_src, partial.ptrs, partial.flags, partial.epoch
+    return partial.data_ptr(), partial.stride(0), partial.shape[0], None, flags, epoch
+
+
 def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None, residual_out=None,
                             normed_out=None, flags=None, epoch=None, wait_budget_ms=0, owner_ids=None, experts_per_owner=1,
                             owner_span=1):
-    """See csrc/kernels/norm.cu. partial: [n_src, rows, H] or None. Returns (residual_out, normed_out)."""
-    src = residual if residual is not None else partial
+    """See csrc/kernels/norm.cu. partial: [n_src, rows, H], peer partials, or None. Returns (residual_out, normed_out)."""
+    peer = hasattr(partial, "ptrs")
+    src = residual if residual is not None else (partial.local if peer else partial)
     if not src.is_cuda:
         return ref.reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx, row_w, owner_ids, experts_per_owner, owner_span)
     H = src.shape[-1]
-    B = residual.shape[0] if residual is not None else (row_idx.shape[0] if row_idx is not None else partial.shape[1])
+    B = residual.shape[0] if residual is not None else (row_idx.shape[0] if row_idx is not None else
+                                                        (partial.rows if peer else partial.shape[1]))
     if residual_out is None:
         residual_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
     if normed_out is None and gamma is not None:
         normed_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
-    n_src = partial.shape[0] if partial is not None else 0
-    src_stride = partial.stride(0) if partial is not None else 0
+    pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
     topk = row_idx.shape[1] if row_idx is not None else 0
     ws = workspace()
     rc = _lib.lib().skein_reduce_residual_rmsnorm(
-        _lib.ptr(residual), _lib.ptr(partial), _lib.ptr(row_idx), _lib.ptr(row_w), _lib.ptr(gamma),
+        _lib.ptr(residual), pptr, _lib.ptr(row_idx), _lib.ptr(row_w), _lib.ptr(gamma),
         _lib.ptr(residual_out), _lib.ptr(normed_out), _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(),
         src_stride, B, H, n_src, topk, float(eps), wait_budget_ms, _lib.ptr(owner_ids), experts_per_owner, owner_span,
-        _lib.stream_ptr())
+        ptrs, _lib.stream_ptr())
     _lib.check(rc, "reduce_residual_rmsnorm")
     _lib.count_launch()
     return residual_out, normed_out
@@ -286,7 +298,8 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
     (residual_out, normed_out, expert_ids [T,k], weights [T,k], counts [E], offsets [E+1], row_of [T*k],
     src_token [T*k], xs [T*k, H]).
     """
-    src = residual if residual is not None else partial
+    peer = hasattr(partial, "ptrs")
+    src = residual if residual is not None else (partial.local if peer else partial)
     E = wg.shape[0]
     e_count = E if e_count is None else e_count
     if not src.is_cuda:
@@ -295,7 +308,7 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
         counts, offsets, row_of, src_token = ref.router_plan(ids, E, e_first, e_count)
         return res, normed, ids, w, counts, offsets, row_of, src_token, normed[src_token.long()]
     H = src.shape[-1]
-    T = residual.shape[0] if residual is not None else partial.shape[1]
+    T = residual.shape[0] if residual is not None else (partial.rows if peer else partial.shape[1])
     dev = src.device
     residual_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     normed_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
@@ -305,15 +318,14 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
     counts, offsets = meta[:E], meta[E:2 * E + 1]
     row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
     xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev)
-    n_src = partial.shape[0] if partial is not None else 0
-    src_stride = partial.stride(0) if partial is not None else 0
+    pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
     ws = workspace()
     rc = _lib.lib().skein_reduce_norm_route(
-        _lib.ptr(residual), _lib.ptr(partial), gamma.data_ptr(), residual_out.data_ptr(), normed_out.data_ptr(),
+        _lib.ptr(residual), pptr, gamma.data_ptr(), residual_out.data_ptr(), normed_out.data_ptr(),
         _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(), src_stride, T, H, n_src, float(eps), wait_budget_ms,
         wg.data_ptr(), E, topk, e_first, e_count, ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
         row_of.data_ptr(), src_token.data_ptr(), xs.data_ptr(), ws.route_barrier.data_ptr(), ws.sm_count,
-        _lib.stream_ptr())
+        ptrs, _lib.stream_ptr())
     _lib.check(rc, "reduce_norm_route")
     _lib.count_launch()
     return residual_out, normed_out, ids, w, counts, offsets, row_of, src_token, xs
@@ -582,20 +594,21 @@ def advance_decode_state(sampled, tokens, positions, seq_lens, step_counter=None
     _lib.count_launch()
 
 
-def linear_push(x, w, peer_out, peer_flag, epoch, done_counter, ldo, grouped=None, n_tile=None, rows_hint=None,
+def linear_push(x, w, out_local, peer_flag, epoch, done_counter, ldo, grouped=None, n_tile=None, rows_hint=None,
                 wait_budget_ms=0):
-    """Row-parallel projection whose epilogue stores the partial result into every peer's buffer.
+    """Row-parallel projection that publishes its partial result to the tensor-parallel peers.
 
-    peer_out[i] / peer_flag[i] are raw addresses valid in this process (peer-mapped memory): the bf16
-    destination of this rank's partial on peer i, and the flag word this rank owns there. `epoch` and
-    `done_counter` are local int32 device tensors. grouped = (counts, offsets) selects the per-expert form.
+    The partial is stored into `out_local` (a [rows, ldo] bf16 buffer of this rank that the peers have mapped) and,
+    when the whole launch is done, this rank's flag word on every peer is set: peer_flag[i] are raw addresses valid
+    in this process. `epoch` and `done_counter` are local int32 device tensors. grouped = (counts, offsets) selects
+    the per-expert form. The consumers pull the buffer over NVLink (reduce_residual_rmsnorm with peer partials).
     """
     _check_act(x)
     rows, K = x.shape
     wv, rows_pg, packed = _wview(w)
     if grouped is None:
         F = w.shape[0]
-        p = _base_params(x, wv, None, F, K, n_tile or pick_n_tile(rows, False), 2)
+        p = _base_params(x, wv, out_local, F, K, n_tile or pick_n_tile(rows, False), 2)
         p.w_rows_per_group = F
     else:
         counts, offsets = grouped
@@ -603,14 +616,13 @@ def linear_push(x, w, peer_out, peer_flag, epoch, done_counter, ldo, grouped=Non
         if n_tile is None:
             avg = (rows_hint if rows_hint is not None else rows) / E
             n_tile = pick_n_tile(int(math.ceil(avg * 1.5)), False)
-        p = _base_params(x, wv, None, F, K, n_tile, 2)
+        p = _base_params(x, wv, out_local, F, K, n_tile, 2)
         p.G, p.w_rows_per_group = E, rows_pg
         p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
     p.w_packed = packed
     p.ldo = ldo
-    p.n_peers = len(peer_out)
-    for i, (po, pf) in enumerate(zip(peer_out, peer_flag)):
-        p.peer_out[i] = po
+    p.n_peers = len(peer_flag)
+    for i, pf in enumerate(peer_flag):
         p.peer_flag[i] = pf
     p.epoch = epoch.data_ptr()
     p.done_counter = done_counter.data_ptr()

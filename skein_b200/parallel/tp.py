@@ -1,12 +1,17 @@
 """Tensor-parallel communicator: the collectives of a decoder block, fused into its kernels.
 
 Fused mode (decode and small prefill chunks). A row-parallel projection (o_proj, expert down)
-stores its partial output from the GEMM epilogue straight into every rank's receive buffer (slot =
-source rank) over NVLink peer stores and then releases a per-source flag on each peer; the kernel
-that consumes the sum (residual + RMSNorm, csrc/kernels/norm.cu) waits on the flags and adds the
-slots. A block therefore launches no collective. Two receive buffers alternate: a rank can only be
-one all-reduce ahead of the slowest peer, because it cannot finish all-reduce k+1 without that peer's
-contribution, which the peer sends only after it has consumed all-reduce k.
+stores its partial output from the GEMM epilogue into a local buffer that every peer has mapped, and
+the last CTA of the launch sets this rank's flag word on every peer (one system-scope fence per
+launch). The kernel that consumes the sum (residual + RMSNorm, csrc/kernels/norm.cu) waits on the
+flags and pulls all ranks' partials over NVLink with plain peer loads, every load of a row in flight
+at once, and adds them in rank order. A block therefore launches no collective, the GEMM issues no
+remote store, and the NVLink traffic sits in a kernel with thousands of independent loads. (Pushing
+the tile into every peer from the GEMM epilogue instead, as an earlier version did, measured 28 us per
+all-reduce at 8 ranks: two system-scope fences and 8 stores per element on 128 epilogue threads.)
+Two buffers alternate: a rank can only be one all-reduce ahead of the slowest peer, because it cannot
+finish all-reduce k+1 without that peer's flag, which the peer sets only after it has consumed (read)
+all-reduce k; so nobody overwrites a buffer that is still being read.
 
 NCCL mode (large prefill chunks, or SKEIN_COMM=nccl as the un-fused baseline): the same math with
 a library all-reduce between the local GEMM and the reduce kernel.
@@ -31,6 +36,15 @@ from ..ops import _lib
 from .symm import SymmetricHeap
 
 
+class PeerPartials:
+    """Operand of the reduce kernels: rank s's partial result is the [rows, H] buffer at ptrs[s] (peer-mapped
+    memory), complete once flags[s] has reached the device-side epoch."""
+
+    def __init__(self, local, ptrs, n_src, flags, epoch):
+        self.local, self.ptrs, self.n_src, self.flags, self.epoch = local, ptrs, n_src, flags, epoch
+        self.rows = local.shape[0]
+
+
 class TPComm:
     def __init__(self, group, device, hidden: int, fused_rows: int = 512, max_batch: int = 256, mode: str | None = None,
                  wait_budget_ms: int = 10000):
@@ -40,18 +54,17 @@ class TPComm:
         self.mode = mode or os.environ.get("SKEIN_COMM", "fused")
         self.wait_budget_ms = wait_budget_ms
         N = self.size
-        slot_bytes = fused_rows * hidden * 2
-        heap_bytes = 2 * N * slot_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
+        buf_bytes = fused_rows * hidden * 2
+        heap_bytes = 2 * buf_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
         self.heap = SymmetricHeap(group, device, heap_bytes)
         h = self.heap
-        self.buf_off = [h.alloc(N * slot_bytes) for _ in range(2)]
+        self.buf_off = [h.alloc(buf_bytes) for _ in range(2)]
         self.flag_off = [h.alloc(256) for _ in range(2)]
         self.cand_val_off = h.alloc(N * max_batch * 4)
         self.cand_idx_off = h.alloc(N * max_batch * 4)
         self.cand_flag_off = h.alloc(256)
-        self.slot_bytes = slot_bytes
-        self.bufs = [h.view(o, (N, fused_rows, hidden), torch.bfloat16) for o in self.buf_off]
-        self.flags = [h.view(o, (N,), torch.int32) for o in self.flag_off]
+        self.bufs = [h.view(o, (fused_rows, hidden), torch.bfloat16) for o in self.buf_off]   # this rank's partials
+        self.flags = [h.view(o, (N,), torch.int32) for o in self.flag_off]                     # [source rank]
         self.cand_val = h.view(self.cand_val_off, (N, max_batch), torch.float32)
         self.cand_idx = h.view(self.cand_idx_off, (N, max_batch), torch.int32)
         self.cand_flags = h.view(self.cand_flag_off, (N,), torch.int32)
@@ -60,14 +73,16 @@ class TPComm:
         self.done = torch.zeros(3, dtype=torch.int32, device=device)
         self.cur = 0
         r = self.rank
-        self._peer_out = [[h.peer_ptr(p, self.buf_off[b] + r * slot_bytes) for p in range(N)] for b in range(2)]
-        self._peer_flag = [[h.peer_ptr(p, self.flag_off[b] + 4 * r) for p in range(N)] for b in range(2)]
         VP = C.c_void_p * N
+        self._src_ptrs = [VP(*[h.peer_ptr(p, self.buf_off[b]) for p in range(N)]) for b in range(2)]
+        self._peer_flag = [[h.peer_ptr(p, self.flag_off[b] + 4 * r) for p in range(N)] for b in range(2)]
         self._cand_val_ptrs = VP(*[h.peer_ptr(p, self.cand_val_off + 4 * r * max_batch) for p in range(N)])
         self._cand_idx_ptrs = VP(*[h.peer_ptr(p, self.cand_idx_off + 4 * r * max_batch) for p in range(N)])
         self._cand_flag_ptrs = VP(*[h.peer_ptr(p, self.cand_flag_off + 4 * r) for p in range(N)])
-        self._push_dst = [VP(*self._peer_out[b]) for b in range(2)]
         self._push_flag = [VP(*self._peer_flag[b]) for b in range(2)]
+
+    def _partials(self, b: int, rows: int) -> PeerPartials:
+        return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1])
 
     @staticmethod
     def create(group, device, max_rows: int, hidden: int, **kw) -> "TPComm":
@@ -78,7 +93,8 @@ class TPComm:
         return self.mode == "fused" and rows <= self.fused_rows
 
     def linear_push(self, x, w, grouped=None):
-        """Returns (partial [n_src, rows, H], flags or None, epoch or None) for ops.reduce_residual_rmsnorm."""
+        """Returns (partial, flags, epoch) for ops.reduce_residual_rmsnorm: peer partials in fused mode, else the
+        all-reduced [1, rows, H] tensor and no flags."""
         rows = x.shape[0]
         if not self._fused_ok(rows):
             y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
@@ -86,12 +102,13 @@ class TPComm:
             return y.unsqueeze(0), None, None
         b = self.cur
         self.cur ^= 1
-        ops.linear_push(x, w, self._peer_out[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+        ops.linear_push(x, w, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
                         self.hidden, grouped=grouped, wait_budget_ms=0)
-        return self.bufs[b], self.flags[b], self.epochs[b:b + 1]
+        part = self._partials(b, rows)
+        return part, part.flags, part.epoch
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
-        """Stand-alone sum all-reduce of a [rows, H] bf16 tensor (one-shot push + local reduce)."""
+        """Stand-alone sum all-reduce of a [rows, H] bf16 tensor (publish + pull-and-sum)."""
         rows = x.shape[0]
         if not self._fused_ok(rows) or x.shape[1] != self.hidden:
             y = x.clone()
@@ -99,13 +116,14 @@ class TPComm:
             return y
         b = self.cur
         self.cur ^= 1
-        rc = _lib.lib().skein_push_rows(x.data_ptr(), x.numel() * 2, self._push_dst[b], self._push_flag[b], self.size,
-                                        self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
-                                        _lib.stream_ptr())
-        _lib.check(rc, "push_rows")
+        x = x.contiguous()
+        rc = _lib.lib().skein_publish_rows(x.data_ptr(), x.numel() * 2, self.bufs[b].data_ptr(), self._push_flag[b],
+                                           self.size, self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
+                                           _lib.stream_ptr())
+        _lib.check(rc, "publish_rows")
         _lib.count_launch()
-        out, _ = ops.reduce_residual_rmsnorm(None, self.bufs[b][:, :rows], None, 0.0, flags=self.flags[b],
-                                             epoch=self.epochs[b:b + 1], wait_budget_ms=self.wait_budget_ms)
+        out, _ = ops.reduce_residual_rmsnorm(None, self._partials(b, rows), None, 0.0,
+                                             wait_budget_ms=self.wait_budget_ms)
         return out
 
     # ---- vocabulary-parallel greedy sampling ----------------------------------------------------------
