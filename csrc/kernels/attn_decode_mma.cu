@@ -19,6 +19,7 @@
 // kernel/decode_attention.rs:66-139) and its FlashInfer batch-decode wrapper
 // (vendor/luminal/crates/luminal_cuda_lite/src/host/flashinfer/wrapper.cu:123-251).
 #include "ptx.cuh"
+#include "launch.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -88,6 +89,8 @@ __device__ __forceinline__ void am_wait() { asm volatile("cp.async.wait_group %0
 __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnMmaParams p) {
   extern __shared__ __align__(128) uint8_t am_smem[];
   __shared__ int is_last;
+  pdl_trigger();
+  pdl_wait();   // q, the cache and the sequence lengths come from earlier kernels of the step
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.G, ps = p.page_size;
@@ -410,8 +413,7 @@ static int attn_decode_mma_launch(const void* q, long long q_stride, void* kv, c
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
   p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
   dim3 grid(splits, Hkv, B);
-  attn_decode_mma_kernel<<<grid, AM_THREADS, AM_SMEM_BYTES, (cudaStream_t)stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(attn_decode_mma_kernel, grid, dim3(AM_THREADS), (size_t)AM_SMEM_BYTES, (cudaStream_t)stream, p);
 }
 
 extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const void* kv, const int* block_table,

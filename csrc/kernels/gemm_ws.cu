@@ -23,6 +23,7 @@
 #include "gemm_ws.cuh"
 #include "gemm_sched.cuh"
 #include "ptx.cuh"
+#include "launch.cuh"
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <mutex>
@@ -34,13 +35,25 @@ namespace skein {
 constexpr int TILE_F = 128;       // output features per tile (UMMA M)
 constexpr int BLOCK_KB = 128;     // bytes of K per stage row (64 bf16 or 128 e4m3)
 constexpr int W_TILE_BYTES = TILE_F * BLOCK_KB;  // 16 KB
-constexpr int ACC_STRIDE = 256;   // TMEM columns per accumulator buffer
+constexpr int ACC_STRIDE_MAX = 256;   // TMEM columns per accumulator buffer, at most
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_STAGES = 12;
 
+// Optional phase timer (compile with -DSKEIN_GEMM_TIMING): every CTA records %globaltimer at the points marked
+// TS(i) below into g_gemm_times[cta][i]; skein_gemm_times() copies the table out. Points: 0 entry, 1 set-up done,
+// 2 first stage landed (MMA warp), 3 first accumulator ready (epilogue), 4 partial parked and counted in,
+// 5 all contributors seen, 6 slice reduced and stored, 7 before TMEM release.
+#ifdef SKEIN_GEMM_TIMING
+__device__ unsigned long long g_gemm_times[160][8];
+#define TS(i) do { g_gemm_times[blockIdx.x][i] = global_timer_ns(); } while (0)
+#else
+#define TS(i) do { } while (0)
+#endif
+
 struct KernelArgs {
   SkeinGemmParams p;
+  int acc_stride;   // TMEM columns per accumulator buffer: power of two >= (dual ? 2 : 1) * n_tile, at least 32
   int stages;
   int stage_bytes;
   int x_tile_bytes;
@@ -68,9 +81,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   // ---- set-up ---------------------------------------------------------------------------------
+  // Nothing before pdl_wait() touches global memory: barriers, TMEM and the descriptor prefetch overlap the
+  // tail of the previous kernel in the stream (launch.cuh).
+  pdl_trigger();
   if (threadIdx.x == 0) {
+    TS(0);
     abort_flag = 0;
-    build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x, p.line_cut_only == 0);
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -82,13 +98,20 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_smem), 512);
+    tmem_alloc(smem_u32(&tmem_base_smem), 2 * a.acc_stride);
     tmem_relinquish();
   }
+  if (warp == 0 && elect_one()) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  pdl_wait();
+  if (threadIdx.x == 0) build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x, p.line_cut_only == 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  if (threadIdx.x == 0) TS(1);
 
   const int KB = sched.KB;
   const long long kb_begin = cta_begin(sched, blockIdx.x);
@@ -101,8 +124,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (warp == 0) {
       // ================= TMA producer =================
       if (elect_one()) {
-        tma_prefetch_desc(&tmW);
-        tma_prefetch_desc(&tmX);
         const uint64_t pol_w = l2_policy_evict_first();
         const uint64_t pol_x = l2_policy_evict_last();
         const uint32_t tx_bytes = (DUAL ? 2 : 1) * W_TILE_BYTES + a.x_tile_bytes;
@@ -163,7 +184,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             break;
           }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + b * ACC_STRIDE;
+          const uint32_t d_tmem = tmem_base + b * a.acc_stride;
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s = it % a.stages;
             const uint32_t ph = (it / a.stages) & 1;
@@ -174,6 +195,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               break;
             }
             tc_fence_after();
+            if (it == 0) TS(2);
             const uint32_t st = smem_base + s * a.stage_bytes;
             const uint64_t dw = umma_desc_sw128(st);
             const uint64_t dx = umma_desc_sw128(st + (DUAL ? 2 : 1) * W_TILE_BYTES);
@@ -239,7 +261,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           break;
         }
         tc_fence_after();
-        const uint32_t t_acc = tmem_base + b * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
+        if (et == 0 && seg == 0) TS(3);
+        const uint32_t t_acc = tmem_base + b * a.acc_stride + ((uint32_t)(q * 32) << 16);
         int valid = sched.cnt[un.g] - un.n * n_tile;
         if (valid > n_tile) valid = n_tile;
         const int f = un.m * TILE_F + r;
@@ -252,22 +275,35 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tile_ctas(sched, u, c_first, c_last_unused);
           const int my_slot = cta_slot(sched, blockIdx.x, u);
           float* ws = p.workspace + ((size_t)blockIdx.x * 2 + my_slot) * slot_elems;
-          for (int c0 = 0; c0 < acc_cols; c0 += 16) {
+          // two 16-column chunks per round: both TMEM loads are issued before the one wait
+          for (int c0 = 0; c0 < acc_cols; c0 += 32) {
             // skip column chunks that hold only padding tokens
-            const int cc = DUAL ? (c0 >= n_tile ? c0 - n_tile : c0) : c0;
-            if (cc >= valid) continue;
-            uint32_t v[16];
-            tmem_ld16(t_acc + c0, v);
+            const int cc0 = DUAL ? (c0 >= n_tile ? c0 - n_tile : c0) : c0;
+            const int c1 = c0 + 16;
+            const int cc1 = DUAL ? (c1 >= n_tile ? c1 - n_tile : c1) : c1;
+            const bool do0 = cc0 < valid, do1 = c1 < acc_cols && cc1 < valid;
+            uint32_t v0[16], v1[16];
+            if (do0) tmem_ld16(t_acc + c0, v0);
+            if (do1) tmem_ld16(t_acc + c1, v1);
             tmem_ld_wait();
+            if (do0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)   // column-major partials [col][feature]: a warp writes 128 contiguous bytes
-              ws[(size_t)(c0 + j) * TILE_F + r] = __uint_as_float(v[j]);
+              for (int j = 0; j < 16; ++j)   // column-major partials [col][feature]: a warp writes 128 contiguous bytes
+                ws[(size_t)(c0 + j) * TILE_F + r] = __uint_as_float(v0[j]);
+            }
+            if (do1) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                ws[(size_t)(c1 + j) * TILE_F + r] = __uint_as_float(v1[j]);
+            }
           }
           tc_fence_before();
           mbar_arrive(smem_u32(&bar_tempty[b]));
-          __threadfence();
+          // the barrier orders the 128 threads' partial stores before thread 0's device-scope release, which
+          // publishes them (cumulatively) to the CTA that later acquires the counter
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) atomicAdd(&p.counters[c_first], 1);
+          if (et == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(&p.counters[c_first]) : "memory");
+          if (et == 0) TS(4);
           if (n_pseg < 2) ps_u[n_pseg] = u;
           ++n_pseg;
         } else {
@@ -299,6 +335,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         int c_first, c_last;
         tile_ctas(sched, u, c_first, c_last);
         const int nc = c_last - c_first + 1;
+        const int first_slot = cta_slot(sched, c_first, u);   // (64-bit divisions: once per tile, not per load)
         int valid = sched.cnt[un.g] - un.n * n_tile;
         if (valid > n_tile) valid = n_tile;
         const long long row0 = (long long)sched.off[un.g] + (long long)un.n * n_tile;
@@ -316,6 +353,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             abort_flag = 1;
           }
           epi_last = arrived >= nc;
+          TS(5);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const bool go = epi_last != 0;
@@ -336,14 +374,17 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           float g8[8], u8[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) { g8[j] = 0.f; u8[j] = 0.f; }
-          for (int cb = c_first; cb <= c_last; cb += 4) {
-            float4 tg[4][2], tu[4][2];
+          // up to 8 contributors per batch: all of their loads are in flight together (one L2 round trip)
+          for (int cb = c_first; cb <= c_last; cb += 8) {
+            float4 tg[8][2], tu[8][2];
 #pragma unroll
-            for (int ci = 0; ci < 4; ++ci) {   // four contributors' loads in flight together
+            for (int ci = 0; ci < 8; ++ci) {
               const int c = cb + ci;
-              tg[ci][0] = tg[ci][1] = tu[ci][0] = tu[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+              tg[ci][0] = tg[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (DUAL) tu[ci][0] = tu[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
               if (c <= c_last) {
-                const int slot = cta_slot(sched, c, u);
+                // every contributor but possibly the first begins inside this tile and used its slot 0
+                const int slot = (c == c_first) ? first_slot : 0;
                 const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems + (size_t)col * TILE_F + rr;
                 tg[ci][0] = __ldcg(reinterpret_cast<const float4*>(ws));
                 tg[ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + 4));
@@ -354,7 +395,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               }
             }
 #pragma unroll
-            for (int ci = 0; ci < 4; ++ci) {   // fixed summation order
+            for (int ci = 0; ci < 8; ++ci) {   // fixed summation order
               g8[0] += tg[ci][0].x; g8[1] += tg[ci][0].y; g8[2] += tg[ci][0].z; g8[3] += tg[ci][0].w;
               g8[4] += tg[ci][1].x; g8[5] += tg[ci][1].y; g8[6] += tg[ci][1].z; g8[7] += tg[ci][1].w;
               if (DUAL) {
@@ -389,6 +430,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         // count this CTA out; the last one out re-arms the counter for the next launch
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) TS(6);
         if (et == 0) {
           const int old = atomicAdd(&p.counters[c_first], 0x10000);
           if ((old >> 16) == nc - 1) p.counters[c_first] = 0;
@@ -424,6 +466,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // ---- tear-down --------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TS(7);
   if (abort_flag) {
     // let TMA copies that are still in flight land before the shared memory is given back
     const uint64_t t0 = global_timer_ns();
@@ -431,7 +474,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 2 * a.acc_stride);
   }
 }
 
@@ -527,6 +570,13 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   if (p->mode == 2 && (p->n_peers < 1 || p->n_peers > SKEIN_MAX_PEERS)) return -5;
   if (p->fp8) return -6;  // block-scaled e4m3 goes through skein_gemm_ws_fp8
   ka->p = *p;
+  {
+    const int acc_cols = (dual ? 2 : 1) * p->n_tile;
+    int st = 32;
+    while (st < acc_cols) st <<= 1;
+    if (st > ACC_STRIDE_MAX) return -3;
+    ka->acc_stride = st;   // two buffers: 64..512 columns, a power of two as the allocator requires
+  }
   ka->x_tile_bytes = p->n_tile * BLOCK_KB;
   ka->stage_bytes = (dual ? 2 : 1) * W_TILE_BYTES + ka->x_tile_bytes;
   const int budget = 200 * 1024;
@@ -545,6 +595,13 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
 }  // namespace skein
 
 extern "C" int skein_sm_count(void) { return skein::sm_count_cached(); }
+
+#ifdef SKEIN_GEMM_TIMING
+// out: [160][8] nanosecond stamps of the last launch (synchronises the device).
+extern "C" int skein_gemm_times(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, skein::g_gemm_times, sizeof(unsigned long long) * 160 * 8);
+}
+#endif
 
 extern "C" int64_t skein_gemm_ws_workspace_bytes(const SkeinGemmParams* p) {
   const int grid = p->grid > 0 ? p->grid : skein::sm_count_cached();
@@ -581,7 +638,7 @@ extern "C" int skein_gemm_ws(const SkeinGemmParams* p, void* stream) {
     if (e != cudaSuccess) return (int)e;
     attr_done[dual] = true;
   }
-  if (dual) gemm_ws_kernel<true><<<grid, NUM_THREADS, smem, s>>>(tmW, tmX, ka);
-  else gemm_ws_kernel<false><<<grid, NUM_THREADS, smem, s>>>(tmW, tmX, ka);
-  return (int)cudaGetLastError();
+  const cudaError_t le = dual ? launch_pdl(gemm_ws_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem, s, tmW, tmX, ka)
+                             : launch_pdl(gemm_ws_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem, s, tmW, tmX, ka);
+  return (int)le;
 }

@@ -1,0 +1,50 @@
+// Kernel launch with programmatic dependent launch (PDL).
+//
+// A decode step is ~260 short kernels in one stream. Launched the plain way, kernel N+1 is only handed to
+// the GPU when kernel N has drained; with the programmatic-stream-serialization attribute its CTAs are
+// scheduled as soon as every CTA of kernel N has executed pdl_trigger() (ptx.cuh), they run their
+// prologue (barrier set-up, TMEM allocation, descriptor prefetch) and then block in pdl_wait() until
+// kernel N has completed and its memory is visible. Every kernel launched through launch_pdl() therefore
+// calls pdl_wait() before its first access to memory that an earlier kernel may have written, and before
+// its first write to memory that an earlier kernel may still read. The attribute is recorded by stream
+// capture, so the overlap is kept inside CUDA graphs.
+//
+// Off unless SKEIN_PDL=1: on the decode step of the flagship model it measured 1-2 % slower than plain
+// serialization (132.6 -> 135.1 us per layer at the 8-way tensor-parallel shard shapes). The weight-streaming
+// GEMM needs ~200 KB of shared memory, so its CTAs cannot become resident before the previous kernel's CTAs
+// have left the SM, and the other kernels have no prologue worth overlapping.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdlib.h>
+#include <string.h>
+#include <utility>
+
+namespace skein {
+
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SKEIN_PDL");
+    on = (e != nullptr && strcmp(e, "1") == 0) ? 1 : 0;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+}  // namespace skein

@@ -18,6 +18,7 @@
 // elementwise residual adds and the NCCL all-reduce + copy-back
 // (crates/skein_runtime/src/cuda/nccl.rs:196-245).
 #include "ptx.cuh"
+#include "launch.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -187,6 +188,8 @@ __global__ void __launch_bounds__(512) reduce_residual_rmsnorm_kernel(const Norm
   __shared__ float sh[32];
   __shared__ int wait_failed;
   uint4 nb[MAX_PASSES];
+  pdl_trigger();
+  pdl_wait();
   reduce_norm_row<MAX_PASSES>(p, blockIdx.x, sh, wait_failed, nb);
 }
 
@@ -234,6 +237,8 @@ __global__ void __launch_bounds__(512) reduce_norm_route_kernel(const NormParams
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   const int T = gridDim.x, E = r.E, topk = r.topk;
   uint4 nb[MAX_PASSES];
+  pdl_trigger();
+  pdl_wait();
   const bool have_row = reduce_norm_row<MAX_PASSES>(p, t, sh, wait_failed, nb);
   // a row that failed still takes part in the barrier below, so that the other CTAs do not wait for it
   const int per_pass = blockDim.x * 8;
@@ -384,10 +389,9 @@ extern "C" int skein_reduce_residual_rmsnorm(
   if (threads > 512) threads = 512;
   const int passes = (H + threads * 8 - 1) / (threads * 8);
   cudaStream_t s = (cudaStream_t)stream;
-  if (passes <= 1) reduce_residual_rmsnorm_kernel<1><<<B, threads, 0, s>>>(p);
-  else if (passes <= 2) reduce_residual_rmsnorm_kernel<2><<<B, threads, 0, s>>>(p);
-  else reduce_residual_rmsnorm_kernel<4><<<B, threads, 0, s>>>(p);
-  return (int)cudaGetLastError();
+  if (passes <= 1) return (int)launch_pdl(reduce_residual_rmsnorm_kernel<1>, dim3(B), dim3(threads), 0, s, p);
+  if (passes <= 2) return (int)launch_pdl(reduce_residual_rmsnorm_kernel<2>, dim3(B), dim3(threads), 0, s, p);
+  return (int)launch_pdl(reduce_residual_rmsnorm_kernel<4>, dim3(B), dim3(threads), 0, s, p);
 }
 
 // Fused variant for decode-sized batches (see reduce_norm_route_kernel). `barrier` is two zeroed device
@@ -425,8 +429,7 @@ extern "C" int skein_reduce_norm_route(
   if (threads > 512) threads = 512;
   const int passes = (H + threads * 8 - 1) / (threads * 8);
   cudaStream_t s = (cudaStream_t)stream;
-  if (passes <= 1) reduce_norm_route_kernel<1><<<B, threads, 0, s>>>(p, r);
-  else if (passes <= 2) reduce_norm_route_kernel<2><<<B, threads, 0, s>>>(p, r);
-  else reduce_norm_route_kernel<4><<<B, threads, 0, s>>>(p, r);
-  return (int)cudaGetLastError();
+  if (passes <= 1) return (int)launch_pdl(reduce_norm_route_kernel<1>, dim3(B), dim3(threads), 0, s, p, r);
+  if (passes <= 2) return (int)launch_pdl(reduce_norm_route_kernel<2>, dim3(B), dim3(threads), 0, s, p, r);
+  return (int)launch_pdl(reduce_norm_route_kernel<4>, dim3(B), dim3(threads), 0, s, p, r);
 }

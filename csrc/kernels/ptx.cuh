@@ -36,6 +36,12 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// Programmatic dependent launch (see launch.cuh). pdl_trigger: this CTA no longer holds back the launch of
+// the next kernel in the stream. pdl_wait: block until every earlier kernel in the stream has completed and
+// its memory is visible. Both are no-ops in a kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(

@@ -350,13 +350,13 @@ def rope_kv_append(qkv, positions, seq_of_token, block_table, cos_sin, kv_cache,
 
 
 def pick_splits(B, Hkv, ctx_hint, sm_count=148):
-    # split only while there are fewer than two CTAs per SM; at least 128 tokens per split
-    ctas = max(B * Hkv, 1)
+    """Split-KV factor of decode attention: only while there are fewer (sequence, kv head) pairs than SMs, never
+    below 512 tokens per split, never more CTAs than SMs. Each split adds a workspace round trip and a last-arriver
+    merge, which at 64 sequences costs more than the extra parallelism brings."""
     if os.environ.get("SKEIN_ATTN_SPLITS"):
         return int(os.environ["SKEIN_ATTN_SPLITS"])
-    s = max(1, (2 * sm_count + ctas - 1) // ctas) if ctas < 2 * sm_count else 1
-    s = min(s, max(1, ctx_hint // 128), 16)
-    return s
+    ctas = max(B * Hkv, 1)
+    return max(1, min(sm_count // ctas, ctx_hint // 512, 16))
 
 
 def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=None, splits=None, ctx_hint=1024,
