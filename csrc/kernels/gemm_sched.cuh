@@ -10,6 +10,7 @@
 // Group sizes are read from device memory, so every CTA rebuilds the same table at start-up.
 #pragma once
 #include "gemm_ws.cuh"
+#include "ptx.cuh"
 #include <cuda.h>
 
 namespace skein {
@@ -39,29 +40,33 @@ __device__ __forceinline__ Unit decode_unit(const Sched& s, int G, int u) {
 
 // K-block range of CTA c on the line, the CTAs that share tile u, and which of its two workspace slots CTA c
 // uses for tile u (slot 0: the tile its range begins in).
-__device__ __forceinline__ long long cta_begin(const Sched& s, int c) {
+// (32-bit arithmetic: these run on every segment of every role, and 64-bit divisions cost microseconds there;
+//  build_sched refuses a line of 2^31 K-blocks or more.)
+__device__ __forceinline__ int cta_begin(const Sched& s, int c) {
+  const int tk = (int)s.TK;
   if (s.split > 0) {
     const int u = c / s.split, pc = c - u * s.split;
-    if (u >= s.U) return s.TK;
-    return (long long)u * s.KB + (long long)pc * s.KB / s.split;
+    if (u >= s.U) return tk;
+    return u * s.KB + pc * s.KB / s.split;
   }
   const long long b = (long long)c * s.per;
-  return b < s.TK ? b : s.TK;
+  return b < tk ? (int)b : tk;
 }
-__device__ __forceinline__ long long cta_end(const Sched& s, int c) {
+__device__ __forceinline__ int cta_end(const Sched& s, int c) {
+  const int tk = (int)s.TK;
   if (s.split > 0) {
     const int u = c / s.split, pc = c - u * s.split;
-    if (u >= s.U) return s.TK;
-    return (long long)u * s.KB + (long long)(pc + 1) * s.KB / s.split;
+    if (u >= s.U) return tk;
+    return u * s.KB + (pc + 1) * s.KB / s.split;
   }
   const long long e = (long long)(c + 1) * s.per;
-  return e < s.TK ? e : s.TK;
+  return e < tk ? (int)e : tk;
 }
 __device__ __forceinline__ void tile_ctas(const Sched& s, int u, int& c_first, int& c_last) {
   if (s.split > 0) { c_first = u * s.split; c_last = c_first + s.split - 1; return; }
-  const long long ub = (long long)u * s.KB;
-  c_first = (int)(ub / s.per);
-  c_last = (int)((ub + s.KB - 1) / s.per);
+  const int ub = u * s.KB;
+  c_first = ub / s.per;
+  c_last = (ub + s.KB - 1) / s.per;
 }
 __device__ __forceinline__ int cta_slot(const Sched& s, int c, int u) { return cta_begin(s, c) / s.KB == u ? 0 : 1; }
 
@@ -86,6 +91,11 @@ __device__ __forceinline__ void build_sched(Sched& sched, const SkeinGemmParams&
   sched.KB = p.K / k_elems_per_block;
   sched.U = acc;
   sched.TK = (long long)acc * sched.KB;
+  if (sched.TK >= (1ll << 31)) {   // no work is handed out; the host sees the status
+    report_status(p.status, ST_BAD_INDEX, acc);
+    sched.U = 0;
+    sched.TK = 0;
+  }
   // equal share per CTA, but never so small that a tile is cut into more than 8 pieces
   long long per = (sched.TK + grid - 1) / grid;
   const long long min_per = sched.KB >= 32 ? sched.KB / 8 : 4;

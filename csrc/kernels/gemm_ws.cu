@@ -114,8 +114,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (threadIdx.x == 0) TS(1);
 
   const int KB = sched.KB;
-  const long long kb_begin = cta_begin(sched, blockIdx.x);
-  const long long kb_end = cta_end(sched, blockIdx.x);
+  const int kb_begin = cta_begin(sched, blockIdx.x);
+  const int kb_end = cta_end(sched, blockIdx.x);
   const bool has_work = kb_begin < kb_end;
   const int n_tile = p.n_tile;
   const int k_elems = p.fp8 ? 128 : 64;
@@ -128,13 +128,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const uint64_t pol_x = l2_policy_evict_last();
         const uint32_t tx_bytes = (DUAL ? 2 : 1) * W_TILE_BYTES + a.x_tile_bytes;
         uint32_t it = 0;
-        long long pos = kb_begin;
+        int pos = kb_begin;
         bool ok = true;
         while (pos < kb_end && ok) {
-          const int u = (int)(pos / KB);
-          const int kb0 = (int)(pos - (long long)u * KB);
+          const int u = pos / KB;
+          const int kb0 = pos - u * KB;
           int kb1 = KB;
-          if ((long long)u * KB + KB > kb_end) kb1 = (int)(kb_end - (long long)u * KB);
+          if (u * KB + KB > kb_end) kb1 = kb_end - u * KB;
           const Unit un = decode_unit(sched, p.G, u);
           const int w_row = un.g * p.w_rows_per_group + un.m * TILE_F;
           const int x_row = sched.off[un.g] + un.n * n_tile;
@@ -160,7 +160,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
             tma_load_2d(st + (DUAL ? 2 : 1) * W_TILE_BYTES, &tmX, full, kb * k_elems, x_row, pol_x);
           }
-          pos = (long long)u * KB + kb1;
+          pos = u * KB + kb1;
         }
       }
     } else if (warp == 1) {
@@ -169,13 +169,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const uint32_t idesc = p.fp8 ? umma_idesc(0, 0, TILE_F, n_tile) : umma_idesc(1, 1, TILE_F, n_tile);
         uint32_t it = 0;
         uint32_t seg = 0;
-        long long pos = kb_begin;
+        int pos = kb_begin;
         bool ok = true;
         while (pos < kb_end && ok) {
-          const int u = (int)(pos / KB);
-          const int kb0 = (int)(pos - (long long)u * KB);
+          const int u = pos / KB;
+          const int kb0 = pos - u * KB;
           int kb1 = KB;
-          if ((long long)u * KB + KB > kb_end) kb1 = (int)(kb_end - (long long)u * KB);
+          if (u * KB + KB > kb_end) kb1 = kb_end - u * KB;
           const uint32_t b = seg & 1;
           const uint32_t bph = (seg >> 1) & 1;
           if (!mbar_wait(smem_u32(&bar_tempty[b]), bph ^ 1, &abort_flag, a.budget_ns)) {
@@ -215,7 +215,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (!ok) break;
           tc_commit(smem_u32(&bar_tfull[b]));
           ++seg;
-          pos = (long long)u * KB + kb1;
+          pos = u * KB + kb1;
         }
       }
     } else {
@@ -243,13 +243,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int ps_u[2] = {0, 0};
       int n_pseg = 0;
       uint32_t seg = 0;
-      long long pos = kb_begin;
+      int pos = kb_begin;
       bool ok = true;
       while (pos < kb_end && ok) {
-        const int u = (int)(pos / KB);
-        const int kb0 = (int)(pos - (long long)u * KB);
+        const int u = pos / KB;
+        const int kb0 = pos - u * KB;
         int kb1 = KB;
-        if ((long long)u * KB + KB > kb_end) kb1 = (int)(kb_end - (long long)u * KB);
+        if (u * KB + KB > kb_end) kb1 = kb_end - u * KB;
         const bool full_seg = (kb0 == 0 && kb1 == KB);
         const Unit un = decode_unit(sched, p.G, u);
         const uint32_t b = seg & 1;
@@ -325,7 +325,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           mbar_arrive(smem_u32(&bar_tempty[b]));
         }
         ++seg;
-        pos = (long long)u * KB + kb1;
+        pos = u * KB + kb1;
       }
 
       // ---- phase 2: reduce this CTA's slice of every tile it shares ----
