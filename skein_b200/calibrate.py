@@ -269,3 +269,43 @@ def calibrate_drift(report_layers, plan: dict) -> dict:
             if d[comp] != "bf16":
                 out[(l["layer"], comp, d[comp])] = l["mse"]
     return out
+
+
+def autotune_decode_gemms(cfg, tp: int, batch: int, out_path, seed: int = 0):
+    """Measure launch configurations for the GEMM shapes of one decode step of `cfg` at tensor-parallel degree
+    `tp` and `batch` sequences, and write them to `out_path` (the artifact's cache/kernel_configs.json).
+
+    Random weights of the shard shapes and an even routing are used: the winner depends on shapes, not values.
+    Returns {shape name: best config}. The reference memoises its kernel search the same way
+    (crates/skein_compile/src/search_cache.rs:71-150)."""
+    import torch
+
+    from . import ops
+    from .ops import tuning
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    bf = lambda *s, std=0.02: (torch.randn(*s, device=dev, generator=g) * std).bfloat16()
+    H, D = cfg.hidden_size, cfg.head_dim
+    hq, hkv = cfg.num_heads // tp, max(1, cfg.num_kv_heads // tp)
+    inter = cfg.intermediate_size // tp
+    cache = tuning.KernelConfigCache(out_path)
+    x = bf(batch, H, std=1.0)
+    found = {}
+    found["qkv"] = ops.tune_linear(x, bf((hq + 2 * hkv) * D, H), cache=cache)[0]
+    found["o_proj"] = ops.tune_linear(bf(batch, hq * D, std=1.0), bf(H, hq * D), cache=cache)[0]
+    found["lm_head"] = ops.tune_linear(x, bf(cfg.vocab_size // tp, H), cache=cache)[0]
+    if cfg.is_moe:
+        E, k = cfg.num_experts, cfg.top_k
+        per = max(1, batch * k // E)
+        cnt = torch.full((E,), per, dtype=torch.int32, device=dev)
+        off = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+        off[1:] = torch.cumsum(cnt, 0)
+        found["moe_gate_up"] = ops.tune_grouped(bf(E * per, H, std=1.0), bf(E, 2 * inter, H), cnt, off, True, cache)[0]
+        found["moe_down"] = ops.tune_grouped(bf(E * per, inter, std=1.0), bf(E, H, inter), cnt, off, False, cache)[0]
+    else:
+        found["gate_up"] = ops.tune_linear(x, bf(2 * inter, H), swiglu=True, cache=cache)[0]
+        found["down"] = ops.tune_linear(bf(batch, inter, std=1.0), bf(H, inter), cache=cache)[0]
+    ops.workspace().check_status()
+    cache.save()
+    return found

@@ -150,8 +150,18 @@ def cmd_calibrate(args, emit) -> int:
         name = Path(args.model).stem.replace("_config", "")
         dpath = Path(args.out_drift_dir) / f"{name}_drift.toml"
         dpath.write_text(cal.write_drift_table(_read(dpath), drift))
-    emit(args, {"efficiencies": {f"{k[0]}.{k[1]}": v for k, v in eff.items()}, "drift_entries": len(drift)},
-         f"calibrated {len(eff)} kernel efficiencies, {len(drift)} drift entries")
+    tuned = {}
+    if getattr(args, "autotune", False) and torch.cuda.is_available():
+        from ..compile.artifact import Artifact
+        from ..models.config import ModelConfig
+        art = Artifact(args.candidate_artifact) if args.candidate_artifact else None
+        cfg = art.cfg if art is not None else ModelConfig.from_file(args.model)
+        tp = int(art.plan["parallelism"]["tp"]) if art is not None else 1
+        out = args.autotune_out or (art.path / "cache" / "kernel_configs.json" if art is not None else "kernel_configs.json")
+        tuned = cal.autotune_decode_gemms(cfg, tp, args.autotune_batch, out)
+    emit(args, {"efficiencies": {f"{k[0]}.{k[1]}": v for k, v in eff.items()}, "drift_entries": len(drift),
+                "tuned_gemms": tuned},
+         f"calibrated {len(eff)} kernel efficiencies, {len(drift)} drift entries, {len(tuned)} tuned GEMM shapes")
     return 0
 
 

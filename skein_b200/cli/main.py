@@ -91,6 +91,11 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--candidate-artifact", default=None)
     k.add_argument("--out-cost", default="cluster/cost_constants.toml")
     k.add_argument("--out-drift-dir", default="models/")
+    k.add_argument("--autotune", action="store_true",
+                   help="also measure GEMM launch configurations for the decode step and store them in the candidate "
+                        "artifact's cache/kernel_configs.json (or --autotune-out)")
+    k.add_argument("--autotune-out", default=None)
+    k.add_argument("--autotune-batch", type=int, default=64)
 
     b = sub.add_parser("bench", help="replay a workload trace against an artifact and report throughput / goodput / drift compliance")
     b.add_argument("--artifact", required=True)

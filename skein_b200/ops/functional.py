@@ -18,7 +18,7 @@ import os
 
 import torch
 
-from . import _lib, reference as ref
+from . import _lib, reference as ref, tuning
 
 _WORKSPACES: dict = {}
 
@@ -88,13 +88,21 @@ def pick_n_tile(rows_hint: int, dual: bool) -> int:
     return max(16, min(cap, _round_up(max(rows_hint, 1), 16)))
 
 
-def _gemm_launch(p: "_lib.GemmParams", what: str):
+def _gemm_launch(p: "_lib.GemmParams", what: str, cfg: dict | None = None):
+    """Launch with (in this order) an explicit configuration, the measured one from the kernel-configuration cache
+    (tuning.py), or the heuristics below."""
     ws = workspace()
     p.workspace = ws.gemm_ws.data_ptr()
     p.counters = ws.gemm_counters.data_ptr()
     p.status = ws.status.data_ptr()
     p.line_cut_only = 1 if os.environ.get("SKEIN_GEMM_ALIGNED", "1") == "0" else 0
-    if p.grid == 0 and os.environ.get("SKEIN_GEMM_AUTOGRID", "1") == "1":
+    if cfg is None:
+        cache = tuning.active()
+        if cache is not None:
+            cfg = cache.get("gemm", tuning.gemm_shape_key(p.mode, p.G, p.F, p.K, p.x_rows))
+    if cfg is not None:
+        p.n_tile, p.grid, p.line_cut_only = int(cfg["n_tile"]), int(cfg["grid"]), int(cfg["line_cut_only"])
+    elif p.grid == 0 and os.environ.get("SKEIN_GEMM_AUTOGRID", "1") == "1":
         # With between one and two tiles per SM, give every CTA a whole number of tiles: no tile is split, so
         # the stream-K partial store / reduce disappears; measured 3-12 % faster than equal K-shares on all
         # CTAs. (With fewer tiles than SMs the kernel itself cuts each tile into aligned pieces; with many
@@ -171,7 +179,7 @@ def _check_act(x):
         raise ValueError("activations must be contiguous bf16")
 
 
-def linear(x, w, out=None, residual=None, n_tile=None):
+def linear(x, w, out=None, residual=None, n_tile=None, _cfg=None):
     """y[t, f] = sum_k x[t, k] w[f, k] (+ residual[t, f])."""
     if not x.is_cuda:
         y = ref.linear(x, w.unpack() if isinstance(w, PackedWeight) else w, residual)
@@ -191,11 +199,11 @@ def linear(x, w, out=None, residual=None, n_tile=None):
     p.w_rows_per_group, p.w_packed = F, packed
     if residual is not None:
         p.residual = residual.data_ptr()
-    _gemm_launch(p, "linear")
+    _gemm_launch(p, "linear", _cfg)
     return out
 
 
-def swiglu_linear(x, w13, out=None, n_tile=None):
+def swiglu_linear(x, w13, out=None, n_tile=None, _cfg=None):
     """silu(x @ w13[:I].T) * (x @ w13[I:].T) with both products from one pass over x."""
     if not x.is_cuda:
         return ref.swiglu_linear(x, w13.unpack() if isinstance(w13, PackedWeight) else w13)
@@ -210,11 +218,11 @@ def swiglu_linear(x, w13, out=None, n_tile=None):
     p = _base_params(x, wv, out, inter, K, n_tile or pick_n_tile(T, True), 1)
     p.w_rows_per_group, p.w_packed = rows_pg, packed
     p.up_row_off = inter
-    _gemm_launch(p, "swiglu_linear")
+    _gemm_launch(p, "swiglu_linear", _cfg)
     return out
 
 
-def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, rows_hint=None, grid=0):
+def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, rows_hint=None, grid=0, _cfg=None):
     """Per-expert linear over an expert-sorted activation matrix.
 
     xs [rows, K]; w [E, F, K] (or [E, 2I, K] with gate rows first when swiglu); counts / offsets are
@@ -242,7 +250,7 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
     p.group_off = offsets.data_ptr()
     p.group_cnt = counts.data_ptr()
     p.grid = grid
-    _gemm_launch(p, "grouped_linear")
+    _gemm_launch(p, "grouped_linear", _cfg)
     return out
 
 
@@ -628,3 +636,19 @@ def linear_push(x, w, out_local, peer_flag, epoch, done_counter, ldo, grouped=No
     p.done_counter = done_counter.data_ptr()
     p.wait_budget_ms = wait_budget_ms
     _gemm_launch(p, "linear_push")
+
+
+def tune_linear(x, w, swiglu=False, cache=None):
+    """Measure the launch configurations of this dense GEMM shape and record the fastest (tuning.py)."""
+    F = w.shape[0] // 2 if swiglu else w.shape[0]
+    out = torch.empty(x.shape[0], F, dtype=torch.bfloat16, device=x.device)
+    run = (lambda c: swiglu_linear(x, w, out=out, _cfg=c)) if swiglu else (lambda c: linear(x, w, out=out, _cfg=c))
+    return tuning.tune_gemm(run, 1 if swiglu else 0, 1, F, x.shape[1], x.shape[0], cache)
+
+
+def tune_grouped(xs, w, counts, offsets, swiglu=False, cache=None):
+    """Same for a grouped (per-expert) GEMM with the given routing."""
+    F = w.shape[1] // 2 if swiglu else w.shape[1]
+    out = torch.empty(xs.shape[0], F, dtype=torch.bfloat16, device=xs.device)
+    run = lambda c: grouped_linear(xs, w, counts, offsets, swiglu=swiglu, out=out, _cfg=c)
+    return tuning.tune_gemm(run, 1 if swiglu else 0, w.shape[0], F, xs.shape[1], xs.shape[0], cache)
