@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 #include <stdio.h>
 
@@ -368,42 +369,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int n_grp = r_hi > r_lo ? (r_hi - r_lo) / 8 : 0;
         const int n_items = n_grp * valid;
         const bool wide_ok = (p.ldo % 8 == 0) && (p.out_col0 % 8 == 0);
-        for (int i = et; i < n_items; i += EPI_THREADS) {
-          const int rr = r_lo + (i % n_grp) * 8;     // consecutive threads -> consecutive feature groups
-          const int col = i / n_grp;                 // token column (< valid)
-          float g8[8], u8[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { g8[j] = 0.f; u8[j] = 0.f; }
-          // up to 8 contributors per batch: all of their loads are in flight together (one L2 round trip)
-          for (int cb = c_first; cb <= c_last; cb += 8) {
-            float4 tg[8][2], tu[8][2];
-#pragma unroll
-            for (int ci = 0; ci < 8; ++ci) {
-              const int c = cb + ci;
-              tg[ci][0] = tg[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (DUAL) tu[ci][0] = tu[ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (c <= c_last) {
-                // every contributor but possibly the first begins inside this tile and used its slot 0
-                const int slot = (c == c_first) ? first_slot : 0;
-                const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems + (size_t)col * TILE_F + rr;
-                tg[ci][0] = __ldcg(reinterpret_cast<const float4*>(ws));
-                tg[ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + 4));
-                if (DUAL) {
-                  tu[ci][0] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F));
-                  tu[ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F + 4));
-                }
-              }
-            }
-#pragma unroll
-            for (int ci = 0; ci < 8; ++ci) {   // fixed summation order
-              g8[0] += tg[ci][0].x; g8[1] += tg[ci][0].y; g8[2] += tg[ci][0].z; g8[3] += tg[ci][0].w;
-              g8[4] += tg[ci][1].x; g8[5] += tg[ci][1].y; g8[6] += tg[ci][1].z; g8[7] += tg[ci][1].w;
-              if (DUAL) {
-                u8[0] += tu[ci][0].x; u8[1] += tu[ci][0].y; u8[2] += tu[ci][0].z; u8[3] += tu[ci][0].w;
-                u8[4] += tu[ci][1].x; u8[5] += tu[ci][1].y; u8[6] += tu[ci][1].z; u8[7] += tu[ci][1].w;
-              }
-            }
-          }
+        // one item = 8 consecutive features of one token column
+        auto store_item = [&](int rr, int col, const float* g8, const float* u8) {
           const int f0 = un.m * TILE_F + rr;
           const long long row = row0 + col;
           if (wide_ok && f0 + 8 <= p.F) {
@@ -427,7 +394,69 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int j = 0; j < 8; ++j)
               if (f0 + j < p.F) emit(g8[j], u8[j], row, f0 + j);
           }
-        }
+        };
+        // IPB items of a thread are reduced together, CB = 8 / IPB contributors per batch: 16 (32 with the up half)
+        // 16-byte loads are in flight per thread whatever the number of contributors, and a tile cut in two
+        // costs one L2 round trip per 4 items instead of one per item. Contributors are added in rank order.
+        auto reduce_items = [&](auto ipb_c) {
+          constexpr int IPB = decltype(ipb_c)::value;
+          constexpr int CB = 8 / IPB;
+          for (int i0 = et; i0 < n_items; i0 += EPI_THREADS * IPB) {
+            int rr[IPB], col[IPB];
+            bool live[IPB];
+            float g8[IPB][8], u8[IPB][8];
+#pragma unroll
+            for (int k = 0; k < IPB; ++k) {
+              const int i = i0 + k * EPI_THREADS;
+              live[k] = i < n_items;
+              rr[k] = r_lo + (i % n_grp) * 8;     // consecutive threads -> consecutive feature groups
+              col[k] = i / n_grp;                 // token column (< valid)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { g8[k][j] = 0.f; u8[k][j] = 0.f; }
+            }
+            for (int cb = c_first; cb <= c_last; cb += CB) {
+              float4 tg[IPB][CB][2], tu[IPB][CB][2];
+#pragma unroll
+              for (int k = 0; k < IPB; ++k) {
+#pragma unroll
+                for (int ci = 0; ci < CB; ++ci) {
+                  const int c = cb + ci;
+                  tg[k][ci][0] = tg[k][ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  if (DUAL) tu[k][ci][0] = tu[k][ci][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  if (live[k] && c <= c_last) {
+                    // every contributor but possibly the first begins inside this tile and used its slot 0
+                    const int slot = (c == c_first) ? first_slot : 0;
+                    const float* ws = p.workspace + ((size_t)c * 2 + slot) * slot_elems + (size_t)col[k] * TILE_F + rr[k];
+                    tg[k][ci][0] = __ldcg(reinterpret_cast<const float4*>(ws));
+                    tg[k][ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + 4));
+                    if (DUAL) {
+                      tu[k][ci][0] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F));
+                      tu[k][ci][1] = __ldcg(reinterpret_cast<const float4*>(ws + (size_t)n_tile * TILE_F + 4));
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int k = 0; k < IPB; ++k) {
+#pragma unroll
+                for (int ci = 0; ci < CB; ++ci) {   // fixed summation order
+                  g8[k][0] += tg[k][ci][0].x; g8[k][1] += tg[k][ci][0].y; g8[k][2] += tg[k][ci][0].z; g8[k][3] += tg[k][ci][0].w;
+                  g8[k][4] += tg[k][ci][1].x; g8[k][5] += tg[k][ci][1].y; g8[k][6] += tg[k][ci][1].z; g8[k][7] += tg[k][ci][1].w;
+                  if (DUAL) {
+                    u8[k][0] += tu[k][ci][0].x; u8[k][1] += tu[k][ci][0].y; u8[k][2] += tu[k][ci][0].z; u8[k][3] += tu[k][ci][0].w;
+                    u8[k][4] += tu[k][ci][1].x; u8[k][5] += tu[k][ci][1].y; u8[k][6] += tu[k][ci][1].z; u8[k][7] += tu[k][ci][1].w;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < IPB; ++k)
+              if (live[k]) store_item(rr[k], col[k], g8[k], u8[k]);
+          }
+        };
+        if (!DUAL && nc <= 2) reduce_items(std::integral_constant<int, 4>{});
+        else if (!DUAL && nc <= 4) reduce_items(std::integral_constant<int, 2>{});
+        else reduce_items(std::integral_constant<int, 1>{});
         // count this CTA out; the last one out re-arms the counter for the next launch
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (et == 0) TS(6);

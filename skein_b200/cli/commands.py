@@ -165,9 +165,72 @@ def cmd_calibrate(args, emit) -> int:
     return 0
 
 
+def bench_collectives(emit, args) -> int:
+    """Time the stand-alone all-reduce (publish + peer pull) against the library all-reduce for decode-sized messages.
+
+    Run under `python -m torch.distributed.run --nproc-per-node N ... skein bench --collectives ...`: one process per
+    GPU. CUDA events on the launching stream, 20 launches per sample, max over ranks. Counterpart of the reference's
+    SKEIN_ALLREDUCE_BENCH (crates/skein_runtime/src/cuda/nccl.rs: bench_all_reduce)."""
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from .. import ops
+    from ..parallel.tp import TPComm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2 or not torch.cuda.is_available():
+        raise ValueError("--collectives needs one process per GPU: launch with torch.distributed.run, 2 or more ranks")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    hidden = 4096
+    comm = TPComm(dist.group.WORLD, dev, hidden=hidden, fused_rows=512, mode="fused")
+    rows_out = []
+    for rows in (16, 64, 128, 256, 512):
+        x = torch.randn(rows, hidden, device=dev).bfloat16()
+
+        def timed(fn, n=20):
+            for _ in range(3):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(n):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([s.elapsed_time(e) * 1e3 / n], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t[0])
+
+        y = x.clone()
+        fused_us = timed(lambda: comm.all_reduce(x))
+        nccl_us = timed(lambda: dist.all_reduce(y))
+        rows_out.append({"rows": rows, "bytes": rows * hidden * 2, "fused_us": round(fused_us, 2), "nccl_us": round(nccl_us, 2)})
+    torch.cuda.synchronize()
+    ops.workspace().check_status()
+    if dist.get_rank() == 0:
+        emit(args, {"world": world, "hidden": hidden, "all_reduce": rows_out},
+             "\n".join(f"{r['rows']:4d} rows ({r['bytes']} B): fused {r['fused_us']} us, nccl {r['nccl_us']} us" for r in rows_out))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
 def cmd_bench(args, emit) -> int:
     """Replay a trace (arrival times honoured, scaled by --time-scale) against a single-process engine."""
     import torch
+
+    if getattr(args, "collectives", False):
+        return bench_collectives(emit, args)
+    if not args.artifact or not args.workload:
+        raise ValueError("`skein bench` needs --artifact and --workload (or --collectives under torch.distributed.run)")
 
     from ..compile.artifact import Artifact
     from ..parallel import worker

@@ -98,8 +98,8 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--autotune-batch", type=int, default=64)
 
     b = sub.add_parser("bench", help="replay a workload trace against an artifact and report throughput / goodput / drift compliance")
-    b.add_argument("--artifact", required=True)
-    b.add_argument("--workload", required=True)
+    b.add_argument("--artifact", default=None)
+    b.add_argument("--workload", default=None)
     b.add_argument("--baseline", default=None, help="URL or label of the system the numbers are compared with")
     b.add_argument("--metrics", default="throughput,goodput,drift_compliance")
     b.add_argument("--max-requests", type=int, default=0)
