@@ -58,13 +58,21 @@ def make_key(op: str, shape, dtype: str = "bf16", arch: str | None = None, build
 
 
 class KernelConfigCache:
-    def __init__(self, path: str | os.PathLike | None = None):
+    def __init__(self, path: str | os.PathLike | None = None, strict: bool = True):
+        """strict=False: an unreadable or corrupt file counts as an empty cache (`load_error` says why) instead of
+        raising, so that a damaged cache can never keep a server from starting."""
         self.path = Path(path) if path else None
         self.entries: dict[str, dict] = {}
         self.hits = 0
         self.misses = 0
+        self.load_error: str | None = None
         if self.path is not None and self.path.exists():
-            self.load()
+            try:
+                self.load()
+            except (OSError, ValueError) as e:   # json.JSONDecodeError is a ValueError
+                if strict:
+                    raise
+                self.entries, self.load_error = {}, f"{type(e).__name__}: {e}"
 
     def load(self) -> None:
         with open(self.path) as f:
@@ -109,7 +117,7 @@ def active() -> KernelConfigCache | None:
     global _ACTIVE
     with _LOCK:
         if _ACTIVE is None and os.environ.get("SKEIN_TUNE_CACHE"):
-            _ACTIVE = KernelConfigCache(os.environ["SKEIN_TUNE_CACHE"])
+            _ACTIVE = KernelConfigCache(os.environ["SKEIN_TUNE_CACHE"], strict=False)
         return _ACTIVE
 
 

@@ -48,7 +48,7 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
     tuned = art.path / "cache" / "kernel_configs.json"
     if tuned.exists() and device.type == "cuda":
         from ..ops import tuning
-        tuning.activate(tuning.KernelConfigCache(tuned))   # measured launch configurations win over the heuristics
+        tuning.activate(tuning.KernelConfigCache(tuned, strict=False))   # measured configurations win over the heuristics
     weights = art.load_weights(rank, device)
     pages = size_kv_pool(art, lay, device, args.total_kv_bytes)
     pages = min(pages, max(8, (args.max_seq_len // 16 + 1) * max(1, args.max_batch or art.plan["batching"]["max_batch"]) * 2))

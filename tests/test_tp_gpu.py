@@ -11,14 +11,14 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world, env_extra=None, port=29541):
+def _run(world, env_extra=None, port=29541, worker="tp_worker.py", ok="TP_WORKER_OK"):
     env = dict(os.environ)
     env.update({"NCCL_NVLS_ENABLE": "0"})
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "workers", "tp_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "workers", worker)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
-    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and ok in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -34,3 +34,31 @@ def test_tp2_nccl_baseline_mode():
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp4_fused():
     _run(4, port=29543)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep2_fused():
+    """Expert parallelism over 2 GPUs: experts divided, owner-aware combine pulls each row from its owner."""
+    _run(2, {"SKEIN_TEST_TP": "1"}, port=29544, worker="ep_worker.py", ok="EP_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_tp2_ep2_fused():
+    _run(4, {"SKEIN_TEST_TP": "2"}, port=29545, worker="ep_worker.py", ok="EP_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pp2_gpu(tmp_path):
+    """Two pipeline stages on two GPUs (NCCL point-to-point of the residual stream, token feedback, micro-batched
+    pipelined decode) produce exactly the single-stage tokens. See workers/pp_worker.py."""
+    from skein_b200.parallel import launcher
+
+    procs = []
+    for l in launcher.plan_launch([0, 1], str(tmp_path / "rdv")):
+        _, env = launcher.build_command(l, [])
+        env.update({"PP_WORKER_DEVICE": "cuda", "NCCL_NVLS_ENABLE": "0"})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "workers", "pp_worker.py")], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=200) for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[1][-2000:] for o in outs)
+    assert "PP_WORKER_OK" in outs[0][0]

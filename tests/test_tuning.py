@@ -39,6 +39,15 @@ def test_round_trip_and_stale_pruning(tmp_path):
     path.write_text(json.dumps({"version": 7, "entries": {}}))
     with pytest.raises(ValueError):
         tuning.KernelConfigCache(path)
+    # a corrupt file: strict loading raises, the serving path falls back to an empty cache and says why
+    path.write_text("{ not json")
+    with pytest.raises(ValueError):
+        tuning.KernelConfigCache(path)
+    lenient = tuning.KernelConfigCache(path, strict=False)
+    assert lenient.entries == {} and "JSONDecodeError" in lenient.load_error
+    lenient.put("gemm", (0, 1, 128, 64, 16), {"n_tile": 16, "grid": 0, "line_cut_only": 0}, arch="sm_100", build="b1")
+    lenient.save()
+    assert tuning.KernelConfigCache(path).get("gemm", (0, 1, 128, 64, 16), arch="sm_100", build="b1")["n_tile"] == 16
 
 
 def test_candidates_respect_the_epilogue_limits():
