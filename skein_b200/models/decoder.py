@@ -18,6 +18,8 @@ the graph instead of luminal and hand-written kernels instead of searched ones.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 
 import torch
@@ -126,7 +128,8 @@ class Decoder:
     """One rank's share of the model: weights, KV cache and the step function."""
 
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
-                 num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None):
+                 num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None,
+                 pack_moe: bool | None = None):
         self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
         self.comm = comm          # tensor-parallel communicator over this rank's TP group, or None
         self.comm_moe = comm_moe  # communicator over all tp x ep ranks of the stage (expert parallelism), or None
@@ -143,6 +146,16 @@ class Decoder:
         self.kv = [torch.zeros(num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
                    for _ in weights.layers] if num_pages > 0 else []
         self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
+        if pack_moe is None:
+            pack_moe = os.environ.get("SKEIN_PACK_MOE", "0") == "1"
+        if pack_moe and cfg.is_moe and dev.type == "cuda":
+            # expert weights re-laid tile by tile (ops.pack_weight): each 128 x 64 tile the GEMM streams is one
+            # contiguous 16 KB block instead of 128 rows that are a whole K apart
+            for lw in weights.layers:
+                for name in ("w13", "w2"):
+                    w = getattr(lw, name)
+                    if isinstance(w, torch.Tensor) and w.dim() == 3 and w.shape[1] % 128 == 0 and w.shape[2] % 64 == 0:
+                        setattr(lw, name, ops.pack_weight(w))
 
     # ---- pieces ---------------------------------------------------------------------------------
     def _attention(self, li: int, normed, inp: BatchInputs):
@@ -180,9 +193,12 @@ class Decoder:
         w8 = lw.fp8.get(name)
         if w8 is not None and single:
             return self._col_linear(x, lw, name, grouped=grouped).unsqueeze(0), None, None
+        if w8 is not None and x.is_cuda and hasattr(self.comm, "linear_push_fp8"):
+            xq, xs = ops.quant_fp8_block128(x)
+            return self.comm.linear_push_fp8(xq, xs, w8, grouped)
         w = getattr(lw, name)
         if w is None:
-            w = w8.dequant()      # fp8 row-parallel projections under TP run W8A16 until the fp8 push epilogue lands
+            w = w8.dequant()      # CPU ranks (reference operators): dequantise, then the bf16 path
         if single:
             y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
             return y.unsqueeze(0), None, None
@@ -211,8 +227,13 @@ class Decoder:
                 ids, wts, counts, offsets, row_of, src_token, xs = routed
             cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
             h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep)
-            w2 = lw.w2 if lw.w2 is not None else lw.fp8["w2"].dequant()
-            part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
+            w8 = lw.fp8.get("w2")
+            if w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
+                hq, hs = ops.quant_fp8_block128(h)
+                part, flags, epoch = self.comm_moe.linear_push_fp8(hq, hs, w8, (cnt_l, off_l))
+            else:
+                w2 = lw.w2 if lw.w2 is not None else w8.dequant()
+                part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
             self._owner = (ids, e_local, self.layout.tp)
             return part, flags, epoch, row_of.view(T, cfg.top_k), wts
         if routed is None:

@@ -121,3 +121,36 @@ def grouped_linear(xq, xs, w: Fp8Weight, counts, offsets, swiglu: bool = False, 
     p.ldo, p.mode, p.fp8 = out.stride(0), (1 if swiglu else 0), 1
     _launch(p, "fp8 grouped_linear")
     return out
+
+
+def linear_publish(xq, xs, w: Fp8Weight, out_local, peer_flag, epoch, done_counter, ldo, grouped=None, n_tile=None,
+                   rows_hint=None):
+    """Row-parallel fp8 projection that publishes its partial result to the tensor-parallel peers: the bf16 partial
+    goes into `out_local` (peer-mapped), then this rank's flag on every peer is set (same contract as
+    ops.linear_push; csrc/kernels/gemm_ws_fp8.cu mode 2)."""
+    R, K = xq.shape
+    p = _lib.GemmParams()
+    p.W, p.X, p.out = w.q.data_ptr(), xq.data_ptr(), out_local.data_ptr()
+    p.w_scale, p.x_scale = w.scale_t.data_ptr(), xs.data_ptr()
+    if grouped is None:
+        rows = w.shape[-2]
+        p.G, p.F, p.K = 1, rows, K
+        p.w_rows_per_group = rows
+        p.n_tile = n_tile or _n_tile(R, False)
+    else:
+        counts, offsets = grouped
+        E, rows = w.shape[0], w.shape[1]
+        p.G, p.F, p.K = E, rows, K
+        p.w_rows_per_group = rows
+        p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
+        avg = (rows_hint if rows_hint is not None else R) / E
+        p.n_tile = n_tile or _n_tile(int(math.ceil(avg * 1.5)), False)
+    p.up_row_off = 0
+    p.x_rows, p.t_static = R, R
+    p.ldo, p.mode, p.fp8 = ldo, 2, 1
+    p.n_peers = len(peer_flag)
+    for i, pf in enumerate(peer_flag):
+        p.peer_flag[i] = pf
+    p.epoch = epoch.data_ptr()
+    p.done_counter = done_counter.data_ptr()
+    _launch(p, "fp8 linear_publish")

@@ -149,6 +149,12 @@ class PackedWeight:
     def data_ptr(self):
         return self.data.data_ptr()
 
+    def copy_(self, src):
+        """In-place update from a plain [groups?, rows, K] tensor or another PackedWeight (hot swap keeps the storage
+        that captured CUDA graphs point at)."""
+        self.data.copy_(src.data if isinstance(src, PackedWeight) else pack_weight(src).data)
+        return self
+
     def unpack(self) -> torch.Tensor:
         *g, R, K = self.shape
         G = g[0] if g else 1

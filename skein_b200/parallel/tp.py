@@ -107,6 +107,21 @@ class TPComm:
         part = self._partials(b, rows)
         return part, part.flags, part.epoch
 
+    def linear_push_fp8(self, xq, xs, w8, grouped=None, rows_hint=None):
+        """linear_push for a block-scaled e4m3 weight and pre-quantised activations (ops/fp8.py)."""
+        from ..ops import fp8
+        rows = xq.shape[0]
+        if not self._fused_ok(rows):
+            y = fp8.grouped_linear(xq, xs, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear(xq, xs, w8)
+            dist.all_reduce(y, group=self.group)
+            return y.unsqueeze(0), None, None
+        b = self.cur
+        self.cur ^= 1
+        fp8.linear_publish(xq, xs, w8, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+                           self.hidden, grouped=grouped, rows_hint=rows_hint)
+        part = self._partials(b, rows)
+        return part, part.flags, part.epoch
+
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         """Stand-alone sum all-reduce of a [rows, H] bf16 tensor (publish + pull-and-sum)."""
         rows = x.shape[0]

@@ -111,6 +111,10 @@ def op_moe(which, tp, a):
         fn = lambda: ops.grouped_linear(xs, w, cnt, off, swiglu=False, out=out)
         fl = 2 * rows * H * F
     by = w.numel() * 2 + xs.numel() * 2 + out.numel() * 2
+    if a.packed:   # tile-packed weights: every 128 x 64 tile the GEMM loads is one contiguous 16 KB block
+        wp = ops.pack_weight(w)
+        del w
+        fn = (lambda: ops.grouped_linear(xs, wp, cnt, off, swiglu=(which == "gate_up"), out=out))
     return fn, by, fl
 
 
@@ -178,6 +182,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--packed", action="store_true", help="MoE ops: use tile-packed weights (ops.pack_weight)")
     ap.add_argument("--graph", action="store_true",
                     help="time launches back to back inside a CUDA graph over rotating operand copies (cold L2, "
                          "no per-launch event overhead) instead of one launch per event pair")
