@@ -63,6 +63,16 @@ def main():
         r2, n2 = ref.reduce_residual_rmsnorm(res, ref.linear(x_full, w_full).unsqueeze(0), gamma, 1e-5)
         assert rel(r1, r2) < 2e-2 and rel(n1, n2) < 2e-2, ("dense", it, rel(r1, r2), rel(n1, n2))
 
+    # 2a'. the same projection through the block-scaled fp8 GEMM with the publish epilogue
+    from skein_b200.ops import fp8
+    w8 = fp8.quantize_weight(w_full[:, ks].contiguous().to(dev))
+    xq, xsc = ops.quant_fp8_block128(x_full[:, ks].contiguous().to(dev))
+    for it in range(2):
+        part, flags, epoch = comm.linear_push_fp8(xq, xsc, w8)
+        r1, n1 = ops.reduce_residual_rmsnorm(res.to(dev), part, gamma.to(dev), 1e-5, flags=flags, epoch=epoch)
+        r2, n2 = ref.reduce_residual_rmsnorm(res, ref.linear(x_full, w_full).unsqueeze(0), gamma, 1e-5)
+        assert rel(r1, r2) < 6e-2 and rel(n1, n2) < 6e-2, ("fp8 dense", it, rel(r1, r2), rel(n1, n2))
+
     # 2b. grouped (MoE down projection + top-2 combine)
     E, topk, Kp = 4, 2, 256
     ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).to(torch.int32)
