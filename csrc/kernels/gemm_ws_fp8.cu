@@ -303,7 +303,7 @@ static int launch_f8(const CUtensorMap& tmW, const CUtensorMap& tmX, const F8Arg
 
 }  // namespace skein
 
-// mode 0 store, 1 SwiGLU pair (dual), 2 push to peers. n_tile in {16, 32, 64} (dual: {16, 32}).
+// mode 0 store, 1 SwiGLU pair (dual), 2 store + publish flags to peers. n_tile in {16, 32, 64} (dual: {16, 32}).
 extern "C" int skein_gemm_ws_fp8(const SkeinGemmParams* p, void* stream) {
   using namespace skein;
   if (!p || p->G < 1 || p->G > SKEIN_MAX_GROUPS) return -1;

@@ -4,15 +4,15 @@
 // One kernel covers every "sum things into the residual stream, then normalise" point of a
 // decoder block:
 //   acc[h] = residual[b, h]
-//          + sum over sources s (tensor-parallel ranks that pushed a partial result into this
-//            rank's buffer; 1 on a single GPU)
+//          + sum over sources s (the tensor-parallel ranks' partial results: slots of a local tensor, or
+//            every rank's own peer-mapped buffer, pulled over NVLink; 1 on a single GPU)
 //              of   partial[s][b, h]                                   (dense: attention o_proj)
 //              or   sum_j weight[b, j] * partial[s][row[b, j], h]      (MoE: rows are in
 //                                                                       expert-sorted order)
 //   residual_out[b, h] = bf16(acc[h])
 //   normed_out[b, h]   = bf16(residual_out[b, h] * rsqrt(mean(residual_out^2) + eps) * gamma[h])
 // When sources are other GPUs the kernel first waits (bounded) until every source's flag has
-// reached this buffer's current epoch.
+// reached this buffer's current epoch, then reads the peers' buffers with plain loads.
 //
 // Replaces the reference's unfused rms_norm graph (crates/skein_emit/src/op_wiring.rs:1787), its
 // elementwise residual adds and the NCCL all-reduce + copy-back
