@@ -168,8 +168,8 @@ def cmd_calibrate(args, emit) -> int:
 def bench_collectives(emit, args) -> int:
     """Time the stand-alone all-reduce (publish + peer pull) against the library all-reduce for decode-sized messages.
 
-    Run under `python -m torch.distributed.run --nproc-per-node N ... skein bench --collectives ...`: one process per
-    GPU. CUDA events on the launching stream, 20 launches per sample, max over ranks. Counterpart of the reference's
+    Run under `python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m skein_b200 bench
+    --collectives`: one process per GPU. CUDA events on the launching stream, 20 launches per sample, max over ranks. Counterpart of the reference's
     SKEIN_ALLREDUCE_BENCH (crates/skein_runtime/src/cuda/nccl.rs: bench_all_reduce)."""
     import datetime
 

@@ -59,8 +59,11 @@ def _launch(p, what):
 
 
 def _n_tile(rows_hint: int, dual: bool) -> int:
-    cap = 32 if dual else 64
-    return max(16, min(cap, (max(rows_hint, 1) + 15) // 16 * 16 if rows_hint <= cap else cap))
+    """Token-tile width the fp8 kernel is instantiated for: 16, 32 or (single accumulator only) 64."""
+    for t in ((16, 32) if dual else (16, 32, 64)):
+        if rows_hint <= t:
+            return t
+    return 32 if dual else 64
 
 
 def _ref_linear(xq, xs, w: Fp8Weight, swiglu):
