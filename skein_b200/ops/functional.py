@@ -287,6 +287,8 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
     if normed_out is None and gamma is not None:
         normed_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
     pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
+    if peer and wait_budget_ms == 0:
+        wait_budget_ms = partial.wait_budget_ms
     topk = row_idx.shape[1] if row_idx is not None else 0
     ws = workspace()
     rc = _lib.lib().skein_reduce_residual_rmsnorm(
@@ -333,6 +335,8 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
     row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
     xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev)
     pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
+    if peer and wait_budget_ms == 0:
+        wait_budget_ms = partial.wait_budget_ms
     ws = workspace()
     rc = _lib.lib().skein_reduce_norm_route(
         _lib.ptr(residual), pptr, gamma.data_ptr(), residual_out.data_ptr(), normed_out.data_ptr(),

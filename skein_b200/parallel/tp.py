@@ -40,9 +40,10 @@ class PeerPartials:
     """Operand of the reduce kernels: rank s's partial result is the [rows, H] buffer at ptrs[s] (peer-mapped
     memory), complete once flags[s] has reached the device-side epoch."""
 
-    def __init__(self, local, ptrs, n_src, flags, epoch):
+    def __init__(self, local, ptrs, n_src, flags, epoch, wait_budget_ms=0):
         self.local, self.ptrs, self.n_src, self.flags, self.epoch = local, ptrs, n_src, flags, epoch
         self.rows = local.shape[0]
+        self.wait_budget_ms = wait_budget_ms   # how long the consumer waits for a peer's flag (0: kernel default)
 
 
 class TPComm:
@@ -82,7 +83,8 @@ class TPComm:
         self._push_flag = [VP(*self._peer_flag[b]) for b in range(2)]
 
     def _partials(self, b: int, rows: int) -> PeerPartials:
-        return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1])
+        return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1],
+                            self.wait_budget_ms)
 
     @staticmethod
     def create(group, device, max_rows: int, hidden: int, **kw) -> "TPComm":

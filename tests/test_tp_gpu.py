@@ -62,3 +62,9 @@ def test_pp2_gpu(tmp_path):
     outs = [p.communicate(timeout=200) for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(o[1][-2000:] for o in outs)
     assert "PP_WORKER_OK" in outs[0][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_silent_rank_is_detected_by_the_bounded_wait():
+    """A rank that stops publishing makes the peer's wait run out after its budget: an error status, not a hang."""
+    _run(2, port=29546, worker="tp_timeout_worker.py", ok="TP_TIMEOUT_OK")
