@@ -125,7 +125,10 @@ class BatchInputs:
 
 
 class Decoder:
-    """One rank's share of the model: weights, KV cache and the step function."""
+    """One rank's share of the model: weights, KV cache and the step function.
+
+    The decoder takes ownership of `weights`: on a GPU the expert matrices are replaced in place by their tile-packed
+    form (`ops.PackedWeight`: `.shape`, `.cpu()`, `.unpack()`, `.copy_()`), so that no second copy stays alive."""
 
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
                  num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None,
@@ -147,10 +150,11 @@ class Decoder:
                    for _ in weights.layers] if num_pages > 0 else []
         self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
         if pack_moe is None:
-            pack_moe = os.environ.get("SKEIN_PACK_MOE", "0") == "1"
+            pack_moe = os.environ.get("SKEIN_PACK_MOE", "1") == "1"
         if pack_moe and cfg.is_moe and dev.type == "cuda":
             # expert weights re-laid tile by tile (ops.pack_weight): each 128 x 64 tile the GEMM streams is one
-            # contiguous 16 KB block instead of 128 rows that are a whole K apart
+            # contiguous 16 KB block instead of 128 rows that are a whole K apart. Measured in-graph on B200:
+            # gate/up 80.4 -> 71.2 us at the TP=4 shard shape, 43.2 -> 40.4 us at TP=8, unchanged at TP=1 (HBM-bound)
             for lw in weights.layers:
                 for name in ("w13", "w2"):
                     w = getattr(lw, name)

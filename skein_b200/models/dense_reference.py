@@ -52,29 +52,32 @@ def forward_full(cfg: ModelConfig, w: ModelWeights, token_ids: torch.Tensor, cap
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, dim=-1), v).reshape(T, Hq * D)
         x = x + a @ lw.wo.float().t()
         h = _rms(x, lw.ffn_norm, cfg.rms_norm_eps)
+        # a Decoder on the same weights may have re-laid the expert matrices tile by tile: read the logical view
+        w13 = lw.w13.unpack() if hasattr(lw.w13, "unpack") else lw.w13
+        w2 = lw.w2.unpack() if hasattr(lw.w2, "unpack") else lw.w2
         if cfg.is_moe:
             logits = h @ lw.router.float().t()
             probs = torch.softmax(logits, dim=-1)
             topv, topi = probs.topk(cfg.top_k, dim=-1)
             topv = topv / topv.sum(-1, keepdim=True)
             y = torch.zeros_like(x)
-            I = lw.w13.shape[1] // 2
+            I = w13.shape[1] // 2
             for e in range(cfg.num_experts):
                 sel = (topi == e)
                 rows = sel.any(-1).nonzero().squeeze(-1)
                 if rows.numel() == 0:
                     continue
                 he = h[rows]
-                g = he @ lw.w13[e, :I].float().t()
-                u = he @ lw.w13[e, I:].float().t()
-                o = (torch.nn.functional.silu(g) * u) @ lw.w2[e].float().t()
+                g = he @ w13[e, :I].float().t()
+                u = he @ w13[e, I:].float().t()
+                o = (torch.nn.functional.silu(g) * u) @ w2[e].float().t()
                 y[rows] += o * (topv[rows] * sel[rows].float()).sum(-1, keepdim=True)
             x = x + y
         else:
-            I = lw.w13.shape[0] // 2
-            g = h @ lw.w13[:I].float().t()
-            u = h @ lw.w13[I:].float().t()
-            x = x + (torch.nn.functional.silu(g) * u) @ lw.w2.float().t()
+            I = w13.shape[0] // 2
+            g = h @ w13[:I].float().t()
+            u = h @ w13[I:].float().t()
+            x = x + (torch.nn.functional.silu(g) * u) @ w2.float().t()
         if capture_hidden is not None:
             capture_hidden.append(x.clone())
     h = _rms(x, w.final_norm, cfg.rms_norm_eps)

@@ -155,6 +155,10 @@ class PackedWeight:
         self.data.copy_(src.data if isinstance(src, PackedWeight) else pack_weight(src).data)
         return self
 
+    def cpu(self) -> torch.Tensor:
+        """The logical (row-major) tensor on the host."""
+        return self.unpack().cpu()
+
     def unpack(self) -> torch.Tensor:
         *g, R, K = self.shape
         G = g[0] if g else 1
