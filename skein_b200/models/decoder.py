@@ -132,7 +132,7 @@ class Decoder:
 
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
                  num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None,
-                 pack_moe: bool | None = None):
+                 pack_moe: bool | None = None):   # pack_moe: tile-pack the FFN / expert weights
         self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
         self.comm = comm          # tensor-parallel communicator over this rank's TP group, or None
         self.comm_moe = comm_moe  # communicator over all tp x ep ranks of the stage (expert parallelism), or None
@@ -151,14 +151,18 @@ class Decoder:
         self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
         if pack_moe is None:
             pack_moe = os.environ.get("SKEIN_PACK_MOE", "1") == "1"
-        if pack_moe and cfg.is_moe and dev.type == "cuda":
+        if pack_moe and dev.type == "cuda":
             # expert weights re-laid tile by tile (ops.pack_weight): each 128 x 64 tile the GEMM streams is one
             # contiguous 16 KB block instead of 128 rows that are a whole K apart. Measured in-graph on B200:
             # gate/up 80.4 -> 71.2 us at the TP=4 shard shape, 43.2 -> 40.4 us at TP=8, unchanged at TP=1 (HBM-bound)
             for lw in weights.layers:
                 for name in ("w13", "w2"):
                     w = getattr(lw, name)
-                    if isinstance(w, torch.Tensor) and w.dim() == 3 and w.shape[1] % 128 == 0 and w.shape[2] % 64 == 0:
+                    if not isinstance(w, torch.Tensor) or w.dim() not in (2, 3):
+                        continue
+                    rows, K = w.shape[-2], w.shape[-1]
+                    half_ok = name != "w13" or (rows // 2) % 128 == 0     # the up half starts on a tile boundary
+                    if rows % 128 == 0 and K % 64 == 0 and half_ok:
                         setattr(lw, name, ops.pack_weight(w))
 
     # ---- pieces ---------------------------------------------------------------------------------
