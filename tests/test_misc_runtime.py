@@ -59,3 +59,29 @@ def test_profiling_is_a_no_op_by_default():
     assert profiling.report() == {} or "x" in profiling.report()
     profiling.count_h2d(10); profiling.count_d2h(4)
     assert profiling.host_bytes()["h2d"] >= 10
+
+
+def test_packed_weight_round_trip_and_in_place_update():
+    """Tile-packed weights keep the logical tensor: unpack / cpu give it back, copy_ re-packs in place (hot swap)."""
+    import torch
+
+    from skein_b200 import ops
+
+    g = torch.Generator().manual_seed(0)
+    for shape in ((256, 128), (3, 384, 192)):
+        w = torch.randn(*shape, generator=g).bfloat16()
+        p = ops.pack_weight(w)
+        assert p.shape == tuple(shape) and torch.equal(p.unpack(), w) and torch.equal(p.cpu(), w)
+        storage = p.data.data_ptr()
+        w2 = torch.randn(*shape, generator=g).bfloat16()
+        p.copy_(w2)
+        assert p.data.data_ptr() == storage and torch.equal(p.unpack(), w2)
+        p.copy_(ops.pack_weight(w))
+        assert torch.equal(p.unpack(), w)
+        # the CPU operators accept the packed form
+        x = torch.randn(5, shape[-1], generator=g).bfloat16()
+        if len(shape) == 2:
+            assert torch.equal(ops.linear(x, p), ops.linear(x, w))
+    import pytest
+    with pytest.raises(ValueError):
+        ops.pack_weight(torch.zeros(100, 64))
