@@ -7,7 +7,7 @@
 // cache into shared memory with cp.async while earlier tiles are being multiplied.
 //
 //   grid = (splits, Hkv, B), 128 threads. The split's range of 16-token tiles is dealt round-robin
-//   to the 4 warps. Each warp runs its own 3-stage pipeline (no CTA-wide barrier in the loop):
+//   to the 4 warps. Each warp runs its own 3- or 6-stage pipeline (no CTA-wide barrier in the loop):
 //       cp.async tile i+2 (K 4 KB + V 4 KB, XOR-swizzled rows)      wait tile i
 //       S = Q K^T  (2 n-tiles x 8 k-steps)   online softmax in registers   O += P V (16 n-tiles)
 //   and keeps (m, l, O) for its share of the tokens. The warps' states are merged through shared
@@ -29,11 +29,12 @@ constexpr int AM_THREADS = 128;
 constexpr int AM_WARPS = 4;
 constexpr int AM_D = 128;
 constexpr int AM_TILE = 16;                       // tokens per tile
-constexpr int AM_STAGES = 3;
+// cp.async ring depth per warp: 3 (two CTAs per SM, for launches with more CTAs than SMs) or 6 (one CTA per SM gets
+// the whole shared memory: twice the bytes in flight per CTA when there are fewer CTAs than SMs)
 constexpr int AM_TILE_BYTES = AM_TILE * AM_D * 2;  // 4 KB (K or V)
 constexpr int AM_STAGE_BYTES = 2 * AM_TILE_BYTES;  // K then V
-constexpr int AM_WARP_BYTES = AM_STAGES * AM_STAGE_BYTES;
-constexpr int AM_SMEM_BYTES = AM_WARPS * AM_WARP_BYTES + AM_TILE_BYTES;  // + the Q tile
+constexpr int am_warp_bytes(int stages) { return stages * AM_STAGE_BYTES; }
+constexpr int am_smem_bytes(int stages) { return AM_WARPS * am_warp_bytes(stages) + AM_TILE_BYTES; }  // + the Q tile
 constexpr int AM_MAX_SPLITS = 16;
 
 struct AttnMmaParams {
@@ -86,7 +87,9 @@ __device__ __forceinline__ void am_commit() { asm volatile("cp.async.commit_grou
 template <int N>
 __device__ __forceinline__ void am_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
+template <int AM_STAGES>
 __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnMmaParams p) {
+  constexpr int AM_WARP_BYTES = AM_STAGES * AM_STAGE_BYTES;
   extern __shared__ __align__(128) uint8_t am_smem[];
   __shared__ int is_last;
   pdl_trigger();
@@ -399,8 +402,10 @@ static int attn_decode_mma_launch(const void* q, long long q_stride, void* kv, c
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -4;
   if (!attr_set[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               AM_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         am_smem_bytes(3));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_mma_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, am_smem_bytes(6));
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
@@ -413,7 +418,11 @@ static int attn_decode_mma_launch(const void* q, long long q_stride, void* kv, c
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
   p.splits = splits; p.scale_log2e = scale * 1.4426950408889634f;
   dim3 grid(splits, Hkv, B);
-  return (int)launch_pdl(attn_decode_mma_kernel, grid, dim3(AM_THREADS), (size_t)AM_SMEM_BYTES, (cudaStream_t)stream, p);
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  if ((long long)splits * Hkv * B <= sms)
+    return (int)launch_pdl(attn_decode_mma_kernel<6>, grid, dim3(AM_THREADS), (size_t)am_smem_bytes(6), (cudaStream_t)stream, p);
+  return (int)launch_pdl(attn_decode_mma_kernel<3>, grid, dim3(AM_THREADS), (size_t)am_smem_bytes(3), (cudaStream_t)stream, p);
 }
 
 extern "C" int skein_attn_decode_mma(const void* q, long long q_stride, const void* kv, const int* block_table,
