@@ -53,7 +53,7 @@ def parse():
 
 def reference_arm(args):
     # The reference is a Rust workspace (cargo, luminal, cudarc). It has no Python package to install
-    # (`pip install /root/reference`: "Neither 'setup.py' nor 'pyproject.toml' found") and this image
+    # (`pip install` of its source tree: "Neither 'setup.py' nor 'pyproject.toml' found") and this image
     # has no Rust toolchain, so it cannot be built or run here.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Rust/cargo workspace: pip reports no setup.py/pyproject.toml "

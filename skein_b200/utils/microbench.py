@@ -143,6 +143,14 @@ def op_reduce(a):
     return fn, 4 * B * H * 2, 6 * B * H
 
 
+def op_reduce_route(a):
+    """Post-attention point of a MoE block: partial sum + residual + RMSNorm + router + expert-sorted scatter."""
+    B, H = a.tokens, 4096
+    res, part, g, wg = _bf(B, H, std=1.0), _bf(1, B, H, std=1.0), _bf(H, std=1.0), _bf(8, H)
+    fn = lambda: ops.reduce_norm_route(res, part, g, 1e-5, wg, 2)
+    return fn, (6 * B * H + 8 * H) * 2, 2 * B * 8 * H
+
+
 def op_router(a):
     x, wg = _bf(a.tokens, 4096, std=1.0), _bf(8, 4096)
     fn = lambda: ops.route(x, wg, 2)
@@ -167,10 +175,12 @@ def build(name, a):
         return op_reduce(a)
     if name == "router":
         return op_router(a)
+    if name == "reduce_route":
+        return op_reduce_route(a)
     raise SystemExit(f"unknown op {name}")
 
 
-OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "router")
+OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "reduce_route", "router")
 
 
 def main(argv=None):
