@@ -310,9 +310,11 @@ def main():
     if rank == 0:
         ttft.sort()
         out = {
-            "metric": "mixtral_8x7b_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s",
+            "metric": args.model.replace("-", "_") + "_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16",
+            "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_TOK_S, 2) if args.model == "mixtral-8x7b" and not args.layers else None,
+            "dtype": "bf16",
             "data": "synthetic (random-init weights N(0,0.02), random prompt token ids)",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
                        "global_batch": B, "seq_len": P, "gen_len": Gn, "parallelism": f"tp{world}",

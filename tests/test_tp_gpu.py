@@ -42,6 +42,12 @@ def test_ep2_fused():
     _run(2, {"SKEIN_TEST_TP": "1"}, port=29544, worker="ep_worker.py", ok="EP_WORKER_OK")
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep2_fp8_experts():
+    """The same with block-scaled fp8 expert weights: grouped fp8 GEMMs, fp8 publish epilogue, owner-aware combine."""
+    _run(2, {"SKEIN_TEST_TP": "1", "SKEIN_TEST_FP8": "1"}, port=29547, worker="ep_worker.py", ok="EP_WORKER_OK")
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp2_ep2_fused():
     _run(4, {"SKEIN_TEST_TP": "2"}, port=29545, worker="ep_worker.py", ok="EP_WORKER_OK")

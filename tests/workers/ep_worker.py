@@ -39,12 +39,21 @@ def main():
         comm = TPComm(groups[rank // tp], dev, hidden=H, fused_rows=256, max_batch=64)
     comm_moe = TPComm(dist.group.WORLD, dev, hidden=H, fused_rows=256, max_batch=64)
     g = torch.Generator().manual_seed(7)
+    # e4m3 activations and weights carry ~2^-4 relative noise per element: near-ties are wider than in bf16
+    fp8_run = os.environ.get("SKEIN_TEST_FP8") == "1"
+    tie_margin, gap_tol, max_diffs = (0.3, 0.3, 6) if fp8_run else (0.06, 0.08, 4)
 
     # tiny Mixtral, TP x EP = world, graph decode with fused collectives vs the CPU reference graph
     cfg = mc.tiny_mixtral(layers=2, hidden=H, inter=512 * tp, heads=8, kv_heads=2 * tp, experts=4 * ep, vocab=1024)
     full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=11, std=0.05)
-    dec = Decoder(cfg, shard_model(full, cfg, lay, dev), lay, num_pages=32, page_size=16, max_pos=256, comm=comm,
-                  comm_moe=comm_moe)
+    shard = shard_model(full, cfg, lay, dev)
+    if fp8_run:
+        # block-scaled e4m3 expert weights on both sides (experts are divided whole, so the shards quantise exactly
+        # like the full matrices): the row-parallel down projection publishes through the fp8 GEMM
+        from skein_b200.models.decoder import quantize_blocks
+        quantize_blocks(shard, range(cfg.num_layers), names=("w13", "w2"))
+        quantize_blocks(full, range(cfg.num_layers), names=("w13", "w2"))
+    dec = Decoder(cfg, shard, lay, num_pages=32, page_size=16, max_pos=256, comm=comm, comm_moe=comm_moe)
     dec_ref = Decoder(cfg, full, num_pages=32, page_size=16, max_pos=256)
     B = 3
     prompts = torch.randint(0, cfg.vocab_size, (B, 21), generator=g).tolist()
@@ -88,7 +97,7 @@ def main():
         ref.router_topk = ref_router
         # first decode step (1-based, matching ref_toks) at which a sequence met a router near-tie, else none
         n_l = cfg.num_layers
-        tie_from = [min([t + 1 for t in range(steps) if min(margins[t * n_l + l][s_] for l in range(n_l)) < 0.06],
+        tie_from = [min([t + 1 for t in range(steps) if min(margins[t * n_l + l][s_] for l in range(n_l)) < tie_margin],
                         default=steps + 1) for s_ in range(B)]
         payload = [ref_toks, gaps, tie_from]
     else:
@@ -113,8 +122,8 @@ def main():
     # which the reference routed that sequence on a near-tie between experts (its cache rows differ from then on)
     diffs = [(t, s_, got[t][s_], ref_toks[t][s_], round(gaps[t][s_], 4))
              for t in range(steps + 1) for s_ in range(B) if got[t][s_] != ref_toks[t][s_]]
-    hard = [d for d in diffs if d[4] >= 0.08 and d[0] < tie_from[d[1]]]
-    assert not hard and len(diffs) <= 4, ("(step, seq, got, want, reference top-2 gap)", diffs, "router tie from", tie_from)
+    hard = [d for d in diffs if d[4] >= gap_tol and d[0] < tie_from[d[1]]]
+    assert not hard and len(diffs) <= max_diffs, ("(step, seq, got, want, reference top-2 gap)", diffs, "router tie from", tie_from)
     dist.barrier()
     if rank == 0:
         print("EP_WORKER_OK world", world, "tp", tp, "ep", ep)
