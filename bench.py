@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (tensor parallel = gpus / ep)")
+    ap.add_argument("--fp8-experts", action="store_true", help="block-scaled e4m3 expert / FFN weights (marks dtype)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--eager", action="store_true",
                     help="launch the step's kernels one by one instead of replaying the captured graph "
@@ -173,25 +175,37 @@ def main():
             raise SystemExit("launch multi-GPU runs with torch.distributed.run (WORLD_SIZE must equal --gpus)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    comm = None
+    cfg = {"mixtral-8x7b": mc.mixtral_8x7b, "mixtral-8x22b": mc.mixtral_8x22b, "llama3-70b": mc.llama3_70b}[args.model]()
+    if args.layers:
+        cfg.num_layers = args.layers
+    ep = max(1, args.ep)
+    if world % ep != 0 or (ep > 1 and not cfg.is_moe):
+        raise SystemExit("--ep must divide the number of GPUs and needs a mixture-of-experts model")
+    tp = world // ep
+    comm, comm_moe = None, None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         import datetime
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         from skein_b200.parallel.tp import TPComm
-        comm = TPComm.create(dist.group.WORLD, dev, max_rows=max(8192, 2 * args.batch), hidden=4096)
-
-    cfg = {"mixtral-8x7b": mc.mixtral_8x7b, "mixtral-8x22b": mc.mixtral_8x22b, "llama3-70b": mc.llama3_70b}[args.model]()
-    if args.layers:
-        cfg.num_layers = args.layers
-    lay = mc.ParallelLayout(tp=world, rank=rank)
+        if tp > 1:
+            groups = [dist.new_group(list(range(b0, b0 + tp))) for b0 in range(0, world, tp)] if ep > 1 else [dist.group.WORLD]
+            comm = TPComm.create(groups[rank // tp] if ep > 1 else groups[0], dev, max_rows=max(8192, 2 * args.batch),
+                                 hidden=cfg.hidden_size)
+        if ep > 1:   # communicator over all tp x ep ranks for the expert-parallel combine
+            comm_moe = TPComm.create(dist.group.WORLD, dev, max_rows=max(8192, 2 * args.batch), hidden=cfg.hidden_size)
+    lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
     B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1
     num_pages = B * blocks_per_seq + 8
     t0 = time.time()
     weights = random_weights(cfg, lay, dev, seed=0, std=0.02)
-    dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm)
-    use_graphs = (comm is None or comm.mode == "fused") and not args.eager   # the NCCL baseline mode launches eagerly
+    if args.fp8_experts:
+        from skein_b200.models.decoder import quantize_blocks
+        quantize_blocks(weights, range(len(weights.layers)), names=("w13", "w2"))
+    dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm, comm_moe=comm_moe)
+    fused = all(c is None or c.mode == "fused" for c in (comm, comm_moe))
+    use_graphs = fused and not args.eager   # the NCCL baseline mode launches eagerly
     runner = ModelRunner(dec, max_blocks_per_seq=blocks_per_seq, use_graphs=use_graphs, ctx_hint=P + Gn // 2)
     torch.cuda.synchronize()
     t_init = time.time() - t0
@@ -314,12 +328,13 @@ def main():
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
             "scaling": "strong",
             "vs_baseline": round(value / BASELINE_TOK_S, 2) if args.model == "mixtral-8x7b" and not args.layers else None,
-            "dtype": "bf16",
+            "dtype": "bf16" if not args.fp8_experts else "bf16 activations, fp8 expert weights",
             "data": "synthetic (random-init weights N(0,0.02), random prompt token ids)",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
-                       "global_batch": B, "seq_len": P, "gen_len": Gn, "parallelism": f"tp{world}",
+                       "global_batch": B, "seq_len": P, "gen_len": Gn, "parallelism": f"tp{tp}" + (f"xep{ep}" if ep > 1 else ""),
                        "kv": "paged, block 16", "l2": "inputs (weights) larger than L2, no flush",
-                       "cuda_graph": use_graphs, "comm": (comm.mode if comm else "none")},
+                       "cuda_graph": use_graphs, "comm": ((comm or comm_moe).mode if (comm or comm_moe) else "none"),
+                       "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16"},
             "ttft_p50_ms": round(ttft[len(ttft) // 2], 2),
             "tpot_p99_ms": e2e["tpot_p99_ms"] if e2e else None,
             "e2e": e2e, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,
