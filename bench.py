@@ -157,6 +157,15 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
 
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1. Keep the real stdout for the one JSON
+    # line and send everything else that lands on descriptor 1 to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit_json(obj):
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -227,7 +236,7 @@ def main():
             dist.all_reduce(code, op=dist.ReduceOp.MAX)
         if int(code[0]) != 0:
             if rank == 0:
-                print(json.dumps({"error": f"device status {int(code[0])} after {where}", "n_gpus": world}))
+                emit_json({"error": f"device status {int(code[0])} after {where}", "n_gpus": world})
             if world > 1:
                 dist.destroy_process_group()
             sys.exit(3)
@@ -340,7 +349,7 @@ def main():
             "e2e": e2e, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,
             "clocks": clocks, "init_s": round(t_init, 1), "impl": "ours",
         }
-        print(json.dumps(out))
+        emit_json(out)
     if world > 1:
         dist.destroy_process_group()
     return 0
