@@ -1,7 +1,10 @@
 """One process per GPU: launch plan, per-rank command/environment, file rendezvous, wait-and-count.
 
 The parent computes one command per rank (environment: SKEIN_RANK, SKEIN_WORLD_SIZE, SKEIN_RENDEZVOUS,
-CUDA_VISIBLE_DEVICES), spawns them, waits, and reports how many failed. Ranks meet through a file
+CUDA_VISIBLE_DEVICES, SKEIN_LOCAL_DEVICE), spawns them, waits, and reports how many failed. Every rank sees all
+GPUs of the job, in job order, and computes on the one at index SKEIN_LOCAL_DEVICE: the tensor-parallel kernels read
+the peers' buffers through CUDA IPC mappings, which can only be opened for a device the process can see. If one
+rank dies, the others get a grace period and are then terminated, so a job never outlives a lost rank. Ranks meet through a file
 rendezvous: the leader publishes a small blob atomically (tmp + rename), the others poll for it with a
 timeout and get a clear error if it never appears. torch.distributed is then initialised from the
 address carried in the blob.
@@ -31,6 +34,7 @@ class RankLaunch:
     world_size: int
     gpu: int
     rendezvous: str
+    gpus: tuple = ()      # all devices of the job, in rank order (empty: only `gpu`)
 
 
 def parse_gpus(spec: str) -> list[int]:
@@ -43,18 +47,63 @@ def parse_gpus(spec: str) -> list[int]:
 
 
 def plan_launch(gpus: list[int], rendezvous: str) -> list[RankLaunch]:
-    return [RankLaunch(r, len(gpus), g, rendezvous) for r, g in enumerate(gpus)]
+    return [RankLaunch(r, len(gpus), g, rendezvous, tuple(gpus)) for r, g in enumerate(gpus)]
+
+
+def visible_devices(gpus, parent_visible: str | None) -> str:
+    """CUDA_VISIBLE_DEVICES of a child: the job's devices in rank order. Ids given to --gpus index the devices the
+    parent itself can see, so a launcher that runs under a restricted CUDA_VISIBLE_DEVICES hands down the right ones."""
+    if parent_visible:
+        seen = [x.strip() for x in parent_visible.split(",") if x.strip()]
+        if any(g >= len(seen) for g in gpus):
+            raise ValueError(f"--gpus names device {max(gpus)} but only {len(seen)} are visible ({parent_visible})")
+        return ",".join(seen[g] for g in gpus)
+    return ",".join(str(g) for g in gpus)
 
 
 def build_command(launch: RankLaunch, argv: list[str], base_env: dict | None = None):
     """Returns (argv, env) of the child for this rank."""
     env = dict(base_env if base_env is not None else os.environ)
+    gpus = launch.gpus or (launch.gpu,)
     env.update({"SKEIN_RANK": str(launch.rank), "SKEIN_WORLD_SIZE": str(launch.world_size),
-                "SKEIN_RENDEZVOUS": launch.rendezvous, "CUDA_VISIBLE_DEVICES": str(launch.gpu)})
+                "SKEIN_RENDEZVOUS": launch.rendezvous, "SKEIN_LOCAL_DEVICE": str(gpus.index(launch.gpu)),
+                "CUDA_VISIBLE_DEVICES": visible_devices(gpus, env.get("CUDA_VISIBLE_DEVICES"))})
     return [sys.executable, "-m", "skein_b200.parallel.worker", *argv], env
 
 
-def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: float | None = None) -> int:
+def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, poll_s: float = 0.05) -> list[int]:
+    """Wait for every rank. Once one has failed, the rest get `grace_s` to finish by themselves (they usually notice
+    through their own time-outs) and are then terminated. Returns the exit codes in rank order."""
+    t0 = time.monotonic()
+    first_failure = None
+    codes: list = [None] * len(procs)
+    while any(c is None for c in codes):
+        for i, p in enumerate(procs):
+            if codes[i] is None:
+                codes[i] = p.poll()
+                if codes[i] not in (None, 0) and first_failure is None:
+                    first_failure = time.monotonic()
+        now = time.monotonic()
+        overdue = timeout_s is not None and now - t0 > timeout_s
+        orphaned = first_failure is not None and now - first_failure > grace_s
+        if overdue or orphaned:
+            for i, p in enumerate(procs):
+                if codes[i] is None:
+                    p.terminate()
+            for i, p in enumerate(procs):
+                if codes[i] is None:
+                    try:
+                        p.wait(5.0)
+                    except subprocess.TimeoutExpired:
+                        p.kill()
+                        p.wait()
+                    codes[i] = p.returncode if p.returncode != 0 else -15
+            break
+        time.sleep(poll_s)
+    return codes
+
+
+def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: float | None = None, grace_s: float = 10.0) -> int:
     """Spawn every rank, wait for all, return the number of ranks that failed."""
     rdv = Path(rendezvous)
     if rdv.exists():
@@ -63,16 +112,12 @@ def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: f
     for l in plan_launch(gpus, rendezvous):
         cmd, env = build_command(l, argv)
         procs.append(subprocess.Popen(cmd, env=env))
-    failed = 0
-    deadline = None if timeout_s is None else time.monotonic() + timeout_s
-    for p in procs:
-        try:
-            rc = p.wait(None if deadline is None else max(0.1, deadline - time.monotonic()))
-        except subprocess.TimeoutExpired:
-            p.kill()
-            rc = -9
-        failed += rc != 0
-    return failed
+    return sum(rc != 0 for rc in wait_ranks(procs, timeout_s, grace_s))
+
+
+def local_device_index() -> int:
+    """Index (within this process's visible devices) of the GPU this rank computes on."""
+    return int(os.environ.get("SKEIN_LOCAL_DEVICE", "0"))
 
 
 def world_from_env():

@@ -185,7 +185,8 @@ def run_rank(args) -> int:
     env = launcher.world_from_env()
     rank, world, rdv = env if env else (0, 1, args.rendezvous)
     use_cuda = torch.cuda.is_available() and not args.cpu
-    device = torch.device("cuda", 0) if use_cuda else torch.device("cpu")   # CUDA_VISIBLE_DEVICES selects the GPU
+    # every rank sees all GPUs of the job (the peers' buffers are mapped through CUDA IPC) and computes on its own
+    device = torch.device("cuda", launcher.local_device_index()) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
     art = Artifact(args.artifact)

@@ -171,11 +171,31 @@ def test_launch_plan_and_commands():
     assert [(l.rank, l.world_size, l.gpu) for l in plan] == [(0, 2, 3), (1, 2, 5)]
     cmd, env = launcher.build_command(plan[1], ["--artifact", "a"], base_env={})
     assert cmd[1:4] == ["-m", "skein_b200.parallel.worker", "--artifact"]
-    assert env == {"SKEIN_RANK": "1", "SKEIN_WORLD_SIZE": "2", "SKEIN_RENDEZVOUS": "/tmp/rdv", "CUDA_VISIBLE_DEVICES": "5"}
+    # every rank sees all devices of the job (peer buffers are CUDA IPC mappings) and computes on its own
+    assert env == {"SKEIN_RANK": "1", "SKEIN_WORLD_SIZE": "2", "SKEIN_RENDEZVOUS": "/tmp/rdv", "CUDA_VISIBLE_DEVICES": "3,5",
+                   "SKEIN_LOCAL_DEVICE": "1"}
+    # --gpus ids index what the launcher itself can see
+    assert launcher.build_command(plan[0], [], base_env={"CUDA_VISIBLE_DEVICES": "0,2,4,6,7,1"})[1]["CUDA_VISIBLE_DEVICES"] == "6,1"
+    with pytest.raises(ValueError):
+        launcher.build_command(plan[1], [], base_env={"CUDA_VISIBLE_DEVICES": "0,1"})
     with pytest.raises(ValueError):
         launcher.parse_gpus("1,1")
     with pytest.raises(ValueError):
         launcher.parse_gpus("")
+
+
+def test_a_lost_rank_ends_the_job():
+    """One rank exits with an error while the other would run for a minute: the survivor is terminated after the grace period."""
+    import time as _t
+    procs = [subprocess.Popen([sys.executable, "-c", "import sys; sys.exit(3)"]),
+             subprocess.Popen([sys.executable, "-c", "import time; time.sleep(60)"])]
+    t0 = _t.monotonic()
+    codes = launcher.wait_ranks(procs, grace_s=0.5)
+    assert codes[0] == 3 and codes[1] != 0 and _t.monotonic() - t0 < 20
+    ok = [subprocess.Popen([sys.executable, "-c", "pass"]) for _ in range(2)]
+    assert launcher.wait_ranks(ok) == [0, 0]
+    slow = [subprocess.Popen([sys.executable, "-c", "import time; time.sleep(60)"])]
+    assert launcher.wait_ranks(slow, timeout_s=0.3)[0] != 0          # an overall limit ends a job that never finishes
 
 
 def test_rendezvous_publish_fetch_and_timeout(tmp_path):

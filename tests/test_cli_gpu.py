@@ -1,0 +1,74 @@
+"""The user-facing flow on GPUs: compile an artifact (parity gate on the CPU oracle), verify it on the device, serve a
+generation job (one process per GPU for the tensor-parallel artifact), replay a trace, autotune the GEMM launches.
+
+The reference only tests this flow on CPU with zero weights (crates/skein_runtime/tests/serve_driver.rs:1-239) and runs
+multi-GPU serving by hand.
+"""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+TINY = {"architectures": ["MixtralForCausalLM"], "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "num_local_experts": 4, "num_experts_per_tok": 2,
+        "vocab_size": 512, "rope_theta": 1e6, "rms_norm_eps": 1e-5, "max_position_embeddings": 512}
+
+
+def _cli(args, env=None, timeout=400):
+    r = subprocess.run([sys.executable, "-m", "skein_b200.cli.main", "--output", "json", *args], capture_output=True, text=True,
+                       cwd=ROOT, timeout=timeout, env={**os.environ, **(env or {})})
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def _compile(tmp_path, cluster, env=None):
+    cfg = tmp_path / "tiny_config.json"
+    cfg.write_text(json.dumps(TINY))
+    drift = tmp_path / "tiny_drift.toml"
+    drift.write_text((ROOT / "models/mixtral_8x7b_drift.toml").read_text())
+    common = ["--model", str(cfg), "--cluster", str(ROOT / "cluster" / cluster), "--trace", str(ROOT / "cluster/sample_trace.jsonl"),
+              "--drift", str(drift), "--cost", str(ROOT / "cluster/cost_constants.toml")]
+    rep = _cli(["compile", *common, "--out", str(tmp_path / "art"), "--n-parity-prompts", "2", "--enforce-parity"], env)
+    assert rep["parity"]["passed"]
+    latest = tmp_path / "art" / "LATEST"
+    return str(tmp_path / "art" / os.readlink(latest)), str(cfg)
+
+
+def test_compile_verify_serve_bench_autotune_on_one_gpu(tmp_path):
+    art, cfg = _compile(tmp_path, "b200_1x.toml")
+    cost = str(ROOT / "cluster/cost_constants.toml")
+    v = _cli(["verify", "--artifact", art, "--hf-reference", "--cost", cost, "--n-prompts", "2", "--device", "cuda"])
+    assert v["avg_final_kl"] < 0.05          # CUDA kernels + paged cache vs the cache-free dense oracle
+    out = _cli(["serve", "--artifact", art, "--prompt", "hello", "--max-new-tokens", "6", "--max-seq-len", "128"])
+    assert len(out["generated"][0]) == 6 and out["tokens_per_s"] > 0
+    b = _cli(["bench", "--artifact", art, "--workload", str(ROOT / "cluster/sample_trace.jsonl"), "--max-requests", "3",
+              "--time-scale", "1000"])
+    assert b["requests_ok"] + b["requests_rejected"] == 3
+    corpus = tmp_path / "corpus.toml"
+    corpus.write_text('workload_trace_path = "t.jsonl"\nn_drift_prompts = 2\nsampling_strategy = "stratified_by_length"\nsampling_seed = 1\n'
+                      '[[kernel_samples]]\nop_kind = "gemm"\ndtype = "bf16"\nshape = [1024, 1024]\nrepeats = 5\n')
+    cost_copy = tmp_path / "cost.toml"
+    cost_copy.write_text(Path(cost).read_text())
+    t = _cli(["calibrate", "--hardware", "b200", "--model", cfg, "--corpus", str(corpus), "--candidate-artifact", art,
+              "--out-cost", str(cost_copy), "--out-drift-dir", str(tmp_path), "--autotune", "--autotune-batch", "8"])
+    assert set(t["tuned_gemms"]) >= {"qkv", "o_proj", "moe_gate_up", "moe_down"}
+    assert (Path(art) / "cache" / "kernel_configs.json").exists()
+    again = _cli(["serve", "--artifact", art, "--prompt", "hello", "--max-new-tokens", "6", "--max-seq-len", "128"])
+    assert again["generated"] == out["generated"]      # tuned launch configurations change the speed, not the tokens
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_artifact_served_by_two_processes(tmp_path):
+    art, _ = _compile(tmp_path, "b200_2x.toml", {"SKEIN_FORCE_TP": "2", "SKEIN_FORCE_PP": "1", "SKEIN_FORCE_EP": "1"})
+    plan = json.loads((Path(art) / "plan.json").read_text())
+    assert plan["parallelism"]["tp"] == 2
+    r = _cli(["serve", "--artifact", art, "--gpus", "0,1", "--prompt", "hello", "--max-new-tokens", "6", "--max-seq-len", "128",
+              "--rendezvous", str(tmp_path / "rdv")], {"NCCL_NVLS_ENABLE": "0"})
+    assert r["ranks"] == 2 and r["failed"] == 0

@@ -19,7 +19,7 @@ from skein_b200.runtime.runner import ModelRunner  # noqa: E402
 def main():
     rank, world, rdv = launcher.world_from_env()
     use_cuda = os.environ.get("PP_WORKER_DEVICE", "cpu") == "cuda"
-    dev = torch.device("cuda", 0) if use_cuda else torch.device("cpu")
+    dev = torch.device("cuda", launcher.local_device_index()) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(dev)
     launcher.init_process_group(rank, world, rdv, "nccl" if use_cuda else "gloo", timeout_s=60, device=dev if use_cuda else None)
