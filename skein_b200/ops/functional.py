@@ -103,16 +103,17 @@ def _gemm_launch(p: "_lib.GemmParams", what: str, cfg: dict | None = None):
     if cfg is not None:
         p.n_tile, p.grid, p.line_cut_only = int(cfg["n_tile"]), int(cfg["grid"]), int(cfg["line_cut_only"])
     elif p.grid == 0 and os.environ.get("SKEIN_GEMM_AUTOGRID", "1") == "1":
-        # With between one and two tiles per SM, give every CTA a whole number of tiles: no tile is split, so
-        # the stream-K partial store / reduce disappears; measured 3-12 % faster than equal K-shares on all
-        # CTAs. (With fewer tiles than SMs the kernel itself cuts each tile into aligned pieces; with many
-        # tiles per SM the equal-share split measured ~2 % faster end to end, so it stays the default there.)
+        # With between one and two tiles per SM there are two ways to deal the work. Whole tiles per CTA: no tile is
+        # split, so there is no partial store / reduce, but the CTAs with two tiles set the time and the rest idle.
+        # Equal K shares on every SM: balanced, at the price of the fix-up (~6 us measured, about 16 K-blocks of
+        # streaming). Whole tiles win while the K-blocks they waste per CTA stay under that price: Mixtral's expert
+        # down projection at 8 ranks (28 K-blocks per tile) 26.3 vs 29.7 us; the same projection on one GPU
+        # (224 K-blocks per tile) 157.4 vs 143.6 us, so that one takes the equal shares.
+        # (With fewer tiles than SMs the kernel itself cuts each tile into aligned pieces.)
         # The estimate assumes one token tile per group (decode); a wrong guess only changes the split.
         rows = p.t_static if not p.group_cnt else p.n_tile
         units = p.G * ((p.F + 127) // 128) * max(1, (rows + p.n_tile - 1) // p.n_tile)
-        if ws.sm_count < units <= 2 * ws.sm_count:
-            per_cta = (units + ws.sm_count - 1) // ws.sm_count
-            p.grid = (units + per_cta - 1) // per_cta
+        p.grid = tuning.heuristic_grid(units, p.K // (128 if p.fp8 else 64), ws.sm_count)
     _lib.check(_lib.lib().skein_gemm_ws(C.byref(p), _lib.stream_ptr()), what)
     _lib.count_launch()
 

@@ -132,6 +132,21 @@ def gemm_shape_key(mode: int, G: int, F: int, K: int, rows: int):
     return (mode, G, F, K, (max(rows, 1) + 15) // 16 * 16)
 
 
+WHOLE_TILE_WASTE_LIMIT = 24   # K-blocks a CTA may idle before equal K shares (and their fix-up) are the better deal
+
+
+def heuristic_grid(units: int, k_blocks: int, sm_count: int) -> int:
+    """Grid for a GEMM of `units` output tiles of `k_blocks` K-blocks each when nothing was measured for its shape:
+    a whole number of tiles per CTA (fewer CTAs than SMs) when there are between one and two tiles per SM and the
+    idle time that costs is below the price of splitting tiles; else 0 (one CTA per SM, equal K shares)."""
+    if not (sm_count < units <= 2 * sm_count):
+        return 0
+    per_cta = (units + sm_count - 1) // sm_count
+    if k_blocks * (per_cta - units / sm_count) > WHOLE_TILE_WASTE_LIMIT:
+        return 0
+    return (units + per_cta - 1) // per_cta
+
+
 def gemm_candidates(mode: int, G: int, F: int, rows: int, sm_count: int):
     """Launch configurations worth timing for one GEMM shape."""
     per_group = max(1, rows // max(G, 1))

@@ -79,3 +79,13 @@ def test_tuned_configuration_is_used_and_exact():
     finally:
         tuning.activate(None)
     assert float((got.float() - want.float()).abs().max()) < 2e-2 * float(want.float().abs().max())
+
+
+def test_heuristic_grid_whole_tiles_only_when_they_waste_little():
+    # expert down projection of Mixtral (8 experts x 32 feature tiles = 256 tiles) on 148 SMs
+    assert tuning.heuristic_grid(256, 28, 148) == 128      # 8 ranks, K = 1792: two whole tiles per CTA
+    assert tuning.heuristic_grid(256, 56, 148) == 128
+    assert tuning.heuristic_grid(256, 112, 148) == 0       # 2 ranks: the idle SM time costs more than the fix-up
+    assert tuning.heuristic_grid(256, 224, 148) == 0       # 1 GPU, K = 14336
+    assert tuning.heuristic_grid(250, 64, 148) == 125      # lm_head, 32000 x 4096
+    assert tuning.heuristic_grid(100, 64, 148) == 0 and tuning.heuristic_grid(896, 64, 148) == 0   # outside (SMs, 2 SMs]
