@@ -199,10 +199,9 @@ def main():
         from skein_b200.parallel.tp import TPComm
         if tp > 1:
             groups = [dist.new_group(list(range(b0, b0 + tp))) for b0 in range(0, world, tp)] if ep > 1 else [dist.group.WORLD]
-            comm = TPComm.create(groups[rank // tp] if ep > 1 else groups[0], dev, max_rows=max(8192, 2 * args.batch),
-                                 hidden=cfg.hidden_size)
+            comm = TPComm(groups[rank // tp] if ep > 1 else groups[0], dev, hidden=cfg.hidden_size)
         if ep > 1:   # communicator over all tp x ep ranks for the expert-parallel combine
-            comm_moe = TPComm.create(dist.group.WORLD, dev, max_rows=max(8192, 2 * args.batch), hidden=cfg.hidden_size)
+            comm_moe = TPComm(dist.group.WORLD, dev, hidden=cfg.hidden_size)
     lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
     B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1

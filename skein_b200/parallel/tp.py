@@ -86,10 +86,6 @@ class TPComm:
         return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1],
                             self.wait_budget_ms)
 
-    @staticmethod
-    def create(group, device, max_rows: int, hidden: int, **kw) -> "TPComm":
-        return TPComm(group, device, hidden, **kw)
-
     # ---- row-parallel projection + all-reduce ------------------------------------------------------
     def _fused_ok(self, rows: int) -> bool:
         return self.mode == "fused" and rows <= self.fused_rows
