@@ -8,14 +8,18 @@
 //   * argmax_push: vocabulary-parallel greedy sampling. Each rank reduces its logit shard to one
 //     (value, global index) pair per row and pushes 8 bytes per row to every peer
 //     (merge_candidates in sample.cu picks the winner).
+//   * pull_collective: after a publish, all-gather / reduce-scatter / all-to-all as ONE pull kernel: wait
+//     (bounded) for every rank's flag, then read the chunks this rank needs straight out of the peers'
+//     published buffers, eight 16-byte peer loads in flight per thread, summing in rank order where the
+//     collective reduces.
 //   * copy_pages: KV pages to (or from) a peer's cache, for prefill/decode disaggregation.
 // Flags carry monotonically increasing epochs kept in device memory, so the same launches replay
 // inside a CUDA graph. Every wait on a flag is bounded (ptx.cuh: wait_flag_ge).
 //
 // Replaces the reference's NCCL all-reduce + copy-back (crates/skein_runtime/src/cuda/nccl.rs:196-245),
 // its 2-rank host-shared-memory all-reduce with an unbounded spin (crates/skein_runtime/src/cuda/
-// shm_allreduce.rs:24-69), the logits all-gather (nccl.rs:251-298) and the host-staged KV block
-// transport (nccl.rs:504-588).
+// shm_allreduce.rs:24-69), the logits all-gather (nccl.rs:251-298), the grouped send/recv exchanges
+// (nccl.rs:422-445) and the host-staged KV block transport (nccl.rs:504-588).
 #include "ptx.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
@@ -106,6 +110,76 @@ __global__ void __launch_bounds__(256) copy_pages_kernel(const uint4* __restrict
   for (long long i = threadIdx.x; i < vec_per_page; i += blockDim.x) d[i] = s[i];
 }
 
+// ---- pull collectives ---------------------------------------------------------------------------------
+// Every rank has published a buffer of `n_chunks_src` chunks of `chunk_vec` 16-byte vectors (src[s] is rank s's
+// buffer as this process maps it). What this rank pulls:
+//   PULL_ALL_GATHER      (1 chunk per source):  out[s][i] = src[s][i]
+//   PULL_ALL_TO_ALL      (N chunks per source): out[s][i] = src[s][rank][i]
+//   PULL_REDUCE_SCATTER  (N chunks per source): out[i]    = sum over s (rank order, fp32) of src[s][rank][i], bf16
+enum { PULL_ALL_GATHER = 0, PULL_ALL_TO_ALL = 1, PULL_REDUCE_SCATTER = 2 };
+
+struct PullParams {
+  const uint4* src[MAXP];
+  uint4* out;
+  const int* flags;       // [n_src] local flag words, written by the peers
+  const int* epoch;       // epoch the flags must have reached (this rank's own publish count)
+  int* status;
+  unsigned long long budget_ns;
+  long long chunk_vec;
+  int n_src, rank, mode;
+};
+
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4 v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+}
+
+__global__ void __launch_bounds__(256) pull_collective_kernel(const PullParams p) {
+  __shared__ int wait_failed;
+  if (threadIdx.x == 0) wait_failed = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < p.n_src) {
+    const bool poisoned = p.status != nullptr && *(volatile int*)p.status == ST_TIMEOUT_PEER_FLAG;
+    if (poisoned || !wait_flag_ge(p.flags + threadIdx.x, *p.epoch, p.budget_ns)) {
+      report_status(p.status, ST_TIMEOUT_PEER_FLAG, threadIdx.x);
+      wait_failed = 1;
+    }
+  }
+  __syncthreads();
+  if (wait_failed) return;   // the output keeps its old contents; the host reads the status word
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long own = p.mode == PULL_ALL_GATHER ? 0 : (long long)p.rank * p.chunk_vec;
+  if (p.mode == PULL_REDUCE_SCATTER) {
+    for (long long i = first; i < p.chunk_vec; i += stride) {
+      uint4 v[MAXP];
+#pragma unroll
+      for (int s = 0; s < MAXP; ++s)
+        if (s < p.n_src) v[s] = p.src[s][own + i];          // all sources in flight before the first add
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < MAXP; ++s)
+        if (s < p.n_src) add_bf16x8(acc, v[s]);
+      uint4 o;
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ob[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      p.out[i] = o;
+    }
+  } else {
+    for (long long i = first; i < p.chunk_vec; i += stride) {
+      uint4 v[MAXP];
+#pragma unroll
+      for (int s = 0; s < MAXP; ++s)
+        if (s < p.n_src) v[s] = p.src[s][own + i];
+#pragma unroll
+      for (int s = 0; s < MAXP; ++s)
+        if (s < p.n_src) p.out[(long long)s * p.chunk_vec + i] = v[s];
+    }
+  }
+}
+
 // A wait that nothing satisfies within its budget: used to test the timeout path without a fault.
 __global__ void wait_flag_kernel(const int* flag, int epoch, unsigned long long budget_ns, int* status) {
   if (!wait_flag_ge(flag, epoch, budget_ns)) report_status(status, ST_TIMEOUT_PEER_FLAG, 0);
@@ -149,6 +223,30 @@ extern "C" int skein_publish_rows(const void* src, long long bytes, void* dst_lo
   if (grid < 1) grid = 1;
   publish_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst_local, n_vec, pp, epoch,
                                                              done_counter);
+  return (int)cudaGetLastError();
+}
+
+// src_ptrs[s]: rank s's published buffer as mapped here; chunk_bytes: size of one chunk (a multiple of 16).
+extern "C" int skein_pull_collective(int mode, const void* const* src_ptrs, int n_src, int rank, long long chunk_bytes,
+                                     void* out, const int* flags, const int* epoch, int* status, int budget_ms,
+                                     void* stream) {
+  using namespace skein;
+  if (n_src < 1 || n_src > MAXP || rank < 0 || rank >= n_src || chunk_bytes % 16 != 0 || mode < 0 || mode > 2) return -1;
+  if (chunk_bytes == 0) return 0;
+  PullParams p;
+  for (int s = 0; s < MAXP; ++s) p.src[s] = s < n_src ? (const uint4*)src_ptrs[s] : nullptr;
+  p.out = (uint4*)out;
+  p.flags = flags;
+  p.epoch = epoch;
+  p.status = status;
+  p.budget_ns = (unsigned long long)(budget_ms > 0 ? budget_ms : 10000) * 1000000ull;
+  p.chunk_vec = chunk_bytes / 16;
+  p.n_src = n_src;
+  p.rank = rank;
+  p.mode = mode;
+  long long grid = (p.chunk_vec + 255) / 256;
+  if (grid > 592) grid = 592;   // 4 CTAs per SM: enough loads in flight to cover the NVLink round trip
+  pull_collective_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(p);
   return (int)cudaGetLastError();
 }
 

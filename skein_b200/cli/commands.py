@@ -189,25 +189,24 @@ def bench_collectives(emit, args) -> int:
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     hidden = 4096
     comm = TPComm(dist.group.WORLD, dev, hidden=hidden, fused_rows=512, mode="fused")
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) * 1e3 / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
     rows_out = []
     for rows in (16, 64, 128, 256, 512):
         x = torch.randn(rows, hidden, device=dev).bfloat16()
-
-        def timed(fn, n=20):
-            for _ in range(3):
-                fn()
-            dist.barrier()
-            torch.cuda.synchronize()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            for _ in range(n):
-                fn()
-            e.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([s.elapsed_time(e) * 1e3 / n], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t[0])
-
         y = x.clone()
         fused_us = timed(lambda: comm.all_reduce(x))
         nccl_us = timed(lambda: dist.all_reduce(y))
@@ -222,12 +221,34 @@ def bench_collectives(emit, args) -> int:
         graph_us = timed(g.replay, n=5) / 20
         rows_out.append({"rows": rows, "bytes": rows * hidden * 2, "fused_eager_us": round(fused_us, 2),
                          "fused_graph_us": round(graph_us, 2), "nccl_eager_us": round(nccl_us, 2)})
+    # the other pull collectives at one decode-sized message (64 rows per rank): in a CUDA graph vs the library, eager
+    others = {}
+    rows = 64 * world
+    x = torch.randn(rows, hidden, device=dev).bfloat16()
+    shard = x[:64].contiguous()
+    lib_out = {"all_gather": torch.empty(rows, hidden, device=dev, dtype=torch.bfloat16),
+               "reduce_scatter": torch.empty(64, hidden, device=dev, dtype=torch.bfloat16), "all_to_all": torch.empty_like(x)}
+    cases = {"all_gather": (lambda: comm.all_gather(shard), lambda: dist.all_gather_into_tensor(lib_out["all_gather"], shard)),
+             "reduce_scatter": (lambda: comm.reduce_scatter(x), lambda: dist.reduce_scatter_tensor(lib_out["reduce_scatter"], x)),
+             "all_to_all": (lambda: comm.all_to_all(x), lambda: dist.all_to_all_single(lib_out["all_to_all"], x))}
+    for name, (ours, lib) in cases.items():
+        ours()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                ours()
+        others[name] = {"rows_per_rank": 64, "pull_graph_us": round(timed(g.replay, n=5) / 20, 2),
+                        "pull_eager_us": round(timed(ours), 2), "nccl_eager_us": round(timed(lib), 2)}
     torch.cuda.synchronize()
     ops.workspace().check_status()
     if dist.get_rank() == 0:
-        emit(args, {"world": world, "hidden": hidden, "all_reduce": rows_out},
-             "\n".join(f"{r['rows']:4d} rows ({r['bytes']} B): fused {r['fused_eager_us']} us eager / {r['fused_graph_us']} us "
-                       f"in a CUDA graph, nccl {r['nccl_eager_us']} us eager" for r in rows_out))
+        emit(args, {"world": world, "hidden": hidden, "all_reduce": rows_out, **others},
+             "\n".join([f"{r['rows']:4d} rows ({r['bytes']} B): fused {r['fused_eager_us']} us eager / {r['fused_graph_us']} us "
+                        f"in a CUDA graph, nccl {r['nccl_eager_us']} us eager" for r in rows_out]
+                       + [f"{k}: pull {v['pull_eager_us']} us eager / {v['pull_graph_us']} us in a CUDA graph, nccl "
+                          f"{v['nccl_eager_us']} us eager" for k, v in others.items()]))
     dist.barrier()
     comm.close()
     dist.destroy_process_group()

@@ -99,6 +99,7 @@ def lib():
     _sig(L, "skein_ipc_close", i32, [vp])
     _sig(L, "skein_ipc_handle_bytes", i32, [])
     _sig(L, "skein_publish_rows", i32, [vp, i64, vp, pvp, i32, vp, vp, vp])
+    _sig(L, "skein_pull_collective", i32, [i32, pvp, i32, i32, i64, vp, vp, vp, vp, i32, vp])
     _sig(L, "skein_argmax_push", i32, [vp, i64, i32, i32, i32, pvp, pvp, pvp, i32, vp, vp, vp])
     _sig(L, "skein_copy_pages", i32, [vp, vp, vp, vp, i32, i64, vp])
     _sig(L, "skein_wait_flag", i32, [vp, i32, i32, vp, vp])

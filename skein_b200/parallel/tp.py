@@ -16,6 +16,11 @@ all-reduce k; so nobody overwrites a buffer that is still being read.
 NCCL mode (large prefill chunks, or SKEIN_COMM=nccl as the un-fused baseline): the same math with
 a library all-reduce between the local GEMM and the reduce kernel.
 
+The stand-alone collectives (all_reduce, all_gather, reduce_scatter, all_to_all) are the same two steps
+without a GEMM in front: copy into the published buffer and raise the flags, then one pull kernel
+(csrc/kernels/comm.cu) that reads the chunks this rank needs out of every peer's buffer. Messages
+larger than the buffer go through the library.
+
 Greedy sampling is vocabulary-parallel: each rank reduces its logit shard to one candidate per row
 and pushes 8 bytes per row to every peer.
 
@@ -138,6 +143,64 @@ class TPComm:
         out, _ = ops.reduce_residual_rmsnorm(None, self._partials(b, rows), None, 0.0,
                                              wait_budget_ms=self.wait_budget_ms)
         return out
+
+    # ---- all-gather / reduce-scatter / all-to-all ----------------------------------------------------
+    _PULL_ALL_GATHER, _PULL_ALL_TO_ALL, _PULL_REDUCE_SCATTER = 0, 1, 2
+
+    def _publish_and_pull(self, x: torch.Tensor, mode: int, chunk_bytes: int, out: torch.Tensor) -> torch.Tensor:
+        """Copy `x` into this rank's peer-mapped buffer, raise the flags, and pull what `mode` says from every rank."""
+        b = self.cur
+        self.cur ^= 1
+        L = _lib.lib()
+        _lib.check(L.skein_publish_rows(x.data_ptr(), x.numel() * x.element_size(), self.bufs[b].data_ptr(), self._push_flag[b],
+                                        self.size, self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
+                                        _lib.stream_ptr()), "publish_rows")
+        _lib.check(L.skein_pull_collective(mode, self._src_ptrs[b], self.size, self.rank, chunk_bytes, out.data_ptr(),
+                                           self.flags[b].data_ptr(), self.epochs[b:b + 1].data_ptr(),
+                                           ops.workspace().status.data_ptr(), self.wait_budget_ms, _lib.stream_ptr()),
+                   "pull_collective")
+        _lib.count_launch(2)
+        return out
+
+    def _pull_ok(self, x: torch.Tensor, chunk_bytes: int) -> bool:
+        nbytes = x.numel() * x.element_size()
+        return (self.mode == "fused" and x.is_cuda and 0 < nbytes <= self.bufs[0].numel() * 2 and nbytes % 16 == 0
+                and chunk_bytes % 16 == 0)
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """[rows, ...] on every rank -> [N * rows, ...] in rank order (any dtype; a byte copy)."""
+        x = x.contiguous()
+        out = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        nbytes = x.numel() * x.element_size()
+        if not self._pull_ok(x, nbytes):
+            dist.all_gather_into_tensor(out, x, group=self.group)
+            return out
+        return self._publish_and_pull(x, self._PULL_ALL_GATHER, nbytes, out)
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """[N * rows, W] bf16 partials on every rank -> this rank's [rows, W] block of the sum over ranks
+        (fp32 accumulation in rank order, so every run gives the same bits)."""
+        x = x.contiguous()
+        if x.shape[0] % self.size != 0:
+            raise ValueError(f"reduce_scatter: {x.shape[0]} rows do not divide into {self.size} ranks")
+        out = torch.empty((x.shape[0] // self.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        chunk = x.numel() * x.element_size() // self.size
+        if x.dtype != torch.bfloat16 or not self._pull_ok(x, chunk):
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+            return out
+        return self._publish_and_pull(x, self._PULL_REDUCE_SCATTER, chunk, out)
+
+    def all_to_all(self, x: torch.Tensor) -> torch.Tensor:
+        """[N * rows, ...]: block d goes to rank d; returns [N * rows, ...] whose block s came from rank s."""
+        x = x.contiguous()
+        if x.shape[0] % self.size != 0:
+            raise ValueError(f"all_to_all: {x.shape[0]} rows do not divide into {self.size} ranks")
+        out = torch.empty_like(x)
+        chunk = x.numel() * x.element_size() // self.size
+        if not self._pull_ok(x, chunk):
+            dist.all_to_all_single(out, x, group=self.group)
+            return out
+        return self._publish_and_pull(x, self._PULL_ALL_TO_ALL, chunk, out)
 
     # ---- vocabulary-parallel greedy sampling ----------------------------------------------------------
     def vocab_parallel_argmax(self, logits: torch.Tensor, v_local: int) -> torch.Tensor:

@@ -54,6 +54,12 @@ def test_tp2_ep2_fused():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pull_collectives_match_the_library():
+    """all-gather, reduce-scatter, all-to-all and all-reduce as publish + one pull kernel over peer memory."""
+    _run(min(torch.cuda.device_count(), 4), port=29548, worker="coll_worker.py", ok="COLL_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_pp2_gpu(tmp_path):
     """Two pipeline stages on two GPUs (NCCL point-to-point of the residual stream, token feedback, micro-batched
     pipelined decode) produce exactly the single-stage tokens. See workers/pp_worker.py."""
