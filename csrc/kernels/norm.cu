@@ -12,7 +12,8 @@
 //   residual_out[b, h] = bf16(acc[h])
 //   normed_out[b, h]   = bf16(residual_out[b, h] * rsqrt(mean(residual_out^2) + eps) * gamma[h])
 // When sources are other GPUs the kernel first waits (bounded) until every source's flag has
-// reached this buffer's current epoch, then reads the peers' buffers with plain loads.
+// reached this buffer's current epoch, then reads the peers' buffers with plain loads, or, when the
+// buffers are bound to an NVLink multicast object, with one in-switch reducing load per 16 bytes.
 //
 // Replaces the reference's unfused rms_norm graph (crates/skein_emit/src/op_wiring.rs:1787), its
 // elementwise residual adds and the NCCL all-reduce + copy-back
@@ -30,6 +31,9 @@ struct NormParams {
   const __nv_bfloat16* src_base[8];  // with use_ptrs: source s is the [rows][H] buffer at src_base[s] (a peer's memory,
                                    // read over NVLink) instead of partial + s * src_stride
   int use_ptrs;
+  const __nv_bfloat16* mc_base;    // non-null: the multicast mapping of the same [rows][H] buffer on all n_src ranks; the
+                                   // sum over ranks then is ONE multimem.ld_reduce per 16 bytes (added inside the
+                                   // NVSwitch, fp32 accumulation) instead of n_src peer loads
   const int* row_idx;              // [B, topk] rows into partial, or null (row = b)
   const float* row_w;              // [B, topk] weights, or null
   const int* owner_ids;            // [B, topk] expert id of each pair, or null: with it only the sources that own the
@@ -119,6 +123,13 @@ __device__ __forceinline__ bool reduce_norm_row(const NormParams& p, const int b
           s_lo = (own8[j] / p.experts_per_owner) * p.owner_span;
           s_hi = s_lo + p.owner_span;
           if (s_lo < 0 || s_hi > p.n_src) continue;
+        }
+        if (p.mc_base != nullptr && p.owner_ids == nullptr) {
+          const uint4 r = multimem_ld_reduce_add_bf16x8(p.mc_base + (size_t)row * p.H + h);
+          const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(rb[i]); a[2 * i] += w * f.x; a[2 * i + 1] += w * f.y; }
+          continue;
         }
         // sources in batches of 8: every load of a batch is issued before the first is consumed (the partials of
         // 8 tensor-parallel ranks would otherwise cost 8 dependent round trips); the sum order stays s_lo..s_hi
@@ -370,13 +381,14 @@ extern "C" int skein_reduce_residual_rmsnorm(
     const void* residual, const void* partial, const int* row_idx, const float* row_w, const void* gamma,
     void* residual_out, void* normed_out, const int* flags, const int* epoch, int* status,
     long long src_stride, int B, int H, int n_src, int topk, float eps, int wait_budget_ms, const int* owner_ids,
-    int experts_per_owner, int owner_span, const void* const* src_ptrs, void* stream) {
+    int experts_per_owner, int owner_span, const void* const* src_ptrs, const void* mc_base, void* stream) {
   using namespace skein;
   if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0 || topk > 8) return -1;
   if (src_ptrs != nullptr && (n_src < 1 || n_src > 8)) return -1;
   if (B == 0) return 0;
   NormParams p;
   p.use_ptrs = src_ptrs != nullptr;
+  p.mc_base = p.use_ptrs ? (const __nv_bfloat16*)mc_base : nullptr;
   for (int i = 0; i < 8; ++i) p.src_base[i] = (p.use_ptrs && i < n_src) ? (const __nv_bfloat16*)src_ptrs[i] : nullptr;
   p.residual = (const __nv_bfloat16*)residual; p.partial = (const __nv_bfloat16*)partial;
   p.row_idx = row_idx; p.row_w = row_w; p.gamma = (const __nv_bfloat16*)gamma;
@@ -402,7 +414,7 @@ extern "C" int skein_reduce_norm_route(
     const int* flags, const int* epoch, int* status, long long src_stride, int B, int H, int n_src, float eps,
     int wait_budget_ms, const void* wg, int E, int topk, int e_first, int e_count, int* expert_ids, float* expert_w,
     int* counts, int* offsets, int* row_of, int* src_token, void* xs, int* barrier, int max_resident_ctas,
-    const void* const* src_ptrs, void* stream) {
+    const void* const* src_ptrs, const void* mc_base, void* stream) {
   using namespace skein;
   if (H % 8 != 0 || H > 4 * 512 * 8 || B < 0) return -1;
   if (B == 0) return 0;
@@ -412,6 +424,7 @@ extern "C" int skein_reduce_norm_route(
   if (src_ptrs != nullptr && (n_src < 1 || n_src > 8)) return -1;
   NormParams p;
   p.use_ptrs = src_ptrs != nullptr;
+  p.mc_base = p.use_ptrs ? (const __nv_bfloat16*)mc_base : nullptr;
   for (int i = 0; i < 8; ++i) p.src_base[i] = (p.use_ptrs && i < n_src) ? (const __nv_bfloat16*)src_ptrs[i] : nullptr;
   p.residual = (const __nv_bfloat16*)residual; p.partial = (const __nv_bfloat16*)partial;
   p.row_idx = nullptr; p.row_w = nullptr; p.gamma = (const __nv_bfloat16*)gamma;

@@ -223,6 +223,15 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* p) {
   asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Sum over all GPUs of a multicast group of the 8 bf16 values at a multicast address: the NVSwitch reads every
+// GPU's copy, adds in fp32 and returns bf16. The data must have been made visible before (flag acquire).
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+
 // Wait until *flag >= epoch (epochs only grow). Bounded by `budget_ns`.
 __device__ __forceinline__ bool wait_flag_ge(const int* flag, int epoch, uint64_t budget_ns) {
   if (ld_acquire_sys(flag) - epoch >= 0) return true;

@@ -67,10 +67,10 @@ def lib():
     _sig(L, "skein_gemm_ws_workspace_bytes", i64, [C.POINTER(GemmParams)])
     _sig(L, "skein_sm_count", i32, [])
     _sig(L, "skein_reduce_residual_rmsnorm", i32,
-         [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, i32, vp, i32, i32, vp, vp])
+         [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, i32, vp, i32, i32, vp, vp, vp])
     _sig(L, "skein_reduce_norm_route", i32,
          [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, f32, i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
-          vp, vp, i32, vp, vp])
+          vp, vp, i32, vp, vp, vp])
     _sig(L, "skein_rope_kv_append", i32,
          [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp])
     _sig(L, "skein_embed_gather", i32, [vp, vp, vp, i32, i32, i32, i32, vp])

@@ -266,14 +266,15 @@ def grouped_linear(xs, w, counts, offsets, swiglu=False, out=None, n_tile=None, 
 
 
 def _partial_args(partial, flags, epoch):
-    """(data pointer, source stride, n_src, per-source pointer array or None, flags, epoch) of a partial-sum operand:
-    a [n_src, rows, H] tensor, or peer partials (parallel/tp.py: one peer-mapped [rows, H] buffer per rank, pulled
-    over NVLink by the kernel)."""
+    """(data pointer, source stride, n_src, per-source pointer array or None, multicast address or None, flags, epoch)
+    of a partial-sum operand: a [n_src, rows, H] tensor, or peer partials (parallel/tp.py: one peer-mapped [rows, H]
+    buffer per rank, pulled over NVLink by the kernel, through the multicast mapping when there is one)."""
     if partial is None:
-        return None, 0, 0, None, flags, epoch
+        return None, 0, 0, None, None, flags, epoch
     if hasattr(partial, "ptrs"):
-        return partial.local.data_ptr(), 0, partial.n_src, partial.ptrs, partial.flags, partial.epoch
-    return partial.data_ptr(), partial.stride(0), partial.shape[0], None, flags, epoch
+        return (partial.local.data_ptr(), 0, partial.n_src, partial.ptrs, getattr(partial, "mc", 0) or None, partial.flags,
+                partial.epoch)
+    return partial.data_ptr(), partial.stride(0), partial.shape[0], None, None, flags, epoch
 
 
 def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=None, residual_out=None,
@@ -291,7 +292,7 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
         residual_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
     if normed_out is None and gamma is not None:
         normed_out = torch.empty(B, H, dtype=torch.bfloat16, device=src.device)
-    pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
+    pptr, src_stride, n_src, ptrs, mc, flags, epoch = _partial_args(partial, flags, epoch)
     if peer and wait_budget_ms == 0:
         wait_budget_ms = partial.wait_budget_ms
     topk = row_idx.shape[1] if row_idx is not None else 0
@@ -300,7 +301,7 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
         _lib.ptr(residual), pptr, _lib.ptr(row_idx), _lib.ptr(row_w), _lib.ptr(gamma),
         _lib.ptr(residual_out), _lib.ptr(normed_out), _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(),
         src_stride, B, H, n_src, topk, float(eps), wait_budget_ms, _lib.ptr(owner_ids), experts_per_owner, owner_span,
-        ptrs, _lib.stream_ptr())
+        ptrs, mc, _lib.stream_ptr())
     _lib.check(rc, "reduce_residual_rmsnorm")
     _lib.count_launch()
     return residual_out, normed_out
@@ -339,7 +340,7 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
     counts, offsets = meta[:E], meta[E:2 * E + 1]
     row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
     xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev)
-    pptr, src_stride, n_src, ptrs, flags, epoch = _partial_args(partial, flags, epoch)
+    pptr, src_stride, n_src, ptrs, mc, flags, epoch = _partial_args(partial, flags, epoch)
     if peer and wait_budget_ms == 0:
         wait_budget_ms = partial.wait_budget_ms
     ws = workspace()
@@ -348,7 +349,7 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
         _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(), src_stride, T, H, n_src, float(eps), wait_budget_ms,
         wg.data_ptr(), E, topk, e_first, e_count, ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
         row_of.data_ptr(), src_token.data_ptr(), xs.data_ptr(), ws.route_barrier.data_ptr(), ws.sm_count,
-        ptrs, _lib.stream_ptr())
+        ptrs, mc, _lib.stream_ptr())
     _lib.check(rc, "reduce_norm_route")
     _lib.count_launch()
     return residual_out, normed_out, ids, w, counts, offsets, row_of, src_token, xs

@@ -45,15 +45,16 @@ class PeerPartials:
     """Operand of the reduce kernels: rank s's partial result is the [rows, H] buffer at ptrs[s] (peer-mapped
     memory), complete once flags[s] has reached the device-side epoch."""
 
-    def __init__(self, local, ptrs, n_src, flags, epoch, wait_budget_ms=0):
+    def __init__(self, local, ptrs, n_src, flags, epoch, wait_budget_ms=0, mc=0):
         self.local, self.ptrs, self.n_src, self.flags, self.epoch = local, ptrs, n_src, flags, epoch
+        self.mc = mc                           # multicast address of the same buffer on all ranks (0: none)
         self.rows = local.shape[0]
         self.wait_budget_ms = wait_budget_ms   # how long the consumer waits for a peer's flag (0: kernel default)
 
 
 class TPComm:
     def __init__(self, group, device, hidden: int, fused_rows: int = 512, max_batch: int = 256, mode: str | None = None,
-                 wait_budget_ms: int = 10000):
+                 wait_budget_ms: int = 10000, multimem: bool | None = None):
         self.group, self.device = group, device
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
         self.hidden, self.fused_rows, self.max_batch = hidden, fused_rows, max_batch
@@ -62,7 +63,11 @@ class TPComm:
         N = self.size
         buf_bytes = fused_rows * hidden * 2
         heap_bytes = 2 * buf_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
-        self.heap = SymmetricHeap(group, device, heap_bytes)
+        # In-switch reduction (SKEIN_MULTIMEM=1): the heap is bound to an NVLink multicast object and the reduce
+        # kernels sum the ranks' partials with one multimem load. Off by default: a rank that dies while bound
+        # faults its peers, and the plain peer loads are what the failure-handling tests exercise.
+        self.multimem = (os.environ.get("SKEIN_MULTIMEM", "0") == "1") if multimem is None else bool(multimem)
+        self.heap = SymmetricHeap(group, device, heap_bytes, multicast=self.multimem and self.mode == "fused")
         h = self.heap
         self.buf_off = [h.alloc(buf_bytes) for _ in range(2)]
         self.flag_off = [h.alloc(256) for _ in range(2)]
@@ -89,7 +94,7 @@ class TPComm:
 
     def _partials(self, b: int, rows: int) -> PeerPartials:
         return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1],
-                            self.wait_budget_ms)
+                            self.wait_budget_ms, mc=self.heap.mc_addr(self.buf_off[b]))
 
     # ---- row-parallel projection + all-reduce ------------------------------------------------------
     def _fused_ok(self, rows: int) -> bool:

@@ -31,6 +31,12 @@ def test_tp2_nccl_baseline_mode():
     _run(2, {"SKEIN_COMM": "nccl"}, port=29542)
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_in_switch_reduction():
+    """The same checks with the partials summed inside the NVSwitch (multimem.ld_reduce on a multicast mapping)."""
+    _run(2, {"SKEIN_MULTIMEM": "1"}, port=29549, ok="multimem 1")
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp4_fused():
     _run(4, port=29543)

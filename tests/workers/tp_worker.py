@@ -177,10 +177,23 @@ def main():
     assert not hard and len(diffs) <= 4, ("(step, seq, got, want, reference top-2 gap)", diffs, "router tie from", tie_from)
     dist.barrier()
     if rank == 0:
-        print("TP_WORKER_OK world", world, "mode", comm.mode)
+        print("TP_WORKER_OK world", world, "mode", comm.mode, "multimem", int(comm.heap.mc_ptr != 0))
     comm.close()
     dist.destroy_process_group()
 
 
 if __name__ == "__main__":
-    main()
+    if os.environ.get("SKEIN_MULTIMEM") == "1":
+        # A rank must not leave while its heap is bound to the multicast object and a peer may still read through the
+        # switch: on a failure, stay alive until the peers' bounded waits (10 s) have run out, then report.
+        try:
+            main()
+        except BaseException:
+            import time
+            import traceback
+            traceback.print_exc()
+            sys.stdout.flush()
+            time.sleep(15)
+            os._exit(1)
+    else:
+        main()
