@@ -157,6 +157,39 @@ def op_router(a):
     return fn, (x.numel() + wg.numel()) * 2, 2 * a.tokens * 8 * 4096
 
 
+def op_attn_prefill(tp, a):
+    """Causal prefill attention over the paged cache: 16 prompts of --ctx tokens in one launch."""
+    S, L, Hq, Hkv, D = 16, a.ctx, 32 // tp, max(1, 8 // tp), 128
+    nb = (L + 15) // 16
+    kv = _bf(S * nb + 1, 2, Hkv, 16, D, std=1.0)
+    bt = torch.arange(S * nb, dtype=torch.int32, device="cuda").view(S, nb) + 1
+    q = _bf(S * L, Hq * D, std=1.0)
+    out = torch.empty_like(q)
+    q_start = torch.arange(S, dtype=torch.int32, device="cuda") * L
+    q_len = torch.full((S,), L, dtype=torch.int32, device="cuda")
+    fn = lambda: ops.attn_prefill(q, kv, bt, q_start, q_len, q_len, L, Hq, Hkv, D, out=out)
+    return fn, (2 * q.numel() + S * L * 2 * Hkv * D) * 2, 4 * Hq * D * S * L * (L + 1) // 2
+
+
+def op_prefill_gemm(tp, a):
+    """The qkv projection at prefill size (8192 tokens): the compute-bound regime of the same GEMM kernel."""
+    T, F, K = 8192, (32 + 16) * 128 // tp, 4096
+    x, w = _bf(T, K, std=1.0), _bf(F, K)
+    out = torch.empty(T, F, dtype=torch.bfloat16, device="cuda")
+    return (lambda: ops.linear(x, w, out=out)), (w.numel() + x.numel() + out.numel()) * 2, 2 * T * F * K
+
+
+def op_argmax(tp, a):
+    logits = _bf(a.tokens, 32000 // tp, std=1.0)
+    out = torch.empty(a.tokens, dtype=torch.int32, device="cuda")
+    return (lambda: ops.sample_argmax(logits, out=out)), logits.numel() * 2, logits.numel()
+
+
+def op_quant_fp8(a):
+    x = _bf(16384, 4096, std=1.0)
+    return (lambda: ops.quant_fp8_block128(x)), x.numel() * 3 + x.numel() // 128 * 4, 2 * x.numel()
+
+
 def build(name, a):
     tp = a.tp
     if name == "moe_gate_up":
@@ -177,10 +210,19 @@ def build(name, a):
         return op_router(a)
     if name == "reduce_route":
         return op_reduce_route(a)
+    if name == "attn_prefill":
+        return op_attn_prefill(tp, a)
+    if name == "prefill_qkv":
+        return op_prefill_gemm(tp, a)
+    if name == "argmax":
+        return op_argmax(tp, a)
+    if name == "quant_fp8":
+        return op_quant_fp8(a)
     raise SystemExit(f"unknown op {name}")
 
 
-OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "reduce_route", "router")
+OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "reduce_route", "router",
+       "attn_prefill", "prefill_qkv", "argmax", "quant_fp8")
 
 
 def main(argv=None):

@@ -27,7 +27,7 @@ def _check_status():
 
 
 @pytest.mark.parametrize("T,F,K", [(64, 256, 512), (1, 128, 64), (17, 384, 4096), (64, 6144, 4096),
-                                    (200, 1000, 1024), (513, 4096, 512)])
+                                    (200, 1000, 1024), (513, 4096, 512), (1000, 3200, 512)])
 def test_linear(T, F, K):
     torch.manual_seed(0)
     x = torch.randn(T, K, device=DEV).bfloat16()
