@@ -113,7 +113,7 @@ def _gemm_launch(p: "_lib.GemmParams", what: str, cfg: dict | None = None):
         # The estimate assumes one token tile per group (decode); a wrong guess only changes the split.
         rows = p.t_static if not p.group_cnt else p.n_tile
         units = p.G * ((p.F + 127) // 128) * max(1, (rows + p.n_tile - 1) // p.n_tile)
-        p.grid = tuning.heuristic_grid(units, p.K // (128 if p.fp8 else 64), ws.sm_count)
+        p.grid = tuning.heuristic_grid(units, p.K // (128 if p.fp8 else 64), ws.sm_count, dual=(p.mode == 1))
     _lib.check(_lib.lib().skein_gemm_ws(C.byref(p), _lib.stream_ptr()), what)
     _lib.count_launch()
 

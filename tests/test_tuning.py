@@ -88,4 +88,6 @@ def test_heuristic_grid_whole_tiles_only_when_they_waste_little():
     assert tuning.heuristic_grid(256, 112, 148) == 0       # 2 ranks: the idle SM time costs more than the fix-up
     assert tuning.heuristic_grid(256, 224, 148) == 0       # 1 GPU, K = 14336
     assert tuning.heuristic_grid(250, 64, 148) == 125      # lm_head, 32000 x 4096
+    assert tuning.heuristic_grid(224, 64, 148) == 0        # 31 idle K-blocks per CTA ...
+    assert tuning.heuristic_grid(224, 64, 148, dual=True) == 112   # ... but the two-accumulator kernel keeps whole tiles
     assert tuning.heuristic_grid(100, 64, 148) == 0 and tuning.heuristic_grid(896, 64, 148) == 0   # outside (SMs, 2 SMs]
