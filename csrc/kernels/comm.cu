@@ -30,8 +30,7 @@ namespace skein {
 constexpr int MAXP = 8;
 
 struct PeerPtrs {
-  void* dst[MAXP];
-  int* flag[MAXP];
+  int* flag[MAXP];   // this rank's flag word on every rank of the group (its own included)
   int n;
 };
 
@@ -216,7 +215,7 @@ extern "C" int skein_publish_rows(const void* src, long long bytes, void* dst_lo
   if (bytes % 16 != 0 || n_peers < 1 || n_peers > MAXP) return -1;
   PeerPtrs pp;
   pp.n = n_peers;
-  for (int i = 0; i < n_peers; ++i) { pp.dst[i] = nullptr; pp.flag[i] = peer_flag[i]; }
+  for (int i = 0; i < n_peers; ++i) pp.flag[i] = peer_flag[i];
   const long long n_vec = bytes / 16;
   int grid = (int)((n_vec + 255) / 256);
   if (grid > 296) grid = 296;
@@ -259,7 +258,7 @@ extern "C" int skein_argmax_push(const void* logits, long long ld, int B, int V,
   CandPtrs cp;
   PeerPtrs pp;
   pp.n = n_peers;
-  for (int i = 0; i < n_peers; ++i) { cp.val[i] = peer_val[i]; cp.idx[i] = peer_idx[i]; pp.flag[i] = peer_flag[i]; pp.dst[i] = nullptr; }
+  for (int i = 0; i < n_peers; ++i) { cp.val[i] = peer_val[i]; cp.idx[i] = peer_idx[i]; pp.flag[i] = peer_flag[i]; }
   argmax_push_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V, idx_offset, cp, pp,
                                                            epoch, done_counter);
   return (int)cudaGetLastError();
