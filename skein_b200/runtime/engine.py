@@ -70,6 +70,7 @@ class Engine:
         self.clock = clock or (lambda: int(time.monotonic() * 1000))
         self._next_id = 1
         self._step = 0
+        self._graph_seen = (0, 0)   # runner.graph_captures / graph_replays already added to the metrics
         self._last = {}          # request id -> last sampled token (input of its next decode step)
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
 
@@ -106,10 +107,23 @@ class Engine:
                 self._last.pop(ev.request_id, None)
                 self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
             self.metrics.count("skein_step_failures_total")
+            if "peer flag" in str(e):     # a bounded device wait on another rank ran out (ops.Workspace.check_status)
+                self.metrics.count("skein_comm_timeout_total")
+        self._count_graph_activity()
         us = (time.perf_counter() - t0) * 1e6
         self.metrics.record_step(self._step, len(decode) + len(prefill), us, 0.0, self.kv.in_use_pages)
         self._step += 1
         return events
+
+    def _count_graph_activity(self) -> None:
+        """skein_graph_captures_total / skein_graph_replays_total follow the runner's CUDA-graph counters."""
+        cap, rep = getattr(self.runner, "graph_captures", 0), getattr(self.runner, "graph_replays", 0)
+        seen_cap, seen_rep = self._graph_seen
+        if cap > seen_cap:
+            self.metrics.count("skein_graph_captures_total", cap - seen_cap)
+        if rep > seen_rep:
+            self.metrics.count("skein_graph_replays_total", rep - seen_rep)
+        self._graph_seen = (cap, rep)
 
     def _run(self, prefill, decode, now) -> list[TokenEvent]:
         events: list[TokenEvent] = []

@@ -78,6 +78,20 @@ def test_failing_step_retires_batch_and_engine_keeps_serving_cpu():
     assert "skein_step_failures_total 1" in eng.metrics.render()
     eng.failure_injector = None
     assert len(eng.generate([[5, 6, 7]], 3)[0]) == 3           # still serving
+    assert "skein_comm_timeout_total" not in eng.metrics.render()
+
+    # a peer wait that ran out surfaces as a step failure AND as a communication time-out; graph counters follow the runner
+    def lost_peer(step):
+        raise RuntimeError("kernel status 5 (a peer flag never reached its epoch), detail 1")
+    eng.failure_injector = lost_peer
+    eng.submit([1, 2, 3], 2)
+    eng.run_until_done()
+    eng.failure_injector = None
+    assert "skein_comm_timeout_total 1" in eng.metrics.render() and "skein_step_failures_total 2" in eng.metrics.render()
+    eng.runner.graph_captures, eng.runner.graph_replays = 2, 7    # what a CUDA-graph runner would have counted
+    eng.generate([[9, 8, 7]], 2)
+    text = eng.metrics.render()
+    assert "skein_graph_captures_total 2" in text and "skein_graph_replays_total 7" in text
 
 
 @pytest.mark.gpu
