@@ -118,7 +118,7 @@ def cmd_serve(args, emit) -> int:
         argv += ["--demo-prompts", "The quick brown fox|Blackwell tensor cores|Paged attention is"]
     if launcher.world_from_env() is None and args.gpus:
         gpus = launcher.parse_gpus(args.gpus)
-        failed = launcher.launch_ranks(gpus, args.rendezvous, argv)
+        failed = launcher.launch_ranks(gpus, args.rendezvous, argv, restarts=max(0, args.restarts))
         emit(args, {"ranks": len(gpus), "failed": failed}, f"{len(gpus)} ranks finished, {failed} failed")
         return 1 if failed else 0
     return worker.run_rank(worker.parse(argv))

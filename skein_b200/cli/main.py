@@ -76,6 +76,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--prompt", default=None)
     s.add_argument("--max-new-tokens", type=int, default=32)
     s.add_argument("--rendezvous", default="/tmp/skein_rendezvous")
+    s.add_argument("--restarts", type=int, default=0,
+                   help="with --gpus: start the whole rank group again, up to this many times, after a rank was lost")
     s.add_argument("--batch-demo", action="store_true")
     s.add_argument("--demo-prompts", default=None)
     s.add_argument("--cuda-graphs", action="store_true", default=True)

@@ -4,7 +4,8 @@ The parent computes one command per rank (environment: SKEIN_RANK, SKEIN_WORLD_S
 CUDA_VISIBLE_DEVICES, SKEIN_LOCAL_DEVICE), spawns them, waits, and reports how many failed. Every rank sees all
 GPUs of the job, in job order, and computes on the one at index SKEIN_LOCAL_DEVICE: the tensor-parallel kernels read
 the peers' buffers through CUDA IPC mappings, which can only be opened for a device the process can see. If one
-rank dies, the others get a grace period and are then terminated, so a job never outlives a lost rank. Ranks meet through a file
+rank dies, the others get a grace period and are then terminated, so a job never outlives a lost rank; with
+`restarts` the whole group is then started again from the artifact (the ranks hold no other state). Ranks meet through a file
 rendezvous: the leader publishes a small blob atomically (tmp + rename), the others poll for it with a
 timeout and get a clear error if it never appears. torch.distributed is then initialised from the
 address carried in the blob.
@@ -103,16 +104,37 @@ def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, pol
     return codes
 
 
-def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: float | None = None, grace_s: float = 10.0) -> int:
-    """Spawn every rank, wait for all, return the number of ranks that failed."""
-    rdv = Path(rendezvous)
-    if rdv.exists():
-        rdv.unlink()
-    procs = []
-    for l in plan_launch(gpus, rendezvous):
-        cmd, env = build_command(l, argv)
-        procs.append(subprocess.Popen(cmd, env=env))
-    return sum(rc != 0 for rc in wait_ranks(procs, timeout_s, grace_s))
+def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s: float = 10.0, log=None):
+    """Run a rank group to completion, starting it again (from scratch: the ranks keep no state outside the
+    artifact) up to `restarts` times when a rank is lost. `spawn()` starts one process per rank and returns them.
+    Returns (number of ranks that failed in the last attempt, attempts made)."""
+    attempt = 0
+    while True:
+        attempt += 1
+        codes = wait_ranks(spawn(), timeout_s, grace_s)
+        failed = sum(rc != 0 for rc in codes)
+        if failed == 0 or attempt > restarts:
+            return failed, attempt
+        if log is not None:
+            log(f"rank group lost {failed} rank(s) (exit codes {codes}); restart {attempt} of {restarts}")
+
+
+def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: float | None = None, grace_s: float = 10.0,
+                 restarts: int = 0) -> int:
+    """Spawn every rank, wait for all, return the number of ranks that failed (after `restarts` fresh starts of the
+    whole group, if asked for)."""
+    def spawn():
+        rdv = Path(rendezvous)
+        if rdv.exists():
+            rdv.unlink()            # a restarted group must not meet through the previous group's blob
+        procs = []
+        for l in plan_launch(gpus, rendezvous):
+            cmd, env = build_command(l, argv)
+            procs.append(subprocess.Popen(cmd, env=env))
+        return procs
+
+    failed, _ = supervise(spawn, restarts, timeout_s, grace_s, log=lambda m: print(m, file=sys.stderr, flush=True))
+    return failed
 
 
 def local_device_index() -> int:

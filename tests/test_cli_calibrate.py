@@ -194,6 +194,20 @@ def test_a_lost_rank_ends_the_job():
     assert codes[0] == 3 and codes[1] != 0 and _t.monotonic() - t0 < 20
     ok = [subprocess.Popen([sys.executable, "-c", "pass"]) for _ in range(2)]
     assert launcher.wait_ranks(ok) == [0, 0]
+    # a lost rank with restarts allowed: the whole group starts again, and the second attempt succeeds
+    attempts = []
+
+    def spawn():
+        attempts.append(1)
+        bad = "import sys; sys.exit(7)" if len(attempts) == 1 else "pass"
+        return [subprocess.Popen([sys.executable, "-c", bad]), subprocess.Popen([sys.executable, "-c", "pass"])]
+
+    notes = []
+    assert launcher.supervise(spawn, restarts=2, grace_s=0.5, log=notes.append) == (0, 2)
+    assert len(notes) == 1 and "restart 1 of 2" in notes[0]
+    attempts.clear()
+    always_bad = lambda: [subprocess.Popen([sys.executable, "-c", "import sys; sys.exit(1)"])]
+    assert launcher.supervise(always_bad, restarts=1, grace_s=0.2) == (1, 2)      # gives up after the allowed restarts
     slow = [subprocess.Popen([sys.executable, "-c", "import time; time.sleep(60)"])]
     assert launcher.wait_ranks(slow, timeout_s=0.3)[0] != 0          # an overall limit ends a job that never finishes
 
