@@ -25,6 +25,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="skein", description="Blackwell-native LLM serving compiler and runtime")
     ap.add_argument("--log-level", default="info")
     ap.add_argument("--output", default="text", choices=["text", "json"])
+    ap.add_argument("--runtime-config", default=None,
+                    help="TOML file whose [runtime] table sets the runtime switches (skein_b200/utils/runtime_config.py); "
+                         "the environment overrides the file")
     sub = ap.add_subparsers(dest="command", required=True)
 
     def planner_inputs(p):
@@ -121,6 +124,11 @@ def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     logging.basicConfig(level=getattr(logging, args.log_level.upper(), logging.INFO), format="%(levelname)s %(name)s: %(message)s")
     try:
+        if args.runtime_config:
+            from ..utils.runtime_config import RuntimeConfig
+            rc = RuntimeConfig.resolve(toml_text=_read(args.runtime_config))
+            rc.apply_to_env()       # rank processes started by `serve --gpus` inherit it
+            log.info("runtime config: %s", rc.describe())
         from . import commands
         return getattr(commands, "cmd_" + args.command)(args, emit)
     except Exception as e:  # one-line JSON error objects, like the reference
