@@ -72,11 +72,15 @@ def build_command(launch: RankLaunch, argv: list[str], base_env: dict | None = N
     return [sys.executable, "-m", "skein_b200.parallel.worker", *argv], env
 
 
-def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, poll_s: float = 0.05) -> list[int]:
+def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, poll_s: float = 0.05, monitor=None,
+               log=None) -> list[int]:
     """Wait for every rank. Once one has failed, the rest get `grace_s` to finish by themselves (they usually notice
-    through their own time-outs) and are then terminated. Returns the exit codes in rank order."""
+    through their own time-outs) and are then terminated. `monitor` (watchdog.Monitor over the ranks' heartbeat
+    files) also catches a rank whose process is alive but has stopped beating: it is terminated, which makes it a
+    failed rank like any other. Returns the exit codes in rank order."""
     t0 = time.monotonic()
     first_failure = None
+    next_beat_check = t0
     codes: list = [None] * len(procs)
     while any(c is None for c in codes):
         for i, p in enumerate(procs):
@@ -85,6 +89,13 @@ def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, pol
                 if codes[i] not in (None, 0) and first_failure is None:
                     first_failure = time.monotonic()
         now = time.monotonic()
+        if monitor is not None and now >= next_beat_check:
+            next_beat_check = now + 0.2
+            for r in monitor.dead_ranks(now, started_only=True):
+                if r < len(procs) and codes[r] is None:
+                    if log is not None:
+                        log(f"rank {r} stopped beating: terminating it")
+                    procs[r].terminate()
         overdue = timeout_s is not None and now - t0 > timeout_s
         orphaned = first_failure is not None and now - first_failure > grace_s
         if overdue or orphaned:
@@ -104,14 +115,15 @@ def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, pol
     return codes
 
 
-def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s: float = 10.0, log=None):
+def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s: float = 10.0, log=None, make_monitor=None):
     """Run a rank group to completion, starting it again (from scratch: the ranks keep no state outside the
     artifact) up to `restarts` times when a rank is lost. `spawn()` starts one process per rank and returns them.
     Returns (number of ranks that failed in the last attempt, attempts made)."""
     attempt = 0
     while True:
         attempt += 1
-        codes = wait_ranks(spawn(), timeout_s, grace_s)
+        procs = spawn()
+        codes = wait_ranks(procs, timeout_s, grace_s, monitor=make_monitor() if make_monitor else None, log=log)
         failed = sum(rc != 0 for rc in codes)
         if failed == 0 or attempt > restarts:
             return failed, attempt
@@ -123,17 +135,27 @@ def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: f
                  restarts: int = 0) -> int:
     """Spawn every rank, wait for all, return the number of ranks that failed (after `restarts` fresh starts of the
     whole group, if asked for)."""
+    from .watchdog import Monitor
+    hb_dir = Path(rendezvous + ".hb")
+
     def spawn():
         rdv = Path(rendezvous)
         if rdv.exists():
             rdv.unlink()            # a restarted group must not meet through the previous group's blob
+        if hb_dir.is_dir():
+            for f in hb_dir.glob("rank_*.hb"):
+                f.unlink()
         procs = []
         for l in plan_launch(gpus, rendezvous):
             cmd, env = build_command(l, argv)
+            env["SKEIN_HEARTBEAT_DIR"] = str(hb_dir)
             procs.append(subprocess.Popen(cmd, env=env))
         return procs
 
-    failed, _ = supervise(spawn, restarts, timeout_s, grace_s, log=lambda m: print(m, file=sys.stderr, flush=True))
+    # a beat every 0.5 s; 120 missed beats (60 s) before a rank that is still running counts as lost: weight loading
+    # and graph capture can hold the interpreter for seconds at a time
+    failed, _ = supervise(spawn, restarts, timeout_s, grace_s, log=lambda m: print(m, file=sys.stderr, flush=True),
+                          make_monitor=lambda: Monitor(str(hb_dir), len(gpus), interval_s=0.5, missed_beats=120))
     return failed
 
 

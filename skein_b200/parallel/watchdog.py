@@ -1,7 +1,7 @@
 """Host-side failure detection: heartbeats in a shared directory and a monitor that declares a rank dead.
 
 Each rank touches `<dir>/rank_<r>.hb` with a monotonically increasing counter from a daemon thread. The
-monitor (any rank, or the launcher) reads the files; a rank whose counter has not moved for
+monitor (any rank, or the launcher: `launcher.launch_ranks` watches the ranks it started) reads the files; a rank whose counter has not moved for
 `missed_beats x interval` is reported dead, after which the caller aborts its communicator / stops launching
 fused steps and fails in-flight requests with a retriable status. Nothing here touches a GPU: device-side
 waits are bounded on their own (status word), this layer catches ranks that died on the host.
@@ -53,7 +53,9 @@ class Monitor:
         self.limit_s = interval_s * missed_beats
         self._last = {}     # rank -> (counter, time it last changed)
 
-    def dead_ranks(self, now: float | None = None) -> list[int]:
+    def dead_ranks(self, now: float | None = None, started_only: bool = False) -> list[int]:
+        """Ranks whose counter has not moved for the limit. started_only: a rank that has not written its first
+        beat yet (still importing, loading weights) is not judged."""
         now = time.monotonic() if now is None else now
         dead = []
         for r in range(self.world):
@@ -62,6 +64,8 @@ class Monitor:
                 n = int(p.read_text() or 0)
             except (FileNotFoundError, ValueError):
                 n = -1
+            if n < 0 and started_only:
+                continue
             prev = self._last.get(r)
             if prev is None or prev[0] != n:
                 self._last[r] = (n, now)

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import queue
 import sys
 import threading
@@ -189,6 +190,10 @@ def run_rank(args) -> int:
     device = torch.device("cuda", launcher.local_device_index()) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
+    beat = None
+    if os.environ.get("SKEIN_HEARTBEAT_DIR"):      # set by the launcher, which watches the file (watchdog.py)
+        from .watchdog import Heartbeat
+        beat = Heartbeat(os.environ["SKEIN_HEARTBEAT_DIR"], rank, interval_s=0.5).start()
     art = Artifact(args.artifact)
     if art.num_devices != world:
         raise SystemExit(f"artifact was compiled for {art.num_devices} devices, launched with {world}")
@@ -259,6 +264,8 @@ def run_rank(args) -> int:
             if c is not None:
                 c.close()
         dist.destroy_process_group()
+    if beat is not None:
+        beat.stop()
     return rc
 
 

@@ -95,6 +95,30 @@ def test_compile_verify_serve_job_cpu(tmp_path, capsys):
     assert b["requests_ok"] + b["requests_rejected"] == 2 and b["drift_compliance"] is True
 
 
+def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
+    """`serve --gpus 0,1` on a PP=2 artifact: the launcher starts two rank processes (gloo on CPU), watches their
+    heartbeats, and reports none failed."""
+    cfg = tmp_path / "tiny_config.json"
+    cfg.write_text(json.dumps(TINY))
+    drift = tmp_path / "tiny_drift.toml"
+    drift.write_text((ROOT / "models/mixtral_8x7b_drift.toml").read_text())
+    env = {**os.environ, "CUDA_VISIBLE_DEVICES": "", "SKEIN_FORCE_TP": "1", "SKEIN_FORCE_PP": "2", "SKEIN_FORCE_EP": "1"}
+    cli = [sys.executable, "-m", "skein_b200.cli.main", "--output", "json"]
+    r = subprocess.run([*cli, "compile", "--model", str(cfg), "--cluster", str(ROOT / "cluster/b200_2x.toml"), "--trace",
+                        str(ROOT / "cluster/sample_trace.jsonl"), "--drift", str(drift), "--cost", str(ROOT / "cluster/cost_constants.toml"),
+                        "--out", str(tmp_path / "art"), "--n-parity-prompts", "2", "--enforce-parity"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    art = str(tmp_path / "art" / os.readlink(tmp_path / "art" / "LATEST"))
+    assert json.loads((Path(art) / "plan.json").read_text())["parallelism"] == {"tp": 1, "pp": 2, "ep": 1}
+    r = subprocess.run([*cli, "serve", "--artifact", art, "--gpus", "0,1", "--prompt", "hello", "--max-new-tokens", "4",
+                        "--max-seq-len", "128", "--rendezvous", str(tmp_path / "rdv")],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1]) == {"failed": 0, "ranks": 2}
+    assert sorted(p.name for p in (tmp_path / "rdv.hb").glob("*.hb")) == ["rank_0.hb", "rank_1.hb"]
+
+
 # ---- calibration ----------------------------------------------------------------------------------------------------
 CORPUS = """workload_trace_path = "traces/t.jsonl"
 n_drift_prompts = 4
@@ -208,6 +232,19 @@ def test_a_lost_rank_ends_the_job():
     attempts.clear()
     always_bad = lambda: [subprocess.Popen([sys.executable, "-c", "import sys; sys.exit(1)"])]
     assert launcher.supervise(always_bad, restarts=1, grace_s=0.2) == (1, 2)      # gives up after the allowed restarts
+    # a rank that is alive but has stopped beating is terminated by the launcher's monitor and counts as lost
+    import tempfile
+    from skein_b200.parallel.watchdog import Monitor
+    hb = tempfile.mkdtemp()
+    beating = ("import sys, time; sys.path.insert(0, %r); from skein_b200.parallel.watchdog import Heartbeat; "
+               "h = Heartbeat(%r, %%d, interval_s=0.1).start(); time.sleep(%%f); %%s") % (str(ROOT), hb)
+    procs = [subprocess.Popen([sys.executable, "-c", beating % (0, 60.0, "h.stop()")]),
+             subprocess.Popen([sys.executable, "-c", beating % (1, 1.0, "h.stop(); time.sleep(60)")])]     # stalls after 1 s
+    notes = []
+    t0 = _t.monotonic()
+    codes = launcher.wait_ranks(procs, grace_s=0.5, monitor=Monitor(hb, 2, interval_s=0.1, missed_beats=10), log=notes.append)
+    assert codes[1] != 0 and codes[0] != 0 and _t.monotonic() - t0 < 30
+    assert any("rank 1 stopped beating" in n for n in notes)
     slow = [subprocess.Popen([sys.executable, "-c", "import time; time.sleep(60)"])]
     assert launcher.wait_ranks(slow, timeout_s=0.3)[0] != 0          # an overall limit ends a job that never finishes
 
