@@ -48,6 +48,9 @@ def test_compile_verify_serve_bench_autotune_on_one_gpu(tmp_path):
     assert v["avg_final_kl"] < 0.05          # CUDA kernels + paged cache vs the cache-free dense oracle
     out = _cli(["serve", "--artifact", art, "--prompt", "hello", "--max-new-tokens", "6", "--max-seq-len", "128"])
     assert len(out["generated"][0]) == 6 and out["tokens_per_s"] > 0
+    one = _cli(["serve", "--artifact", art, "--gpus", "0", "--prompt", "hello", "--max-new-tokens", "6", "--max-seq-len", "128",
+                "--rendezvous", str(tmp_path / "rdv1")])               # the same job as a launched rank process with a heartbeat
+    assert one == {"failed": 0, "ranks": 1} and (tmp_path / "rdv1.hb" / "rank_0.hb").exists()
     b = _cli(["bench", "--artifact", art, "--workload", str(ROOT / "cluster/sample_trace.jsonl"), "--max-requests", "3",
               "--time-scale", "1000"])
     assert b["requests_ok"] + b["requests_rejected"] == 3
