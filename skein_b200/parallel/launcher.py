@@ -5,7 +5,8 @@ CUDA_VISIBLE_DEVICES, SKEIN_LOCAL_DEVICE), spawns them, waits, and reports how m
 GPUs of the job, in job order, and computes on the one at index SKEIN_LOCAL_DEVICE: the tensor-parallel kernels read
 the peers' buffers through CUDA IPC mappings, which can only be opened for a device the process can see. If one
 rank dies, the others get a grace period and are then terminated, so a job never outlives a lost rank; with
-`restarts` the whole group is then started again from the artifact (the ranks hold no other state). Ranks meet through a file
+`restarts` the whole group is then started again from the artifact (the ranks hold no other state). SIGTERM / SIGINT
+to the launcher is passed on to rank 0 only, which shuts the group down cleanly between steps. Ranks meet through a file
 rendezvous: the leader publishes a small blob atomically (tmp + rename), the others poll for it with a
 timeout and get a clear error if it never appears. torch.distributed is then initialised from the
 address carried in the blob.
@@ -115,7 +116,24 @@ def wait_ranks(procs, timeout_s: float | None = None, grace_s: float = 10.0, pol
     return codes
 
 
-def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s: float = 10.0, log=None, make_monitor=None):
+class StopRequest:
+    """Set by the launcher's SIGTERM / SIGINT handler. The signal is passed on to rank 0 only: rank 0 closes its HTTP
+    front end, drains, and announces the stop to the other ranks over the control group, so that every rank leaves
+    between steps with nothing in flight. A stopped group is never restarted."""
+
+    def __init__(self):
+        self.requested = False
+        self.procs = []
+
+    def __call__(self, signum=None, frame=None):
+        import signal
+        self.requested = True
+        if self.procs and self.procs[0].poll() is None:
+            self.procs[0].send_signal(signal.SIGTERM)
+
+
+def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s: float = 10.0, log=None, make_monitor=None,
+              stop: "StopRequest | None" = None):
     """Run a rank group to completion, starting it again (from scratch: the ranks keep no state outside the
     artifact) up to `restarts` times when a rank is lost. `spawn()` starts one process per rank and returns them.
     Returns (number of ranks that failed in the last attempt, attempts made)."""
@@ -123,9 +141,13 @@ def supervise(spawn, restarts: int = 0, timeout_s: float | None = None, grace_s:
     while True:
         attempt += 1
         procs = spawn()
+        if stop is not None:
+            stop.procs = procs
+            if stop.requested:       # the signal came while the group was being started
+                stop()
         codes = wait_ranks(procs, timeout_s, grace_s, monitor=make_monitor() if make_monitor else None, log=log)
         failed = sum(rc != 0 for rc in codes)
-        if failed == 0 or attempt > restarts:
+        if failed == 0 or attempt > restarts or (stop is not None and stop.requested):
             return failed, attempt
         if log is not None:
             log(f"rank group lost {failed} rank(s) (exit codes {codes}); restart {attempt} of {restarts}")
@@ -152,10 +174,22 @@ def launch_ranks(gpus: list[int], rendezvous: str, argv: list[str], timeout_s: f
             procs.append(subprocess.Popen(cmd, env=env))
         return procs
 
-    # a beat every 0.5 s; 120 missed beats (60 s) before a rank that is still running counts as lost: weight loading
-    # and graph capture can hold the interpreter for seconds at a time
-    failed, _ = supervise(spawn, restarts, timeout_s, grace_s, log=lambda m: print(m, file=sys.stderr, flush=True),
-                          make_monitor=lambda: Monitor(str(hb_dir), len(gpus), interval_s=0.5, missed_beats=120))
+    import signal
+    import threading
+    stop = StopRequest()
+    previous = {}
+    if threading.current_thread() is threading.main_thread():      # handlers can only be installed there
+        for sig in (signal.SIGTERM, signal.SIGINT):
+            previous[sig] = signal.signal(sig, stop)
+    try:
+        # a beat every 0.5 s; 120 missed beats (60 s) before a rank that is still running counts as lost: weight
+        # loading and graph capture can hold the interpreter for seconds at a time
+        failed, _ = supervise(spawn, restarts, timeout_s, grace_s, log=lambda m: print(m, file=sys.stderr, flush=True),
+                              make_monitor=lambda: Monitor(str(hb_dir), len(gpus), interval_s=0.5, missed_beats=120),
+                              stop=stop)
+    finally:
+        for sig, h in previous.items():
+            signal.signal(sig, h)
     return failed
 
 

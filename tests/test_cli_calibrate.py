@@ -118,6 +118,43 @@ def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
     assert json.loads(r.stdout.strip().splitlines()[-1]) == {"failed": 0, "ranks": 2}
     assert sorted(p.name for p in (tmp_path / "rdv.hb").glob("*.hb")) == ["rank_0.hb", "rank_1.hb"]
 
+    # the same two ranks behind the HTTP front end (rank 0 hosts it and announces every step to rank 1); SIGTERM to the
+    # launcher reaches rank 0 only, which stops the group between steps: both ranks exit 0
+    import signal
+    import socket
+    import time
+    import urllib.request
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    p = subprocess.Popen([*cli, "serve", "--artifact", art, "--gpus", "0,1", "--port", str(port), "--max-seq-len", "128",
+                          "--rendezvous", str(tmp_path / "rdv_http")], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                         cwd=ROOT, env=env)
+    try:
+        up = False
+        for _ in range(600):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/healthz", timeout=1) as h:
+                    up = h.status == 200
+                    break
+            except OSError:
+                assert p.poll() is None, p.stderr.read()[-2000:]
+                time.sleep(0.2)
+        assert up
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"prompt": "hello", "max_tokens": 4}).encode())
+        with urllib.request.urlopen(req, timeout=120) as resp:
+            body = json.loads(resp.read().decode())
+        assert len(body["tokens"]) == 4 and body["finish_reason"] == "length"
+        p.send_signal(signal.SIGTERM)
+        out, err = p.communicate(timeout=90)
+    finally:
+        if p.poll() is None:
+            p.kill()
+    assert p.returncode == 0, err[-2000:]
+    assert json.loads(out.strip().splitlines()[-1]) == {"failed": 0, "ranks": 2}
+
 
 # ---- calibration ----------------------------------------------------------------------------------------------------
 CORPUS = """workload_trace_path = "traces/t.jsonl"
