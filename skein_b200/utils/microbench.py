@@ -5,7 +5,8 @@
     python -m skein_b200.utils.microbench --op moe_gate_up --tp 4 --iters 1 --warmup 1     # a profiler-sized run
 
 Shapes are the decode step of Mixtral-8x7B (64 sequences, top-2 of 8 experts, hidden 4096, ffn 14336,
-32/8 heads of 128) divided by --tp the way the tensor-parallel shards divide them. Every op is timed
+32/8 heads of 128) divided by --tp the way the tensor-parallel shards divide them; attn_prefill, prefill_qkv,
+argmax and quant_fp8 time the prefill-sized launches (16 prompts of --ctx tokens, 8192-token projection). Every op is timed
 with CUDA events after warm-up, with a 256 MiB write between iterations so that nothing is served from
 L2, and reported as the median. The denominators are the machine's measured copy bandwidth and bf16
 GEMM rate when a MEASURED_PEAKS.json sits at the repository root, else the stated fallback.
