@@ -62,7 +62,7 @@ def test_tp2_ep2_fused():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_pull_collectives_match_the_library():
     """all-gather, reduce-scatter, all-to-all and all-reduce as publish + one pull kernel over peer memory."""
-    _run(min(torch.cuda.device_count(), 4), port=29548, worker="coll_worker.py", ok="COLL_WORKER_OK")
+    _run(2, port=29548, worker="coll_worker.py", ok="COLL_WORKER_OK")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
