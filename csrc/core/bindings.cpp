@@ -265,7 +265,9 @@ PYBIND11_MODULE(_skein_core, m) {
       .def_property_readonly("prefix_hit_tokens_total", &KvBlockManager::prefix_hit_tokens_total).def_property_readonly("num_requests", &KvBlockManager::num_requests)
       .def("generation_of", &KvBlockManager::generation_of).def("try_prefix_reuse", &KvBlockManager::try_prefix_reuse)
       .def("can_admit", &KvBlockManager::can_admit, py::arg("prompt"), py::arg("reserve_tokens") = 0)
-      .def("admit", &KvBlockManager::admit).def("advance", &KvBlockManager::advance).def("release", &KvBlockManager::release)
+      .def("admit", &KvBlockManager::admit).def("advance", &KvBlockManager::advance)
+      .def("release", &KvBlockManager::release, py::arg("request_id"), py::arg("discard") = false)
+      .def("mark_computed", &KvBlockManager::mark_computed).def("clear_prefix_cache", &KvBlockManager::clear_prefix_cache)
       .def("pages_for", [](const KvBlockManager& k, uint64_t id) -> py::object { auto* t = k.table(id); if (!t) return py::none(); return py::cast(t->pages); })
       .def("table", [](const KvBlockManager& k, uint64_t id) -> py::object { auto* t = k.table(id); if (!t) return py::none(); return py::cast(*t); });
 
@@ -275,12 +277,13 @@ PYBIND11_MODULE(_skein_core, m) {
       .def_readonly("until_ms", &AdmissionDecision::until_ms).def_readonly("reason", &AdmissionDecision::reason);
   py::class_<ContinuousBatcher>(m, "ContinuousBatcher")
       .def(py::init([](uint32_t max_batch, uint32_t chunk_tokens, double ttft_ms, double tpot_ms, double base_us, double exponent, double prefill_us,
-                       KvBlockManager* kv, uint32_t max_prefill_tokens) {
-             return new ContinuousBatcher(max_batch, chunk_tokens, SloTargets{ttft_ms, tpot_ms}, LatencyEstimator{base_us, exponent, prefill_us}, kv, max_prefill_tokens);
+                       KvBlockManager* kv, uint32_t max_prefill_tokens, uint32_t interleave_prefill_tokens) {
+             return new ContinuousBatcher(max_batch, chunk_tokens, SloTargets{ttft_ms, tpot_ms}, LatencyEstimator{base_us, exponent, prefill_us}, kv, max_prefill_tokens,
+                                          interleave_prefill_tokens);
            }),
            py::arg("max_batch"), py::arg("chunk_tokens") = 0, py::arg("ttft_ms") = 500.0, py::arg("tpot_ms") = 50.0, py::arg("decode_us_at_b1") = 8000.0,
            py::arg("batch_exponent") = 0.7, py::arg("prefill_per_token_us") = 25.0, py::arg("kv") = nullptr, py::arg("max_prefill_tokens") = 8192,
-           py::keep_alive<1, 9>())
+           py::arg("interleave_prefill_tokens") = 0, py::keep_alive<1, 9>())
       .def("decide", [](const ContinuousBatcher& b, uint64_t id, const std::vector<int32_t>& prompt, uint32_t max_new, uint64_t now) {
         return b.decide(IncomingRequest{id, prompt, max_new, now}, now);
       })
@@ -300,7 +303,7 @@ PYBIND11_MODULE(_skein_core, m) {
         if (!o) return py::none();
         return py::make_tuple(o->finished, o->generated);
       }, py::arg("id"), py::arg("token"), py::arg("now_ms"), py::arg("eos_token") = -1)
-      .def("retire", &ContinuousBatcher::retire).def("retire_all", &ContinuousBatcher::retire_all)
+      .def("retire", &ContinuousBatcher::retire, py::arg("id"), py::arg("failed") = false).def("retire_all", &ContinuousBatcher::retire_all)
       .def("current_sequence", &ContinuousBatcher::current_sequence)
       .def("request_info", [](const ContinuousBatcher& b, uint64_t id) -> py::object {
         auto* r = b.get(id);
@@ -357,6 +360,7 @@ PYBIND11_MODULE(_skein_core, m) {
         r.record_request(RequestMetrics{id, status, ttft, tpot, hit, out});
       })
       .def("count", &MetricsRegistry::count, py::arg("name"), py::arg("n") = 1)
+      .def("set_gauge", &MetricsRegistry::set_gauge)
       .def("render", &MetricsRegistry::render).def("ttft_p50", &MetricsRegistry::ttft_p50).def("tpot_p99", &MetricsRegistry::tpot_p99)
       .def_property_readonly("steps_buffered", &MetricsRegistry::steps_buffered).def_property_readonly("requests_buffered", &MetricsRegistry::requests_buffered);
 }

@@ -69,6 +69,9 @@ template <int MAX_PASSES>
 __device__ __forceinline__ bool reduce_norm_row(const NormParams& p, const int b, float* sh, int& wait_failed,
                                                 uint4 (&nb)[MAX_PASSES]) {
   if (p.flags != nullptr) {
+    // row 0's CTA records how long it stood waiting for the peers (exposed communication time): a 64-bit
+    // nanosecond total in status[2..3], read by the host together with the status word
+    const uint64_t t_wait0 = (b == 0 && threadIdx.x == 0) ? global_timer_ns() : 0;
     if (threadIdx.x == 0) wait_failed = 0;
     __syncthreads();
     if ((int)threadIdx.x < p.n_src) {
@@ -82,6 +85,8 @@ __device__ __forceinline__ bool reduce_norm_row(const NormParams& p, const int b
       }
     }
     __syncthreads();
+    if (b == 0 && threadIdx.x == 0 && p.status != nullptr)
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 2), (unsigned long long)(global_timer_ns() - t_wait0));
     if (wait_failed) return false;
   }
   float vals[MAX_PASSES][8];

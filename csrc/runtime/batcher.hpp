@@ -69,8 +69,9 @@ struct AcceptOutcome { bool finished = false; uint32_t generated = 0; };
 class ContinuousBatcher {
  public:
   ContinuousBatcher(uint32_t max_batch, uint32_t chunk_tokens, SloTargets slo, LatencyEstimator est, KvBlockManager* kv,
-                    uint32_t max_prefill_tokens_per_step = 8192)
-      : max_batch_(max_batch), chunk_tokens_(chunk_tokens), slo_(slo), est_(est), kv_(kv), max_prefill_tokens_(max_prefill_tokens_per_step) {}
+                    uint32_t max_prefill_tokens_per_step = 8192, uint32_t interleave_prefill_tokens = 0)
+      : max_batch_(max_batch), chunk_tokens_(chunk_tokens), slo_(slo), est_(est), kv_(kv), max_prefill_tokens_(max_prefill_tokens_per_step),
+        interleave_tokens_(interleave_prefill_tokens) {}
 
   AdmissionDecision decide(const IncomingRequest& r, uint64_t now_ms) const {
     AdmissionDecision d;
@@ -113,6 +114,9 @@ class ContinuousBatcher {
       InflightRequest& r = kv.second;
       if (r.phase == Phase::Decode) b.decode.push_back(kv.first);
     }
+    // while sequences are decoding, a step carries only a slice of the waiting prompts, so that a long
+    // prompt delays the decoding sequences' next token by one slice and not by its whole prefill
+    if (interleave_tokens_ > 0 && !b.decode.empty()) budget = std::min(budget, interleave_tokens_);
     for (auto& kv : inflight_) {
       InflightRequest& r = kv.second;
       if (r.phase != Phase::Prefill || budget == 0) continue;
@@ -132,13 +136,18 @@ class ContinuousBatcher {
     auto it = inflight_.find(id);
     if (it == inflight_.end()) return;
     it->second.prefilled = new_end;
+    // only now may other requests share these pages through the prefix cache
+    if (kv_ && kv_->table(id)) kv_->mark_computed(id, it->second.req.prompt, new_end);
   }
 
   std::optional<AcceptOutcome> accept_token(uint64_t id, int32_t token, uint64_t now_ms, int32_t eos_token = -1) {
     auto it = inflight_.find(id);
     if (it == inflight_.end()) return std::nullopt;
     InflightRequest& r = it->second;
-    if (r.phase == Phase::Prefill) { r.phase = Phase::Decode; r.first_token_ms = now_ms; r.prefilled = (uint32_t)r.req.prompt.size(); }
+    if (r.phase == Phase::Prefill) {
+      r.phase = Phase::Decode; r.first_token_ms = now_ms; r.prefilled = (uint32_t)r.req.prompt.size();
+      if (kv_ && kv_->table(id)) kv_->mark_computed(id, r.req.prompt, r.prefilled);
+    }
     r.generated.push_back(token);
     r.last_token_ms = now_ms;
     AcceptOutcome o;
@@ -149,10 +158,11 @@ class ContinuousBatcher {
     return o;
   }
 
-  void retire(uint64_t id) {
+  // `failed`: the request is dropped after a step that did not complete; its pages leave the prefix cache.
+  void retire(uint64_t id, bool failed = false) {
     auto it = inflight_.find(id);
     if (it == inflight_.end()) throw RuntimeError("retire: unknown request " + std::to_string(id));
-    if (kv_ && kv_->table(id)) kv_->release(id);
+    if (kv_ && kv_->table(id)) kv_->release(id, failed);
     inflight_.erase(it);
     ++retired_;
   }
@@ -160,7 +170,7 @@ class ContinuousBatcher {
   std::vector<uint64_t> retire_all() {
     std::vector<uint64_t> ids;
     for (auto& kv : inflight_) ids.push_back(kv.first);
-    for (uint64_t id : ids) retire(id);
+    for (uint64_t id : ids) retire(id, true);
     return ids;
   }
 
@@ -183,7 +193,7 @@ class ContinuousBatcher {
   SloTargets slo_;
   LatencyEstimator est_;
   KvBlockManager* kv_;
-  uint32_t max_prefill_tokens_;
+  uint32_t max_prefill_tokens_, interleave_tokens_;
   std::map<uint64_t, InflightRequest> inflight_;
   std::deque<Queued> queue_;
   uint64_t rejected_ = 0, retired_ = 0;

@@ -5,13 +5,17 @@
 // list of unreferenced pages that still hold a cached prefix, and a trie over whole pages of prompt
 // tokens. Sharing is page-granular: a new request reuses the longest run of full pages whose tokens
 // match, never a partially filled page (it would have to write into it), and never its whole prompt
-// (at least one token must be computed to produce logits).
+// (at least one token must be computed to produce logits). A page enters the trie only once its
+// KV has been computed (`mark_computed`, called as prefill chunks finish), so a second request with
+// the same prefix can never attend over pages that are reserved but still empty; a request that is
+// dropped after a failed step takes its unshared pages out of the cache (`release(id, true)`).
 //
 // Role of the reference's PagedKVAllocator + RadixPrefixTree (crates/skein_runtime/src/kv/
 // allocator.rs:17-308, radix.rs:18-130): same admit / advance / release life cycle, refcounts,
 // generation check against stale trie entries and LRU eviction; block tables are handed to the
 // kernels instead of assembling contiguous host buffers (kv/paged_cache.rs:30-370).
 #pragma once
+#include <algorithm>
 #include <cstdint>
 #include <deque>
 #include <list>
@@ -32,6 +36,7 @@ struct PageTable {
   uint32_t num_tokens = 0;          // tokens whose KV is (or is about to be) in the cache
   uint32_t prefix_hit_tokens = 0;   // tokens served from the prefix cache at admission
   uint32_t registered_pages = 0;    // leading pages that are entered in the trie
+  bool no_register = false;         // the prefix cache was cleared while this request was in flight
 };
 
 class RadixPrefixTree {
@@ -72,7 +77,12 @@ class RadixPrefixTree {
         it = n->children.emplace(std::move(k), std::move(c)).first;
         ++nodes_;
       } else if (it->second->page != pages[p]) {
-        break;  // another request already caches this prefix in a different page; ours stays private
+        Node* c = it->second.get();
+        const bool stale = c->page < 0 || (size_t)c->page >= generations.size() || generations[c->page] != c->generation;
+        if (!stale) break;  // another request already caches this prefix in a different page; ours stays private
+        c->page = pages[p];             // the old page was evicted: the entry now points at ours
+        c->generation = generations[pages[p]];
+        c->children.clear();
       }
       n = it->second.get();
       ++registered;
@@ -105,7 +115,7 @@ class RadixPrefixTree {
 class KvBlockManager {
  public:
   KvBlockManager(uint32_t total_pages, uint32_t page_size, bool prefix_cache = true, uint32_t radix_max_depth = 4096)
-      : ps_(page_size), refcount_(total_pages, 0), generation_(total_pages, 0), cached_(total_pages, 0) {
+      : ps_(page_size), radix_depth_(radix_max_depth), refcount_(total_pages, 0), generation_(total_pages, 0), cached_(total_pages, 0) {
     if (page_size == 0 || total_pages == 0) throw RuntimeError("KV manager needs pages and a page size");
     for (uint32_t p = 0; p < total_pages; ++p) free_.push_back((int32_t)p);
     if (prefix_cache) radix_ = std::make_unique<RadixPrefixTree>(page_size, radix_max_depth);
@@ -158,12 +168,36 @@ class KvBlockManager {
     pt.num_tokens = (uint32_t)prompt.size();
     pt.prefix_hit_tokens = (uint32_t)matched.size() * ps_;
     hit_tokens_total_ += pt.prefix_hit_tokens;
-    if (radix_) {
-      pt.registered_pages = (uint32_t)radix_->insert(prompt, pt.pages, generation_);
-      for (uint32_t i = 0; i < pt.registered_pages; ++i) cached_[pt.pages[i]] = 1;
-    }
+    pt.registered_pages = (uint32_t)matched.size();   // the matched pages already sit in the trie
     tables_[request_id] = pt;
     return pt;
+  }
+  // The KV of the first `computed_tokens` tokens of `prompt` is now in the request's pages: enter the full
+  // pages below that point in the trie. Returns the number of leading pages registered so far.
+  uint32_t mark_computed(uint64_t request_id, const std::vector<int32_t>& prompt, uint32_t computed_tokens) {
+    auto it = tables_.find(request_id);
+    if (it == tables_.end()) throw RuntimeError("unknown request " + std::to_string(request_id));
+    PageTable& pt = it->second;
+    if (!radix_ || pt.no_register) return pt.registered_pages;
+    const uint32_t upto = std::min<uint32_t>(computed_tokens, (uint32_t)prompt.size()) / ps_;
+    if (upto <= pt.registered_pages) return pt.registered_pages;
+    std::vector<int32_t> pages(pt.pages.begin(), pt.pages.begin() + std::min<size_t>(upto, pt.pages.size()));
+    const uint32_t reg = (uint32_t)radix_->insert(prompt, pages, generation_);
+    for (uint32_t i = pt.registered_pages; i < reg; ++i) cached_[pt.pages[i]] = 1;
+    // a shorter count means another request cached the same prefix in other pages first: ours stay private
+    if (reg < upto) pt.no_register = true;
+    pt.registered_pages = std::max(pt.registered_pages, reg);
+    return pt.registered_pages;
+  }
+  // Forget every cached prefix (the weights changed): all trie entries become stale, unreferenced cached
+  // pages return to the free list, and requests in flight no longer register their pages.
+  void clear_prefix_cache() {
+    for (size_t p = 0; p < generation_.size(); ++p) { ++generation_[p]; cached_[p] = 0; }
+    for (int32_t p : lru_) free_.push_back(p);
+    lru_.clear();
+    lru_pos_.clear();
+    if (radix_) radix_ = std::make_unique<RadixPrefixTree>(ps_, radix_depth_);
+    for (auto& kv : tables_) { kv.second.no_register = true; kv.second.registered_pages = 0; }
   }
   // Makes room for `n_new` more tokens; returns the pages that were added to the table.
   std::vector<int32_t> advance(uint64_t request_id, uint32_t n_new) {
@@ -181,10 +215,15 @@ class KvBlockManager {
     pt.num_tokens = next;
     return added;
   }
-  void release(uint64_t request_id) {
+  // `discard`: the request's step failed, so what its pages hold is not trusted; pages that no other request
+  // references leave the prefix cache (generation bump, back to the free list).
+  void release(uint64_t request_id, bool discard = false) {
     auto it = tables_.find(request_id);
     if (it == tables_.end()) throw RuntimeError("unknown request " + std::to_string(request_id));
-    for (int32_t p : it->second.pages) unref(p);
+    for (int32_t p : it->second.pages) {
+      if (discard && refcount_[p] == 1) { ++generation_[p]; cached_[p] = 0; }
+      unref(p);
+    }
     tables_.erase(it);
   }
   const PageTable* table(uint64_t request_id) const {
@@ -194,7 +233,7 @@ class KvBlockManager {
   size_t num_requests() const { return tables_.size(); }
 
  private:
-  uint32_t ps_;
+  uint32_t ps_, radix_depth_;
   std::vector<uint32_t> refcount_;
   std::vector<uint64_t> generation_;
   std::vector<char> cached_;              // page is registered in the trie

@@ -227,6 +227,7 @@ class MetricsRegistry {
     if (req_buf_.size() > cap_) req_buf_.pop_front();
   }
   void count(const std::string& name, uint64_t n = 1) { std::lock_guard<std::mutex> g(mu_); extra_[name] += n; }
+  void set_gauge(const std::string& name, double v) { std::lock_guard<std::mutex> g(mu_); gauges_[name] = v; }
   size_t steps_buffered() const { return steps_buf_.size(); }
   size_t requests_buffered() const { return req_buf_.size(); }
   double ttft_p50() const { return ttft_hist_.quantile(0.5); }
@@ -245,6 +246,7 @@ class MetricsRegistry {
     tpot_hist_.render(o, "skein_tpot_ms_histogram", "Time per output token (ms)");
     o << "# HELP skein_prefix_cache_hit_tokens_total Prompt tokens served from the prefix cache\n# TYPE skein_prefix_cache_hit_tokens_total counter\nskein_prefix_cache_hit_tokens_total " << prefix_hits_ << "\n";
     for (auto& kv : extra_) o << "# TYPE " << kv.first << " counter\n" << kv.first << " " << kv.second << "\n";
+    for (auto& kv : gauges_) o << "# TYPE " << kv.first << " gauge\n" << kv.first << " " << kv.second << "\n";
     return o.str();
   }
 
@@ -256,6 +258,7 @@ class MetricsRegistry {
   uint32_t kv_pages_ = 0;
   Histogram batch_hist_, ttft_hist_, tpot_hist_;
   std::map<std::string, uint64_t> requests_, extra_;
+  std::map<std::string, double> gauges_;
   std::deque<StepMetrics> steps_buf_;
   std::deque<RequestMetrics> req_buf_;
 };

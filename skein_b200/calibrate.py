@@ -271,11 +271,12 @@ def calibrate_drift(report_layers, plan: dict) -> dict:
     return out
 
 
-def autotune_decode_gemms(cfg, tp: int, batch: int, out_path, seed: int = 0):
+def autotune_decode_gemms(cfg, tp: int, batch: int, out_path, seed: int = 0, budget: int = 0):
     """Measure launch configurations for the GEMM shapes of one decode step of `cfg` at tensor-parallel degree
     `tp` and `batch` sequences, and write them to `out_path` (the artifact's cache/kernel_configs.json).
 
     Random weights of the shard shapes and an even routing are used: the winner depends on shapes, not values.
+    `budget` > 0 caps the launch configurations timed per shape (the compile command's --search-budget).
     Returns {shape name: best config}. The reference memoises its kernel search the same way
     (crates/skein_compile/src/search_cache.rs:71-150)."""
     import torch
@@ -292,20 +293,20 @@ def autotune_decode_gemms(cfg, tp: int, batch: int, out_path, seed: int = 0):
     cache = tuning.KernelConfigCache(out_path)
     x = bf(batch, H, std=1.0)
     found = {}
-    found["qkv"] = ops.tune_linear(x, bf((hq + 2 * hkv) * D, H), cache=cache)[0]
-    found["o_proj"] = ops.tune_linear(bf(batch, hq * D, std=1.0), bf(H, hq * D), cache=cache)[0]
-    found["lm_head"] = ops.tune_linear(x, bf(cfg.vocab_size // tp, H), cache=cache)[0]
+    found["qkv"] = ops.tune_linear(x, bf((hq + 2 * hkv) * D, H), cache=cache, budget=budget)[0]
+    found["o_proj"] = ops.tune_linear(bf(batch, hq * D, std=1.0), bf(H, hq * D), cache=cache, budget=budget)[0]
+    found["lm_head"] = ops.tune_linear(x, bf(cfg.vocab_size // tp, H), cache=cache, budget=budget)[0]
     if cfg.is_moe:
         E, k = cfg.num_experts, cfg.top_k
         per = max(1, batch * k // E)
         cnt = torch.full((E,), per, dtype=torch.int32, device=dev)
         off = torch.zeros(E + 1, dtype=torch.int32, device=dev)
         off[1:] = torch.cumsum(cnt, 0)
-        found["moe_gate_up"] = ops.tune_grouped(bf(E * per, H, std=1.0), bf(E, 2 * inter, H), cnt, off, True, cache)[0]
-        found["moe_down"] = ops.tune_grouped(bf(E * per, inter, std=1.0), bf(E, H, inter), cnt, off, False, cache)[0]
+        found["moe_gate_up"] = ops.tune_grouped(bf(E * per, H, std=1.0), bf(E, 2 * inter, H), cnt, off, True, cache, budget)[0]
+        found["moe_down"] = ops.tune_grouped(bf(E * per, inter, std=1.0), bf(E, H, inter), cnt, off, False, cache, budget)[0]
     else:
-        found["gate_up"] = ops.tune_linear(x, bf(2 * inter, H), swiglu=True, cache=cache)[0]
-        found["down"] = ops.tune_linear(bf(batch, inter, std=1.0), bf(H, inter), cache=cache)[0]
+        found["gate_up"] = ops.tune_linear(x, bf(2 * inter, H), swiglu=True, cache=cache, budget=budget)[0]
+        found["down"] = ops.tune_linear(bf(batch, inter, std=1.0), bf(H, inter), cache=cache, budget=budget)[0]
     ops.workspace().check_status()
     cache.save()
     return found

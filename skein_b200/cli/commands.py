@@ -56,7 +56,7 @@ def cmd_compile(args, emit) -> int:
         prompts = [json.loads(l)["tokens"] for l in _read(args.parity_prompts_path).splitlines() if l.strip()]
     r = compile_model(_read(args.model), _read(args.cluster), _read(args.trace), _read(args.drift), _read(args.cost), args.out,
                       weights=args.weights, options=_search_options(args), n_parity_prompts=args.n_parity_prompts, prompts=prompts,
-                      enforce_parity=args.enforce_parity, seed=args.seed)
+                      enforce_parity=args.enforce_parity, seed=args.seed, search_budget=args.search_budget)
     if r.replans:
         Path(args.drift).write_text(r.drift_toml)    # the feedback edge: the next extract sees the raised entries
     rep = r.report
@@ -110,7 +110,15 @@ def cmd_serve(args, emit) -> int:
     from ..parallel import launcher, worker
 
     argv = ["--artifact", args.artifact, "--port", str(args.port), "--total-kv-bytes", str(args.total_kv_bytes), "--max-new-tokens",
-            str(args.max_new_tokens), "--rendezvous", args.rendezvous, "--max-batch", str(args.max_batch), "--max-seq-len", str(args.max_seq_len)]
+            str(args.max_new_tokens), "--rendezvous", args.rendezvous, "--max-batch", str(args.max_batch), "--max-seq-len", str(args.max_seq_len),
+            "--bytes-per-token", str(args.bytes_per_token), "--temperature", str(args.temperature), "--top-k", str(args.top_k),
+            "--top-p", str(args.top_p), "--seed", str(args.seed)]
+    if args.enable_hot_swap:
+        argv.append("--enable-hot-swap")
+    if not args.cuda_graphs:
+        argv.append("--no-cuda-graphs")
+    if args.speculative_draft:
+        argv += ["--speculative-draft", args.speculative_draft, "--speculative-k", str(args.speculative_k)]
     for flag, val in (("--workload", args.workload), ("--cost", args.cost), ("--prompt", args.prompt), ("--demo-prompts", args.demo_prompts)):
         if val is not None:
             argv += [flag, val]
@@ -144,7 +152,10 @@ def cmd_calibrate(args, emit) -> int:
         from ..compile.pipeline import default_parity_prompts
         art = Artifact(args.candidate_artifact)
         ref = Artifact(args.reference_artifact) if args.reference_artifact else Artifact(art.path / "reference_bf16")
-        prompts = default_parity_prompts(art.cfg, min(corpus.n_drift_prompts, 8), seed=corpus.sampling_seed)
+        if args.drift_prompts_path:     # JSONL of {"tokens": [...]}: the prompts the drift entries are measured on
+            prompts = [json.loads(l)["tokens"] for l in _read(args.drift_prompts_path).splitlines() if l.strip()][:corpus.n_drift_prompts]
+        else:
+            prompts = default_parity_prompts(art.cfg, min(corpus.n_drift_prompts, 8), seed=corpus.sampling_seed)
         rep = parity.verify(parity.ArtifactForward(art), parity.ArtifactForward(ref), prompts, art.plan, 1.0, consts.get("parity_tolerance_mse", {}))
         drift = cal.calibrate_drift(json.loads(rep.to_json())["layers"], art.plan)
         name = Path(args.model).stem.replace("_config", "")

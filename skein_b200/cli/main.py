@@ -47,7 +47,8 @@ def build_parser() -> argparse.ArgumentParser:
     planner_inputs(c)
     c.add_argument("--weights", default=None, help="HF safetensors file or directory; omit for seeded random weights")
     c.add_argument("--out", default="artifacts/")
-    c.add_argument("--search-budget", type=int, default=100, help="accepted for compatibility; kernels are ahead-of-time compiled")
+    c.add_argument("--search-budget", type=int, default=100, help="with a GPU present: launch configurations timed per GEMM shape of the decode step; the winners go "
+                        "into the artifact's cache/kernel_configs.json (0 = skip the search)")
     c.add_argument("--enforce-parity", action="store_true")
     c.add_argument("--parity-prompts-path", default=None)
     c.add_argument("--n-parity-prompts", type=int, default=8)
@@ -72,9 +73,11 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--workload", default=None)
     s.add_argument("--cost", default="cluster/cost_constants.toml")
     s.add_argument("--port", type=int, default=8080)
-    s.add_argument("--enable-hot-swap", action="store_true")
+    s.add_argument("--enable-hot-swap", action="store_true",
+                   help="expose POST /admin/hotswap {\"artifact\": path}: verify shapes, drain, mount on every rank")
     s.add_argument("--total-kv-bytes", type=int, default=0, help="0 = size the pool from free device memory")
-    s.add_argument("--bytes-per-token", type=int, default=0)
+    s.add_argument("--bytes-per-token", type=int, default=0,
+                   help="with --total-kv-bytes: KV bytes one token takes on this rank (0 = derived from the model and the plan)")
     s.add_argument("--gpus", default=None, help="comma-separated device ids; one process per GPU")
     s.add_argument("--prompt", default=None)
     s.add_argument("--max-new-tokens", type=int, default=32)
@@ -83,7 +86,14 @@ def build_parser() -> argparse.ArgumentParser:
                    help="with --gpus: start the whole rank group again, up to this many times, after a rank was lost")
     s.add_argument("--batch-demo", action="store_true")
     s.add_argument("--demo-prompts", default=None)
-    s.add_argument("--cuda-graphs", action="store_true", default=True)
+    s.add_argument("--cuda-graphs", action=argparse.BooleanOptionalAction, default=True,
+                   help="replay captured decode steps (--no-cuda-graphs launches every kernel eagerly)")
+    s.add_argument("--temperature", type=float, default=0.0, help="generation job (--prompt / --demo-prompts): 0 = greedy")
+    s.add_argument("--top-k", type=int, default=0)
+    s.add_argument("--top-p", type=float, default=1.0)
+    s.add_argument("--seed", type=int, default=0)
+    s.add_argument("--speculative-draft", default=None, help="artifact of a smaller draft model: speculative decoding in the generation job")
+    s.add_argument("--speculative-k", type=int, default=4, help="draft tokens proposed per verification step")
     s.add_argument("--max-batch", type=int, default=0)
     s.add_argument("--max-seq-len", type=int, default=4096)
 

@@ -45,7 +45,10 @@ def default_parity_prompts(cfg: ModelConfig, n: int, length: int = 24, seed: int
 def compile_model(config_json: str, cluster_toml: str, trace_jsonl: str, drift_toml: str, constants_toml: str, out_root,
                   weights: str | None = None, options: dict | None = None, n_parity_prompts: int = 8, prompts=None,
                   enforce_parity: bool = False, max_replans: int = 2, parity_device: str = "cpu", seed: int = 0,
-                  run_parity: bool = True, tokenizer_json=None) -> CompileResult:
+                  run_parity: bool = True, tokenizer_json=None, search_budget: int = 0) -> CompileResult:
+    """`search_budget` > 0 on a machine with a GPU: time up to that many launch configurations for every GEMM shape
+    of the plan's decode step and store the winners in the artifact's cache/kernel_configs.json, which `serve`
+    loads (the role of the reference's kernel search at compile time, crates/skein_compile/src/search_cache.rs:73)."""
     cfg = ModelConfig.from_hf_dict(json.loads(config_json))
     source = WeightSource(cfg, weights, seed=seed)
     consts = json.loads(core.cost_constants_json(constants_toml))
@@ -87,5 +90,9 @@ def compile_model(config_json: str, cluster_toml: str, trace_jsonl: str, drift_t
     if enforce_parity and report is not None and not report.passed:
         raise RuntimeError(f"parity gate failed after {replans} re-plans: avg final KL {report.avg_final_kl:.3g}, "
                            f"{len(report.failing)} failing layers")
+    if search_budget > 0 and torch.cuda.is_available():
+        from ..calibrate import autotune_decode_gemms
+        autotune_decode_gemms(cfg, int(plan["parallelism"]["tp"]), int(plan["batching"]["max_batch"]),
+                              art_dir / "cache" / "kernel_configs.json", seed=seed, budget=search_budget)
     update_latest_symlink(out_root, art_dir)
     return CompileResult(art_dir, plan, report, replans, drift_toml)

@@ -124,6 +124,16 @@ class BatchInputs:
     ctx_hint: int = 1024                       # host-side typical context length (chooses split-KV)
 
 
+@dataclass
+class SamplingInputs:
+    """Per-row sampling parameters of a step (device tensors): rows with temperature <= 0 are greedy."""
+    temperature: torch.Tensor          # [B] fp32
+    top_k: torch.Tensor                # [B] int32 (0: the kernel's maximum of 64 candidates)
+    top_p: torch.Tensor                # [B] fp32 in (0, 1]
+    seeds: torch.Tensor                # [B] int64: one random stream per request
+    step: torch.Tensor                 # [1] int32: position in the stream, advanced once per step
+
+
 class Decoder:
     """One rank's share of the model: weights, KV cache and the step function.
 
@@ -301,12 +311,25 @@ class Decoder:
             normed = normed.index_select(0, inp.logit_rows).contiguous()
         return ops.linear(normed, self.w.lm_head)
 
-    def forward(self, inp: BatchInputs, hidden_in=None):
-        """Full step on a single stage: returns (greedy tokens int32 [rows], logits shard)."""
+    def forward(self, inp: BatchInputs, hidden_in=None, sampling: SamplingInputs | None = None):
+        """Full step on a single stage: returns (next tokens int32 [rows], logits shard). Greedy unless `sampling`
+        is given."""
         _, normed = self.forward_hidden(inp, hidden_in)
         lg = self.logits(normed, inp)
-        if self.comm is not None and self.comm.size > 1:
-            tok = self.comm.vocab_parallel_argmax(lg, self.sh["V_local"])
-        else:
-            tok = ops.sample_argmax(lg)
-        return tok, lg
+        return self.sample(lg, sampling), lg
+
+    def sample(self, lg, sampling: SamplingInputs | None = None):
+        """Next token of every row from this rank's logit shard. Greedy: vocabulary-parallel arg-max (8 bytes per row
+        cross NVLink). Sampling: the shards are gathered (every rank then draws the same token from the same
+        per-request random stream), as the reference gathers logits before its sampler
+        (crates/skein_runtime/src/cuda/nccl.rs:251-298)."""
+        tp = self.comm is not None and self.comm.size > 1
+        if sampling is None:
+            return self.comm.vocab_parallel_argmax(lg, self.sh["V_local"]) if tp else ops.sample_argmax(lg)
+        if tp:
+            rows, vl = lg.shape
+            full = self.comm.all_gather(lg.contiguous()).view(self.comm.size, rows, vl).permute(1, 0, 2).reshape(rows, -1)
+            lg = full[:, :self.cfg.vocab_size].contiguous()
+        n = lg.shape[0]
+        return ops.sample(lg, sampling.temperature[:n], sampling.top_k[:n], sampling.top_p[:n], sampling.seeds[:n],
+                          sampling.step)

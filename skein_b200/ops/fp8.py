@@ -37,6 +37,14 @@ class Fp8Weight:
     def nbytes(self) -> int:
         return self.q.numel() + self.scale_t.numel() * 4
 
+    def copy_(self, src: "Fp8Weight"):
+        """In-place update (hot swap keeps the storage that captured CUDA graphs point at)."""
+        if tuple(src.shape) != self.shape:
+            raise ValueError(f"fp8 weight shape {tuple(src.shape)} does not match {self.shape}")
+        self.q.copy_(src.q)
+        self.scale_t.copy_(src.scale_t)
+        return self
+
 
 def quantize_weight(w: torch.Tensor) -> Fp8Weight:
     shape = tuple(w.shape)

@@ -27,8 +27,9 @@ class Workspace:
     """Per-device scratch shared by kernels that run one after another on a stream.
 
     Holds the stream-K partial-tile buffer and arrival counters of the GEMM, the split-KV buffers
-    of decode attention, and the two-int status word that kernels write an error code into when a
-    bounded wait runs out or a debug bounds check trips.
+    of decode attention, and the status word that kernels write an error code into when a
+    bounded wait runs out or a debug bounds check trips (followed by a running total of the time the
+    reduce kernels spent waiting for tensor-parallel peers).
     """
 
     GEMM_WS_BYTES = 148 * 2 * 128 * 256 * 4 + (1 << 20)
@@ -40,31 +41,51 @@ class Workspace:
         self.gemm_ws = torch.empty(max(self.GEMM_WS_BYTES, self.sm_count * 2 * 128 * 256 * 4), dtype=torch.uint8,
                                    device=device)
         self.gemm_counters = torch.zeros(max(self.sm_count, 256), dtype=torch.int32, device=device)
-        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        # [error code, detail, nanoseconds spent waiting for peers (64-bit total in words 2..3)]
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.router_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.route_barrier = torch.zeros(2, dtype=torch.int32, device=device)
-        self.attn_ws = None
-        self.attn_counters = None
+        # Split-KV scratch of decode attention, sized ONCE for the worst case and never reallocated: captured CUDA
+        # graphs keep its address, so growing it on demand would leave earlier graphs writing into freed memory.
+        # Splits are only used while (sequences x kv heads x splits) <= SM count (pick_splits) with at most
+        # MAX_GROUP query heads per kv head, which bounds B * Hq * splits; the counters are one per (sequence, kv head).
+        self.attn_rows_cap = self.sm_count * self.MAX_GROUP
+        self.attn_ws = torch.empty(int(L.skein_attn_decode_workspace_floats(self.attn_rows_cap, 1, 1)),
+                                   dtype=torch.float32, device=device)
+        self.attn_counters = torch.zeros(max(self.sm_count, 256), dtype=torch.int32, device=device)
+        self.peer_state = []     # (epochs, done) tensors of live communicators, re-armed after a device error
+
+    MAX_GROUP = 16   # query heads per kv head that the tensor-core decode attention accepts
 
     def attn_scratch(self, B, Hq, Hkv, splits):
-        n = _lib.lib().skein_attn_decode_workspace_floats(B, Hq, splits)
-        if self.attn_ws is None or self.attn_ws.numel() < n:
-            self.attn_ws = torch.empty(int(n), dtype=torch.float32, device=self.device)
-        if self.attn_counters is None or self.attn_counters.numel() < B * Hkv:
-            self.attn_counters = torch.zeros(B * Hkv, dtype=torch.int32, device=self.device)
+        """The fixed split-KV scratch, or None when this launch would not fit it (the caller then runs unsplit)."""
+        if B * Hq * splits > self.attn_rows_cap or B * Hkv > self.attn_counters.numel():
+            return None
         return self.attn_ws, self.attn_counters
 
     def check_status(self):
         """Host read of the status word (synchronises). Raises on a recorded device-side error."""
-        code, detail = self.status.tolist()
+        code, detail = self.status[:2].tolist()
         if code != 0:
-            self.status.zero_()
-            self.route_barrier.zero_()   # a grid barrier that gave up leaves its counters dirty
+            self.reset_after_error()
             names = {1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
                      3: "timeout waiting for an accumulator", 4: "timeout waiting for a drained accumulator",
-                     5: "timeout waiting for a peer flag", 7: "index out of range",
-                     8: "timeout at a grid-wide arrival counter"}
+                     5: "timeout waiting for a peer flag", 6: "timeout waiting for the other pieces of a split tile",
+                     7: "index out of range", 8: "timeout at a grid-wide arrival counter"}
             raise RuntimeError(f"device status {code} ({names.get(code, 'unknown')}), detail {detail}")
+
+
+    def reset_after_error(self):
+        """A kernel that gave up leaves its arrival counters dirty: the split-K arrive/depart words of the GEMM, the
+        grid barrier of the fused router, the last-arriver counters of split-KV attention and the "all CTAs done"
+        counters of the publish epilogues. Clear them all together with the status word."""
+        self.status[:2].zero_()
+        self.route_barrier.zero_()
+        self.gemm_counters.zero_()
+        self.attn_counters.zero_()
+        self.router_counter.zero_()
+        for _, done in self.peer_state:
+            done.zero_()
 
 
 def workspace(device=None) -> Workspace:
@@ -400,7 +421,11 @@ def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=
         splits = pick_splits(B, Hkv, ctx_hint, ws.sm_count)
     wsf, ctr = (None, None)
     if splits > 1:
-        wsf, ctr = ws.attn_scratch(B, Hq, Hkv, splits)
+        scratch = ws.attn_scratch(B, Hq, Hkv, splits)
+        if scratch is None:
+            splits = 1
+        else:
+            wsf, ctr = scratch
     impl = impl or os.environ.get("SKEIN_ATTN_DECODE", "mma")
     if kv_cache.shape[3] % 16 != 0 or Hq // Hkv > 16:
         impl = "scalar"
@@ -436,7 +461,11 @@ def attn_decode_rope(qkv, positions, block_table, cos_sin, kv_cache, seq_lens, H
         splits = pick_splits(B, Hkv, ctx_hint, ws.sm_count)
     wsf, ctr = (None, None)
     if splits > 1:
-        wsf, ctr = ws.attn_scratch(B, Hq, Hkv, splits)
+        scratch = ws.attn_scratch(B, Hq, Hkv, splits)
+        if scratch is None:
+            splits = 1
+        else:
+            wsf, ctr = scratch
     rc = _lib.lib().skein_attn_decode_rope_mma(
         qkv.data_ptr(), qkv.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
         positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[0], out.data_ptr(), _lib.ptr(wsf), _lib.ptr(ctr),
@@ -576,7 +605,7 @@ def sample_argmax(logits, idx_offset=0, out=None, out_val=None):
 def sample(logits, temperature, top_k, top_p, seeds, step, out=None):
     """Temperature / top-k / top-p sampling; per-row parameters are device tensors."""
     if not logits.is_cuda:
-        raise NotImplementedError("stochastic sampling runs on the GPU; use sample_argmax on CPU")
+        return ref.sample(logits, temperature, top_k, top_p, seeds, step)
     B, V = logits.shape
     if out is None:
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
@@ -654,17 +683,17 @@ def linear_push(x, w, out_local, peer_flag, epoch, done_counter, ldo, grouped=No
     _gemm_launch(p, "linear_push")
 
 
-def tune_linear(x, w, swiglu=False, cache=None):
+def tune_linear(x, w, swiglu=False, cache=None, budget=0):
     """Measure the launch configurations of this dense GEMM shape and record the fastest (tuning.py)."""
     F = w.shape[0] // 2 if swiglu else w.shape[0]
     out = torch.empty(x.shape[0], F, dtype=torch.bfloat16, device=x.device)
     run = (lambda c: swiglu_linear(x, w, out=out, _cfg=c)) if swiglu else (lambda c: linear(x, w, out=out, _cfg=c))
-    return tuning.tune_gemm(run, 1 if swiglu else 0, 1, F, x.shape[1], x.shape[0], cache)
+    return tuning.tune_gemm(run, 1 if swiglu else 0, 1, F, x.shape[1], x.shape[0], cache, budget=budget)
 
 
-def tune_grouped(xs, w, counts, offsets, swiglu=False, cache=None):
+def tune_grouped(xs, w, counts, offsets, swiglu=False, cache=None, budget=0):
     """Same for a grouped (per-expert) GEMM with the given routing."""
     F = w.shape[1] // 2 if swiglu else w.shape[1]
     out = torch.empty(xs.shape[0], F, dtype=torch.bfloat16, device=xs.device)
     run = lambda c: grouped_linear(xs, w, counts, offsets, swiglu=swiglu, out=out, _cfg=c)
-    return tuning.tune_gemm(run, 1 if swiglu else 0, w.shape[0], F, xs.shape[1], xs.shape[0], cache)
+    return tuning.tune_gemm(run, 1 if swiglu else 0, w.shape[0], F, xs.shape[1], xs.shape[0], cache, budget=budget)

@@ -196,6 +196,66 @@ def sample_argmax(logits):
     return idx.min(dim=-1).values.to(torch.int32)
 
 
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return x ^ (x >> 31)
+
+
+def sample(logits, temperature, top_k, top_p, seeds, step):
+    """Temperature / top-k / top-p sampling with the counter-based generator of csrc/kernels/sample.cu: the
+    candidate list is the top_k (at most 64) largest logits in (value descending, index ascending) order, top_p
+    keeps its shortest prefix whose probability reaches p, and one uniform draw from splitmix64(seed ^
+    splitmix64(step + 1)) selects the token. Rows with temperature <= 0 are greedy."""
+    import numpy as np
+    lf = logits.float()
+    B, V = lf.shape
+    st = int(step.reshape(-1)[0]) if step is not None else 0
+    out = []
+    f32 = np.float32
+    for b in range(B):
+        T = float(temperature[b]) if temperature is not None else 0.0
+        K = 1 if T <= 0 else (int(top_k[b]) if top_k is not None else 64)
+        if K <= 0 or K > 64:
+            K = 64
+        K = min(K, V)
+        row = lf[b]
+        order = sorted(range(V), key=lambda i: (-float(row[i]), i))[:K]
+        if K == 1:
+            out.append(order[0])
+            continue
+        vals = [f32(row[i]) for i in order]
+        pr = [f32(np.exp((v - vals[0]) / f32(T), dtype=f32)) for v in vals]
+        den = f32(0)
+        for x in pr:
+            den = f32(den + x)
+        P = f32(top_p[b]) if top_p is not None else f32(1)
+        keep, cum = K, f32(0)
+        for k in range(K):
+            cum = f32(cum + f32(pr[k] / den))
+            if cum >= P:
+                keep = k + 1
+                break
+        kept = f32(0)
+        for k in range(keep):
+            kept = f32(kept + pr[k])
+        seed = (int(seeds[b]) & _M64) if seeds is not None else 0x1234
+        s64 = _splitmix64(seed ^ _splitmix64((st + 1) & _M64))
+        u = f32(f32(f32((s64 >> 40) & 0xFFFFFF) / f32(16777216.0)) * kept)
+        run, pick = f32(0), order[keep - 1]
+        for k in range(keep):
+            run = f32(run + pr[k])
+            if u < run:
+                pick = order[k]
+                break
+        out.append(pick)
+    return torch.tensor(out, dtype=torch.int32)
+
+
 def embed(ids, table, vocab_start=0):
     loc = ids.long() - vocab_start
     ok = (loc >= 0) & (loc < table.shape[0])

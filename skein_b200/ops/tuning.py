@@ -167,18 +167,22 @@ def gemm_candidates(mode: int, G: int, F: int, rows: int, sm_count: int):
     return out
 
 
-def tune_gemm(run, mode: int, G: int, F: int, K: int, rows: int, cache: KernelConfigCache | None = None, iters: int = 9):
+def tune_gemm(run, mode: int, G: int, F: int, K: int, rows: int, cache: KernelConfigCache | None = None, iters: int = 9,
+              budget: int = 0):
     """Time `run(config)` (one launch of the GEMM with that configuration) for every candidate and record the fastest.
 
     run: callable taking a dict {"n_tile", "grid", "line_cut_only"}; it must launch on the current stream. Returns
-    (best_config, {config_json: median_us})."""
+    (best_config, {config_json: median_us}). `budget` > 0 caps the number of candidates that are timed."""
     import torch
     from .functional import workspace
     cache = cache if cache is not None else (active() or KernelConfigCache())
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     results = {}
     best, best_us = None, float("inf")
-    for cfg in gemm_candidates(mode, G, F, rows, workspace().sm_count):
+    candidates = gemm_candidates(mode, G, F, rows, workspace().sm_count)
+    if budget > 0:
+        candidates = candidates[:budget]
+    for cfg in candidates:
         try:
             run(cfg)
             torch.cuda.synchronize()

@@ -63,7 +63,7 @@ class PipelineStage:
     def _n_out_rows(self, inp: BatchInputs) -> int:
         return inp.logit_rows.shape[0] if (inp.is_prefill and inp.logit_rows is not None) else inp.token_ids.shape[0]
 
-    def forward(self, inp: BatchInputs):
+    def forward(self, inp: BatchInputs, sampling=None):
         """One step through the whole pipeline. Every stage calls this with the same `inp`."""
         T, H = inp.token_ids.shape[0], self.cfg.hidden_size
         hidden = None
@@ -78,11 +78,7 @@ class PipelineStage:
             logits = None
         else:
             logits = self.dec.logits(normed, inp)
-            if self.dec.comm is not None and self.dec.comm.size > 1:
-                tokens = self.dec.comm.vocab_parallel_argmax(logits, self.dec.sh["V_local"])
-            else:
-                from .. import ops
-                tokens = ops.sample_argmax(logits)
+            tokens = self.dec.sample(logits, sampling)
         # token feedback to every stage of this pipeline group
         dist.broadcast(tokens, src=self.pp_ranks[-1], group=self.pp_group)
         return tokens, logits

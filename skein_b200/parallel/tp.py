@@ -91,6 +91,18 @@ class TPComm:
         self._cand_idx_ptrs = VP(*[h.peer_ptr(p, self.cand_idx_off + 4 * r * max_batch) for p in range(N)])
         self._cand_flag_ptrs = VP(*[h.peer_ptr(p, self.cand_flag_off + 4 * r) for p in range(N)])
         self._push_flag = [VP(*self._peer_flag[b]) for b in range(2)]
+        ops.workspace(device).peer_state.append((self.epochs, self.done))
+
+    def reset(self):
+        """Back to the state of a fresh communicator: flag words, epochs, arrival counters zero, buffer 0 next. Every
+        rank of the group must call this between the same two steps, with none of its kernels in flight and a
+        barrier on both sides (parallel/worker.py: make_resync)."""
+        for f in self.flags:
+            f.zero_()
+        self.cand_flags.zero_()
+        self.epochs.zero_()
+        self.done.zero_()
+        self.cur = 0
 
     def _partials(self, b: int, rows: int) -> PeerPartials:
         return PeerPartials(self.bufs[b][:rows], self._src_ptrs[b], self.size, self.flags[b], self.epochs[b:b + 1],
@@ -238,4 +250,6 @@ class TPComm:
         return out
 
     def close(self):
+        ws = ops.workspace(self.device)
+        ws.peer_state[:] = [st for st in ws.peer_state if st[0] is not self.epochs]
         self.heap.close()

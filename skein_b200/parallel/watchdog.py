@@ -1,6 +1,9 @@
 """Host-side failure detection: heartbeats in a shared directory and a monitor that declares a rank dead.
 
-Each rank touches `<dir>/rank_<r>.hb` with a monotonically increasing counter from a daemon thread. The
+Each rank touches `<dir>/rank_<r>.hb` with a monotonically increasing counter from a daemon thread; the thread
+stops beating while the rank's main loop has been inside one step for longer than `stall_limit_s` (the engine
+publishes when a step began), so a rank whose main thread is stuck in a synchronisation or a collective looks
+dead to the monitor although its process is alive, while an idle rank keeps beating. The
 monitor (any rank, or the launcher: `launcher.launch_ranks` watches the ranks it started) reads the files; a rank whose counter has not moved for
 `missed_beats x interval` is reported dead, after which the caller aborts its communicator / stops launching
 fused steps and fails in-flight requests with a retriable status. Nothing here touches a GPU: device-side
@@ -19,9 +22,12 @@ from pathlib import Path
 
 
 class Heartbeat:
-    def __init__(self, directory: str, rank: int, interval_s: float = 0.2):
+    def __init__(self, directory: str, rank: int, interval_s: float = 0.2, step_started_at=None, stall_limit_s: float = 30.0):
+        """step_started_at: callable returning the monotonic time at which the step in progress began, or None
+        between steps."""
         self.path = Path(directory) / f"rank_{rank}.hb"
         self.interval_s = interval_s
+        self.step_started_at, self.stall_limit_s = step_started_at, stall_limit_s
         self._stop = threading.Event()
         self._n = 0
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -42,9 +48,16 @@ class Heartbeat:
         tmp.write_text(str(self._n))
         os.replace(tmp, self.path)
 
+    def stalled(self, now: float | None = None) -> bool:
+        if self.step_started_at is None:
+            return False
+        t = self.step_started_at()
+        return t is not None and (time.monotonic() if now is None else now) - t > self.stall_limit_s
+
     def _run(self):
         while not self._stop.wait(self.interval_s):
-            self._beat()
+            if not self.stalled():
+                self._beat()
 
 
 class Monitor:

@@ -2,8 +2,10 @@
 (rank 0 hosts the front end and broadcasts the request stream) or runs a generation job.
 
 Every rank runs the same Engine on the same inputs: rank 0 is the only one that sees clients; each
-scheduler iteration it broadcasts {new requests, clock, stop} over a CPU (gloo) control group, all ranks
-apply it and step. Data-plane traffic (the fused collectives) never touches the host.
+scheduler iteration it announces {clock, has payload} through a shared-memory control page and broadcasts
+the payload (new requests, stop, hot swap) over a CPU (gloo) group only when there is one; all ranks apply
+it, step, and agree on whether the step failed anywhere (runtime/driver.py). Data-plane traffic (the fused
+collectives) never touches the host.
 
 Counterpart of RankServer::bootstrap / run_rank (crates/skein_runtime/src/distributed/gpu_rank.rs:104-410,
 crates/skein_cli/src/cmd/serve.rs:322), with the HTTP server in front of the multi-GPU workers instead
@@ -14,9 +16,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import queue
 import sys
-import threading
 import time
 
 import torch
@@ -24,17 +24,22 @@ import torch.distributed as dist
 
 from ..compile.artifact import Artifact
 from ..models.decoder import Decoder
-from ..runtime.engine import Engine, EngineConfig, TokenEvent
+from ..runtime.driver import EngineDriver, LocalControl, SharedControl, follower_loop
+from ..runtime.engine import Engine, EngineConfig, SamplingParams
 from ..runtime.tokenizer import Tokenizer
 from . import launcher
 
 
-def size_kv_pool(art: Artifact, lay, device, total_kv_bytes: int, page_size: int = 16, reserve_frac: float = 0.08) -> int:
-    """Pages in the per-layer pool: from an explicit byte budget, else from the memory left after the weights."""
+def size_kv_pool(art: Artifact, lay, device, total_kv_bytes: int, page_size: int = 16, reserve_frac: float = 0.08,
+                 bytes_per_token: int = 0) -> int:
+    """Pages in the per-layer pool: from an explicit byte budget (with the model's KV bytes per token on this rank,
+    or the caller's `bytes_per_token`), else from the memory left after the weights."""
     cfg = art.cfg
     n_layers = len(lay.stage_layers(cfg.num_layers))
     kv_heads = cfg.num_kv_heads // lay.tp
     page_bytes = 2 * kv_heads * page_size * cfg.head_dim * 2 * n_layers
+    if bytes_per_token > 0:
+        page_bytes = bytes_per_token * page_size
     if total_kv_bytes > 0:
         return max(8, total_kv_bytes // page_bytes)
     if device.type != "cuda":
@@ -51,7 +56,7 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
         from ..ops import tuning
         tuning.activate(tuning.KernelConfigCache(tuned, strict=False))   # measured configurations win over the heuristics
     weights = art.load_weights(rank, device)
-    pages = size_kv_pool(art, lay, device, args.total_kv_bytes)
+    pages = size_kv_pool(art, lay, device, args.total_kv_bytes, bytes_per_token=getattr(args, "bytes_per_token", 0))
     pages = min(pages, max(8, (args.max_seq_len // 16 + 1) * max(1, args.max_batch or art.plan["batching"]["max_batch"]) * 2))
     dec = Decoder(art.cfg, weights, lay, num_pages=pages, page_size=art.plan["kv"]["layout"].get("page_size", 16),
                   max_pos=min(args.max_seq_len, art.cfg.max_position_embeddings), comm=comm, comm_moe=comm_moe)
@@ -63,11 +68,17 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
     ecfg = EngineConfig(max_batch=args.max_batch or batching["max_batch"], chunk_tokens=batching.get("chunk_tokens", 0),
                         prefix_cache=art.plan["execution"]["prefix_cache"]["enable"],
                         # stage-to-stage NCCL p2p and library collectives are launched eagerly, never captured
-                        use_graphs=device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused and pp_info is None)
+                        use_graphs=(device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused
+                                    and pp_info is None and not getattr(args, "no_cuda_graphs", False)))
     if args.workload:
         from .. import core
-        w = core.workload_parse(open(args.workload).read())
+        text = open(args.workload).read()
+        w = core.workload_parse(text)
         ecfg.ttft_ms, ecfg.tpot_ms = w["ttft_p95_ms"], w["tpot_p95_ms"]
+        # the prompt lengths the plan was extracted for are the baseline of the workload drift monitor
+        lens = [json.loads(l).get("prompt_tokens") for l in text.splitlines()[1:] if l.strip()]
+        ecfg.drift_baseline = tuple(int(x) for x in lens if x)
+        ecfg.drift_threshold_kl = float(w.get("recompile_drift_threshold_kl", ecfg.drift_threshold_kl))
     if args.cost:
         from .. import core
         c = json.loads(core.cost_constants_json(open(args.cost).read())).get("runtime_estimator", {})
@@ -77,109 +88,26 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
     return Engine(dec, ecfg)
 
 
-class ControlPlane:
-    """Keeps the ranks' engines in lock step. Rank 0 calls `lead`, the others `follow`."""
+def make_resync(comms):
+    """Re-arm the fused communicators after a step that failed on any rank: behind a barrier (no rank is still
+    launching), every rank zeroes its flag words, epochs and arrival counters and clears its device status, so that
+    all ranks start the next step from the same epoch. A rank that is really gone makes the barrier time out, the
+    process exits and the launcher restarts the group."""
+    comms = [c for c in comms if c is not None]
 
-    def __init__(self, group, rank: int):
-        self.group, self.rank = group, rank
-
-    def lead(self, new_requests, now_ms: int, stop: bool = False):
-        msg = [{"new": new_requests, "now": now_ms, "stop": stop}]
-        if self.group is not None:
-            dist.broadcast_object_list(msg, src=0, group=self.group)
-        return msg[0]
-
-    def follow(self):
-        msg = [None]
-        dist.broadcast_object_list(msg, src=0, group=self.group)
-        return msg[0]
-
-
-class DistributedDriver:
-    """Rank 0's engine driver for a multi-rank job: like runtime.server.EngineDriver, but every iteration is
-    announced to the follower ranks first."""
-
-    def __init__(self, engine: Engine, control: ControlPlane):
-        self.engine, self.control = engine, control
-        self._inbox: "queue.Queue" = queue.Queue()
-        self._streams = {}
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, name="skein-dist-driver", daemon=True)
-        self.draining = False
-        self._next_id = 1
-
-    def start(self):
-        self._thread.start()
-        return self
-
-    def stop(self, timeout=10.0):
-        self._stop.set()
-        self._thread.join(timeout)
-
-    @property
-    def inflight(self):
-        return len(self._streams)
-
-    def submit(self, prompt_ids, max_new_tokens):
-        reply: "queue.Queue" = queue.Queue(maxsize=1)
-        self._inbox.put((prompt_ids, max_new_tokens, reply))
-        return reply.get()
-
-    def _run(self):
-        eng = self.engine
-        while True:
-            batch = []
-            try:
-                block = eng.idle and not self._stop.is_set()
-                item = self._inbox.get(timeout=0.05) if block else self._inbox.get_nowait()
-                batch.append(item)
-                while True:
-                    batch.append(self._inbox.get_nowait())
-            except queue.Empty:
-                pass
-            stop = self._stop.is_set() and eng.idle and not batch
-            if eng.idle and not batch and not stop:
-                continue
-            now = eng.clock()
-            new = []
-            for prompt, max_new, reply in batch:
-                rid = self._next_id
-                self._next_id += 1
-                new.append((rid, prompt, max_new))
-            self.control.lead(new, now, stop)
-            if stop:
-                return
-            for (rid, prompt, max_new), (_, _, reply) in zip(new, batch):
-                try:
-                    _, d = eng.submit(prompt, max_new, now_ms=now, request_id=rid)
-                except ValueError as e:
-                    reply.put((rid, "reject", str(e), None))
-                    continue
-                if d.kind == "reject":
-                    reply.put((rid, "reject", d.reason, None))
-                else:
-                    q: "queue.Queue[TokenEvent]" = queue.Queue()
-                    self._streams[rid] = q
-                    reply.put((rid, d.kind, d.reason, q))
-            for ev in eng.step(now):
-                q = self._streams.get(ev.request_id)
-                if q is not None:
-                    q.put(ev)
-                    if ev.is_final:
-                        del self._streams[ev.request_id]
-
-
-def follower_loop(engine: Engine, control: ControlPlane):
-    while True:
-        msg = control.follow()
-        if msg["stop"]:
-            return
-        for rid, prompt, max_new in msg["new"]:
-            try:
-                engine.submit(prompt, max_new, now_ms=msg["now"], request_id=rid)
-            except ValueError:
-                pass
-        engine.step(msg["now"])
+    def resync(control):
+        import torch as _t
+        control.barrier()
+        if _t.cuda.is_available():
+            _t.cuda.synchronize()
+        for c in comms:
+            c.reset()
+        if comms:
+            from .. import ops
+            ops.workspace().reset_after_error()
+            _t.cuda.synchronize()
+        control.barrier()
+    return resync
 
 
 def run_rank(args) -> int:
@@ -223,41 +151,39 @@ def run_rank(args) -> int:
         if pp > 1:
             pp_info = (pp_ranks, pp_group)
     engine = build_engine(art, rank, device, comm, args, comm_moe, pp_info)
-    control = ControlPlane(control_group, rank)
+    if beat is not None:
+        beat.step_started_at = lambda: engine.step_started_at     # a rank stuck inside a step stops beating
+    if world > 1:
+        control = SharedControl(str(rdv) + ".control", rank, world, control_group)
+    else:
+        control = LocalControl()
+    resync = make_resync([comm, comm_moe]) if world > 1 else None
     tok = Tokenizer(art.cfg.vocab_size, art.tokenizer_path())
+    sampling = SamplingParams(args.temperature, args.top_k, args.top_p, args.seed) if args.temperature > 0 else None
     rc = 0
     if rank != 0:
-        follower_loop(engine, control)
+        follower_loop(engine, control, rank, resync)
     else:
-        driver = DistributedDriver(engine, control).start()
+        driver = EngineDriver(engine, control, rank=0, resync=resync).start()
         try:
             if args.prompt is not None or args.demo_prompts:
                 prompts = [args.prompt] if args.prompt is not None else [p for p in args.demo_prompts.split("|") if p]
-                t0 = time.perf_counter()
-                subs = [driver.submit(tok.encode(p), args.max_new_tokens) for p in prompts]
-                results, first = [], None
-                for rid, kind, reason, q in subs:
-                    toks = []
-                    while q is not None:
-                        ev = q.get()
-                        if first is None:
-                            first = time.perf_counter() - t0
-                        if ev.error is None:
-                            toks.append(ev.token)
-                        if ev.is_final:
-                            break
-                    results.append(toks)
-                dt = time.perf_counter() - t0
-                n = sum(len(r) for r in results)
-                print(json.dumps({"generated": results, "text": [tok.decode(r) for r in results], "ttft_ms": round((first or 0) * 1e3, 2),
-                                  "tokens_per_s": round(n / dt, 2), "tpot_p99_ms": engine.metrics.tpot_p99()}))
+                if args.speculative_draft and world == 1:
+                    print(json.dumps(_speculative_job(art, engine, tok, prompts, args, device)))
+                else:
+                    print(json.dumps(_generation_job(driver, engine, tok, prompts, args.max_new_tokens, sampling)))
             else:
                 from aiohttp import web
 
                 from ..runtime.server import build_app
-                web.run_app(build_app(driver, tok), host="0.0.0.0", port=args.port, print=None)
+                hs = None
+                if args.enable_hot_swap:
+                    from ..runtime.hotswap import HotSwap
+                    hs = HotSwap(driver, art, rank=0)
+                web.run_app(build_app(driver, tok, hs, art.path.parent), host="0.0.0.0", port=args.port, print=None)
         finally:
             driver.stop()
+    control.close()
     if world > 1:
         dist.barrier()
         for c in (comm, comm_moe):
@@ -267,6 +193,50 @@ def run_rank(args) -> int:
     if beat is not None:
         beat.stop()
     return rc
+
+
+def _generation_job(driver, engine, tok, prompts, max_new_tokens, sampling=None) -> dict:
+    """Submit every prompt, collect the streams (the reference's multi-GPU generation job,
+    crates/skein_runtime/src/distributed/gpu_rank.rs:724-877)."""
+    t0 = time.perf_counter()
+    subs = [driver.submit(tok.encode(p), max_new_tokens, sampling) for p in prompts]
+    results, first = [], None
+    for rid, kind, reason, q in subs:
+        toks = []
+        while q is not None:
+            ev = q.get()
+            if first is None:
+                first = time.perf_counter() - t0
+            if ev.error is None:
+                toks.append(ev.token)
+            if ev.is_final:
+                break
+        results.append(toks)
+    dt = time.perf_counter() - t0
+    n = sum(len(r) for r in results)
+    return {"generated": results, "text": [tok.decode(r) for r in results], "ttft_ms": round((first or 0) * 1e3, 2),
+            "tokens_per_s": round(n / dt, 2), "tpot_p99_ms": engine.metrics.tpot_p99()}
+
+
+def _speculative_job(art, engine, tok, prompts, args, device) -> dict:
+    """Generation with a draft model proposing `--speculative-k` tokens per verification step of the target
+    (runtime/speculative.py; the reference's run_speculative_generation, distributed/gpu_rank.rs:2197)."""
+    from ..runtime.speculative import SpeculativeDecoder
+    draft_art = Artifact(args.speculative_draft)
+    draft = Decoder(draft_art.cfg, draft_art.load_weights(0, device), draft_art.layout(0), num_pages=engine.dec.num_pages,
+                    page_size=engine.dec.page_size, max_pos=engine.dec.max_pos)
+    spec = SpeculativeDecoder(engine.dec, draft, k=args.speculative_k)
+    t0 = time.perf_counter()
+    results, stats = [], {"proposed": 0, "accepted": 0, "target_steps": 0}
+    for p in prompts:
+        out, st = spec.generate(tok.encode(p), args.max_new_tokens, temperature=args.temperature, seed=args.seed)
+        results.append(out)
+        for k in stats:
+            stats[k] += st[k]
+    dt = time.perf_counter() - t0
+    n = sum(len(r) for r in results)
+    return {"generated": results, "text": [tok.decode(r) for r in results], "tokens_per_s": round(n / dt, 2),
+            "speculative": dict(stats, acceptance=round(stats["accepted"] / max(1, stats["proposed"]), 3))}
 
 
 def parse(argv=None):
@@ -283,6 +253,15 @@ def parse(argv=None):
     ap.add_argument("--max-batch", type=int, default=0)
     ap.add_argument("--max-seq-len", type=int, default=4096)
     ap.add_argument("--cpu", action="store_true")
+    ap.add_argument("--bytes-per-token", type=int, default=0)
+    ap.add_argument("--enable-hot-swap", action="store_true")
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--speculative-draft", default=None)
+    ap.add_argument("--speculative-k", type=int, default=4)
     return ap.parse_args(argv)
 
 

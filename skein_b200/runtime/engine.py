@@ -6,9 +6,14 @@
                  (eager) and the decode batch (CUDA-graph replay of the batch-size bucket), hand the
                  sampled tokens back to the batcher, retire finished requests, record metrics
 
+While sequences are decoding, a step carries at most `interleave_prefill_tokens` of waiting prompt, so
+a long prompt is spread over several steps instead of stalling every decoding sequence for its whole
+prefill. Requests may ask for temperature / top-k / top-p sampling with their own seed; the step then
+runs the sampling variant of the captured graph.
+
 Under tensor parallelism every rank runs the same engine on the same request stream (rank 0
-broadcasts submissions and the clock, see DistributedFrontend), so all ranks take identical
-scheduling decisions and meet in the fused collectives.
+announces submissions and the clock, see runtime/driver.py), so all ranks take identical scheduling
+decisions and meet in the fused collectives.
 
 A failing step does not take the server down: the batch is retired, its streams are closed with an
 error, queued requests stay queued (the reference wraps each step in catch_unwind for the same
@@ -21,9 +26,7 @@ process; distributed/batch_driver.rs:77-514 single-GPU continuous batching; dist
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
-
-import torch
+from dataclasses import dataclass
 
 from .. import core
 from .runner import ModelRunner
@@ -34,6 +37,7 @@ class EngineConfig:
     max_batch: int = 64
     chunk_tokens: int = 0              # 0 = whole prompt in one chunk (bounded by max_prefill_tokens)
     max_prefill_tokens: int = 8192
+    interleave_prefill_tokens: int = 2048   # prompt tokens per step while other sequences decode (0: no limit)
     ttft_ms: float = 500.0
     tpot_ms: float = 50.0
     decode_us_at_b1: float = 8000.0
@@ -42,6 +46,27 @@ class EngineConfig:
     prefix_cache: bool = True
     eos_token: int = -1
     use_graphs: bool = True
+    drift_baseline: tuple = ()         # prompt lengths the plan was extracted for (workload drift monitor)
+    drift_threshold_kl: float = 0.05
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    """temperature 0 = greedy. top_k 0 = the sampler's maximum (64 candidates). One random stream per seed."""
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    def row(self):
+        return (float(self.temperature), int(self.top_k), float(self.top_p), int(self.seed))
+
+
+GREEDY = SamplingParams()
 
 
 @dataclass
@@ -63,7 +88,8 @@ class Engine:
         self.batcher = core.ContinuousBatcher(
             max_batch=c.max_batch, chunk_tokens=c.chunk_tokens, ttft_ms=c.ttft_ms, tpot_ms=c.tpot_ms,
             decode_us_at_b1=c.decode_us_at_b1, batch_exponent=c.batch_exponent,
-            prefill_per_token_us=c.prefill_per_token_us, kv=self.kv, max_prefill_tokens=c.max_prefill_tokens)
+            prefill_per_token_us=c.prefill_per_token_us, kv=self.kv, max_prefill_tokens=c.max_prefill_tokens,
+            interleave_prefill_tokens=c.interleave_prefill_tokens)
         self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
         self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
         self.metrics = metrics or core.MetricsRegistry()
@@ -72,10 +98,18 @@ class Engine:
         self._step = 0
         self._graph_seen = (0, 0)   # runner.graph_captures / graph_replays already added to the metrics
         self._last = {}          # request id -> last sampled token (input of its next decode step)
+        self._sampling = {}      # request id -> SamplingParams (only requests that sample)
+        self._wait_ns_seen = 0
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
+        self.last_step_failed = False
+        self.step_started_at = None    # monotonic time at which the step in progress began (the rank's heartbeat reads it)
+        # workload drift: prompt lengths seen so far against the lengths the plan was made for
+        self._drift = core.DriftMonitor(list(c.drift_baseline), c.drift_threshold_kl) if c.drift_baseline else None
+        self._seen_lengths: list[int] = []
 
     # ---- admission ----------------------------------------------------------------------------------------
-    def submit(self, prompt_ids, max_new_tokens: int = 32, now_ms: int | None = None, request_id: int | None = None):
+    def submit(self, prompt_ids, max_new_tokens: int = 32, now_ms: int | None = None, request_id: int | None = None,
+               sampling: SamplingParams | None = None):
         """Returns (request_id, decision) with decision.kind in {"admit", "delay", "reject"}."""
         rid = request_id if request_id is not None else self._next_id
         self._next_id = max(self._next_id, rid) + 1
@@ -87,32 +121,66 @@ class Engine:
         d = self.batcher.submit(rid, prompt, max_new_tokens, now)
         if d.kind == "reject":
             self.metrics.record_request(rid, "rejected", 0.0, 0.0, 0, 0)
+        else:
+            if sampling is not None and not sampling.greedy:
+                self._sampling[rid] = sampling
+            self._observe_length(len(prompt))
         return rid, d
+
+    def _observe_length(self, n: int) -> None:
+        if self._drift is None:
+            return
+        self._seen_lengths.append(n)
+        if len(self._seen_lengths) > 4096:
+            del self._seen_lengths[:2048]
+        if len(self._seen_lengths) % 32 == 0:
+            kl, drifted, _ = self._drift.assess(self._seen_lengths)
+            self.metrics.set_gauge("skein_workload_drift_kl", float(kl))
+            self.metrics.set_gauge("skein_workload_drifted", 1.0 if drifted else 0.0)
+
+    def drift(self):
+        """(kl, drifted, samples) of the prompt lengths seen so far against the plan's workload, or None."""
+        return self._drift.assess(self._seen_lengths) if self._drift is not None else None
 
     # ---- one scheduler iteration ----------------------------------------------------------------------------
     def step(self, now_ms: int | None = None) -> list[TokenEvent]:
         now = self.clock() if now_ms is None else now_ms
         self.batcher.promote_ready(now)
         prefill, decode = self.batcher.next_step_batch()
+        self.last_step_failed = False
         if not prefill and not decode:
             return []
         t0 = time.perf_counter()
+        self.step_started_at = time.monotonic()
         try:
             if self.failure_injector is not None:
                 self.failure_injector(self._step)
             events = self._run(prefill, decode, now)
         except Exception as e:  # retire the batch, keep serving
-            events = [TokenEvent(rid, -1, True, error=f"{type(e).__name__}: {e}") for rid in self.batcher.retire_all()]
-            for ev in events:
-                self._last.pop(ev.request_id, None)
-                self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
+            events = self.abort_all(f"{type(e).__name__}: {e}")
+            self.last_step_failed = True
             self.metrics.count("skein_step_failures_total")
-            if "peer flag" in str(e):     # a bounded device wait on another rank ran out (ops.Workspace.check_status)
+            if getattr(e, "peer_timeout", False) or "peer flag" in str(e):
+                # a bounded device wait on another rank ran out (ops.Workspace.check_status)
                 self.metrics.count("skein_comm_timeout_total")
         self._count_graph_activity()
         us = (time.perf_counter() - t0) * 1e6
-        self.metrics.record_step(self._step, len(decode) + len(prefill), us, 0.0, self.kv.in_use_pages)
+        wait_ns = getattr(self.runner, "last_wait_ns", 0)
+        comm_us = max(0, wait_ns - self._wait_ns_seen) / 1e3     # time the reduce kernels stood waiting for peers
+        self._wait_ns_seen = wait_ns
+        self.metrics.record_step(self._step, len(decode) + len(prefill), max(0.0, us - comm_us), comm_us, self.kv.in_use_pages)
         self._step += 1
+        self.step_started_at = None
+        return events
+
+    def abort_all(self, reason: str) -> list[TokenEvent]:
+        """Drop everything in flight (a step failed here or on another rank): the requests' streams end with an
+        error and their pages leave the prefix cache; queued requests stay queued."""
+        events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
+        for ev in events:
+            self._last.pop(ev.request_id, None)
+            self._sampling.pop(ev.request_id, None)
+            self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
         return events
 
     def _count_graph_activity(self) -> None:
@@ -125,6 +193,12 @@ class Engine:
             self.metrics.count("skein_graph_replays_total", rep - seen_rep)
         self._graph_seen = (cap, rep)
 
+    def _rows(self, rids):
+        """Per-row sampling parameters of a step, or None when every request in it is greedy."""
+        if not self._sampling or not any(r in self._sampling for r in rids):
+            return None
+        return [self._sampling.get(r, GREEDY).row() for r in rids]
+
     def _run(self, prefill, decode, now) -> list[TokenEvent]:
         events: list[TokenEvent] = []
         if prefill:
@@ -132,7 +206,7 @@ class Engine:
             for rid, start, end, last in prefill:
                 prompt = self.batcher.prompt(rid)
                 seqs.append((prompt[start:end], self.kv.pages_for(rid), start))
-            toks = self.runner.prefill(seqs)
+            toks = self.runner.prefill(seqs, sampling=self._rows([p[0] for p in prefill]))
             for (rid, start, end, last), tok in zip(prefill, toks):
                 self.batcher.prefill_advanced(rid, end)
                 if last:
@@ -143,8 +217,9 @@ class Engine:
             lens = [p + 1 for p in pos]
             tables = [self.kv.pages_for(rid) for rid in decode]
             bk = self.runner.bucket(len(decode))
-            self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables)
-            out = self.runner.decode_step(bk)
+            rows = self._rows(decode)
+            self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables, sampling=rows)
+            out = self.runner.decode_step(bk, sampling=rows is not None)
             for i, rid in enumerate(decode):
                 events.append(self._accept(rid, int(out[i]), now))
         return events
@@ -159,6 +234,7 @@ class Engine:
             self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
             self.batcher.retire(rid)
             self._last.pop(rid, None)
+            self._sampling.pop(rid, None)
         return TokenEvent(rid, int(tok), bool(finished))
 
     # ---- helpers ------------------------------------------------------------------------------------------------
@@ -181,11 +257,11 @@ class Engine:
             steps += 1
         return out
 
-    def generate(self, prompts, max_new_tokens: int = 32) -> list[list[int]]:
+    def generate(self, prompts, max_new_tokens: int = 32, sampling: SamplingParams | None = None) -> list[list[int]]:
         """Convenience: submit every prompt now and run to completion. Returns generated ids per prompt."""
         ids = []
         for p in prompts:
-            rid, d = self.submit(p, max_new_tokens)
+            rid, d = self.submit(p, max_new_tokens, sampling=sampling)
             if d.kind == "reject":
                 raise RuntimeError(f"request rejected: {d.reason}")
             ids.append(rid)

@@ -2,11 +2,18 @@
 
 The decode step of one batch bucket is captured once into a CUDA graph (every kernel of the step,
 sampling included) and replayed. A step's host inputs travel in ONE pinned buffer and ONE
-host-to-device copy:
+host-to-device copy (int32 words; B = bucket size):
 
-    [ token ids B | positions B | seq_lens B | block table B x max_blocks ]      (int32)
+    [ token ids B | positions B | seq_lens B | temperature B (fp32) | top_k B | top_p B (fp32)
+      | seeds B (64-bit) | block table B x max_blocks ]
 
-and its result in one device-to-host copy: [ sampled tokens B | device status word 2 ].
+and its result in one device-to-host copy:
+
+    [ sampled tokens B | device status word 2 | nanoseconds the step waited for peers (64-bit) ]
+
+Two graphs exist per bucket: the greedy one (arg-max, vocabulary-parallel under TP) and the sampling one
+(temperature / top-k / top-p per row, rows with temperature 0 stay greedy); a step uses the second only
+when one of its requests asked for sampling.
 
 Capture classes are padded batch sizes (the reference keys its full-step captures per micro-batch:
 crates/skein_runtime/src/distributed/gpu_rank.rs:466-555; its dispatcher for capture classes is a
@@ -18,9 +25,10 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..models.decoder import BatchInputs, Decoder
+from ..models.decoder import BatchInputs, Decoder, SamplingInputs
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+N_RESULT_EXTRA = 4    # status code, detail, peer-wait nanoseconds (2 words)
 
 
 def bucket_for(n: int) -> int:
@@ -33,21 +41,28 @@ def bucket_for(n: int) -> int:
 class _Bucket:
     def __init__(self, B: int, max_blocks: int, device):
         self.B, self.max_blocks = B, max_blocks
-        n_in = 3 * B + B * max_blocks
+        n_in = 8 * B + B * max_blocks
         pin = device.type == "cuda"
         self.host_in = torch.zeros(n_in, dtype=torch.int32, pin_memory=pin)
         self.dev_in = torch.zeros(n_in, dtype=torch.int32, device=device)
-        self.host_out = torch.zeros(B + 2, dtype=torch.int32, pin_memory=pin)
-        self.dev_out = torch.zeros(B + 2, dtype=torch.int32, device=device)
+        self.host_out = torch.zeros(B + N_RESULT_EXTRA, dtype=torch.int32, pin_memory=pin)
+        self.dev_out = torch.zeros(B + N_RESULT_EXTRA, dtype=torch.int32, device=device)
         self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.graph = None          # one step, host-fed
-        self.graph_loop = None     # one step + device-side token feedback
+        self.graphs = {}           # (feedback, sampling) -> captured step
         self.np_views = None
         self.host_in[B:2 * B] = -1
+        self.host_in[5 * B:6 * B].view(torch.float32).fill_(1.0)     # top_p
 
     def views(self, buf):
+        """(token ids, positions, seq_lens, block table) views of a staging buffer."""
         B, mb = self.B, self.max_blocks
-        return buf[:B], buf[B:2 * B], buf[2 * B:3 * B], buf[3 * B:].view(B, mb)
+        return buf[:B], buf[B:2 * B], buf[2 * B:3 * B], buf[8 * B:].view(B, mb)
+
+    def sampling_views(self, buf):
+        """(temperature fp32, top_k int32, top_p fp32, seeds int64) views of a staging buffer."""
+        B = self.B
+        return (buf[3 * B:4 * B].view(torch.float32), buf[4 * B:5 * B], buf[5 * B:6 * B].view(torch.float32),
+                buf[6 * B:8 * B].view(torch.int64))
 
     @property
     def h2d_bytes(self):
@@ -56,6 +71,15 @@ class _Bucket:
     @property
     def d2h_bytes(self):
         return self.host_out.numel() * 4
+
+    # kept for callers that hold one graph per kind
+    @property
+    def graph(self):
+        return self.graphs.get((False, False))
+
+    @property
+    def graph_loop(self):
+        return self.graphs.get((True, False))
 
 
 class ModelRunner:
@@ -68,6 +92,7 @@ class ModelRunner:
         self.buckets: dict[int, _Bucket] = {}
         self.graph_captures = 0
         self.graph_replays = 0
+        self.last_wait_ns = 0      # running total of the device-side peer-wait counter, as of the last synchronised step
 
     # ---- decode -----------------------------------------------------------------------------------
     def bucket(self, n: int) -> _Bucket:
@@ -77,40 +102,49 @@ class ModelRunner:
             bk = self.buckets[B] = _Bucket(B, self.max_blocks, self.device)
         return bk
 
-    def _decode_body(self, bk: _Bucket, feedback: bool):
+    def _decode_body(self, bk: _Bucket, feedback: bool, sampling: bool = False):
         tok, pos, lens, bt = bk.views(bk.dev_in)
         inp = BatchInputs(token_ids=tok, positions=pos, block_table=bt, seq_lens=lens, ctx_hint=self.ctx_hint)
-        sampled, _ = self.dec.forward(inp)
+        smp = None
+        if sampling:
+            t, k, p, seeds = bk.sampling_views(bk.dev_in)
+            smp = SamplingInputs(t, k, p, seeds, bk.step_counter)
+        sampled, _ = self.dec.forward(inp, sampling=smp)
         bk.dev_out[:bk.B].copy_(sampled)
         if self.device.type == "cuda":
             bk.dev_out[bk.B:].copy_(ops.workspace().status)
-        if feedback:
-            ops.advance_decode_state(sampled, tok, pos, lens, bk.step_counter)
+        if feedback or sampling:
+            # the step counter also drives the sampler's random stream
+            ops.advance_decode_state(sampled, tok, pos, lens, bk.step_counter) if feedback else bk.step_counter.add_(1)
 
-    def _ensure_graph(self, bk: _Bucket, feedback: bool):
-        attr = "graph_loop" if feedback else "graph"
-        if getattr(bk, attr) is not None:
-            return getattr(bk, attr)
+    def _ensure_graph(self, bk: _Bucket, feedback: bool, sampling: bool = False):
+        key = (feedback, sampling)
+        g = bk.graphs.get(key)
+        if g is not None:
+            return g
         # eager warm-up allocates workspaces and descriptor caches outside the capture
         saved = bk.dev_in.clone()
-        self._decode_body(bk, False)
+        saved_step = bk.step_counter.clone()
+        self._decode_body(bk, False, sampling)
         torch.cuda.synchronize()
         bk.dev_in.copy_(saved)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._decode_body(bk, feedback)
+            self._decode_body(bk, feedback, sampling)
         torch.cuda.synchronize()
         bk.dev_in.copy_(saved)  # the capture itself does not run, but keep the inputs pristine
+        bk.step_counter.copy_(saved_step)
         self.graph_captures += 1
-        setattr(bk, attr, g)
+        bk.graphs[key] = g
         return g
 
-    def load_decode_inputs(self, bk: _Bucket, tokens, positions, seq_lens, block_tables):
-        """Fill the pinned staging buffer from host lists (rows beyond len(tokens) are padding)."""
+    def load_decode_inputs(self, bk: _Bucket, tokens, positions, seq_lens, block_tables, sampling=None):
+        """Fill the pinned staging buffer from host lists (rows beyond len(tokens) are padding). `sampling` is a
+        list of (temperature, top_k, top_p, seed) per row, or None for an all-greedy step."""
         n = len(tokens)
         if bk.np_views is None:   # numpy views share the pinned buffer: no tensor objects per row on the hot path
-            bk.np_views = tuple(v.numpy() for v in bk.views(bk.host_in))
-        t, p, l, bt = bk.np_views
+            bk.np_views = tuple(v.numpy() for v in bk.views(bk.host_in)) + tuple(v.numpy() for v in bk.sampling_views(bk.host_in))
+        t, p, l, bt, st, sk, sp, ss = bk.np_views
         t[:n] = tokens
         p[:n] = positions
         l[:n] = seq_lens
@@ -119,20 +153,29 @@ class ModelRunner:
         l[n:] = 0
         for i, row in enumerate(block_tables):
             bt[i, :len(row)] = row
+        if sampling is not None:
+            st[:n] = [s[0] for s in sampling]
+            sk[:n] = [s[1] for s in sampling]
+            sp[:n] = [s[2] for s in sampling]
+            ss[:n] = [s[3] for s in sampling]
+            st[n:] = 0.0
+        else:
+            st[:] = 0.0
 
-    def decode_step(self, bk: _Bucket, sync: bool = True):
+    def decode_step(self, bk: _Bucket, sync: bool = True, sampling: bool = False):
         """H2D of the staged inputs, one step, D2H of the result. Returns the host result view."""
         bk.dev_in.copy_(bk.host_in, non_blocking=True)
         if self.use_graphs:
-            self._ensure_graph(bk, False).replay()
+            self._ensure_graph(bk, False, sampling).replay()
             self.graph_replays += 1
         else:
-            self._decode_body(bk, False)
+            self._decode_body(bk, False, sampling)
         bk.host_out.copy_(bk.dev_out, non_blocking=True)
         if sync and self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
             if int(bk.host_out[bk.B]) != 0:
                 ops.workspace().check_status()
+            self.last_wait_ns = int(bk.host_out[bk.B + 2:bk.B + 4].view(torch.int64)[0])
         return bk.host_out[:bk.B]
 
     def decode_loop_step(self, bk: _Bucket):
@@ -144,9 +187,10 @@ class ModelRunner:
             self._decode_body(bk, True)
 
     # ---- prefill ----------------------------------------------------------------------------------
-    def prefill(self, seqs, want_logits: bool = False):
+    def prefill(self, seqs, want_logits: bool = False, sampling=None):
         """seqs: list of (new_token_ids, block_table_row, cached_len). Runs one eager chunk holding every new
-        token of every listed sequence. Returns greedy next tokens (host list) [and logits]."""
+        token of every listed sequence. Returns the next token of every sequence (host list) [and logits]; greedy
+        unless `sampling` gives (temperature, top_k, top_p, seed) per sequence."""
         dev = self.device
         toks, pos, sot, qs, ql, kl, rows = [], [], [], [], [], [], []
         S = len(seqs)
@@ -160,6 +204,13 @@ class ModelRunner:
         inp = BatchInputs(token_ids=i32(toks), positions=i32(pos), block_table=bt.to(dev), seq_lens=i32(kl),
                           is_prefill=True, seq_of_token=i32(sot), q_start=i32(qs), q_len=i32(ql), max_q_len=max(ql),
                           logit_rows=torch.tensor(rows, dtype=torch.int64, device=dev))
-        tok, lg = self.dec.forward(inp)
+        smp = None
+        if sampling is not None and any(s[0] > 0 for s in sampling) and dev.type == "cuda":
+            smp = SamplingInputs(torch.tensor([s[0] for s in sampling], dtype=torch.float32, device=dev),
+                                 i32([s[1] for s in sampling]),
+                                 torch.tensor([s[2] for s in sampling], dtype=torch.float32, device=dev),
+                                 torch.tensor([s[3] for s in sampling], dtype=torch.int64, device=dev),
+                                 torch.zeros(1, dtype=torch.int32, device=dev))
+        tok, lg = self.dec.forward(inp, sampling=smp)
         out = tok.cpu().tolist()
         return (out, lg) if want_logits else out

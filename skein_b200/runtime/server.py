@@ -1,10 +1,12 @@
 """HTTP front end: POST /v1/completions (JSON or SSE token stream), GET /metrics, GET /healthz.
 
-    POST /v1/completions   {"prompt": str | [int], "max_tokens": int, "stream": bool}
+    POST /v1/completions   {"prompt": str | [int], "max_tokens": int, "stream": bool,
+                            "temperature": float, "top_k": int, "top_p": float, "seed": int}   (sampling optional)
         stream=false -> {"id", "tokens", "text", "finish_reason"}
         stream=true  -> text/event-stream with `event: token` / data {"id", "token", "text", "is_final"}
         429 when admission rejects the request, 400 on a malformed body
     GET /metrics           Prometheus text of the engine's instruments
+    POST /admin/hotswap    {"artifact": path} (only with hot swap enabled): verify, drain, mount on every rank
 
 One driver thread owns the engine and steps it whenever work exists; request handlers talk to it
 through a thread-safe inbox and receive token events on per-request asyncio queues. The same wire
@@ -16,92 +18,16 @@ from __future__ import annotations
 
 import asyncio
 import json
-import queue
 import threading
-import time
 
-from .engine import Engine, TokenEvent
+from .driver import EngineDriver
+from .engine import Engine, SamplingParams
 from .tokenizer import Tokenizer
 
-
-class EngineDriver:
-    """Runs `engine.step()` on its own thread. Thread-safe `submit` returns an event queue."""
-
-    def __init__(self, engine: Engine, idle_sleep_s: float = 0.001):
-        self.engine = engine
-        self._inbox: "queue.Queue" = queue.Queue()
-        self._streams: dict[int, "queue.Queue[TokenEvent]"] = {}
-        self._stop = threading.Event()
-        self._idle_sleep = idle_sleep_s
-        self._thread = threading.Thread(target=self._run, name="skein-engine-driver", daemon=True)
-        self.draining = False
-
-    def start(self):
-        self._thread.start()
-        return self
-
-    def stop(self, timeout: float = 5.0):
-        self._stop.set()
-        self._thread.join(timeout)
-
-    def submit(self, prompt_ids, max_new_tokens):
-        """Returns (request_id, decision_kind, reason, event_queue or None). Blocks until the driver has decided."""
-        reply: "queue.Queue" = queue.Queue(maxsize=1)
-        self._inbox.put((prompt_ids, max_new_tokens, reply))
-        return reply.get()
-
-    @property
-    def inflight(self) -> int:
-        return len(self._streams)
-
-    def drain(self, timeout_s: float) -> bool:
-        """Stop admitting, wait for in-flight requests to finish. True if drained in time."""
-        self.draining = True
-        t0 = time.monotonic()
-        while self._streams and time.monotonic() - t0 < timeout_s:
-            time.sleep(0.005)
-        ok = not self._streams
-        if not ok:
-            self.draining = False     # timeout: keep serving on the old state
-        return ok
-
-    def _run(self):
-        eng = self.engine
-        while not self._stop.is_set():
-            try:
-                while True:
-                    prompt, max_new, reply = self._inbox.get_nowait()
-                    if self.draining:
-                        reply.put((0, "reject", "draining", None))
-                        continue
-                    try:
-                        rid, d = eng.submit(prompt, max_new)
-                    except ValueError as e:
-                        reply.put((0, "reject", str(e), None))
-                        continue
-                    if d.kind == "reject":
-                        reply.put((rid, "reject", d.reason, None))
-                    else:
-                        q: "queue.Queue[TokenEvent]" = queue.Queue()
-                        self._streams[rid] = q
-                        reply.put((rid, d.kind, d.reason, q))
-            except queue.Empty:
-                pass
-            if eng.idle:
-                time.sleep(self._idle_sleep)
-                continue
-            events = eng.step()
-            if not events:
-                time.sleep(self._idle_sleep)
-            for ev in events:
-                q = self._streams.get(ev.request_id)
-                if q is not None:
-                    q.put(ev)
-                    if ev.is_final:
-                        del self._streams[ev.request_id]
+__all__ = ["EngineDriver", "build_app", "serve", "serve_metrics_only"]
 
 
-def build_app(driver: EngineDriver, tokenizer: Tokenizer):
+def build_app(driver: EngineDriver, tokenizer: Tokenizer, hotswap=None, artifacts_root=None):
     from aiohttp import web
 
     async def next_event(q):
@@ -117,10 +43,16 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer):
             ids = tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
             if not ids or max_tokens < 1:
                 raise ValueError("empty prompt or max_tokens < 1")
+            sampling = None
+            if float(body.get("temperature", 0.0)) > 0.0:
+                sampling = SamplingParams(temperature=float(body["temperature"]), top_k=int(body.get("top_k", 0)),
+                                          top_p=float(body.get("top_p", 1.0)), seed=int(body.get("seed", 0)))
+                if not (0.0 < sampling.top_p <= 1.0) or sampling.top_k < 0:
+                    raise ValueError("top_p must be in (0, 1] and top_k >= 0")
         except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
             return web.json_response({"error": {"kind": "bad_request", "message": str(e)}}, status=400)
         loop = asyncio.get_running_loop()
-        rid, kind, reason, q = await loop.run_in_executor(None, driver.submit, ids, max_tokens)
+        rid, kind, reason, q = await loop.run_in_executor(None, driver.submit, ids, max_tokens, sampling)
         if kind == "reject":
             return web.json_response({"error": {"kind": "rejected", "message": reason}}, status=429)
         if stream:
@@ -156,20 +88,41 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer):
     async def healthz(_):
         return web.json_response({"ok": True, "inflight": driver.inflight, "draining": driver.draining})
 
+    async def admin_hotswap(request: "web.Request"):
+        from .hotswap import HotSwapError
+        try:
+            path = (await request.json())["artifact"]
+        except (KeyError, TypeError, json.JSONDecodeError) as e:
+            return web.json_response({"error": {"kind": "bad_request", "message": str(e)}}, status=400)
+        loop = asyncio.get_running_loop()
+        try:
+            new = await loop.run_in_executor(None, hotswap.swap, path, artifacts_root)
+        except (HotSwapError, OSError, ValueError) as e:
+            return web.json_response({"error": {"kind": "hotswap_failed", "message": str(e)}}, status=409)
+        return web.json_response({"mounted": str(new.path)})
+
     app = web.Application()
+    if hotswap is not None:
+        app.router.add_post("/admin/hotswap", admin_hotswap)
     app.router.add_post("/v1/completions", completions)
     app.router.add_get("/metrics", metrics)
     app.router.add_get("/healthz", healthz)
     return app
 
 
-def serve(engine: Engine, tokenizer: Tokenizer, host: str = "0.0.0.0", port: int = 8080):
-    """Blocking: start the driver and the HTTP server."""
+def serve(engine: Engine, tokenizer: Tokenizer, host: str = "0.0.0.0", port: int = 8080, mounted=None,
+          enable_hot_swap: bool = False, artifacts_root=None):
+    """Blocking: start the driver and the HTTP server. With `enable_hot_swap`, POST /admin/hotswap replaces the
+    weights of `mounted` (an Artifact) by those of another artifact with the same shapes."""
     from aiohttp import web
 
     driver = EngineDriver(engine).start()
+    hs = None
+    if enable_hot_swap and mounted is not None:
+        from .hotswap import HotSwap
+        hs = HotSwap(driver, mounted)
     try:
-        web.run_app(build_app(driver, tokenizer), host=host, port=port, print=None)
+        web.run_app(build_app(driver, tokenizer, hs, artifacts_root), host=host, port=port, print=None)
     finally:
         driver.stop()
 

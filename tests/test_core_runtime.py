@@ -37,7 +37,11 @@ def test_prefix_reuse_refcounts_and_lru_eviction():
     kv = core.KvBlockManager(6, 4, True)
     a = list(range(10))                                # 2 full pages + 2 tokens
     pa = kv.admit(1, a)
-    assert pa.prefix_hit_tokens == 0 and pa.registered_pages == 2
+    assert pa.prefix_hit_tokens == 0 and pa.registered_pages == 0
+    # pages that are reserved but not computed yet are invisible to other requests
+    assert kv.try_prefix_reuse(a) == 0
+    assert kv.mark_computed(1, a, 5) == 1 and kv.try_prefix_reuse(a) == 4
+    assert kv.mark_computed(1, a, 10) == 2
     pb = kv.admit(2, a[:8] + [99, 98, 97])             # shares the two full pages
     assert pb.prefix_hit_tokens == 8 and pb.pages[:2] == pa.pages[:2] and pb.pages[2] != pa.pages[2]
     assert kv.in_use_pages == 4 and kv.prefix_hit_tokens_total == 8
@@ -64,8 +68,30 @@ def test_radix_hit_rate_on_shared_system_prompt():
     for i in range(8):
         pt = kv.admit(i, system + [i, i + 1, i + 2])
         hits += pt.prefix_hit_tokens
+        kv.mark_computed(i, system + [i, i + 1, i + 2], 67)
         kv.release(i)
     assert hits == 7 * 64
+
+
+def test_failed_request_and_cleared_cache_leave_no_stale_prefix():
+    kv = core.KvBlockManager(8, 4, True)
+    a = list(range(12))
+    kv.admit(1, a)
+    kv.mark_computed(1, a, 8)                          # two pages computed, then the step fails
+    kv.release(1, True)
+    assert kv.try_prefix_reuse(a) == 0 and kv.available_pages == 8
+    # a page shared with a live request survives the failure of the other one
+    kv.admit(2, a); kv.mark_computed(2, a, 12)
+    pb = kv.admit(3, a + [50])
+    assert pb.prefix_hit_tokens == 12
+    kv.release(3, True)
+    assert kv.try_prefix_reuse(a + [50]) == 12
+    kv.release(2)
+    # new weights: everything cached is forgotten, the pages are free again
+    kv.clear_prefix_cache()
+    assert kv.try_prefix_reuse(a + [50]) == 0 and kv.available_pages == 8
+    kv.admit(4, a); kv.mark_computed(4, a, 12)
+    assert kv.try_prefix_reuse(a + [50]) == 12
 
 
 # ---- batcher --------------------------------------------------------------------------------------------------------
@@ -93,7 +119,10 @@ def test_batch_life_cycle_with_kv_and_chunked_prefill():
     assert kv.in_use_pages == 5 + 2
     pre, dec = b.next_step_batch()
     assert pre == [(1, 0, 32, False), (2, 0, 16, False)] and dec == []      # 48-token budget shared in order
+    # a request with the same prompt arriving now shares only what request 1 has computed so far
+    assert kv.try_prefix_reuse(list(range(70))) == 0
     b.prefill_advanced(1, 32); b.prefill_advanced(2, 16)
+    assert kv.try_prefix_reuse(list(range(70))) == 32
     pre, dec = b.next_step_batch()
     assert pre == [(1, 32, 64, False), (2, 16, 20, True)]
     b.prefill_advanced(1, 64); b.prefill_advanced(2, 20)

@@ -49,6 +49,40 @@ def test_prefix_cache_and_chunked_prefill_do_not_change_outputs_cpu():
     assert "skein_prefix_cache_hit_tokens_total 96" in eng.metrics.render()
 
 
+def test_same_prefix_in_flight_together_with_chunked_prefill_cpu():
+    """Two requests with one prefix, admitted in the same iteration, prefilling in chunks: the second must not attend
+    over pages that the first has reserved but not written yet."""
+    cfg, dec = _decoder()
+    system = _prompts(cfg, 1, [64], seed=5)[0]
+    prompts = [system + tail for tail in _prompts(cfg, 2, [6, 11], seed=6)]
+    plain = Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, prefix_cache=False)).generate(prompts, 4)
+    cfg, dec = _decoder()
+    eng = Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, prefix_cache=True, chunk_tokens=16))
+    assert eng.generate(prompts, 4) == plain
+    # afterwards the prefix is cached and a third request uses it
+    third = system + [1, 2, 3]
+    want = Engine(_decoder()[1], EngineConfig(max_batch=1, tpot_ms=1e6, use_graphs=False, prefix_cache=False)).generate([third], 3)
+    assert eng.generate([third], 3) == want and eng.kv.prefix_hit_tokens_total >= 64
+
+
+def test_failed_step_does_not_poison_the_prefix_cache_cpu():
+    cfg, dec = _decoder()
+    prompt = _prompts(cfg, 1, [50], seed=8)[0]
+    want = Engine(dec, EngineConfig(max_batch=1, tpot_ms=1e6, use_graphs=False, prefix_cache=False)).generate([prompt], 4)
+    cfg, dec = _decoder()
+    eng = Engine(dec, EngineConfig(max_batch=2, tpot_ms=1e6, use_graphs=False, prefix_cache=True, chunk_tokens=16))
+
+    def boom(step):
+        if step == 1:
+            raise RuntimeError("injected step failure")
+    eng.failure_injector = boom
+    eng.submit(prompt, 4)
+    eng.run_until_done()                                        # first chunk ran, second iteration failed
+    eng.failure_injector = None
+    assert eng.kv.try_prefix_reuse(prompt) == 0                 # nothing of the dropped request stays matchable
+    assert eng.generate([prompt], 4) == want
+
+
 def test_delay_then_admit_and_reject_cpu():
     cfg, dec = _decoder()
     eng = Engine(dec, EngineConfig(max_batch=1, tpot_ms=1e6, use_graphs=False, prefill_per_token_us=25.0, ttft_ms=1.0))
