@@ -19,7 +19,9 @@
  *     the capacity is refused with SKEIN_NOALLOC_ERR_TOO_LARGE and touches nothing.
  *   - The function calls no cudaMalloc / cudaFree and no allocating library routine. The first call on a
  *     device looks up the device address of the built-in scratch (one cudaGetSymbolAddress per array, with
- *     that device current) and remembers it; make that first call outside any CUDA stream capture.
+ *     that device current) and remembers it; make that first call outside any CUDA stream capture. Two host
+ *     threads that make their first call on the same device at the same time both perform the look-up and
+ *     both store the same address (a benign double write of one pointer-sized value; no lock is taken).
  *   - All calls on a device share the one scratch array, and it keeps whatever the previous call left in
  *     it. Each call clears the arrival counters on `stream` before launching. Two calls whose kernels can
  *     overlap on the GPU (different streams, or different host threads without ordering) race on the

@@ -614,7 +614,7 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   if (p->stages > 0 && p->stages < st) st = p->stages;
   if (st < 2) return -7;
   ka->stages = st;
-  ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : 2000) * 1000000ull;
+  ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : gemm_wait_budget_ms()) * 1000000ull;
   *grid = p->grid > 0 ? p->grid : sm_count_cached();
   if (*grid > sm_count_cached()) *grid = sm_count_cached();   // the split-K reduction needs every CTA resident
   *smem = (size_t)st * ka->stage_bytes + 1024;

@@ -19,6 +19,7 @@
 // with per-tensor scales (host/cublaslt/mod.rs:1050-1071).
 #include "gemm_sched.cuh"
 #include "ptx.cuh"
+#include "launch.cuh"
 #include <cuda_runtime.h>
 
 namespace skein {
@@ -327,7 +328,7 @@ extern "C" int skein_gemm_ws_fp8(const SkeinGemmParams* p, void* stream) {
   ka.buf_cols = acc < 32 ? 32 : acc;
   ka.n_bufs = 512 / ka.buf_cols;
   if (ka.n_bufs > F8_MAX_BUFS) ka.n_bufs = F8_MAX_BUFS;
-  ka.budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : 2000) * 1000000ull;
+  ka.budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : gemm_wait_budget_ms()) * 1000000ull;
   const int grid = p->grid > 0 ? p->grid : skein_sm_count();
   const size_t smem = (size_t)st * ka.stage_bytes + 1024;
   CUtensorMap tmW, tmX;

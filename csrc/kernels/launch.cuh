@@ -30,6 +30,17 @@ inline bool pdl_enabled() {
   return on == 1;
 }
 
+// Wait budgets of the kernels that wait on other CTAs of their own launch, in milliseconds, from the environment
+// (set as a group through RuntimeConfig: grid_barrier_ms, gemm_wait_ms). Read once per process.
+inline int env_ms(const char* name, int fallback) {
+  const char* e = getenv(name);
+  if (e == nullptr || *e == 0) return fallback;
+  const long v = strtol(e, nullptr, 10);
+  return (v > 0 && v < 3600000) ? (int)v : fallback;
+}
+inline int grid_barrier_budget_ms() { static int v = env_ms("SKEIN_GRID_BARRIER_MS", 2000); return v; }
+inline int gemm_wait_budget_ms() { static int v = env_ms("SKEIN_GEMM_WAIT_MS", 2000); return v; }
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args&&... args) {

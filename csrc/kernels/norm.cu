@@ -442,7 +442,7 @@ extern "C" int skein_reduce_norm_route(
   r.wg = (const __nv_bfloat16*)wg; r.expert_ids = expert_ids; r.expert_w = expert_w; r.counts = counts;
   r.offsets = offsets; r.row_of = row_of; r.src_token = src_token; r.xs = (__nv_bfloat16*)xs; r.barrier = barrier;
   r.E = E; r.topk = topk; r.e_first = e_first; r.e_count = e_count;
-  r.barrier_budget_ns = 2000ull * 1000000ull;
+  r.barrier_budget_ns = (unsigned long long)grid_barrier_budget_ms() * 1000000ull;
   int threads = (H / 8 + 31) / 32 * 32;
   if (threads > 512) threads = 512;
   const int passes = (H + threads * 8 - 1) / (threads * 8);

@@ -100,10 +100,13 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
 }
 
 // temperature[b] <= 0 means greedy. top_k[b] in [1, 64] (0 -> 64). top_p[b] in (0, 1].
+// The draw of row b comes from splitmix64(seed[b] ^ splitmix64(counter + 1)) with counter = step[b * step_stride]:
+// one counter for the whole batch (stride 0) or one per row (stride 1: the token's position, which makes a
+// request's random stream a function of its seed and position only, whatever else is in the batch).
 __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
                                                                  int V, const float* temperature, const int* top_k,
                                                                  const float* top_p, const unsigned long long* seeds,
-                                                                 const int* step, int* __restrict__ out_idx) {
+                                                                 const int* step, int step_stride, int* __restrict__ out_idx) {
   __shared__ ValIdx sh[32];
   __shared__ float cand_v[64];
   __shared__ int cand_i[64];
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const __nv_bfloa
     }
     float kept = 0.f;
     for (int k = 0; k < keep; ++k) kept += pr[k];
-    const unsigned long long s = splitmix64((seeds ? seeds[b] : 0x1234ull) ^ splitmix64((unsigned long long)(step ? *step : 0) + 1));
+    const unsigned long long s = splitmix64((seeds ? seeds[b] : 0x1234ull) ^ splitmix64((unsigned long long)(step ? step[(size_t)b * step_stride] : 0) + 1));
     const float u = (float)((s >> 40) & 0xFFFFFF) / 16777216.0f * kept;
     float run = 0.f;
     int pick = cand_i[keep - 1];
@@ -196,9 +199,9 @@ extern "C" int skein_merge_candidates(const float* cand_val, const int* cand_idx
 
 extern "C" int skein_sample_topk_topp(const void* logits, long long ld, int B, int V, const float* temperature,
                                       const int* top_k, const float* top_p, const unsigned long long* seeds,
-                                      const int* step, int* out_idx, void* stream) {
+                                      const int* step, int step_stride, int* out_idx, void* stream) {
   if (B == 0) return 0;
   skein::sample_topk_topp_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V, temperature,
-                                                                       top_k, top_p, seeds, step, out_idx);
+                                                                       top_k, top_p, seeds, step, step_stride, out_idx);
   return (int)cudaGetLastError();
 }

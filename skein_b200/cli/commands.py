@@ -94,8 +94,12 @@ def cmd_verify(args, emit) -> int:
     if args.hf_reference:
         if args.reference_dtype not in ("bfloat16", "float32"):
             raise ValueError("reference dtype must be bfloat16 or float32")
-        refw = ref_art.load_full_weights(args.device)
-        reference = parity.DenseForward(art.cfg, refw)
+        reference = None
+        if args.hf_checkpoint:      # HuggingFace transformers on the original checkpoint: the outside oracle
+            reference = parity.HFForward(args.hf_checkpoint, args.reference_dtype)
+        if reference is None:       # no checkpoint given: the in-process dense model on the artifact's bf16 weights
+            refw = ref_art.load_full_weights(args.device)
+            reference = parity.DenseForward(art.cfg, refw)
     else:
         reference = parity.ArtifactForward(ref_art, args.device)
     tol = json.loads(core.cost_constants_json(_read(args.cost))).get("parity_tolerance_mse", {})

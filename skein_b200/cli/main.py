@@ -62,6 +62,8 @@ def build_parser() -> argparse.ArgumentParser:
     v.add_argument("--cost", default="cluster/cost_constants.toml")
     v.add_argument("--enforce", action="store_true")
     v.add_argument("--hf-reference", action="store_true", help="compare against the cache-free dense oracle on the bf16 weights")
+    v.add_argument("--hf-checkpoint", default=None,
+                   help="with --hf-reference: checkpoint directory (config.json + safetensors) to run through HuggingFace transformers")
     v.add_argument("--reference-dtype", default="bfloat16")
     v.add_argument("--dump-only", action="store_true")
     v.add_argument("--tokens-file", default=None)

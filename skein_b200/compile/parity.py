@@ -10,6 +10,7 @@ the pipeline.
 Forwards are anything with `run(prompt_ids) -> (hidden_after_block list of [T, H] fp32, final_logits [V] fp32)`:
   ArtifactForward   a compiled artifact run through the runtime's decoder (candidate, or its reference_bf16)
   DenseForward      the cache-free straight-line model (the "HF-style" oracle)
+  HFForward         HuggingFace transformers on the original checkpoint (the outside oracle)
   and the fakes used by the tests (offset / tilted forwards).
 
 Counterpart of crates/skein_parity/src/verify.rs:46-315, comparison.rs:16-72, tolerance.rs:14-57, report.rs:10-36,
@@ -77,6 +78,36 @@ class DenseForward:
         hid = []
         logits = dense_reference.forward_full(self.cfg, self.w, torch.tensor(prompt_ids), capture_hidden=hid)
         return [h.float().cpu() for h in hid], logits[-1].float().cpu()
+
+
+class HFForward:
+    """The HuggingFace `transformers` implementation of the model as the oracle: loads a checkpoint directory
+    (config.json + safetensors) with AutoModelForCausalLM, runs the prompt in fp32 (or bf16) and returns the residual
+    stream after every decoder layer and the last position's logits. This is the one reference that is not written
+    by the same hand as the kernels: it pins the RoPE convention, the router's renormalisation and the GQA head
+    order from outside. Role of the reference's verify_reference.py subprocess
+    (crates/skein_parity/src/reference.rs:65-104, crates/skein_parity/reference/verify_reference.py)."""
+
+    def __init__(self, checkpoint_dir, dtype: str = "float32"):
+        try:
+            import transformers
+        except ImportError as e:     # the caller falls back to the in-process dense oracle
+            raise RuntimeError("the `transformers` package is not installed") from e
+        td = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        self.model = transformers.AutoModelForCausalLM.from_pretrained(str(checkpoint_dir), dtype=td).eval()
+
+    @torch.no_grad()
+    def run(self, prompt_ids):
+        hid, hooks = [], []
+        for layer in self.model.model.layers:
+            hooks.append(layer.register_forward_hook(
+                lambda _m, _i, out: hid.append((out[0] if isinstance(out, tuple) else out)[0].float().cpu())))
+        try:
+            out = self.model(input_ids=torch.tensor([list(prompt_ids)], dtype=torch.long), use_cache=False)
+        finally:
+            for h in hooks:
+                h.remove()
+        return hid, out.logits[0, -1].float().cpu()
 
 
 class DecoderForward:

@@ -131,7 +131,7 @@ class SamplingInputs:
     top_k: torch.Tensor                # [B] int32 (0: the kernel's maximum of 64 candidates)
     top_p: torch.Tensor                # [B] fp32 in (0, 1]
     seeds: torch.Tensor                # [B] int64: one random stream per request
-    step: torch.Tensor                 # [1] int32: position in the stream, advanced once per step
+    step: torch.Tensor                 # [B] int32: counter of each row's random stream (the token's position)
 
 
 class Decoder:
@@ -332,4 +332,4 @@ class Decoder:
             lg = full[:, :self.cfg.vocab_size].contiguous()
         n = lg.shape[0]
         return ops.sample(lg, sampling.temperature[:n], sampling.top_k[:n], sampling.top_p[:n], sampling.seeds[:n],
-                          sampling.step)
+                          sampling.step[:n])

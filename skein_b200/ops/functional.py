@@ -603,7 +603,8 @@ def sample_argmax(logits, idx_offset=0, out=None, out_val=None):
 
 
 def sample(logits, temperature, top_k, top_p, seeds, step, out=None):
-    """Temperature / top-k / top-p sampling; per-row parameters are device tensors."""
+    """Temperature / top-k / top-p sampling; per-row parameters are device tensors. `step` is the counter of the
+    random stream: one int32 for the whole batch, or one per row (the token's position)."""
     if not logits.is_cuda:
         return ref.sample(logits, temperature, top_k, top_p, seeds, step)
     B, V = logits.shape
@@ -611,7 +612,8 @@ def sample(logits, temperature, top_k, top_p, seeds, step, out=None):
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
     rc = _lib.lib().skein_sample_topk_topp(logits.data_ptr(), logits.stride(0), B, V, _lib.ptr(temperature),
                                            _lib.ptr(top_k), _lib.ptr(top_p), _lib.ptr(seeds), _lib.ptr(step),
-                                           out.data_ptr(), _lib.stream_ptr())
+                                           0 if (step is None or step.numel() == 1) else 1, out.data_ptr(),
+                                           _lib.stream_ptr())
     _lib.check(rc, "sample")
     _lib.count_launch()
     return out

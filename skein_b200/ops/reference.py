@@ -214,7 +214,7 @@ def sample(logits, temperature, top_k, top_p, seeds, step):
     import numpy as np
     lf = logits.float()
     B, V = lf.shape
-    st = int(step.reshape(-1)[0]) if step is not None else 0
+    steps = [0] * B if step is None else ([int(step.reshape(-1)[0])] * B if step.numel() == 1 else [int(x) for x in step[:B]])
     out = []
     f32 = np.float32
     for b in range(B):
@@ -244,7 +244,7 @@ def sample(logits, temperature, top_k, top_p, seeds, step):
         for k in range(keep):
             kept = f32(kept + pr[k])
         seed = (int(seeds[b]) & _M64) if seeds is not None else 0x1234
-        s64 = _splitmix64(seed ^ _splitmix64((st + 1) & _M64))
+        s64 = _splitmix64(seed ^ _splitmix64((steps[b] + 1) & _M64))
         u = f32(f32(f32((s64 >> 40) & 0xFFFFFF) / f32(16777216.0)) * kept)
         run, pick = f32(0), order[keep - 1]
         for k in range(keep):

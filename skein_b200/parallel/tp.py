@@ -13,8 +13,10 @@ Two buffers alternate: a rank can only be one all-reduce ahead of the slowest pe
 finish all-reduce k+1 without that peer's flag, which the peer sets only after it has consumed (read)
 all-reduce k; so nobody overwrites a buffer that is still being read.
 
-NCCL mode (large prefill chunks, or SKEIN_COMM=nccl as the un-fused baseline): the same math with
-a library all-reduce between the local GEMM and the reduce kernel.
+Comparison arms: SKEIN_COMM=unfused keeps the data path but takes the fusion out (GEMM stores to ordinary
+memory, a copy kernel publishes, the reduce kernel pulls; still capturable into the step's CUDA graph, so
+graph-against-graph it shows what the publish epilogue saves); SKEIN_COMM=nccl replaces the whole exchange by
+a library all-reduce between the local GEMM and the reduce kernel, launched eagerly.
 
 The stand-alone collectives (all_reduce, all_gather, reduce_scatter, all_to_all) are the same two steps
 without a GEMM in front: copy into the published buffer and raise the flags, then one pull kernel
@@ -54,12 +56,12 @@ class PeerPartials:
 
 class TPComm:
     def __init__(self, group, device, hidden: int, fused_rows: int = 512, max_batch: int = 256, mode: str | None = None,
-                 wait_budget_ms: int = 10000, multimem: bool | None = None):
+                 wait_budget_ms: int | None = None, multimem: bool | None = None):
         self.group, self.device = group, device
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
         self.hidden, self.fused_rows, self.max_batch = hidden, fused_rows, max_batch
         self.mode = mode or os.environ.get("SKEIN_COMM", "fused")
-        self.wait_budget_ms = wait_budget_ms
+        self.wait_budget_ms = wait_budget_ms if wait_budget_ms is not None else int(os.environ.get("SKEIN_PEER_WAIT_MS", "10000"))
         N = self.size
         buf_bytes = fused_rows * hidden * 2
         heap_bytes = 2 * buf_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
@@ -67,7 +69,7 @@ class TPComm:
         # kernels sum the ranks' partials with one multimem load. Off by default: a rank that dies while bound
         # faults its peers, and the plain peer loads are what the failure-handling tests exercise.
         self.multimem = (os.environ.get("SKEIN_MULTIMEM", "0") == "1") if multimem is None else bool(multimem)
-        self.heap = SymmetricHeap(group, device, heap_bytes, multicast=self.multimem and self.mode == "fused")
+        self.heap = SymmetricHeap(group, device, heap_bytes, multicast=self.multimem and self.mode in ("fused", "unfused"))
         h = self.heap
         self.buf_off = [h.alloc(buf_bytes) for _ in range(2)]
         self.flag_off = [h.alloc(256) for _ in range(2)]
@@ -110,7 +112,15 @@ class TPComm:
 
     # ---- row-parallel projection + all-reduce ------------------------------------------------------
     def _fused_ok(self, rows: int) -> bool:
-        return self.mode == "fused" and rows <= self.fused_rows
+        return self.mode in ("fused", "unfused") and rows <= self.fused_rows
+
+    def _publish(self, y: torch.Tensor, b: int) -> None:
+        """Copy a finished [rows, H] result into this rank's peer-mapped buffer `b` and raise the flags (one launch)."""
+        rc = _lib.lib().skein_publish_rows(y.data_ptr(), y.numel() * 2, self.bufs[b].data_ptr(), self._push_flag[b],
+                                           self.size, self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
+                                           _lib.stream_ptr())
+        _lib.check(rc, "publish_rows")
+        _lib.count_launch()
 
     def linear_push(self, x, w, grouped=None):
         """Returns (partial, flags, epoch) for ops.reduce_residual_rmsnorm: peer partials in fused mode, else the
@@ -122,8 +132,14 @@ class TPComm:
             return y.unsqueeze(0), None, None
         b = self.cur
         self.cur ^= 1
-        ops.linear_push(x, w, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
-                        self.hidden, grouped=grouped, wait_budget_ms=0)
+        if self.mode == "unfused":
+            # comparison arm: the same data path without the fusion. The GEMM stores into ordinary memory, a second
+            # kernel copies the result into the published buffer and raises the flags; the consumer pulls as usual.
+            y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
+            self._publish(y, b)
+        else:
+            ops.linear_push(x, w, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+                            self.hidden, grouped=grouped, wait_budget_ms=0)
         part = self._partials(b, rows)
         return part, part.flags, part.epoch
 
@@ -137,8 +153,12 @@ class TPComm:
             return y.unsqueeze(0), None, None
         b = self.cur
         self.cur ^= 1
-        fp8.linear_publish(xq, xs, w8, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
-                           self.hidden, grouped=grouped, rows_hint=rows_hint)
+        if self.mode == "unfused":
+            y = fp8.grouped_linear(xq, xs, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear(xq, xs, w8)
+            self._publish(y, b)
+        else:
+            fp8.linear_publish(xq, xs, w8, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+                               self.hidden, grouped=grouped, rows_hint=rows_hint)
         part = self._partials(b, rows)
         return part, part.flags, part.epoch
 
@@ -151,12 +171,7 @@ class TPComm:
             return y
         b = self.cur
         self.cur ^= 1
-        x = x.contiguous()
-        rc = _lib.lib().skein_publish_rows(x.data_ptr(), x.numel() * 2, self.bufs[b].data_ptr(), self._push_flag[b],
-                                           self.size, self.epochs[b:b + 1].data_ptr(), self.done[b:b + 1].data_ptr(),
-                                           _lib.stream_ptr())
-        _lib.check(rc, "publish_rows")
-        _lib.count_launch()
+        self._publish(x.contiguous(), b)
         out, _ = ops.reduce_residual_rmsnorm(None, self._partials(b, rows), None, 0.0,
                                              wait_budget_ms=self.wait_budget_ms)
         return out
@@ -181,7 +196,7 @@ class TPComm:
 
     def _pull_ok(self, x: torch.Tensor, chunk_bytes: int) -> bool:
         nbytes = x.numel() * x.element_size()
-        return (self.mode == "fused" and x.is_cuda and 0 < nbytes <= self.bufs[0].numel() * 2 and nbytes % 16 == 0
+        return (self.mode in ("fused", "unfused") and x.is_cuda and 0 < nbytes <= self.bufs[0].numel() * 2 and nbytes % 16 == 0
                 and chunk_bytes % 16 == 0)
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:

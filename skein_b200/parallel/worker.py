@@ -64,7 +64,7 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
         from .pp import PipelineStage
         dec = PipelineStage(dec, lay, *pp_info)
     batching = art.plan["batching"]
-    fused = all(c is None or c.mode == "fused" for c in (comm, comm_moe))
+    fused = all(c is None or c.mode != "nccl" for c in (comm, comm_moe))
     ecfg = EngineConfig(max_batch=args.max_batch or batching["max_batch"], chunk_tokens=batching.get("chunk_tokens", 0),
                         prefix_cache=art.plan["execution"]["prefix_cache"]["enable"],
                         # stage-to-stage NCCL p2p and library collectives are launched eagerly, never captured

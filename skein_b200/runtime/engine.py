@@ -201,6 +201,10 @@ class Engine:
 
     def _run(self, prefill, decode, now) -> list[TokenEvent]:
         events: list[TokenEvent] = []
+        t_begin = time.perf_counter()
+        # a token's time stamp is the step's clock plus the time the step has taken so far, so that TTFT and TPOT
+        # include the step that produced the token
+        stamp = lambda: now + int((time.perf_counter() - t_begin) * 1000)
         if prefill:
             seqs = []
             for rid, start, end, last in prefill:
@@ -210,7 +214,7 @@ class Engine:
             for (rid, start, end, last), tok in zip(prefill, toks):
                 self.batcher.prefill_advanced(rid, end)
                 if last:
-                    events.append(self._accept(rid, tok, now))
+                    events.append(self._accept(rid, tok, stamp()))
         if decode:
             pos = self.batcher.decode_positions(decode)
             toks_in = [self._last[rid] for rid in decode]
@@ -220,8 +224,9 @@ class Engine:
             rows = self._rows(decode)
             self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables, sampling=rows)
             out = self.runner.decode_step(bk, sampling=rows is not None)
+            t_tok = stamp()
             for i, rid in enumerate(decode):
-                events.append(self._accept(rid, int(out[i]), now))
+                events.append(self._accept(rid, int(out[i]), t_tok))
         return events
 
     def _accept(self, rid, tok, now) -> TokenEvent:

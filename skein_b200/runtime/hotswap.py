@@ -62,8 +62,8 @@ class HotSwap:
         self.driver, self.mounted, self.rank, self.drain_timeout_s = driver, mounted, rank, drain_timeout_s
 
     def swap(self, new_path, out_root=None) -> Artifact:
-        new = Artifact(new_path)
         try:
+            new = Artifact(new_path)
             verify_shape_compatibility(self.mounted, new)
         except ArtifactError as e:
             raise HotSwapError(f"rejected: {e}") from e

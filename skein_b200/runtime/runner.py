@@ -108,14 +108,13 @@ class ModelRunner:
         smp = None
         if sampling:
             t, k, p, seeds = bk.sampling_views(bk.dev_in)
-            smp = SamplingInputs(t, k, p, seeds, bk.step_counter)
+            smp = SamplingInputs(t, k, p, seeds, pos)      # the random stream is indexed by the token's position
         sampled, _ = self.dec.forward(inp, sampling=smp)
         bk.dev_out[:bk.B].copy_(sampled)
         if self.device.type == "cuda":
             bk.dev_out[bk.B:].copy_(ops.workspace().status)
-        if feedback or sampling:
-            # the step counter also drives the sampler's random stream
-            ops.advance_decode_state(sampled, tok, pos, lens, bk.step_counter) if feedback else bk.step_counter.add_(1)
+        if feedback:
+            ops.advance_decode_state(sampled, tok, pos, lens, bk.step_counter)
 
     def _ensure_graph(self, bk: _Bucket, feedback: bool, sampling: bool = False):
         key = (feedback, sampling)
@@ -124,7 +123,6 @@ class ModelRunner:
             return g
         # eager warm-up allocates workspaces and descriptor caches outside the capture
         saved = bk.dev_in.clone()
-        saved_step = bk.step_counter.clone()
         self._decode_body(bk, False, sampling)
         torch.cuda.synchronize()
         bk.dev_in.copy_(saved)
@@ -133,7 +131,6 @@ class ModelRunner:
             self._decode_body(bk, feedback, sampling)
         torch.cuda.synchronize()
         bk.dev_in.copy_(saved)  # the capture itself does not run, but keep the inputs pristine
-        bk.step_counter.copy_(saved_step)
         self.graph_captures += 1
         bk.graphs[key] = g
         return g
@@ -205,12 +202,12 @@ class ModelRunner:
                           is_prefill=True, seq_of_token=i32(sot), q_start=i32(qs), q_len=i32(ql), max_q_len=max(ql),
                           logit_rows=torch.tensor(rows, dtype=torch.int64, device=dev))
         smp = None
-        if sampling is not None and any(s[0] > 0 for s in sampling) and dev.type == "cuda":
+        if sampling is not None and any(s[0] > 0 for s in sampling):
             smp = SamplingInputs(torch.tensor([s[0] for s in sampling], dtype=torch.float32, device=dev),
                                  i32([s[1] for s in sampling]),
                                  torch.tensor([s[2] for s in sampling], dtype=torch.float32, device=dev),
                                  torch.tensor([s[3] for s in sampling], dtype=torch.int64, device=dev),
-                                 torch.zeros(1, dtype=torch.int32, device=dev))
+                                 i32([n - 1 for n in kl]))
         tok, lg = self.dec.forward(inp, sampling=smp)
         out = tok.cpu().tolist()
         return (out, lg) if want_logits else out

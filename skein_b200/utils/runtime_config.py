@@ -35,7 +35,7 @@ def _bool(v) -> bool:
 
 # field -> (environment variable, parser, allowed values or None)
 _FIELDS = {
-    "comm": ("SKEIN_COMM", str, ("fused", "nccl")),
+    "comm": ("SKEIN_COMM", str, ("fused", "unfused", "nccl")),
     "multimem": ("SKEIN_MULTIMEM", _bool, None),
     "profile": ("SKEIN_PROFILE", int, (0, 1, 2, 3)),
     "attn_decode": ("SKEIN_ATTN_DECODE", str, ("mma", "scalar")),
@@ -47,6 +47,9 @@ _FIELDS = {
     "pack_moe": ("SKEIN_PACK_MOE", _bool, None),
     "pdl": ("SKEIN_PDL", _bool, None),
     "tune_cache": ("SKEIN_TUNE_CACHE", str, None),
+    "grid_barrier_ms": ("SKEIN_GRID_BARRIER_MS", int, None),
+    "gemm_wait_ms": ("SKEIN_GEMM_WAIT_MS", int, None),
+    "peer_wait_ms": ("SKEIN_PEER_WAIT_MS", int, None),
 }
 
 
@@ -64,6 +67,9 @@ class RuntimeConfig:
     pack_moe: bool = True          # tile-packed expert weights
     pdl: bool = False              # programmatic dependent launch between the per-layer kernels
     tune_cache: str = ""           # kernel-configuration cache to load ("" = the artifact's own, if any)
+    grid_barrier_ms: int = 2000    # budget of the grid-wide arrival counter in the fused reduce + router kernel
+    gemm_wait_ms: int = 2000       # budget of the GEMM's pipeline waits and of its wait for the other pieces of a split tile
+    peer_wait_ms: int = 10000      # budget of a reduce kernel's wait for a tensor-parallel peer's flag
 
     def __post_init__(self):
         for name, (_, _, allowed) in _FIELDS.items():
@@ -72,8 +78,11 @@ class RuntimeConfig:
                 raise RuntimeConfigError(f"runtime.{name} = {v!r}: expected one of {list(allowed)}")
         if not 0 <= self.attn_splits <= 16:
             raise RuntimeConfigError(f"runtime.attn_splits = {self.attn_splits}: expected 0..16")
-        if self.multimem and self.comm != "fused":
-            raise RuntimeConfigError("runtime.multimem needs runtime.comm = \"fused\"")
+        for name in ("grid_barrier_ms", "gemm_wait_ms", "peer_wait_ms"):
+            if not 1 <= getattr(self, name) <= 3600000:
+                raise RuntimeConfigError(f"runtime.{name} = {getattr(self, name)}: expected 1..3600000 milliseconds")
+        if self.multimem and self.comm == "nccl":
+            raise RuntimeConfigError("runtime.multimem needs runtime.comm = \"fused\" (or \"unfused\")")
 
     # ---- sources -----------------------------------------------------------------------------------------------
     @classmethod

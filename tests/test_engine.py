@@ -145,3 +145,68 @@ def test_engine_gpu_graphs_equal_cpu_reference():
     agree = sum(g == w for g, w in zip(got, want))
     assert agree >= 4, (got, want)                             # one near-tie flip is tolerated
     assert eng.runner.graph_replays > 0
+
+
+def test_sampling_through_the_engine_cpu():
+    """temperature / top-k / top-p / seed reach the sampler: a seed fixes the stream, temperature 0 stays greedy,
+    top_k = 1 is greedy whatever the temperature, and a greedy request in the same batch is not disturbed."""
+    from skein_b200.runtime.engine import SamplingParams
+    cfg, dec = _decoder()
+    prompts = _prompts(cfg, 2, [12, 20], seed=11)
+    eng = Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, prefix_cache=False))
+    greedy = eng.generate(prompts, 6)
+    hot = SamplingParams(temperature=1.5, top_k=50, top_p=0.95, seed=7)
+    a = eng.generate(prompts, 6, sampling=hot)
+    b = eng.generate(prompts, 6, sampling=hot)
+    c = eng.generate(prompts, 6, sampling=SamplingParams(temperature=1.5, top_k=50, top_p=0.95, seed=8))
+    assert a == b and a != greedy and c != a
+    assert eng.generate(prompts, 6, sampling=SamplingParams(temperature=1.5, top_k=1, seed=3)) == greedy
+    assert eng.generate(prompts, 6, sampling=SamplingParams(temperature=0.0, seed=3)) == greedy
+    # mixed batch: request 1 samples, request 2 is greedy and must produce the greedy tokens
+    r1, _ = eng.submit(prompts[0], 6, sampling=hot)
+    r2, _ = eng.submit(prompts[1], 6)
+    out = eng.run_until_done()
+    assert out[r2] == greedy[1] and out[r1] == a[0]
+
+
+def test_long_prompt_is_interleaved_with_decoding_cpu():
+    """A prompt that arrives while another sequence decodes is prefilled in slices of interleave_prefill_tokens, so
+    the decoding sequence gets a token every step; the outputs do not change."""
+    cfg, dec = _decoder()
+    short, long = _prompts(cfg, 1, [8], seed=1)[0], _prompts(cfg, 1, [90], seed=2)[0]
+    plain = Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, prefix_cache=False,
+                                     interleave_prefill_tokens=0)).generate([short, long], 8)
+    cfg, dec = _decoder()
+    eng = Engine(dec, EngineConfig(max_batch=4, tpot_ms=1e6, use_graphs=False, prefix_cache=False, interleave_prefill_tokens=32))
+    a, _ = eng.submit(short, 8)
+    eng.step()                                   # the short request prefills and starts decoding
+    b, _ = eng.submit(long, 8)
+    per_step = []
+    out = {a: [plain[0][0]], b: []}
+    while not eng.idle:
+        evs = eng.step()
+        per_step.append(sorted(e.request_id for e in evs))
+        for e in evs:
+            out[e.request_id].append(e.token)
+    assert per_step[0] == [a] and per_step[1] == [a] and per_step[2] == [a, b]     # 90 tokens = 3 slices of 32
+    assert out[a] == plain[0] and out[b] == plain[1]
+
+
+@pytest.mark.gpu
+def test_engine_gpu_sampling_graph_is_reproducible_and_keeps_greedy_rows():
+    from skein_b200.runtime.engine import SamplingParams
+    cfg, dec = _decoder("cuda", seed=7)
+    prompts = _prompts(cfg, 3, [20, 7, 33], seed=9)
+    eng = Engine(dec, EngineConfig(max_batch=8, tpot_ms=1e6, use_graphs=True, prefix_cache=False))
+    greedy = eng.generate(prompts, 5)
+    hot = SamplingParams(temperature=1.4, top_k=40, top_p=0.9, seed=21)
+    a = eng.generate(prompts, 5, sampling=hot)
+    b = eng.generate(prompts, 5, sampling=hot)
+    assert a == b and a != greedy
+    r1, _ = eng.submit(prompts[0], 5, sampling=hot)
+    r2, _ = eng.submit(prompts[1], 5)
+    out = eng.run_until_done()
+    assert out[r2] == greedy[1] and out[r1] == a[0]
+    assert eng.runner.graph_captures >= 2            # the greedy and the sampling variant of a bucket
+    from skein_b200 import ops
+    torch.cuda.synchronize(); ops.workspace().check_status()

@@ -85,3 +85,49 @@ def test_packed_weight_round_trip_and_in_place_update():
     import pytest
     with pytest.raises(ValueError):
         ops.pack_weight(torch.zeros(100, 64))
+
+
+def test_heartbeat_stops_while_a_step_is_stuck(tmp_path):
+    """The beat follows the step loop: a rank that has been inside one step for longer than the limit looks dead to
+    the monitor although its process (and the beating thread) is alive; an idle rank keeps beating."""
+    started = {"t": None}
+    hb = Heartbeat(str(tmp_path), 0, 0.02, step_started_at=lambda: started["t"], stall_limit_s=0.1).start()
+    mon = Monitor(str(tmp_path), 1, interval_s=0.02, missed_beats=5)
+    try:
+        time.sleep(0.3)
+        assert mon.dead_ranks() == []                   # idle: beats
+        time.sleep(0.15)
+        assert mon.dead_ranks() == []
+        started["t"] = time.monotonic()                 # a step begins and never ends
+        time.sleep(0.5)
+        mon.dead_ranks()
+        time.sleep(0.2)
+        assert mon.dead_ranks() == [0]
+        started["t"] = None                             # the step finished after all
+        time.sleep(0.2)
+        assert mon.dead_ranks() == []
+    finally:
+        hb.stop()
+
+
+def test_speculative_decoding_with_a_draft_model_equals_target_greedy():
+    """A draft Decoder proposes, the target Decoder verifies k + 1 positions in one chunk over its paged KV cache: with
+    temperature 0 the output is the target's greedy decode for a good and for a useless draft."""
+    from skein_b200.models import config as mc
+    from skein_b200.models.decoder import Decoder, random_weights
+    from skein_b200.runtime.engine import Engine, EngineConfig
+
+    cfg = mc.tiny_mixtral()
+    mk = lambda c, seed: Decoder(c, random_weights(c, mc.ParallelLayout(), "cpu", seed=seed, std=0.05), num_pages=32, page_size=16, max_pos=256)
+    prompt = list(range(5, 25))
+    want = Engine(mk(cfg, 0), EngineConfig(max_batch=1, tpot_ms=1e6, use_graphs=False, prefix_cache=False)).generate([prompt], 12)[0]
+    out, st = sp.SpeculativeDecoder(mk(cfg, 0), mk(cfg, 0), k=3).generate(prompt, 12)
+    assert out == want and st["accepted"] == st["proposed"] and st["target_steps"] <= 5      # 4 tokens per target step
+    small = mc.tiny_mixtral(layers=1)
+    out, st = sp.SpeculativeDecoder(mk(cfg, 0), mk(small, 3), k=3).generate(prompt, 12)
+    assert out == want and st["accepted"] < st["proposed"]
+    # with a temperature the rule samples from the target: same seed, same tokens; the draft being the target
+    # itself, every proposal is accepted
+    a, sa = sp.SpeculativeDecoder(mk(cfg, 0), mk(cfg, 0), k=3).generate(prompt, 10, temperature=0.9, seed=4)
+    b, _ = sp.SpeculativeDecoder(mk(cfg, 0), mk(cfg, 0), k=3).generate(prompt, 10, temperature=0.9, seed=4)
+    assert a == b and len(a) == 10 and sa["accepted"] == sa["proposed"]

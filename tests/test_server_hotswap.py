@@ -121,3 +121,51 @@ def test_hot_swap_reject_drain_and_timeout(tmp_path):
         assert driver.submit([9], 1)[1] in ("admit", "delay")
     finally:
         driver.stop()
+
+
+def test_hot_swap_over_http_forgets_cached_prefixes_and_swaps_fp8_weights(tmp_path):
+    """POST /admin/hotswap (serve --enable-hot-swap): after the swap the same prompt is answered by the new weights
+    from scratch, although its prefix was cached under the old ones; block-scaled fp8 tensors are swapped too."""
+    from aiohttp.test_utils import TestClient, TestServer
+
+    a = make_artifact(tmp_path / "a", seed=0)
+    b = make_artifact(tmp_path / "b", seed=1)
+    eng = make_engine(a, prefix_cache=True)
+    driver = EngineDriver(eng).start()
+    prompt = list(range(3, 43))                                    # 40 tokens: two full pages are cacheable
+    fresh_b = make_engine(b, prefix_cache=False).generate([prompt], 5)[0]
+
+    async def scenario():
+        async with TestClient(TestServer(build_app(driver, Tokenizer(300), HotSwap(driver, a), tmp_path))) as c:
+            r1 = await (await c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 5})).json()
+            r1b = await (await c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 5})).json()
+            assert r1["tokens"] == r1b["tokens"] and eng.kv.prefix_hit_tokens_total == 32
+            bad = await c.post("/admin/hotswap", json={"artifact": str(tmp_path / "nope")})
+            assert bad.status == 409
+            ok = await c.post("/admin/hotswap", json={"artifact": str(b.path)})
+            assert ok.status == 200 and (await ok.json())["mounted"] == str(b.path)
+            assert eng.kv.try_prefix_reuse(prompt) == 0            # KV computed with the old weights is unreachable
+            r2 = await (await c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 5})).json()
+            assert r2["tokens"] == fresh_b and r2["tokens"] != r1["tokens"]
+            # sampling parameters travel through the API; a seed fixes the stream
+            s1 = await (await c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 5, "temperature": 1.3, "top_k": 40, "seed": 5})).json()
+            s2 = await (await c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 5, "temperature": 1.3, "top_k": 40, "seed": 5})).json()
+            assert s1["tokens"] == s2["tokens"] and s1["tokens"] != r2["tokens"]
+            assert (await c.post("/v1/completions", json={"prompt": prompt, "temperature": 1.0, "top_p": 1.5})).status == 400
+
+    try:
+        asyncio.run(asyncio.wait_for(scenario(), 120))
+    finally:
+        driver.stop()
+    assert (tmp_path / "LATEST").is_symlink()
+    # fp8 blocks are copied in place as well
+    from skein_b200.models.decoder import quantize_blocks
+    from skein_b200.runtime.hotswap import _copy_into
+    wa, wb = a.load_weights(0, "cpu"), b.load_weights(0, "cpu")
+    quantize_blocks(wa, [0], names=("w13",)); quantize_blocks(wb, [0], names=("w13",))
+    q_before = wa.layers[0].fp8["w13"].q.clone()
+    wa.layers[0].fp8["w13"].copy_(wb.layers[0].fp8["w13"])
+    assert not torch.equal(q_before.view(torch.uint8), wa.layers[0].fp8["w13"].q.view(torch.uint8))
+    assert torch.equal(wa.layers[0].fp8["w13"].q.view(torch.uint8), wb.layers[0].fp8["w13"].q.view(torch.uint8))
+    with pytest.raises(HotSwapError):
+        _copy_into(None, wb.layers[0].wqkv)
