@@ -276,7 +276,8 @@ def main():
                 if c is not None:
                     c.close()
         if tp > 1:
-            comm = TPComm(tp_group, dev, hidden=cfg.hidden_size)
+            # room for the partials of one 8192-token prefill chunk (its expert-sorted rows for a MoE model)
+            comm = TPComm(tp_group, dev, hidden=cfg.hidden_size, fused_rows=max(512, 8192 * max(1, cfg.top_k if cfg.is_moe else 1)))
         if ep > 1:   # communicator over all tp x ep ranks for the expert-parallel combine
             comm_moe = TPComm(dist.group.WORLD, dev, hidden=cfg.hidden_size)
     lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
@@ -284,7 +285,7 @@ def main():
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1
     num_pages = B * blocks_per_seq + 8
     t0 = time.time()
-    weights = random_weights(cfg, lay, dev, seed=0, std=0.02)
+    weights = random_weights(cfg, lay, dev, seed=0, std=0.02, shard_embed=True)    # vocabulary-parallel embedding under TP
     if args.fp8_experts:
         from skein_b200.models.decoder import quantize_blocks
         quantize_blocks(weights, range(len(weights.layers)), names=("w13", "w2"))
@@ -385,7 +386,7 @@ def main():
     unfused_ms = None
     if world > 1 and not args.no_unfused and use_graphs and all(c is None or c.mode == "fused" for c in (comm, comm_moe)):
         from skein_b200.parallel.tp import TPComm
-        u1 = TPComm(comm.group, dev, hidden=cfg.hidden_size, mode="unfused", multimem=comm.multimem) if comm is not None else None
+        u1 = TPComm(comm.group, dev, hidden=cfg.hidden_size, mode="unfused", multimem=comm.multimem, max_batch=comm.max_batch) if comm is not None else None
         u2 = TPComm(comm_moe.group, dev, hidden=cfg.hidden_size, mode="unfused", multimem=comm_moe.multimem) if comm_moe is not None else None
         dec_u = Decoder(cfg, weights, lay, num_pages=0, page_size=ps, max_pos=P + Gn + 64, comm=u1, comm_moe=u2)
         dec_u.kv, dec_u.num_pages = dec.kv, dec.num_pages          # same weights, same cache

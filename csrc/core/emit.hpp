@@ -7,7 +7,8 @@
 // handoff.rs:23-211, segment.rs:55-87, io_manifest.rs:17-45, lib.rs:58-71), with the differences this
 // runtime has: expert parallelism is token-routed (all-to-all dispatch and combine, as the
 // reference's cost model and docs describe but its executor rejects), experts are owned in contiguous
-// blocks, the embedding is replicated, and sampling exchanges (value, index) candidates.
+// blocks, and sampling exchanges (value, index) candidates. The embedding table is vocabulary-parallel as in the
+// reference (its lookups are summed by an all-reduce that the first RMSNorm carries).
 #pragma once
 #include "cost.hpp"
 
@@ -31,9 +32,9 @@ inline ParamRole param_kind_for(const std::string& name) {
     r.expert_column = !has(".w2.");
     return r;
   }
-  if (has("q_proj") || has("k_proj") || has("v_proj") || has("gate_proj") || has("up_proj") || has("lm_head")) r.kind = ParamKind::ColumnParallel;
+  if (has("q_proj") || has("k_proj") || has("v_proj") || has("gate_proj") || has("up_proj") || has("lm_head") || has("embed_tokens")) r.kind = ParamKind::ColumnParallel;
   else if (has("o_proj") || has("down_proj")) r.kind = ParamKind::RowParallel;
-  return r;  // norms, router gate, embedding: replicated
+  return r;  // norms, router gate: replicated (the embedding table is split by vocabulary rows like lm_head)
 }
 
 struct ShardSlice {
@@ -94,6 +95,9 @@ inline std::vector<TopologyEntry> emit_topology(const Plan& plan, const Graph& i
   auto add = [&](const char* kind, std::vector<size_t> parts, std::string tensor, std::vector<uint64_t> shape, Dtype dt, std::string after, bool fused) {
     out.push_back({seq++, kind, std::move(parts), std::move(tensor), std::move(after), dtype_name(dt), std::move(shape), fused});
   };
+  if (pl.tp > 1)
+    for (uint32_t e = 0; e < pl.ep; ++e)
+      add("ring_allreduce", tp_group_of_stage(0, e, pl), "embed_out", {B, 1, H}, plan_act_dtype(plan, 0), "embed_tokens", true);
   for (size_t b = 0; b < ir.meta.num_layers; ++b) {
     const uint32_t stage = block_to_stage(b, ir.meta.num_layers, pl.pp);
     const Dtype ad = plan_act_dtype(plan, b);
@@ -180,7 +184,12 @@ inline LoweredDevice lower_device(const Plan& plan, const Graph& ir, size_t devi
     cur = Segment{d.segments.size(), "segment_" + std::to_string(d.segments.size()), {tensor}, {}, {}};
   };
   bool first_on_stage = true;
-  if (stage == 0) { cur.inputs.push_back(handoff_input_tokens()); cur.ops.push_back("embed_tokens"); }
+  if (stage == 0) {
+    cur.inputs.push_back(handoff_input_tokens());
+    cur.ops.push_back("embed_tokens");
+    // vocabulary-parallel table: the ranks' lookups are summed before the first norm
+    if (pl.tp > 1) cut("ring_allreduce", handoff_embed_out(), pl.tp_group(device));
+  }
   for (size_t b = 0; b < ir.meta.num_layers; ++b) {
     if (block_to_stage(b, ir.meta.num_layers, pl.pp) != stage) continue;
     if (first_on_stage && stage > 0) {

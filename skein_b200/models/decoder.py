@@ -66,8 +66,9 @@ def shard_shapes(cfg: ModelConfig, lay: ParallelLayout):
 
 
 def random_weights(cfg: ModelConfig, lay: ParallelLayout, device, seed: int = 0, std: float = 0.02,
-                   dtype=torch.bfloat16) -> ModelWeights:
-    """Random-init weights N(0, std) of this rank's shard shapes (norm gains are 1, as HF initialises them)."""
+                   dtype=torch.bfloat16, shard_embed: bool = False) -> ModelWeights:
+    """Random-init weights N(0, std) of this rank's shard shapes (norm gains are 1, as HF initialises them).
+    shard_embed: the embedding table holds only this rank's vocabulary rows (tensor parallelism)."""
     sh = shard_shapes(cfg, lay)
     g = torch.Generator(device=device)
     g.manual_seed(seed * 1000003 + lay.rank)
@@ -89,7 +90,7 @@ def random_weights(cfg: ModelConfig, lay: ParallelLayout, device, seed: int = 0,
             wo=rnd(H, sh["Hq"] * D), ffn_norm=torch.ones(H, dtype=dtype, device=device), router=router, w13=w13, w2=w2))
     first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
     return ModelWeights(
-        embed=rnd(cfg.vocab_size, H) if first else None, layers=layers,
+        embed=rnd(sh["V_local"] if (shard_embed and lay.tp > 1) else cfg.vocab_size, H) if first else None, layers=layers,
         final_norm=torch.ones(H, dtype=dtype, device=device) if last else None,
         lm_head=rnd(sh["V_local"], H) if last else None)
 
@@ -159,6 +160,13 @@ class Decoder:
         self.kv = [torch.zeros(num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
                    for _ in weights.layers] if num_pages > 0 else []
         self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
+        # vocabulary-parallel embedding: when the table holds only this rank's rows (models/sharding.py, random_weights
+        # with shard_embed), the first row it owns; None for a replicated table
+        self.embed_vocab_start = None
+        if (weights.embed is not None and comm is not None and comm.size > 1 and weights.embed.shape[0] != cfg.vocab_size):
+            if weights.embed.shape[0] > self.sh["V_local"]:      # the last rank's shard may be short
+                raise ValueError("the embedding table is neither whole nor this rank's vocabulary shard")
+            self.embed_vocab_start = self.layout.tp_rank * self.sh["V_local"]
         if pack_moe is None:
             pack_moe = os.environ.get("SKEIN_PACK_MOE", "1") == "1"
         if pack_moe and dev.type == "cuda":
@@ -269,13 +277,19 @@ class Decoder:
         """Runs this stage's blocks. Returns (residual stream [T, H], normed [T, H]) where `normed` is the final
         norm on the last stage and the next stage's first attn_norm input otherwise (None)."""
         cfg = self.cfg
-        if hidden_in is None:
-            residual = ops.embed(inp.token_ids, self.w.embed)
-        else:
-            residual = hidden_in
         layers = self.w.layers
-        normed = ops.rmsnorm(residual, layers[0].attn_norm, cfg.rms_norm_eps)
+        if hidden_in is None and self.embed_vocab_start is not None:
+            # table sharded by vocabulary rows: the ranks' lookups are summed inside the first RMSNorm
+            residual, normed = self.comm.embed_reduce(inp.token_ids, self.w.embed, self.embed_vocab_start,
+                                                      layers[0].attn_norm, cfg.rms_norm_eps)
+        else:
+            residual = ops.embed(inp.token_ids, self.w.embed) if hidden_in is None else hidden_in
+            normed = ops.rmsnorm(residual, layers[0].attn_norm, cfg.rms_norm_eps)
         last_stage = self.w.final_norm is not None
+        T = residual.shape[0]
+        if (inp.is_prefill and self.comm is not None and self.comm.size > 1 and self.layout.ep == 1 and residual.is_cuda
+                and hasattr(self.comm, "sp_ok") and self.comm.sp_ok(T, T * max(1, cfg.top_k if cfg.is_moe else 1))):
+            return self._forward_hidden_sp(inp, residual, normed, last_stage)
         for li, lw in enumerate(layers):
             attn = self._attention(li, normed, inp)
             part, flags, epoch = self._row_parallel(attn, lw, "wo")
@@ -304,6 +318,43 @@ class Decoder:
             if self.capture_hidden is not None:
                 self.capture_hidden.append(residual.detach().float().cpu())
         return residual, normed
+
+    def _forward_hidden_sp(self, inp: BatchInputs, residual, normed, last_stage: bool):
+        """Prefill-sized chunks under tensor parallelism: sequence-parallel between the projections. The row-parallel
+        GEMMs (o_proj, down) publish their partials; every rank reduces, adds the residual and normalises only its
+        own slice of the token rows (reduce-scatter fused with residual + RMSNorm, peer loads or the in-switch
+        reduction), the residual stream stays sharded by rows from layer to layer, and the normalised slices are
+        gathered into local memory for the next column-parallel GEMM (parallel/tp.py). No library collective runs.
+        The reference keeps activations replicated and all-reduces twice per block through NCCL
+        (crates/skein_emit/src/handoff.rs:104-211, crates/skein_runtime/src/cuda/nccl.rs:196-245)."""
+        cfg, comm, layers = self.cfg, self.comm, self.w.layers
+        T = residual.shape[0]
+        r0, n, _ = comm.sp_slice(T)
+        res_loc = residual[r0:r0 + n].contiguous()
+        for li, lw in enumerate(layers):
+            attn = self._attention(li, normed, inp)
+            part, _, _ = self._row_parallel(attn, lw, "wo")
+            res_loc, normed_loc = comm.reduce_scatter_norm(res_loc, part, lw.ffn_norm, cfg.rms_norm_eps, T)
+            normed = comm.gather_rows(normed_loc, T)
+            part, _, _, row_idx, row_w = self._ffn(li, normed, None)
+            if li + 1 < len(layers):
+                next_gamma = layers[li + 1].attn_norm
+            else:
+                next_gamma = self.w.final_norm if last_stage else None
+            res_loc, normed_loc = comm.reduce_scatter_norm(res_loc, part, next_gamma, cfg.rms_norm_eps, T, row_idx, row_w)
+            normed = comm.gather_rows(normed_loc, T) if next_gamma is not None else None
+            if self.capture_hidden is not None:
+                self.capture_hidden.append(self._gather_residual(res_loc, T).float().cpu())
+        residual = self._gather_residual(res_loc, T) if not last_stage else None
+        return residual, normed
+
+    def _gather_residual(self, res_loc, T):
+        """The full residual stream from its row slices (only where a whole copy is needed: the hand-off to the next
+        pipeline stage, the parity gate's per-layer capture)."""
+        _, n, per = self.comm.sp_slice(T)
+        pad = torch.zeros(per, res_loc.shape[1], dtype=res_loc.dtype, device=res_loc.device)
+        pad[:n] = res_loc
+        return self.comm.gather_rows(pad, T)
 
     def logits(self, normed, inp: BatchInputs):
         """Logits of this rank's vocabulary shard for the rows that need them."""

@@ -4,8 +4,8 @@ Roles follow the reference's shard_role table (crates/skein_emit/src/shard_role.
 stage first, then expert ownership, then tensor parallelism; column-parallel q/k/v/w1/w3/lm_head,
 row-parallel o/w2), with two differences: experts are owned in contiguous blocks
 (expert e lives on ep rank e // (E / ep)) so that a rank's experts form one slice of the stacked
-weight, and the embedding table is replicated instead of vocabulary-sharded (it is small next to
-180 GB and saves an all-reduce per step).
+weight. The embedding table is vocabulary-sharded on request (`shard_embed`; the decoder then sums the ranks'
+lookups inside its first RMSNorm) and replicated otherwise.
 """
 from __future__ import annotations
 
@@ -42,8 +42,10 @@ def shard_layer(lw: LayerWeights, cfg: ModelConfig, lay: ParallelLayout) -> Laye
     return LayerWeights(attn_norm=lw.attn_norm, wqkv=wqkv, wo=wo, ffn_norm=lw.ffn_norm, router=router, w13=w13, w2=w2)
 
 
-def shard_model(full: ModelWeights, cfg: ModelConfig, lay: ParallelLayout, device=None) -> ModelWeights:
-    """full holds every block (pp = tp = ep = 1 shapes). Returns the shard of `lay.rank`, moved to `device`."""
+def shard_model(full: ModelWeights, cfg: ModelConfig, lay: ParallelLayout, device=None, shard_embed: bool = False) -> ModelWeights:
+    """full holds every block (pp = tp = ep = 1 shapes). Returns the shard of `lay.rank`, moved to `device`.
+    shard_embed: vocabulary-parallel embedding table (this rank's rows, zero-padded to the common shard size), whose
+    lookups the decoder sums inside its first RMSNorm; otherwise the table is replicated."""
     sh = shard_shapes(cfg, lay)
     stage = lay.stage_layers(cfg.num_layers)
     first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
@@ -58,5 +60,10 @@ def shard_model(full: ModelWeights, cfg: ModelConfig, lay: ParallelLayout, devic
                                       ("attn_norm", "wqkv", "wo", "ffn_norm", "router", "w13", "w2")}))
     v0 = lay.tp_rank * sh["V_local"]
     lm = full.lm_head[v0:v0 + sh["V_local"]].contiguous() if last else None
-    return ModelWeights(embed=mv(full.embed) if first else None, layers=layers,
+    emb = full.embed
+    if shard_embed and lay.tp > 1 and first:
+        emb = torch.zeros(sh["V_local"], full.embed.shape[1], dtype=full.embed.dtype)
+        rows = full.embed[v0:v0 + sh["V_local"]]
+        emb[:rows.shape[0]] = rows
+    return ModelWeights(embed=mv(emb) if first else None, layers=layers,
                         final_norm=mv(full.final_norm) if last else None, lm_head=mv(lm))

@@ -57,6 +57,14 @@ class BarrierComm:
     def all_reduce(self, x):
         return torch.stack([v.float() for v in self._exchange(x)]).sum(0).to(x.dtype)
 
+    def embed_reduce(self, ids, table_shard, vocab_start, gamma, eps):
+        """Vocabulary-parallel embedding: each rank looks up the rows it owns (zeros elsewhere), the sum is the row."""
+        x = self.all_reduce(ops.embed(ids, table_shard, vocab_start))
+        return x, ops.rmsnorm(x, gamma, eps)
+
+    def all_gather(self, x):
+        return torch.cat(self._exchange(x), dim=0)
+
     def vocab_parallel_argmax(self, logits, v_local):
         return ops.sample_argmax(torch.cat(self._exchange(logits), dim=1))
 

@@ -38,7 +38,7 @@ def teacher_forced_check(world: int, rank: int, dev, comm=None, comm_moe=None, t
         cfg.num_kv_heads = heads
     full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=seed, std=0.05)
     lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
-    w = shard_model(full, cfg, lay, dev)
+    w = shard_model(full, cfg, lay, dev, shard_embed=comm is not None and tp > 1)    # vocabulary-parallel embedding
     if fp8_experts:
         from ..models.decoder import quantize_blocks
         quantize_blocks(w, range(len(w.layers)), names=("w13", "w2"))

@@ -56,15 +56,21 @@ class PeerPartials:
 
 class TPComm:
     def __init__(self, group, device, hidden: int, fused_rows: int = 512, max_batch: int = 256, mode: str | None = None,
-                 wait_budget_ms: int | None = None, multimem: bool | None = None):
+                 wait_budget_ms: int | None = None, multimem: bool | None = None, sp_min_rows: int = 512,
+                 embed_rows: int | None = None):
         self.group, self.device = group, device
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
         self.hidden, self.fused_rows, self.max_batch = hidden, fused_rows, max_batch
+        self.sp_min_rows = sp_min_rows     # chunks with more token rows than this are sharded by rows between projections
         self.mode = mode or os.environ.get("SKEIN_COMM", "fused")
         self.wait_budget_ms = wait_budget_ms if wait_budget_ms is not None else int(os.environ.get("SKEIN_PEER_WAIT_MS", "10000"))
         N = self.size
         buf_bytes = fused_rows * hidden * 2
-        heap_bytes = 2 * buf_bytes + 4 * 256 + 2 * N * max_batch * 4 + 4096
+        # a third, smaller buffer carries the vocabulary-parallel embedding rows (one exchange per step, which must not
+        # alternate with the two buffers of the per-block exchanges: a step has an even number of those)
+        self.embed_rows = min(fused_rows, 8192) if embed_rows is None else embed_rows
+        embed_bytes = self.embed_rows * hidden * 2
+        heap_bytes = 2 * buf_bytes + embed_bytes + 6 * 256 + 2 * N * max_batch * 4 + 8192
         # In-switch reduction (SKEIN_MULTIMEM=1): the heap is bound to an NVLink multicast object and the reduce
         # kernels sum the ranks' partials with one multimem load. Off by default: a rank that dies while bound
         # faults its peers, and the plain peer loads are what the failure-handling tests exercise.
@@ -76,14 +82,19 @@ class TPComm:
         self.cand_val_off = h.alloc(N * max_batch * 4)
         self.cand_idx_off = h.alloc(N * max_batch * 4)
         self.cand_flag_off = h.alloc(256)
+        self.embed_off = h.alloc(max(embed_bytes, 256))
+        self.embed_flag_off = h.alloc(256)
+        self.embed_buf = h.view(self.embed_off, (self.embed_rows, hidden), torch.bfloat16) if self.embed_rows else None
+        self.embed_flags = h.view(self.embed_flag_off, (N,), torch.int32)
         self.bufs = [h.view(o, (fused_rows, hidden), torch.bfloat16) for o in self.buf_off]   # this rank's partials
         self.flags = [h.view(o, (N,), torch.int32) for o in self.flag_off]                     # [source rank]
         self.cand_val = h.view(self.cand_val_off, (N, max_batch), torch.float32)
         self.cand_idx = h.view(self.cand_idx_off, (N, max_batch), torch.int32)
         self.cand_flags = h.view(self.cand_flag_off, (N,), torch.int32)
-        # local, not shared: epochs and "all CTAs done" counters of buffers 0/1 and of the candidate exchange
-        self.epochs = torch.zeros(3, dtype=torch.int32, device=device)
-        self.done = torch.zeros(3, dtype=torch.int32, device=device)
+        # local, not shared: epochs and "all CTAs done" counters of buffers 0/1, of the candidate exchange and of
+        # the embedding exchange
+        self.epochs = torch.zeros(4, dtype=torch.int32, device=device)
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
         self.cur = 0
         r = self.rank
         VP = C.c_void_p * N
@@ -93,6 +104,8 @@ class TPComm:
         self._cand_idx_ptrs = VP(*[h.peer_ptr(p, self.cand_idx_off + 4 * r * max_batch) for p in range(N)])
         self._cand_flag_ptrs = VP(*[h.peer_ptr(p, self.cand_flag_off + 4 * r) for p in range(N)])
         self._push_flag = [VP(*self._peer_flag[b]) for b in range(2)]
+        self._embed_src_ptrs = VP(*[h.peer_ptr(p, self.embed_off) for p in range(N)])
+        self._embed_push_flag = VP(*[h.peer_ptr(p, self.embed_flag_off + 4 * r) for p in range(N)])
         ops.workspace(device).peer_state.append((self.epochs, self.done))
 
     def reset(self):
@@ -102,6 +115,7 @@ class TPComm:
         for f in self.flags:
             f.zero_()
         self.cand_flags.zero_()
+        self.embed_flags.zero_()
         self.epochs.zero_()
         self.done.zero_()
         self.cur = 0
@@ -175,6 +189,79 @@ class TPComm:
         out, _ = ops.reduce_residual_rmsnorm(None, self._partials(b, rows), None, 0.0,
                                              wait_budget_ms=self.wait_budget_ms)
         return out
+
+    # ---- vocabulary-parallel embedding ---------------------------------------------------------------------------
+    def embed_reduce(self, ids, table_shard, vocab_start: int, gamma, eps):
+        """Embedding lookup with the table sharded by vocabulary rows: every rank gathers the rows it owns (zeros for
+        the others) straight into its published buffer, raises its flags, and the first RMSNorm of the step sums the
+        ranks' contributions as it reads them (the same pull / in-switch reduction as the per-block exchanges).
+        Returns (residual stream [T, H], its RMSNorm with `gamma`). The reference's vocab_parallel_embed masks and
+        all-reduces (crates/skein_emit/src/op_wiring.rs:1819)."""
+        T = ids.shape[0]
+        if T > self.embed_rows or self.mode == "nccl":
+            x = ops.embed(ids, table_shard, vocab_start)
+            dist.all_reduce(x, group=self.group)
+            return x, ops.rmsnorm(x, gamma, eps)
+        ops.embed(ids, table_shard, vocab_start, out=self.embed_buf[:T])
+        rc = _lib.lib().skein_publish_rows(None, 0, None, self._embed_push_flag, self.size, self.epochs[3:4].data_ptr(),
+                                           self.done[3:4].data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "publish embedding rows")
+        _lib.count_launch()
+        part = PeerPartials(self.embed_buf[:T], self._embed_src_ptrs, self.size, self.embed_flags, self.epochs[3:4],
+                            self.wait_budget_ms, mc=self.heap.mc_addr(self.embed_off))
+        return ops.reduce_residual_rmsnorm(None, part, gamma, eps)
+
+    # ---- sequence-parallel dataflow for prefill-sized chunks ------------------------------------------------
+    # Between a row-parallel projection and the next column-parallel one the activations are sharded by token rows:
+    #   GEMM publishes its partial [T, H]  ->  rank r reduces rows [r*per, (r+1)*per) over all ranks (peer loads or one
+    #   in-switch reducing load), adds its slice of the residual stream, normalises it  (reduce-scatter + norm)
+    #   ->  the normalised slices are published and pulled into every rank's local [T, H]  (all-gather)
+    #   ->  the next q/k/v or gate/up GEMM reads local memory.
+    # Each rank moves (N-1)/N of the message twice instead of pulling N-1 whole copies, normalises T/N rows instead of
+    # T, and the residual stream stays sharded from layer to layer. No library collective is launched.
+    def sp_ok(self, rows: int, partial_rows: int | None = None) -> bool:
+        """True when a chunk of `rows` tokens takes the sequence-parallel path: more rows than the replicated
+        (decode-style) exchange is meant for, and the partial results fit the published buffers."""
+        pr = partial_rows if partial_rows is not None else rows
+        return (self.mode in ("fused", "unfused") and self.size > 1 and rows > self.sp_min_rows and pr <= self.fused_rows
+                and self.sp_slice(rows)[2] * self.size <= self.fused_rows)
+
+    def sp_slice(self, rows: int):
+        """(first row, row count, rows per rank) of this rank's slice of a [rows, H] activation."""
+        per = (rows + self.size - 1) // self.size
+        per = (per + 7) // 8 * 8
+        r0 = min(self.rank * per, rows)
+        return r0, min(per, rows - r0), per
+
+    def reduce_scatter_norm(self, res_loc, part: "PeerPartials", gamma, eps, rows: int, row_idx=None, row_w=None):
+        """This rank's slice of (residual + sum over ranks of the partials), and its RMSNorm. `part` is what
+        linear_push returned for the whole chunk; `row_idx` / `row_w` ([rows, k]) select the MoE combine form, whose
+        partial rows are addressed through row_idx. Returns (residual slice [n, H], normed slice [per, H]: rows beyond n
+        are padding so that every rank's slice has the same size)."""
+        r0, n, per = self.sp_slice(rows)
+        H = self.hidden
+        normed = torch.zeros(per, H, dtype=torch.bfloat16, device=self.device) if n < per else \
+            torch.empty(per, H, dtype=torch.bfloat16, device=self.device)
+        res_out = torch.empty(n, H, dtype=torch.bfloat16, device=self.device)
+        if n == 0:
+            return res_out, normed
+        if row_idx is not None:
+            sl = PeerPartials(part.local, part.ptrs, part.n_src, part.flags, part.epoch, part.wait_budget_ms, mc=part.mc)
+            ri, rw = row_idx[r0:r0 + n].contiguous(), row_w[r0:r0 + n].contiguous()
+        else:
+            off = r0 * H * 2
+            VP = C.c_void_p * self.size
+            sl = PeerPartials(part.local[r0:r0 + n], VP(*[int(p) + off for p in part.ptrs]), part.n_src, part.flags,
+                              part.epoch, part.wait_budget_ms, mc=(part.mc + off) if part.mc else 0)
+            ri = rw = None
+        ops.reduce_residual_rmsnorm(res_loc, sl, gamma, eps, ri, rw, residual_out=res_out,
+                                    normed_out=normed[:n] if gamma is not None else None)
+        return res_out, normed
+
+    def gather_rows(self, x_loc: torch.Tensor, rows: int) -> torch.Tensor:
+        """All-gather of equally sized row slices ([per, H] on every rank) into the full [rows, H] activation, in local
+        memory (publish + one pull kernel): the operand of the next column-parallel GEMM."""
+        return self.all_gather(x_loc)[:rows]
 
     # ---- all-gather / reduce-scatter / all-to-all ----------------------------------------------------
     _PULL_ALL_GATHER, _PULL_ALL_TO_ALL, _PULL_REDUCE_SCATTER = 0, 1, 2

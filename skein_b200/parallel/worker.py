@@ -142,8 +142,10 @@ def run_rank(args) -> int:
                 stage_group = g
         if use_cuda:
             from .tp import TPComm
+            # the published buffers hold the partials of one prefill chunk (its expert-sorted rows for a MoE model)
+            rows = max(512, 8192 * max(1, art.cfg.top_k if art.cfg.is_moe else 1))
             if tp > 1:
-                comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size)
+                comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size, fused_rows=rows)
             if ep > 1:
                 comm_moe = TPComm(stage_group, device, hidden=art.cfg.hidden_size)
         elif tp > 1 or ep > 1:

@@ -172,7 +172,8 @@ class ModelRunner:
             torch.cuda.current_stream().synchronize()
             if int(bk.host_out[bk.B]) != 0:
                 ops.workspace().check_status()
-            self.last_wait_ns = int(bk.host_out[bk.B + 2:bk.B + 4].view(torch.int64)[0])
+            lo, hi = int(bk.host_out[bk.B + 2]), int(bk.host_out[bk.B + 3])      # a 64-bit total in two words
+            self.last_wait_ns = ((hi & 0xFFFFFFFF) << 32) | (lo & 0xFFFFFFFF)
         return bk.host_out[:bk.B]
 
     def decode_loop_step(self, bk: _Bucket):

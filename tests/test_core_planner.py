@@ -295,7 +295,9 @@ def test_drift_table_lookup_update_and_byte_stability():
 def test_topology_and_segments():
     p = make_plan(tp=2)
     topo = json.loads(core.emit_topology(p, CFG))["collectives"]
-    assert len(topo) == 2 * 32 + 1 and topo[0]["tensor_name"] == "block_0_attn_out" and topo[-1]["kind"] == "allgather"
+    # the vocabulary-parallel embedding's sum, two all-reduces per block, the candidate exchange of the sampler
+    assert len(topo) == 1 + 2 * 32 + 1 and topo[0]["tensor_name"] == "embed_out" and topo[1]["tensor_name"] == "block_0_attn_out"
+    assert topo[-1]["kind"] == "allgather"
     assert [e["sequence_idx"] for e in topo] == list(range(len(topo)))
     low = json.loads(core.lower_device(p, CFG, 0))
     n_coll = sum(1 for s in low["sequencing"] if s["kind"] == "collective")
@@ -322,6 +324,8 @@ def test_shard_roles_and_io_manifest():
     assert core.param_kind_for("model.layers.0.block_sparse_moe.gate.weight")[0] == "replicated"
     assert core.param_kind_for("model.norm.weight")[0] == "replicated"
     io = {t["name"]: t for t in json.loads(core.io_manifest(make_plan(tp=2, ep=2, pp=2), CFG, 7))["tensors"]}   # stage 1, ep 1, tp 1
+    io0 = {t["name"]: t for t in json.loads(core.io_manifest(make_plan(tp=2, ep=2, pp=2), CFG, 1))["tensors"]}      # stage 0, ep 0, tp 1
+    assert io0["model.embed_tokens.weight"]["shape"] == [16000, 4096] and io0["model.embed_tokens.weight"]["start"] == 16000
     assert "model.embed_tokens.weight" not in io and "lm_head.weight" in io and "model.layers.0.input_layernorm.weight" not in io
     assert io["lm_head.weight"]["shape"] == [16000, 4096] and io["lm_head.weight"]["start"] == 16000
     assert io["model.layers.20.self_attn.o_proj.weight"]["shape"] == [4096, 2048] and io["model.layers.20.self_attn.o_proj.weight"]["axis"] == 1

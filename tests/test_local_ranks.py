@@ -41,7 +41,10 @@ def test_tp_shards_reproduce_the_unsharded_model(tp, cfg):
 
     def rank_fn(r, comm):
         lay = mc.ParallelLayout(tp=tp, rank=r)
-        dec = Decoder(cfg, shard_model(full, cfg, lay), lay, num_pages=16, page_size=16, max_pos=128, comm=comm)
+        # the embedding table is vocabulary-parallel (each rank holds V / tp rows) except in the last case
+        w = shard_model(full, cfg, lay, shard_embed=cfg.is_moe)
+        assert w.embed.shape[0] == (cfg.vocab_size // tp if cfg.is_moe else cfg.vocab_size)
+        dec = Decoder(cfg, w, lay, num_pages=16, page_size=16, max_pos=128, comm=comm)
         return _generate(dec, prompts, tables)
 
     results, errors = run_ranks(tp, rank_fn)

@@ -17,7 +17,7 @@ def _run(world, env_extra=None, port=29541, worker="tp_worker.py", ok="TP_WORKER
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "workers", worker)]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0 and ok in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
@@ -40,6 +40,21 @@ def test_tp2_in_switch_reduction():
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp4_fused():
     _run(4, port=29543)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_tp4_in_switch_reduction():
+    _run(4, {"SKEIN_MULTIMEM": "1"}, port=29551, ok="multimem 1")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp8_fused():
+    _run(8, port=29552)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp8_in_switch_reduction():
+    _run(8, {"SKEIN_MULTIMEM": "1"}, port=29553, ok="multimem 1")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

@@ -101,6 +101,33 @@ def main():
     from skein_b200.parallel.selfcheck import teacher_forced_check
     info = teacher_forced_check(world, rank, dev, comm=comm, tp=world, hidden=H)
     assert info["tokens_compared"] == 21
+
+    # 5. sequence-parallel dataflow (prefill-sized chunks): reduce-scatter fused with residual + RMSNorm on this rank's
+    #    row slice, all-gather of the normalised slices; against the fp32 reference of the unsharded op
+    if comm.mode != "nccl":
+        T2 = 100                                    # not a multiple of the rank count: the last slice is short
+        x2 = torch.randn(T2, K, generator=g).bfloat16()
+        res2 = torch.randn(T2, H, generator=g).bfloat16()
+        part, _, _ = comm.linear_push(x2[:, ks].contiguous().to(dev), w_full[:, ks].contiguous().to(dev))
+        r0, n, per = comm.sp_slice(T2)
+        res_loc, normed_loc = comm.reduce_scatter_norm(res2[r0:r0 + n].to(dev), part, gamma.to(dev), 1e-5, T2)
+        full = comm.gather_rows(normed_loc, T2)
+        r_ref, n_ref = ref.reduce_residual_rmsnorm(res2, ref.linear(x2, w_full).unsqueeze(0), gamma, 1e-5)
+        assert res_loc.shape[0] == n and full.shape[0] == T2
+        assert rel(res_loc, r_ref[r0:r0 + n]) < 2e-2 and rel(full, n_ref) < 2e-2, ("sp dense", rel(full, n_ref))
+        # MoE combine form: partial rows are addressed through row_idx
+        part, _, _ = comm.linear_push(h_full[:, kp].contiguous().to(dev), w2_full[:, :, kp].contiguous().to(dev),
+                                      (counts.to(dev), offsets.to(dev)))
+        r0, n, per = comm.sp_slice(T)
+        res_loc, normed_loc = comm.reduce_scatter_norm(res[r0:r0 + n].to(dev), part, gamma.to(dev), 1e-5, T,
+                                                       row_of.view(T, topk).to(dev), wts.to(dev))
+        full = comm.gather_rows(normed_loc, T)
+        assert rel(full, n2) < 2e-2, ("sp grouped", rel(full, n2))
+        # the whole model with its prefill on the sequence-parallel path (63 prompt tokens > the threshold below)
+        comm.sp_min_rows = 16
+        info = teacher_forced_check(world, rank, dev, comm=comm, tp=world, hidden=H, seed=12)
+        assert info["tokens_compared"] == 21
+        comm.sp_min_rows = 512
     dist.barrier()
     if rank == 0:
         print("TP_WORKER_OK world", world, "mode", comm.mode, "multimem", int(comm.heap.mc_ptr != 0))
