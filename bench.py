@@ -406,6 +406,7 @@ def main():
         else:
             ctl = LocalControl()
         e2e_vals, step_ms = [], []
+        parts = {"announce": 0.0, "engine_step": 0.0, "agree": 0.0, "n": 0}
         for r in range(min(R, 3)):
             eng = Engine(dec, ecfg)
             eng.runner = runner                                   # reuse the captured graphs
@@ -417,6 +418,7 @@ def main():
             t_wall0 = time.perf_counter()
 
             def one_step():
+                t0_ = time.perf_counter()
                 if world > 1:
                     if rank == 0:
                         now = eng.clock()
@@ -425,9 +427,13 @@ def main():
                         _, now = ctl.follow()
                 else:
                     now = eng.clock()
+                t1_ = time.perf_counter()
                 evs = eng.step(now)
+                t2_ = time.perf_counter()
                 if ctl.agree_failed(eng.last_step_failed):
                     raise RuntimeError("an engine step failed: " + str([e.error for e in evs if e.error][:1]))
+                t3_ = time.perf_counter()
+                parts["announce"] += t1_ - t0_; parts["engine_step"] += t2_ - t1_; parts["agree"] += t3_ - t2_; parts["n"] += 1
                 return evs
 
             # prefill iterations, then warm-up decode iterations
@@ -440,6 +446,8 @@ def main():
                     if n_decode_steps >= W:
                         break
             barrier()
+            for k_ in parts:
+                parts[k_] = 0 if k_ == "n" else 0.0
             t_a = time.perf_counter()
             for _ in range(K):
                 t_s = time.perf_counter()
@@ -461,7 +469,8 @@ def main():
         e2e = {"value": round(e2e_vals[len(e2e_vals) // 2], 2), "unit": "tokens/s", "h2d_bytes_per_step": bk.h2d_bytes,
                "d2h_bytes_per_step": bk.d2h_bytes, "tpot_p50_ms": round(step_ms[len(step_ms) // 2], 3), "tpot_p99_ms": tpot_p99,
                "path": "Engine.step (C++ batcher + paged-KV manager) -> ModelRunner.decode_step; lock-step control page at N > 1",
-               "repeats": [round(v, 1) for v in e2e_vals]}
+               "repeats": [round(v, 1) for v in e2e_vals],
+               "host_us_per_step_rank0": {k: round(v / max(1, parts["n"]) * 1e6, 1) for k, v in parts.items() if k != "n"}}
 
     if rank == 0:
         out = {

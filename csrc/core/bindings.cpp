@@ -326,6 +326,19 @@ PYBIND11_MODULE(_skein_core, m) {
         }
         return out;
       })
+      // raw host addresses of int32 arrays (the runner's pinned staging buffer): no per-row Python objects on the hot path
+      .def("fill_decode_inputs", [](const ContinuousBatcher& b, const std::vector<uint64_t>& ids, uintptr_t tok, uintptr_t pos, uintptr_t lens,
+                                    uintptr_t bt, size_t max_blocks, size_t rows) {
+        b.fill_decode_inputs(ids, reinterpret_cast<int32_t*>(tok), reinterpret_cast<int32_t*>(pos), reinterpret_cast<int32_t*>(lens),
+                             reinterpret_cast<int32_t*>(bt), max_blocks, rows);
+      })
+      .def("accept_tokens", [](ContinuousBatcher& b, const std::vector<uint64_t>& ids, uintptr_t tokens, uint64_t now, int32_t eos) {
+        auto o = b.accept_tokens(ids, reinterpret_cast<const int32_t*>(tokens), now, eos);
+        std::vector<uint8_t> fin(o.size());
+        std::vector<uint32_t> n(o.size());
+        for (size_t i = 0; i < o.size(); ++i) { fin[i] = o[i].finished; n[i] = o[i].generated; }
+        return py::make_tuple(fin, n);
+      }, py::arg("ids"), py::arg("tokens_addr"), py::arg("now_ms"), py::arg("eos_token") = -1)
       .def_property_readonly("inflight_len", &ContinuousBatcher::inflight_len).def_property_readonly("queued_len", &ContinuousBatcher::queued_len)
       .def_property_readonly("rejected", &ContinuousBatcher::rejected).def_property_readonly("retired", &ContinuousBatcher::retired)
       .def_property_readonly("max_batch", &ContinuousBatcher::max_batch).def("inflight_ids", &ContinuousBatcher::inflight_ids);

@@ -159,6 +159,38 @@ class ContinuousBatcher {
   }
 
   // `failed`: the request is dropped after a step that did not complete; its pages leave the prefix cache.
+  // The host inputs of a decode step, written straight into the step's staging arrays (pinned memory that one
+  // host-to-device copy then moves): row i feeds request ids[i] its last token at its position; rows from ids.size()
+  // to `rows` are padding (position -1, length 0). Block-table rows are `max_blocks` wide.
+  void fill_decode_inputs(const std::vector<uint64_t>& ids, int32_t* tok, int32_t* pos, int32_t* lens, int32_t* block_table,
+                          size_t max_blocks, size_t rows) const {
+    if (ids.size() > rows) throw RuntimeError("decode batch is larger than its staging buffer");
+    for (size_t i = 0; i < ids.size(); ++i) {
+      const InflightRequest* r = get(ids[i]);
+      if (!r || r->generated.empty()) throw RuntimeError("request " + std::to_string(ids[i]) + " is not decoding");
+      const int32_t p = (int32_t)(r->req.prompt.size() + r->generated.size()) - 1;
+      tok[i] = r->generated.back();
+      pos[i] = p;
+      lens[i] = p + 1;
+      if (kv_) {
+        const PageTable* t = kv_->table(ids[i]);
+        if (!t || t->pages.size() > max_blocks) throw RuntimeError("request " + std::to_string(ids[i]) + ": page table does not fit the block table");
+        std::copy(t->pages.begin(), t->pages.end(), block_table + i * max_blocks);
+      }
+    }
+    for (size_t i = ids.size(); i < rows; ++i) { tok[i] = 0; pos[i] = -1; lens[i] = 0; }
+  }
+  // accept_token for a whole decode batch; out[i] = (finished, tokens generated so far) of ids[i].
+  std::vector<AcceptOutcome> accept_tokens(const std::vector<uint64_t>& ids, const int32_t* tokens, uint64_t now_ms, int32_t eos_token = -1) {
+    std::vector<AcceptOutcome> out;
+    out.reserve(ids.size());
+    for (size_t i = 0; i < ids.size(); ++i) {
+      auto o = accept_token(ids[i], tokens[i], now_ms, eos_token);
+      out.push_back(o ? *o : AcceptOutcome{});
+    }
+    return out;
+  }
+
   void retire(uint64_t id, bool failed = false) {
     auto it = inflight_.find(id);
     if (it == inflight_.end()) throw RuntimeError("retire: unknown request " + std::to_string(id));

@@ -97,7 +97,6 @@ class Engine:
         self._next_id = 1
         self._step = 0
         self._graph_seen = (0, 0)   # runner.graph_captures / graph_replays already added to the metrics
-        self._last = {}          # request id -> last sampled token (input of its next decode step)
         self._sampling = {}      # request id -> SamplingParams (only requests that sample)
         self._wait_ns_seen = 0
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
@@ -178,7 +177,6 @@ class Engine:
         error and their pages leave the prefix cache; queued requests stay queued."""
         events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
         for ev in events:
-            self._last.pop(ev.request_id, None)
             self._sampling.pop(ev.request_id, None)
             self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
         return events
@@ -216,31 +214,31 @@ class Engine:
                 if last:
                     events.append(self._accept(rid, tok, stamp()))
         if decode:
-            pos = self.batcher.decode_positions(decode)
-            toks_in = [self._last[rid] for rid in decode]
-            lens = [p + 1 for p in pos]
-            tables = [self.kv.pages_for(rid) for rid in decode]
             bk = self.runner.bucket(len(decode))
             rows = self._rows(decode)
-            self.runner.load_decode_inputs(bk, toks_in, pos, lens, tables, sampling=rows)
+            self.runner.stage_decode_inputs(bk, self.batcher, decode, sampling=rows)
             out = self.runner.decode_step(bk, sampling=rows is not None)
-            t_tok = stamp()
-            for i, rid in enumerate(decode):
-                events.append(self._accept(rid, int(out[i]), t_tok))
+            fin, counts = self.batcher.accept_tokens(decode, out.data_ptr(), stamp(), self.cfg.eos_token)
+            toks = out[:len(decode)].tolist()
+            for rid, tok, f, n in zip(decode, toks, fin, counts):
+                if f:
+                    self._finish(rid, n)
+                events.append(TokenEvent(rid, tok, bool(f)))
         return events
 
     def _accept(self, rid, tok, now) -> TokenEvent:
         finished, n = self.batcher.accept_token(rid, int(tok), now, self.cfg.eos_token)
-        self._last[rid] = int(tok)
         if finished:
-            info = self.batcher.request_info(rid)
-            ttft = float(info["first_token_ms"] - info["arrival_ms"])
-            tpot = float(info["last_token_ms"] - info["first_token_ms"]) / max(1, n - 1)
-            self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
-            self.batcher.retire(rid)
-            self._last.pop(rid, None)
-            self._sampling.pop(rid, None)
+            self._finish(rid, n)
         return TokenEvent(rid, int(tok), bool(finished))
+
+    def _finish(self, rid, n) -> None:
+        info = self.batcher.request_info(rid)
+        ttft = float(info["first_token_ms"] - info["arrival_ms"])
+        tpot = float(info["last_token_ms"] - info["first_token_ms"]) / max(1, n - 1)
+        self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
+        self.batcher.retire(rid)
+        self._sampling.pop(rid, None)
 
     # ---- helpers ------------------------------------------------------------------------------------------------
     @property

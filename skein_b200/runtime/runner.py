@@ -159,6 +159,26 @@ class ModelRunner:
         else:
             st[:] = 0.0
 
+    def stage_decode_inputs(self, bk: _Bucket, batcher, ids, sampling=None):
+        """load_decode_inputs for the serving engine: the C++ batcher writes tokens, positions, lengths and block tables of
+        the listed requests straight into the pinned staging buffer (one call, no per-row Python objects)."""
+        t, p, l, bt = bk.views(bk.host_in)
+        batcher.fill_decode_inputs(ids, t.data_ptr(), p.data_ptr(), l.data_ptr(), bt.data_ptr(), bk.max_blocks, bk.B)
+        if bk.np_views is None:
+            bk.np_views = tuple(v.numpy() for v in bk.views(bk.host_in)) + tuple(v.numpy() for v in bk.sampling_views(bk.host_in))
+        st, sk, sp, ss = bk.np_views[4:]
+        n = len(ids)
+        if sampling is not None:
+            st[:n] = [s[0] for s in sampling]
+            sk[:n] = [s[1] for s in sampling]
+            sp[:n] = [s[2] for s in sampling]
+            ss[:n] = [s[3] for s in sampling]
+            st[n:] = 0.0
+            bk.sampling_dirty = True
+        elif getattr(bk, "sampling_dirty", True):
+            st[:] = 0.0
+            bk.sampling_dirty = False
+
     def decode_step(self, bk: _Bucket, sync: bool = True, sampling: bool = False):
         """H2D of the staged inputs, one step, D2H of the result. Returns the host result view."""
         bk.dev_in.copy_(bk.host_in, non_blocking=True)
