@@ -52,7 +52,9 @@ def parse():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
-    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (tensor parallel = gpus / ep)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (tensor parallel = gpus / ep / pp)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (tensor parallel = gpus / pp inside every stage)")
+    ap.add_argument("--fp8-blocks", default="", help="'a:b' = blocks a..b-1 (of the whole model) in block-scaled fp8, all four projections")
     ap.add_argument("--fp8-experts", action="store_true", help="block-scaled e4m3 expert / FFN weights (marks dtype)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--repeats", type=int, default=5, help="how often each timed K-step loop is repeated (median reported)")
@@ -208,10 +210,207 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
+def run_pipeline(args, emit_json):
+    """--pp > 1: tensor parallel inside each of `pp` stages (BASELINE config 3: Llama-3-70B, TP=4 x PP=2). The device-
+    timed loop is the steady-state pipelined decode (pp micro-batches in flight across steps, per-stage CUDA graphs,
+    asynchronous point-to-point between stages); the end-to-end number runs the serving engine over the pipeline."""
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from skein_b200 import ops
+    from skein_b200.models import config as mc
+    from skein_b200.models.decoder import BatchInputs, Decoder, quantize_blocks, random_weights
+    from skein_b200.parallel import pp as pp_mod
+    from skein_b200.parallel.tp import TPComm
+    from skein_b200.runtime.driver import SharedControl
+    from skein_b200.runtime.engine import Engine, EngineConfig
+    from skein_b200.runtime.runner import ModelRunner
+
+    world, rank, local_rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+    control_group = dist.new_group(backend="gloo")
+    cfg = {"mixtral-8x7b": mc.mixtral_8x7b, "mixtral-8x22b": mc.mixtral_8x22b, "llama3-70b": mc.llama3_70b}[args.model]()
+    if args.layers:
+        cfg.num_layers = args.layers
+    npp = args.pp
+    tp = world // npp
+    lay = mc.ParallelLayout(tp=tp, pp=npp, rank=rank)
+    tp_group, pp_ranks, pp_group = pp_mod.make_groups((tp, npp, 1), rank)
+    fb_group = dist.new_group(list(range(world)))        # token feedback travels on its own communicator
+    comm = TPComm(tp_group, dev, hidden=cfg.hidden_size, fused_rows=8192) if tp > 1 else None
+    B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
+    blocks_per_seq = (P + Gn + ps - 1) // ps + 1
+    num_pages = B * blocks_per_seq + 8
+    weights = random_weights(cfg, lay, dev, seed=0, std=0.02, shard_embed=True)
+    fp8_note = "bf16"
+    if args.fp8_blocks:
+        a, b = (int(x) for x in args.fp8_blocks.split(":"))
+        mine = list(lay.stage_layers(cfg.num_layers))
+        quantize_blocks(weights, [i for i, g in enumerate(mine) if a <= g < b])
+        fp8_note = f"blocks {a}..{b - 1} block-scaled fp8 (e4m3, 1x128), the rest bf16"
+    dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm)
+    stage = pp_mod.PipelineStage(dec, lay, pp_ranks, pp_group)
+    runner = ModelRunner(stage, max_blocks_per_seq=blocks_per_seq, use_graphs=False, ctx_hint=P + Gn // 2)
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g).tolist()
+    tables = [list(range(1 + s * blocks_per_seq, 1 + (s + 1) * blocks_per_seq)) for s in range(B)]
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def check_all(where):
+        code = ops.workspace().status[:1].clone()
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if int(code[0]) != 0:
+            if rank == 0:
+                emit_json({"error": f"device status {int(code[0])} after {where}", "n_gpus": world})
+            os._exit(3)
+
+    # ---- prefill: chunks of up to 8192 tokens through the pipeline ----
+    per_chunk = max(1, 8192 // P)
+    barrier()
+    t_pf = time.perf_counter()
+    first_tokens = []
+    for c0 in range(0, B, per_chunk):
+        first_tokens.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
+    torch.cuda.synchronize()
+    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)
+    check_all("prefill")
+
+    # ---- steady-state pipelined decode: pp micro-batches in flight ----
+    M = npp
+    per = B // M
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    K, W, R = args.steps, max(args.warmup, 3), max(1, args.repeats)
+
+    def make_micro():
+        micro = []
+        for m in range(M):
+            rows = list(range(m * per, (m + 1) * per))
+            bt = torch.zeros(per, blocks_per_seq, dtype=torch.int32, device=dev)
+            for i, r_ in enumerate(rows):
+                bt[i] = i32(tables[r_])
+            micro.append(BatchInputs(token_ids=i32([first_tokens[r_] for r_ in rows]), positions=i32([P] * per), block_table=bt,
+                                     seq_lens=i32([P + 1] * per), ctx_hint=P + Gn // 2))
+        return micro
+
+    micro = make_micro()
+
+    def advance(inp, toks):
+        ops.advance_decode_state(toks if toks is not None else inp.token_ids, inp.token_ids, inp.positions, inp.seq_lens)
+
+    def reset(micro):
+        for m, inp in enumerate(micro):
+            rows = list(range(m * per, (m + 1) * per))
+            inp.token_ids.copy_(i32([first_tokens[r_] for r_ in rows]))
+            inp.positions.fill_(P)
+            inp.seq_lens.fill_(P + 1)
+
+    from skein_b200.ops import _lib
+    times, idle, launches_per_step = [], None, None
+    for r in range(R):
+        reset(micro)
+        torch.cuda.synchronize()
+        l0 = _lib.launches()
+        pp_mod.pipelined_decode(stage, micro, W, advance, fb_group, resume=False, more=True)
+        if r == 0:
+            # the first step ran eagerly and the second was captured: each counted this rank's launches of one step once
+            # (minus the position updates, which are counted on every step)
+            launches_per_step = (_lib.launches() - l0 - M * (W - 1)) // 2
+        barrier()
+        stage.stage_busy_events, stage.time_stages = [], (r == R - 1)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        pp_mod.pipelined_decode(stage, micro, K, advance, fb_group, resume=True, more=False)
+        ev1.record()
+        barrier()
+        ms_r = ev0.elapsed_time(ev1)
+        if r == R - 1:
+            idle = stage.idle_fraction(ms_r)
+            stage.time_stages = False
+        times.append(max_over_ranks(ms_r))
+        check_all("the pipelined decode")
+    times.sort()
+    ms = times[len(times) // 2]
+    value = B * K / (ms / 1e3)
+    idles = [None] * world
+    dist.all_gather_object(idles, idle)
+
+    # ---- end to end: the serving engine over the pipeline (micro-batched steps, lock-step control page) ----
+    e2e = None
+    if not args.no_e2e:
+        for kv in dec.kv:
+            kv.zero_()
+        ecfg = EngineConfig(max_batch=B, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False, max_prefill_tokens=8192,
+                            interleave_prefill_tokens=0)
+        ctl = SharedControl(f"/dev/shm/skein_bench_ctl_{os.environ.get('MASTER_PORT', '0')}", rank, world, control_group, wait_s=300)
+        eng = Engine(stage, ecfg)
+        for s_ in range(B):
+            eng.submit(prompts[s_], Gn, now_ms=0, request_id=s_ + 1)
+
+        def one_step():
+            if rank == 0:
+                now = eng.clock()
+                ctl.lead(None, now)
+            else:
+                _, now = ctl.follow()
+            evs = eng.step(now)
+            if ctl.agree_failed(eng.last_step_failed):
+                raise RuntimeError("an engine step failed: " + str([e.error for e in evs if e.error][:1]))
+            return evs
+
+        n_dec = 0
+        while n_dec < W:
+            evs = one_step()
+            if len(evs) == B and all(not e.is_final for e in evs):
+                n_dec += 1
+        barrier()
+        t_a = time.perf_counter()
+        for _ in range(K):
+            one_step()
+        torch.cuda.synchronize()
+        wall = max_over_ranks(time.perf_counter() - t_a)
+        bk = eng.runner.bucket(B)
+        e2e = {"value": round(B * K / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": bk.h2d_bytes, "d2h_bytes_per_step": bk.d2h_bytes,
+               "path": "Engine.step over PipelineStage (pp micro-batches per step, per-stage CUDA graphs); lock-step control page"}
+        ctl.close()
+    if rank == 0:
+        emit_json({
+            "metric": args.model.replace("-", "_") + "_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16" if not args.fp8_blocks else "bf16 activations; " + fp8_note,
+            "data": "synthetic (random-init weights N(0,0.02), random prompt token ids)",
+            "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"), "global_batch": B, "seq_len": P,
+                       "gen_len": Gn, "parallelism": f"tp{tp}xpp{npp}", "kv": "paged, block 16", "micro_batches": M,
+                       "l2": "inputs (weights) larger than L2, no flush", "cuda_graph": "per stage and micro-batch",
+                       "weights": fp8_note, "repeats": R},
+            "prefill_ms": round(prefill_ms, 1), "stage_idle_fraction_per_rank": [None if x is None else round(x, 3) for x in idles],
+            "e2e": e2e, "gpu_launches": (launches_per_step or 0) * K, "kernels_per_step_on_rank0": launches_per_step, "impl": "ours"})
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.pp > 1:
+        sys.stdout.flush()
+        fd = os.dup(1)
+        os.dup2(2, 1)
+        return run_pipeline(args, lambda obj: os.write(fd, (json.dumps(obj) + "\n").encode()))
 
     # Libraries (NCCL's version banner, for one) write to file descriptor 1. Keep the real stdout for the one JSON
     # line and send everything else that lands on descriptor 1 to stderr.

@@ -270,12 +270,127 @@ def bench_collectives(emit, args) -> int:
     return 0
 
 
+def bench_over_http(args, emit) -> int:
+    """Replay a trace against a running server (`skein serve`, any number of GPUs behind it) over HTTP with SSE token
+    streams: arrival times honoured (scaled by --time-scale), one connection per request, TTFT and inter-token times
+    measured at the client. This is how a multi-GPU artifact is benchmarked end to end."""
+    import asyncio
+
+    import aiohttp
+    import torch
+
+    lines = [json.loads(l) for l in _read(args.workload).splitlines() if l.strip()]
+    slo, reqs = lines[0]["slo"], lines[1:]
+    if args.max_requests:
+        reqs = reqs[:args.max_requests]
+    g = torch.Generator().manual_seed(0)
+    vocab = args.vocab_size
+    max_ctx = args.max_seq_len
+    stats = {"ok": 0, "rejected": 0, "failed": 0, "tokens": 0, "ttft": [], "gaps": []}
+
+    async def one(session, r, t0):
+        await asyncio.sleep(max(0.0, r["arrival_ms"] / 1000.0 / args.time_scale - (time.monotonic() - t0)))
+        n_out = int(r["output_tokens"])
+        n_prompt = max(1, min(int(r["prompt_tokens"]), max_ctx - n_out - 1))
+        ids = torch.randint(0, vocab, (n_prompt,), generator=g).tolist()
+        t_send = time.monotonic()
+        try:
+            async with session.post(args.url.rstrip("/") + "/v1/completions", json={"prompt": ids, "max_tokens": n_out, "stream": True}) as resp:
+                if resp.status == 429:
+                    stats["rejected"] += 1
+                    return
+                if resp.status != 200:
+                    stats["failed"] += 1
+                    return
+                last, n, err = None, 0, False
+                async for raw in resp.content:
+                    line = raw.decode().strip()
+                    if not line.startswith("data: "):
+                        continue
+                    ev = json.loads(line[6:])
+                    now = time.monotonic()
+                    if ev.get("error"):
+                        err = True
+                        break
+                    n += 1
+                    if last is None:
+                        stats["ttft"].append((now - t_send) * 1e3)
+                    else:
+                        stats["gaps"].append((now - last) * 1e3)
+                    last = now
+                stats["tokens"] += n
+                stats["failed" if err else "ok"] += 1
+        except aiohttp.ClientError:
+            stats["failed"] += 1
+
+    async def run():
+        t0 = time.monotonic()
+        conn = aiohttp.TCPConnector(limit=0)
+        async with aiohttp.ClientSession(connector=conn, timeout=aiohttp.ClientTimeout(total=None)) as session:
+            await asyncio.gather(*[one(session, r, t0) for r in reqs])
+        return time.monotonic() - t0
+
+    wall = asyncio.run(run())
+    q = lambda xs, f: (sorted(xs)[min(len(xs) - 1, int(f * len(xs)))] if xs else None)
+    ttft_p50, ttft_p95, tpot_p99 = q(stats["ttft"], 0.5), q(stats["ttft"], 0.95), q(stats["gaps"], 0.99)
+    meets = ttft_p95 is not None and ttft_p95 <= slo["ttft_p95_ms"] and (tpot_p99 is None or q(stats["gaps"], 0.95) <= slo["tpot_p95_ms"])
+    out = {"url": args.url, "throughput_tok_s": round(stats["tokens"] / wall, 2), "goodput_req_s": round((stats["ok"] if meets else 0) / wall, 3),
+           "requests_ok": stats["ok"], "requests_rejected": stats["rejected"], "requests_failed": stats["failed"],
+           "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2), "ttft_p95_ms": None if ttft_p95 is None else round(ttft_p95, 2),
+           "tpot_p99_ms": None if tpot_p99 is None else round(tpot_p99, 3), "wall_s": round(wall, 2), "baseline": args.baseline}
+    emit(args, out, "\n".join(f"{k:20s} {v}" for k, v in out.items()))
+    return 0
+
+
+def bench_op_profile(args, emit) -> int:
+    """One decode step of the artifact's batch size, launched kernel by kernel with CUDA events around every operator:
+    the per-operator table (calls, device time, share, host time per launch) of a served step."""
+    import torch
+
+    from ..compile.artifact import Artifact
+    from ..parallel import worker
+    from ..utils.op_profile import OpProfiler
+
+    art = Artifact(args.artifact)
+    if art.num_devices != 1 or not torch.cuda.is_available():
+        raise ValueError("--op-profile runs a single-GPU artifact on a GPU")
+    device = torch.device("cuda", 0)
+    eng = worker.build_engine(art, 0, device, None, worker.parse(["--artifact", args.artifact]))
+    B = eng.cfg.max_batch
+    g = torch.Generator().manual_seed(0)
+    n_prompt = max(1, min(64, eng.dec.max_pos // 2))
+    for _ in range(B):
+        eng.submit(torch.randint(0, art.cfg.vocab_size, (n_prompt,), generator=g).tolist(), 8)
+    while eng.batcher.inflight_len and not all(eng.batcher.request_info(i)["phase"] == "decode" for i in eng.batcher.inflight_ids()):
+        eng.step()
+    ids = eng.batcher.inflight_ids()
+    bk = eng.runner.bucket(len(ids))
+    eng.runner.stage_decode_inputs(bk, eng.batcher, ids)
+    bk.dev_in.copy_(bk.host_in)
+    eng.runner._decode_body(bk, False)            # warm-up (descriptor caches, workspaces)
+    bk.dev_in.copy_(bk.host_in)
+    with OpProfiler() as prof:
+        eng.runner._decode_body(bk, False)
+    sm = prof.summary()
+    emit(args, {"batch": len(ids), "operators": sm}, prof.table())
+    return 0
+
+
 def cmd_bench(args, emit) -> int:
-    """Replay a trace (arrival times honoured, scaled by --time-scale) against a single-process engine."""
+    """Replay a trace (arrival times honoured, scaled by --time-scale) against a single-process engine, or with --url
+    against a running server over HTTP."""
     import torch
 
     if getattr(args, "collectives", False):
         return bench_collectives(emit, args)
+    if getattr(args, "url", None):
+        if not args.workload:
+            raise ValueError("`skein bench --url` needs --workload")
+        return bench_over_http(args, emit)
+    if getattr(args, "op_profile", False):
+        if not args.artifact:
+            raise ValueError("`skein bench --op-profile` needs --artifact")
+        return bench_op_profile(args, emit)
     if not args.artifact or not args.workload:
         raise ValueError("`skein bench` needs --artifact and --workload (or --collectives under torch.distributed.run)")
 
@@ -284,7 +399,7 @@ def cmd_bench(args, emit) -> int:
 
     art = Artifact(args.artifact)
     if art.num_devices != 1:
-        raise ValueError("`skein bench` drives a single-process engine; launch multi-GPU artifacts with `skein serve --gpus` and bench over HTTP")
+        raise ValueError("this artifact needs several ranks: start it with `skein serve --gpus ...` and run `skein bench --url http://host:port --workload ...`")
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
     wargs = worker.parse(["--artifact", args.artifact, "--workload", args.workload])
     eng = worker.build_engine(art, 0, device, None, wargs)

@@ -122,6 +122,11 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--max-requests", type=int, default=0)
     b.add_argument("--time-scale", type=float, default=1.0, help="divide arrival times by this factor")
     b.add_argument("--collectives", action="store_true", help="micro-benchmark the stand-alone collectives instead")
+    b.add_argument("--url", default=None, help="replay the trace against a running server (e.g. http://127.0.0.1:8080) over HTTP/SSE "
+                                               "instead of an in-process engine: the way to benchmark `serve --gpus` end to end")
+    b.add_argument("--vocab-size", type=int, default=32000, help="with --url: range of the random prompt token ids")
+    b.add_argument("--max-seq-len", type=int, default=4096, help="with --url: prompts are clipped so that prompt + output fit")
+    b.add_argument("--op-profile", action="store_true", help="print the per-operator table of one decode step (eager launches, CUDA events)")
     return ap
 
 

@@ -143,7 +143,9 @@ class Decoder:
 
     def __init__(self, cfg: ModelConfig, weights: ModelWeights, layout: ParallelLayout | None = None,
                  num_pages: int = 0, page_size: int = 16, max_pos: int | None = None, comm=None, comm_moe=None,
-                 pack_moe: bool | None = None):   # pack_moe: tile-pack the FFN / expert weights
+                 pack_moe: bool | None = None, kv_pools=None):
+        # pack_moe: tile-pack the FFN / expert weights. kv_pools: per-layer page pools allocated by the caller
+        # (peer-mapped pools of a prefill/decode pair, parallel/disagg.py) instead of pools allocated here
         self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
         self.comm = comm          # tensor-parallel communicator over this rank's TP group, or None
         self.comm_moe = comm_moe  # communicator over all tp x ep ranks of the stage (expert parallelism), or None
@@ -157,8 +159,14 @@ class Decoder:
         self.max_pos = max_pos or cfg.max_position_embeddings
         self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev)
         self.num_pages = num_pages
-        self.kv = [torch.zeros(num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
-                   for _ in weights.layers] if num_pages > 0 else []
+        if kv_pools is not None:
+            want = (num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim)
+            if len(kv_pools) != len(weights.layers) or any(tuple(p.shape) != want for p in kv_pools):
+                raise ValueError(f"kv_pools must be {len(weights.layers)} tensors of shape {want}")
+            self.kv = list(kv_pools)
+        else:
+            self.kv = [torch.zeros(num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+                       for _ in weights.layers] if num_pages > 0 else []
         self.capture_hidden = None  # set to a list to record the residual stream after every block (parity gate)
         # vocabulary-parallel embedding: when the table holds only this rank's rows (models/sharding.py, random_weights
         # with shard_embed), the first row it owns; None for a replicated table

@@ -1,18 +1,25 @@
 """Pipeline parallelism: the decoder's blocks are split into stages (remainder spread over the first stages);
-the residual stream [tokens, hidden] crosses each stage boundary with NCCL point-to-point on the compute
-stream (enqueued asynchronously, no host synchronisation), the last stage samples, and the sampled tokens
-travel back to every stage of the pipeline group (they are the next step's embedding input on stage 0 and
-the scheduler's input on every rank).
+the residual stream [tokens, hidden] crosses each stage boundary with NCCL point-to-point, the last stage
+samples, and the sampled tokens travel back (they are the next step's embedding input on stage 0 and the
+scheduler's input on every rank).
 
-`PipelineStage` has the same `forward(inp) -> (tokens, logits)` contract as `Decoder`, so the runner and the
-engine drive a pipeline exactly like a single stage. `pipelined_decode` additionally keeps `pp` micro-batches
-in flight so that all stages work at the same time (steady-state 1F1B for any pp, not only pp == 2).
+Three levels:
 
-Within a stage, tensor parallelism uses that stage's own TPComm (fused collectives over the stage's ranks).
+* `PipelineStage.forward(inp)` has the contract of `Decoder.forward`, so the runner and the serving engine drive a
+  pipeline like a single stage. A decode step is cut into `pp` micro-batches (row slices of the step's static
+  buffers) that follow one another through the stages, so stage s works on micro-batch m while stage s + 1 works
+  on m - 1. Point-to-point transfers are asynchronous (`isend` / `irecv` run on the communicator's own stream;
+  the compute stream only waits, by event, for the transfer it needs next) and the compute between a receive
+  and a send is captured as a per-stage, per-micro-batch CUDA graph.
+* `pipelined_decode(...)` is the steady-state loop of a generation job: `pp` micro-batches stay in flight ACROSS
+  steps (1F1B), positions advance on the device, and the token feedback from the last stage to the first
+  travels on its own communicator, so that in steady state no stage idles.
+* Within a stage, tensor parallelism uses that stage's own TPComm (fused collectives over the stage's ranks).
 
 Counterpart of the reference's PP send/recv wiring (crates/skein_emit/src/op_wiring.rs:688,710;
-crates/skein_runtime/src/distributed/rank_executor.rs:255-300), token broadcast (gpu_rank.rs:601-624) and the
-pp == 2 micro-batched decode (gpu_rank.rs:1029-1290).
+crates/skein_runtime/src/distributed/rank_executor.rs:255-300), its grouped send/recv (crates/skein_runtime/
+src/cuda/nccl.rs:362-445), token broadcast (gpu_rank.rs:601-624), the pp == 2 micro-batched decode
+(gpu_rank.rs:1029-1290) and its continuous pipelined loops (gpu_rank.rs:1293,1566).
 """
 from __future__ import annotations
 
@@ -20,7 +27,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.config import ParallelLayout
-from ..models.decoder import BatchInputs, Decoder
+from ..models.decoder import BatchInputs, Decoder, SamplingInputs
 
 
 def make_groups(layout_dims, rank: int, backend=None):
@@ -48,8 +55,33 @@ def make_groups(layout_dims, rank: int, backend=None):
     return my_tp, me.pp_group(), my_pp
 
 
+def _rows(inp: BatchInputs, lo: int, hi: int) -> BatchInputs:
+    """Rows lo..hi of a decode step's inputs (views of the same static buffers)."""
+    return BatchInputs(token_ids=inp.token_ids[lo:hi], positions=inp.positions[lo:hi], block_table=inp.block_table[lo:hi],
+                       seq_lens=inp.seq_lens[lo:hi], ctx_hint=inp.ctx_hint)
+
+
+def _sampling_rows(s: SamplingInputs | None, lo: int, hi: int):
+    if s is None:
+        return None
+    return SamplingInputs(s.temperature[lo:hi], s.top_k[lo:hi], s.top_p[lo:hi], s.seeds[lo:hi], s.step[lo:hi])
+
+
+class _StageGraph:
+    """The captured compute of one stage for one micro-batch: static receive buffer in, residual (or tokens) out."""
+
+    def __init__(self):
+        self.graph = None
+        self.hidden_in = None
+        self.out = None          # residual stream [rows, H] (not last stage) or sampled tokens [rows] (last stage)
+        self.logits = None
+        self.seen = 0
+        self.pending_send = None
+
+
 class PipelineStage:
-    def __init__(self, decoder: Decoder, layout: ParallelLayout, pp_ranks, pp_group):
+    def __init__(self, decoder: Decoder, layout: ParallelLayout, pp_ranks, pp_group, micro_batches: int | None = None,
+                 use_graphs: bool | None = None):
         self.dec, self.layout, self.pp_ranks, self.pp_group = decoder, layout, pp_ranks, pp_group
         self.stage, self.n_stages = layout.pp_rank, layout.pp
         self.first, self.last = self.stage == 0, self.stage == layout.pp - 1
@@ -59,75 +91,149 @@ class PipelineStage:
         self.cfg, self.device, self.num_pages, self.page_size, self.max_pos, self.w = (
             decoder.cfg, decoder.device, decoder.num_pages, decoder.page_size, decoder.max_pos, decoder.w)
         self.comm = decoder.comm
+        self.micro_batches = micro_batches if micro_batches is not None else self.n_stages
+        fused = decoder.comm is None or decoder.comm.mode != "nccl"
+        self.use_graphs = (self.device.type == "cuda" and fused) if use_graphs is None else (use_graphs and self.device.type == "cuda")
+        self._graphs: dict = {}
+        self.stage_busy_events = []     # (start, end) CUDA events around this stage's compute, when `time_stages` is set
+        self.time_stages = False
+
+    # ---- one stage's compute for one (micro-)batch ------------------------------------------------------------------
+    def _compute(self, inp: BatchInputs, hidden, sampling):
+        residual, normed = self.dec.forward_hidden(inp, hidden)
+        if not self.last:
+            return residual.contiguous(), None
+        logits = self.dec.logits(normed, inp)
+        return self.dec.sample(logits, sampling), logits
+
+    def _run_stage(self, inp: BatchInputs, sampling, key):
+        """Receive (if not first), compute (captured graph when enabled), return (out, logits). The receive is waited for
+        by the compute stream only; the host does not block."""
+        rows, H = inp.token_ids.shape[0], self.cfg.hidden_size
+        sg = self._graphs.get(key)
+        if sg is None:
+            sg = self._graphs[key] = _StageGraph()
+            if not self.first:
+                sg.hidden_in = torch.empty(rows, H, dtype=torch.bfloat16, device=self.device)
+        if sg.pending_send is not None:       # last step's send of this slot must have left before its buffer is rewritten
+            sg.pending_send.wait()
+            sg.pending_send = None
+        if not self.first:
+            dist.irecv(sg.hidden_in, src=self.prev).wait()
+        ev = None
+        if self.time_stages and self.device.type == "cuda":
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        sg.seen += 1
+        if self.use_graphs and not inp.is_prefill:
+            if sg.graph is None and sg.seen >= 2:      # the first sight runs eagerly: it allocates workspaces and caches
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize()
+                # thread-local capture mode: the process group's watchdog thread keeps querying the events of transfers
+                # in flight, which the default (global) mode would count as a violation of this thread's capture
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    sg.out, sg.logits = self._compute(inp, sg.hidden_in, sampling)
+                sg.graph = g
+            if sg.graph is not None:
+                sg.graph.replay()
+            else:
+                sg.out, sg.logits = self._compute(inp, sg.hidden_in, sampling)
+        else:
+            sg.out, sg.logits = self._compute(inp, sg.hidden_in, sampling)
+        if ev is not None:
+            ev[1].record()
+            self.stage_busy_events.append(ev)
+        if not self.last:
+            sg.pending_send = dist.isend(sg.out, dst=self.next)
+        return sg.out, sg.logits
 
     def _n_out_rows(self, inp: BatchInputs) -> int:
         return inp.logit_rows.shape[0] if (inp.is_prefill and inp.logit_rows is not None) else inp.token_ids.shape[0]
 
     def forward(self, inp: BatchInputs, sampling=None):
         """One step through the whole pipeline. Every stage calls this with the same `inp`."""
-        T, H = inp.token_ids.shape[0], self.cfg.hidden_size
-        hidden = None
-        if not self.first:
-            hidden = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
-            dist.recv(hidden, src=self.prev)
-        residual, normed = self.dec.forward_hidden(inp, hidden)
         n_out = self._n_out_rows(inp)
-        if not self.last:
-            dist.send(residual.contiguous(), dst=self.next)
-            tokens = torch.empty(n_out, dtype=torch.int32, device=self.device)
-            logits = None
+        T = inp.token_ids.shape[0]
+        M = self.micro_batches if (not inp.is_prefill and self.n_stages > 1 and T >= 2 * self.micro_batches
+                                   and T % self.micro_batches == 0) else 1
+        if M == 1:
+            key = ("whole", inp.token_ids.data_ptr(), T, sampling is not None) if not inp.is_prefill else ("prefill", T)
+            if inp.is_prefill:
+                self._graphs.pop(key, None)          # prefill chunks differ in shape from call to call: nothing is kept
+            out, logits = self._run_stage(inp, sampling, key)
+            tokens = out if self.last else torch.empty(n_out, dtype=torch.int32, device=self.device)
+            if inp.is_prefill:
+                sg = self._graphs.pop(key, None)
+                if sg is not None and sg.pending_send is not None:
+                    sg.pending_send.wait()
         else:
-            logits = self.dec.logits(normed, inp)
-            tokens = self.dec.sample(logits, sampling)
+            per = T // M
+            tokens = torch.empty(T, dtype=torch.int32, device=self.device)
+            logits = None
+            for m in range(M):
+                lo, hi = m * per, (m + 1) * per
+                out, _ = self._run_stage(_rows(inp, lo, hi), _sampling_rows(sampling, lo, hi),
+                                         ("micro", inp.token_ids.data_ptr(), T, m, sampling is not None))
+                if self.last:
+                    tokens[lo:hi].copy_(out)
         # token feedback to every stage of this pipeline group
         dist.broadcast(tokens, src=self.pp_ranks[-1], group=self.pp_group)
         return tokens, logits
 
+    def idle_fraction(self, wall_ms: float) -> float | None:
+        """1 - (time this stage spent computing) / wall time, from the CUDA events recorded while `time_stages` was set."""
+        if not self.stage_busy_events or wall_ms <= 0:
+            return None
+        torch.cuda.synchronize()
+        busy = sum(s.elapsed_time(e) for s, e in self.stage_busy_events)
+        return max(0.0, 1.0 - busy / wall_ms)
 
-def pipelined_decode(stage: PipelineStage, micro_inputs: list, steps: int, advance, feedback_group=None):
+
+def pipelined_decode(stage: PipelineStage, micro_inputs: list, steps: int, advance, feedback_group=None,
+                     resume: bool = False, more: bool = False, prev_tokens=None):
     """Steady-state pipelined greedy decode of len(micro_inputs) micro-batches for `steps` tokens each.
 
     micro_inputs[m] is the BatchInputs of micro-batch m (device tensors that `advance(inp, tokens)` updates in
     place for the next step; `tokens` is None on stages that do not embed). Stage s works on micro-batch m
     while stage s + 1 works on m - 1, so with at least `pp` micro-batches no stage idles after the fill phase.
     Point-to-point ops are enqueued in the same order on both sides of every boundary, which is what makes the
-    send/recv pairs match. Sampled tokens go from the last stage to the first on `feedback_group`, a separate
-    communicator, so that the feedback never queues behind activation traffic.
-    Returns [steps][micro] token tensors on the last stage (None entries elsewhere).
+    send/recv pairs match; they run on the communicators' own streams and the compute stream waits, by event,
+    only for the transfer it needs next. Each micro-batch's stage compute is a captured CUDA graph (from its second
+    step on). Sampled tokens go from the last stage to the first on `feedback_group`, a separate communicator, so
+    that the feedback never queues behind activation traffic.
+    `more`: another call will continue this decode, so the last step's tokens are fed back as well; `resume`: this
+    call continues one that ended with `more` (its first step receives that feedback; a single-stage "pipeline" takes
+    the tokens from `prev_tokens`). Returns [steps][micro] token tensors on the last stage (None entries elsewhere).
     """
     M = len(micro_inputs)
     out = [[None] * M for _ in range(steps)]
-    H = stage.cfg.hidden_size
-    from .. import ops
     first_rank, last_rank = stage.pp_ranks[0], stage.pp_ranks[-1]
-    pending = []   # keeps isend handles and their buffers alive
+    pending = []   # isend handles of the token feedback, with their buffers
+    tok_in = [torch.empty(inp.token_ids.shape[0], dtype=torch.int32, device=stage.device) for inp in micro_inputs]
     for t in range(steps):
         for m in range(M):
             inp = micro_inputs[m]
-            if t > 0:
+            if t > 0 or resume:
                 # token feedback of the previous step, received only now: the pipeline never waits on it while
                 # it still has other micro-batches to work on
                 toks_prev = None
                 if stage.first and stage.n_stages > 1:
-                    toks_prev = torch.empty(inp.token_ids.shape[0], dtype=torch.int32, device=stage.device)
-                    dist.recv(toks_prev, src=last_rank, group=feedback_group)
+                    dist.irecv(tok_in[m], src=last_rank, group=feedback_group).wait()
+                    toks_prev = tok_in[m]
                 elif stage.n_stages == 1:
-                    toks_prev = out[t - 1][m]
+                    toks_prev = out[t - 1][m] if t > 0 else prev_tokens[m]
                 advance(inp, toks_prev)
-            hidden = None
-            if not stage.first:
-                hidden = torch.empty(inp.token_ids.shape[0], H, dtype=torch.bfloat16, device=stage.device)
-                dist.recv(hidden, src=stage.prev)
-            residual, normed = stage.dec.forward_hidden(inp, hidden)
+            res, _ = stage._run_stage(inp, None, ("steady", m))
             if not stage.last:
-                dist.send(residual.contiguous(), dst=stage.next)
                 continue
-            lg = stage.dec.logits(normed, inp)
-            toks = stage.dec.comm.vocab_parallel_argmax(lg, stage.dec.sh["V_local"]) if (stage.dec.comm and stage.dec.comm.size > 1) else ops.sample_argmax(lg)
+            toks = res.clone()          # the graph's output buffer is rewritten by the next replay
             out[t][m] = toks
-            if stage.n_stages > 1 and t + 1 < steps:
-                # asynchronous on the feedback communicator: the compute stream goes on with the next micro-batch
+            if stage.n_stages > 1 and (t + 1 < steps or more):
                 pending.append((dist.isend(toks, dst=first_rank, group=feedback_group), toks))
     for w, _ in pending:
         w.wait()
+    for sg in stage._graphs.values():
+        if sg.pending_send is not None:
+            sg.pending_send.wait()
+            sg.pending_send = None
     return out

@@ -147,6 +147,16 @@ def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
         with urllib.request.urlopen(req, timeout=120) as resp:
             body = json.loads(resp.read().decode())
         assert len(body["tokens"]) == 4 and body["finish_reason"] == "length"
+        # the trace replayed against the running two-rank server over HTTP/SSE (how a multi-rank artifact is benchmarked)
+        trace = tmp_path / "t.jsonl"
+        trace.write_text(json.dumps({"slo": {"ttft_p95_ms": 60000, "tpot_p95_ms": 60000, "max_accuracy_drift": 0.01,
+                                             "recompile_drift_threshold_kl": 0.05}}) + "\n" +
+                         "".join(json.dumps({"prompt_tokens": 10 + i, "output_tokens": 3, "arrival_ms": 5 * i}) + "\n" for i in range(3)))
+        rb = subprocess.run([*cli, "bench", "--url", f"http://127.0.0.1:{port}", "--workload", str(trace), "--vocab-size", "300",
+                             "--max-seq-len", "128"], capture_output=True, text=True, cwd=ROOT, timeout=180, env=env)
+        assert rb.returncode == 0, rb.stderr[-2000:]
+        bj = json.loads(rb.stdout.strip().splitlines()[-1])
+        assert bj["requests_ok"] == 3 and bj["requests_failed"] == 0 and bj["ttft_p50_ms"] > 0 and bj["throughput_tok_s"] > 0
         p.send_signal(signal.SIGTERM)
         out, err = p.communicate(timeout=90)
     finally:

@@ -81,6 +81,13 @@ def test_pull_collectives_match_the_library():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_prefill_decode_disaggregation_over_peer_memory():
+    """A prompt prefilled on GPU 0, its KV pages stored into GPU 1's pools by the page-copy kernel over NVLink, decoded
+    on GPU 1: same tokens as prefill + decode on one GPU. See workers/disagg_worker.py."""
+    _run(2, port=29554, worker="disagg_worker.py", ok="DISAGG_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_pp2_gpu(tmp_path):
     """Two pipeline stages on two GPUs (NCCL point-to-point of the residual stream, token feedback, micro-batched
     pipelined decode) produce exactly the single-stage tokens. See workers/pp_worker.py."""

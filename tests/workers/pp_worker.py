@@ -71,7 +71,12 @@ def main():
         inp.positions.add_(1)
         inp.seq_lens.add_(1)
 
-    out = pp.pipelined_decode(stage, micro, 4, advance, fb_group)
+    # in two calls: the second continues where the first stopped (its first step receives the fed-back tokens); the
+    # stage compute runs as a captured graph from each micro-batch's second step on when the stages are on GPUs
+    out = pp.pipelined_decode(stage, micro, 2, advance, fb_group, more=True)
+    out += pp.pipelined_decode(stage, micro, 2, advance, fb_group, resume=True)
+    if use_cuda:
+        assert all(sg.graph is not None for k, sg in stage._graphs.items() if k[0] == "steady")
     if rank == world - 1:
         piped = [[int(x) for m in range(2) for x in out[t][m].tolist()] for t in range(4)]
     else:
