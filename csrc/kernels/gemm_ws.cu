@@ -16,6 +16,11 @@
 //     token tile, or a store of the partial result into a peer-mapped local buffer followed by a
 //     release of this rank's flag on every tensor-parallel peer (the all-reduce is finished by the
 //     consumer, which pulls the partials over NVLink: see norm.cu, reduce_residual_rmsnorm).
+//   * block-scaled fp8 weights with bf16 activations (the plan's weight fp8_e4m3 / activation bf16 combination):
+//     the weight tile travels as e4m3 (half the bytes of the decode step's dominant traffic), four more warps
+//     turn each landed tile into bf16 in shared memory, multiplying every row by its 1 x 128 block scale on the
+//     way, and the tensor cores run the same bf16 MMAs into ONE accumulator for the whole K range. Nothing is
+//     drained per K block and the activations are not quantised at all.
 //
 // Replaces the reference's cuBLASLt matmul host op (vendor/luminal/crates/luminal_cuda_lite/src/
 // host/cublaslt/mod.rs:888-1130), its fp8 GEMV (same file :797-886) and the GLUMoE GEMV kernels
@@ -38,8 +43,10 @@ constexpr int BLOCK_KB = 128;     // bytes of K per stage row (64 bf16 or 128 e4
 constexpr int W_TILE_BYTES = TILE_F * BLOCK_KB;  // 16 KB
 constexpr int ACC_STRIDE_MAX = 256;   // TMEM columns per accumulator buffer, at most
 constexpr int NUM_THREADS = 192;
+constexpr int W8_THREADS = 320;   // + 4 converter warps (e4m3 -> scaled bf16 in shared memory)
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_STAGES = 12;
+constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks (64 K elements: one 16 KB bf16 tile per weight tile)
 
 // Optional phase timer (compile with -DSKEIN_GEMM_TIMING): every CTA records %globaltimer at the points marked
 // TS(i) below into g_gemm_times[cta][i]; skein_gemm_times() copies the table out. Points: 0 entry, 1 set-up done,
@@ -58,17 +65,27 @@ struct KernelArgs {
   int stages;
   int stage_bytes;
   int x_tile_bytes;
+  int conv_base;    // W8: byte offset of the converted-tile ring inside the dynamic shared memory
   uint64_t budget_ns;
 };
 
-template <bool DUAL>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// Two e4m3 values -> two floats (exact: e4m3 is a subset of f16).
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"(v));
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+template <bool DUAL, bool W8>
+__global__ void __launch_bounds__(W8 ? W8_THREADS : NUM_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                const KernelArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ Sched sched;
   __shared__ __align__(8) uint64_t bar_full[MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_empty[MAX_STAGES];
+  __shared__ __align__(8) uint64_t bar_cfull[W8_CONV_SLOTS];    // W8: a converted half K-block is ready for the MMA warp
+  __shared__ __align__(8) uint64_t bar_cempty[W8_CONV_SLOTS];   // W8: the MMAs that read it are done
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_smem;
@@ -96,6 +113,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       mbar_init(smem_u32(&bar_tfull[b]), 1);
       mbar_init(smem_u32(&bar_tempty[b]), EPI_THREADS);
     }
+    if (W8) {
+      for (int c = 0; c < W8_CONV_SLOTS; ++c) {
+        mbar_init(smem_u32(&bar_cfull[c]), 128);
+        mbar_init(smem_u32(&bar_cempty[c]), 1);
+      }
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -107,7 +130,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tma_prefetch_desc(&tmX);
   }
   pdl_wait();
-  if (threadIdx.x == 0) build_sched(sched, p, p.fp8 ? 128 : 64, (int)gridDim.x, p.line_cut_only == 0);
+  if (threadIdx.x == 0) build_sched(sched, p, W8 ? 128 : 64, (int)gridDim.x, p.line_cut_only == 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -119,7 +142,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int kb_end = cta_end(sched, blockIdx.x);
   const bool has_work = kb_begin < kb_end;
   const int n_tile = p.n_tile;
-  const int k_elems = p.fp8 ? 128 : 64;
+  const int k_elems = W8 ? 128 : 64;
+  constexpr int W_STAGE_BYTES = (DUAL ? 2 : 1) * W_TILE_BYTES;   // weight bytes of one stage (bf16: 64 K, e4m3: 128 K)
 
   if (has_work) {
     if (warp == 0) {
@@ -159,7 +183,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               tma_load_2d(st, &tmW, full, kb * k_elems, w_row, pol_w);
               if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, full, kb * k_elems, w_row + p.up_row_off, pol_w);
             }
-            tma_load_2d(st + (DUAL ? 2 : 1) * W_TILE_BYTES, &tmX, full, kb * k_elems, x_row, pol_x);
+            tma_load_2d(st + W_STAGE_BYTES, &tmX, full, kb * k_elems, x_row, pol_x);
+            // e4m3 weights: a stage covers 128 K elements, i.e. two 64-wide bf16 activation tiles
+            if (W8) tma_load_2d(st + W_STAGE_BYTES + a.x_tile_bytes / 2, &tmX, full, kb * k_elems + 64, x_row, pol_x);
           }
           pos = u * KB + kb1;
         }
@@ -167,7 +193,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else if (warp == 1) {
       // ================= MMA issuer =================
       if (elect_one()) {
-        const uint32_t idesc = p.fp8 ? umma_idesc(0, 0, TILE_F, n_tile) : umma_idesc(1, 1, TILE_F, n_tile);
+        const uint32_t idesc = umma_idesc(1, 1, TILE_F, n_tile);
         uint32_t it = 0;
         uint32_t seg = 0;
         int pos = kb_begin;
@@ -189,6 +215,35 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s = it % a.stages;
             const uint32_t ph = (it / a.stages) & 1;
+            const uint32_t st = smem_base + s * a.stage_bytes;
+            if (W8) {
+              // the weights of this stage arrive as two converted halves (64 K elements each) from the converter warps
+#pragma unroll 1
+              for (int h = 0; h < 2 && ok; ++h) {
+                const uint32_t hit = 2 * it + h, c = hit % W8_CONV_SLOTS, cph = (hit / W8_CONV_SLOTS) & 1;
+                if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
+                  report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
+                  abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+                if (hit == 0) TS(2);
+                const uint32_t cw = smem_base + a.conv_base + c * W_STAGE_BYTES;
+                const uint64_t dw = umma_desc_sw128(cw);
+                const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
+                  mma_f16(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
+                  if (DUAL) mma_f16(d_tmem + n_tile, umma_desc_sw128(cw + W_TILE_BYTES) + 2 * k, dx + 2 * k, idesc, accum);
+                }
+                tc_commit(smem_u32(&bar_cempty[c]));
+              }
+              if (!ok) break;
+              tc_commit(smem_u32(&bar_empty[s]));  // the activation tiles of the stage have been read as well
+              continue;
+            }
             if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, a.budget_ns)) {
               report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
               abort_flag = 1;
@@ -197,18 +252,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
             tc_fence_after();
             if (it == 0) TS(2);
-            const uint32_t st = smem_base + s * a.stage_bytes;
             const uint64_t dw = umma_desc_sw128(st);
-            const uint64_t dx = umma_desc_sw128(st + (DUAL ? 2 : 1) * W_TILE_BYTES);
+            const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
               const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-              if (p.fp8) mma_f8(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
-              else mma_f16(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
+              mma_f16(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
               if (DUAL) {
                 const uint64_t du = umma_desc_sw128(st + W_TILE_BYTES);
-                if (p.fp8) mma_f8(d_tmem + n_tile, du + 2 * k, dx + 2 * k, idesc, accum);
-                else mma_f16(d_tmem + n_tile, du + 2 * k, dx + 2 * k, idesc, accum);
+                mma_f16(d_tmem + n_tile, du + 2 * k, dx + 2 * k, idesc, accum);
               }
             }
             tc_commit(smem_u32(&bar_empty[s]));  // frees the stage when these MMAs are done
@@ -219,7 +271,78 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           pos = u * KB + kb1;
         }
       }
-    } else {
+    } else if (W8 && warp >= 6) {
+      // ================= converters (warps 6..9): e4m3 tile -> bf16 tile scaled by the row's 1 x 128 block scale =========
+      // Thread r owns weight row r of the tile. The raw tile was written by TMA with the 128-byte swizzle (16-byte chunk
+      // c of row r sits at chunk c ^ (r & 7)); the bf16 tiles the tensor cores read use the same pattern, so a 16-byte
+      // chunk of e4m3 (16 K elements) becomes two 16-byte chunks of the 64-K-wide half it belongs to.
+      const int r = threadIdx.x - 192;
+      const long long w_rows_total = (long long)p.G * p.w_rows_per_group;
+      uint32_t it = 0;
+      int pos = kb_begin;
+      bool ok = true;
+      while (pos < kb_end && ok) {
+        const int u = pos / KB;
+        const int kb0 = pos - u * KB;
+        int kb1 = KB;
+        if (u * KB + KB > kb_end) kb1 = kb_end - u * KB;
+        const Unit un = decode_unit(sched, p.G, u);
+        const long long w_row = (long long)un.g * p.w_rows_per_group + un.m * TILE_F + r;
+        for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+          const uint32_t s = it % a.stages, ph = (it / a.stages) & 1;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, a.budget_ns)) {
+            report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint8_t* raw = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * a.stage_bytes;
+          float sc[DUAL ? 2 : 1];
+#pragma unroll
+          for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
+            const long long row = w_row + (t ? p.up_row_off : 0);
+            // rows beyond the matrix were zero-filled by TMA: any finite scale will do
+            sc[t] = (row < w_rows_total && (un.m * TILE_F + r) < p.F)
+                        ? __ldg(p.w_scale + (size_t)kb * w_rows_total + row) : 0.f;
+          }
+#pragma unroll 1
+          for (int h = 0; h < 2 && ok; ++h) {
+            const uint32_t hit = 2 * it + h, c = hit % W8_CONV_SLOTS, cph = (hit / W8_CONV_SLOTS) & 1;
+            if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
+              report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            uint8_t* conv = smem_raw + (smem_base - smem_u32(smem_raw)) + a.conv_base + (size_t)c * W_STAGE_BYTES;
+#pragma unroll
+            for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
+              const uint8_t* src_row = raw + t * W_TILE_BYTES + r * 128;
+              uint8_t* dst_row = conv + t * W_TILE_BYTES + r * 128;
+#pragma unroll
+              for (int cc = 0; cc < 4; ++cc) {           // the half's four 16-byte chunks of e4m3
+                const int chunk = h * 4 + cc;
+                const uint4 v = *reinterpret_cast<const uint4*>(src_row + ((chunk ^ (r & 7)) << 4));
+                const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+                uint4 o[2];
+                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float2 f = e4m3x2_to_float2(e[j]);
+                  ob[j] = __floats2bfloat162_rn(f.x * sc[t], f.y * sc[t]);
+                }
+                *reinterpret_cast<uint4*>(dst_row + (((2 * cc) ^ (r & 7)) << 4)) = o[0];
+                *reinterpret_cast<uint4*>(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)) = o[1];
+              }
+            }
+            // make the generic-proxy stores visible to the tensor cores' (async proxy) reads, then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bar_cfull[c]));
+          }
+        }
+        pos = u * KB + kb1;
+      }
+    } else if (warp < 6) {
       // ================= epilogue (warps 2..5) =================
       const int q = warp & 3;                 // TMEM lane quarter this warp may read
       const int r = q * 32 + lane;            // feature row inside the tile
@@ -473,7 +596,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // epilogue thread orders its stores device-wide, the CTAs count themselves in, and the last one issues the
   // single system-scope fence that orders all of those stores before the flag words it then writes.
   if (p.mode == 2) {
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
@@ -591,13 +714,15 @@ static int sm_count_cached() {
 
 static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* smem) {
   if (!p || p->G < 1 || p->G > SKEIN_MAX_GROUPS) return -1;
-  const int kelem = p->fp8 ? 128 : 64;
+  const bool w8 = p->fp8 == 2;   // e4m3 weights with 1 x 128 block scales, bf16 activations
+  const int kelem = w8 ? 128 : 64;
   if (p->K <= 0 || p->K % kelem != 0) return -2;
   const bool dual = p->mode == 1;
   if (p->n_tile < 16 || p->n_tile % 16 != 0 || p->n_tile > (dual ? 128 : 256)) return -3;
   if (p->mode < 0 || p->mode > 2) return -4;
   if (p->mode == 2 && (p->n_peers < 1 || p->n_peers > SKEIN_MAX_PEERS)) return -5;
-  if (p->fp8) return -6;  // block-scaled e4m3 goes through skein_gemm_ws_fp8
+  if (p->fp8 == 1) return -6;  // e4m3 x e4m3 with both operands block-scaled goes through skein_gemm_ws_fp8
+  if (w8 && (p->w_scale == nullptr || p->w_packed)) return -6;
   ka->p = *p;
   {
     const int acc_cols = (dual ? 2 : 1) * p->n_tile;
@@ -606,18 +731,21 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
     if (st > ACC_STRIDE_MAX) return -3;
     ka->acc_stride = st;   // two buffers: 64..512 columns, a power of two as the allocator requires
   }
-  ka->x_tile_bytes = p->n_tile * BLOCK_KB;
+  ka->x_tile_bytes = p->n_tile * BLOCK_KB * (w8 ? 2 : 1);    // e4m3 stage: 128 K elements = two bf16 activation tiles
   ka->stage_bytes = (dual ? 2 : 1) * W_TILE_BYTES + ka->x_tile_bytes;
-  const int budget = 200 * 1024;
+  int budget = 200 * 1024;
+  ka->conv_base = 0;
+  if (w8) budget -= W8_CONV_SLOTS * (dual ? 2 : 1) * W_TILE_BYTES;
   int st = budget / ka->stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
   if (p->stages > 0 && p->stages < st) st = p->stages;
   if (st < 2) return -7;
   ka->stages = st;
+  ka->conv_base = st * ka->stage_bytes;      // the converted-tile ring follows the stages (both are multiples of 1 KB)
   ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : gemm_wait_budget_ms()) * 1000000ull;
   *grid = p->grid > 0 ? p->grid : sm_count_cached();
   if (*grid > sm_count_cached()) *grid = sm_count_cached();   // the split-K reduction needs every CTA resident
-  *smem = (size_t)st * ka->stage_bytes + 1024;
+  *smem = (size_t)st * ka->stage_bytes + (w8 ? W8_CONV_SLOTS * (dual ? 2 : 1) * W_TILE_BYTES : 0) + 1024;
   return 0;
 }
 
@@ -647,27 +775,33 @@ extern "C" int skein_gemm_ws(const SkeinGemmParams* p, void* stream) {
   if (rc) return rc;
   if (!p->workspace || !p->counters) return -8;
   CUtensorMap tmW, tmX;
-  const int eb = p->fp8 ? 1 : 2;
+  const bool w8 = p->fp8 == 2;
   if (p->w_packed) {
     if (p->w_rows_per_group % TILE_F != 0 || (p->mode == 1 && p->up_row_off % TILE_F != 0)) return -9;
-    const uint64_t tiles = (uint64_t)p->G * (p->w_rows_per_group / TILE_F) * (p->K / (p->fp8 ? 128 : 64));
-    rc = cached_tmap_2d(&tmW, p->W, tiles * TILE_F, p->fp8 ? 128 : 64, eb, TILE_F);
+    const uint64_t tiles = (uint64_t)p->G * (p->w_rows_per_group / TILE_F) * (p->K / 64);
+    rc = cached_tmap_2d(&tmW, p->W, tiles * TILE_F, 64, 2, TILE_F);
   } else {
-    rc = cached_tmap_2d(&tmW, p->W, (uint64_t)p->G * p->w_rows_per_group, p->K, eb, TILE_F);
+    rc = cached_tmap_2d(&tmW, p->W, (uint64_t)p->G * p->w_rows_per_group, p->K, w8 ? 1 : 2, TILE_F);
   }
   if (rc) return rc;
-  rc = cached_tmap_2d(&tmX, p->X, p->x_rows, p->K, eb, p->n_tile);
+  rc = cached_tmap_2d(&tmX, p->X, p->x_rows, p->K, 2, p->n_tile);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static bool attr_done[2] = {false, false};
+  static bool attr_done[4] = {false, false, false, false};
   const bool dual = p->mode == 1;
-  if (!attr_done[dual]) {
-    cudaError_t e = dual ? cudaFuncSetAttribute(gemm_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048)
-                         : cudaFuncSetAttribute(gemm_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
-    if (e != cudaSuccess) return (int)e;
-    attr_done[dual] = true;
+  const int variant = (w8 ? 2 : 0) + (dual ? 1 : 0);
+  auto with_kernel = [&](auto fn) -> cudaError_t {
+    if (!attr_done[variant]) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+      if (e != cudaSuccess) return e;
+      attr_done[variant] = true;
+    }
+    return launch_pdl(fn, dim3(grid), dim3(w8 ? W8_THREADS : NUM_THREADS), smem, s, tmW, tmX, ka);
+  };
+  switch (variant) {
+    case 0: return (int)with_kernel(gemm_ws_kernel<false, false>);
+    case 1: return (int)with_kernel(gemm_ws_kernel<true, false>);
+    case 2: return (int)with_kernel(gemm_ws_kernel<false, true>);
+    default: return (int)with_kernel(gemm_ws_kernel<true, true>);
   }
-  const cudaError_t le = dual ? launch_pdl(gemm_ws_kernel<true>, dim3(grid), dim3(NUM_THREADS), smem, s, tmW, tmX, ka)
-                             : launch_pdl(gemm_ws_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem, s, tmW, tmX, ka);
-  return (int)le;
 }

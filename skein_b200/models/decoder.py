@@ -212,10 +212,11 @@ class Decoder:
         selected fp8 for this block, its block-scaled e4m3 copy (activations quantised on the fly)."""
         w8 = lw.fp8.get(name)
         if w8 is not None:
-            xq, xs = ops.quant_fp8_block128(x)
+            # weights e4m3 with 1 x 128 block scales, activations bf16: the GEMM streams the e4m3 tiles and rescales them
+            # to bf16 in shared memory (ops/fp8.py)
             if grouped is not None:
-                return fp8.grouped_linear(xq, xs, w8, *grouped, swiglu=swiglu, rows_hint=rows_hint)
-            return fp8.linear(xq, xs, w8, swiglu=swiglu)
+                return fp8.grouped_linear_a16(x, w8, *grouped, swiglu=swiglu, rows_hint=rows_hint)
+            return fp8.linear_a16(x, w8, swiglu=swiglu)
         w = getattr(lw, name)
         if grouped is not None:
             return ops.grouped_linear(x, w, *grouped, swiglu=swiglu, rows_hint=rows_hint)
@@ -228,8 +229,7 @@ class Decoder:
         if w8 is not None and single:
             return self._col_linear(x, lw, name, grouped=grouped).unsqueeze(0), None, None
         if w8 is not None and x.is_cuda and hasattr(self.comm, "linear_push_fp8"):
-            xq, xs = ops.quant_fp8_block128(x)
-            return self.comm.linear_push_fp8(xq, xs, w8, grouped)
+            return self.comm.linear_push_fp8(x, None, w8, grouped)
         w = getattr(lw, name)
         if w is None:
             w = w8.dequant()      # CPU ranks (reference operators): dequantise, then the bf16 path
@@ -263,8 +263,7 @@ class Decoder:
             h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep)
             w8 = lw.fp8.get("w2")
             if w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
-                hq, hs = ops.quant_fp8_block128(h)
-                part, flags, epoch = self.comm_moe.linear_push_fp8(hq, hs, w8, (cnt_l, off_l))
+                part, flags, epoch = self.comm_moe.linear_push_fp8(h, None, w8, (cnt_l, off_l))
             else:
                 w2 = lw.w2 if lw.w2 is not None else w8.dequant()
                 part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))

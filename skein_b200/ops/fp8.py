@@ -1,8 +1,14 @@
 """Block-scaled fp8 (e4m3, one fp32 scale per 1 x 128 block along K) linear operators.
 
-Weights are quantised once (`quantize_weight`), activations on the fly (`ops.quant_fp8_block128`); the GEMM
-(csrc/kernels/gemm_ws_fp8.cu) multiplies e4m3 x e4m3 on the tensor cores and applies both scales per
-K-block. On CPU the same math runs through the fp32 reference (dequantise, matmul).
+Two forms:
+  * weights fp8, activations bf16 (`linear_a16`, `grouped_linear_a16`, `linear_publish_a16`): what the plan's dtype
+    map selects (weight fp8_e4m3, activation bf16). The weight-streaming GEMM (csrc/kernels/gemm_ws.cu) moves the
+    e4m3 tiles, turns them into scaled bf16 in shared memory and keeps one accumulator for the whole K range, so
+    the bytes of a decode step halve and nothing else changes. This is the form the decoder uses.
+  * both operands fp8 (`linear`, `grouped_linear`, `linear_publish`; csrc/kernels/gemm_ws_fp8.cu): activations
+    quantised on the fly (`ops.quant_fp8_block128`), e4m3 x e4m3 on the tensor cores, both scales applied per K-block.
+Weights are quantised once (`quantize_weight`). On CPU the same math runs through the fp32 reference (dequantise,
+matmul).
 """
 from __future__ import annotations
 
@@ -165,3 +171,80 @@ def linear_publish(xq, xs, w: Fp8Weight, out_local, peer_flag, epoch, done_count
     p.epoch = epoch.data_ptr()
     p.done_counter = done_counter.data_ptr()
     _launch(p, "fp8 linear_publish")
+
+
+# ---- fp8 weights, bf16 activations -----------------------------------------------------------------------------------
+def _a16_params(x, w: Fp8Weight, out, F_out, n_tile, mode):
+    w2d = w.q.view(-1, w.shape[-1])
+    p = F._base_params(x, w2d, out, F_out, x.shape[1], n_tile, mode)
+    p.w_scale = w.scale_t.data_ptr()
+    p.fp8 = 2
+    return p
+
+
+def linear_a16(x, w: Fp8Weight, swiglu: bool = False, out=None, n_tile=None, _cfg=None):
+    """bf16 x [T, K] times a block-scaled e4m3 weight -> bf16 [T, F] (F = rows, or rows / 2 with the SwiGLU pair epilogue)."""
+    if not x.is_cuda:
+        wd = w.dequant()
+        return ref.swiglu_linear(x, wd) if swiglu else ref.linear(x, wd)
+    F._check_act(x)
+    T = x.shape[0]
+    rows = w.shape[-2]
+    Fo = rows // 2 if swiglu else rows
+    if out is None:
+        out = torch.empty(T, Fo, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    p = _a16_params(x, w, out, Fo, n_tile or F.pick_n_tile(T, swiglu), 1 if swiglu else 0)
+    p.w_rows_per_group, p.up_row_off = rows, (Fo if swiglu else 0)
+    F._gemm_launch(p, "fp8-weight linear", _cfg)
+    return out
+
+
+def grouped_linear_a16(xs, w: Fp8Weight, counts, offsets, swiglu: bool = False, out=None, n_tile=None, rows_hint=None, _cfg=None):
+    """Per-expert linear over expert-sorted bf16 rows with block-scaled e4m3 expert weights. w.shape = [E, rows, K]."""
+    if not xs.is_cuda:
+        return ref.grouped_linear(xs, w.dequant(), counts, offsets, swiglu)
+    F._check_act(xs)
+    R = xs.shape[0]
+    E, rows = w.shape[0], w.shape[1]
+    Fo = rows // 2 if swiglu else rows
+    if out is None:
+        out = torch.empty(R, Fo, dtype=torch.bfloat16, device=xs.device)
+    if R == 0:
+        return out
+    if n_tile is None:
+        avg = (rows_hint if rows_hint is not None else R) / E
+        n_tile = F.pick_n_tile(int(math.ceil(avg * 1.5)), swiglu)
+    p = _a16_params(xs, w, out, Fo, n_tile, 1 if swiglu else 0)
+    p.G, p.w_rows_per_group, p.up_row_off = E, rows, (Fo if swiglu else 0)
+    p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
+    F._gemm_launch(p, "fp8-weight grouped_linear", _cfg)
+    return out
+
+
+def linear_publish_a16(x, w: Fp8Weight, out_local, peer_flag, epoch, done_counter, ldo, grouped=None, n_tile=None, rows_hint=None):
+    """Row-parallel projection with e4m3 weights and bf16 activations whose partial result is published to the
+    tensor-parallel peers (the contract of ops.linear_push)."""
+    F._check_act(x)
+    R = x.shape[0]
+    if grouped is None:
+        rows = w.shape[-2]
+        p = _a16_params(x, w, out_local, rows, n_tile or F.pick_n_tile(R, False), 2)
+        p.w_rows_per_group = rows
+    else:
+        counts, offsets = grouped
+        E, rows = w.shape[0], w.shape[1]
+        if n_tile is None:
+            avg = (rows_hint if rows_hint is not None else R) / E
+            n_tile = F.pick_n_tile(int(math.ceil(avg * 1.5)), False)
+        p = _a16_params(x, w, out_local, rows, n_tile, 2)
+        p.G, p.w_rows_per_group = E, rows
+        p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
+    p.ldo = ldo
+    p.n_peers = len(peer_flag)
+    for i, pf in enumerate(peer_flag):
+        p.peer_flag[i] = pf
+    p.epoch = epoch.data_ptr()
+    p.done_counter = done_counter.data_ptr()
+    F._gemm_launch(p, "fp8-weight linear_publish")

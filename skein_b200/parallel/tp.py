@@ -158,9 +158,27 @@ class TPComm:
         return part, part.flags, part.epoch
 
     def linear_push_fp8(self, xq, xs, w8, grouped=None, rows_hint=None):
-        """linear_push for a block-scaled e4m3 weight and pre-quantised activations (ops/fp8.py)."""
+        """linear_push for a block-scaled e4m3 weight (ops/fp8.py). With `xs` None, `xq` holds bf16 activations
+        (weights fp8, activations bf16: the form the decoder uses); otherwise pre-quantised e4m3 activations with
+        their block scales."""
         from ..ops import fp8
         rows = xq.shape[0]
+        if xs is None:
+            x = xq
+            if not self._fused_ok(rows):
+                y = fp8.grouped_linear_a16(x, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear_a16(x, w8)
+                dist.all_reduce(y, group=self.group)
+                return y.unsqueeze(0), None, None
+            b = self.cur
+            self.cur ^= 1
+            if self.mode == "unfused":
+                y = fp8.grouped_linear_a16(x, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear_a16(x, w8)
+                self._publish(y, b)
+            else:
+                fp8.linear_publish_a16(x, w8, self.bufs[b], self._peer_flag[b], self.epochs[b:b + 1], self.done[b:b + 1],
+                                       self.hidden, grouped=grouped, rows_hint=rows_hint)
+            part = self._partials(b, rows)
+            return part, part.flags, part.epoch
         if not self._fused_ok(rows):
             y = fp8.grouped_linear(xq, xs, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear(xq, xs, w8)
             dist.all_reduce(y, group=self.group)

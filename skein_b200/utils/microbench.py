@@ -112,6 +112,12 @@ def op_moe(which, tp, a):
         fn = lambda: ops.grouped_linear(xs, w, cnt, off, swiglu=False, out=out)
         fl = 2 * rows * H * F
     by = w.numel() * 2 + xs.numel() * 2 + out.numel() * 2
+    if getattr(a, "fp8", False):   # e4m3 expert weights with 1 x 128 block scales, bf16 activations
+        from ..ops import fp8
+        wq = fp8.quantize_weight(w)
+        del w
+        by = wq.nbytes() + xs.numel() * 2 + out.numel() * 2
+        return (lambda: fp8.grouped_linear_a16(xs, wq, cnt, off, swiglu=(which == "gate_up"), out=out)), by, fl
     if a.packed:   # tile-packed weights: every 128 x 64 tile the GEMM loads is one contiguous 16 KB block
         wp = ops.pack_weight(w)
         del w
@@ -236,6 +242,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--packed", action="store_true", help="MoE ops: use tile-packed weights (ops.pack_weight)")
+    ap.add_argument("--fp8", action="store_true", help="MoE ops: block-scaled e4m3 expert weights with bf16 activations")
     ap.add_argument("--graph", action="store_true",
                     help="time launches back to back inside a CUDA graph over rotating operand copies (cold L2, "
                          "no per-launch event overhead) instead of one launch per event pair")
@@ -247,7 +254,7 @@ def main(argv=None):
             us = timeit_graph(lambda: build(name, a), by, a.iters, a.warmup)
         else:
             us = timeit(fn, a.iters, a.warmup, flush=not a.no_flush)
-        _report(f"{name}/tp{a.tp}" + ("/graph" if a.graph else ""), us, by, fl, pk)
+        _report(f"{name}/tp{a.tp}" + ("/fp8w" if a.fp8 and name.startswith("moe") else "") + ("/graph" if a.graph else ""), us, by, fl, pk)
     ops.workspace().check_status()
 
 

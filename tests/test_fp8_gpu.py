@@ -52,3 +52,40 @@ def test_fp8_grouped(swiglu):
     torch.cuda.synchronize(); ops.workspace().check_status()
     want = fp8.grouped_linear(xq.cpu(), xs.cpu(), fp8.Fp8Weight(wq.q.cpu(), wq.scale_t.cpu(), wq.shape), cnt.cpu(), off.cpu(), swiglu=swiglu)
     assert rel(y, want) < 1e-2
+
+
+# ---- e4m3 weights with bf16 activations: e4m3 tiles streamed, rescaled to bf16 in shared memory, one accumulator --------
+@pytest.mark.parametrize("T,F,K,swiglu", [(16, 256, 512, False), (64, 1024, 4096, False), (7, 384, 1024, True), (40, 1792, 4096, True),
+                                          (130, 512, 2048, False), (64, 4096, 1792 + 128 * 2, False), (3, 200, 256, False)])
+def test_fp8_weight_bf16_activation_linear(T, F, K, swiglu):
+    torch.manual_seed(0)
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * F if swiglu else F, K, device=DEV) / math.sqrt(K)).bfloat16()
+    wq = fp8.quantize_weight(w)
+    y = fp8.linear_a16(x, wq, swiglu=swiglu)
+    y2 = fp8.linear_a16(x, wq, swiglu=swiglu)
+    torch.cuda.synchronize(); ops.workspace().check_status()
+    assert torch.equal(y, y2)                                   # deterministic whatever the split of the K loop
+    wd = fp8.Fp8Weight(wq.q.cpu(), wq.scale_t.cpu(), wq.shape).dequant()
+    want = ref.swiglu_linear(x.cpu(), wd) if swiglu else ref.linear(x.cpu(), wd)     # fp32 reference on the dequantised weight
+    assert rel(y, want) < 8e-3, rel(y, want)
+    full = ref.swiglu_linear(x, w) if swiglu else ref.linear(x, w)
+    assert rel(y, full) < 0.06                                  # quantisation error against the bf16 weight
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_fp8_weight_bf16_activation_grouped(swiglu):
+    torch.manual_seed(1)
+    E, F, K = 8, 512, 1024
+    counts = [1, 33, 0, 16, 40, 5, 12, 7]
+    rows = sum(counts)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    off = torch.zeros(E + 1, dtype=torch.int32, device=DEV); off[1:] = torch.cumsum(cnt, 0)
+    xs_ = torch.randn(rows, K, device=DEV).bfloat16()
+    w = (torch.randn(E, 2 * F if swiglu else F, K, device=DEV) / math.sqrt(K)).bfloat16()
+    wq = fp8.quantize_weight(w)
+    y = fp8.grouped_linear_a16(xs_, wq, cnt, off, swiglu=swiglu)
+    torch.cuda.synchronize(); ops.workspace().check_status()
+    wd = fp8.Fp8Weight(wq.q.cpu(), wq.scale_t.cpu(), wq.shape).dequant()
+    want = ref.grouped_linear(xs_.cpu(), wd, cnt.cpu(), off.cpu(), swiglu)
+    assert rel(y, want) < 8e-3, rel(y, want)
