@@ -221,6 +221,13 @@ PYBIND11_MODULE(_skein_core, m) {
   m.def("lower_device", [](const std::string& plan, const std::string& cfg, size_t device) {
     return lowered_to_json(lower_device(Plan::from_json(Json::parse(plan)), import_model_str(cfg), device)).dump();
   });
+  // the same lowering for a placement given by its three degrees (the decoder asks for the program of its own rank
+  // when it is built without an artifact: benchmarks, tests)
+  m.def("lower_device_for", [](const std::string& cfg, uint32_t tp, uint32_t pp, uint32_t ep, size_t device) {
+    Plan p;
+    p.parallelism.tp = tp; p.parallelism.pp = pp; p.parallelism.ep = ep;
+    return lowered_to_json(lower_device(p, import_model_str(cfg), device)).dump();
+  });
   m.def("io_manifest", [](const std::string& plan, const std::string& cfg, size_t device) {
     return io_manifest(Plan::from_json(Json::parse(plan)), import_model_str(cfg), device).dump();
   });

@@ -89,6 +89,17 @@ class ModelConfig:
         cfg.validate()
         return cfg
 
+    def to_hf_dict(self) -> dict:
+        """The HuggingFace config.json fields that describe this model (what the planner and the lowering read)."""
+        d = {"architectures": [self.architecture], "hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
+             "num_hidden_layers": self.num_layers, "num_attention_heads": self.num_heads, "num_key_value_heads": self.num_kv_heads,
+             "head_dim": self.head_dim, "vocab_size": self.vocab_size, "rms_norm_eps": self.rms_norm_eps, "rope_theta": self.rope_theta,
+             "max_position_embeddings": self.max_position_embeddings, "tie_word_embeddings": self.tie_word_embeddings,
+             "hidden_act": "silu"}
+        if self.is_moe:
+            d.update(num_local_experts=self.num_experts, num_experts_per_tok=self.top_k)
+        return d
+
     @staticmethod
     def from_file(path) -> "ModelConfig":
         p = Path(path)

@@ -149,7 +149,6 @@ class Decoder:
         self.cfg, self.w, self.layout = cfg, weights, layout or ParallelLayout()
         self.comm = comm          # tensor-parallel communicator over this rank's TP group, or None
         self.comm_moe = comm_moe  # communicator over all tp x ep ranks of the stage (expert parallelism), or None
-        self._owner = None
         if self.layout.ep > 1 and comm_moe is None:
             raise ValueError("expert parallelism needs a communicator over the stage's tp x ep ranks (comm_moe)")
         self.sh = shard_shapes(cfg, self.layout)
@@ -175,6 +174,11 @@ class Decoder:
             if weights.embed.shape[0] > self.sh["V_local"]:      # the last rank's shard may be short
                 raise ValueError("the embedding table is neither whole nor this rank's vocabulary shard")
             self.embed_vocab_start = self.layout.tp_rank * self.sh["V_local"]
+        self.program = self._load_program()
+        self._ops = {name[4:]: getattr(self, name) for name in dir(self) if name.startswith("_op_")}
+        missing = sorted({it[1] for it in self.program if it[0] == "op"} - set(self._ops))
+        if missing:
+            raise RuntimeError(f"the lowering names operators this runtime does not implement: {missing}")
         if pack_moe is None:
             pack_moe = os.environ.get("SKEIN_PACK_MOE", "1") == "1"
         if pack_moe and dev.type == "cuda":
@@ -191,25 +195,226 @@ class Decoder:
                     if rows % 128 == 0 and K % 64 == 0 and half_ok:
                         setattr(lw, name, ops.pack_weight(w))
 
-    # ---- pieces ---------------------------------------------------------------------------------
-    def _attention(self, li: int, normed, inp: BatchInputs):
-        cfg, sh, lw = self.cfg, self.sh, self.w.layers[li]
-        qkv = self._col_linear(normed, lw, "wqkv")
-        if not inp.is_prefill and inp.seq_of_token is None and ops.can_fuse_rope(self.kv[li], sh["Hq"], sh["Hkv"]):
-            # decode: RoPE and the cache append ride in the attention kernel
-            return ops.attn_decode_rope(qkv, inp.positions, inp.block_table, self.cos_sin, self.kv[li], inp.seq_lens,
-                                        sh["Hq"], sh["Hkv"], cfg.head_dim, ctx_hint=inp.ctx_hint)
-        ops.rope_kv_append(qkv, inp.positions, inp.seq_of_token, inp.block_table, self.cos_sin, self.kv[li],
-                           sh["Hq"], sh["Hkv"], cfg.head_dim)
-        if inp.is_prefill:
-            return ops.attn_prefill(qkv, self.kv[li], inp.block_table, inp.q_start, inp.q_len, inp.seq_lens,
-                                    inp.max_q_len, sh["Hq"], sh["Hkv"], cfg.head_dim)
-        return ops.attn_decode(qkv, self.kv[li], inp.block_table, inp.seq_lens, sh["Hq"], sh["Hkv"], cfg.head_dim,
-                               ctx_hint=inp.ctx_hint)
+    # ---- the lowered program ------------------------------------------------------------------------
+    def _load_program(self):
+        """This rank's schedule from the lowering (csrc/core/emit.hpp: lower_device): the named operators of every
+        segment and the collectives between the segments, in order. It is what forward_hidden executes, so where a
+        collective sits is decided in one place, the lowering, and the artifact's segments.json describes exactly what
+        runs (compile/artifact.py: check_lowering compares the two)."""
+        import json
+
+        from .. import core
+        lay = self.layout
+        low = json.loads(core.lower_device_for(json.dumps(self.cfg.to_hf_dict()), lay.tp, lay.pp, lay.ep, lay.rank))
+        first_block = lay.stage_layers(self.cfg.num_layers)[0] if len(lay.stage_layers(self.cfg.num_layers)) else 0
+        segs = {s_["idx"]: s_["ops"] for s_ in low["segments"]}
+        prog = []
+        for st in low["sequencing"]:
+            if st["kind"] == "execute_segment":
+                for name in segs[st["segment"]]:
+                    if name.startswith("block_"):
+                        _, b, op = name.split("_", 2)
+                        prog.append(("op", op, int(b) - first_block))
+                    else:
+                        prog.append(("op", name, -1))
+            elif st["kind"] == "collective":
+                prog.append(("collective", st["collective"], st["tensor"]))
+        return prog
+
+    class _Run:
+        """State of one pass over the program."""
+        __slots__ = ("inp", "residual", "normed", "qkv", "attn", "pending", "pending_kind", "routed", "h", "sp", "T",
+                     "crossing", "embed_deferred", "row_idx", "row_w", "owner")
+
+        def __init__(self, inp, residual):
+            self.inp, self.residual = inp, residual
+            self.normed = self.qkv = self.attn = self.pending = self.routed = self.h = None
+            self.pending_kind, self.crossing, self.sp, self.T = None, None, False, 0
+            self.embed_deferred = False
+            self.row_idx = self.row_w = self.owner = None
+
+    @property
+    def _multi(self) -> bool:
+        return (self.comm is not None and self.comm.size > 1) or (self.comm_moe is not None and self.comm_moe.size > 1)
+
+    # ---- operators of the program (one method per operator name of the lowering) -----------------------
+    def _op_embed_tokens(self, st, _):
+        if self.embed_vocab_start is not None:
+            st.embed_deferred = True       # the ranks' lookups are summed where the lowering puts the embed_out all-reduce
+        else:
+            st.residual = ops.embed(st.inp.token_ids, self.w.embed)
+
+    def _op_input_layernorm(self, st, li):
+        gamma = self.w.layers[li].attn_norm
+        if st.pending is not None:
+            self._reduce(st, gamma)
+        elif st.normed is None:
+            st.normed = ops.rmsnorm(st.residual, gamma, self.cfg.rms_norm_eps)
+        if li == 0:
+            self._maybe_shard_rows(st)
+
+    def _maybe_shard_rows(self, st):
+        """Prefill-sized chunks under tensor parallelism take the sequence-parallel dataflow: from here on the residual
+        stream is this rank's slice of the token rows (see _reduce)."""
+        cfg, comm = self.cfg, self.comm
+        st.T = T = st.residual.shape[0]
+        if (st.inp.is_prefill and comm is not None and comm.size > 1 and self.layout.ep == 1 and st.residual.is_cuda
+                and hasattr(comm, "sp_ok") and comm.sp_ok(T, T * max(1, cfg.top_k if cfg.is_moe else 1))):
+            r0, n, _ = comm.sp_slice(T)
+            st.residual = st.residual[r0:r0 + n].contiguous()
+            st.sp = True
+
+    def _op_qkv_proj(self, st, li):
+        st.qkv = self._col_linear(st.normed, self.w.layers[li], "wqkv")
+
+    def _rope_fused(self, st, li) -> bool:
+        inp = st.inp
+        return (not inp.is_prefill and inp.seq_of_token is None
+                and ops.can_fuse_rope(self.kv[li], self.sh["Hq"], self.sh["Hkv"]))
+
+    def _op_rope_kv_append(self, st, li):
+        if self._rope_fused(st, li):
+            return          # decode: RoPE and the cache append ride in the attention kernel
+        inp, sh = st.inp, self.sh
+        ops.rope_kv_append(st.qkv, inp.positions, inp.seq_of_token, inp.block_table, self.cos_sin, self.kv[li],
+                           sh["Hq"], sh["Hkv"], self.cfg.head_dim)
+
+    def _op_attention(self, st, li):
+        inp, sh, D = st.inp, self.sh, self.cfg.head_dim
+        if self._rope_fused(st, li):
+            st.attn = ops.attn_decode_rope(st.qkv, inp.positions, inp.block_table, self.cos_sin, self.kv[li], inp.seq_lens,
+                                           sh["Hq"], sh["Hkv"], D, ctx_hint=inp.ctx_hint)
+        elif inp.is_prefill:
+            st.attn = ops.attn_prefill(st.qkv, self.kv[li], inp.block_table, inp.q_start, inp.q_len, inp.seq_lens,
+                                       inp.max_q_len, sh["Hq"], sh["Hkv"], D)
+        else:
+            st.attn = ops.attn_decode(st.qkv, self.kv[li], inp.block_table, inp.seq_lens, sh["Hq"], sh["Hkv"], D,
+                                      ctx_hint=inp.ctx_hint)
+
+    def _op_o_proj(self, st, li):
+        st.pending = self._row_parallel(st.attn, self.w.layers[li], "wo")
+        st.pending_kind, st.row_idx, st.row_w, st.owner, st.crossing = "attn", None, None, None, None
+
+    def _op_post_attention_layernorm(self, st, li):
+        cfg, lw = self.cfg, self.w.layers[li]
+        residual = st.residual
+        if (cfg.is_moe and not st.sp and residual.is_cuda and ops.can_fuse_route(residual.shape[0], cfg.top_k, residual.device)):
+            # decode-sized batches: the router and the expert-sorted scatter ride in the reduce kernel
+            self._check_crossing(st)
+            ep = self.layout.ep > 1
+            e_first = 0 if ep else self.layout.ep_rank * self.sh["E_local"]
+            e_cnt = cfg.num_experts if ep else self.sh["E_local"]
+            part, flags, epoch = st.pending
+            out = ops.reduce_norm_route(residual, part, lw.ffn_norm, cfg.rms_norm_eps, lw.router, cfg.top_k,
+                                        e_first, e_cnt, flags=flags, epoch=epoch)
+            st.residual, st.normed, st.routed = out[0], out[1], out[2:]
+            st.pending = None
+        else:
+            self._reduce(st, lw.ffn_norm)
+            st.routed = None
+
+    def _op_router(self, st, li):
+        if st.routed is not None:
+            return          # produced by the fused reduce + router kernel
+        cfg, lw = self.cfg, self.w.layers[li]
+        e_local = self.sh["E_local"]
+        if self.layout.ep > 1:
+            # every rank of the stage routes all tokens the same way (global expert-sorted layout)
+            ids, wts, counts, offsets, row_of, src_token = ops.route(st.normed, lw.router, cfg.top_k)
+        else:
+            ids, wts, counts, offsets, row_of, src_token = ops.route(st.normed, lw.router, cfg.top_k,
+                                                                     self.layout.ep_rank * e_local, e_local)
+        xs = ops.gather_rows(st.normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
+        st.routed = (ids, wts, counts, offsets, row_of, src_token, xs)
+
+    def _op_experts_gate_up(self, st, li):
+        cfg, lw = self.cfg, self.w.layers[li]
+        T = st.normed.shape[0]
+        e_local = self.sh["E_local"]
+        first = self.layout.ep_rank * e_local
+        ids, wts, counts, offsets, row_of, src_token, xs = st.routed
+        cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
+        st.h = (self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep),
+                cnt_l, off_l)
+
+    def _op_experts_down(self, st, li):
+        cfg, lw = self.cfg, self.w.layers[li]
+        T = st.normed.shape[0]
+        ids, wts, counts, offsets, row_of, src_token, xs = st.routed
+        h, cnt_l, off_l = st.h
+        if self.layout.ep > 1:
+            # Expert parallel: a rank computes only the rows of the experts it owns and its down projection publishes them;
+            # the combine then reads each (token, slot) pair from the ranks that own its expert. Row positions are global,
+            # so no index exchange is needed.
+            w8 = lw.fp8.get("w2")
+            if w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
+                st.pending = self.comm_moe.linear_push_fp8(h, None, w8, (cnt_l, off_l))
+            else:
+                w2 = lw.w2 if lw.w2 is not None else w8.dequant()
+                st.pending = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
+            st.owner = (ids, self.sh["E_local"], self.layout.tp)
+        else:
+            st.pending = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
+            st.owner = None
+        st.pending_kind, st.row_idx, st.row_w, st.crossing = "ffn", row_of.view(T, cfg.top_k), wts, None
+        st.h = st.routed = None
+
+    def _op_gate_up_proj(self, st, li):
+        st.h = self._col_linear(st.normed, self.w.layers[li], "w13", swiglu=True)
+
+    def _op_down_proj(self, st, li):
+        st.pending = self._row_parallel(st.h, self.w.layers[li], "w2")
+        st.pending_kind, st.row_idx, st.row_w, st.owner, st.crossing, st.h = "ffn", None, None, None, None, None
+
+    def _op_norm(self, st, _):
+        self._reduce(st, self.w.final_norm)
+
+    def _op_lm_head(self, st, _):     # logits() and sample() run these on the rows that need them
+        pass
+
+    _op_sample = _op_lm_head
+
+    def _collective(self, st, kind, tensor):
+        if tensor == "embed_out":
+            if st.embed_deferred:
+                st.residual, st.normed = self.comm.embed_reduce(st.inp.token_ids, self.w.embed, self.embed_vocab_start,
+                                                                self.w.layers[0].attn_norm, self.cfg.rms_norm_eps)
+                st.embed_deferred = False
+        elif kind in ("ring_allreduce", "alltoall"):
+            # the exchange itself is carried by the kernels on both sides of this point (publish epilogue of the producing
+            # GEMM, pull inside the consuming reduce): record that the lowering put one here
+            st.crossing = tensor
+        # send_recv between pipeline stages is issued by parallel/pp.py around this stage's program; the sampler's
+        # candidate exchange belongs to sample()
+
+    def _check_crossing(self, st):
+        if self._multi and st.pending is not None and hasattr(st.pending[0], "ptrs") and st.crossing is None:
+            raise RuntimeError("partial results of other ranks are about to be summed, but the lowering placed no collective here")
+
+    def _reduce(self, st, gamma):
+        """residual += sum over ranks of the pending partial (dense, or the weighted top-k combine of expert rows), then
+        RMSNorm with `gamma` (None: no normalised output). Sequence-parallel form: only this rank's row slice, followed
+        by the all-gather of the normalised slices (parallel/tp.py)."""
+        cfg = self.cfg
+        self._check_crossing(st)
+        part, flags, epoch = st.pending
+        kind = st.pending_kind
+        if st.sp:
+            st.residual, normed_loc = self.comm.reduce_scatter_norm(st.residual, part, gamma, cfg.rms_norm_eps, st.T,
+                                                                    st.row_idx, st.row_w)
+            st.normed = self.comm.gather_rows(normed_loc, st.T) if gamma is not None else None
+        else:
+            own = {} if st.owner is None else dict(owner_ids=st.owner[0], experts_per_owner=st.owner[1], owner_span=st.owner[2])
+            st.residual, st.normed = ops.reduce_residual_rmsnorm(st.residual, part, gamma, cfg.rms_norm_eps, st.row_idx, st.row_w,
+                                                                 flags=flags, epoch=epoch, **own)
+        st.pending = st.row_idx = st.row_w = st.owner = None
+        if kind == "ffn" and self.capture_hidden is not None:
+            full = self._gather_residual(st.residual, st.T) if st.sp else st.residual
+            self.capture_hidden.append(full.detach().float().cpu())
 
     def _col_linear(self, x, lw, name, swiglu=False, grouped=None, rows_hint=None):
         """Column-parallel (local) projection through the block's bf16 weight or, when the plan's dtype map
-        selected fp8 for this block, its block-scaled e4m3 copy (activations quantised on the fly)."""
+        selected fp8 for this block, its block-scaled e4m3 copy."""
         w8 = lw.fp8.get(name)
         if w8 is not None:
             # weights e4m3 with 1 x 128 block scales, activations bf16: the GEMM streams the e4m3 tiles and rescales them
@@ -238,122 +443,34 @@ class Decoder:
             return y.unsqueeze(0), None, None
         return self.comm.linear_push(x, w, grouped)
 
-    def _ffn(self, li: int, normed, routed=None):
-        """Returns (partial, flags, epoch, row_idx, row_w) feeding the fused combine/reduce. `routed` carries the
-        router's outputs and the expert-sorted activations when the preceding reduce kernel already made them."""
-        cfg, lw = self.cfg, self.w.layers[li]
-        if not cfg.is_moe:
-            h = self._col_linear(normed, lw, "w13", swiglu=True)
-            part, flags, epoch = self._row_parallel(h, lw, "w2")
-            return part, flags, epoch, None, None
-        T = normed.shape[0]
-        e_local = self.sh["E_local"]
-        first = self.layout.ep_rank * e_local
-        if self.layout.ep > 1:
-            # Expert parallel: every rank of the stage routes all tokens the same way (global expert-sorted
-            # layout), computes only the rows of the experts it owns, and its down projection stores those rows
-            # into every rank's receive slot; the combine then reads each (token, slot) pair from the ranks that
-            # own its expert. Row positions are global, so no index exchange is needed.
-            if routed is None:
-                ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k)
-                xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
-            else:
-                ids, wts, counts, offsets, row_of, src_token, xs = routed
-            cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
-            h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep)
-            w8 = lw.fp8.get("w2")
-            if w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
-                part, flags, epoch = self.comm_moe.linear_push_fp8(h, None, w8, (cnt_l, off_l))
-            else:
-                w2 = lw.w2 if lw.w2 is not None else w8.dequant()
-                part, flags, epoch = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
-            self._owner = (ids, e_local, self.layout.tp)
-            return part, flags, epoch, row_of.view(T, cfg.top_k), wts
-        if routed is None:
-            ids, wts, counts, offsets, row_of, src_token = ops.route(normed, lw.router, cfg.top_k, first, e_local)
-            xs = ops.gather_rows(normed, src_token, n_rows_dev=offsets[cfg.num_experts:])
-        else:
-            ids, wts, counts, offsets, row_of, src_token, xs = routed
-        cnt_l, off_l = counts[first:first + e_local], offsets[first:first + e_local]
-        h = self._col_linear(xs, lw, "w13", swiglu=True, grouped=(cnt_l, off_l), rows_hint=T * cfg.top_k)
-        part, flags, epoch = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
-        return part, flags, epoch, row_of.view(T, cfg.top_k), wts
-
     # ---- the step ---------------------------------------------------------------------------------
     def forward_hidden(self, inp: BatchInputs, hidden_in: torch.Tensor | None = None):
-        """Runs this stage's blocks. Returns (residual stream [T, H], normed [T, H]) where `normed` is the final
-        norm on the last stage and the next stage's first attn_norm input otherwise (None)."""
-        cfg = self.cfg
-        layers = self.w.layers
-        if hidden_in is None and self.embed_vocab_start is not None:
-            # table sharded by vocabulary rows: the ranks' lookups are summed inside the first RMSNorm
-            residual, normed = self.comm.embed_reduce(inp.token_ids, self.w.embed, self.embed_vocab_start,
-                                                      layers[0].attn_norm, cfg.rms_norm_eps)
-        else:
-            residual = ops.embed(inp.token_ids, self.w.embed) if hidden_in is None else hidden_in
-            normed = ops.rmsnorm(residual, layers[0].attn_norm, cfg.rms_norm_eps)
-        last_stage = self.w.final_norm is not None
-        T = residual.shape[0]
-        if (inp.is_prefill and self.comm is not None and self.comm.size > 1 and self.layout.ep == 1 and residual.is_cuda
-                and hasattr(self.comm, "sp_ok") and self.comm.sp_ok(T, T * max(1, cfg.top_k if cfg.is_moe else 1))):
-            return self._forward_hidden_sp(inp, residual, normed, last_stage)
-        for li, lw in enumerate(layers):
-            attn = self._attention(li, normed, inp)
-            part, flags, epoch = self._row_parallel(attn, lw, "wo")
-            routed = None
-            if cfg.is_moe and residual.is_cuda and ops.can_fuse_route(residual.shape[0], cfg.top_k, residual.device):
-                # decode-sized batches: the router and the expert-sorted scatter ride in the reduce kernel
-                ep = self.layout.ep > 1
-                e_first = 0 if ep else self.layout.ep_rank * self.sh["E_local"]
-                e_cnt = cfg.num_experts if ep else self.sh["E_local"]
-                out = ops.reduce_norm_route(residual, part, lw.ffn_norm, cfg.rms_norm_eps, lw.router, cfg.top_k,
-                                            e_first, e_cnt, flags=flags, epoch=epoch)
-                residual, normed, routed = out[0], out[1], out[2:]
-            else:
-                residual, normed = ops.reduce_residual_rmsnorm(residual, part, lw.ffn_norm, cfg.rms_norm_eps,
-                                                               flags=flags, epoch=epoch)
-            self._owner = None
-            part, flags, epoch, row_idx, row_w = self._ffn(li, normed, routed)
-            if li + 1 < len(layers):
-                next_gamma = layers[li + 1].attn_norm
-            else:
-                next_gamma = self.w.final_norm if last_stage else None
-            own = {} if self._owner is None else dict(owner_ids=self._owner[0], experts_per_owner=self._owner[1],
-                                                      owner_span=self._owner[2])
-            residual, normed = ops.reduce_residual_rmsnorm(residual, part, next_gamma, cfg.rms_norm_eps, row_idx,
-                                                           row_w, flags=flags, epoch=epoch, **own)
-            if self.capture_hidden is not None:
-                self.capture_hidden.append(residual.detach().float().cpu())
-        return residual, normed
+        """Runs this stage's part of the lowered program. Returns (residual stream [T, H], normed [T, H]) where `normed`
+        is the final norm on the last stage and None otherwise.
 
-    def _forward_hidden_sp(self, inp: BatchInputs, residual, normed, last_stage: bool):
-        """Prefill-sized chunks under tensor parallelism: sequence-parallel between the projections. The row-parallel
-        GEMMs (o_proj, down) publish their partials; every rank reduces, adds the residual and normalises only its
-        own slice of the token rows (reduce-scatter fused with residual + RMSNorm, peer loads or the in-switch
-        reduction), the residual stream stays sharded by rows from layer to layer, and the normalised slices are
-        gathered into local memory for the next column-parallel GEMM (parallel/tp.py). No library collective runs.
+        Under tensor parallelism the two row-parallel projections of a block (o_proj, down) publish their partial
+        results from the GEMM epilogue and the reduce that follows pulls the peers' partials, so a block launches no
+        stand-alone collective; prefill-sized chunks run sequence-parallel between the projections (reduce-scatter fused
+        with residual + RMSNorm on this rank's rows, all-gather of the normalised rows, no library collective).
         The reference keeps activations replicated and all-reduces twice per block through NCCL
         (crates/skein_emit/src/handoff.rs:104-211, crates/skein_runtime/src/cuda/nccl.rs:196-245)."""
-        cfg, comm, layers = self.cfg, self.comm, self.w.layers
-        T = residual.shape[0]
-        r0, n, _ = comm.sp_slice(T)
-        res_loc = residual[r0:r0 + n].contiguous()
-        for li, lw in enumerate(layers):
-            attn = self._attention(li, normed, inp)
-            part, _, _ = self._row_parallel(attn, lw, "wo")
-            res_loc, normed_loc = comm.reduce_scatter_norm(res_loc, part, lw.ffn_norm, cfg.rms_norm_eps, T)
-            normed = comm.gather_rows(normed_loc, T)
-            part, _, _, row_idx, row_w = self._ffn(li, normed, None)
-            if li + 1 < len(layers):
-                next_gamma = layers[li + 1].attn_norm
+        st = Decoder._Run(inp, hidden_in)
+        if hidden_in is not None:
+            st.T = hidden_in.shape[0]
+        for item in self.program:
+            if item[0] == "op":
+                self._ops[item[1]](st, item[2])
             else:
-                next_gamma = self.w.final_norm if last_stage else None
-            res_loc, normed_loc = comm.reduce_scatter_norm(res_loc, part, next_gamma, cfg.rms_norm_eps, T, row_idx, row_w)
-            normed = comm.gather_rows(normed_loc, T) if next_gamma is not None else None
-            if self.capture_hidden is not None:
-                self.capture_hidden.append(self._gather_residual(res_loc, T).float().cpu())
-        residual = self._gather_residual(res_loc, T) if not last_stage else None
-        return residual, normed
+                self._collective(st, item[1], item[2])
+        last_stage = self.w.final_norm is not None
+        if st.pending is not None:        # a stage that is not the last: its final partial goes into the residual stream
+            if st.crossing is None and self._multi and self.layout.tp > 1:
+                st.crossing = "carry"     # the hand-off to the next stage follows; the lowering cut the segment there
+            self._reduce(st, None)
+        residual = st.residual
+        if st.sp:
+            residual = self._gather_residual(residual, st.T) if not last_stage else None
+        return residual, (st.normed if last_stage else None)
 
     def _gather_residual(self, res_loc, T):
         """The full residual stream from its row slices (only where a whole copy is needed: the hand-off to the next
