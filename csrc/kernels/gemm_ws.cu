@@ -46,7 +46,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int W8_THREADS = 320;   // + 4 converter warps (e4m3 -> scaled bf16 in shared memory)
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_STAGES = 12;
-constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks (64 K elements: one 16 KB bf16 tile per weight tile)
+constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks (64 K elements: one 16 KB bf16 tile per weight tile), at most
 
 // Optional phase timer (compile with -DSKEIN_GEMM_TIMING): every CTA records %globaltimer at the points marked
 // TS(i) below into g_gemm_times[cta][i]; skein_gemm_times() copies the table out. Points: 0 entry, 1 set-up done,
@@ -66,14 +66,27 @@ struct KernelArgs {
   int stage_bytes;
   int x_tile_bytes;
   int conv_base;    // W8: byte offset of the converted-tile ring inside the dynamic shared memory
+  int conv_slots;   // W8: slots of that ring (2 or 3)
+  int scale_off;    // W8: byte offset, inside a stage, of the tile's block scales (128 floats per weight tile)
   uint64_t budget_ns;
 };
 
-// Two e4m3 values -> two floats (exact: e4m3 is a subset of f16).
-__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
-  uint32_t h;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"(v));
-  return __half22float2(*reinterpret_cast<__half2*>(&h));
+// Four e4m3 bytes of `w` -> four bf16 values times the block scale, without a conversion instruction (those issue
+// at a fraction of the arithmetic rate and capped this path at 0.4 of the memory bandwidth). An e4m3 byte
+// s eeee mmm, moved to s 0000eeee mmm0000, is a bf16 number whose value is the e4m3 value times 2^-120, subnormals
+// and zero included (both formats count their subnormals from the same exponent field value 0). One bf16x2
+// multiplication by (block scale * 2^120) therefore yields the scaled weight; it is exact when the scale is a
+// power of two, which is how this framework quantises weights (ops/fp8.py: quantize_weight).
+__device__ __forceinline__ void e4m3x4_to_scaled_bf16x4(uint32_t w, __nv_bfloat162 sc2, uint32_t& lo, uint32_t& hi) {
+  uint32_t t0, t1;
+  asm("prmt.b32 %0, %1, 0, 0x1404;" : "=r"(t0) : "r"(w));   // bytes 0,1 -> the high byte of each 16-bit half
+  asm("prmt.b32 %0, %1, 0, 0x3424;" : "=r"(t1) : "r"(w));   // bytes 2,3
+  const uint32_t r0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
+  const uint32_t r1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
+  const uint32_t s2 = *reinterpret_cast<const uint32_t*>(&sc2);
+  // spelled out so that no fast-math flag turns it into a form that flushes the subnormal inputs
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(r0), "r"(s2));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(r1), "r"(s2));
 }
 
 template <bool DUAL, bool W8>
@@ -114,7 +127,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       mbar_init(smem_u32(&bar_tempty[b]), EPI_THREADS);
     }
     if (W8) {
-      for (int c = 0; c < W8_CONV_SLOTS; ++c) {
+      for (int c = 0; c < a.conv_slots; ++c) {
         mbar_init(smem_u32(&bar_cfull[c]), 128);
         mbar_init(smem_u32(&bar_cempty[c]), 1);
       }
@@ -151,7 +164,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (elect_one()) {
         const uint64_t pol_w = l2_policy_evict_first();
         const uint64_t pol_x = l2_policy_evict_last();
-        const uint32_t tx_bytes = (DUAL ? 2 : 1) * W_TILE_BYTES + a.x_tile_bytes;
+        uint32_t tx_bytes = (DUAL ? 2 : 1) * W_TILE_BYTES + a.x_tile_bytes;
+        const uint32_t tx_base = tx_bytes;
+        const long long w_rows_total = (long long)p.G * p.w_rows_per_group;
         uint32_t it = 0;
         int pos = kb_begin;
         bool ok = true;
@@ -163,6 +178,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           const Unit un = decode_unit(sched, p.G, u);
           const int w_row = un.g * p.w_rows_per_group + un.m * TILE_F;
           const int x_row = sched.off[un.g] + un.n * n_tile;
+          // W8: the 128 block scales of each weight tile travel with the stage (512 bytes per tile), unless the tile
+          // sticks out of the matrix; the converters then read the few scales they need themselves
+          const bool scales_by_copy = W8 && (w_row + (DUAL ? p.up_row_off : 0) + TILE_F <= w_rows_total) &&
+                                      (un.m * TILE_F + TILE_F <= p.F) && (w_rows_total % 4 == 0) && (p.up_row_off % 4 == 0);
+          if (W8) tx_bytes = tx_base + (scales_by_copy ? (DUAL ? 2 : 1) * 512u : 0u);
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s = it % a.stages;
             const uint32_t ph = (it / a.stages) & 1;
@@ -185,7 +205,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
             tma_load_2d(st + W_STAGE_BYTES, &tmX, full, kb * k_elems, x_row, pol_x);
             // e4m3 weights: a stage covers 128 K elements, i.e. two 64-wide bf16 activation tiles
-            if (W8) tma_load_2d(st + W_STAGE_BYTES + a.x_tile_bytes / 2, &tmX, full, kb * k_elems + 64, x_row, pol_x);
+            if (W8) {
+              tma_load_2d(st + W_STAGE_BYTES + a.x_tile_bytes / 2, &tmX, full, kb * k_elems + 64, x_row, pol_x);
+              if (scales_by_copy) {
+                const float* sp = p.w_scale + (size_t)kb * w_rows_total + w_row;
+                bulk_load_1d(st + a.scale_off, sp, 512, full);
+                if (DUAL) bulk_load_1d(st + a.scale_off + 512, sp + p.up_row_off, 512, full);
+              }
+            }
           }
           pos = u * KB + kb1;
         }
@@ -220,7 +247,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               // the weights of this stage arrive as two converted halves (64 K elements each) from the converter warps
 #pragma unroll 1
               for (int h = 0; h < 2 && ok; ++h) {
-                const uint32_t hit = 2 * it + h, c = hit % W8_CONV_SLOTS, cph = (hit / W8_CONV_SLOTS) & 1;
+                const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
                 if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
                   report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
                   abort_flag = 1;
@@ -288,6 +315,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (u * KB + KB > kb_end) kb1 = kb_end - u * KB;
         const Unit un = decode_unit(sched, p.G, u);
         const long long w_row = (long long)un.g * p.w_rows_per_group + un.m * TILE_F + r;
+        const bool scales_by_copy = ((long long)un.g * p.w_rows_per_group + un.m * TILE_F + (DUAL ? p.up_row_off : 0) + TILE_F <= w_rows_total) &&
+                                    (un.m * TILE_F + TILE_F <= p.F) && (w_rows_total % 4 == 0) && (p.up_row_off % 4 == 0);
         for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const uint32_t s = it % a.stages, ph = (it / a.stages) & 1;
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, a.budget_ns)) {
@@ -297,17 +326,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             break;
           }
           const uint8_t* raw = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * a.stage_bytes;
-          float sc[DUAL ? 2 : 1];
+          __nv_bfloat162 sc[DUAL ? 2 : 1];
 #pragma unroll
           for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
             const long long row = w_row + (t ? p.up_row_off : 0);
-            // rows beyond the matrix were zero-filled by TMA: any finite scale will do
-            sc[t] = (row < w_rows_total && (un.m * TILE_F + r) < p.F)
-                        ? __ldg(p.w_scale + (size_t)kb * w_rows_total + row) : 0.f;
+            float f;
+            if (scales_by_copy) f = reinterpret_cast<const float*>(raw + a.scale_off)[t * 128 + r];   // arrived with the stage
+            else  // a tile that sticks out of the matrix: rows beyond it were zero-filled by TMA, any finite scale will do
+              f = (row < w_rows_total && (un.m * TILE_F + r) < p.F) ? __ldg(p.w_scale + (size_t)kb * w_rows_total + row) : 0.f;
+            sc[t] = __float2bfloat162_rn(f * 0x1p120f);
           }
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
-            const uint32_t hit = 2 * it + h, c = hit % W8_CONV_SLOTS, cph = (hit / W8_CONV_SLOTS) & 1;
+            const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
             if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
               report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
               abort_flag = 1;
@@ -323,16 +354,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               for (int cc = 0; cc < 4; ++cc) {           // the half's four 16-byte chunks of e4m3
                 const int chunk = h * 4 + cc;
                 const uint4 v = *reinterpret_cast<const uint4*>(src_row + ((chunk ^ (r & 7)) << 4));
-                const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
-                uint4 o[2];
-                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(o);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const float2 f = e4m3x2_to_float2(e[j]);
-                  ob[j] = __floats2bfloat162_rn(f.x * sc[t], f.y * sc[t]);
-                }
-                *reinterpret_cast<uint4*>(dst_row + (((2 * cc) ^ (r & 7)) << 4)) = o[0];
-                *reinterpret_cast<uint4*>(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)) = o[1];
+                uint4 o0, o1;
+                e4m3x4_to_scaled_bf16x4(v.x, sc[t], o0.x, o0.y);
+                e4m3x4_to_scaled_bf16x4(v.y, sc[t], o0.z, o0.w);
+                e4m3x4_to_scaled_bf16x4(v.z, sc[t], o1.x, o1.y);
+                e4m3x4_to_scaled_bf16x4(v.w, sc[t], o1.z, o1.w);
+                *reinterpret_cast<uint4*>(dst_row + (((2 * cc) ^ (r & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)) = o1;
               }
             }
             // make the generic-proxy stores visible to the tensor cores' (async proxy) reads, then signal
@@ -733,9 +761,17 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   }
   ka->x_tile_bytes = p->n_tile * BLOCK_KB * (w8 ? 2 : 1);    // e4m3 stage: 128 K elements = two bf16 activation tiles
   ka->stage_bytes = (dual ? 2 : 1) * W_TILE_BYTES + ka->x_tile_bytes;
+  ka->scale_off = ka->stage_bytes;
+  if (w8) ka->stage_bytes += 1024;                            // the weight tiles' block scales (keeps the 1 KB alignment)
   int budget = 200 * 1024;
   ka->conv_base = 0;
-  if (w8) budget -= W8_CONV_SLOTS * (dual ? 2 : 1) * W_TILE_BYTES;
+  ka->conv_slots = 0;
+  if (w8) {
+    // three slots of converted half K-blocks unless that leaves fewer than two stages for the loads
+    ka->conv_slots = W8_CONV_SLOTS;
+    if ((budget - ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES) / ka->stage_bytes < 2) ka->conv_slots = 2;
+    budget -= ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES;
+  }
   int st = budget / ka->stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
   if (p->stages > 0 && p->stages < st) st = p->stages;
@@ -745,7 +781,7 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : gemm_wait_budget_ms()) * 1000000ull;
   *grid = p->grid > 0 ? p->grid : sm_count_cached();
   if (*grid > sm_count_cached()) *grid = sm_count_cached();   // the split-K reduction needs every CTA resident
-  *smem = (size_t)st * ka->stage_bytes + (w8 ? W8_CONV_SLOTS * (dual ? 2 : 1) * W_TILE_BYTES : 0) + 1024;
+  *smem = (size_t)st * ka->stage_bytes + (size_t)ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES + 1024;
   return 0;
 }
 

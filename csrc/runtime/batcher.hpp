@@ -160,12 +160,13 @@ class ContinuousBatcher {
 
   // `failed`: the request is dropped after a step that did not complete; its pages leave the prefix cache.
   // The host inputs of a decode step, written straight into the step's staging arrays (pinned memory that one
-  // host-to-device copy then moves): row i feeds request ids[i] its last token at its position; rows from ids.size()
-  // to `rows` are padding (position -1, length 0). Block-table rows are `max_blocks` wide.
+  // host-to-device copy then moves): row i feeds request ids[i] its last token at its position; id 0 and the rows
+  // from ids.size() to `rows` are padding (position -1, length 0). Block-table rows are `max_blocks` wide.
   void fill_decode_inputs(const std::vector<uint64_t>& ids, int32_t* tok, int32_t* pos, int32_t* lens, int32_t* block_table,
                           size_t max_blocks, size_t rows) const {
     if (ids.size() > rows) throw RuntimeError("decode batch is larger than its staging buffer");
     for (size_t i = 0; i < ids.size(); ++i) {
+      if (ids[i] == 0) { tok[i] = 0; pos[i] = -1; lens[i] = 0; continue; }   // a padding row inside the batch
       const InflightRequest* r = get(ids[i]);
       if (!r || r->generated.empty()) throw RuntimeError("request " + std::to_string(ids[i]) + " is not decoding");
       const int32_t p = (int32_t)(r->req.prompt.size() + r->generated.size()) - 1;
@@ -185,6 +186,7 @@ class ContinuousBatcher {
     std::vector<AcceptOutcome> out;
     out.reserve(ids.size());
     for (size_t i = 0; i < ids.size(); ++i) {
+      if (ids[i] == 0) { out.push_back(AcceptOutcome{}); continue; }
       auto o = accept_token(ids[i], tokens[i], now_ms, eos_token);
       out.push_back(o ? *o : AcceptOutcome{});
     }

@@ -137,7 +137,7 @@ def build_artifact(plan_json: str, config_json: str, out_root: str | Path, sourc
             t = source.get(e["name"], full_shape)
             t = _slice(t, e)
             if e["dtype"] in FP8_DTYPES and t.dim() == 2 and t.shape[1] % 128 == 0:
-                q, s = ref.quant_fp8_block128(t)
+                q, s = ref.quant_fp8_block128(t, pow2_scales=True)     # weights: exact in-kernel rescaling (ops/fp8.py)
                 tensors[e["name"]] = q.view(torch.uint8)
                 tensors[e["name"] + ".scale"] = s
             else:

@@ -174,6 +174,11 @@ class Decoder:
             if weights.embed.shape[0] > self.sh["V_local"]:      # the last rank's shard may be short
                 raise ValueError("the embedding table is neither whole nor this rank's vocabulary shard")
             self.embed_vocab_start = self.layout.tp_rank * self.sh["V_local"]
+        # Expert parallelism with data-parallel attention (decode): every expert-parallel rank runs attention, norms and
+        # the router for its own slice of the step's rows and the MoE blocks exchange tokens (dispatch) and expert outputs
+        # (combine) over peer memory. The caller must keep a sequence on the same slice for its whole life, because only
+        # that rank's cache receives the sequence's new tokens (runtime/engine.py does; a benchmark's rows are static).
+        self.dp_attention = False
         self.program = self._load_program()
         self._ops = {name[4:]: getattr(self, name) for name in dir(self) if name.startswith("_op_")}
         missing = sorted({it[1] for it in self.program if it[0] == "op"} - set(self._ops))
@@ -224,14 +229,29 @@ class Decoder:
     class _Run:
         """State of one pass over the program."""
         __slots__ = ("inp", "residual", "normed", "qkv", "attn", "pending", "pending_kind", "routed", "h", "sp", "T",
-                     "crossing", "embed_deferred", "row_idx", "row_w", "owner")
+                     "crossing", "embed_deferred", "row_idx", "row_w", "owner", "dp", "wts")
 
         def __init__(self, inp, residual):
             self.inp, self.residual = inp, residual
             self.normed = self.qkv = self.attn = self.pending = self.routed = self.h = None
             self.pending_kind, self.crossing, self.sp, self.T = None, None, False, 0
             self.embed_deferred = False
-            self.row_idx = self.row_w = self.owner = None
+            self.row_idx = self.row_w = self.owner = self.wts = None
+            self.dp = 0          # rows per rank under data-parallel attention (0: every rank holds all rows)
+
+    def _dp_rows(self, inp: BatchInputs) -> int:
+        """Rows per rank when this step runs with data-parallel attention, else 0."""
+        lay = self.layout
+        if not (self.dp_attention and lay.ep > 1 and lay.tp == 1 and lay.pp == 1 and self.cfg.is_moe):
+            return 0
+        B = inp.token_ids.shape[0]
+        if inp.is_prefill or inp.seq_of_token is not None or not inp.token_ids.is_cuda or B % lay.ep:
+            return 0
+        per = B // lay.ep
+        # the sampled tokens of a slice are gathered 16 bytes at a time; the fused reduce + router needs one CTA per row
+        if per % 4 or not ops.can_fuse_route(per, self.cfg.top_k, inp.token_ids.device) or B * self.cfg.top_k > 2048:
+            return 0
+        return per
 
     @property
     def _multi(self) -> bool:
@@ -298,6 +318,25 @@ class Decoder:
     def _op_post_attention_layernorm(self, st, li):
         cfg, lw = self.cfg, self.w.layers[li]
         residual = st.residual
+        if st.dp:
+            # this rank's rows only: residual + RMSNorm + router in one launch, with the normalised rows and the expert
+            # choices written straight into the published buffer; one pull kernel then gathers the rows of this rank's
+            # experts from all ranks (parallel/tp.py: ep_dispatch, csrc/kernels/ep_dispatch.cu)
+            part, flags, epoch = st.pending
+            e_local = self.sh["E_local"]
+            box = {}
+
+            def fill(normed_view, ids_view):
+                out = ops.reduce_norm_route(residual, part, lw.ffn_norm, cfg.rms_norm_eps, lw.router, cfg.top_k, 0, cfg.num_experts,
+                                            flags=flags, epoch=epoch, normed_out=normed_view, ids_out=ids_view, scatter=False)
+                box["res"], box["wts"] = out[0], out[3]
+            ids_all, counts, offsets, row_of, src_token, xs = self.comm_moe.ep_dispatch(
+                st.dp, cfg.top_k, cfg.num_experts, self.layout.ep_rank * e_local, e_local, fill)
+            st.residual, st.wts = box["res"], box["wts"]
+            st.normed = None        # lives in the published buffer; the experts read xs
+            st.routed = (ids_all, None, counts, offsets, row_of, src_token, xs)
+            st.pending = None
+            return
         if (cfg.is_moe and not st.sp and residual.is_cuda and ops.can_fuse_route(residual.shape[0], cfg.top_k, residual.device)):
             # decode-sized batches: the router and the expert-sorted scatter ride in the reduce kernel
             self._check_crossing(st)
@@ -329,7 +368,7 @@ class Decoder:
 
     def _op_experts_gate_up(self, st, li):
         cfg, lw = self.cfg, self.w.layers[li]
-        T = st.normed.shape[0]
+        T = st.dp * self.layout.ep if st.dp else st.normed.shape[0]
         e_local = self.sh["E_local"]
         first = self.layout.ep_rank * e_local
         ids, wts, counts, offsets, row_of, src_token, xs = st.routed
@@ -339,7 +378,7 @@ class Decoder:
 
     def _op_experts_down(self, st, li):
         cfg, lw = self.cfg, self.w.layers[li]
-        T = st.normed.shape[0]
+        T = st.dp * self.layout.ep if st.dp else st.normed.shape[0]
         ids, wts, counts, offsets, row_of, src_token, xs = st.routed
         h, cnt_l, off_l = st.h
         if self.layout.ep > 1:
@@ -357,6 +396,11 @@ class Decoder:
             st.pending = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
             st.owner = None
         st.pending_kind, st.row_idx, st.row_w, st.crossing = "ffn", row_of.view(T, cfg.top_k), wts, None
+        if st.dp:
+            # the combine of this rank's own rows: their pairs' global row positions, weights and expert ids
+            lo, hi = self.layout.ep_rank * st.dp, (self.layout.ep_rank + 1) * st.dp
+            st.row_idx, st.row_w = st.row_idx[lo:hi].contiguous(), st.wts
+            st.owner = (ids[lo:hi].contiguous(), self.sh["E_local"], self.layout.tp)
         st.h = st.routed = None
 
     def _op_gate_up_proj(self, st, li):
@@ -457,6 +501,12 @@ class Decoder:
         st = Decoder._Run(inp, hidden_in)
         if hidden_in is not None:
             st.T = hidden_in.shape[0]
+        st.dp = self._dp_rows(inp)
+        if st.dp:
+            r, per = self.layout.ep_rank, st.dp
+            st.inp = BatchInputs(token_ids=inp.token_ids[r * per:(r + 1) * per], positions=inp.positions[r * per:(r + 1) * per],
+                                 block_table=inp.block_table[r * per:(r + 1) * per], seq_lens=inp.seq_lens[r * per:(r + 1) * per],
+                                 ctx_hint=inp.ctx_hint)
         for item in self.program:
             if item[0] == "op":
                 self._ops[item[1]](st, item[2])
@@ -490,6 +540,19 @@ class Decoder:
         """Full step on a single stage: returns (next tokens int32 [rows], logits shard). Greedy unless `sampling`
         is given."""
         _, normed = self.forward_hidden(inp, hidden_in)
+        per = self._dp_rows(inp) if hidden_in is None else 0
+        if per:
+            # data-parallel attention: this rank holds the final hidden state of its own rows; every rank samples its
+            # slice and the tokens are gathered through the small published buffer
+            r = self.layout.ep_rank
+            lg = ops.linear(normed, self.w.lm_head)
+            smp = None
+            if sampling is not None:
+                smp = SamplingInputs(sampling.temperature[r * per:(r + 1) * per], sampling.top_k[r * per:(r + 1) * per],
+                                     sampling.top_p[r * per:(r + 1) * per], sampling.seeds[r * per:(r + 1) * per],
+                                     sampling.step[r * per:(r + 1) * per])
+            tok = ops.sample_argmax(lg) if smp is None else ops.sample(lg, smp.temperature, smp.top_k, smp.top_p, smp.seeds, smp.step)
+            return self.comm_moe.all_gather_aux(tok), lg
         lg = self.logits(normed, inp)
         return self.sample(lg, sampling), lg
 

@@ -92,6 +92,7 @@ def lib():
     _sig(L, "skein_quant_fp8_block128", i32, [vp, vp, vp, i64, i32, vp])
     _sig(L, "skein_advance_decode_state", i32, [vp, vp, vp, vp, i32, vp, vp])
     pvp = C.POINTER(C.c_void_p)
+    _sig(L, "skein_ep_dispatch_pull", i32, [pvp, pvp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp])
     _sig(L, "skein_ipc_alloc", i32, [pvp, i64])
     _sig(L, "skein_ipc_free", i32, [vp])
     _sig(L, "skein_ipc_get_handle", i32, [vp, C.c_char_p])

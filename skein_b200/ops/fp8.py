@@ -52,11 +52,17 @@ class Fp8Weight:
         return self
 
 
-def quantize_weight(w: torch.Tensor) -> Fp8Weight:
+def quantize_weight(w: torch.Tensor, pow2_scales: bool = True) -> Fp8Weight:
+    """e4m3 with one fp32 scale per 1 x 128 block along K. With `pow2_scales` (the default for weights) every scale is
+    the smallest power of two that brings the block's largest magnitude inside the e4m3 range: e4m3 is a floating-point
+    format, so this costs no relative precision, and the GEMM's in-kernel rescaling of the tile to bf16 is then exact."""
     shape = tuple(w.shape)
     K = shape[-1]
     w2 = w.reshape(-1, K).contiguous()
-    q, s = F.quant_fp8_block128(w2) if w2.is_cuda else ref.quant_fp8_block128(w2)
+    if not pow2_scales:
+        q, s = F.quant_fp8_block128(w2) if w2.is_cuda else ref.quant_fp8_block128(w2)
+    else:
+        q, s = ref.quant_fp8_block128(w2, pow2_scales=True)      # plain tensor ops: runs on the weight's device
     return Fp8Weight(q.view(*shape), s.t().contiguous(), shape)
 
 

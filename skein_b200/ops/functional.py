@@ -334,12 +334,14 @@ def can_fuse_route(T, topk, device=None) -> bool:
 
 
 def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_count=None, flags=None, epoch=None,
-                      wait_budget_ms=0):
+                      wait_budget_ms=0, normed_out=None, ids_out=None, scatter=True):
     """Residual add + (all-reduce consumer) + RMSNorm + MoE router + scatter into expert-sorted order, one launch.
 
     Equals reduce_residual_rmsnorm followed by route and gather_rows (csrc/kernels/norm.cu). Returns
     (residual_out, normed_out, expert_ids [T,k], weights [T,k], counts [E], offsets [E+1], row_of [T*k],
-    src_token [T*k], xs [T*k, H]).
+    src_token [T*k], xs [T*k, H]). `normed_out` / `ids_out` let the caller have the normalised rows and the expert
+    choices written somewhere else (a published buffer: expert-parallel dispatch); scatter=False skips the
+    expert-sorted copy (xs is then None).
     """
     peer = hasattr(partial, "ptrs")
     src = residual if residual is not None else (partial.local if peer else partial)
@@ -354,13 +356,14 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
     T = residual.shape[0] if residual is not None else (partial.rows if peer else partial.shape[1])
     dev = src.device
     residual_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    normed_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    if normed_out is None:
+        normed_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    ids = ids_out if ids_out is not None else torch.empty(T, topk, dtype=torch.int32, device=dev)
     w = torch.empty(T, topk, dtype=torch.float32, device=dev)
     meta = torch.empty(2 * E + 1 + 2 * T * topk, dtype=torch.int32, device=dev)
     counts, offsets = meta[:E], meta[E:2 * E + 1]
     row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * topk], meta[2 * E + 1 + T * topk:]
-    xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev)
+    xs = torch.empty(T * topk, H, dtype=torch.bfloat16, device=dev) if scatter else None
     pptr, src_stride, n_src, ptrs, mc, flags, epoch = _partial_args(partial, flags, epoch)
     if peer and wait_budget_ms == 0:
         wait_budget_ms = partial.wait_budget_ms
@@ -369,7 +372,7 @@ def reduce_norm_route(residual, partial, gamma, eps, wg, topk, e_first=0, e_coun
         _lib.ptr(residual), pptr, gamma.data_ptr(), residual_out.data_ptr(), normed_out.data_ptr(),
         _lib.ptr(flags), _lib.ptr(epoch), ws.status.data_ptr(), src_stride, T, H, n_src, float(eps), wait_budget_ms,
         wg.data_ptr(), E, topk, e_first, e_count, ids.data_ptr(), w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
-        row_of.data_ptr(), src_token.data_ptr(), xs.data_ptr(), ws.route_barrier.data_ptr(), ws.sm_count,
+        row_of.data_ptr(), src_token.data_ptr(), _lib.ptr(xs), ws.route_barrier.data_ptr(), ws.sm_count,
         ptrs, mc, _lib.stream_ptr())
     _lib.check(rc, "reduce_norm_route")
     _lib.count_launch()

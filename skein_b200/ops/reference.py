@@ -263,12 +263,15 @@ def embed(ids, table, vocab_start=0):
     return out * ok.unsqueeze(1).to(out.dtype)
 
 
-def quant_fp8_block128(x):
-    """Returns (q float8_e4m3fn [rows, K], scales fp32 [rows, K/128])."""
+def quant_fp8_block128(x, pow2_scales: bool = False):
+    """Returns (q float8_e4m3fn [rows, K], scales fp32 [rows, K/128]). pow2_scales: every scale is the smallest power
+    of two that brings the block's largest magnitude inside the e4m3 range (used for weights)."""
     rows, K = x.shape
     xb = x.float().view(rows, K // 128, 128)
     amax = xb.abs().amax(dim=-1)
     scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    if pow2_scales:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = (xb / scale.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(rows, K)
     return q, scale
 

@@ -229,6 +229,64 @@ class TPComm:
                             self.wait_budget_ms, mc=self.heap.mc_addr(self.embed_off))
         return ops.reduce_residual_rmsnorm(None, part, gamma, eps)
 
+    # ---- expert-parallel token dispatch (data-parallel attention) ---------------------------------------------------
+    def ep_dispatch(self, per: int, k: int, E: int, e_first: int, e_count: int, fill):
+        """Token dispatch of an expert-parallel MoE block whose ranks each own `per` of the step's tokens.
+
+        `fill(normed_out [per, H] bf16, ids_out [per, k] int32)` must launch the kernels that write this rank's
+        normalised rows and expert choices into the given views of its published buffer. The flags are then raised and
+        one pull kernel (csrc/kernels/ep_dispatch.cu) derives the global expert-sorted layout from all ranks' choices and
+        gathers, over NVLink, the rows routed to this rank's experts. Returns (ids_all [T, k], counts [E], offsets [E + 1],
+        row_of [T * k], src_token [T * k], xs [T * k, H]) with T = ranks x per, the tuple the grouped expert GEMMs and the
+        owner-aware combine take."""
+        H, N = self.hidden, self.size
+        rows_bytes = per * H * 2
+        if rows_bytes + per * k * 4 > self.fused_rows * H * 2 or N * per * k > 2048 or N * per * k > self.fused_rows:
+            raise ValueError("dispatch does not fit the published buffers")
+        b = self.cur
+        self.cur ^= 1
+        normed_view = self.bufs[b][:per]
+        ids_view = self.heap.view(self.buf_off[b] + rows_bytes, (per, k), torch.int32)
+        fill(normed_view, ids_view)
+        L = _lib.lib()
+        _lib.check(L.skein_publish_rows(None, 0, None, self._push_flag[b], N, self.epochs[b:b + 1].data_ptr(),
+                                        self.done[b:b + 1].data_ptr(), _lib.stream_ptr()), "publish dispatch rows")
+        T = N * per
+        dev = self.device
+        ids_all = torch.empty(T, k, dtype=torch.int32, device=dev)
+        meta = torch.empty(2 * E + 1 + 2 * T * k, dtype=torch.int32, device=dev)
+        counts, offsets = meta[:E], meta[E:2 * E + 1]
+        row_of, src_token = meta[2 * E + 1:2 * E + 1 + T * k], meta[2 * E + 1 + T * k:]
+        xs = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+        VP = C.c_void_p * N
+        ids_ptrs = VP(*[self.heap.peer_ptr(p, self.buf_off[b] + rows_bytes) for p in range(N)])
+        _lib.check(L.skein_ep_dispatch_pull(self._src_ptrs[b], ids_ptrs, N, per, k, E, e_first, e_count, H,
+                                            self.flags[b].data_ptr(), self.epochs[b:b + 1].data_ptr(),
+                                            ops.workspace().status.data_ptr(), self.wait_budget_ms, ids_all.data_ptr(),
+                                            counts.data_ptr(), offsets.data_ptr(), row_of.data_ptr(), src_token.data_ptr(),
+                                            xs.data_ptr(), _lib.stream_ptr()), "ep_dispatch_pull")
+        _lib.count_launch(2)
+        return ids_all, counts, offsets, row_of, src_token, xs
+
+    def all_gather_aux(self, x: torch.Tensor) -> torch.Tensor:
+        """All-gather of a small tensor (the step's sampled tokens) through the third published buffer, which does not
+        take part in the alternation of the two per-block buffers."""
+        x = x.contiguous()
+        nbytes = x.numel() * x.element_size()
+        out = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if self.mode == "nccl" or nbytes % 16 != 0 or nbytes > self.embed_rows * self.hidden * 2:
+            dist.all_gather_into_tensor(out, x, group=self.group)
+            return out
+        L = _lib.lib()
+        _lib.check(L.skein_publish_rows(x.data_ptr(), nbytes, self.embed_buf.data_ptr(), self._embed_push_flag, self.size,
+                                        self.epochs[3:4].data_ptr(), self.done[3:4].data_ptr(), _lib.stream_ptr()), "publish_rows")
+        _lib.check(L.skein_pull_collective(self._PULL_ALL_GATHER, self._embed_src_ptrs, self.size, self.rank, nbytes, out.data_ptr(),
+                                           self.embed_flags.data_ptr(), self.epochs[3:4].data_ptr(),
+                                           ops.workspace().status.data_ptr(), self.wait_budget_ms, _lib.stream_ptr()),
+                   "pull_collective")
+        _lib.count_launch(2)
+        return out
+
     # ---- sequence-parallel dataflow for prefill-sized chunks ------------------------------------------------
     # Between a row-parallel projection and the next column-parallel one the activations are sharded by token rows:
     #   GEMM publishes its partial [T, H]  ->  rank r reduces rows [r*per, (r+1)*per) over all ranks (peer loads or one

@@ -98,6 +98,13 @@ class Engine:
         self._step = 0
         self._graph_seen = (0, 0)   # runner.graph_captures / graph_replays already added to the metrics
         self._sampling = {}      # request id -> SamplingParams (only requests that sample)
+        # Expert parallelism with data-parallel attention: each decoding sequence belongs to one rank's slice of the
+        # step's rows for its whole life (only that rank's cache receives its new tokens). Every rank's engine takes
+        # the same decisions, so the assignment needs no communication.
+        inner = getattr(decoder, "dec", decoder)
+        self._dp = inner.layout.ep if getattr(inner, "dp_attention", False) else 1
+        self._dp_of: dict[int, int] = {}
+        self._dp_load = [0] * self._dp
         self._wait_ns_seen = 0
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
         self.last_step_failed = False
@@ -178,6 +185,7 @@ class Engine:
         events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
         for ev in events:
             self._sampling.pop(ev.request_id, None)
+            self._dp_release(ev.request_id)
             self.metrics.record_request(ev.request_id, "failed", 0.0, 0.0, 0, 0)
         return events
 
@@ -195,7 +203,7 @@ class Engine:
         """Per-row sampling parameters of a step, or None when every request in it is greedy."""
         if not self._sampling or not any(r in self._sampling for r in rids):
             return None
-        return [self._sampling.get(r, GREEDY).row() for r in rids]
+        return [self._sampling.get(r, GREEDY).row() for r in rids]      # id 0 (a padding row) is greedy like any other
 
     def _run(self, prefill, decode, now) -> list[TokenEvent]:
         events: list[TokenEvent] = []
@@ -214,6 +222,8 @@ class Engine:
                 if last:
                     events.append(self._accept(rid, tok, stamp()))
         if decode:
+            if self._dp > 1:
+                decode = self._dp_layout(decode)
             bk = self.runner.bucket(len(decode))
             rows = self._rows(decode)
             self.runner.stage_decode_inputs(bk, self.batcher, decode, sampling=rows)
@@ -221,10 +231,38 @@ class Engine:
             fin, counts = self.batcher.accept_tokens(decode, out.data_ptr(), stamp(), self.cfg.eos_token)
             toks = out[:len(decode)].tolist()
             for rid, tok, f, n in zip(decode, toks, fin, counts):
+                if rid == 0:
+                    continue            # a padding row of a data-parallel slice
                 if f:
                     self._finish(rid, n)
                 events.append(TokenEvent(rid, tok, bool(f)))
         return events
+
+    def _dp_layout(self, decode):
+        """Rows of a decode step under data-parallel attention: one equally sized slice per rank, a sequence always in
+        the slice of the rank it was assigned to when it started decoding (the least loaded one), padding rows (id 0)
+        at the end of every slice."""
+        from .runner import BUCKETS, bucket_for
+        groups = [[] for _ in range(self._dp)]
+        for rid in decode:
+            r = self._dp_of.get(rid)
+            if r is None:
+                r = min(range(self._dp), key=lambda i: (self._dp_load[i], i))
+                self._dp_of[rid] = r
+                self._dp_load[r] += 1
+            groups[r].append(rid)
+        per = max(4, bucket_for(max(len(g) for g in groups)))
+        if per * self._dp > BUCKETS[-1]:
+            raise RuntimeError(f"{per} rows per rank x {self._dp} ranks exceed the largest capture class {BUCKETS[-1]}")
+        rows = []
+        for g in groups:
+            rows.extend(g + [0] * (per - len(g)))
+        return rows
+
+    def _dp_release(self, rid) -> None:
+        r = self._dp_of.pop(rid, None)
+        if r is not None:
+            self._dp_load[r] -= 1
 
     def _accept(self, rid, tok, now) -> TokenEvent:
         finished, n = self.batcher.accept_token(rid, int(tok), now, self.cfg.eos_token)
@@ -239,6 +277,7 @@ class Engine:
         self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
         self.batcher.retire(rid)
         self._sampling.pop(rid, None)
+        self._dp_release(rid)
 
     # ---- helpers ------------------------------------------------------------------------------------------------
     @property

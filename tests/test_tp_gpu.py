@@ -69,6 +69,23 @@ def test_ep2_fp8_experts():
     _run(2, {"SKEIN_TEST_TP": "1", "SKEIN_TEST_FP8": "1"}, port=29547, worker="ep_worker.py", ok="EP_WORKER_OK")
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep2_token_dispatch_with_data_parallel_attention():
+    """Token-routed expert parallelism: dispatch / combine round trip with identity experts, and a tiny Mixtral served
+    EP=2 through the engine with every rank attending only over its own slice of the sequences."""
+    _run(2, port=29555, worker="ep_dp_worker.py", ok="EP_DP_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_ep4_token_dispatch_with_data_parallel_attention():
+    _run(4, port=29556, worker="ep_dp_worker.py", ok="EP_DP_WORKER_OK")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_ep8_token_dispatch_with_data_parallel_attention():
+    _run(8, port=29557, worker="ep_dp_worker.py", ok="EP_DP_WORKER_OK")
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp2_ep2_fused():
     _run(4, {"SKEIN_TEST_TP": "2"}, port=29545, worker="ep_worker.py", ok="EP_WORKER_OK")
