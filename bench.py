@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--fp8-blocks", default="", help="'a:b' = blocks a..b-1 (of the whole model) in block-scaled fp8, all four projections")
     ap.add_argument("--fp8-experts", action="store_true", help="block-scaled e4m3 expert / FFN weights (marks dtype)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--replicated-attention", action="store_true",
+                    help="expert parallelism: every rank runs attention for all sequences (the comparison arm) instead of "
+                         "each rank attending over its own slice with token dispatch between the ranks")
     ap.add_argument("--repeats", type=int, default=5, help="how often each timed K-step loop is repeated (median reported)")
     ap.add_argument("--no-selfcheck", action="store_true")
     ap.add_argument("--no-unfused", action="store_true", help="skip the un-fused comparison arm at N > 1")
@@ -464,7 +467,8 @@ def main():
             c2 = TPComm(dist.group.WORLD, dev, hidden=1024, fused_rows=256, max_batch=64) if ep > 1 else None
             try:
                 info = teacher_forced_check(world, rank, dev, comm=c1, comm_moe=c2, tp=tp, ep=ep, hidden=1024,
-                                            fp8_experts=args.fp8_experts)
+                                            fp8_experts=args.fp8_experts,
+                                            dp_attention=ep > 1 and tp == 1 and not args.replicated_attention)
                 selfcheck = dict(info, result="ok")
             except AssertionError as e:
                 if rank == 0:
@@ -489,6 +493,8 @@ def main():
         from skein_b200.models.decoder import quantize_blocks
         quantize_blocks(weights, range(len(weights.layers)), names=("w13", "w2"))
     dec = Decoder(cfg, weights, lay, num_pages=num_pages, page_size=ps, max_pos=P + Gn + 64, comm=comm, comm_moe=comm_moe)
+    if ep > 1 and tp == 1 and not args.replicated_attention:
+        dec.dp_attention = True      # rows are static in this benchmark: a sequence stays on its rank
     fused = all(c is None or c.mode != "nccl" for c in (comm, comm_moe))
     use_graphs = fused and not args.eager   # the NCCL baseline mode launches eagerly
     runner = ModelRunner(dec, max_blocks_per_seq=blocks_per_seq, use_graphs=use_graphs, ctx_hint=P + Gn // 2)
@@ -684,6 +690,8 @@ def main():
                        "kv": "paged, block 16", "l2": "inputs (weights) larger than L2, no flush",
                        "cuda_graph": use_graphs, "comm": ((comm or comm_moe).mode if (comm or comm_moe) else "none"),
                        "in_switch_reduction": bool((comm or comm_moe).heap.mc_ptr) if (comm or comm_moe) else False,
+                       "attention": ("data-parallel (each expert-parallel rank attends over its own sequences, token dispatch "
+                                     "over peer memory)" if dec.dp_attention else "replicated across expert-parallel ranks") if ep > 1 else "tensor-parallel",
                        "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16",
                        "repeats": R, "ms_per_k_steps_all_repeats": [round(x, 3) for x in all_ms]},
             "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world),

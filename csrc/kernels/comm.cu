@@ -231,7 +231,7 @@ extern "C" int skein_pull_collective(int mode, const void* const* src_ptrs, int 
                                      void* stream) {
   using namespace skein;
   if (n_src < 1 || n_src > MAXP || rank < 0 || rank >= n_src || chunk_bytes % 16 != 0 || mode < 0 || mode > 2) return -1;
-  if (chunk_bytes == 0) return 0;
+  // chunk_bytes == 0: nothing to move, but the launch still waits for every rank's flag (an empty exchange)
   PullParams p;
   for (int s = 0; s < MAXP; ++s) p.src[s] = s < n_src ? (const uint4*)src_ptrs[s] : nullptr;
   p.out = (uint4*)out;
@@ -244,6 +244,7 @@ extern "C" int skein_pull_collective(int mode, const void* const* src_ptrs, int 
   p.rank = rank;
   p.mode = mode;
   long long grid = (p.chunk_vec + 255) / 256;
+  if (grid < 1) grid = 1;
   if (grid > 592) grid = 592;   // 4 CTAs per SM: enough loads in flight to cover the NVLink round trip
   pull_collective_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(p);
   return (int)cudaGetLastError();

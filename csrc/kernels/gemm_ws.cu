@@ -325,13 +325,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             ok = false;
             break;
           }
-          const uint8_t* raw = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * a.stage_bytes;
+          // shared-memory addresses (32-bit, shared state space): loads and stores below are ld.shared / st.shared, not
+          // generic accesses, which the hardware tracks like global ones (they showed up as the kernel's dominant stall)
+          const uint32_t raw = smem_base + s * a.stage_bytes;
           __nv_bfloat162 sc[DUAL ? 2 : 1];
 #pragma unroll
           for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
             const long long row = w_row + (t ? p.up_row_off : 0);
             float f;
-            if (scales_by_copy) f = reinterpret_cast<const float*>(raw + a.scale_off)[t * 128 + r];   // arrived with the stage
+            if (scales_by_copy)     // arrived with the stage
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(raw + a.scale_off + (t * 128 + r) * 4));
             else  // a tile that sticks out of the matrix: rows beyond it were zero-filled by TMA, any finite scale will do
               f = (row < w_rows_total && (un.m * TILE_F + r) < p.F) ? __ldg(p.w_scale + (size_t)kb * w_rows_total + row) : 0.f;
             sc[t] = __float2bfloat162_rn(f * 0x1p120f);
@@ -345,22 +348,28 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               ok = false;
               break;
             }
-            uint8_t* conv = smem_raw + (smem_base - smem_u32(smem_raw)) + a.conv_base + (size_t)c * W_STAGE_BYTES;
+            const uint32_t conv = smem_base + a.conv_base + c * W_STAGE_BYTES;
 #pragma unroll
             for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
-              const uint8_t* src_row = raw + t * W_TILE_BYTES + r * 128;
-              uint8_t* dst_row = conv + t * W_TILE_BYTES + r * 128;
+              const uint32_t src_row = raw + t * W_TILE_BYTES + r * 128;
+              const uint32_t dst_row = conv + t * W_TILE_BYTES + r * 128;
+              uint4 v[4];
 #pragma unroll
-              for (int cc = 0; cc < 4; ++cc) {           // the half's four 16-byte chunks of e4m3
-                const int chunk = h * 4 + cc;
-                const uint4 v = *reinterpret_cast<const uint4*>(src_row + ((chunk ^ (r & 7)) << 4));
+              for (int cc = 0; cc < 4; ++cc)             // the half's four 16-byte chunks of e4m3, all loads first
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v[cc].x), "=r"(v[cc].y), "=r"(v[cc].z), "=r"(v[cc].w)
+                             : "r"(src_row + (((h * 4 + cc) ^ (r & 7)) << 4)));
+#pragma unroll
+              for (int cc = 0; cc < 4; ++cc) {
                 uint4 o0, o1;
-                e4m3x4_to_scaled_bf16x4(v.x, sc[t], o0.x, o0.y);
-                e4m3x4_to_scaled_bf16x4(v.y, sc[t], o0.z, o0.w);
-                e4m3x4_to_scaled_bf16x4(v.z, sc[t], o1.x, o1.y);
-                e4m3x4_to_scaled_bf16x4(v.w, sc[t], o1.z, o1.w);
-                *reinterpret_cast<uint4*>(dst_row + (((2 * cc) ^ (r & 7)) << 4)) = o0;
-                *reinterpret_cast<uint4*>(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)) = o1;
+                e4m3x4_to_scaled_bf16x4(v[cc].x, sc[t], o0.x, o0.y);
+                e4m3x4_to_scaled_bf16x4(v[cc].y, sc[t], o0.z, o0.w);
+                e4m3x4_to_scaled_bf16x4(v[cc].z, sc[t], o1.x, o1.y);
+                e4m3x4_to_scaled_bf16x4(v[cc].w, sc[t], o1.z, o1.w);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((2 * cc) ^ (r & 7)) << 4)),
+                             "r"(o0.x), "r"(o0.y), "r"(o0.z), "r"(o0.w) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)),
+                             "r"(o1.x), "r"(o1.y), "r"(o1.z), "r"(o1.w) : "memory");
               }
             }
             // make the generic-proxy stores visible to the tensor cores' (async proxy) reads, then signal

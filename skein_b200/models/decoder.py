@@ -391,7 +391,9 @@ class Decoder:
             else:
                 w2 = lw.w2 if lw.w2 is not None else w8.dequant()
                 st.pending = self.comm_moe.linear_push(h, w2, (cnt_l, off_l))
-            st.owner = (ids, self.sh["E_local"], self.layout.tp)
+            # the owner-aware pull only applies to published partials; a chunk too large for the published buffers came back
+            # from the library all-reduce as one complete tensor
+            st.owner = (ids, self.sh["E_local"], self.layout.tp) if hasattr(st.pending[0], "ptrs") else None
         else:
             st.pending = self._row_parallel(h, lw, "w2", (cnt_l, off_l))
             st.owner = None
@@ -400,7 +402,7 @@ class Decoder:
             # the combine of this rank's own rows: their pairs' global row positions, weights and expert ids
             lo, hi = self.layout.ep_rank * st.dp, (self.layout.ep_rank + 1) * st.dp
             st.row_idx, st.row_w = st.row_idx[lo:hi].contiguous(), st.wts
-            st.owner = (ids[lo:hi].contiguous(), self.sh["E_local"], self.layout.tp)
+            st.owner = (ids[lo:hi].contiguous(), self.sh["E_local"], self.layout.tp) if st.owner is not None else None
         st.h = st.routed = None
 
     def _op_gate_up_proj(self, st, li):
@@ -539,6 +541,13 @@ class Decoder:
     def forward(self, inp: BatchInputs, hidden_in=None, sampling: SamplingInputs | None = None):
         """Full step on a single stage: returns (next tokens int32 [rows], logits shard). Greedy unless `sampling`
         is given."""
+        out = self._forward(inp, hidden_in, sampling)
+        for c in (self.comm, self.comm_moe):
+            if c is not None and hasattr(c, "even_out"):
+                c.even_out()
+        return out
+
+    def _forward(self, inp: BatchInputs, hidden_in=None, sampling: SamplingInputs | None = None):
         _, normed = self.forward_hidden(inp, hidden_in)
         per = self._dp_rows(inp) if hidden_in is None else 0
         if per:

@@ -108,6 +108,25 @@ class TPComm:
         self._embed_push_flag = VP(*[h.peer_ptr(p, self.embed_flag_off + 4 * r) for p in range(N)])
         ops.workspace(device).peer_state.append((self.epochs, self.done))
 
+    def even_out(self):
+        """Called at the end of a step. The two published buffers alternate, and using the same buffer for two
+        CONSECUTIVE exchanges is the one thing the protocol does not allow (a fast rank would overwrite what a slow peer
+        still reads; any exchange in between proves that everybody has finished reading). A step with an odd number of
+        exchanges would end on the buffer the next step (or the next replay of its captured graph) starts with, so it
+        gets one empty exchange on the other buffer: flags only, no data."""
+        if self.cur == 0 or self.mode == "nccl" or self.size == 1:
+            return
+        b = self.cur
+        self.cur ^= 1
+        L = _lib.lib()
+        _lib.check(L.skein_publish_rows(None, 0, None, self._push_flag[b], self.size, self.epochs[b:b + 1].data_ptr(),
+                                        self.done[b:b + 1].data_ptr(), _lib.stream_ptr()), "publish (empty exchange)")
+        _lib.check(L.skein_pull_collective(self._PULL_ALL_GATHER, self._src_ptrs[b], self.size, self.rank, 0, self.bufs[b].data_ptr(),
+                                           self.flags[b].data_ptr(), self.epochs[b:b + 1].data_ptr(),
+                                           ops.workspace().status.data_ptr(), self.wait_budget_ms, _lib.stream_ptr()),
+                   "wait (empty exchange)")
+        _lib.count_launch(2)
+
     def reset(self):
         """Back to the state of a fresh communicator: flag words, epochs, arrival counters zero, buffer 0 next. Every
         rank of the group must call this between the same two steps, with none of its kernels in flight and a

@@ -18,7 +18,8 @@ def _run(world, env_extra=None, port=29541, worker="tp_worker.py", ok="TP_WORKER
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "workers", worker)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
-    assert r.returncode == 0 and ok in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    first_tb = r.stderr.find("Traceback")       # the worker's own traceback comes before the launcher's summary
+    assert r.returncode == 0 and ok in r.stdout, r.stdout[-2000:] + r.stderr[max(0, first_tb):][:4000] + r.stderr[-1500:]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

@@ -38,7 +38,7 @@ def main():
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     H, E, k, per = 512, 2 * world, 2, 8
-    comm = TPComm(dist.group.WORLD, dev, hidden=H, fused_rows=256, max_batch=64)
+    comm = TPComm(dist.group.WORLD, dev, hidden=H, fused_rows=1024, max_batch=64)
     g = torch.Generator().manual_seed(3)
     T = world * per
     x_all = torch.randn(T, H, generator=g).bfloat16()
@@ -94,7 +94,7 @@ def main():
         # a router near-tie may flip a token under bf16 rounding, after which that sequence diverges: first tokens of
         # every sequence and most sequences in full must agree
         same = sum(a == b for a, b in zip(got, want))
-        assert all(a[0] == b[0] for a, b in zip(got, want)) and same >= len(prompts) - 2, (got, want)
+        assert all(a[0] == b[0] for a, b in zip(got, want)) and same >= len(prompts) - 2, ("got", got, "want", want)
     dist.barrier()
     if rank == 0:
         print("EP_DP_WORKER_OK world", world)
