@@ -17,10 +17,13 @@
 //     release of this rank's flag on every tensor-parallel peer (the all-reduce is finished by the
 //     consumer, which pulls the partials over NVLink: see norm.cu, reduce_residual_rmsnorm).
 //   * block-scaled fp8 weights with bf16 activations (the plan's weight fp8_e4m3 / activation bf16 combination):
-//     the weight tile travels as e4m3 (half the bytes of the decode step's dominant traffic), four more warps
-//     turn each landed tile into bf16 in shared memory, multiplying every row by its 1 x 128 block scale on the
-//     way, and the tensor cores run the same bf16 MMAs into ONE accumulator for the whole K range. Nothing is
-//     drained per K block and the activations are not quantised at all.
+//     the weight tile travels as e4m3 (half the bytes of the decode step's dominant traffic), eight more warps
+//     turn each landed tile into bf16, multiplying every row by its 1 x 128 block scale on the way, and write it
+//     into TENSOR MEMORY, from where the tensor cores take it as the A operand of the same bf16 MMAs (the token
+//     tile stays in shared memory), accumulating into ONE accumulator for the whole K range. Nothing is drained
+//     per K block, the activations are not quantised, and shared memory carries only the e4m3 bytes: with a bf16
+//     copy of the tile in shared memory the kernel was bound by shared-memory bandwidth (tile written by TMA, read
+//     and written again by the conversion, read by the MMA), not by HBM.
 //
 // Replaces the reference's cuBLASLt matmul host op (vendor/luminal/crates/luminal_cuda_lite/src/
 // host/cublaslt/mod.rs:888-1130), its fp8 GEMV (same file :797-886) and the GLUMoE GEMV kernels
@@ -31,6 +34,7 @@
 #include "launch.cuh"
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -43,10 +47,12 @@ constexpr int BLOCK_KB = 128;     // bytes of K per stage row (64 bf16 or 128 e4
 constexpr int W_TILE_BYTES = TILE_F * BLOCK_KB;  // 16 KB
 constexpr int ACC_STRIDE_MAX = 256;   // TMEM columns per accumulator buffer, at most
 constexpr int NUM_THREADS = 192;
-constexpr int W8_THREADS = 320;   // + 4 converter warps (e4m3 -> scaled bf16 in shared memory)
+constexpr int W8_CONV_THREADS = 256;
+constexpr int W8_THREADS = NUM_THREADS + W8_CONV_THREADS;   // + 8 converter warps (e4m3 -> scaled bf16 in shared memory)
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_STAGES = 12;
-constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks (64 K elements: one 16 KB bf16 tile per weight tile), at most
+constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks in tensor memory (64 K elements = 32 columns per weight tile)
+constexpr int W8_SLOT_COLS = 32;  // 32-bit columns of one converted weight tile half: 64 bf16 K elements, two per column
 
 // Optional phase timer (compile with -DSKEIN_GEMM_TIMING): every CTA records %globaltimer at the points marked
 // TS(i) below into g_gemm_times[cta][i]; skein_gemm_times() copies the table out. Points: 0 entry, 1 set-up done,
@@ -55,8 +61,16 @@ constexpr int W8_CONV_SLOTS = 3;  // ring of converted half K-blocks (64 K eleme
 #ifdef SKEIN_GEMM_TIMING
 __device__ unsigned long long g_gemm_times[160][8];
 #define TS(i) do { g_gemm_times[blockIdx.x][i] = global_timer_ns(); } while (0)
+// Cycle accounting of the e4m3-weight pipeline, per CTA: [0] converter waits for a landed stage, [1] converter waits
+// for a free converted slot, [2] converter converts, [3] MMA thread waits for a converted half, [4] MMA thread issues,
+// [5] producer waits for a free stage, [6] half K-blocks processed.
+__device__ unsigned long long g_w8_prof[160][8];
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(i) do { g_w8_prof[blockIdx.x][i] += (unsigned long long)(clock64() - prof_t0_); } while (0)
 #else
 #define TS(i) do { } while (0)
+#define PROF_T0() do { } while (0)
+#define PROF_ADD(i) do { } while (0)
 #endif
 
 struct KernelArgs {
@@ -65,28 +79,28 @@ struct KernelArgs {
   int stages;
   int stage_bytes;
   int x_tile_bytes;
-  int conv_base;    // W8: byte offset of the converted-tile ring inside the dynamic shared memory
-  int conv_slots;   // W8: slots of that ring (2 or 3)
+  int conv_base;    // W8: first tensor-memory column of the converted-tile ring (behind the two accumulators)
+  int conv_slots;   // W8: slots of that ring
   int scale_off;    // W8: byte offset, inside a stage, of the tile's block scales (128 floats per weight tile)
   uint64_t budget_ns;
 };
 
-// Four e4m3 bytes of `w` -> four bf16 values times the block scale, without a conversion instruction (those issue
-// at a fraction of the arithmetic rate and capped this path at 0.4 of the memory bandwidth). An e4m3 byte
+// Four e4m3 bytes of `w` -> four bf16 values times the block scale, without a conversion instruction. An e4m3 byte
 // s eeee mmm, moved to s 0000eeee mmm0000, is a bf16 number whose value is the e4m3 value times 2^-120, subnormals
 // and zero included (both formats count their subnormals from the same exponent field value 0). One bf16x2
 // multiplication by (block scale * 2^120) therefore yields the scaled weight; it is exact when the scale is a
 // power of two, which is how this framework quantises weights (ops/fp8.py: quantize_weight).
-__device__ __forceinline__ void e4m3x4_to_scaled_bf16x4(uint32_t w, __nv_bfloat162 sc2, uint32_t& lo, uint32_t& hi) {
+// (The hardware conversion e4m3x2 -> f16x2 would be cheaper, but the MMA then needs f16 for BOTH operands: an f16 A
+// operand with bf16 activations is not a legal operand pair of kind::f16.)
+__device__ __forceinline__ void e4m3x4_to_scaled_bf16x4(uint32_t w, uint32_t sc2, uint32_t& lo, uint32_t& hi) {
   uint32_t t0, t1;
   asm("prmt.b32 %0, %1, 0, 0x1404;" : "=r"(t0) : "r"(w));   // bytes 0,1 -> the high byte of each 16-bit half
   asm("prmt.b32 %0, %1, 0, 0x3424;" : "=r"(t1) : "r"(w));   // bytes 2,3
   const uint32_t r0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
   const uint32_t r1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
-  const uint32_t s2 = *reinterpret_cast<const uint32_t*>(&sc2);
   // spelled out so that no fast-math flag turns it into a form that flushes the subnormal inputs
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(r0), "r"(s2));
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(r1), "r"(s2));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(r0), "r"(sc2));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(r1), "r"(sc2));
 }
 
 template <bool DUAL, bool W8>
@@ -128,14 +142,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
     if (W8) {
       for (int c = 0; c < a.conv_slots; ++c) {
-        mbar_init(smem_u32(&bar_cfull[c]), 128);
+        mbar_init(smem_u32(&bar_cfull[c]), W8_CONV_THREADS);
         mbar_init(smem_u32(&bar_cempty[c]), 1);
       }
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_smem), 2 * a.acc_stride);
+    tmem_alloc(smem_u32(&tmem_base_smem), W8 ? 512 : 2 * a.acc_stride);
     tmem_relinquish();
   }
   if (warp == 0 && elect_one()) {
@@ -186,11 +200,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s = it % a.stages;
             const uint32_t ph = (it / a.stages) & 1;
-            if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, a.budget_ns)) {
-              report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
-              abort_flag = 1;
-              ok = false;
-              break;
+            {
+              PROF_T0();
+              if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, a.budget_ns)) {
+                report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              if (W8) PROF_ADD(5);
             }
             const uint32_t full = smem_u32(&bar_full[s]);
             const uint32_t st = smem_base + s * a.stage_bytes;
@@ -248,24 +266,29 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll 1
               for (int h = 0; h < 2 && ok; ++h) {
                 const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
-                if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
-                  report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
-                  abort_flag = 1;
-                  ok = false;
-                  break;
+                {
+                  PROF_T0();
+                  if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
+                    report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
+                    abort_flag = 1;
+                    ok = false;
+                    break;
+                  }
+                  PROF_ADD(3);
                 }
+                PROF_T0();
                 tc_fence_after();
                 if (hit == 0) TS(2);
-                const uint32_t cw = smem_base + a.conv_base + c * W_STAGE_BYTES;
-                const uint64_t dw = umma_desc_sw128(cw);
+                const uint32_t aw = tmem_base + a.conv_base + c * (DUAL ? 2 : 1) * W8_SLOT_COLS;   // converted weights, in TMEM
                 const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < 4; ++k) {      // 16 K elements = 8 columns of the A operand per MMA
                   const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
-                  mma_f16(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
-                  if (DUAL) mma_f16(d_tmem + n_tile, umma_desc_sw128(cw + W_TILE_BYTES) + 2 * k, dx + 2 * k, idesc, accum);
+                  mma_f16_ts(d_tmem, aw + 8 * k, dx + 2 * k, idesc, accum);
+                  if (DUAL) mma_f16_ts(d_tmem + n_tile, aw + W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
                 }
                 tc_commit(smem_u32(&bar_cempty[c]));
+                PROF_ADD(4);
               }
               if (!ok) break;
               tc_commit(smem_u32(&bar_empty[s]));  // the activation tiles of the stage have been read as well
@@ -299,11 +322,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
       }
     } else if (W8 && warp >= 6) {
-      // ================= converters (warps 6..9): e4m3 tile -> bf16 tile scaled by the row's 1 x 128 block scale =========
-      // Thread r owns weight row r of the tile. The raw tile was written by TMA with the 128-byte swizzle (16-byte chunk
-      // c of row r sits at chunk c ^ (r & 7)); the bf16 tiles the tensor cores read use the same pattern, so a 16-byte
-      // chunk of e4m3 (16 K elements) becomes two 16-byte chunks of the 64-K-wide half it belongs to.
-      const int r = threadIdx.x - 192;
+      // ================= converters (warps 6..13): e4m3 tile -> bf16 rows, scaled by the row's 1 x 128 block scale, in TMEM ==
+      // Two threads share weight row r of the tile, each taking two of the four 16-byte chunks of a 64-K half (eight
+      // warps: two per scheduler, so that one warp's dependent instructions are covered by the other's). The raw tile
+      // was written by TMA with the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)). A warp can
+      // reach the tensor-memory lanes 32 * (warp % 4) .. + 31 only, and lane = row of the A operand, so a warp converts
+      // the rows of its own lane quarter; 16 K elements become 8 columns.
+      const int r = (warp & 3) * 32 + lane;
+      const int part = (warp - 6) >> 2;                      // which two chunks of every half this thread converts
       const long long w_rows_total = (long long)p.G * p.w_rows_per_group;
       uint32_t it = 0;
       int pos = kb_begin;
@@ -319,16 +345,20 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                     (un.m * TILE_F + TILE_F <= p.F) && (w_rows_total % 4 == 0) && (p.up_row_off % 4 == 0);
         for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const uint32_t s = it % a.stages, ph = (it / a.stages) & 1;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, a.budget_ns)) {
-            report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
-            abort_flag = 1;
-            ok = false;
-            break;
+          {
+            PROF_T0();
+            if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, a.budget_ns)) {
+              report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            if (r == 0 && part == 0) PROF_ADD(0);
           }
           // shared-memory addresses (32-bit, shared state space): loads and stores below are ld.shared / st.shared, not
           // generic accesses, which the hardware tracks like global ones (they showed up as the kernel's dominant stall)
           const uint32_t raw = smem_base + s * a.stage_bytes;
-          __nv_bfloat162 sc[DUAL ? 2 : 1];
+          uint32_t sc[DUAL ? 2 : 1];     // the row's block scale times 2^120 as a packed bf16 pair
 #pragma unroll
           for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
             const long long row = w_row + (t ? p.up_row_off : 0);
@@ -337,44 +367,52 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(raw + a.scale_off + (t * 128 + r) * 4));
             else  // a tile that sticks out of the matrix: rows beyond it were zero-filled by TMA, any finite scale will do
               f = (row < w_rows_total && (un.m * TILE_F + r) < p.F) ? __ldg(p.w_scale + (size_t)kb * w_rows_total + row) : 0.f;
-            sc[t] = __float2bfloat162_rn(f * 0x1p120f);
+            const __nv_bfloat162 hs = __float2bfloat162_rn(f * 0x1p120f);
+            sc[t] = *reinterpret_cast<const uint32_t*>(&hs);
           }
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
             const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
-            if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
-              report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
-              abort_flag = 1;
-              ok = false;
-              break;
+            {
+              PROF_T0();
+              if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
+                report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              if (r == 0 && part == 0) PROF_ADD(1);
             }
-            const uint32_t conv = smem_base + a.conv_base + c * W_STAGE_BYTES;
+            PROF_T0();
+            tc_fence_after();
+            // this thread's 16 columns of its lane: slot c, tile t, columns part * 16 .. + 15
+            const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * (DUAL ? 2 : 1) * W8_SLOT_COLS + part * 16;
 #pragma unroll
             for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
               const uint32_t src_row = raw + t * W_TILE_BYTES + r * 128;
-              const uint32_t dst_row = conv + t * W_TILE_BYTES + r * 128;
-              uint4 v[4];
+              uint32_t o[16];
+              uint4 v[2];
 #pragma unroll
-              for (int cc = 0; cc < 4; ++cc)             // the half's four 16-byte chunks of e4m3, all loads first
+              for (int ci = 0; ci < 2; ++ci)             // this thread's two 16-byte chunks of e4m3, both loads first
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(v[cc].x), "=r"(v[cc].y), "=r"(v[cc].z), "=r"(v[cc].w)
-                             : "r"(src_row + (((h * 4 + cc) ^ (r & 7)) << 4)));
+                             : "=r"(v[ci].x), "=r"(v[ci].y), "=r"(v[ci].z), "=r"(v[ci].w)
+                             : "r"(src_row + (((h * 4 + part * 2 + ci) ^ (r & 7)) << 4)));
 #pragma unroll
-              for (int cc = 0; cc < 4; ++cc) {
-                uint4 o0, o1;
-                e4m3x4_to_scaled_bf16x4(v[cc].x, sc[t], o0.x, o0.y);
-                e4m3x4_to_scaled_bf16x4(v[cc].y, sc[t], o0.z, o0.w);
-                e4m3x4_to_scaled_bf16x4(v[cc].z, sc[t], o1.x, o1.y);
-                e4m3x4_to_scaled_bf16x4(v[cc].w, sc[t], o1.z, o1.w);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((2 * cc) ^ (r & 7)) << 4)),
-                             "r"(o0.x), "r"(o0.y), "r"(o0.z), "r"(o0.w) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((2 * cc + 1) ^ (r & 7)) << 4)),
-                             "r"(o1.x), "r"(o1.y), "r"(o1.z), "r"(o1.w) : "memory");
+              for (int ci = 0; ci < 2; ++ci) {
+                e4m3x4_to_scaled_bf16x4(v[ci].x, sc[t], o[8 * ci + 0], o[8 * ci + 1]);
+                e4m3x4_to_scaled_bf16x4(v[ci].y, sc[t], o[8 * ci + 2], o[8 * ci + 3]);
+                e4m3x4_to_scaled_bf16x4(v[ci].z, sc[t], o[8 * ci + 4], o[8 * ci + 5]);
+                e4m3x4_to_scaled_bf16x4(v[ci].w, sc[t], o[8 * ci + 6], o[8 * ci + 7]);
               }
+              tmem_st16(conv + t * W8_SLOT_COLS, o);
             }
-            // make the generic-proxy stores visible to the tensor cores' (async proxy) reads, then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // the stores to tensor memory must have completed before the MMA warp is told
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(smem_u32(&bar_cfull[c]));
+#ifdef SKEIN_GEMM_TIMING
+            if (r == 0 && part == 0) { PROF_ADD(2); g_w8_prof[blockIdx.x][6] += 1; }
+#endif
           }
         }
         pos = u * KB + kb1;
@@ -663,7 +701,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * a.acc_stride);
+    tmem_dealloc(tmem_base, W8 ? 512 : 2 * a.acc_stride);
   }
 }
 
@@ -772,25 +810,24 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   ka->stage_bytes = (dual ? 2 : 1) * W_TILE_BYTES + ka->x_tile_bytes;
   ka->scale_off = ka->stage_bytes;
   if (w8) ka->stage_bytes += 1024;                            // the weight tiles' block scales (keeps the 1 KB alignment)
-  int budget = 200 * 1024;
+  const int budget = 200 * 1024;
   ka->conv_base = 0;
   ka->conv_slots = 0;
   if (w8) {
-    // three slots of converted half K-blocks unless that leaves fewer than two stages for the loads
+    // the converted weights live in tensor memory behind the two accumulators: 512 columns in all
     ka->conv_slots = W8_CONV_SLOTS;
-    if ((budget - ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES) / ka->stage_bytes < 2) ka->conv_slots = 2;
-    budget -= ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES;
+    ka->conv_base = 2 * ka->acc_stride;
+    if (ka->conv_base + ka->conv_slots * (dual ? 2 : 1) * W8_SLOT_COLS > 512) return -3;   // token tile too wide for this form
   }
   int st = budget / ka->stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
   if (p->stages > 0 && p->stages < st) st = p->stages;
   if (st < 2) return -7;
   ka->stages = st;
-  ka->conv_base = st * ka->stage_bytes;      // the converted-tile ring follows the stages (both are multiples of 1 KB)
   ka->budget_ns = (uint64_t)(p->wait_budget_ms > 0 ? p->wait_budget_ms : gemm_wait_budget_ms()) * 1000000ull;
   *grid = p->grid > 0 ? p->grid : sm_count_cached();
   if (*grid > sm_count_cached()) *grid = sm_count_cached();   // the split-K reduction needs every CTA resident
-  *smem = (size_t)st * ka->stage_bytes + (size_t)ka->conv_slots * (dual ? 2 : 1) * W_TILE_BYTES + 1024;
+  *smem = (size_t)st * ka->stage_bytes + 1024;
   return 0;
 }
 
@@ -802,6 +839,13 @@ extern "C" int skein_sm_count(void) { return skein::sm_count_cached(); }
 // out: [160][8] nanosecond stamps of the last launch (synchronises the device).
 extern "C" int skein_gemm_times(unsigned long long* out) {
   return (int)cudaMemcpyFromSymbol(out, skein::g_gemm_times, sizeof(unsigned long long) * 160 * 8);
+}
+// out: [160][8] cycle totals of the e4m3-weight pipeline since the last call, which also clears them.
+extern "C" int skein_w8_profile(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, skein::g_w8_prof, sizeof(unsigned long long) * 160 * 8);
+  if (e != cudaSuccess) return (int)e;
+  static unsigned long long zeros[160 * 8];
+  return (int)cudaMemcpyToSymbol(skein::g_w8_prof, zeros, sizeof(zeros));
 }
 #endif
 

@@ -180,6 +180,12 @@ def linear_publish(xq, xs, w: Fp8Weight, out_local, peer_flag, epoch, done_count
 
 
 # ---- fp8 weights, bf16 activations -----------------------------------------------------------------------------------
+def _a16_n_tile(rows_hint: int, dual: bool) -> int:
+    """Token-tile width of the e4m3-weight form: the converted weight tiles share the 512 tensor-memory columns with the
+    two accumulators, which leaves room for 64 tokens per tile with the SwiGLU pair epilogue and 128 without."""
+    return min(F.pick_n_tile(rows_hint, dual), 64 if dual else 128)
+
+
 def _a16_params(x, w: Fp8Weight, out, F_out, n_tile, mode):
     w2d = w.q.view(-1, w.shape[-1])
     p = F._base_params(x, w2d, out, F_out, x.shape[1], n_tile, mode)
@@ -201,7 +207,7 @@ def linear_a16(x, w: Fp8Weight, swiglu: bool = False, out=None, n_tile=None, _cf
         out = torch.empty(T, Fo, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
-    p = _a16_params(x, w, out, Fo, n_tile or F.pick_n_tile(T, swiglu), 1 if swiglu else 0)
+    p = _a16_params(x, w, out, Fo, n_tile or _a16_n_tile(T, swiglu), 1 if swiglu else 0)
     p.w_rows_per_group, p.up_row_off = rows, (Fo if swiglu else 0)
     F._gemm_launch(p, "fp8-weight linear", _cfg)
     return out
@@ -221,7 +227,7 @@ def grouped_linear_a16(xs, w: Fp8Weight, counts, offsets, swiglu: bool = False, 
         return out
     if n_tile is None:
         avg = (rows_hint if rows_hint is not None else R) / E
-        n_tile = F.pick_n_tile(int(math.ceil(avg * 1.5)), swiglu)
+        n_tile = _a16_n_tile(int(math.ceil(avg * 1.5)), swiglu)
     p = _a16_params(xs, w, out, Fo, n_tile, 1 if swiglu else 0)
     p.G, p.w_rows_per_group, p.up_row_off = E, rows, (Fo if swiglu else 0)
     p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
@@ -236,14 +242,14 @@ def linear_publish_a16(x, w: Fp8Weight, out_local, peer_flag, epoch, done_counte
     R = x.shape[0]
     if grouped is None:
         rows = w.shape[-2]
-        p = _a16_params(x, w, out_local, rows, n_tile or F.pick_n_tile(R, False), 2)
+        p = _a16_params(x, w, out_local, rows, n_tile or _a16_n_tile(R, False), 2)
         p.w_rows_per_group = rows
     else:
         counts, offsets = grouped
         E, rows = w.shape[0], w.shape[1]
         if n_tile is None:
             avg = (rows_hint if rows_hint is not None else R) / E
-            n_tile = F.pick_n_tile(int(math.ceil(avg * 1.5)), False)
+            n_tile = _a16_n_tile(int(math.ceil(avg * 1.5)), False)
         p = _a16_params(x, w, out_local, rows, n_tile, 2)
         p.G, p.w_rows_per_group = E, rows
         p.group_off, p.group_cnt = offsets.data_ptr(), counts.data_ptr()
