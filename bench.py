@@ -482,7 +482,8 @@ def main():
             # room for the partials of one 8192-token prefill chunk (its expert-sorted rows for a MoE model)
             comm = TPComm(tp_group, dev, hidden=cfg.hidden_size, fused_rows=max(512, 8192 * max(1, cfg.top_k if cfg.is_moe else 1)))
         if ep > 1:   # communicator over all tp x ep ranks for the expert-parallel combine
-            comm_moe = TPComm(dist.group.WORLD, dev, hidden=cfg.hidden_size)
+            comm_moe = TPComm(dist.group.WORLD, dev, hidden=cfg.hidden_size, fused_rows=max(512, 8192 * cfg.top_k),
+                              max_batch=max(256, args.batch))
     lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
     B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1

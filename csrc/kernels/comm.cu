@@ -21,6 +21,7 @@
 // shm_allreduce.rs:24-69), the logits all-gather (nccl.rs:251-298), the grouped send/recv exchanges
 // (nccl.rs:422-445) and the host-staged KV block transport (nccl.rs:504-588).
 #include "ptx.cuh"
+#include "argmax.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
 #include <string.h>
@@ -58,11 +59,6 @@ __global__ void __launch_bounds__(256) publish_rows_kernel(const uint4* __restri
   publish_when_all_done(pp, epoch, done_counter);
 }
 
-struct ValIdx { float v; int i; };
-__device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
-  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
-  return a;
-}
 
 // grid = B rows, 1024 threads. val_dst[p] / idx_dst[p] point at this rank's [B] slot on peer p.
 struct CandPtrs {
@@ -75,27 +71,9 @@ __global__ void __launch_bounds__(1024) argmax_push_kernel(const __nv_bfloat16* 
   __shared__ ValIdx sh[32];
   const int b = blockIdx.x;
   const __nv_bfloat16* row = logits + (size_t)b * ld;
-  ValIdx best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = __bfloat162float(row[i]);
-    if (v > best.v) { best.v = v; best.i = i; }
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    ValIdx y{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
-    best = better(best, y);
-  }
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  if (l == 0) sh[w] = best;
-  __syncthreads();
-  if (w == 0) {
-    ValIdx r = sh[l];
-    for (int o = 16; o > 0; o >>= 1) {
-      ValIdx y{__shfl_xor_sync(0xffffffffu, r.v, o), __shfl_xor_sync(0xffffffffu, r.i, o)};
-      r = better(r, y);
-    }
-    if (l == 0) {
-      for (int p = 0; p < pp.n; ++p) { cp.val[p][b] = r.v; cp.idx[p][b] = r.i + idx_offset; }
-    }
+  const ValIdx r = block_argmax(thread_argmax_row(row, V), sh);
+  if (threadIdx.x == 0) {
+    for (int p = 0; p < pp.n; ++p) { cp.val[p][b] = r.v; cp.idx[p][b] = r.i + idx_offset; }
   }
   publish_when_all_done(pp, epoch, done_counter);
 }

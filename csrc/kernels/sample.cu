@@ -13,38 +13,11 @@
 // smem tree) and the all-gather of logit shards before it (crates/skein_runtime/src/cuda/
 // nccl.rs:251-298).
 #include "ptx.cuh"
+#include "argmax.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
 
 namespace skein {
-
-struct ValIdx { float v; int i; };
-
-__device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
-  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
-  return a;
-}
-
-__device__ __forceinline__ ValIdx block_argmax(ValIdx x, ValIdx* sh) {
-  for (int o = 16; o > 0; o >>= 1) {
-    ValIdx y;
-    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
-    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
-    x = better(x, y);
-  }
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
-  if (l == 0) sh[w] = x;
-  __syncthreads();
-  ValIdx r = (l < nw) ? sh[l] : ValIdx{-INFINITY, 0x7fffffff};
-  for (int o = 16; o > 0; o >>= 1) {
-    ValIdx y;
-    y.v = __shfl_xor_sync(0xffffffffu, r.v, o);
-    y.i = __shfl_xor_sync(0xffffffffu, r.i, o);
-    r = better(r, y);
-  }
-  __syncthreads();
-  return r;
-}
 
 __global__ void __launch_bounds__(1024) sample_argmax_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
                                                               int V, int idx_offset, int* __restrict__ out_idx,
@@ -52,12 +25,7 @@ __global__ void __launch_bounds__(1024) sample_argmax_kernel(const __nv_bfloat16
   __shared__ ValIdx sh[32];
   const int b = blockIdx.x;
   const __nv_bfloat16* row = logits + (size_t)b * ld;
-  ValIdx best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = __bfloat162float(row[i]);
-    if (v > best.v) { best.v = v; best.i = i; }   // ascending i per thread: strict > keeps the lowest index
-  }
-  best = block_argmax(best, sh);
+  const ValIdx best = block_argmax(thread_argmax_row(row, V), sh);
   if (threadIdx.x == 0) {
     if (out_idx) out_idx[b] = best.i + idx_offset;
     if (out_val) out_val[b] = best.v;

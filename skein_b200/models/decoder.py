@@ -386,7 +386,9 @@ class Decoder:
             # the combine then reads each (token, slot) pair from the ranks that own its expert. Row positions are global,
             # so no index exchange is needed.
             w8 = lw.fp8.get("w2")
-            if w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
+            if w8 is not None and self._expand_fp8(h, w8, (cnt_l, off_l), rows_hint=T * cfg.top_k // self.layout.ep):
+                st.pending = self.comm_moe.linear_push(h, w8.dequant(), (cnt_l, off_l))
+            elif w8 is not None and h.is_cuda and hasattr(self.comm_moe, "linear_push_fp8"):
                 st.pending = self.comm_moe.linear_push_fp8(h, None, w8, (cnt_l, off_l))
             else:
                 w2 = lw.w2 if lw.w2 is not None else w8.dequant()
@@ -462,21 +464,39 @@ class Decoder:
         """Column-parallel (local) projection through the block's bf16 weight or, when the plan's dtype map
         selected fp8 for this block, its block-scaled e4m3 copy."""
         w8 = lw.fp8.get(name)
+        w = getattr(lw, name)
+        if w8 is not None and self._expand_fp8(x, w8, grouped, rows_hint):
+            w, w8 = w8.dequant(), None
         if w8 is not None:
             # weights e4m3 with 1 x 128 block scales, activations bf16: the GEMM streams the e4m3 tiles and rescales them
-            # to bf16 in shared memory (ops/fp8.py)
+            # to bf16 on their way to the tensor cores (ops/fp8.py)
             if grouped is not None:
                 return fp8.grouped_linear_a16(x, w8, *grouped, swiglu=swiglu, rows_hint=rows_hint)
             return fp8.linear_a16(x, w8, swiglu=swiglu)
-        w = getattr(lw, name)
         if grouped is not None:
             return ops.grouped_linear(x, w, *grouped, swiglu=swiglu, rows_hint=rows_hint)
         return ops.swiglu_linear(x, w) if swiglu else ops.linear(x, w)
+
+    def _expand_fp8(self, x, w8, grouped=None, rows_hint=None) -> bool:
+        """Whether an e4m3 weight is expanded to a transient bf16 matrix for this call. The weight-fp8 GEMM rescales a
+        weight tile once per token tile that uses it, which is free while a step is a few token tiles wide (decode) and
+        dominates at prefill size; there one expansion pass (csrc/kernels/quant.cu) plus the bf16 GEMM is faster."""
+        if not x.is_cuda or getattr(self, "fp8_expand_rows", 256) <= 0:
+            return False
+        groups = w8.shape[0] if (grouped is not None and len(w8.shape) == 3) else 1
+        rows = rows_hint if rows_hint is not None else x.shape[0]
+        return rows / groups > getattr(self, "fp8_expand_rows", 256)
 
     def _row_parallel(self, x, lw, name, grouped=None):
         """Row-parallel projection. Returns (partial [n_src, rows, H], flags, epoch) for the fused reduce."""
         single = self.comm is None or self.comm.size == 1
         w8 = lw.fp8.get(name)
+        if w8 is not None and self._expand_fp8(x, w8, grouped):
+            w = w8.dequant()
+            if single:
+                y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
+                return y.unsqueeze(0), None, None
+            return self.comm.linear_push(x, w, grouped)
         if w8 is not None and single:
             return self._col_linear(x, lw, name, grouped=grouped).unsqueeze(0), None, None
         if w8 is not None and x.is_cuda and hasattr(self.comm, "linear_push_fp8"):

@@ -90,6 +90,7 @@ def lib():
     _sig(L, "skein_merge_candidates", i32, [vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, vp])
     _sig(L, "skein_sample_topk_topp", i32, [vp, i64, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp])
     _sig(L, "skein_quant_fp8_block128", i32, [vp, vp, vp, i64, i32, vp])
+    _sig(L, "skein_dequant_fp8_block128_t", i32, [vp, vp, vp, i64, i32, vp])
     _sig(L, "skein_advance_decode_state", i32, [vp, vp, vp, vp, i32, vp, vp])
     pvp = C.POINTER(C.c_void_p)
     _sig(L, "skein_ep_dispatch_pull", i32, [pvp, pvp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp])

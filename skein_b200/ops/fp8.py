@@ -35,8 +35,15 @@ class Fp8Weight:
         return self.q.is_cuda
 
     def dequant(self) -> torch.Tensor:
+        """The weight as bf16, in its logical shape. On a GPU one kernel pass (csrc/kernels/quant.cu)."""
         rows_total = self.scale_t.shape[1]
         K = self.shape[-1]
+        if self.q.is_cuda:
+            out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.q.device)
+            _lib.check(_lib.lib().skein_dequant_fp8_block128_t(self.q.data_ptr(), self.scale_t.data_ptr(), out.data_ptr(),
+                                                               rows_total, K, _lib.stream_ptr()), "dequant_fp8_block128")
+            _lib.count_launch()
+            return out
         w = ref.dequant_fp8_block128(self.q.reshape(rows_total, K), self.scale_t.t().contiguous())
         return w.view(*self.shape).to(torch.bfloat16)
 

@@ -155,12 +155,16 @@ class TPComm:
         _lib.check(rc, "publish_rows")
         _lib.count_launch()
 
+    def _zeros(self, rows):
+        return torch.zeros(rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+
     def linear_push(self, x, w, grouped=None):
         """Returns (partial, flags, epoch) for ops.reduce_residual_rmsnorm: peer partials in fused mode, else the
         all-reduced [1, rows, H] tensor and no flags."""
         rows = x.shape[0]
         if not self._fused_ok(rows):
-            y = ops.grouped_linear(x, w, *grouped) if grouped is not None else ops.linear(x, w)
+            # rows that belong to no local expert (expert parallelism) must add nothing to the sum
+            y = (ops.grouped_linear(x, w, *grouped, out=self._zeros(rows)) if grouped is not None else ops.linear(x, w))
             dist.all_reduce(y, group=self.group)
             return y.unsqueeze(0), None, None
         b = self.cur
@@ -185,7 +189,8 @@ class TPComm:
         if xs is None:
             x = xq
             if not self._fused_ok(rows):
-                y = fp8.grouped_linear_a16(x, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear_a16(x, w8)
+                y = (fp8.grouped_linear_a16(x, w8, *grouped, rows_hint=rows_hint, out=self._zeros(rows)) if grouped is not None
+                     else fp8.linear_a16(x, w8))
                 dist.all_reduce(y, group=self.group)
                 return y.unsqueeze(0), None, None
             b = self.cur
@@ -199,7 +204,8 @@ class TPComm:
             part = self._partials(b, rows)
             return part, part.flags, part.epoch
         if not self._fused_ok(rows):
-            y = fp8.grouped_linear(xq, xs, w8, *grouped, rows_hint=rows_hint) if grouped is not None else fp8.linear(xq, xs, w8)
+            y = (fp8.grouped_linear(xq, xs, w8, *grouped, rows_hint=rows_hint, out=self._zeros(rows)) if grouped is not None
+                 else fp8.linear(xq, xs, w8))
             dist.all_reduce(y, group=self.group)
             return y.unsqueeze(0), None, None
         b = self.cur

@@ -89,3 +89,31 @@ def test_fp8_weight_bf16_activation_grouped(swiglu):
     wd = fp8.Fp8Weight(wq.q.cpu(), wq.scale_t.cpu(), wq.shape).dequant()
     want = ref.grouped_linear(xs_.cpu(), wd, cnt.cpu(), off.cpu(), swiglu)
     assert rel(y, want) < 8e-3, rel(y, want)
+
+
+@pytest.mark.parametrize("shape", [(384, 1024), (3, 256, 512), (1000, 128)])
+@pytest.mark.parametrize("pow2", [True, False])
+def test_fp8_weight_expansion_matches_reference(shape, pow2):
+    """The one-pass expansion of an e4m3 weight to bf16 (prefill-sized projections) against the reference
+    dequantisation of the same stored blocks; with power-of-two scales it is exact."""
+    torch.manual_seed(5)
+    w = (torch.randn(*shape, device=DEV) * 0.05).bfloat16()
+    wq = fp8.quantize_weight(w, pow2_scales=pow2)
+    got = wq.dequant()
+    rows_total, K = wq.scale_t.shape[1], shape[-1]
+    want = ref.dequant_fp8_block128(wq.q.reshape(rows_total, K).cpu(), wq.scale_t.t().contiguous().cpu()).view(*shape)
+    assert got.shape == tuple(shape) and got.dtype == torch.bfloat16
+    assert torch.equal(got.cpu(), want.to(torch.bfloat16))
+    assert rel(got, w) < 0.05
+
+
+def test_quantiser_matches_reference_blocks():
+    """The block quantiser (half a warp per 1 x 128 block) against the CPU restatement: scales and codes."""
+    torch.manual_seed(6)
+    x = (torch.randn(77, 1024, device=DEV) * 3).bfloat16()
+    x[5, 128:256] = 0          # a zero block keeps scale 1
+    q, s = ops.quant_fp8_block128(x)
+    q_ref, s_ref = ref.quant_fp8_block128(x.cpu())
+    assert torch.allclose(s.cpu(), s_ref, rtol=1e-6, atol=0)
+    same = (q.cpu().view(torch.uint8) == q_ref.view(torch.uint8)).float().mean()
+    assert same > 0.999, same          # a code may differ by one step where x / scale sits on a rounding boundary

@@ -265,6 +265,25 @@ def test_reduce_norm_route_equals_separate_kernels(T, H, E, n_src):
     assert ops.workspace().route_barrier.tolist() == [0, 0]
 
 
+@pytest.mark.parametrize("V,off", [(1003, 0), (1003, 3), (7, 1), (32000, 5), (4099, 8)])
+def test_argmax_ragged_rows(V, off):
+    """Rows that start off a 16-byte boundary and lengths that are no multiple of eight: the vector scan's head and
+    tail, ties included."""
+    torch.manual_seed(V + off)
+    B = 6
+    buf = torch.randn(B, V + 16, device=DEV).bfloat16()
+    logits = buf[:, off:off + V]
+    logits[2, V - 1] = 40
+    logits[3, 0] = 41
+    logits[4, V - 1] = 39
+    logits[4, min(V - 1, 2)] = 39   # tie -> lower index
+    val = torch.empty(B, device=DEV)
+    a = ops.sample_argmax(logits, idx_offset=11, out_val=val)
+    want = ref.sample_argmax(logits.cpu().contiguous())
+    assert torch.equal(a.cpu(), (want + 11).to(torch.int32))
+    assert torch.equal(val.cpu(), logits.float().max(dim=1).values.cpu())
+
+
 def test_sampling():
     torch.manual_seed(9)
     B, V = 5, 32000

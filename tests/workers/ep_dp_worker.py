@@ -91,10 +91,16 @@ def main():
     if rank == 0:
         want = Engine(Decoder(cfg, full, num_pages=96, page_size=16, max_pos=256),
                       EngineConfig(max_batch=16, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False)).generate(prompts, 6)
-        # a router near-tie may flip a token under bf16 rounding, after which that sequence diverges: first tokens of
-        # every sequence and most sequences in full must agree
+        # free-running comparison: a router near-tie may flip a token under bf16 rounding, after which that sequence
+        # diverges, so most sequences must agree in full here; the strict check is the teacher-forced one below
         same = sum(a == b for a, b in zip(got, want))
-        assert all(a[0] == b[0] for a, b in zip(got, want)) and same >= len(prompts) - 2, ("got", got, "want", want)
+        assert same >= (2 * len(prompts)) // 3, ("got", got, "want", want)
+    dist.barrier()
+
+    # 3. the same layout teacher-forced with the CPU model's tokens, every mismatch explained by a near-tie
+    from skein_b200.parallel.selfcheck import teacher_forced_check
+    info = teacher_forced_check(world, rank, dev, comm_moe=comm, tp=1, ep=world, hidden=H, dp_attention=True)
+    assert info["dp_attention"] and info["graph_replays"] > 0, info
     dist.barrier()
     if rank == 0:
         print("EP_DP_WORKER_OK world", world)
