@@ -486,6 +486,16 @@ def attn_prefill(q, kv_cache, block_table, q_start, q_len, kv_len, max_q_len, Hq
     if out is None:
         out = torch.empty(q.shape[0], Hq * D, dtype=torch.bfloat16, device=q.device)
     ws = workspace()
+    if D == 128 and kv_cache.shape[3] == 16 and os.environ.get("SKEIN_ATTN_PREFILL", "tc") != "mma":
+        # tcgen05 kernel (csrc/kernels/attn_prefill_tc.cu): Q / K / V tiles by TMA, S, P and O in tensor memory
+        rc = _lib.lib().skein_attn_prefill_tc(
+            q.data_ptr(), q.stride(0), q.shape[0], kv_cache.data_ptr(), block_table.data_ptr(), q_start.data_ptr(),
+            q_len.data_ptr(), kv_len.data_ptr(), out.data_ptr(), ws.status.data_ptr(), q_len.shape[0], int(max_q_len), Hq, Hkv, D,
+            kv_cache.shape[3], block_table.stride(0), kv_cache.shape[0], float(scale), _lib.stream_ptr())
+        if rc != -1:
+            _lib.check(rc, "attn_prefill_tc")
+            _lib.count_launch()
+            return out
     rc = _lib.lib().skein_attn_prefill(
         q.data_ptr(), q.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), q_start.data_ptr(), q_len.data_ptr(),
         kv_len.data_ptr(), out.data_ptr(), ws.status.data_ptr(), q_len.shape[0], int(max_q_len), Hq, Hkv, D,

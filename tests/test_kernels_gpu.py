@@ -166,8 +166,11 @@ def test_attn_decode_rope_fusion_equals_separate_kernels(Hq, Hkv, splits):
     assert _rel_err(o1, o2) < 5e-3
 
 
+@pytest.mark.parametrize("impl", ["tc", "mma"])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
-def test_attn_prefill(Hq, Hkv):
+def test_attn_prefill(Hq, Hkv, impl, monkeypatch):
+    """tc: the tcgen05 kernel (tensor-memory accumulators, TMA page tiles); mma: the mma.sync fallback."""
+    monkeypatch.setenv("SKEIN_ATTN_PREFILL", impl)
     torch.manual_seed(6)
     D, ps = 128, 16
     q_lens = [64, 1, 100, 37]
@@ -181,6 +184,38 @@ def test_attn_prefill(Hq, Hkv):
     o = ops.attn_prefill(q, kv, bt, qs, ql, kl, max(q_lens), Hq, Hkv, D)
     _check_status()
     assert _rel_err(o, ref.attn_prefill(q, kv, bt, qs, ql, kl, Hq, Hkv, D)) < 1e-2
+
+
+@pytest.mark.parametrize("impl", ["tc", "mma"])
+def test_attn_prefill_long_and_poisoned(impl, monkeypatch):
+    """Several 128-row query tiles and 128-token context tiles per sequence, chunks that start off a tile boundary, and
+    a cache whose slots past every sequence's length hold NaN: nothing beyond the context may reach the result."""
+    monkeypatch.setenv("SKEIN_ATTN_PREFILL", impl)
+    torch.manual_seed(16)
+    Hq, Hkv, D, ps = 8, 2, 128, 16
+    q_lens = [300, 129, 512, 5]
+    kv_lens = [300, 641, 1000, 133]
+    kv, bt, mb = _make_cache(len(q_lens), kv_lens, Hkv, D, ps)
+    for s_, n in enumerate(kv_lens):                     # poison every slot past the context, and the unused pages
+        for b in range(mb):
+            lo = max(0, n - b * ps)
+            if lo < ps:
+                kv[bt[s_, b].long(), :, :, lo:, :] = float("nan")
+    T = sum(q_lens)
+    q = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    starts = [0]
+    for n in q_lens[:-1]:
+        starts.append(starts[-1] + n)
+    qs = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    ql = torch.tensor(q_lens, dtype=torch.int32, device=DEV)
+    kl = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    o = ops.attn_prefill(q, kv, bt, qs, ql, kl, max(q_lens), Hq, Hkv, D)
+    o2 = ops.attn_prefill(q, kv, bt, qs, ql, kl, max(q_lens), Hq, Hkv, D)
+    _check_status()
+    assert torch.isfinite(o.float()).all()
+    assert torch.equal(o, o2)
+    clean = torch.nan_to_num(kv.float(), nan=0.0).bfloat16()
+    assert _rel_err(o, ref.attn_prefill(q, clean, bt, qs, ql, kl, Hq, Hkv, D)) < 1e-2
 
 
 def test_rope_kv_append_matches_reference():
