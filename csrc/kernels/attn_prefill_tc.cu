@@ -193,36 +193,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_after();
       const bool masked = n0 + TC_BN - 1 > pos0 + q0;   // some row of the tile sees only part of these keys
       const int limit = pos_r - n0;                     // this row sees columns 0 .. limit of the tile
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
+      // pass 1: row maximum of the raw scores (64 columns per round: both loads in flight before the wait)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < TC_BN / 16; ++c) {
-        uint32_t sv[16];
-        tmem_ld16(tm_s + lane_addr + c * 16, sv);
+      for (int h = 0; h < TC_BN / 64; ++h) {
+        uint32_t sv[64];
+        tmem_ld32(tm_s + lane_addr + h * 64, sv);
+        tmem_ld32(tm_s + lane_addr + h * 64 + 32, sv + 32);
         tmem_ld_wait();
         if (masked) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, (c * 16 + i <= limit) ? __uint_as_float(sv[i]) : -INFINITY);
+          for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], (h * 64 + i <= limit) ? __uint_as_float(sv[i]) : -INFINITY);
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
         }
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2e);           // the scale is positive
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;    // the scale is positive
+      // The running maximum only moves when the tile's maximum exceeds it by more than 2^8: until then the
+      // probabilities of this tile are at most 256 (exact in bf16 and harmless in the fp32 sums), and O needs no
+      // rescaling; the final division by the row sum undoes whatever reference the row ended on.
+      const float m_new = (m == -INFINITY || mx > m + 8.f) ? fmaxf(m, mx) : m;
       const float alpha = (m == -INFINITY) ? 1.f : exp2f(m - m_new);
       if (j > 0) {
-        // O of the previous tiles is complete in tensor memory; bring it to the new maximum if some row moved
+        // O of the previous tiles is complete in tensor memory; bring it to the new reference if some row moved
         if (!mbar_wait(bar_odone, (j - 1) & 1, abort_flag, TC_BUDGET_NS)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < TC_D / 16; ++c) {
-            uint32_t ov[16];
-            tmem_ld16(tm_o + lane_addr + c * 16, ov);
+          for (int h = 0; h < TC_D / 64; ++h) {
+            uint32_t ov[64];
+            tmem_ld32(tm_o + lane_addr + h * 64, ov);
+            tmem_ld32(tm_o + lane_addr + h * 64 + 32, ov + 32);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st16(tm_o + lane_addr + c * 16, ov);
+            for (int i = 0; i < 64; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st16(tm_o + lane_addr + h * 64 + c * 16, ov + c * 16);
           }
         }
       }
@@ -231,31 +238,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // pass 2: p = exp2(s * scale - m), row sum, bf16 pairs written over the columns of S already consumed
       float rs = 0.f;
 #pragma unroll
-      for (int c2 = 0; c2 < TC_BN / 32; ++c2) {
-        uint32_t pk[16];
+      for (int h = 0; h < TC_BN / 64; ++h) {
+        uint32_t sv[64];
+        tmem_ld32(tm_s + lane_addr + h * 64, sv);
+        tmem_ld32(tm_s + lane_addr + h * 64 + 32, sv + 32);
+        tmem_ld_wait();
+        uint32_t pk[32];
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
-          const int c = c2 * 2 + hc;
-          uint32_t sv[16];
-          tmem_ld16(tm_s + lane_addr + c * 16, sv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float x0 = fmaf(__uint_as_float(sv[i]), p.scale_log2e, -m_new);
-            float x1 = fmaf(__uint_as_float(sv[i + 1]), p.scale_log2e, -m_new);
-            if (masked) {
-              if (c * 16 + i > limit) x0 = -INFINITY;
-              if (c * 16 + i + 1 > limit) x1 = -INFINITY;
-            }
-            const float p0 = exp2f(x0), p1 = exp2f(x1);
-            // the row sum is taken over the rounded values, the ones the tensor cores multiply
-            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            const float2 pf = __bfloat1622float2(pb);
-            rs += pf.x + pf.y;
-            pk[hc * 8 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&pb);
+        for (int i = 0; i < 64; i += 2) {
+          float x0 = fmaf(__uint_as_float(sv[i]), p.scale_log2e, -m_new);
+          float x1 = fmaf(__uint_as_float(sv[i + 1]), p.scale_log2e, -m_new);
+          if (masked) {
+            if (h * 64 + i > limit) x0 = -INFINITY;
+            if (h * 64 + i + 1 > limit) x1 = -INFINITY;
           }
+          const float p0 = exp2f(x0), p1 = exp2f(x1);
+          // the row sum is taken over the rounded values, the ones the tensor cores multiply
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          const float2 pf = __bfloat1622float2(pb);
+          rs += pf.x + pf.y;
+          pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
         }
-        tmem_st16(tm_p + lane_addr + c2 * 16, pk);
+        // columns [32 h, 32 h + 32) of P lie inside columns [0, 64 h + 64) of S, all of which have been read
+        tmem_st16(tm_p + lane_addr + h * 32, pk);
+        tmem_st16(tm_p + lane_addr + h * 32 + 16, pk + 16);
       }
       l += rs;
       if (n0 + TC_BN > kv_hi) {
