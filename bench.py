@@ -57,6 +57,11 @@ def parse():
     ap.add_argument("--fp8-blocks", default="", help="'a:b' = blocks a..b-1 (of the whole model) in block-scaled fp8, all four projections")
     ap.add_argument("--fp8-experts", action="store_true", help="block-scaled e4m3 expert / FFN weights (marks dtype)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--burst", type=int, default=0,
+                    help="also replay a synthetic burst trace of this many requests through the serving engine (on/off Poisson "
+                         "arrivals 50 / 2 per second every 10 s, log-normal prompts of median 600 capped at --prompt, outputs "
+                         "uniform 32 .. --gen): adds the key 'burst' (TTFT / TPOT under load)")
+    ap.add_argument("--burst-time-scale", type=float, default=1.0, help="trace seconds per wall second")
     ap.add_argument("--replicated-attention", action="store_true",
                     help="expert parallelism: every rank runs attention for all sequences (the comparison arm) instead of "
                          "each rank attending over its own slice with token dispatch between the ranks")
@@ -211,6 +216,76 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
+
+
+def replay_burst(args, cfg, dec, runner, make_control, world, rank, B, P, Gn, use_graphs, max_over_ranks, barrier):
+    """Replays a synthetic burst trace (BASELINE config 4's arrival process) through the serving engine on all ranks in
+    lock step: rank 0's clock is announced through the control page every step, every rank submits the requests that
+    have arrived by then (the trace is generated from a seed, identically everywhere) and steps its engine. Chunked
+    prefill interleaves with decode (at most 2048 prompt tokens per step while sequences decode), at most B sequences
+    run at a time, the rest queue. Times are wall clock on rank 0, from a request's arrival to its tokens."""
+    import torch
+
+    from skein_b200 import core
+    from skein_b200.runtime.engine import Engine, EngineConfig
+
+    lines = core.synth_burst_trace(args.burst, 0, 50.0, 2.0, 10.0, 600.0, P, 32, Gn).splitlines()
+    reqs = [json.loads(l) for l in lines[1:] if l.strip()]
+    g = torch.Generator().manual_seed(4321)
+    for kv in dec.kv:
+        kv.zero_()
+    ecfg = EngineConfig(max_batch=B, tpot_ms=1e9, ttft_ms=1e9, use_graphs=use_graphs, prefix_cache=False,
+                        max_prefill_tokens=8192, interleave_prefill_tokens=2048)
+    eng = Engine(dec, ecfg)
+    eng.runner = runner
+    ctl = make_control()
+    prompts = [torch.randint(0, cfg.vocab_size, (max(1, min(int(r["prompt_tokens"]), P)),), generator=g).tolist() for r in reqs]
+    arrival = [float(r["arrival_ms"]) / args.burst_time_scale for r in reqs]       # wall milliseconds after the start
+    nxt, n_tok = 0, 0
+    t_first, t_last, n_out, step_ms, batch_sizes = {}, {}, {}, [], []
+    barrier()
+    t0 = time.perf_counter()
+    while nxt < len(reqs) or not eng.idle:
+        t_s = time.perf_counter()
+        if world > 1:
+            if rank == 0:
+                now = int((time.perf_counter() - t0) * 1e3)
+                ctl.lead(None, now)
+            else:
+                _, now = ctl.follow()
+        else:
+            now = int((time.perf_counter() - t0) * 1e3)
+        while nxt < len(reqs) and arrival[nxt] <= now:
+            eng.submit(prompts[nxt], int(reqs[nxt]["output_tokens"]), now_ms=now, request_id=nxt + 1)
+            nxt += 1
+        evs = eng.step(now)
+        if ctl.agree_failed(eng.last_step_failed):
+            raise RuntimeError("an engine step failed during the burst replay: " + str([e.error for e in evs if e.error][:1]))
+        t_e = time.perf_counter()
+        if evs:
+            step_ms.append((t_e - t_s) * 1e3)
+            batch_sizes.append(len(evs))
+        else:
+            time.sleep(0.0002)
+        for e in evs:
+            if e.error is None:
+                n_tok += 1
+                t_first.setdefault(e.request_id, t_e)
+                t_last[e.request_id] = t_e
+                n_out[e.request_id] = n_out.get(e.request_id, 0) + 1
+    torch.cuda.synchronize()
+    wall = max_over_ranks(time.perf_counter() - t0)
+    ctl.close()
+    q = lambda xs, f: (sorted(xs)[min(len(xs) - 1, int(f * len(xs)))] if xs else None)
+    ttft = [(t_first[i + 1] - t0) * 1e3 - arrival[i] for i in range(len(reqs)) if i + 1 in t_first]
+    tpot = [(t_last[i] - t_first[i]) * 1e3 / (n_out[i] - 1) for i in t_first if n_out[i] > 1]
+    rnd = lambda v: None if v is None else round(v, 2)
+    return {"requests": len(reqs), "completed": len(t_first), "output_tokens": n_tok, "wall_s": round(wall, 2),
+            "tokens_per_s": round(n_tok / wall, 1), "ttft_p50_ms": rnd(q(ttft, 0.5)), "ttft_p95_ms": rnd(q(ttft, 0.95)),
+            "tpot_p50_ms": rnd(q(tpot, 0.5)), "tpot_p99_ms": rnd(q(tpot, 0.99)), "step_p50_ms": rnd(q(step_ms, 0.5)),
+            "step_p99_ms": rnd(q(step_ms, 0.99)), "mean_batch": rnd(sum(batch_sizes) / max(1, len(batch_sizes))),
+            "max_concurrent": B, "time_scale": args.burst_time_scale,
+            "trace": "on/off Poisson 50 / 2 req/s every 10 s, log-normal prompts (median 600, max %d), outputs uniform 32..%d, seed 0" % (P, Gn)}
 
 
 def run_pipeline(args, emit_json):
@@ -599,6 +674,11 @@ def main():
         run_u = ModelRunner(dec_u, max_blocks_per_seq=blocks_per_seq, use_graphs=True, ctx_hint=P + Gn // 2)
         unfused_ms, _, _, _ = device_timed(run_u, "unfused")
 
+    def make_control():
+        if world > 1:
+            return SharedControl(f"/dev/shm/skein_bench_ctl_{os.environ.get('MASTER_PORT', '0')}", rank, world, control_group, wait_s=120)
+        return LocalControl()
+
     # ---- end to end through the serving engine ----------------------------------------------------------------
     e2e, ttft_p50, tpot_p99 = None, None, None
     if not args.no_e2e:
@@ -606,11 +686,7 @@ def main():
                             max_prefill_tokens=8192, interleave_prefill_tokens=0)
         for kv in dec.kv:
             kv.zero_()
-        if world > 1:
-            path = f"/dev/shm/skein_bench_ctl_{os.environ.get('MASTER_PORT', '0')}"
-            ctl = SharedControl(path, rank, world, control_group, wait_s=120)
-        else:
-            ctl = LocalControl()
+        ctl = make_control()
         e2e_vals, step_ms = [], []
         parts = {"announce": 0.0, "engine_step": 0.0, "agree": 0.0, "n": 0}
         for r in range(min(R, 3)):
@@ -678,6 +754,10 @@ def main():
                "repeats": [round(v, 1) for v in e2e_vals],
                "host_us_per_step_rank0": {k: round(v / max(1, parts["n"]) * 1e6, 1) for k, v in parts.items() if k != "n"}}
 
+    burst = None
+    if args.burst > 0:
+        burst = replay_burst(args, cfg, dec, runner, make_control, world, rank, B, P, Gn, use_graphs, max_over_ranks, barrier)
+
     if rank == 0:
         out = {
             "metric": args.model.replace("-", "_") + "_decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s",
@@ -698,7 +778,7 @@ def main():
             "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world),
             "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2),
             "tpot_p99_ms": tpot_p99,
-            "e2e": e2e, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,
+            "e2e": e2e, "burst": burst, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,
             "selfcheck": selfcheck["result"] if selfcheck else ("skipped" if world > 1 else "single rank"),
             "selfcheck_detail": selfcheck,
             "unfused_ms_per_step": None if unfused_ms is None else round(unfused_ms / K, 4),

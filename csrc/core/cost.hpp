@@ -53,6 +53,8 @@ struct CostConstants {
   std::map<std::string, std::map<std::string, double>> efficiency;   // op kind -> dtype -> fraction
   std::map<std::string, double> collective_efficiency;
   std::map<std::string, double> hbm_gbps;                            // device kind -> GB/s (optional)
+  std::map<std::string, double> stream_efficiency;                   // weight dtype -> measured fraction of hbm_gbps the
+                                                                     // weight-streaming kernels reach (optional, default 1)
   std::map<std::string, double> fused_overlap;                       // collective -> hidden fraction (optional)
   std::map<std::string, double> parity_tolerance_mse;
   uint32_t prefill_tokens = 1024, decode_kv_tokens = 2048;
@@ -77,6 +79,7 @@ struct CostConstants {
       for (auto& kv : j.at("efficiency").members()) c.efficiency[kv.first] = table(kv.second);
       c.collective_efficiency = table(j.at("collective_efficiency"));
       if (const Json* h = j.find("hbm_gbps")) c.hbm_gbps = table(*h);
+      if (const Json* h = j.find("stream_efficiency")) c.stream_efficiency = table(*h);
       if (const Json* h = j.find("fused_overlap")) c.fused_overlap = table(*h);
       if (const Json* h = j.find("parity_tolerance_mse")) c.parity_tolerance_mse = table(*h);
       if (const Json* r = j.find("representative_workload")) {
@@ -196,8 +199,14 @@ inline double compute_time_with_dtype(const Layer& l, const ModelMeta& meta, Dty
   const double div = (double)std::max<uint64_t>(1, compute_divisor(l.kind, pl));
   double t = flops / (peak * 1e12 * eff * div) * 1e6;
   auto hb = c.hbm_gbps.find(kind);
-  if (hb != c.hbm_gbps.end() && hb->second > 0)
-    t = std::max(t, layer_stream_bytes(l, meta, wd, kvd, pl, wl) / (hb->second * 1e9) * 1e6);
+  if (hb != c.hbm_gbps.end() && hb->second > 0) {
+    // a narrower weight type moves fewer bytes but its kernel may reach a smaller share of the copy bandwidth (the e4m3
+    // tiles are rescaled to bf16 on their way to the tensor cores): the measured share per weight dtype decides whether
+    // the dtype map gains time or only memory
+    auto se = c.stream_efficiency.find(dtype_name(wd));
+    const double frac = (se != c.stream_efficiency.end() && se->second > 0) ? se->second : 1.0;
+    t = std::max(t, layer_stream_bytes(l, meta, wd, kvd, pl, wl) / (hb->second * frac * 1e9) * 1e6);
+  }
   return t;
 }
 

@@ -196,6 +196,38 @@ def op_quant_fp8(a):
     x = _bf(16384, 4096, std=1.0)
     return (lambda: ops.quant_fp8_block128(x)), x.numel() * 3 + x.numel() // 128 * 4, 2 * x.numel()
 
+def op_ep_dispatch(ep, a):
+    """Receiving half of the expert-parallel token dispatch (csrc/kernels/ep_dispatch.cu) for one rank of `ep`, with the
+    other ranks' published buffers standing in this GPU's memory (one launch reads all of them; their flags are already
+    raised): layout from all ranks' expert choices plus the gather of the rows routed to this rank's experts."""
+    import ctypes as C
+    from ..ops import _lib
+    T, k, E, H = a.tokens, 2, 8, 4096
+    ep = max(1, min(ep, 8))
+    per = max(1, T // ep)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows = [_bf(per, H, std=1.0) for _ in range(ep)]
+    ids = [torch.stack([torch.randperm(E, generator=g, device="cuda")[:k] for _ in range(per)]).to(torch.int32) for _ in range(ep)]
+    flags = torch.ones(ep, dtype=torch.int32, device="cuda")
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    n = ep * per * k
+    ids_all = torch.empty(n, dtype=torch.int32, device="cuda")
+    meta = torch.empty(2 * E + 1 + 2 * n, dtype=torch.int32, device="cuda")
+    xs = torch.empty(n, H, dtype=torch.bfloat16, device="cuda")
+    VP = C.c_void_p * ep
+    rp, ip = VP(*[r.data_ptr() for r in rows]), VP(*[i.data_ptr() for i in ids])
+    e_cnt = E // ep
+    keep = (rows, ids)
+
+    def fn():
+        _lib.check(_lib.lib().skein_ep_dispatch_pull(rp, ip, ep, per, k, E, 0, e_cnt, H, flags.data_ptr(), epoch.data_ptr(),
+                                                     ops.workspace().status.data_ptr(), 100, ids_all.data_ptr(), meta.data_ptr(),
+                                                     meta[E:].data_ptr(), meta[2 * E + 1:].data_ptr(),
+                                                     meta[2 * E + 1 + n:].data_ptr(), xs.data_ptr(), _lib.stream_ptr()), "ep_dispatch")
+        return keep
+    # bytes: all choices read once per pair CTA from L2, the gathered rows read and written once
+    return fn, n // ep * H * 2 * 2 + n * 4, n
+
 
 def build(name, a):
     tp = a.tp
@@ -225,11 +257,13 @@ def build(name, a):
         return op_argmax(tp, a)
     if name == "quant_fp8":
         return op_quant_fp8(a)
+    if name == "ep_dispatch":
+        return op_ep_dispatch(tp, a)
     raise SystemExit(f"unknown op {name}")
 
 
 OPS = ("moe_gate_up", "moe_down", "qkv", "o_proj", "lm_head", "attn_decode", "reduce_norm", "reduce_route", "router",
-       "attn_prefill", "prefill_qkv", "argmax", "quant_fp8")
+       "attn_prefill", "prefill_qkv", "argmax", "quant_fp8", "ep_dispatch")
 
 
 def main(argv=None):
