@@ -90,14 +90,17 @@ struct KernelArgs {
 // and zero included (both formats count their subnormals from the same exponent field value 0). One bf16x2
 // multiplication by (block scale * 2^120) therefore yields the scaled weight; it is exact when the scale is a
 // power of two, which is how this framework quantises weights (ops/fp8.py: quantize_weight).
-// (The hardware conversion e4m3x2 -> f16x2 would be cheaper, but the MMA then needs f16 for BOTH operands: an f16 A
-// operand with bf16 activations is not a legal operand pair of kind::f16.)
+// Per pair of values: one byte permute that also spreads each byte's sign over the byte above it (S:b per 16-bit
+// half), one shift left by 4 (sign at bit 15, the seven exponent / mantissa bits at 10..4), one mask that drops the
+// spare sign copies and what the shift carried over from the lower half, one multiplication.
+// (The hardware conversion e4m3x2 -> f16x2 would be cheaper still, but the MMA then needs f16 for BOTH operands: an f16
+// A operand with bf16 activations is not a legal operand pair of kind::f16.)
 __device__ __forceinline__ void e4m3x4_to_scaled_bf16x4(uint32_t w, uint32_t sc2, uint32_t& lo, uint32_t& hi) {
   uint32_t t0, t1;
-  asm("prmt.b32 %0, %1, 0, 0x1404;" : "=r"(t0) : "r"(w));   // bytes 0,1 -> the high byte of each 16-bit half
-  asm("prmt.b32 %0, %1, 0, 0x3424;" : "=r"(t1) : "r"(w));   // bytes 2,3
-  const uint32_t r0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
-  const uint32_t r1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
+  asm("prmt.b32 %0, %1, 0, 0x9180;" : "=r"(t0) : "r"(w));   // [sign(b1), b1, sign(b0), b0]
+  asm("prmt.b32 %0, %1, 0, 0xB3A2;" : "=r"(t1) : "r"(w));   // [sign(b3), b3, sign(b2), b2]
+  const uint32_t r0 = (t0 << 4) & 0x87F087F0u;
+  const uint32_t r1 = (t1 << 4) & 0x87F087F0u;
   // spelled out so that no fast-math flag turns it into a form that flushes the subnormal inputs
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(r0), "r"(sc2));
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(r1), "r"(sc2));
@@ -334,6 +337,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       uint32_t it = 0;
       int pos = kb_begin;
       bool ok = true;
+      // The hand-over of a converted half to the MMA warp is deferred by one step: its tensor-memory stores complete
+      // while the next half is loaded and converted, so the wait for them costs nothing when it finally comes.
+      int pending_slot = -1;
       while (pos < kb_end && ok) {
         const int u = pos / KB;
         const int kb0 = pos - u * KB;
@@ -387,35 +393,48 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tc_fence_after();
             // this thread's 16 columns of its lane: slot c, tile t, columns part * 16 .. + 15
             const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * (DUAL ? 2 : 1) * W8_SLOT_COLS + part * 16;
+            uint32_t o[DUAL ? 2 : 1][16];
+            uint4 v[DUAL ? 2 : 1][2];
 #pragma unroll
             for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
               const uint32_t src_row = raw + t * W_TILE_BYTES + r * 128;
-              uint32_t o[16];
-              uint4 v[2];
 #pragma unroll
-              for (int ci = 0; ci < 2; ++ci)             // this thread's two 16-byte chunks of e4m3, both loads first
+              for (int ci = 0; ci < 2; ++ci)             // this thread's 16-byte chunks of e4m3, all loads first
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(v[ci].x), "=r"(v[ci].y), "=r"(v[ci].z), "=r"(v[ci].w)
+                             : "=r"(v[t][ci].x), "=r"(v[t][ci].y), "=r"(v[t][ci].z), "=r"(v[t][ci].w)
                              : "r"(src_row + (((h * 4 + part * 2 + ci) ^ (r & 7)) << 4)));
+            }
+#pragma unroll
+            for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
 #pragma unroll
               for (int ci = 0; ci < 2; ++ci) {
-                e4m3x4_to_scaled_bf16x4(v[ci].x, sc[t], o[8 * ci + 0], o[8 * ci + 1]);
-                e4m3x4_to_scaled_bf16x4(v[ci].y, sc[t], o[8 * ci + 2], o[8 * ci + 3]);
-                e4m3x4_to_scaled_bf16x4(v[ci].z, sc[t], o[8 * ci + 4], o[8 * ci + 5]);
-                e4m3x4_to_scaled_bf16x4(v[ci].w, sc[t], o[8 * ci + 6], o[8 * ci + 7]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].x, sc[t], o[t][8 * ci + 0], o[t][8 * ci + 1]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].y, sc[t], o[t][8 * ci + 2], o[t][8 * ci + 3]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].z, sc[t], o[t][8 * ci + 4], o[t][8 * ci + 5]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].w, sc[t], o[t][8 * ci + 6], o[t][8 * ci + 7]);
               }
-              tmem_st16(conv + t * W8_SLOT_COLS, o);
             }
-            // the stores to tensor memory must have completed before the MMA warp is told
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bar_cfull[c]));
+            if (pending_slot >= 0) {
+              // the previous half's stores to tensor memory have had this half's conversion to complete
+              tmem_st_wait();
+              tc_fence_before();
+              mbar_arrive(smem_u32(&bar_cfull[pending_slot]));
+            }
+#pragma unroll
+            for (int t = 0; t < (DUAL ? 2 : 1); ++t) tmem_st16(conv + t * W8_SLOT_COLS, o[t]);
+            pending_slot = (int)c;
 #ifdef SKEIN_GEMM_TIMING
             if (r == 0 && part == 0) { PROF_ADD(2); g_w8_prof[blockIdx.x][6] += 1; }
 #endif
           }
         }
         pos = u * KB + kb1;
+      }
+      if (pending_slot >= 0) {
+        // (also on the way out after a failed wait: the MMA warp gives up on the abort flag, an extra arrival is harmless)
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_cfull[pending_slot]));
       }
     } else if (warp < 6) {
       // ================= epilogue (warps 2..5) =================
