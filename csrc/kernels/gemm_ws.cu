@@ -174,6 +174,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int n_tile = p.n_tile;
   const int k_elems = W8 ? 128 : 64;
   constexpr int W_STAGE_BYTES = (DUAL ? 2 : 1) * W_TILE_BYTES;   // weight bytes of one stage (bf16: 64 K, e4m3: 128 K)
+  constexpr int W8_STEPS = DUAL ? 2 : 1;   // W8: converter -> MMA hand-overs per stage (each carries two 32-column sub-tiles)
 
   if (has_work) {
     if (warp == 0) {
@@ -265,10 +266,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t ph = (it / a.stages) & 1;
             const uint32_t st = smem_base + s * a.stage_bytes;
             if (W8) {
-              // the weights of this stage arrive as two converted halves (64 K elements each) from the converter warps
+              // The weights of this stage arrive from the converter warps in steps of two 32-column sub-tiles: with a
+              // gate/up pair one 64-K half of both tiles per step (two steps per stage), else both halves of the one tile.
 #pragma unroll 1
-              for (int h = 0; h < 2 && ok; ++h) {
-                const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
+              for (int h = 0; h < W8_STEPS && ok; ++h) {
+                const uint32_t hit = W8_STEPS * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
                 {
                   PROF_T0();
                   if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
@@ -282,13 +284,23 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 PROF_T0();
                 tc_fence_after();
                 if (hit == 0) TS(2);
-                const uint32_t aw = tmem_base + a.conv_base + c * (DUAL ? 2 : 1) * W8_SLOT_COLS;   // converted weights, in TMEM
-                const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
+                const uint32_t aw = tmem_base + a.conv_base + c * 2 * W8_SLOT_COLS;   // converted weights, in TMEM
+                if (DUAL) {
+                  const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {      // 16 K elements = 8 columns of the A operand per MMA
-                  const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
-                  mma_f16_ts(d_tmem, aw + 8 * k, dx + 2 * k, idesc, accum);
-                  if (DUAL) mma_f16_ts(d_tmem + n_tile, aw + W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
+                  for (int k = 0; k < 4; ++k) {      // 16 K elements = 8 columns of the A operand per MMA
+                    const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
+                    mma_f16_ts(d_tmem, aw + 8 * k, dx + 2 * k, idesc, accum);
+                    mma_f16_ts(d_tmem + n_tile, aw + W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
+                  }
+                } else {
+#pragma unroll
+                  for (int t = 0; t < 2; ++t) {
+                    const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + t * (a.x_tile_bytes / 2));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                      mma_f16_ts(d_tmem, aw + t * W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, (kb > kb0 || t > 0 || k > 0) ? 1u : 0u);
+                  }
                 }
                 tc_commit(smem_u32(&bar_cempty[c]));
                 PROF_ADD(4);
@@ -377,8 +389,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             sc[t] = *reinterpret_cast<const uint32_t*>(&hs);
           }
 #pragma unroll 1
-          for (int h = 0; h < 2 && ok; ++h) {
-            const uint32_t hit = 2 * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
+          for (int h = 0; h < W8_STEPS && ok; ++h) {
+            const uint32_t hit = W8_STEPS * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
             {
               PROF_T0();
               if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
@@ -391,27 +403,30 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
             PROF_T0();
             tc_fence_after();
-            // this thread's 16 columns of its lane: slot c, tile t, columns part * 16 .. + 15
-            const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * (DUAL ? 2 : 1) * W8_SLOT_COLS + part * 16;
-            uint32_t o[DUAL ? 2 : 1][16];
-            uint4 v[DUAL ? 2 : 1][2];
+            // this thread's 16 columns of its lane in each of the step's two sub-tiles: slot c, sub-tile t, columns
+            // part * 16 .. + 15. Sub-tile t is tile t (gate / up) at half h with a pair, else half t of the one tile.
+            const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * 2 * W8_SLOT_COLS + part * 16;
+            uint32_t o[2][16];
+            uint4 v[2][2];
 #pragma unroll
-            for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
-              const uint32_t src_row = raw + t * W_TILE_BYTES + r * 128;
+            for (int t = 0; t < 2; ++t) {
+              const uint32_t src_row = raw + (DUAL ? t : 0) * W_TILE_BYTES + r * 128;
+              const int half = DUAL ? h : t;
 #pragma unroll
               for (int ci = 0; ci < 2; ++ci)             // this thread's 16-byte chunks of e4m3, all loads first
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                              : "=r"(v[t][ci].x), "=r"(v[t][ci].y), "=r"(v[t][ci].z), "=r"(v[t][ci].w)
-                             : "r"(src_row + (((h * 4 + part * 2 + ci) ^ (r & 7)) << 4)));
+                             : "r"(src_row + (((half * 4 + part * 2 + ci) ^ (r & 7)) << 4)));
             }
 #pragma unroll
-            for (int t = 0; t < (DUAL ? 2 : 1); ++t) {
+            for (int t = 0; t < 2; ++t) {
+              const uint32_t sct = sc[DUAL ? t : 0];
 #pragma unroll
               for (int ci = 0; ci < 2; ++ci) {
-                e4m3x4_to_scaled_bf16x4(v[t][ci].x, sc[t], o[t][8 * ci + 0], o[t][8 * ci + 1]);
-                e4m3x4_to_scaled_bf16x4(v[t][ci].y, sc[t], o[t][8 * ci + 2], o[t][8 * ci + 3]);
-                e4m3x4_to_scaled_bf16x4(v[t][ci].z, sc[t], o[t][8 * ci + 4], o[t][8 * ci + 5]);
-                e4m3x4_to_scaled_bf16x4(v[t][ci].w, sc[t], o[t][8 * ci + 6], o[t][8 * ci + 7]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].x, sct, o[t][8 * ci + 0], o[t][8 * ci + 1]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].y, sct, o[t][8 * ci + 2], o[t][8 * ci + 3]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].z, sct, o[t][8 * ci + 4], o[t][8 * ci + 5]);
+                e4m3x4_to_scaled_bf16x4(v[t][ci].w, sct, o[t][8 * ci + 6], o[t][8 * ci + 7]);
               }
             }
             if (pending_slot >= 0) {
@@ -421,7 +436,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               mbar_arrive(smem_u32(&bar_cfull[pending_slot]));
             }
 #pragma unroll
-            for (int t = 0; t < (DUAL ? 2 : 1); ++t) tmem_st16(conv + t * W8_SLOT_COLS, o[t]);
+            for (int t = 0; t < 2; ++t) tmem_st16(conv + t * W8_SLOT_COLS, o[t]);
             pending_slot = (int)c;
 #ifdef SKEIN_GEMM_TIMING
             if (r == 0 && part == 0) { PROF_ADD(2); g_w8_prof[blockIdx.x][6] += 1; }
@@ -836,7 +851,7 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
     // the converted weights live in tensor memory behind the two accumulators: 512 columns in all
     ka->conv_slots = W8_CONV_SLOTS;
     ka->conv_base = 2 * ka->acc_stride;
-    if (ka->conv_base + ka->conv_slots * (dual ? 2 : 1) * W8_SLOT_COLS > 512) return -3;   // token tile too wide for this form
+    if (ka->conv_base + ka->conv_slots * 2 * W8_SLOT_COLS > 512) return -3;   // token tile too wide for this form
   }
   int st = budget / ka->stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
