@@ -174,7 +174,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int n_tile = p.n_tile;
   const int k_elems = W8 ? 128 : 64;
   constexpr int W_STAGE_BYTES = (DUAL ? 2 : 1) * W_TILE_BYTES;   // weight bytes of one stage (bf16: 64 K, e4m3: 128 K)
-  constexpr int W8_STEPS = DUAL ? 2 : 1;   // W8: converter -> MMA hand-overs per stage (each carries two 32-column sub-tiles)
+  // W8: one converter -> MMA hand-over per stage. A slot of the tensor-memory ring holds the whole converted K block of the
+  // stage as pairs of 32-column sub-tiles: with a gate/up pair, (gate, up) of K half 0 then of K half 1; else the two K
+  // halves of the one tile.
+  constexpr int W8_PAIRS = DUAL ? 2 : 1;
+  constexpr int W8_SLOT = W8_PAIRS * 2 * W8_SLOT_COLS;
 
   if (has_work) {
     if (warp == 0) {
@@ -266,45 +270,38 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t ph = (it / a.stages) & 1;
             const uint32_t st = smem_base + s * a.stage_bytes;
             if (W8) {
-              // The weights of this stage arrive from the converter warps in steps of two 32-column sub-tiles: with a
-              // gate/up pair one 64-K half of both tiles per step (two steps per stage), else both halves of the one tile.
-#pragma unroll 1
-              for (int h = 0; h < W8_STEPS && ok; ++h) {
-                const uint32_t hit = W8_STEPS * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
-                {
-                  PROF_T0();
-                  if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
-                    report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
-                    abort_flag = 1;
-                    ok = false;
-                    break;
-                  }
-                  PROF_ADD(3);
-                }
+              // the converted weights of this stage arrive from the converter warps in one slot of the tensor-memory ring
+              const uint32_t c = it % a.conv_slots, cph = (it / a.conv_slots) & 1;
+              {
                 PROF_T0();
-                tc_fence_after();
-                if (hit == 0) TS(2);
-                const uint32_t aw = tmem_base + a.conv_base + c * 2 * W8_SLOT_COLS;   // converted weights, in TMEM
-                if (DUAL) {
-                  const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
+                if (!mbar_wait(smem_u32(&bar_cfull[c]), cph, &abort_flag, a.budget_ns)) {
+                  report_status(p.status, ST_TIMEOUT_SMEM_FULL, blockIdx.x);
+                  abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+                PROF_ADD(3);
+              }
+              PROF_T0();
+              tc_fence_after();
+              if (it == 0) TS(2);
+              const uint32_t aw = tmem_base + a.conv_base + c * W8_SLOT;
 #pragma unroll
-                  for (int k = 0; k < 4; ++k) {      // 16 K elements = 8 columns of the A operand per MMA
-                    const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
-                    mma_f16_ts(d_tmem, aw + 8 * k, dx + 2 * k, idesc, accum);
-                    mma_f16_ts(d_tmem + n_tile, aw + W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
-                  }
-                } else {
+              for (int h = 0; h < 2; ++h) {          // K halves of the stage: 64 K elements = 4 MMAs of 16 (8 columns of A each)
+                const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + h * (a.x_tile_bytes / 2));
 #pragma unroll
-                  for (int t = 0; t < 2; ++t) {
-                    const uint64_t dx = umma_desc_sw128(st + W_STAGE_BYTES + t * (a.x_tile_bytes / 2));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                      mma_f16_ts(d_tmem, aw + t * W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, (kb > kb0 || t > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) {
+                  const uint32_t accum = (kb > kb0 || h > 0 || k > 0) ? 1u : 0u;
+                  if (DUAL) {
+                    mma_f16_ts(d_tmem, aw + h * 2 * W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
+                    mma_f16_ts(d_tmem + n_tile, aw + (h * 2 + 1) * W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
+                  } else {
+                    mma_f16_ts(d_tmem, aw + h * W8_SLOT_COLS + 8 * k, dx + 2 * k, idesc, accum);
                   }
                 }
-                tc_commit(smem_u32(&bar_cempty[c]));
-                PROF_ADD(4);
               }
+              tc_commit(smem_u32(&bar_cempty[c]));
+              PROF_ADD(4);
               if (!ok) break;
               tc_commit(smem_u32(&bar_empty[s]));  // the activation tiles of the stage have been read as well
               continue;
@@ -388,24 +385,25 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const __nv_bfloat162 hs = __float2bfloat162_rn(f * 0x1p120f);
             sc[t] = *reinterpret_cast<const uint32_t*>(&hs);
           }
-#pragma unroll 1
-          for (int h = 0; h < W8_STEPS && ok; ++h) {
-            const uint32_t hit = W8_STEPS * it + h, c = hit % a.conv_slots, cph = (hit / a.conv_slots) & 1;
-            {
-              PROF_T0();
-              if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
-                report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
-                abort_flag = 1;
-                ok = false;
-                break;
-              }
-              if (r == 0 && part == 0) PROF_ADD(1);
-            }
+          const uint32_t c = it % a.conv_slots, cph = (it / a.conv_slots) & 1;
+          {
             PROF_T0();
-            tc_fence_after();
-            // this thread's 16 columns of its lane in each of the step's two sub-tiles: slot c, sub-tile t, columns
-            // part * 16 .. + 15. Sub-tile t is tile t (gate / up) at half h with a pair, else half t of the one tile.
-            const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * 2 * W8_SLOT_COLS + part * 16;
+            if (!mbar_wait(smem_u32(&bar_cempty[c]), cph ^ 1, &abort_flag, a.budget_ns)) {
+              report_status(p.status, ST_TIMEOUT_SMEM_EMPTY, blockIdx.x);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            if (r == 0 && part == 0) PROF_ADD(1);
+          }
+          PROF_T0();
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < W8_PAIRS; ++h) {
+            // this thread's 16 columns of its lane in each of the pair's two sub-tiles: slot c, pair h, sub-tile t, columns
+            // part * 16 .. + 15. Sub-tile t is tile t (gate / up) at K half h with a pair of tiles, else K half t of the one tile.
+            const uint32_t conv = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + a.conv_base + c * W8_SLOT +
+                                  h * 2 * W8_SLOT_COLS + part * 16;
             uint32_t o[2][16];
             uint4 v[2][2];
 #pragma unroll
@@ -429,19 +427,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 e4m3x4_to_scaled_bf16x4(v[t][ci].w, sct, o[t][8 * ci + 6], o[t][8 * ci + 7]);
               }
             }
-            if (pending_slot >= 0) {
-              // the previous half's stores to tensor memory have had this half's conversion to complete
+            if (h == 0 && pending_slot >= 0) {
+              // the previous stage's stores to tensor memory have had this conversion to complete
               tmem_st_wait();
               tc_fence_before();
               mbar_arrive(smem_u32(&bar_cfull[pending_slot]));
             }
 #pragma unroll
             for (int t = 0; t < 2; ++t) tmem_st16(conv + t * W8_SLOT_COLS, o[t]);
-            pending_slot = (int)c;
-#ifdef SKEIN_GEMM_TIMING
-            if (r == 0 && part == 0) { PROF_ADD(2); g_w8_prof[blockIdx.x][6] += 1; }
-#endif
           }
+          pending_slot = (int)c;
+#ifdef SKEIN_GEMM_TIMING
+          if (r == 0 && part == 0) { PROF_ADD(2); g_w8_prof[blockIdx.x][6] += 1; }
+#endif
         }
         pos = u * KB + kb1;
       }
@@ -849,9 +847,12 @@ static int plan(const SkeinGemmParams* p, KernelArgs* ka, int* grid, size_t* sme
   ka->conv_slots = 0;
   if (w8) {
     // the converted weights live in tensor memory behind the two accumulators: 512 columns in all
-    ka->conv_slots = W8_CONV_SLOTS;
+    // a slot holds one stage's converted K block: 64 columns per weight tile of the stage
+    const int slot_cols = (dual ? 2 : 1) * 2 * W8_SLOT_COLS;
     ka->conv_base = 2 * ka->acc_stride;
-    if (ka->conv_base + ka->conv_slots * 2 * W8_SLOT_COLS > 512) return -3;   // token tile too wide for this form
+    ka->conv_slots = (512 - ka->conv_base) / slot_cols;
+    if (ka->conv_slots > W8_CONV_SLOTS) ka->conv_slots = W8_CONV_SLOTS;
+    if (ka->conv_slots < 2) return -3;   // token tile too wide for this form
   }
   int st = budget / ka->stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;

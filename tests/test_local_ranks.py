@@ -31,7 +31,8 @@ def _generate(dec, prompts, tables, steps=3):
 
 
 @pytest.mark.parametrize("tp,cfg", [(2, mc.tiny_mixtral(heads=4, kv_heads=2)), (4, mc.tiny_mixtral(heads=8, kv_heads=4, inter=1024)),
-                                    (2, mc.tiny_llama())], ids=["mixtral-tp2", "mixtral-tp4", "llama-tp2"])
+                                    (8, mc.tiny_mixtral(heads=16, kv_heads=8, inter=2048)),
+                                    (2, mc.tiny_llama())], ids=["mixtral-tp2", "mixtral-tp4", "mixtral-tp8", "llama-tp2"])
 def test_tp_shards_reproduce_the_unsharded_model(tp, cfg):
     torch.manual_seed(0)
     full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=5, std=0.05)
