@@ -203,9 +203,17 @@ inline double compute_time_with_dtype(const Layer& l, const ModelMeta& meta, Dty
     // a narrower weight type moves fewer bytes but its kernel may reach a smaller share of the copy bandwidth (the e4m3
     // tiles are rescaled to bf16 on their way to the tensor cores): the measured share per weight dtype decides whether
     // the dtype map gains time or only memory
-    auto se = c.stream_efficiency.find(dtype_name(wd));
-    const double frac = (se != c.stream_efficiency.end() && se->second > 0) ? se->second : 1.0;
-    t = std::max(t, layer_stream_bytes(l, meta, wd, kvd, pl, wl) / (hb->second * frac * 1e9) * 1e6);
+    auto share = [&](Dtype d) {
+      auto se = c.stream_efficiency.find(dtype_name(d));
+      return (se != c.stream_efficiency.end() && se->second > 0) ? se->second : 1.0;
+    };
+    // the share belongs to the kernel that streams the bytes: the weight dtype's for the weights, the attention kernel's
+    // (bf16 rate) for the KV cache of an attention layer
+    double kv_bytes = 0;
+    if (l.kind == LayerKind::Attention)
+      kv_bytes = (double)dtype_bits(kvd) / 8.0 * 2.0 * l.num_kv_heads * l.head_dim * (double)wl.kv_len * wl.batch / (double)pl.tp;
+    const double w_bytes = layer_stream_bytes(l, meta, wd, kvd, pl, wl) - kv_bytes;
+    t = std::max(t, (w_bytes / share(wd) + kv_bytes / share(Dtype::Bf16)) / (hb->second * 1e9) * 1e6);
   }
   return t;
 }

@@ -119,14 +119,12 @@ def test_drift_update_is_monotonic():
 
 
 def test_compile_end_to_end_with_replan_and_latest(tmp_path):
-    # a drift budget that lets the planner pick fp8 weights somewhere, and constants under which it wants to: the e4m3
-    # kernel streaming at the same share of the copy bandwidth as the bf16 one (the shipped constants carry the measured
-    # share, under which fp8 is chosen for memory only)
+    # a drift budget that lets the planner pick fp8 weights somewhere, at a batch small enough for the step to be bound by
+    # weight streaming (there the e4m3 kernel takes less time than the bf16 one under the measured constants)
     trace = TRACE.replace('"max_accuracy_drift": 0.01', '"max_accuracy_drift": 0.02')
     tiny_mem = cluster(1).replace("device_memory_gb = 180", "device_memory_gb = 1")
-    assert "fp8_e4m3 = 0.42" in CONST
-    const = CONST.replace("fp8_e4m3 = 0.42", "fp8_e4m3 = 0.97")
-    r = compile_model(TINY, tiny_mem, trace, DRIFT, const, tmp_path, options={"force_batch": 4}, n_parity_prompts=2, seed=1)
+    const = CONST
+    r = compile_model(TINY, tiny_mem, trace, DRIFT, const, tmp_path, options={"force_batch": 2}, n_parity_prompts=2, seed=1)
     assert (tmp_path / "LATEST").is_symlink() and os.readlink(tmp_path / "LATEST") == r.artifact_dir.name
     assert (r.artifact_dir / "reference_bf16" / "plan.json").exists() and (r.artifact_dir / "parity_report.json").exists()
     rep = json.loads((r.artifact_dir / "parity_report.json").read_text())
@@ -144,7 +142,7 @@ def test_compile_end_to_end_with_replan_and_latest(tmp_path):
     assert r.report.passed, r.report.to_json()
     # enforce + impossible tolerance -> failure is raised after re-plans that push the drift table up
     strict = const.replace("fp8_e4m3 = 5.0e-3", "fp8_e4m3 = 1.0e-12")
-    r2 = compile_model(TINY, tiny_mem, trace, DRIFT, strict, tmp_path / "b", options={"force_batch": 4}, n_parity_prompts=1, seed=1, max_replans=3)
+    r2 = compile_model(TINY, tiny_mem, trace, DRIFT, strict, tmp_path / "b", options={"force_batch": 2}, n_parity_prompts=1, seed=1, max_replans=3)
     assert r2.replans >= 1 and core.DriftTable.from_toml(r2.drift_toml).num_overrides() >= 1
     assert r2.report.passed and all(d["weight"] == "bf16" for d in r2.plan["dtype_map"]["per_layer"])   # re-planned away from fp8
 
