@@ -84,6 +84,8 @@ def lib():
          [vp, i64, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_prefill", i32,
          [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
+    _sig(L, "skein_attn_decode_tc", i32,
+         [vp, i64, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_attn_prefill_tc", i32,
          [vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp])
     _sig(L, "skein_router_topk", i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp])

@@ -407,6 +407,23 @@ def pick_splits(B, Hkv, ctx_hint, sm_count=148):
     return max(1, min(sm_count // ctas, ctx_hint // 512, 16))
 
 
+def _decode_tc_ok(kv_cache, B, Hq, Hkv, D, splits, impl) -> bool:
+    """Whether the tcgen05 decode kernel (csrc/kernels/attn_decode_tc.cu) takes this launch: one split, head size 128,
+    16-token pages, at most 8 query heads per kv head. "auto" (the default) picks it when the launch has at least 1.5
+    (sequence, kv head) pairs per SM: there the kernel is bandwidth-bound and the tensor-memory form is the faster one
+    (35.6 against 37.0 us at 512 pairs, 18.5 against 19.5 at 256); with fewer pairs a CTA's chain of per-tile latencies
+    decides and the mma.sync kernel, whose four warps run independent pipelines, wins (13.2 against 15.9 us at 64 pairs).
+    SKEIN_ATTN_DECODE=tc|mma|scalar (or impl) forces a kernel."""
+    choice = impl or os.environ.get("SKEIN_ATTN_DECODE", _DECODE_DEFAULT)
+    if choice == "auto":
+        choice = "tc" if 2 * B * Hkv >= 3 * workspace().sm_count else "mma"
+    return (choice == "tc" and splits == 1 and D == 128 and kv_cache.shape[3] == 16 and kv_cache.shape[4] == 128
+            and Hq % Hkv == 0 and Hq // Hkv <= 8)
+
+
+_DECODE_DEFAULT = "auto"
+
+
 def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=None, splits=None, ctx_hint=1024,
                 impl=None):
     """q: [B, row_stride] whose first Hq*D columns are the (rotated) query heads -> [B, Hq*D].
@@ -429,7 +446,18 @@ def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=
             splits = 1
         else:
             wsf, ctr = scratch
-    impl = impl or os.environ.get("SKEIN_ATTN_DECODE", "mma")
+    if _decode_tc_ok(kv_cache, B, Hq, Hkv, D, splits, impl):
+        rc = _lib.lib().skein_attn_decode_tc(
+            q.data_ptr(), q.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), None, None, 0,
+            out.data_ptr(), ws.status.data_ptr(), B, Hq, Hkv, D, kv_cache.shape[3], block_table.stride(0), kv_cache.shape[0],
+            float(scale), _lib.stream_ptr())
+        if rc != -1:
+            _lib.check(rc, "attn_decode_tc")
+            _lib.count_launch()
+            return out
+    impl = impl or os.environ.get("SKEIN_ATTN_DECODE", _DECODE_DEFAULT)
+    if impl in ("tc", "auto"):
+        impl = "mma"
     if kv_cache.shape[3] % 16 != 0 or Hq // Hkv > 16:
         impl = "scalar"
     fn = _lib.lib().skein_attn_decode_mma if impl == "mma" else _lib.lib().skein_attn_decode
@@ -445,11 +473,11 @@ def attn_decode(q, kv_cache, block_table, seq_lens, Hq, Hkv, D, scale=None, out=
 def can_fuse_rope(kv_cache, Hq, Hkv) -> bool:
     """True when attn_decode_rope runs as one kernel (else it falls back to rope_kv_append + attn_decode)."""
     return (kv_cache.is_cuda and kv_cache.shape[3] % 16 == 0 and Hq // Hkv <= 16 and kv_cache.shape[4] == 128
-            and os.environ.get("SKEIN_ATTN_DECODE", "mma") == "mma" and os.environ.get("SKEIN_FUSE_ROPE", "1") != "0")
+            and os.environ.get("SKEIN_ATTN_DECODE", _DECODE_DEFAULT) in ("auto", "mma", "tc") and os.environ.get("SKEIN_FUSE_ROPE", "1") != "0")
 
 
 def attn_decode_rope(qkv, positions, block_table, cos_sin, kv_cache, seq_lens, Hq, Hkv, D, scale=None, out=None,
-                     splits=None, ctx_hint=1024):
+                     splits=None, ctx_hint=1024, impl=None):
     """Decode attention straight from the fused q/k/v projection: RoPE of q and k, append of the new token's k/v
     to the paged cache, attention; one launch (csrc/kernels/attn_decode_mma.cu). qkv: [B, (Hq + 2 Hkv) * D]."""
     if not can_fuse_rope(kv_cache, Hq, Hkv):
@@ -469,6 +497,15 @@ def attn_decode_rope(qkv, positions, block_table, cos_sin, kv_cache, seq_lens, H
             splits = 1
         else:
             wsf, ctr = scratch
+    if _decode_tc_ok(kv_cache, B, Hq, Hkv, D, splits, impl):
+        rc = _lib.lib().skein_attn_decode_tc(
+            qkv.data_ptr(), qkv.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
+            positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[0], out.data_ptr(), ws.status.data_ptr(), B, Hq, Hkv, D,
+            kv_cache.shape[3], block_table.stride(0), kv_cache.shape[0], float(scale), _lib.stream_ptr())
+        if rc != -1:
+            _lib.check(rc, "attn_decode_tc")
+            _lib.count_launch()
+            return out
     rc = _lib.lib().skein_attn_decode_rope_mma(
         qkv.data_ptr(), qkv.stride(0), kv_cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
         positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[0], out.data_ptr(), _lib.ptr(wsf), _lib.ptr(ctr),

@@ -38,7 +38,7 @@ _FIELDS = {
     "comm": ("SKEIN_COMM", str, ("fused", "unfused", "nccl")),
     "multimem": ("SKEIN_MULTIMEM", _bool, None),
     "profile": ("SKEIN_PROFILE", int, (0, 1, 2, 3)),
-    "attn_decode": ("SKEIN_ATTN_DECODE", str, ("mma", "scalar")),
+    "attn_decode": ("SKEIN_ATTN_DECODE", str, ("auto", "tc", "mma", "scalar")),
     "attn_splits": ("SKEIN_ATTN_SPLITS", int, None),
     "fuse_route": ("SKEIN_FUSE_ROUTE", _bool, None),
     "fuse_rope": ("SKEIN_FUSE_ROPE", _bool, None),
@@ -58,7 +58,7 @@ class RuntimeConfig:
     comm: str = "fused"            # tensor-parallel all-reduce: fused into the GEMM / reduce kernels, or a library call
     multimem: bool = False         # sum the tensor-parallel partials inside the NVSwitch (multicast-bound heap)
     profile: int = 0               # 0 off, 1 CUDA-event region timers, 2 + NVTX ranges, 3 + Chrome trace
-    attn_decode: str = "mma"       # decode attention kernel
+    attn_decode: str = "auto"      # decode attention kernel: tcgen05 / mma.sync chosen per launch, or one of them forced
     attn_splits: int = 0           # split-KV factor (0: chosen per launch)
     fuse_route: bool = True        # router inside the post-attention reduce kernel
     fuse_rope: bool = True         # RoPE + KV append inside the decode attention kernel

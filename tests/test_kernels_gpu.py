@@ -166,6 +166,51 @@ def test_attn_decode_rope_fusion_equals_separate_kernels(Hq, Hkv, splits):
     assert _rel_err(o1, o2) < 5e-3
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 2), (4, 1), (6, 2)])
+def test_attn_decode_tcgen05(Hq, Hkv):
+    """The tensor-memory decode kernel (tokens on the M side, query heads on N): ragged lengths around the 16-token page
+    and the 128-token tile, a padding row, NaN in every cache slot past a context's end."""
+    torch.manual_seed(15)
+    B, D, ps = 10, 128, 16
+    lens = [1, 15, 16, 17, 127, 128, 129, 640, 700, 0]
+    kv, bt, _ = _make_cache(B, lens, Hkv, D, ps)
+    for b, l in enumerate(lens):
+        for blk in range(l // ps, bt.shape[1]):
+            lo = l % ps if blk == l // ps else 0
+            kv[int(bt[b, blk]), :, :, lo:, :] = float("nan")
+    q = torch.randn(B, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    o = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=1, impl="tc")
+    o2 = ops.attn_decode(q, kv, bt, sl, Hq, Hkv, D, splits=1, impl="tc")
+    _check_status()
+    assert torch.isfinite(o.float()).all() and torch.equal(o, o2)
+    clean = torch.nan_to_num(kv.float(), nan=0.0).bfloat16()
+    assert _rel_err(o, ref.attn_decode(q, clean, bt, sl, Hq, Hkv, D)) < 1e-2
+    assert _rel_err(o, ops.attn_decode(q, clean, bt, sl, Hq, Hkv, D, splits=1, impl="mma")) < 5e-3
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (4, 1), (16, 2)])
+def test_attn_decode_tcgen05_rope_fusion_equals_separate_kernels(Hq, Hkv):
+    """RoPE + KV append + attention in the tensor-memory kernel against rope_kv_append followed by the mma.sync kernel:
+    same cache contents afterwards, same output."""
+    torch.manual_seed(19)
+    B, D, ps = 8, 128, 16
+    lens = [1, 16, 17, 130, 640, 33, 0, 128]
+    kv, bt, _ = _make_cache(B, [l + 1 for l in lens], Hkv, D, ps)
+    kv2 = kv.clone()
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qkv2 = qkv.clone()
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)     # -1 for the padding row
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tab = ref.rope_cos_sin_table(1024, D, 1e6, DEV)
+    o1 = ops.attn_decode_rope(qkv, pos, bt, tab, kv, sl, Hq, Hkv, D, splits=1, impl="tc")
+    ops.rope_kv_append(qkv2, pos, None, bt, tab, kv2, Hq, Hkv, D)
+    o2 = ops.attn_decode(qkv2, kv2, bt, sl, Hq, Hkv, D, splits=1, impl="mma")
+    _check_status()
+    assert _rel_err(kv, kv2) < 1e-3
+    assert _rel_err(o1, o2) < 5e-3
+
+
 @pytest.mark.parametrize("impl", ["tc", "mma"])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
 def test_attn_prefill(Hq, Hkv, impl, monkeypatch):

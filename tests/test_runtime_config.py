@@ -15,7 +15,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 def test_defaults_are_the_fast_path_and_round_trip_through_the_environment():
     d = RuntimeConfig()
-    assert (d.comm, d.attn_decode, d.fuse_route, d.fuse_rope, d.pack_moe, d.pdl, d.multimem) == ("fused", "mma", True, True, True, False, False)
+    assert (d.comm, d.attn_decode, d.fuse_route, d.fuse_rope, d.pack_moe, d.pdl, d.multimem) == ("fused", "auto", True, True, True, False, False)
     env = d.to_env()
     assert env["SKEIN_COMM"] == "fused" and env["SKEIN_PDL"] == "0" and "SKEIN_TUNE_CACHE" not in env and "SKEIN_ATTN_SPLITS" not in env
     assert RuntimeConfig.from_env(env) == d
