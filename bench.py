@@ -610,9 +610,11 @@ def main():
     per_chunk = max(1, 8192 // P)
     barrier()
     first_tokens = []
+    t_pf = time.perf_counter()
     for c0 in range(0, B, per_chunk):
         first_tokens.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
     torch.cuda.synchronize()
+    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)     # whole batch, first (cold) pass, tokens read back per chunk
     check_all("prefill")
 
     K, W, R = args.steps, max(args.warmup, 3), max(1, args.repeats)
@@ -776,6 +778,7 @@ def main():
                        "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16",
                        "repeats": R, "ms_per_k_steps_all_repeats": [round(x, 3) for x in all_ms]},
             "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world),
+            "prefill_ms": round(prefill_ms, 1), "prefill_tokens_per_s": round(B * P / prefill_ms * 1e3, 1),
             "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2),
             "tpot_p99_ms": tpot_p99,
             "e2e": e2e, "burst": burst, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,
