@@ -180,6 +180,27 @@ class PipelineStage:
         dist.broadcast(tokens, src=self.pp_ranks[-1], group=self.pp_group)
         return tokens, logits
 
+    def forward_prefill_micro(self, items):
+        """Prefill of several micro-chunks (whole sequences each) through the pipeline: `items` is a list of
+        (BatchInputs, SamplingInputs or None), the same on every stage. A stage starts on chunk i + 1 as soon as its send of
+        chunk i is under way, so the stages overlap as they do in decode; the first tokens of all chunks travel back in one
+        broadcast at the end. Returns the tokens of all chunks, in order."""
+        outs, keys = [], []
+        for i, (inp, smp) in enumerate(items):
+            key = ("prefill-micro", i)
+            self._graphs.pop(key, None)          # shapes differ from call to call: nothing is kept
+            keys.append(key)
+            out, _ = self._run_stage(inp, smp, key)
+            outs.append(out)
+        for key in keys:
+            sg = self._graphs.pop(key, None)
+            if sg is not None and sg.pending_send is not None:
+                sg.pending_send.wait()
+        n_out = sum(self._n_out_rows(inp) for inp, _ in items)
+        tokens = torch.cat(outs) if self.last else torch.empty(n_out, dtype=torch.int32, device=self.device)
+        dist.broadcast(tokens, src=self.pp_ranks[-1], group=self.pp_group)
+        return tokens
+
     def idle_fraction(self, wall_ms: float) -> float | None:
         """1 - (time this stage spent computing) / wall time, from the CUDA events recorded while `time_stages` was set."""
         if not self.stage_busy_events or wall_ms <= 0:

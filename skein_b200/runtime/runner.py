@@ -205,10 +205,8 @@ class ModelRunner:
             self._decode_body(bk, True)
 
     # ---- prefill ----------------------------------------------------------------------------------
-    def prefill(self, seqs, want_logits: bool = False, sampling=None):
-        """seqs: list of (new_token_ids, block_table_row, cached_len). Runs one eager chunk holding every new
-        token of every listed sequence. Returns the next token of every sequence (host list) [and logits]; greedy
-        unless `sampling` gives (temperature, top_k, top_p, seed) per sequence."""
+    def _prefill_inputs(self, seqs, sampling):
+        """BatchInputs (and SamplingInputs) of one eager chunk holding every new token of every listed sequence."""
         dev = self.device
         toks, pos, sot, qs, ql, kl, rows = [], [], [], [], [], [], []
         S = len(seqs)
@@ -229,6 +227,30 @@ class ModelRunner:
                                  torch.tensor([s[2] for s in sampling], dtype=torch.float32, device=dev),
                                  torch.tensor([s[3] for s in sampling], dtype=torch.int64, device=dev),
                                  i32([n - 1 for n in kl]))
+        return inp, smp
+
+    def prefill(self, seqs, want_logits: bool = False, sampling=None):
+        """seqs: list of (new_token_ids, block_table_row, cached_len). Runs one eager chunk holding every new
+        token of every listed sequence. Returns the next token of every sequence (host list) [and logits]; greedy
+        unless `sampling` gives (temperature, top_k, top_p, seed) per sequence. Behind a pipeline of several stages the
+        chunk is cut, at sequence boundaries, into one micro-chunk per stage so that the stages overlap."""
+        n_stages = getattr(self.dec, "n_stages", 1)
+        if n_stages > 1 and len(seqs) >= 2 and not want_logits and hasattr(self.dec, "forward_prefill_micro"):
+            M = min(len(seqs), max(2, getattr(self.dec, "micro_batches", n_stages)))
+            total = sum(len(s[0]) for s in seqs)
+            groups, cur, acc = [], [], 0
+            for i, sq in enumerate(seqs):        # contiguous groups of about total / M tokens, none empty
+                cur.append(i)
+                acc += len(sq[0])
+                left = len(seqs) - i - 1
+                if len(groups) < M - 1 and (acc >= total * (len(groups) + 1) / M or left <= M - 1 - len(groups)) and left >= 1:
+                    groups.append(cur)
+                    cur = []
+            groups.append(cur)
+            items = [self._prefill_inputs([seqs[i] for i in g], None if sampling is None else [sampling[i] for i in g])
+                     for g in groups if g]
+            return self.dec.forward_prefill_micro(items).cpu().tolist()
+        inp, smp = self._prefill_inputs(seqs, sampling)
         tok, lg = self.dec.forward(inp, sampling=smp)
         out = tok.cpu().tolist()
         return (out, lg) if want_logits else out
