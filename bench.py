@@ -363,8 +363,18 @@ def run_pipeline(args, emit_json):
     for c0 in range(0, B, per_chunk):
         first_tokens.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
     torch.cuda.synchronize()
-    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)
+    prefill_cold_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)
     check_all("prefill")
+    # the same prefill once more: the first pass also pays for one-time set-up (communicator connections between the
+    # stages, kernel attributes, allocator growth)
+    barrier()
+    t_pf = time.perf_counter()
+    again = []
+    for c0 in range(0, B, per_chunk):
+        again.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
+    torch.cuda.synchronize()
+    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)
+    prefill_repeatable = again == first_tokens
 
     # ---- steady-state pipelined decode: pp micro-batches in flight ----
     M = npp
@@ -473,7 +483,7 @@ def run_pipeline(args, emit_json):
                        "gen_len": Gn, "parallelism": f"tp{tp}xpp{npp}", "kv": "paged, block 16", "micro_batches": M,
                        "l2": "inputs (weights) larger than L2, no flush", "cuda_graph": "per stage and micro-batch",
                        "weights": fp8_note, "repeats": R},
-            "prefill_ms": round(prefill_ms, 1), "stage_idle_fraction_per_rank": [None if x is None else round(x, 3) for x in idles],
+            "prefill_ms": round(prefill_ms, 1), "prefill_first_pass_ms": round(prefill_cold_ms, 1), "prefill_repeatable": prefill_repeatable, "stage_idle_fraction_per_rank": [None if x is None else round(x, 3) for x in idles],
             "e2e": e2e, "gpu_launches": (launches_per_step or 0) * K, "kernels_per_step_on_rank0": launches_per_step, "impl": "ours"})
     dist.barrier()
     dist.destroy_process_group()
@@ -614,8 +624,16 @@ def main():
     for c0 in range(0, B, per_chunk):
         first_tokens.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
     torch.cuda.synchronize()
-    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)     # whole batch, first (cold) pass, tokens read back per chunk
+    prefill_cold_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)   # first pass: also pays for one-time set-up
     check_all("prefill")
+    barrier()
+    t_pf = time.perf_counter()
+    again = []
+    for c0 in range(0, B, per_chunk):
+        again.extend(runner.prefill([(prompts[s], tables[s], 0) for s in range(c0, min(B, c0 + per_chunk))]))
+    torch.cuda.synchronize()
+    prefill_ms = max_over_ranks((time.perf_counter() - t_pf) * 1e3)        # whole batch, tokens read back per chunk
+    prefill_repeatable = again == first_tokens
 
     K, W, R = args.steps, max(args.warmup, 3), max(1, args.repeats)
     if K + W > Gn - 1:
@@ -778,7 +796,8 @@ def main():
                        "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16",
                        "repeats": R, "ms_per_k_steps_all_repeats": [round(x, 3) for x in all_ms]},
             "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world),
-            "prefill_ms": round(prefill_ms, 1), "prefill_tokens_per_s": round(B * P / prefill_ms * 1e3, 1),
+            "prefill_ms": round(prefill_ms, 1), "prefill_first_pass_ms": round(prefill_cold_ms, 1), "prefill_repeatable": prefill_repeatable,
+            "prefill_tokens_per_s": round(B * P / prefill_ms * 1e3, 1),
             "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2),
             "tpot_p99_ms": tpot_p99,
             "e2e": e2e, "burst": burst, "gpu_launches": launches_per_step * K, "kernels_per_step": launches_per_step,

@@ -22,6 +22,8 @@ and are skipped by the kernels.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -235,7 +237,8 @@ class ModelRunner:
         unless `sampling` gives (temperature, top_k, top_p, seed) per sequence. Behind a pipeline of several stages the
         chunk is cut, at sequence boundaries, into one micro-chunk per stage so that the stages overlap."""
         n_stages = getattr(self.dec, "n_stages", 1)
-        if n_stages > 1 and len(seqs) >= 2 and not want_logits and hasattr(self.dec, "forward_prefill_micro"):
+        if (n_stages > 1 and len(seqs) >= 2 and not want_logits and hasattr(self.dec, "forward_prefill_micro")
+                and os.environ.get("SKEIN_PP_PREFILL_MICRO", "1") != "0"):
             M = min(len(seqs), max(2, getattr(self.dec, "micro_batches", n_stages)))
             total = sum(len(s[0]) for s in seqs)
             groups, cur, acc = [], [], 0
