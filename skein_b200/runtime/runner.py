@@ -239,8 +239,10 @@ class ModelRunner:
         n_stages = getattr(self.dec, "n_stages", 1)
         if (n_stages > 1 and len(seqs) >= 2 and not want_logits and hasattr(self.dec, "forward_prefill_micro")
                 and os.environ.get("SKEIN_PP_PREFILL_MICRO", "1") != "0"):
-            M = min(len(seqs), max(2, getattr(self.dec, "micro_batches", n_stages)))
             total = sum(len(s[0]) for s in seqs)
+            # at least one micro-chunk per stage; up to two per stage while a micro-chunk keeps 2048 tokens (fill and drain
+            # of the pipeline cost one micro-chunk's time per call, and the projections want a few thousand tokens)
+            M = min(len(seqs), max(n_stages, min(2 * n_stages, total // 2048)))
             groups, cur, acc = [], [], 0
             for i, sq in enumerate(seqs):        # contiguous groups of about total / M tokens, none empty
                 cur.append(i)
