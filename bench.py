@@ -219,7 +219,7 @@ class ClockSampler:
 
 
 def replay_burst(args, cfg, dec, runner, make_control, world, rank, B, P, Gn, use_graphs, max_over_ranks, barrier):
-    """Replays a synthetic burst trace (BASELINE config 4's arrival process) through the serving engine on all ranks in
+    """Replays a synthetic burst trace (the arrival process of the Mixtral-8x22B serving configuration this build is measured on) through the serving engine on all ranks in
     lock step: rank 0's clock is announced through the control page every step, every rank submits the requests that
     have arrived by then (the trace is generated from a seed, identically everywhere) and steps its engine. Chunked
     prefill interleaves with decode (at most 2048 prompt tokens per step while sequences decode), at most B sequences
@@ -289,7 +289,7 @@ def replay_burst(args, cfg, dec, runner, make_control, world, rank, B, P, Gn, us
 
 
 def run_pipeline(args, emit_json):
-    """--pp > 1: tensor parallel inside each of `pp` stages (BASELINE config 3: Llama-3-70B, TP=4 x PP=2). The device-
+    """--pp > 1: tensor parallel inside each of `pp` stages (the Llama-3-70B configuration: TP=4 x PP=2). The device-
     timed loop is the steady-state pipelined decode (pp micro-batches in flight across steps, per-stage CUDA graphs,
     asynchronous point-to-point between stages); the end-to-end number runs the serving engine over the pipeline."""
     import datetime
