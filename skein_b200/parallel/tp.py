@@ -75,7 +75,29 @@ class TPComm:
         # kernels sum the ranks' partials with one multimem load. Off by default: a rank that dies while bound
         # faults its peers, and the plain peer loads are what the failure-handling tests exercise.
         self.multimem = (os.environ.get("SKEIN_MULTIMEM", "0") == "1") if multimem is None else bool(multimem)
-        self.heap = SymmetricHeap(group, device, heap_bytes, multicast=self.multimem and self.mode in ("fused", "unfused"))
+        want_mc = self.multimem and self.mode in ("fused", "unfused")
+        self.heap = None
+        if want_mc:
+            # a group without NVLink multicast (or a torch build without the symmetric-memory allocator) falls back to the
+            # plain heap, on every rank or on none
+            ok, err = 1, None
+            try:
+                self.heap = SymmetricHeap(group, device, heap_bytes, multicast=True)
+            except Exception as e:      # noqa: BLE001
+                ok, err = 0, e
+            agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            if int(agreed[0]) == 0:
+                if self.heap is not None:
+                    self.heap.close()
+                    self.heap = None
+                if self.rank == 0:
+                    import sys
+                    print(f"skein: no in-switch reduction for this group ({err or 'a peer could not bind its heap'}); "
+                          "using peer loads", file=sys.stderr)
+                self.multimem = False
+        if self.heap is None:
+            self.heap = SymmetricHeap(group, device, heap_bytes, multicast=False)
         h = self.heap
         self.buf_off = [h.alloc(buf_bytes) for _ in range(2)]
         self.flag_off = [h.alloc(256) for _ in range(2)]
