@@ -169,10 +169,13 @@ def rewrite_toml_values(text: str, updates: dict) -> str:
 
 
 def write_cost_constants(text: str, efficiencies: dict, collective_eff: dict | None = None, hbm_gbps: dict | None = None,
-                         peak_tflops: dict | None = None, launch_us: float | None = None) -> str:
+                         peak_tflops: dict | None = None, launch_us: float | None = None,
+                         stream_efficiency: dict | None = None) -> str:
     """efficiencies: {(op_kind, dtype): fraction}; collective_eff: {name: fraction}; hbm_gbps: {device_kind: GB/s};
-    peak_tflops: {(device_kind, dtype): TFLOP/s}."""
+    peak_tflops: {(device_kind, dtype): TFLOP/s}; stream_efficiency: {weight dtype: share of hbm_gbps}."""
     upd = {(f"efficiency.{op}", dt): v for (op, dt), v in efficiencies.items()}
+    for k, v in (stream_efficiency or {}).items():
+        upd[("stream_efficiency", k)] = v
     for k, v in (collective_eff or {}).items():
         upd[("collective_efficiency", k)] = v
     for k, v in (hbm_gbps or {}).items():
@@ -246,6 +249,41 @@ def measure_kernel(sample: KernelSample, peak_tflops: float, hbm_gbps: float):
         us = time_cuda(lambda: ops.attn_decode(q, kv, bt, sl, hq, hkv, d, ctx_hint=ctx), reps)
         return us, kv.numel() * 2 / (hbm_gbps * 1e9) * 1e6
     return None
+
+
+def measure_stream_efficiency(hbm_gbps: float, tokens: int = 64, hidden: int = 4096, inter: int = 14336, experts: int = 8,
+                              repeats: int = 10) -> dict:
+    """Share of the copy bandwidth the weight-streaming expert GEMMs reach at decode size, per weight dtype the runtime has
+    a kernel for: {"bf16": f, "fp8_e4m3": f}. Bytes-weighted over the gate/up and the down projection (the weights of
+    `experts` experts of a Mixtral-sized block, `tokens` tokens routed top-2)."""
+    import torch
+
+    from . import ops
+    from .ops import fp8
+    per = max(1, tokens * 2 // experts)
+    rows = experts * per
+    cnt = torch.full((experts,), per, dtype=torch.int32, device="cuda")
+    off = torch.zeros(experts + 1, dtype=torch.int32, device="cuda")
+    off[1:] = torch.cumsum(cnt, 0)
+    out = {}
+    for dt in ("bf16", "fp8_e4m3"):
+        t_us, n_bytes = 0.0, 0
+        for swiglu, (f_out, k_in) in ((True, (inter, hidden)), (False, (hidden, inter))):
+            xs = torch.randn(rows, k_in, device="cuda").bfloat16()
+            w = (torch.randn(experts, 2 * f_out if swiglu else f_out, k_in, device="cuda") * 0.02).bfloat16()
+            y = torch.empty(rows, f_out, dtype=torch.bfloat16, device="cuda")
+            if dt == "bf16":
+                fn = lambda: ops.grouped_linear(xs, w, cnt, off, swiglu=swiglu, out=y)
+                nb = w.numel() * 2
+            else:
+                wq = fp8.quantize_weight(w)
+                del w
+                fn = lambda: fp8.grouped_linear_a16(xs, wq, cnt, off, swiglu=swiglu, out=y)
+                nb = wq.nbytes()
+            t_us += time_cuda(fn, repeats)
+            n_bytes += nb
+        out[dt] = round(min(1.0, n_bytes / (t_us * 1e-6) / (hbm_gbps * 1e9)), 3)
+    return out
 
 
 def calibrate_kernels(corpus: Corpus, peak_tflops: float, hbm_gbps: float) -> dict:

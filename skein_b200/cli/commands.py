@@ -149,7 +149,9 @@ def cmd_calibrate(args, emit) -> int:
     eff, drift = {}, {}
     if torch.cuda.is_available():
         eff = cal.calibrate_kernels(corpus, consts["peak_tflops"][args.hardware]["bf16"], consts.get("hbm_gbps", {}).get(args.hardware, 6552.0))
-        Path(args.out_cost).write_text(cal.write_cost_constants(cost_text, eff))
+        hbm = consts.get("hbm_gbps", {}).get(args.hardware, 6552.0)
+        stream = cal.measure_stream_efficiency(hbm) if "stream_efficiency" in consts else None
+        Path(args.out_cost).write_text(cal.write_cost_constants(cost_text, eff, stream_efficiency=stream))
     if args.candidate_artifact:
         from ..compile import parity
         from ..compile.artifact import Artifact

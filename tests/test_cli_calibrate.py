@@ -220,6 +220,10 @@ def test_cost_writer_is_byte_stable_and_preserves_unmeasured_entries():
     assert len(changed) == 4 and len(text.split("\n")) == len(new.split("\n"))
     assert "bf16     = 0.91" in new and "ring_allreduce = 0.8" in new and "b200      = 6600.0" in new
     assert "fp8_e4m3 = 0.76" in new                       # unmeasured entry untouched
+    # the measured streaming share per weight dtype is rewritten in place as well
+    st = cal.write_cost_constants(text, {}, stream_efficiency={"bf16": 0.99, "fp8_e4m3": 0.66})
+    assert "[stream_efficiency]\nbf16     = 0.99" in st and "fp8_e4m3 = 0.66" in st and "int8     = 0.6" in st
+    assert len(st.split("\n")) == len(text.split("\n"))
     assert cal.write_cost_constants(new, {("gemm", "bf16"): 0.91}) == new
     # comments after values survive; a new key lands inside its section
     t2 = cal.rewrite_toml_values("[a]\nx = 1.0   # keep me\n[b]\ny = 2.0\n", {("a", "x"): 3.5, ("a", "z"): 7.0})
