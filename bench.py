@@ -56,6 +56,7 @@ def parse():
     ap.add_argument("--pp", type=int, default=1, help="pipeline stages (tensor parallel = gpus / pp inside every stage)")
     ap.add_argument("--fp8-blocks", default="", help="'a:b' = blocks a..b-1 (of the whole model) in block-scaled fp8, all four projections")
     ap.add_argument("--fp8-experts", action="store_true", help="block-scaled e4m3 expert / FFN weights (marks dtype)")
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk (device-timed prefill and the engine)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--burst", type=int, default=0,
                     help="also replay a synthetic burst trace of this many requests through the serving engine (on/off Poisson "
@@ -628,8 +629,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
-    # ---- prefill (chunks of up to 8192 tokens) ---------------------------------------------------------
-    per_chunk = max(1, 8192 // P)
+    # ---- prefill (chunks of up to --prefill-chunk tokens) ----------------------------------------------
+    per_chunk = max(1, args.prefill_chunk // P)
     barrier()
     first_tokens = []
     t_pf = time.perf_counter()
@@ -715,10 +716,12 @@ def main():
     e2e, ttft_p50, tpot_p99 = None, None, None
     if not args.no_e2e:
         ecfg = EngineConfig(max_batch=B, tpot_ms=1e9, ttft_ms=1e9, use_graphs=use_graphs, prefix_cache=False,
-                            max_prefill_tokens=8192, interleave_prefill_tokens=0)
+                            max_prefill_tokens=args.prefill_chunk, interleave_prefill_tokens=0)
         for kv in dec.kv:
             kv.zero_()
         ctl = make_control()
+        if use_graphs:
+            runner.capture_buckets(B)      # as the server does while it starts: no request pays for a graph capture
         e2e_vals, step_ms = [], []
         parts = {"announce": 0.0, "engine_step": 0.0, "agree": 0.0, "n": 0}
         for r in range(min(R, 3)):

@@ -70,6 +70,7 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
                         # stage-to-stage NCCL p2p and library collectives are launched eagerly, never captured
                         use_graphs=(device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused
                                     and pp_info is None and not getattr(args, "no_cuda_graphs", False)))
+    ecfg.warm_graphs = ecfg.use_graphs      # every batch bucket is captured while the server starts, not under load
     if args.workload:
         from .. import core
         text = open(args.workload).read()

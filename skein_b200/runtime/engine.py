@@ -46,6 +46,7 @@ class EngineConfig:
     prefix_cache: bool = True
     eos_token: int = -1
     use_graphs: bool = True
+    warm_graphs: bool = False          # capture the decode graph of every batch bucket up to max_batch at start-up
     drift_baseline: tuple = ()         # prompt lengths the plan was extracted for (workload drift monitor)
     drift_threshold_kl: float = 0.05
 
@@ -92,6 +93,8 @@ class Engine:
             interleave_prefill_tokens=c.interleave_prefill_tokens)
         self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
         self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
+        if c.warm_graphs:
+            self.runner.capture_buckets(c.max_batch)
         self.metrics = metrics or core.MetricsRegistry()
         self.clock = clock or (lambda: int(time.monotonic() * 1000))
         self._next_id = 1

@@ -137,6 +137,25 @@ class ModelRunner:
         bk.graphs[key] = g
         return g
 
+    def capture_buckets(self, max_batch: int, sampling: bool = False) -> int:
+        """Captures the decode step of every batch bucket up to `max_batch` ahead of time (a server does this while it
+        starts, so that no request pays for a capture: a first-seen bucket otherwise costs an eager warm-up step plus the
+        capture in the middle of serving). Padding rows only: nothing is read from or written to the cache.
+        Returns the number of graphs captured."""
+        if not self.use_graphs:
+            return 0
+        n = 0
+        for b in BUCKETS:
+            bk = self.bucket(b)
+            if (False, sampling) not in bk.graphs:
+                self.load_decode_inputs(bk, [], [], [], [])
+                bk.dev_in.copy_(bk.host_in)
+                self._ensure_graph(bk, False, sampling)
+                n += 1
+            if b >= max_batch:
+                break
+        return n
+
     def load_decode_inputs(self, bk: _Bucket, tokens, positions, seq_lens, block_tables, sampling=None):
         """Fill the pinned staging buffer from host lists (rows beyond len(tokens) are padding). `sampling` is a
         list of (temperature, top_k, top_p, seed) per row, or None for an all-greedy step."""
