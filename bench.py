@@ -63,6 +63,9 @@ def parse():
                          "arrivals 50 / 2 per second every 10 s, log-normal prompts of median 600 capped at --prompt, outputs "
                          "uniform 32 .. --gen): adds the key 'burst' (TTFT / TPOT under load)")
     ap.add_argument("--burst-time-scale", type=float, default=1.0, help="trace seconds per wall second")
+    ap.add_argument("--burst-only", action="store_true",
+                    help="run only the burst replay (after the multi-rank self-check): --batch is the number of sequences "
+                         "served at a time, --prompt / --gen cap the trace's prompt and output lengths and size the KV pool")
     ap.add_argument("--replicated-attention", action="store_true",
                     help="expert parallelism: every rank runs attention for all sequences (the comparison arm) instead of "
                          "each rank attending over its own slice with token dispatch between the ranks")
@@ -628,6 +631,31 @@ def main():
         t = torch.tensor([x], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
+
+    if args.burst_only:
+        if args.burst <= 0:
+            raise SystemExit("--burst-only needs --burst N")
+
+        def make_control_():
+            if world > 1:
+                return SharedControl(f"/dev/shm/skein_bench_ctl_{os.environ.get('MASTER_PORT', '0')}", rank, world, control_group, wait_s=120)
+            return LocalControl()
+        if use_graphs:
+            runner.capture_buckets(B)
+        burst = replay_burst(args, cfg, dec, runner, make_control_, world, rank, B, P, Gn, use_graphs, max_over_ranks, barrier)
+        check_all("the burst replay")
+        if rank == 0:
+            emit_json({"metric": args.model.replace("-", "_") + "_burst_trace_tokens_per_s", "value": burst["tokens_per_s"],
+                       "unit": "tokens/s", "n_gpus": world, "higher_is_better": True, "dtype": "bf16" if not args.fp8_experts else
+                       "bf16 activations, fp8 expert weights", "data": "synthetic (random-init weights N(0,0.02), synthetic burst trace)",
+                       "config": {"model": cfg.name, "parallelism": f"tp{tp}" + (f"xep{ep}" if ep > 1 else ""), "max_concurrent": B,
+                                  "cuda_graph": use_graphs, "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16"},
+                       "burst": burst, "selfcheck": "single rank" if world == 1 else (selfcheck or {}).get("result", "skipped"),
+                       "impl": "ours"})
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---- prefill (chunks of up to --prefill-chunk tokens) ----------------------------------------------
     per_chunk = max(1, args.prefill_chunk // P)
