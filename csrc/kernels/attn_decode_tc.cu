@@ -46,7 +46,7 @@ constexpr int DT_OFF_NEW = DT_OFF_ST + DT_GP * DT_BN * 4;       // rotated k row
 constexpr int DT_OFF_STATS = DT_OFF_NEW + 512;                  // m[8], l[8], alpha[8] fp32
 constexpr int DT_OFF_BARS = DT_OFF_STATS + 128;                 // mbarriers, tensor-memory slot, abort flags
 constexpr int DT_SMEM = DT_OFF_BARS + 128 + 1024 /* alignment slack */;
-constexpr int DT_TMEM_COLS = 32;
+constexpr int DT_TMEM_COLS = 64;     // two S^T buffers of 16 columns, O^T at 32
 constexpr uint64_t DT_BUDGET_NS = 4000000000ull;
 
 struct AttnDecodeTcParams {
@@ -107,14 +107,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
   float* l_s = m_s + DT_GP;
   float* alpha_s = l_s + DT_GP;
   const uint32_t bars = base + DT_OFF_BARS;
-  const uint32_t bar_full = bars, bar_empty = bars + 24, bar_sfull = bars + 48, bar_pfull = bars + 56, bar_odone = bars + 64,
-                 bar_qready = bars + 72, bar_kpatch = bars + 80;
+  const uint32_t bar_full = bars, bar_empty = bars + 24, bar_sfull = bars + 48 /* S^T buffer 0 */, bar_pfull = bars + 56,
+                 bar_odone = bars + 64, bar_qready = bars + 72, bar_kpatch = bars + 80;
+  const uint32_t bar_sfull1 = bars + 88;    // S^T buffer 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bp + DT_OFF_BARS + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bp + DT_OFF_BARS + 104);    // [1]: never set
 
   if (tid == 0) {
     for (int i = 0; i < DT_SLOTS; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-    mbar_init(bar_sfull, 1); mbar_init(bar_pfull, 128); mbar_init(bar_odone, 1);
+    mbar_init(bar_sfull, 1); mbar_init(bar_sfull1, 1); mbar_init(bar_pfull, 128); mbar_init(bar_odone, 1);
     mbar_init(bar_qready, 128); mbar_init(bar_kpatch, 128);
     abort_flag[0] = 0; abort_flag[1] = 0;
     fence_mbar_init();
@@ -127,7 +128,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tm_s = tmem, tm_o = tmem + 16;
+  const uint32_t tm_s = tmem, tm_o = tmem + 32;      // S^T of tile j at tm_s + 16 * (j & 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: K_0, V_0, K_1, V_1, ... through the ring
@@ -170,18 +171,30 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
       const uint32_t idesc_s = umma_idesc(1, 1, DT_BN, 16);
       const uint32_t idesc_o = umma_idesc(1, 1, DT_D, 16) | (1u << 15);        // A operand (V) MN-major
       bool ok = mbar_wait(bar_qready, 0, abort_flag, DT_BUDGET_NS);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int itk = 2 * j, itv = 2 * j + 1;
-        const uint32_t ks = base + (itk % DT_SLOTS) * DT_TILE, vs = base + (itv % DT_SLOTS) * DT_TILE;
-        if (!mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
-        if (pos >= 0 && j == n_tiles - 1 && !mbar_wait(bar_kpatch, 0, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
+      // S^T of tile j + 1 is issued before the wait for the softmax of tile j (two S^T buffers), so the scores of the next
+      // tile are ready when the compute warps come for them
+      auto issue_s = [&](int j) -> bool {
+        const int itk = 2 * j;
+        const uint32_t ks = base + (itk % DT_SLOTS) * DT_TILE;
+        if (!mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) return false;
+        if (pos >= 0 && j == n_tiles - 1 && !mbar_wait(bar_kpatch, 0, abort_flag, DT_BUDGET_NS)) return false;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < DT_D / 16; ++k)
-          mma_f16(tm_s, umma_desc_sw128(ks + (k >> 2) * DT_HALF + (k & 3) * 32),
+          mma_f16(tm_s + 16 * (j & 1), umma_desc_sw128(ks + (k >> 2) * DT_HALF + (k & 3) * 32),
                   umma_desc_sw128(q_s + (k >> 2) * DT_QP_HALF + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
         tc_commit(bar_empty + 8 * (itk % DT_SLOTS));
-        tc_commit(bar_sfull);
+        tc_commit((j & 1) ? bar_sfull1 : bar_sfull);
+        return true;
+      };
+      ok = ok && issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int itv = 2 * j + 1;
+        const uint32_t vs = base + (itv % DT_SLOTS) * DT_TILE;
+        // (the last tile of a step with RoPE fused waits for the patch of its K row, which the compute warps make after
+        // their work on tile j: its scores are issued behind O^T of tile j instead of ahead of it)
+        const bool ahead = j + 1 < n_tiles && !(pos >= 0 && j + 1 == n_tiles - 1);
+        if (ahead && !issue_s(j + 1)) { ok = false; break; }
         if (!mbar_wait(bar_pfull, j & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
         if (!mbar_wait(bar_full + 8 * (itv % DT_SLOTS), (itv / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
         tc_fence_after();
@@ -192,6 +205,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
                   idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(bar_empty + 8 * (itv % DT_SLOTS));
         tc_commit(bar_odone);
+        if (j + 1 < n_tiles && !ahead && !issue_s(j + 1)) { ok = false; break; }
       }
       if (!ok && abort_flag[0] == 0) { abort_flag[0] = 1; report_status(p.status, ST_TIMEOUT_SMEM_FULL, 21); }
     }
@@ -257,24 +271,27 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
       dt_bar_compute();
     }
     bool ok = true;
+    // the new token's K row goes into the LAST K tile once TMA has landed it (row pos - the tile's first token, 128-byte
+    // swizzle); the MMA warp issues that tile's scores only after this
+    auto patch_k = [&]() -> bool {
+      const int itk = 2 * (n_tiles - 1);
+      if (!mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) return false;
+      const uint32_t ks = base + (itk % DT_SLOTS) * DT_TILE;
+      const uint16_t kvv = reinterpret_cast<const uint16_t*>(new_kv)[ct];
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(ks + dt_tile_off(pos - (n_tiles - 1) * DT_BN, ct)), "h"(kvv) : "memory");
+      dt_fence_async_smem();
+      mbar_arrive(bar_kpatch);
+      return true;
+    };
     for (int j = 0; j < n_tiles; ++j) {
       const int n0 = j * DT_BN;
       const bool last = j == n_tiles - 1;
-      if (last && pos >= 0) {
-        // patch the new token's K row into the last K tile once TMA has landed it (row pos - n0, 128-byte swizzle)
-        const int itk = 2 * j;
-        if (!mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
-        const uint32_t ks = base + (itk % DT_SLOTS) * DT_TILE;
-        const uint16_t kvv = reinterpret_cast<const uint16_t*>(new_kv)[ct];
-        asm volatile("st.shared.u16 [%0], %1;" ::"r"(ks + dt_tile_off(pos - n0, ct)), "h"(kvv) : "memory");
-        dt_fence_async_smem();
-        mbar_arrive(bar_kpatch);
-      }
-      if (!mbar_wait(bar_sfull, j & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
+      if (pos >= 0 && n_tiles == 1 && !patch_k()) { ok = false; break; }
+      if (!mbar_wait((j & 1) ? bar_sfull1 : bar_sfull, (j >> 1) & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
       tc_fence_after();
       {
         uint32_t sv[16];
-        tmem_ld16(tm_s + lane_addr, sv);
+        tmem_ld16(tm_s + 16 * (j & 1) + lane_addr, sv);
         tmem_ld_wait();
         const bool vis = n0 + row < len;
 #pragma unroll
@@ -282,6 +299,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
       }
       dt_bar_compute();
       // each warp owns heads cw and cw + 4: a lane holds four consecutive tokens of the row
+      uint32_t pk[DT_GP / 4][2];
 #pragma unroll
       for (int i = 0; i < DT_GP / 4; ++i) {
         const int g = cw + 4 * i;
@@ -300,10 +318,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
         float sum = (f01.x + f01.y) + (f23.x + f23.y);        // over the rounded values, the ones the tensor cores multiply
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        // tokens 4 * lane .. + 3 of row g: half (lane >> 4), 16-byte chunk ((lane & 15) >> 1), upper or lower 8 bytes
-        const uint32_t pa = p_s + (lane >> 4) * DT_QP_HALF + g * 128 + ((((lane & 15) >> 1) ^ (g & 7)) << 4) + (lane & 1) * 8;
-        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(pa), "r"(*reinterpret_cast<const uint32_t*>(&p01)),
-                     "r"(*reinterpret_cast<const uint32_t*>(&p23)) : "memory");
+        pk[i][0] = *reinterpret_cast<const uint32_t*>(&p01);
+        pk[i][1] = *reinterpret_cast<const uint32_t*>(&p23);
         if (lane == 0) { m_s[g] = m_new; l_s[g] = l_s[g] * alpha + sum; alpha_s[g] = alpha; }
       }
       dt_bar_compute();
@@ -324,6 +340,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
           tmem_st16(tm_o + lane_addr, ov);
           tmem_st_wait();
         }
+      }
+      // P^T of this tile: only now, when the MMAs that read the previous tile's P^T have completed (o_done above)
+#pragma unroll
+      for (int i = 0; i < DT_GP / 4; ++i) {
+        const int g = cw + 4 * i;
+        // tokens 4 * lane .. + 3 of row g: half (lane >> 4), 16-byte chunk ((lane & 15) >> 1), upper or lower 8 bytes
+        const uint32_t pa = p_s + (lane >> 4) * DT_QP_HALF + g * 128 + ((((lane & 15) >> 1) ^ (g & 7)) << 4) + (lane & 1) * 8;
+        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(pa), "r"(pk[i][0]), "r"(pk[i][1]) : "memory");
       }
       if (last) {
         // V tile: the new token's row (RoPE fused) and zeros in the rest of the last 16-token step, so that 0 * (never
@@ -346,6 +370,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
       dt_fence_async_smem();     // P^T (and the V patch) were written with ordinary stores
       tc_fence_before();
       mbar_arrive(bar_pfull);
+      if (pos >= 0 && n_tiles >= 2 && j == n_tiles - 2 && !patch_k()) { ok = false; break; }
     }
     if (ok && mbar_wait(bar_odone, (n_tiles - 1) & 1, abort_flag, DT_BUDGET_NS)) {
       tc_fence_after();
