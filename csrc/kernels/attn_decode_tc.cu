@@ -37,15 +37,20 @@ constexpr int DT_BN = 128, DT_D = 128, DT_PS = 16, DT_GP = 8;   // tokens per ti
 constexpr int DT_THREADS = 192;
 constexpr int DT_HALF = 128 * 128;                 // bytes of one 64-element half of a 128-row tile (128-byte rows)
 constexpr int DT_TILE = 2 * DT_HALF;               // 32 KB: one K or V tile
-constexpr int DT_SLOTS = 3;
 constexpr int DT_QP_HALF = 16 * 128;               // bytes of one half of a 16-row B operand tile
-constexpr int DT_OFF_Q = DT_SLOTS * DT_TILE;       // Q^T: two halves
-constexpr int DT_OFF_P = DT_OFF_Q + 2 * DT_QP_HALF;
-constexpr int DT_OFF_ST = DT_OFF_P + 2 * DT_QP_HALF;            // fp32 scores [DT_GP][128]
-constexpr int DT_OFF_NEW = DT_OFF_ST + DT_GP * DT_BN * 4;       // rotated k row, v row of the new token (2 x 256 bytes)
-constexpr int DT_OFF_STATS = DT_OFF_NEW + 512;                  // m[8], l[8], alpha[8] fp32
-constexpr int DT_OFF_BARS = DT_OFF_STATS + 128;                 // mbarriers, tensor-memory slot, abort flags
-constexpr int DT_SMEM = DT_OFF_BARS + 128 + 1024 /* alignment slack */;
+// Shared-memory layout for a ring of SLOTS K / V tiles. Three slots (110 KB) let two CTAs share an SM, which is what a
+// launch with more CTAs than SMs wants; a launch with at most one CTA per SM takes six slots (three context tiles in
+// flight), because there a CTA's own copies in flight are all that hides the memory latency.
+template <int SLOTS>
+struct DtLayout {
+  static constexpr int OFF_Q = SLOTS * DT_TILE;                 // Q^T: two halves
+  static constexpr int OFF_P = OFF_Q + 2 * DT_QP_HALF;
+  static constexpr int OFF_ST = OFF_P + 2 * DT_QP_HALF;         // fp32 scores [DT_GP][128]
+  static constexpr int OFF_NEW = OFF_ST + DT_GP * DT_BN * 4;    // rotated k row, v row of the new token (2 x 256 bytes)
+  static constexpr int OFF_STATS = OFF_NEW + 512;               // m[8], l[8], alpha[8] fp32
+  static constexpr int OFF_BARS = OFF_STATS + 128;              // mbarriers, tensor-memory slot, abort flags
+  static constexpr int SMEM = OFF_BARS + 192 + 1024 /* alignment slack */;
+};
 constexpr int DT_TMEM_COLS = 64;     // two S^T buffers of 16 columns, O^T at 32
 constexpr uint64_t DT_BUDGET_NS = 4000000000ull;
 
@@ -80,7 +85,8 @@ __device__ __forceinline__ uint32_t dt_tile_off(int row, int d) {
   return (uint32_t)((d >> 6) * DT_HALF + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2);
 }
 
-__global__ void __launch_bounds__(DT_THREADS, 2)
+template <int DT_SLOTS>
+__global__ void __launch_bounds__(DT_THREADS, DT_SLOTS == 3 ? 2 : 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecodeTcParams p) {
   const int kvh = blockIdx.x, b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -100,18 +106,18 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
   extern __shared__ uint8_t dt_smem_raw[];
   const uint32_t base = (smem_u32(dt_smem_raw) + 1023u) & ~1023u;
   uint8_t* bp = dt_smem_raw + (base - smem_u32(dt_smem_raw));
-  const uint32_t q_s = base + DT_OFF_Q, p_s = base + DT_OFF_P;
-  float* sT = reinterpret_cast<float*>(bp + DT_OFF_ST);
-  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(bp + DT_OFF_NEW);     // [0..127] k row, [128..255] v row
-  float* m_s = reinterpret_cast<float*>(bp + DT_OFF_STATS);
+  const uint32_t q_s = base + DtLayout<DT_SLOTS>::OFF_Q, p_s = base + DtLayout<DT_SLOTS>::OFF_P;
+  float* sT = reinterpret_cast<float*>(bp + DtLayout<DT_SLOTS>::OFF_ST);
+  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(bp + DtLayout<DT_SLOTS>::OFF_NEW);     // [0..127] k row, [128..255] v row
+  float* m_s = reinterpret_cast<float*>(bp + DtLayout<DT_SLOTS>::OFF_STATS);
   float* l_s = m_s + DT_GP;
   float* alpha_s = l_s + DT_GP;
-  const uint32_t bars = base + DT_OFF_BARS;
-  const uint32_t bar_full = bars, bar_empty = bars + 24, bar_sfull = bars + 48 /* S^T buffer 0 */, bar_pfull = bars + 56,
-                 bar_odone = bars + 64, bar_qready = bars + 72, bar_kpatch = bars + 80;
-  const uint32_t bar_sfull1 = bars + 88;    // S^T buffer 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bp + DT_OFF_BARS + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bp + DT_OFF_BARS + 104);    // [1]: never set
+  const uint32_t bars = base + DtLayout<DT_SLOTS>::OFF_BARS;
+  const uint32_t bar_sfull = bars /* S^T buffer 0 */, bar_sfull1 = bars + 8 /* S^T buffer 1 */, bar_pfull = bars + 16,
+                 bar_odone = bars + 24, bar_qready = bars + 32, bar_kpatch = bars + 40;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bp + DtLayout<DT_SLOTS>::OFF_BARS + 48);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bp + DtLayout<DT_SLOTS>::OFF_BARS + 56);    // [1]: never set
+  const uint32_t bar_full = bars + 64, bar_empty = bars + 64 + 8 * DT_SLOTS;       // one pair per ring slot
 
   if (tid == 0) {
     for (int i = 0; i < DT_SLOTS; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
@@ -173,10 +179,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
       bool ok = mbar_wait(bar_qready, 0, abort_flag, DT_BUDGET_NS);
       // S^T of tile j + 1 is issued before the wait for the softmax of tile j (two S^T buffers), so the scores of the next
       // tile are ready when the compute warps come for them
-      auto issue_s = [&](int j) -> bool {
+      auto issue_s = [&](int j, bool k_landed) -> bool {
         const int itk = 2 * j;
         const uint32_t ks = base + (itk % DT_SLOTS) * DT_TILE;
-        if (!mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) return false;
+        if (!k_landed && !mbar_wait(bar_full + 8 * (itk % DT_SLOTS), (itk / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) return false;
         if (pos >= 0 && j == n_tiles - 1 && !mbar_wait(bar_kpatch, 0, abort_flag, DT_BUDGET_NS)) return false;
         tc_fence_after();
 #pragma unroll
@@ -187,15 +193,31 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
         tc_commit((j & 1) ? bar_sfull1 : bar_sfull);
         return true;
       };
-      ok = ok && issue_s(0);
+      ok = ok && issue_s(0, false);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int itv = 2 * j + 1;
         const uint32_t vs = base + (itv % DT_SLOTS) * DT_TILE;
-        // (the last tile of a step with RoPE fused waits for the patch of its K row, which the compute warps make after
-        // their work on tile j: its scores are issued behind O^T of tile j instead of ahead of it)
-        const bool ahead = j + 1 < n_tiles && !(pos >= 0 && j + 1 == n_tiles - 1);
-        if (ahead && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(bar_pfull, j & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
+        // While waiting for P^T of tile j: if the K tile of j + 1 has landed, its scores are issued ahead (never the other
+        // way round: O^T of tile j does not wait for a K tile still in flight). The last tile of a step with RoPE fused
+        // waits for the patch of its K row, which the compute warps make after their work on tile j: not issued ahead.
+        bool s_next = !(j + 1 < n_tiles);
+        const bool may_ahead = j + 1 < n_tiles && !(pos >= 0 && j + 1 == n_tiles - 1);
+        {
+          const int itk = 2 * (j + 1);
+          const uint32_t kbar = bar_full + 8 * (itk % DT_SLOTS), kpar = (itk / DT_SLOTS) & 1;
+          const uint64_t t0 = global_timer_ns();
+          bool p_ready = false;
+          uint32_t spins = 0;
+          while (!p_ready) {
+            if (may_ahead && !s_next && mbar_test_wait(kbar, kpar)) {
+              if (!issue_s(j + 1, true)) { ok = false; break; }
+              s_next = true;
+            }
+            p_ready = mbar_try_wait(bar_pfull, j & 1);
+            if (!p_ready && (++spins & 255) == 0 && (abort_flag[0] || global_timer_ns() - t0 > DT_BUDGET_NS)) { ok = false; break; }
+          }
+          if (!ok) break;
+        }
         if (!mbar_wait(bar_full + 8 * (itv % DT_SLOTS), (itv / DT_SLOTS) & 1, abort_flag, DT_BUDGET_NS)) { ok = false; break; }
         tc_fence_after();
         const int n_valid = min(len, (j + 1) * DT_BN) - j * DT_BN;
@@ -205,7 +227,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmKV, const AttnDecode
                   idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(bar_empty + 8 * (itv % DT_SLOTS));
         tc_commit(bar_odone);
-        if (j + 1 < n_tiles && !ahead && !issue_s(j + 1)) { ok = false; break; }
+        if (!s_next && !issue_s(j + 1, false)) { ok = false; break; }
       }
       if (!ok && abort_flag[0] == 0) { abort_flag[0] = 1; report_status(p.status, ST_TIMEOUT_SMEM_FULL, 21); }
     }
@@ -409,11 +431,21 @@ extern "C" int skein_attn_decode_tc(const void* q, long long q_stride, void* kv,
   using namespace skein;
   if (B == 0) return 0;
   if (D != DT_D || page_size != DT_PS || Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > DT_GP || q_stride % 8 != 0) return -1;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
+  // at most one CTA per SM: the deep ring; otherwise two CTAs per SM with three slots each
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  static int sm_cache[64] = {0};
+  if (dev >= 0 && dev < 64) {
+    if (sm_cache[dev] == 0) cudaDeviceGetAttribute(&sm_cache[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (sm_cache[dev] > 0) sms = sm_cache[dev];
+  }
+  const bool deep = (long long)B * Hkv <= sms;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[deep ? 1 : 0]) {
+    cudaError_t e = deep ? cudaFuncSetAttribute(attn_decode_tc_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, DtLayout<6>::SMEM)
+                         : cudaFuncSetAttribute(attn_decode_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, DtLayout<3>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_set[deep ? 1 : 0] = true;
   }
   CUtensorMap tmKV;
   int rc = cached_tmap_2d(&tmKV, kv, (uint64_t)num_pages * 2 * Hkv * DT_PS, DT_D, 2, DT_PS);
@@ -424,6 +456,9 @@ extern "C" int skein_attn_decode_tc(const void* q, long long q_stride, void* kv,
   p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.max_blocks = max_blocks; p.num_pages = num_pages;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.cos_sin = cos_sin; p.positions = positions; p.max_pos = max_pos;
-  attn_decode_tc_kernel<<<dim3(Hkv, B), DT_THREADS, DT_SMEM, (cudaStream_t)stream>>>(tmKV, p);
+  if (deep)
+    attn_decode_tc_kernel<6><<<dim3(Hkv, B), DT_THREADS, DtLayout<6>::SMEM, (cudaStream_t)stream>>>(tmKV, p);
+  else
+    attn_decode_tc_kernel<3><<<dim3(Hkv, B), DT_THREADS, DtLayout<3>::SMEM, (cudaStream_t)stream>>>(tmKV, p);
   return (int)cudaGetLastError();
 }
