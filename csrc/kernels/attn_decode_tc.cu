@@ -15,8 +15,10 @@
 //   O^T += V^T P    A = V tile read as an MN-major operand (M = head dimension, the reduction runs over the tokens,
 //                   which is how the cache stores V), accumulator 128 lanes (d) x 16 columns (heads)
 //
-// One CTA per (sequence, kv head): warp 0 streams the K and V tiles of the context through a three-slot ring (96 KB, two
-// CTAs per SM: 192 KB of cache in flight per SM), warp 1 issues the MMAs, warps 2-5 do the rest. With RoPE fused, the new
+// One CTA per (sequence, kv head): warp 0 streams the K and V tiles of the context through a ring of 32 KB slots (three
+// slots and two CTAs per SM when the launch has more CTAs than SMs, six slots and one CTA per SM otherwise: 192 KB of
+// cache in flight per SM either way), warp 1 issues the MMAs (the next tile's scores go into a second S^T buffer ahead of
+// the softmax whenever its K tile has already landed), warps 2-5 do the rest. With RoPE fused, the new
 // token's rotated K row and its V row are stored to the cache AND patched into the last tile in shared memory after TMA
 // has landed it, so the kernel never reads back through TMA what it has just written with ordinary stores.
 // Every wait is bounded; on expiry the CTA records a status code, waits (bounded) for its copies in flight, frees its
