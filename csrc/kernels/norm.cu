@@ -317,11 +317,12 @@ __global__ void __launch_bounds__(512) reduce_norm_route_kernel(const NormParams
       r.expert_ids[t * topk + j] = ids[j];
       r.expert_w[t * topk + j] = vals[j] / den;
     }
-    __threadfence();
-    atomicAdd(r.barrier, 1);
+    // release at device scope: this thread's stores of the expert ids / weights above are visible to whoever acquires
+    // the counter (one instruction instead of a full fence followed by a relaxed add)
+    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(r.barrier) : "memory");
     // grid-wide arrival, bounded: all T CTAs are resident, so this only runs out if one never started
     const bool poisoned = p.status != nullptr && *(volatile int*)p.status == ST_TIMEOUT_GRID_BARRIER;
-    const bool ok = !poisoned && wait_flag_ge(r.barrier, T, r.barrier_budget_ns);
+    const bool ok = !poisoned && wait_counter_ge_gpu(r.barrier, T, r.barrier_budget_ns);
     if (!ok) report_status(p.status, ST_TIMEOUT_GRID_BARRIER, t);
     barrier_ok = ok ? 1 : 0;
   }

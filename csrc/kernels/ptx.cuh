@@ -292,6 +292,24 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int epoch, uint64_
   }
 }
 
+// The same for a counter that CTAs of THIS GPU raise (a grid-wide arrival count): device-scope acquire loads, polled
+// back to back (a system-scope acquire costs far more per poll, and the counter is about to fill).
+__device__ __forceinline__ bool wait_counter_ge_gpu(const int* counter, int n, uint64_t budget_ns) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+  if (v - n >= 0) return true;
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v - n >= 0) return true;
+    }
+    if (global_timer_ns() - t0 > budget_ns) return false;
+  }
+}
+
 __device__ __forceinline__ void report_status(int* status, int code, int detail) {
   if (status != nullptr && atomicCAS(status, 0, code) == 0) status[1] = detail;
 }
