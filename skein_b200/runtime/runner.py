@@ -40,6 +40,24 @@ def bucket_for(n: int) -> int:
     raise ValueError(f"batch {n} exceeds the largest capture class {BUCKETS[-1]}")
 
 
+def split_by_tokens(lengths, m: int):
+    """Cuts the sequence indices 0 .. len(lengths) - 1 into at most `m` contiguous, non-empty groups of about equal token
+    counts (a group is closed as soon as the running total reaches its share, or when the sequences left are needed to
+    fill the remaining groups)."""
+    total = sum(lengths)
+    groups, cur, acc = [], [], 0
+    for i, n in enumerate(lengths):
+        cur.append(i)
+        acc += n
+        left = len(lengths) - i - 1
+        if len(groups) < m - 1 and (acc >= total * (len(groups) + 1) / m or left <= m - 1 - len(groups)) and left >= 1:
+            groups.append(cur)
+            cur = []
+    if cur:
+        groups.append(cur)
+    return groups
+
+
 class _Bucket:
     def __init__(self, B: int, max_blocks: int, device):
         self.B, self.max_blocks = B, max_blocks
@@ -262,15 +280,7 @@ class ModelRunner:
             # at least one micro-chunk per stage; up to two per stage while a micro-chunk keeps 2048 tokens (fill and drain
             # of the pipeline cost one micro-chunk's time per call, and the projections want a few thousand tokens)
             M = min(len(seqs), max(n_stages, min(2 * n_stages, total // 2048)))
-            groups, cur, acc = [], [], 0
-            for i, sq in enumerate(seqs):        # contiguous groups of about total / M tokens, none empty
-                cur.append(i)
-                acc += len(sq[0])
-                left = len(seqs) - i - 1
-                if len(groups) < M - 1 and (acc >= total * (len(groups) + 1) / M or left <= M - 1 - len(groups)) and left >= 1:
-                    groups.append(cur)
-                    cur = []
-            groups.append(cur)
+            groups = split_by_tokens([len(s[0]) for s in seqs], M)
             items = [self._prefill_inputs([seqs[i] for i in g], None if sampling is None else [sampling[i] for i in g])
                      for g in groups if g]
             return self.dec.forward_prefill_micro(items).cpu().tolist()

@@ -212,3 +212,41 @@ def test_engine_gpu_sampling_graph_is_reproducible_and_keeps_greedy_rows():
     assert eng.runner.graph_captures >= 2            # the greedy and the sampling variant of a bucket
     from skein_b200 import ops
     torch.cuda.synchronize(); ops.workspace().check_status()
+
+
+def test_prefill_micro_chunks_are_contiguous_balanced_and_never_empty():
+    from skein_b200.runtime.runner import split_by_tokens
+    assert split_by_tokens([5, 5, 5, 5], 2) == [[0, 1], [2, 3]]
+    assert split_by_tokens([10, 1, 1], 2) == [[0], [1, 2]]
+    assert split_by_tokens([1, 1, 10], 2) == [[0, 1], [2]]
+    assert split_by_tokens([4, 4, 4], 4) == [[0], [1], [2]]
+    assert split_by_tokens([7], 2) == [[0]]
+    for lengths, m in (([3, 9, 2, 2, 8, 1, 1], 3), ([2048] * 8, 4), ([1] * 5, 4)):
+        g = split_by_tokens(lengths, m)
+        assert 1 <= len(g) <= m and all(g) and [i for grp in g for i in grp] == list(range(len(lengths)))
+
+
+def test_decode_kernel_choice_and_graph_warm_up_on_cpu():
+    """The per-launch choice between the tensor-memory and the mma.sync decode kernel, and the start-up capture being a
+    no-op where there are no CUDA graphs."""
+    import torch
+    from skein_b200.ops import functional as F
+    kv = torch.empty(4, 2, 8, 16, 128)
+    orig = F.workspace
+
+    class _W:
+        sm_count = 148
+    F.workspace = lambda: _W()
+    try:
+        assert F._decode_tc_ok(kv, 64, 32, 8, 128, 1, None)            # 512 (sequence, kv head) pairs: bandwidth-bound
+        assert not F._decode_tc_ok(kv, 64, 4, 1, 128, 1, None)         # 64 pairs: the mma.sync kernel
+        assert F._decode_tc_ok(kv, 64, 4, 1, 128, 1, "tc")             # forced
+        assert not F._decode_tc_ok(kv, 64, 32, 8, 128, 2, "tc")        # split-KV stays with the mma.sync kernel
+        assert not F._decode_tc_ok(kv, 64, 32, 2, 128, 1, "tc")        # 16 heads per kv head
+        assert not F._decode_tc_ok(torch.empty(4, 2, 8, 32, 128), 64, 32, 8, 128, 1, "tc")   # 32-token pages
+    finally:
+        F.workspace = orig
+    cfg = mc.tiny_mixtral(layers=1, hidden=128, inter=128, heads=2, kv_heads=1, experts=4, vocab=64)
+    dec = Decoder(cfg, random_weights(cfg, mc.ParallelLayout(), "cpu", seed=0), num_pages=8, page_size=16, max_pos=64)
+    eng = Engine(dec, EngineConfig(max_batch=4, use_graphs=True, warm_graphs=True, prefix_cache=False))
+    assert eng.runner.capture_buckets(4) == 0 and eng.runner.graph_captures == 0
