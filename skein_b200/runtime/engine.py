@@ -47,6 +47,7 @@ class EngineConfig:
     eos_token: int = -1
     use_graphs: bool = True
     warm_graphs: bool = False          # capture the decode graph of every batch bucket up to max_batch at start-up
+    prelaunch: bool = True             # enqueue the next decode step as soon as this one's tokens are accepted (see _prelaunch)
     drift_baseline: tuple = ()         # prompt lengths the plan was extracted for (workload drift monitor)
     drift_threshold_kl: float = 0.05
 
@@ -109,6 +110,9 @@ class Engine:
         self._dp_of: dict[int, int] = {}
         self._dp_load = [0] * self._dp
         self._wait_ns_seen = 0
+        # the next decode step, already enqueued on the device: (bucket, request ids as planned, rows as laid out, sampling rows)
+        self._pre = None
+        self._prelaunch_ok = c.prelaunch and getattr(decoder, "n_stages", 1) == 1
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
         self.last_step_failed = False
         self.step_started_at = None    # monotonic time at which the step in progress began (the rank's heartbeat reads it)
@@ -158,6 +162,7 @@ class Engine:
         prefill, decode = self.batcher.next_step_batch()
         self.last_step_failed = False
         if not prefill and not decode:
+            self._drop_prelaunched()
             return []
         t0 = time.perf_counter()
         self.step_started_at = time.monotonic()
@@ -185,6 +190,7 @@ class Engine:
     def abort_all(self, reason: str) -> list[TokenEvent]:
         """Drop everything in flight (a step failed here or on another rank): the requests' streams end with an
         error and their pages leave the prefix cache; queued requests stay queued."""
+        self._drop_prelaunched()
         events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
         for ev in events:
             self._sampling.pop(ev.request_id, None)
@@ -224,22 +230,59 @@ class Engine:
                 self.batcher.prefill_advanced(rid, end)
                 if last:
                     events.append(self._accept(rid, tok, stamp()))
+        pre, self._pre = self._pre, None
+        if pre is not None and pre[1] != list(decode):
+            self.runner.decode_wait(pre[0])     # the plan changed under it (requests were dropped): its result is not used
+            pre = None
         if decode:
-            if self._dp > 1:
-                decode = self._dp_layout(decode)
-            bk = self.runner.bucket(len(decode))
-            rows = self._rows(decode)
-            self.runner.stage_decode_inputs(bk, self.batcher, decode, sampling=rows)
-            out = self.runner.decode_step(bk, sampling=rows is not None)
+            if pre is not None:
+                bk, _, decode, rows = pre
+            else:
+                bk, _, decode, rows = self._launch_decode(decode)
+            out = self.runner.decode_wait(bk)
             fin, counts = self.batcher.accept_tokens(decode, out.data_ptr(), stamp(), self.cfg.eos_token)
             toks = out[:len(decode)].tolist()
-            for rid, tok, f, n in zip(decode, toks, fin, counts):
-                if rid == 0:
-                    continue            # a padding row of a data-parallel slice
-                if f:
+            for rid, f, n in zip(decode, fin, counts):
+                if f and rid != 0:
                     self._finish(rid, n)
-                events.append(TokenEvent(rid, tok, bool(f)))
+            # everything the next decode step depends on is settled: put it on the device before the Python-side
+            # bookkeeping of this one, so that the device does not wait for it
+            self._prelaunch()
+            for rid, tok, f in zip(decode, toks, fin):
+                if rid != 0:                # 0: a padding row of a data-parallel slice
+                    events.append(TokenEvent(rid, tok, bool(f)))
         return events
+
+    def _launch_decode(self, decode):
+        """Stages and enqueues one decode step for the planned request ids; returns (bucket, ids as planned, rows as laid
+        out on the device, sampling rows)."""
+        plan = list(decode)
+        if self._dp > 1:
+            decode = self._dp_layout(decode)
+        bk = self.runner.bucket(len(decode))
+        rows = self._rows(decode)
+        self.runner.stage_decode_inputs(bk, self.batcher, decode, sampling=rows)
+        self.runner.decode_launch(bk, sampling=rows is not None)
+        return bk, plan, decode, rows
+
+    def _prelaunch(self) -> None:
+        """Enqueue the next step's decode right after this step's tokens were accepted (positions, pages and the set of
+        decoding sequences are final then). The next call of step() finds it running and only waits for it; a prefill
+        chunk planned for that step is queued behind it (different sequences). New requests are admitted as before;
+        their prefill simply follows the decode launch of the step instead of preceding it."""
+        if not self._prelaunch_ok:
+            return
+        _, decode = self.batcher.next_step_batch()
+        if decode:
+            self._pre = self._launch_decode(decode)
+
+    def _drop_prelaunched(self) -> None:
+        pre, self._pre = self._pre, None
+        if pre is not None:
+            try:
+                self.runner.decode_wait(pre[0])
+            except Exception:       # noqa: BLE001  (the step is being thrown away)
+                pass
 
     def _dp_layout(self, decode):
         """Rows of a decode step under data-parallel attention: one equally sized slice per rank, a sequence always in

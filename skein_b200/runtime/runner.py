@@ -235,6 +235,20 @@ class ModelRunner:
             self.last_wait_ns = ((hi & 0xFFFFFFFF) << 32) | (lo & 0xFFFFFFFF)
         return bk.host_out[:bk.B]
 
+    def decode_launch(self, bk: _Bucket, sampling: bool = False) -> None:
+        """decode_step without the wait: H2D of the staged inputs, the step, D2H of the result, all enqueued."""
+        self.decode_step(bk, sync=False, sampling=sampling)
+
+    def decode_wait(self, bk: _Bucket):
+        """Waits for a step enqueued by decode_launch; returns the host result view."""
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+            if int(bk.host_out[bk.B]) != 0:
+                ops.workspace().check_status()
+            lo, hi = int(bk.host_out[bk.B + 2]), int(bk.host_out[bk.B + 3])      # a 64-bit total in two words
+            self.last_wait_ns = ((hi & 0xFFFFFFFF) << 32) | (lo & 0xFFFFFFFF)
+        return bk.host_out[:bk.B]
+
     def decode_loop_step(self, bk: _Bucket):
         """One step with device-side token feedback (no host traffic). Inputs must already be on the device."""
         if self.use_graphs:

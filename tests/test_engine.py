@@ -250,3 +250,48 @@ def test_decode_kernel_choice_and_graph_warm_up_on_cpu():
     dec = Decoder(cfg, random_weights(cfg, mc.ParallelLayout(), "cpu", seed=0), num_pages=8, page_size=16, max_pos=64)
     eng = Engine(dec, EngineConfig(max_batch=4, use_graphs=True, warm_graphs=True, prefix_cache=False))
     assert eng.runner.capture_buckets(4) == 0 and eng.runner.graph_captures == 0
+
+
+def test_prelaunched_decode_gives_the_same_tokens_and_survives_a_dropped_request():
+    """The engine enqueues the next decode step as soon as a step's tokens are accepted. Same tokens as without; a request
+    retired behind its back (the plan no longer matches the step in flight) discards that step and carries on."""
+    cfg = mc.tiny_mixtral(layers=2, hidden=128, inter=128, heads=2, kv_heads=1, experts=4, vocab=96)
+    w = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=3)
+    prompts = [[5, 6, 7, 8], [9, 10], [11, 12, 13], [14], [15, 16, 17, 18, 19]]
+
+    def engine(prelaunch):
+        dec = Decoder(cfg, w, num_pages=64, page_size=16, max_pos=96)
+        return Engine(dec, EngineConfig(max_batch=8, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False,
+                                        prelaunch=prelaunch, max_prefill_tokens=6))    # prefill spread over several steps
+    a, b = engine(True), engine(False)
+    assert a.generate(prompts, 7) == b.generate(prompts, 7)
+    assert a._pre is None                                   # nothing left in flight once everything finished
+    # late arrivals: their prefill follows the decode launch of the step that admits them
+    a, b = engine(True), engine(False)
+    outs = []
+    for eng in (a, b):
+        got = {}
+        for i, p in enumerate(prompts[:2]):
+            eng.submit(p, 9, request_id=i + 1)
+        for step in range(40):
+            if step == 3:
+                eng.submit(prompts[2], 5, request_id=3)
+            for ev in eng.step():
+                got.setdefault(ev.request_id, []).append(ev.token)
+        outs.append(got)
+    assert outs[0] == outs[1]
+    # a request retired between two steps: the step in flight is thrown away, the others keep their tokens
+    a, b = engine(True), engine(False)
+    res = []
+    for eng in (a, b):
+        got = {}
+        for i, p in enumerate(prompts[:3]):
+            eng.submit(p, 8, request_id=i + 1)
+        for step in range(30):
+            if step == 4:
+                eng.batcher.retire(2)
+                eng._sampling.pop(2, None)
+            for ev in eng.step():
+                got.setdefault(ev.request_id, []).append(ev.token)
+        res.append(got)
+    assert res[0][1] == res[1][1] and res[0][3] == res[1][3] and len(res[0][1]) == 8
