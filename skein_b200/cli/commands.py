@@ -385,6 +385,18 @@ def cmd_bench(args, emit) -> int:
 
     if getattr(args, "collectives", False):
         return bench_collectives(emit, args)
+    if getattr(args, "synth", None):
+        # the synthetic workloads of the planner tests and of the serving benchmarks, as a trace file
+        n, seed = int(args.synth_requests), int(args.synth_seed)
+        text = (core.synth_uniform_trace(n, seed, 128, 2048, 64, 512, 4.0) if args.synth == "uniform"
+                else core.synth_burst_trace(n, seed, 50.0, 2.0, 10.0, 600.0, 8192, 32, 1024))
+        import tempfile
+        path = args.write_trace or tempfile.NamedTemporaryFile("w", suffix=".jsonl", delete=False).name
+        Path(path).write_text(text)
+        args.workload = path
+        if not args.artifact and not getattr(args, "url", None):
+            emit(args, {"trace": path, "requests": n, "kind": args.synth, "seed": seed}, f"wrote {n} {args.synth} requests to {path}")
+            return 0
     if getattr(args, "url", None):
         if not args.workload:
             raise ValueError("`skein bench --url` needs --workload")

@@ -127,6 +127,13 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--vocab-size", type=int, default=32000, help="with --url: range of the random prompt token ids")
     b.add_argument("--max-seq-len", type=int, default=4096, help="with --url: prompts are clipped so that prompt + output fit")
     b.add_argument("--op-profile", action="store_true", help="print the per-operator table of one decode step (eager launches, CUDA events)")
+    b.add_argument("--synth", choices=["uniform", "burst"], default=None,
+                   help="generate the trace instead of reading --workload: uniform (prompts 128..2048, outputs 64..512, Poisson 4 req/s) "
+                        "or burst (on/off Poisson 50 / 2 req/s every 10 s, log-normal prompts of median 600 capped at 8192, outputs 32..1024)")
+    b.add_argument("--synth-requests", type=int, default=256)
+    b.add_argument("--synth-seed", type=int, default=0)
+    b.add_argument("--write-trace", default=None, help="with --synth: write the generated trace (JSONL) here; without --artifact / --url "
+                                                       "the command stops after writing it")
     return ap
 
 

@@ -54,6 +54,28 @@ def test_extract_end_to_end_deterministic_json(tmp_path, capsys):
     assert "placement   tp=" in capsys.readouterr().out
 
 
+def test_bench_writes_synthetic_traces(tmp_path, capsys):
+    """`bench --synth` generates the uniform and the burst workload as a trace file (seeded, reproducible) that the other
+    commands read like any recorded trace."""
+    p1, p2, p3 = tmp_path / "a.jsonl", tmp_path / "b.jsonl", tmp_path / "c.jsonl"
+    assert main(["--output", "json", "bench", "--synth", "burst", "--synth-requests", "40", "--write-trace", str(p1)]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["requests"] == 40 and rep["kind"] == "burst"
+    assert main(["bench", "--synth", "burst", "--synth-requests", "40", "--write-trace", str(p2)]) == 0
+    assert main(["bench", "--synth", "uniform", "--synth-requests", "40", "--synth-seed", "3", "--write-trace", str(p3)]) == 0
+    capsys.readouterr()
+    assert p1.read_bytes() == p2.read_bytes() != p3.read_bytes()
+    lines = [json.loads(l) for l in p1.read_text().splitlines()]
+    assert "slo" in lines[0] and len(lines) == 41
+    reqs = lines[1:]
+    assert all(1 <= r["prompt_tokens"] <= 8192 and 32 <= r["output_tokens"] <= 1024 for r in reqs)
+    assert [r["arrival_ms"] for r in reqs] == sorted(r["arrival_ms"] for r in reqs)
+    # the planner takes the generated trace
+    assert main(["--output", "json", "extract", *[a if a != str(ROOT / "cluster/sample_trace.jsonl") else str(p3) for a in ARGS],
+                 "--out", str(tmp_path / "plan.json")]) == 0
+    capsys.readouterr()
+
+
 def test_errors_are_json_objects_on_stderr(tmp_path, capsys):
     bad = tmp_path / "cluster.toml"
     bad.write_text((ROOT / "cluster/h100_2x.toml").read_text().replace("num_devices = 2", "num_devices = 5"))
