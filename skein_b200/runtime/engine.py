@@ -29,6 +29,7 @@ import time
 from dataclasses import dataclass
 
 from .. import core
+from ..utils import otlp
 from .runner import ModelRunner
 
 
@@ -113,6 +114,9 @@ class Engine:
         # the next decode step, already enqueued on the device: (bucket, request ids as planned, rows as laid out, sampling rows)
         self._pre = None
         self._prelaunch_ok = c.prelaunch and getattr(decoder, "n_stages", 1) == 1
+        # optional trace export (SKEIN_OTLP_ENDPOINT): one span per engine step and one per finished request
+        self._otlp = otlp.exporter(getattr(getattr(inner, "layout", None), "rank", 0))
+        self._req_t0: dict[int, tuple] = {}      # request id -> (trace id, wall-clock ns at submission), while exporting
         self.failure_injector = None   # tests: callable(step_index) that may raise inside the step
         self.last_step_failed = False
         self.step_started_at = None    # monotonic time at which the step in progress began (the rank's heartbeat reads it)
@@ -138,6 +142,8 @@ class Engine:
             if sampling is not None and not sampling.greedy:
                 self._sampling[rid] = sampling
             self._observe_length(len(prompt))
+            if self._otlp is not None:
+                self._req_t0[rid] = (self._otlp.new_trace_id(), time.time_ns(), len(prompt))
         return rid, d
 
     def _observe_length(self, n: int) -> None:
@@ -183,6 +189,12 @@ class Engine:
         comm_us = max(0, wait_ns - self._wait_ns_seen) / 1e3     # time the reduce kernels stood waiting for peers
         self._wait_ns_seen = wait_ns
         self.metrics.record_step(self._step, len(decode) + len(prefill), max(0.0, us - comm_us), comm_us, self.kv.in_use_pages)
+        if self._otlp is not None:
+            end = time.time_ns()
+            self._otlp.span("engine.step", end - int(us * 1e3), end,
+                            attrs={"step": self._step, "decode_sequences": len(decode), "prefill_sequences": len(prefill),
+                                   "peer_wait_us": float(comm_us), "kv_pages_in_use": int(self.kv.in_use_pages)},
+                            error="step failed" if self.last_step_failed else None)
         self._step += 1
         self.step_started_at = None
         return events
@@ -192,6 +204,12 @@ class Engine:
         error and their pages leave the prefix cache; queued requests stay queued."""
         self._drop_prelaunched()
         events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
+        if self._otlp is not None:
+            for ev in events:
+                tr = self._req_t0.pop(ev.request_id, None)
+                if tr is not None:
+                    self._otlp.span("request", tr[1], time.time_ns(), trace_id=tr[0],
+                                    attrs={"request_id": int(ev.request_id), "prompt_tokens": tr[2]}, error=reason)
         for ev in events:
             self._sampling.pop(ev.request_id, None)
             self._dp_release(ev.request_id)
@@ -321,6 +339,12 @@ class Engine:
         ttft = float(info["first_token_ms"] - info["arrival_ms"])
         tpot = float(info["last_token_ms"] - info["first_token_ms"]) / max(1, n - 1)
         self.metrics.record_request(rid, "ok", ttft, tpot, info["prefix_hit_tokens"], n)
+        if self._otlp is not None:
+            tr = self._req_t0.pop(rid, None)
+            if tr is not None:
+                self._otlp.span("request", tr[1], time.time_ns(), trace_id=tr[0],
+                                attrs={"request_id": int(rid), "prompt_tokens": tr[2], "output_tokens": int(n), "ttft_ms": ttft,
+                                       "tpot_ms": tpot, "prefix_hit_tokens": int(info["prefix_hit_tokens"])})
         self.batcher.retire(rid)
         self._sampling.pop(rid, None)
         self._dp_release(rid)

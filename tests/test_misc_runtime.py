@@ -131,3 +131,64 @@ def test_speculative_decoding_with_a_draft_model_equals_target_greedy():
     a, sa = sp.SpeculativeDecoder(mk(cfg, 0), mk(cfg, 0), k=3).generate(prompt, 10, temperature=0.9, seed=4)
     b, _ = sp.SpeculativeDecoder(mk(cfg, 0), mk(cfg, 0), k=3).generate(prompt, 10, temperature=0.9, seed=4)
     assert a == b and len(a) == 10 and sa["accepted"] == sa["proposed"]
+
+
+def test_spans_are_exported_as_otlp_http_json(monkeypatch):
+    """With SKEIN_OTLP_ENDPOINT set the engine ships one span per step and one per finished request to <endpoint>/v1/traces
+    (OTLP/HTTP JSON); a collector that is down costs nothing but dropped spans."""
+    import http.server
+    import json
+    import threading
+
+    from skein_b200.models import config as mc
+    from skein_b200.models.decoder import Decoder, random_weights
+    from skein_b200.runtime.engine import Engine, EngineConfig
+    from skein_b200.utils import otlp
+
+    got = []
+
+    class Collector(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers["Content-Length"]))
+            got.append((self.path, self.headers["Content-Type"], json.loads(body)))
+            self.send_response(200)
+            self.end_headers()
+            self.wfile.write(b"{}")
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.HTTPServer(("127.0.0.1", 0), Collector)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        otlp.shutdown()
+        monkeypatch.setenv("SKEIN_OTLP_ENDPOINT", f"http://127.0.0.1:{srv.server_address[1]}")
+        monkeypatch.setenv("SKEIN_OTLP_SERVICE", "skein-test")
+        cfg = mc.tiny_mixtral(layers=1, hidden=128, inter=128, heads=2, kv_heads=1, experts=4, vocab=64)
+        dec = Decoder(cfg, random_weights(cfg, mc.ParallelLayout(), "cpu", seed=0), num_pages=16, page_size=16, max_pos=64)
+        eng = Engine(dec, EngineConfig(max_batch=4, use_graphs=False, prefix_cache=False))
+        assert eng._otlp is not None
+        out = eng.generate([[1, 2, 3], [4, 5]], 4)
+        assert [len(o) for o in out] == [4, 4]
+        otlp.shutdown()                       # flushes
+    finally:
+        srv.shutdown()
+    assert got and all(p == "/v1/traces" and ct == "application/json" for p, ct, _ in got)
+    spans = [s for _, _, b in got for rs in b["resourceSpans"] for ss in rs["scopeSpans"] for s in ss["spans"]]
+    res = got[0][2]["resourceSpans"][0]["resource"]["attributes"]
+    assert {"key": "service.name", "value": {"stringValue": "skein-test"}} in res
+    names = [s["name"] for s in spans]
+    assert names.count("request") == 2 and names.count("engine.step") >= 4
+    req = next(s for s in spans if s["name"] == "request")
+    attrs = {a["key"]: a["value"] for a in req["attributes"]}
+    assert attrs["output_tokens"] == {"intValue": "4"} and "ttft_ms" in attrs and len(req["traceId"]) == 32 and len(req["spanId"]) == 16
+    assert int(req["endTimeUnixNano"]) >= int(req["startTimeUnixNano"])
+    # no endpoint: no exporter, no thread
+    monkeypatch.delenv("SKEIN_OTLP_ENDPOINT")
+    assert otlp.exporter() is None
+    # a dead collector: posts fail quietly, a full queue drops
+    ex = otlp.SpanExporter("http://127.0.0.1:9", max_queue=2, flush_s=0.05, timeout_s=0.2)
+    for i in range(50):
+        ex.span("x", 1, 2)
+    ex.close()
+    assert ex.sent == 0 and (ex.dropped > 0 or ex.failed_posts > 0)
