@@ -295,3 +295,32 @@ def test_prelaunched_decode_gives_the_same_tokens_and_survives_a_dropped_request
                 got.setdefault(ev.request_id, []).append(ev.token)
         res.append(got)
     assert res[0][1] == res[1][1] and res[0][3] == res[1][3] and len(res[0][1]) == 8
+
+
+@pytest.mark.gpu
+def test_engine_gpu_long_context_8192_token_prompt():
+    """An 8192-token prompt next to a short one: prefilled in 2048-token chunks through the tcgen05 attention kernel
+    (64 context tiles, chunks on top of cached context), decoded through the CUDA graph, against the CPU engine that
+    prefills each prompt whole."""
+    cfg = mc.tiny_mixtral(layers=1, hidden=256, inter=256, heads=2, kv_heads=1, experts=4, vocab=512)
+    cfg.max_position_embeddings = 16384
+    w_gpu = random_weights(cfg, mc.ParallelLayout(), "cuda", seed=5, std=0.05)
+    w_cpu = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=5, std=0.05)
+    for lc, lg in zip(w_cpu.layers, w_gpu.layers):
+        for name in ("attn_norm", "ffn_norm", "wqkv", "wo", "router", "w13", "w2"):
+            getattr(lc, name).copy_(getattr(lg, name).cpu())
+    w_cpu.embed.copy_(w_gpu.embed.cpu()); w_cpu.lm_head.copy_(w_gpu.lm_head.cpu()); w_cpu.final_norm.copy_(w_gpu.final_norm.cpu())
+    pages = (8192 + 64) // 16 + 16
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (8192,), generator=g).tolist(), torch.randint(0, cfg.vocab_size, (37,), generator=g).tolist()]
+    dec_gpu = Decoder(cfg, w_gpu, num_pages=pages, page_size=16, max_pos=8192 + 64)
+    eng = Engine(dec_gpu, EngineConfig(max_batch=4, tpot_ms=1e9, ttft_ms=1e9, use_graphs=True, prefix_cache=False,
+                                       max_prefill_tokens=2048, interleave_prefill_tokens=2048))
+    got = eng.generate(prompts, 4)
+    from skein_b200 import ops
+    torch.cuda.synchronize(); ops.workspace().check_status()
+    dec_cpu = Decoder(cfg, w_cpu, num_pages=pages, page_size=16, max_pos=8192 + 64)
+    want = Engine(dec_cpu, EngineConfig(max_batch=4, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False,
+                                        max_prefill_tokens=16384)).generate(prompts, 4)
+    assert got[1] == want[1], (got[1], want[1])
+    assert got[0][0] == want[0][0] and sum(a == b for a, b in zip(got[0], want[0])) >= 3, (got[0], want[0])
