@@ -326,6 +326,7 @@ def run_pipeline(args, emit_json):
     fb_group = dist.new_group(list(range(world)))        # token feedback travels on its own communicator
     comm = TPComm(tp_group, dev, hidden=cfg.hidden_size, fused_rows=8192) if tp > 1 else None
     B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
+    Gn = max(Gn, args.steps + max(args.warmup, 3) + 8)       # room for a timed loop longer than the generation length
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1
     num_pages = B * blocks_per_seq + 8
     weights = random_weights(cfg, lay, dev, seed=0, std=0.02, shard_embed=True)
@@ -484,7 +485,7 @@ def run_pipeline(args, emit_json):
             "vs_baseline": None, "dtype": "bf16" if not args.fp8_blocks else "bf16 activations; " + fp8_note,
             "data": "synthetic (random-init weights N(0,0.02), random prompt token ids)",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"), "global_batch": B, "seq_len": P,
-                       "gen_len": Gn, "parallelism": f"tp{tp}xpp{npp}", "kv": "paged, block 16", "micro_batches": M,
+                       "gen_len": args.gen, "parallelism": f"tp{tp}xpp{npp}", "kv": "paged, block 16", "micro_batches": M,
                        "l2": "inputs (weights) larger than L2, no flush", "cuda_graph": "per stage and micro-batch",
                        "weights": fp8_note, "repeats": R},
             "prefill_ms": round(prefill_ms, 1), "prefill_first_pass_ms": round(prefill_cold_ms, 1), "prefill_repeatable": prefill_repeatable, "stage_idle_fraction_per_rank": [None if x is None else round(x, 3) for x in idles],
@@ -587,6 +588,8 @@ def main():
                               max_batch=max(256, args.batch))
     lay = mc.ParallelLayout(tp=tp, ep=ep, rank=rank)
     B, P, Gn, ps = args.batch, args.prompt, args.gen, 16
+    # a timed loop longer than the workload's generation length keeps decoding the same sequences: room for those tokens
+    Gn = max(Gn, args.steps + max(args.warmup, 3) + 8)
     blocks_per_seq = (P + Gn + ps - 1) // ps + 1
     num_pages = B * blocks_per_seq + 8
     t0 = time.time()
@@ -830,7 +833,7 @@ def main():
             "dtype": "bf16" if not args.fp8_experts else "bf16 activations, fp8 expert weights",
             "data": "synthetic (random-init weights N(0,0.02), random prompt token ids)",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
-                       "global_batch": B, "seq_len": P, "gen_len": Gn, "parallelism": f"tp{tp}" + (f"xep{ep}" if ep > 1 else ""),
+                       "global_batch": B, "seq_len": P, "gen_len": args.gen, "parallelism": f"tp{tp}" + (f"xep{ep}" if ep > 1 else ""),
                        "kv": "paged, block 16", "l2": "inputs (weights) larger than L2, no flush",
                        "cuda_graph": use_graphs, "comm": ((comm or comm_moe).mode if (comm or comm_moe) else "none"),
                        "in_switch_reduction": bool((comm or comm_moe).heap.mc_ptr) if (comm or comm_moe) else False,
