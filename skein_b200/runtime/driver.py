@@ -203,6 +203,8 @@ class EngineDriver:
     def stop(self, timeout: float = 10.0):
         self._stop.set()
         self._thread.join(timeout)
+        from ..utils import otlp
+        otlp.shutdown()          # ships the spans still queued (no-op without SKEIN_OTLP_ENDPOINT)
 
     def submit(self, prompt_ids, max_new_tokens, sampling: SamplingParams | None = None):
         """Returns (request_id, decision_kind, reason, event_queue or None). Blocks until the driver has decided."""
