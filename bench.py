@@ -100,9 +100,11 @@ def measured_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
-def step_roofline(cfg, tp, ep, B, ctx, fp8_experts, ms_per_step, n_gpus):
+def step_roofline(cfg, tp, ep, B, ctx, fp8_experts, ms_per_step, n_gpus, dp=1):
     """Bytes one decode step must move per GPU (weights that the batch touches, KV read, logits) and over NVLink,
-    and the step time those imply at the measured peaks. The step's target time is the slower of the two."""
+    and the step time those imply at the measured peaks. The step's target time is the slower of the two.
+    dp: ranks that share the batch's sequences among them for attention (data-parallel attention under expert
+    parallelism): a GPU then reads the KV of B / dp sequences only."""
     H, D, I, L, V = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size, cfg.num_layers, cfg.vocab_size
     hq, hkv = cfg.num_heads // tp, max(1, cfg.num_kv_heads // tp)
     attn_w = ((hq + 2 * hkv) * D * H + H * hq * D) * 2
@@ -115,13 +117,18 @@ def step_roofline(cfg, tp, ep, B, ctx, fp8_experts, ms_per_step, n_gpus):
         ffn_w = min(e_local, hit / ep) * 3 * H * (I // tp) * wb + cfg.num_experts * H * 2
     else:
         ffn_w = 3 * H * (I // tp) * wb
-    kv = B * ctx * 2 * hkv * D * 2
+    kv = (B // dp) * ctx * 2 * hkv * D * 2
     per_layer = attn_w + ffn_w + kv
     hbm = L * per_layer + (V // tp) * H * 2 + B * H * 2 * 8 * L        # + lm_head + activations (small)
     # NVLink: per all-reduce every GPU must receive the other ranks' partials of its batch ([B, H] bf16 each) unless the
     # switch adds them; the lower bound with in-switch reduction is one [B, H] per all-reduce
     n_ar = 2 * L if tp > 1 else 0
     nvl = n_ar * B * H * 2
+    if ep > 1 and cfg.is_moe:
+        # token dispatch: a GPU receives the rows routed to its experts from the other ranks ((ep-1)/ep of B top_k / ep rows
+        # under uniform routing); combine: it fetches the expert outputs of its own rows' pairs from their owners
+        own_rows = B // dp
+        nvl += L * (B * cfg.top_k // ep + own_rows * cfg.top_k) * H * 2 * (ep - 1) // ep
     peaks = measured_peaks()
     t_hbm = hbm / (peaks["hbm_gbs"] * 1e9) * 1e3
     t_nvl = nvl / 770e9 * 1e3
@@ -841,7 +848,8 @@ def main():
                                      "over peer memory)" if dec.dp_attention else "replicated across expert-parallel ranks") if ep > 1 else "tensor-parallel",
                        "expert_weights": "fp8 e4m3 1x128" if args.fp8_experts else "bf16",
                        "repeats": R, "ms_per_k_steps_all_repeats": [round(x, 3) for x in all_ms]},
-            "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world),
+            "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world,
+                                      dp=ep if dec.dp_attention else 1),
             "prefill_ms": round(prefill_ms, 1), "prefill_first_pass_ms": round(prefill_cold_ms, 1), "prefill_repeatable": prefill_repeatable,
             "prefill_tokens_per_s": round(B * P / prefill_ms * 1e3, 1),
             "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2),

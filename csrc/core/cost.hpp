@@ -49,6 +49,11 @@ struct Collective {
 
 struct CostConstants {
   double launch_us_per_kernel = 7.0, overshoot_us_per_gb = 1e6;
+  // Device-side fixed cost of one kernel of a decode step beyond its roofline time (ramp-up, tail and the dependent-launch
+  // gap): it is paid inside a CUDA graph too, so graph coverage does not reduce it. Optional, 0 when the file has none.
+  double kernel_overhead_us = 0.0;
+  std::map<std::string, double> collective_fixed_us;                 // collective -> exposed fixed cost per call beyond
+                                                                     // the link latency (flag wait, rank skew); optional
   std::map<std::string, std::map<std::string, double>> peak_tflops;  // device kind -> dtype -> TFLOP/s
   std::map<std::string, std::map<std::string, double>> efficiency;   // op kind -> dtype -> fraction
   std::map<std::string, double> collective_efficiency;
@@ -75,6 +80,8 @@ struct CostConstants {
     try {
       c.launch_us_per_kernel = j.at("launch_us_per_kernel").as_double();
       c.overshoot_us_per_gb = j.at("overshoot_us_per_gb").as_double();
+      if (const Json* h = j.find("kernel_overhead_us")) c.kernel_overhead_us = h->as_double();
+      if (const Json* h = j.find("collective_fixed_us")) c.collective_fixed_us = table(*h);
       for (auto& kv : j.at("peak_tflops").members()) c.peak_tflops[kv.first] = table(kv.second);
       for (auto& kv : j.at("efficiency").members()) c.efficiency[kv.first] = table(kv.second);
       c.collective_efficiency = table(j.at("collective_efficiency"));
@@ -173,6 +180,11 @@ inline uint64_t compute_divisor(LayerKind k, const Placement& pl) {
 inline uint64_t layer_param_elems(const Layer& l) { uint64_t n = 0; for (auto& p : l.params) n += p.numel(); return n; }
 
 // Bytes a decode step must stream for this layer on one device (weights touched + KV read).
+// Pure expert parallelism runs attention data-parallel: every expert-parallel rank attends over its own 1/ep of the
+// step's sequences with the whole (replicated) attention weights, and the MoE blocks exchange tokens. With tensor or
+// pipeline parallelism beside it the attention is replicated across the expert-parallel ranks instead.
+inline uint64_t attention_dp_ways(const Placement& pl) { return (pl.ep > 1 && pl.tp == 1 && pl.pp == 1) ? pl.ep : 1; }
+
 inline double layer_stream_bytes(const Layer& l, const ModelMeta& meta, Dtype wd, Dtype kvd, const Placement& pl, const WorkloadCtx& wl) {
   const double div = (double)std::max<uint64_t>(1, compute_divisor(l.kind, pl));
   double elems = (double)layer_param_elems(l);
@@ -185,7 +197,8 @@ inline double layer_stream_bytes(const Layer& l, const ModelMeta& meta, Dtype wd
   }
   double bytes = (double)dtype_bits(wd) / 8.0 * elems / div;
   if (l.kind == LayerKind::Attention)
-    bytes += (double)dtype_bits(kvd) / 8.0 * 2.0 * l.num_kv_heads * l.head_dim * (double)wl.kv_len * wl.batch / (double)pl.tp;
+    bytes += (double)dtype_bits(kvd) / 8.0 * 2.0 * l.num_kv_heads * l.head_dim * (double)wl.kv_len * wl.batch /
+             (double)(pl.tp * attention_dp_ways(pl));
   (void)meta;
   return bytes;
 }
@@ -196,7 +209,8 @@ inline double compute_time_with_dtype(const Layer& l, const ModelMeta& meta, Dty
   const std::string& kind = cl.device_kind(device);
   const double peak = c.peak_tflops_for(kind, wd);
   const double eff = c.efficiency_for(op_kind_of(l.kind), wd);
-  const double div = (double)std::max<uint64_t>(1, compute_divisor(l.kind, pl));
+  double div = (double)std::max<uint64_t>(1, compute_divisor(l.kind, pl));
+  if (l.kind == LayerKind::Attention || l.kind == LayerKind::Lmhead) div *= (double)attention_dp_ways(pl);   // 1/ep of the rows
   double t = flops / (peak * 1e12 * eff * div) * 1e6;
   auto hb = c.hbm_gbps.find(kind);
   if (hb != c.hbm_gbps.end() && hb->second > 0) {
@@ -211,7 +225,8 @@ inline double compute_time_with_dtype(const Layer& l, const ModelMeta& meta, Dty
     // (bf16 rate) for the KV cache of an attention layer
     double kv_bytes = 0;
     if (l.kind == LayerKind::Attention)
-      kv_bytes = (double)dtype_bits(kvd) / 8.0 * 2.0 * l.num_kv_heads * l.head_dim * (double)wl.kv_len * wl.batch / (double)pl.tp;
+      kv_bytes = (double)dtype_bits(kvd) / 8.0 * 2.0 * l.num_kv_heads * l.head_dim * (double)wl.kv_len * wl.batch /
+                 (double)(pl.tp * attention_dp_ways(pl));
     const double w_bytes = layer_stream_bytes(l, meta, wd, kvd, pl, wl) - kv_bytes;
     t = std::max(t, (w_bytes / share(wd) + kv_bytes / share(Dtype::Bf16)) / (hb->second * 1e9) * 1e6);
   }
@@ -239,9 +254,9 @@ inline double block_compute_time(size_t block, const Graph& ir, Dtype wd, Dtype 
 // for its unfused graph: crates/skein_cost/src/compute.rs:232-242).
 inline uint32_t kernels_per_layer(const Layer& l) {
   switch (l.kind) {
-    case LayerKind::Attention: return 5;  // qkv GEMM, RoPE+KV append, attention, o_proj GEMM, reduce+norm
+    case LayerKind::Attention: return 4;  // qkv GEMM, RoPE + KV append + attention, o_proj GEMM, reduce + norm (+ router)
     case LayerKind::Mlp: return 3;        // gate/up GEMM (SwiGLU epilogue), down GEMM, reduce+norm
-    case LayerKind::Moe: return 5;        // router+plan, gather, grouped gate/up, grouped down, combine+norm
+    case LayerKind::Moe: return 3;        // grouped gate/up (gathers its rows), grouped down, combine + norm
     case LayerKind::RmsNorm: return 0;    // fused into the reduce kernels above
     default: return 1;
   }
@@ -264,7 +279,8 @@ inline double comm_time(const Collective& col, const Cluster& cl, const CostCons
   if (std::isfinite(path.min_bandwidth_gbps)) transfer = factor * (double)col.bytes / (path.min_bandwidth_gbps * eff * 1e9) * 1e6;
   auto ov = c.fused_overlap.find(collective_name(col.kind));
   if (ov != c.fused_overlap.end()) transfer *= std::max(0.0, 1.0 - ov->second);
-  return path.total_latency_us + transfer;
+  auto fx = c.collective_fixed_us.find(collective_name(col.kind));
+  return path.total_latency_us + transfer + (fx == c.collective_fixed_us.end() ? 0.0 : fx->second);
 }
 
 inline std::vector<Collective> collectives_on_device(const Plan& plan, const Graph& ir, size_t device) {
@@ -286,7 +302,8 @@ inline std::vector<Collective> collectives_on_device(const Plan& plan, const Gra
     auto grp = pl.ep_group(device);
     for (auto& l : ir.layers) {
       if (!l.block_idx || block_to_stage(*l.block_idx, nb, pl.pp) != stage || l.kind != LayerKind::Moe) continue;
-      const uint64_t bytes = dtype_bytes_for(plan_act_dtype(plan, l.block_idx), mb * l.top_k * hidden);
+      // dispatch and combine; under data-parallel attention a rank sends only its own rows' copies
+      const uint64_t bytes = dtype_bytes_for(plan_act_dtype(plan, l.block_idx), mb * l.top_k * hidden) / attention_dp_ways(pl);
       out.push_back({CollectiveKind::AllToAll, grp, bytes});
       out.push_back({CollectiveKind::AllToAll, grp, bytes});
     }
@@ -364,7 +381,7 @@ inline double cuda_graph_coverage(const Plan& plan) {
   return 0.0;
 }
 inline double launch_overhead(const Plan& plan, const CostConstants& c, uint32_t kernels) {
-  return c.launch_us_per_kernel * kernels * (1.0 - cuda_graph_coverage(plan));
+  return kernels * (c.launch_us_per_kernel * (1.0 - cuda_graph_coverage(plan)) + c.kernel_overhead_us);
 }
 
 // ---- the model ------------------------------------------------------------------------------------------------

@@ -179,6 +179,10 @@ class Decoder:
         # (combine) over peer memory. The caller must keep a sequence on the same slice for its whole life, because only
         # that rank's cache receives the sequence's new tokens (runtime/engine.py does; a benchmark's rows are static).
         self.dp_attention = False
+        # Set by a caller that pins sequences to ranks (the engine): a decode step that does not fit the data-parallel
+        # path then raises instead of falling back to attention over all rows, which would read cache pages this rank
+        # never wrote.
+        self.dp_strict = False
         self.program = self._load_program()
         self._ops = {name[4:]: getattr(self, name) for name in dir(self) if name.startswith("_op_")}
         missing = sorted({it[1] for it in self.program if it[0] == "op"} - set(self._ops))
@@ -239,19 +243,39 @@ class Decoder:
             self.row_idx = self.row_w = self.owner = self.wts = None
             self.dp = 0          # rows per rank under data-parallel attention (0: every rank holds all rows)
 
+    def dp_ways(self) -> int:
+        """Expert-parallel ranks that share a decode step's rows among them for attention (1: every rank holds all rows)."""
+        lay = self.layout
+        return lay.ep if (self.dp_attention and lay.ep > 1 and lay.tp == 1 and lay.pp == 1 and self.cfg.is_moe) else 1
+
+    def dp_rows_ok(self, B: int, device=None) -> bool:
+        """True when a decode step of B rows can run with data-parallel attention on this layout."""
+        ways, k = self.dp_ways(), self.cfg.top_k
+        if ways == 1 or B % ways:
+            return False
+        per = B // ways
+        # the sampled tokens of a slice are gathered 16 bytes at a time; the fused reduce + router needs one CTA per row
+        return (per % 4 == 0 and ops.can_fuse_route(per, k, device) and B * k <= 2048
+                and (self.comm_moe is None or self.comm_moe.dispatch_fits(per, k)))
+
+    def dp_rows_limit(self, device=None) -> int:
+        """Largest power-of-two number of rows per rank that dp_rows_ok accepts (0: none does)."""
+        best, per = 0, 4
+        while per <= 1024 and self.dp_rows_ok(per * self.dp_ways(), device):
+            best, per = per, per * 2
+        return best
+
     def _dp_rows(self, inp: BatchInputs) -> int:
         """Rows per rank when this step runs with data-parallel attention, else 0."""
-        lay = self.layout
-        if not (self.dp_attention and lay.ep > 1 and lay.tp == 1 and lay.pp == 1 and self.cfg.is_moe):
+        if self.dp_ways() == 1 or inp.is_prefill or inp.seq_of_token is not None or not inp.token_ids.is_cuda:
             return 0
         B = inp.token_ids.shape[0]
-        if inp.is_prefill or inp.seq_of_token is not None or not inp.token_ids.is_cuda or B % lay.ep:
+        if not self.dp_rows_ok(B, inp.token_ids.device):
+            if self.dp_strict:
+                raise RuntimeError(f"a decode step of {B} rows cannot run with data-parallel attention over {self.dp_ways()} "
+                                   "ranks, and its sequences' new tokens are cached on their own rank only")
             return 0
-        per = B // lay.ep
-        # the sampled tokens of a slice are gathered 16 bytes at a time; the fused reduce + router needs one CTA per row
-        if per % 4 or not ops.can_fuse_route(per, self.cfg.top_k, inp.token_ids.device) or B * self.cfg.top_k > 2048:
-            return 0
-        return per
+        return B // self.dp_ways()
 
     @property
     def _multi(self) -> bool:

@@ -277,6 +277,12 @@ class TPComm:
         return ops.reduce_residual_rmsnorm(None, part, gamma, eps)
 
     # ---- expert-parallel token dispatch (data-parallel attention) ---------------------------------------------------
+    def dispatch_fits(self, per: int, k: int) -> bool:
+        """True when ep_dispatch can carry a step of `per` rows per rank with `k` experts per row: the rows and their
+        expert choices share one published buffer, and the expert-sorted pairs of all ranks one receive buffer."""
+        pairs = self.size * per * k
+        return per * self.hidden * 2 + per * k * 4 <= self.fused_rows * self.hidden * 2 and pairs <= 2048 and pairs <= self.fused_rows
+
     def ep_dispatch(self, per: int, k: int, E: int, e_first: int, e_count: int, fill):
         """Token dispatch of an expert-parallel MoE block whose ranks each own `per` of the step's tokens.
 
@@ -288,7 +294,7 @@ class TPComm:
         owner-aware combine take."""
         H, N = self.hidden, self.size
         rows_bytes = per * H * 2
-        if rows_bytes + per * k * 4 > self.fused_rows * H * 2 or N * per * k > 2048 or N * per * k > self.fused_rows:
+        if not self.dispatch_fits(per, k):
             raise ValueError("dispatch does not fit the published buffers")
         b = self.cur
         self.cur ^= 1

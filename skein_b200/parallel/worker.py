@@ -60,6 +60,14 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
     pages = min(pages, max(8, (args.max_seq_len // 16 + 1) * max(1, args.max_batch or art.plan["batching"]["max_batch"]) * 2))
     dec = Decoder(art.cfg, weights, lay, num_pages=pages, page_size=art.plan["kv"]["layout"].get("page_size", 16),
                   max_pos=min(args.max_seq_len, art.cfg.max_position_embeddings), comm=comm, comm_moe=comm_moe)
+    # Pure expert parallelism decodes with data-parallel attention: every rank attends over its own share of the step's
+    # sequences and the MoE blocks exchange tokens over peer memory (SKEIN_EP_DP_ATTENTION=0: attention over all
+    # sequences on every rank, the expert outputs all-reduced).
+    if (device.type == "cuda" and comm_moe is not None and comm_moe.mode != "nccl" and lay.ep > 1 and lay.tp == 1 and pp_info is None
+            and art.cfg.is_moe and os.environ.get("SKEIN_EP_DP_ATTENTION", "1") != "0"):
+        dec.dp_attention = True
+        if dec.dp_rows_limit(device) == 0:      # e.g. the fused router is switched off: nothing to dispatch from
+            dec.dp_attention = False
     if pp_info is not None:
         from .pp import PipelineStage
         dec = PipelineStage(dec, lay, *pp_info)
@@ -148,7 +156,7 @@ def run_rank(args) -> int:
             if tp > 1:
                 comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size, fused_rows=rows)
             if ep > 1:
-                comm_moe = TPComm(stage_group, device, hidden=art.cfg.hidden_size)
+                comm_moe = TPComm(stage_group, device, hidden=art.cfg.hidden_size, fused_rows=rows)
         elif tp > 1 or ep > 1:
             raise SystemExit("tensor/expert-parallel serving needs GPUs (CPU ranks are covered by skein_b200.parallel.local)")
         if pp > 1:

@@ -88,26 +88,39 @@ class Engine:
         if decoder.num_pages <= 0:
             raise ValueError("the decoder was built without a KV page pool")
         self.kv = core.KvBlockManager(decoder.num_pages, decoder.page_size, c.prefix_cache)
+        # Expert parallelism with data-parallel attention: each decoding sequence belongs to one rank's slice of the
+        # step's rows for its whole life (only that rank's cache receives its new tokens). Every rank's engine takes
+        # the same decisions, so the assignment needs no communication. A slice is never larger than
+        # ceil(max_batch / ranks) rows (a sequence joins the least loaded slice), so bounding max_batch bounds the slices
+        # to what the dispatch kernels carry.
+        inner = getattr(decoder, "dec", decoder)
+        self._dp = inner.dp_ways() if hasattr(inner, "dp_ways") else 1
+        max_batch = c.max_batch
+        if self._dp > 1:
+            inner.dp_strict = True
+            dev = getattr(inner, "device", None)
+            if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+                from .runner import BUCKETS
+                limit = inner.dp_rows_limit(dev)
+                if limit == 0:
+                    raise ValueError("data-parallel attention is on, but no decode step fits its dispatch buffers")
+                max_batch = min(max_batch, limit * self._dp, BUCKETS[-1])
+        self.max_batch = max_batch
         self.batcher = core.ContinuousBatcher(
-            max_batch=c.max_batch, chunk_tokens=c.chunk_tokens, ttft_ms=c.ttft_ms, tpot_ms=c.tpot_ms,
+            max_batch=max_batch, chunk_tokens=c.chunk_tokens, ttft_ms=c.ttft_ms, tpot_ms=c.tpot_ms,
             decode_us_at_b1=c.decode_us_at_b1, batch_exponent=c.batch_exponent,
             prefill_per_token_us=c.prefill_per_token_us, kv=self.kv, max_prefill_tokens=c.max_prefill_tokens,
             interleave_prefill_tokens=c.interleave_prefill_tokens)
         self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
         self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
         if c.warm_graphs:
-            self.runner.capture_buckets(c.max_batch)
+            self.runner.capture_buckets(max_batch)
         self.metrics = metrics or core.MetricsRegistry()
         self.clock = clock or (lambda: int(time.monotonic() * 1000))
         self._next_id = 1
         self._step = 0
         self._graph_seen = (0, 0)   # runner.graph_captures / graph_replays already added to the metrics
         self._sampling = {}      # request id -> SamplingParams (only requests that sample)
-        # Expert parallelism with data-parallel attention: each decoding sequence belongs to one rank's slice of the
-        # step's rows for its whole life (only that rank's cache receives its new tokens). Every rank's engine takes
-        # the same decisions, so the assignment needs no communication.
-        inner = getattr(decoder, "dec", decoder)
-        self._dp = inner.layout.ep if getattr(inner, "dp_attention", False) else 1
         self._dp_of: dict[int, int] = {}
         self._dp_load = [0] * self._dp
         self._wait_ns_seen = 0

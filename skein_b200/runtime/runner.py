@@ -163,7 +163,13 @@ class ModelRunner:
         if not self.use_graphs:
             return 0
         n = 0
+        inner = getattr(self.dec, "dec", self.dec)
+        dp = inner.dp_ways() if hasattr(inner, "dp_ways") else 1
         for b in BUCKETS:
+            if dp > 1 and not inner.dp_rows_ok(b, getattr(inner, "device", None)):
+                if b >= max_batch:      # data-parallel attention: only steps of equal slices per rank ever run
+                    break
+                continue
             bk = self.bucket(b)
             if (False, sampling) not in bk.graphs:
                 self.load_decode_inputs(bk, [], [], [], [])

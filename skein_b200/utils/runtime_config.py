@@ -40,6 +40,7 @@ _FIELDS = {
     "profile": ("SKEIN_PROFILE", int, (0, 1, 2, 3)),
     "attn_decode": ("SKEIN_ATTN_DECODE", str, ("auto", "tc", "mma", "scalar")),
     "attn_splits": ("SKEIN_ATTN_SPLITS", int, None),
+    "ep_dp_attention": ("SKEIN_EP_DP_ATTENTION", _bool, None),
     "fuse_route": ("SKEIN_FUSE_ROUTE", _bool, None),
     "fuse_rope": ("SKEIN_FUSE_ROPE", _bool, None),
     "gemm_aligned": ("SKEIN_GEMM_ALIGNED", _bool, None),
@@ -60,6 +61,7 @@ class RuntimeConfig:
     profile: int = 0               # 0 off, 1 CUDA-event region timers, 2 + NVTX ranges, 3 + Chrome trace
     attn_decode: str = "auto"      # decode attention kernel: tcgen05 / mma.sync chosen per launch, or one of them forced
     attn_splits: int = 0           # split-KV factor (0: chosen per launch)
+    ep_dp_attention: bool = True   # pure expert parallelism: each rank attends over its own share of the sequences
     fuse_route: bool = True        # router inside the post-attention reduce kernel
     fuse_rope: bool = True         # RoPE + KV append inside the decode attention kernel
     gemm_aligned: bool = True      # tile-aligned K pieces when there are fewer tiles than SMs

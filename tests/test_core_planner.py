@@ -22,7 +22,7 @@ B200_8 = (ROOT / "cluster/b200_8x.toml").read_text()
 TRACE = (ROOT / "cluster/sample_trace.jsonl").read_text()
 DRIFT = (ROOT / "models/mixtral_8x7b_drift.toml").read_text()
 CONST = (ROOT / "cluster/cost_constants.toml").read_text()
-REF_CONST = CONST.split("[hbm_gbps]")[0] + "[efficiency.gemm]" + CONST.split("[efficiency.gemm]")[1].split("[fused_overlap]")[0] + \
+REF_CONST = CONST.split("[hbm_gbps]")[0].replace("kernel_overhead_us = 6.5", "kernel_overhead_us = 0.0") + "[efficiency.gemm]" + CONST.split("[efficiency.gemm]")[1].split("[fused_overlap]")[0] + \
     "[representative_workload]" + CONST.split("[representative_workload]")[1]
 
 
@@ -219,6 +219,35 @@ def test_b200_roofline_and_overlap_terms():
     # ... and would not if the fp8 kernel reached less than half of the share of the bf16 one (fp8 then buys memory only)
     slow8 = CONST.replace("fp8_e4m3 = 0.70", "fp8_e4m3 = 0.42")
     assert core.cost_breakdown(p8, CFG, B200_8, slow8, 0)["compute"] >= with_roof["compute"]
+
+
+def test_b200_constants_reproduce_measured_decode_steps():
+    """The constants file carries fits to decode steps measured on B200s (Mixtral-8x7B, CUDA graphs, context about 600 for
+    the tensor-parallel runs of 64 sequences and about 1040 for the expert-parallel runs of 256 with e4m3 weights): the
+    model must land within 10 % of each of them, so that a change of a term or a constant that breaks the fit shows."""
+    def predict(n, kv, **kw):
+        cl = (ROOT / f"cluster/b200_{n}x.toml").read_text()
+        c = CONST.replace("decode_kv_tokens = 2048", f"decode_kv_tokens = {kv}")
+        b = core.cost_breakdown(make_plan(cuda_graphs=True, classes=4, **kw), CFG, cl, c, 0)
+        return b
+    for n, ms in ((1, 16.99), (2, 9.95), (4, 5.79), (8, 4.44)):
+        b = predict(n, 608, tp=n, max_batch=64)
+        assert b["kernels"] == 229                                 # 7 launches per block + embedding, lm_head, 3 per step
+        assert abs(b["total"] / 1e3 - ms) / ms < 0.10, (n, b)
+    for n, ms in ((8, 7.66), (4, 10.28)):
+        b = predict(n, 1040, ep=n, max_batch=256, dtype="fp8_e4m3")
+        assert abs(b["total"] / 1e3 - ms) / ms < 0.10, (n, b)
+    # pure expert parallelism attends data-parallel: a rank streams the KV of its own 1/ep of the sequences, while with
+    # tensor parallelism beside it every expert-parallel group attends over the whole batch
+    one = predict(8, 1040, tp=8, max_batch=256)
+    ep8 = predict(8, 1040, ep=8, max_batch=256)
+    mix = predict(8, 1040, tp=2, ep=4, max_batch=256)
+    kv_full = 256 * 1040 * 2 * 8 * 128 * 2 * 32 / 6552e9 * 1e6      # us to stream the whole batch's KV on one GPU
+    assert ep8["compute"] < one["compute"] + kv_full               # nowhere near a replicated read of the KV
+    assert mix["compute"] > kv_full / 2                            # tp2 x ep4: half of the KV per GPU
+    # the fixed cost per kernel is not hidden by CUDA graphs, the host launch cost is
+    g, e = predict(1, 608, tp=1, max_batch=64), core.cost_breakdown(make_plan(tp=1, max_batch=64), CFG, (ROOT / "cluster/b200_1x.toml").read_text(), CONST, 0)
+    assert 229 * 6.5 <= g["launch"] < 229 * 6.5 + 40 and e["launch"] > g["launch"] + 229 * 2.0
 
 
 # ---- planner ----------------------------------------------------------------------------------------------------------

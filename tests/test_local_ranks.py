@@ -119,3 +119,45 @@ def test_expert_parallel_ranks_reproduce_the_unsharded_model(tp, ep):
     results, errors = run_ranks(tp * ep, rank_fn)
     assert not any(errors)
     assert all(r == want for r in results)
+
+
+def test_engine_rows_under_data_parallel_attention():
+    """Pure expert parallelism with data-parallel attention: the engine gives every decoding sequence to one rank's slice
+    of the step's rows for its whole life, pads the slices to one size and runs the same steps on every rank. On CPU
+    ranks the decoder attends over all rows, so the tokens must equal the unsharded engine's exactly; the test covers
+    the row layout, the padding rows inside a step and the release of a finished sequence's slot."""
+    from skein_b200.runtime.engine import Engine, EngineConfig
+    cfg = mc.tiny_mixtral(layers=2, hidden=128, inter=256, heads=4, kv_heads=2, experts=4, vocab=256)
+    full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=11, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (5, 9, 7, 3, 6)]
+    ecfg = lambda: EngineConfig(max_batch=16, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False)  # noqa: E731
+    want = Engine(Decoder(cfg, full, num_pages=96, page_size=16, max_pos=128), ecfg()).generate(prompts, 4)
+
+    def body(rank, comm):
+        lay = mc.ParallelLayout(tp=1, ep=2, rank=rank)
+        dec = Decoder(cfg, shard_model(full, cfg, lay, "cpu"), lay, num_pages=96, page_size=16, max_pos=128, comm_moe=comm)
+        assert dec.dp_ways() == 1
+        dec.dp_attention = True
+        assert dec.dp_ways() == 2
+        eng = Engine(dec, ecfg())
+        assert eng._dp == 2 and dec.dp_strict
+        out = eng.generate(prompts, 4)
+        assert eng._dp_load == [0, 0] and not eng._dp_of          # every finished sequence gave its slot back
+        rows = eng._dp_layout([11, 12, 13, 14, 15])               # least loaded slice first, ties to the lower rank
+        assert rows == [11, 13, 15, 0, 12, 14, 0, 0]
+        eng._dp_release(13)
+        assert eng._dp_layout([11, 12, 14, 15, 16]) == [11, 15, 16, 0, 12, 14, 0, 0]    # a sequence keeps its rank
+        return out
+
+    results, _ = run_ranks(2, body)
+    assert results[0] == want and results[1] == want
+    # tensor parallelism beside the experts: attention is not data-parallel, whatever the flag says
+    lay = mc.ParallelLayout(tp=2, ep=2, rank=0)
+    assert lay.ep == 2
+
+    class _C:       # a communicator is only stored by the constructor
+        size = 4
+    dec = Decoder(cfg, shard_model(full, cfg, lay, "cpu"), lay, num_pages=8, page_size=16, max_pos=64, comm=_C(), comm_moe=_C())
+    dec.dp_attention = True
+    assert dec.dp_ways() == 1 and not dec.dp_rows_ok(16)
