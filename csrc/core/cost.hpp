@@ -52,6 +52,12 @@ struct CostConstants {
   // Device-side fixed cost of one kernel of a decode step beyond its roofline time (ramp-up, tail and the dependent-launch
   // gap): it is paid inside a CUDA graph too, so graph coverage does not reduce it. Optional, 0 when the file has none.
   double kernel_overhead_us = 0.0;
+  // Pipeline parallelism as this runtime executes a decode step: the batch goes through the stages as
+  // pp x pipeline_micro_per_stage micro-batches, and (pipeline_drain) the step ends when the last of them has left the
+  // last stage. 0 micro-batches per stage (no [pipeline] table) keeps the reference's form: every stage runs the whole
+  // batch once and idles for (pp-1)/pp of that time.
+  uint32_t pipeline_micro_per_stage = 0;
+  bool pipeline_drain = true;
   std::map<std::string, double> collective_fixed_us;                 // collective -> exposed fixed cost per call beyond
                                                                      // the link latency (flag wait, rank skew); optional
   std::map<std::string, std::map<std::string, double>> peak_tflops;  // device kind -> dtype -> TFLOP/s
@@ -82,6 +88,10 @@ struct CostConstants {
       c.overshoot_us_per_gb = j.at("overshoot_us_per_gb").as_double();
       if (const Json* h = j.find("kernel_overhead_us")) c.kernel_overhead_us = h->as_double();
       if (const Json* h = j.find("collective_fixed_us")) c.collective_fixed_us = table(*h);
+      if (const Json* h = j.find("pipeline")) {
+        c.pipeline_micro_per_stage = (uint32_t)h->at("micro_batches_per_stage").as_int();
+        if (h->has("drain_per_step")) c.pipeline_drain = h->at("drain_per_step").as_int() != 0;
+      }
       for (auto& kv : j.at("peak_tflops").members()) c.peak_tflops[kv.first] = table(kv.second);
       for (auto& kv : j.at("efficiency").members()) c.efficiency[kv.first] = table(kv.second);
       c.collective_efficiency = table(j.at("collective_efficiency"));
@@ -404,6 +414,26 @@ class CostModel {
   CostBreakdown per_device(const Plan& plan, const Graph& ir, const Cluster& cl, const WorkloadCtx& wl, size_t device) const {
     CostBreakdown b;
     if (!Placement::from_plan(plan).holds(device)) return b;
+    const uint32_t pp = std::max(1u, plan.parallelism.pp);
+    if (pp > 1 && c_.pipeline_micro_per_stage > 0) {
+      // M micro-batches of batch / M rows each cross this stage one after the other; a step that drains ends pp - 1
+      // stage times after the first stage has sent its last one
+      const uint32_t M = std::max(1u, std::min(pp * c_.pipeline_micro_per_stage, wl.batch));
+      Plan mp = plan;
+      mp.batching.max_batch = (wl.batch + M - 1) / M;
+      WorkloadCtx mwl = wl;
+      mwl.batch = mp.batching.max_batch;
+      const double stage = compute_on_device(mp, ir, cl, mwl, device);
+      double comm = 0;
+      for (auto& col : collectives_on_device(mp, ir, device)) comm += comm_time(col, cl, c_);
+      const double launch = launch_overhead(plan, c_, kernels_per_step_on_device(ir, plan, device));
+      b.compute = M * stage;
+      b.comm = M * comm;
+      b.launch = M * launch;
+      b.bubble = c_.pipeline_drain ? (pp - 1.0) * (stage + comm + launch) : 0.0;
+      b.memory = memory_penalty(plan, ir, cl, c_, device);
+      return b;
+    }
     b.compute = compute_on_device(plan, ir, cl, wl, device);
     for (auto& col : collectives_on_device(plan, ir, device)) b.comm += comm_time(col, cl, c_);
     b.memory = memory_penalty(plan, ir, cl, c_, device);

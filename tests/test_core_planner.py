@@ -245,6 +245,19 @@ def test_b200_constants_reproduce_measured_decode_steps():
     kv_full = 256 * 1040 * 2 * 8 * 128 * 2 * 32 / 6552e9 * 1e6      # us to stream the whole batch's KV on one GPU
     assert ep8["compute"] < one["compute"] + kv_full               # nowhere near a replicated read of the KV
     assert mix["compute"] > kv_full / 2                            # tp2 x ep4: half of the KV per GPU
+    # pipeline parallelism as the runtime runs it: Llama-3-70B on TP4 x PP2, 32 sequences, measured 18.3 ms per drained step
+    # (12.0 ms with the pipeline kept full); a stage streams its weights once per micro-batch, so PP buys memory, not time
+    cl8 = (ROOT / "cluster/b200_8x.toml").read_text()
+    c = CONST.replace("decode_kv_tokens = 2048", "decode_kv_tokens = 1100")
+    pl = make_plan(tp=4, pp=2, max_batch=32, cuda_graphs=True, classes=4, cfg=LLAMA, layers=80)
+    b = core.cost_breakdown(pl, LLAMA, cl8, c, 0)
+    assert abs(b["total"] / 1e3 - 18.3) / 18.3 < 0.12, b
+    full = core.cost_breakdown(pl, LLAMA, cl8, c.replace("drain_per_step = 1", "drain_per_step = 0"), 0)
+    assert full["bubble"] == 0 and abs(full["total"] / 1e3 - 12.0) / 12.0 < 0.12, full
+    assert abs(b["bubble"] - (b["compute"] + b["comm"] + b["launch"]) / 2) < 1e-6        # (pp - 1) of the M = 2 stage passes
+    for n in (2, 4, 8):                                            # on one NVSwitch domain the latency planner shards, never pipelines
+        r = core.extract_plan(CFG, (ROOT / f"cluster/b200_{n}x.toml").read_text(), TRACE, DRIFT, CONST)
+        assert json.loads(r["plan_json"])["parallelism"] == {"tp": n, "pp": 1, "ep": 1}
     # the fixed cost per kernel is not hidden by CUDA graphs, the host launch cost is
     g, e = predict(1, 608, tp=1, max_batch=64), core.cost_breakdown(make_plan(tp=1, max_batch=64), CFG, (ROOT / "cluster/b200_1x.toml").read_text(), CONST, 0)
     assert 229 * 6.5 <= g["launch"] < 229 * 6.5 + 40 and e["launch"] > g["launch"] + 229 * 2.0
