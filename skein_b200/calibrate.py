@@ -126,9 +126,8 @@ def sample_prompts(lengths: list[int], n: int, strategy: str, seed: int) -> list
 
 
 # ---- byte-stable writers ---------------------------------------------------------------------------------------------
-def _fmt(v: float) -> str:
-    s = repr(float(v))
-    return s
+def _fmt(v) -> str:
+    return repr(v) if isinstance(v, int) and not isinstance(v, bool) else repr(float(v))
 
 
 def rewrite_toml_values(text: str, updates: dict) -> str:
@@ -185,6 +184,29 @@ def write_cost_constants(text: str, efficiencies: dict, collective_eff: dict | N
     if launch_us is not None:
         upd[("", "launch_us_per_kernel")] = launch_us
     return rewrite_toml_values(text, upd)
+
+
+def fit_fixed_costs(plan_json: str, model_config_json: str, cluster_toml: str, cost_text: str, measured_step_ms: float,
+                    kv_tokens: int | None = None) -> dict:
+    """Fits the fixed-cost entry of the cost constants that a measured decode step of `plan_json` identifies, so that the
+    model reproduces the measurement: `kernel_overhead_us` from a one-GPU plan (everything else in its step is streaming
+    time), `collective_fixed_us.ring_allreduce` from a tensor-parallel plan, `collective_fixed_us.alltoall` from a purely
+    expert-parallel one. `kv_tokens` is the context length of the measured step (default: the file's decode_kv_tokens).
+    Returns {(section, key): value} for rewrite_toml_values."""
+    plan = json.loads(plan_json)
+    par = plan["parallelism"]
+    tp, pp, ep = int(par["tp"]), int(par["pp"]), int(par["ep"])
+    if pp > 1 or (tp > 1 and ep > 1):
+        raise CalibrationError("a fixed cost is fitted from a step of one GPU, of tensor parallelism or of expert parallelism alone")
+    key = ("", "kernel_overhead_us") if tp == ep == 1 else ("collective_fixed_us", "ring_allreduce" if tp > 1 else "alltoall")
+    text = rewrite_toml_values(cost_text, {key: 0.0})
+    if kv_tokens is not None:
+        text = rewrite_toml_values(text, {("representative_workload", "decode_kv_tokens"): int(kv_tokens)})
+    b = core.cost_breakdown(plan_json, model_config_json, cluster_toml, text, 0)
+    n = b["kernels"] if key[1] == "kernel_overhead_us" else b["collectives"]
+    if n <= 0:
+        raise CalibrationError("the plan has nothing to attach the fixed cost to")
+    return {key: round(max(0.0, measured_step_ms * 1e3 - b["total"]) / n, 2)}
 
 
 def write_drift_table(text: str, measured: dict) -> str:

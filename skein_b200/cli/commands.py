@@ -152,6 +152,15 @@ def cmd_calibrate(args, emit) -> int:
         hbm = consts.get("hbm_gbps", {}).get(args.hardware, 6552.0)
         stream = cal.measure_stream_efficiency(hbm) if "stream_efficiency" in consts else None
         Path(args.out_cost).write_text(cal.write_cost_constants(cost_text, eff, stream_efficiency=stream))
+    fitted = {}
+    if getattr(args, "fit_step_ms", None) is not None:
+        if not (args.fit_plan and args.fit_cluster):
+            raise ValueError("--fit-step-ms needs --fit-plan and --fit-cluster")
+        pp_ = Path(args.fit_plan)
+        plan_text = _read(pp_ / "plan.json") if pp_.is_dir() else _read(pp_)
+        cost_now = _read(args.out_cost)
+        fitted = cal.fit_fixed_costs(plan_text, _read(args.model), _read(args.fit_cluster), cost_now, args.fit_step_ms, args.fit_kv_tokens)
+        Path(args.out_cost).write_text(cal.rewrite_toml_values(cost_now, fitted))
     if args.candidate_artifact:
         from ..compile import parity
         from ..compile.artifact import Artifact
@@ -177,7 +186,7 @@ def cmd_calibrate(args, emit) -> int:
         out = args.autotune_out or (art.path / "cache" / "kernel_configs.json" if art is not None else "kernel_configs.json")
         tuned = cal.autotune_decode_gemms(cfg, tp, args.autotune_batch, out)
     emit(args, {"efficiencies": {f"{k[0]}.{k[1]}": v for k, v in eff.items()}, "drift_entries": len(drift),
-                "tuned_gemms": tuned},
+                "tuned_gemms": tuned, "fitted": {".".join(x for x in k if x): v for k, v in fitted.items()}},
          f"calibrated {len(eff)} kernel efficiencies, {len(drift)} drift entries, {len(tuned)} tuned GEMM shapes")
     return 0
 

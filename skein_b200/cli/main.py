@@ -108,6 +108,12 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--candidate-artifact", default=None)
     k.add_argument("--out-cost", default="cluster/cost_constants.toml")
     k.add_argument("--out-drift-dir", default="models/")
+    k.add_argument("--fit-step-ms", type=float, default=None,
+                   help="measured decode-step time of --fit-plan on --fit-cluster: fits the fixed cost it identifies (per kernel "
+                        "from a one-GPU plan, per all-reduce from a tensor-parallel one, per exchange from an expert-parallel one)")
+    k.add_argument("--fit-plan", default=None, help="plan JSON (or an artifact directory) the step was measured with")
+    k.add_argument("--fit-cluster", default=None, help="cluster TOML the step was measured on")
+    k.add_argument("--fit-kv-tokens", type=int, default=None, help="context length of the measured step")
     k.add_argument("--autotune", action="store_true",
                    help="also measure GEMM launch configurations for the decode step and store them in the candidate "
                         "artifact's cache/kernel_configs.json (or --autotune-out)")

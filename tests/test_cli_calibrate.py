@@ -252,6 +252,48 @@ def test_cost_writer_is_byte_stable_and_preserves_unmeasured_entries():
     assert t2 == "[a]\nx = 3.5   # keep me\nz = 7.0\n[b]\ny = 2.0\n"
 
 
+def test_fixed_costs_fitted_from_a_measured_step(tmp_path, capsys):
+    """`calibrate --fit-step-ms`: the measured step of a one-GPU plan gives the per-kernel fixed cost, a tensor-parallel one the
+    fixed cost per all-reduce, an expert-parallel one the cost per exchange; the writer touches that entry only."""
+    from skein_b200 import core
+    cfg = (ROOT / "configs/mixtral_8x7b_config.json").read_text()
+    text = (ROOT / "cluster/cost_constants.toml").read_text()
+    meta = json.loads(core.model_meta(cfg))
+
+    def plan(tp=1, ep=1, pp=1, batch=64, dtype="bf16"):
+        return json.dumps({
+            "parallelism": {"tp": tp, "pp": pp, "ep": ep}, "kv": {"layout": {"kind": "paged", "page_size": 16}, "kv_sharded": True},
+            "batching": {"kind": "continuous", "max_batch": batch},
+            "dtype_map": {"per_layer": [{"weight": dtype, "activation": "bf16", "kv_cache": "bf16"}] * meta["num_layers"]},
+            "execution": {"cuda_graphs": {"enable": True, "capture_classes": [{"batch_size": 1 + i, "kv_class": 0} for i in range(4)]},
+                          "spec_decode": {"enable": False, "draft": None}, "prefix_cache": {"enable": True, "reuse_policy": "lru_by_last_access"}},
+            "disaggregation": None, "model_meta": meta})
+    cl = lambda n: (ROOT / f"cluster/b200_{n}x.toml").read_text()  # noqa: E731
+    one = cal.fit_fixed_costs(plan(), cfg, cl(1), text, 16.99, kv_tokens=608)
+    assert list(one) == [("", "kernel_overhead_us")] and 6.0 < one[("", "kernel_overhead_us")] < 7.0
+    ar = cal.fit_fixed_costs(plan(tp=2), cfg, cl(2), text, 9.95, kv_tokens=608)
+    assert list(ar) == [("collective_fixed_us", "ring_allreduce")] and 6.0 < ar[("collective_fixed_us", "ring_allreduce")] < 11.0
+    a2a = cal.fit_fixed_costs(plan(ep=8, batch=256, dtype="fp8_e4m3"), cfg, cl(8), text, 7.66, kv_tokens=1040)
+    assert 50.0 < a2a[("collective_fixed_us", "alltoall")] < 66.0
+    # a step faster than the model's streaming time fits a zero, never a negative cost
+    assert cal.fit_fixed_costs(plan(), cfg, cl(1), text, 1.0)[("", "kernel_overhead_us")] == 0.0
+    with pytest.raises(cal.CalibrationError, match="one GPU"):
+        cal.fit_fixed_costs(plan(tp=2, ep=4), cfg, cl(8), text, 5.0)
+    # through the command line: only the fitted entry of the file changes
+    cost, pj = tmp_path / "cost.toml", tmp_path / "plan.json"
+    cost.write_text(text)
+    pj.write_text(plan(tp=8))
+    corpus = tmp_path / "corpus.toml"
+    corpus.write_text(CORPUS)
+    assert main(["--output", "json", "calibrate", "--hardware", "b200", "--model", str(ROOT / "configs/mixtral_8x7b_config.json"),
+                 "--corpus", str(corpus), "--out-cost", str(cost), "--fit-step-ms", "4.44", "--fit-plan", str(pj),
+                 "--fit-cluster", str(ROOT / "cluster/b200_8x.toml"), "--fit-kv-tokens", "608"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    new = cost.read_text()
+    changed = [(a, b) for a, b in zip(text.split("\n"), new.split("\n")) if a != b]
+    assert len(changed) == 1 and changed[0][0] == "ring_allreduce = 8.0" and rep["fitted"]["collective_fixed_us.ring_allreduce"] > 8.0
+
+
 def test_drift_writer_monotonic():
     text = (ROOT / "models/mixtral_8x7b_drift.toml").read_text()
     a = cal.write_drift_table(text, {(3, "weight", "fp8_e4m3"): 0.02})
