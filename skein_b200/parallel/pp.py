@@ -55,6 +55,30 @@ def make_groups(layout_dims, rank: int, backend=None):
     return my_tp, me.pp_group(), my_pp
 
 
+def make_feedback_group(layout_dims, rank: int, backend=None):
+    """A second communicator over every pipeline group, for the sampled tokens that travel from the last stage back to the
+    others: on a communicator of its own the feedback never queues behind activation traffic. Every rank must call this
+    with the same arguments (after make_groups). Returns this rank's group, or None without pipeline parallelism."""
+    tp, pp, ep = layout_dims
+    mine, seen = None, set()
+    for r in range(tp * pp * ep):
+        g = tuple(ParallelLayout(tp=tp, pp=pp, ep=ep, rank=r).pp_group())
+        if g not in seen:
+            seen.add(g)
+            grp = dist.new_group(list(g), backend=backend) if pp > 1 else None
+            if rank in g:
+                mine = grp
+    return mine
+
+
+class _Flight:
+    """One decode step of a group of sequences on its way through the pipeline (PipelineStage.launch / collect)."""
+    __slots__ = ("tokens", "sends", "recv")
+
+    def __init__(self):
+        self.tokens, self.sends, self.recv = None, (), None
+
+
 def _rows(inp: BatchInputs, lo: int, hi: int) -> BatchInputs:
     """Rows lo..hi of a decode step's inputs (views of the same static buffers)."""
     return BatchInputs(token_ids=inp.token_ids[lo:hi], positions=inp.positions[lo:hi], block_table=inp.block_table[lo:hi],
@@ -95,6 +119,7 @@ class PipelineStage:
         fused = decoder.comm is None or decoder.comm.mode != "nccl"
         self.use_graphs = (self.device.type == "cuda" and fused) if use_graphs is None else (use_graphs and self.device.type == "cuda")
         self._graphs: dict = {}
+        self.feedback_group = None      # communicator of the sampled tokens (launch / collect); None: the pp group itself
         self.stage_busy_events = []     # (start, end) CUDA events around this stage's compute, when `time_stages` is set
         self.time_stages = False
 
@@ -146,6 +171,34 @@ class PipelineStage:
         if not self.last:
             sg.pending_send = dist.isend(sg.out, dst=self.next)
         return sg.out, sg.logits
+
+    # ---- continuous serving: several groups of sequences in flight at once ---------------------------------------------
+    def launch(self, inp: BatchInputs, sampling, key) -> _Flight:
+        """Enqueue this stage's share of one decode step of a group of sequences and return without waiting for the
+        step's tokens. Every stage calls launch and, later, collect for the same groups in the same order. The last stage
+        sends the sampled tokens to every other stage on the feedback communicator as soon as they exist; the others post
+        the receive now and wait for it in collect, so a stage keeps working on other groups while this one's tokens
+        travel. `key` names the group (its stage compute is captured as a CUDA graph from the second sight on)."""
+        out, _ = self._run_stage(inp, sampling, key)
+        f = _Flight()
+        grp = self.feedback_group if self.feedback_group is not None else self.pp_group
+        if self.last:
+            f.tokens = out.clone()      # the graph's output buffer is rewritten by the next replay
+            f.sends = [dist.isend(f.tokens, dst=r, group=grp) for r in self.pp_ranks[:-1]]
+        else:
+            f.tokens = torch.empty(inp.token_ids.shape[0], dtype=torch.int32, device=self.device)
+            f.recv = dist.irecv(f.tokens, src=self.pp_ranks[-1], group=grp)
+        return f
+
+    def collect(self, f: _Flight) -> torch.Tensor:
+        """The sampled tokens of a launched step (a device tensor; on CUDA the current stream waits for their arrival)."""
+        if f.recv is not None:
+            f.recv.wait()
+            f.recv = None
+        for w in f.sends:
+            w.wait()
+        f.sends = ()
+        return f.tokens
 
     def _n_out_rows(self, inp: BatchInputs) -> int:
         return inp.logit_rows.shape[0] if (inp.is_prefill and inp.logit_rows is not None) else inp.token_ids.shape[0]

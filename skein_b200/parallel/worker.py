@@ -70,7 +70,8 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
             dec.dp_attention = False
     if pp_info is not None:
         from .pp import PipelineStage
-        dec = PipelineStage(dec, lay, *pp_info)
+        dec = PipelineStage(dec, lay, *pp_info[:2])
+        dec.feedback_group = pp_info[2] if len(pp_info) > 2 else None
     batching = art.plan["batching"]
     fused = all(c is None or c.mode != "nccl" for c in (comm, comm_moe))
     ecfg = EngineConfig(max_batch=args.max_batch or batching["max_batch"], chunk_tokens=batching.get("chunk_tokens", 0),
@@ -79,6 +80,9 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
                         use_graphs=(device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused
                                     and pp_info is None and not getattr(args, "no_cuda_graphs", False)))
     ecfg.warm_graphs = ecfg.use_graphs      # every batch bucket is captured while the server starts, not under load
+    # pipeline parallelism: one group of sequences per stage kept in flight across engine steps instead of a pipeline
+    # drained at the end of every step
+    ecfg.pp_continuous = pp_info is not None and os.environ.get("SKEIN_PP_CONTINUOUS", "0") == "1"
     if args.workload:
         from .. import core
         text = open(args.workload).read()
@@ -160,7 +164,7 @@ def run_rank(args) -> int:
         elif tp > 1 or ep > 1:
             raise SystemExit("tensor/expert-parallel serving needs GPUs (CPU ranks are covered by skein_b200.parallel.local)")
         if pp > 1:
-            pp_info = (pp_ranks, pp_group)
+            pp_info = (pp_ranks, pp_group, pp_mod.make_feedback_group(art.layout_dims, rank))
     engine = build_engine(art, rank, device, comm, args, comm_moe, pp_info)
     if beat is not None:
         beat.step_started_at = lambda: engine.step_started_at     # a rank stuck inside a step stops beating

@@ -49,6 +49,8 @@ class EngineConfig:
     use_graphs: bool = True
     warm_graphs: bool = False          # capture the decode graph of every batch bucket up to max_batch at start-up
     prelaunch: bool = True             # enqueue the next decode step as soon as this one's tokens are accepted (see _prelaunch)
+    pp_continuous: bool = False        # pipeline parallelism: keep one group of sequences per stage in flight across steps
+                                       # instead of draining the pipeline at the end of every step (see _run_continuous)
     drift_baseline: tuple = ()         # prompt lengths the plan was extracted for (workload drift monitor)
     drift_threshold_kl: float = 0.05
 
@@ -127,6 +129,14 @@ class Engine:
         # the next decode step, already enqueued on the device: (bucket, request ids as planned, rows as laid out, sampling rows)
         self._pre = None
         self._prelaunch_ok = c.prelaunch and getattr(decoder, "n_stages", 1) == 1
+        # Pipeline parallelism, continuous form: the decoding sequences are split into one group per stage; a step launches
+        # every group that is not on the device and accepts the tokens of the oldest launch, so that in the steady state
+        # every stage always has a group to work on.
+        self._groups = getattr(decoder, "n_stages", 1) if (c.pp_continuous and hasattr(decoder, "launch")) else 1
+        self._grp_of: dict[int, int] = {}
+        self._grp_load = [0] * self._groups
+        self._flights: list = []       # (group, bucket, request ids), oldest first
+        self.metrics.set_gauge("skein_pipeline_groups_in_flight_max", float(max(0, self._groups - 1)))
         # optional trace export (SKEIN_OTLP_ENDPOINT): one span per engine step and one per finished request
         self._otlp = otlp.exporter(getattr(getattr(inner, "layout", None), "rank", 0))
         self._req_t0: dict[int, tuple] = {}      # request id -> (trace id, wall-clock ns at submission), while exporting
@@ -216,6 +226,7 @@ class Engine:
         """Drop everything in flight (a step failed here or on another rank): the requests' streams end with an
         error and their pages leave the prefix cache; queued requests stay queued."""
         self._drop_prelaunched()
+        self._drop_flights()
         events = [TokenEvent(rid, -1, True, error=reason) for rid in self.batcher.retire_all()]
         if self._otlp is not None:
             for ev in events:
@@ -245,22 +256,80 @@ class Engine:
             return None
         return [self._sampling.get(r, GREEDY).row() for r in rids]      # id 0 (a padding row) is greedy like any other
 
+    def _run_prefill(self, prefill, stamp, events) -> None:
+        seqs = []
+        for rid, start, end, last in prefill:
+            prompt = self.batcher.prompt(rid)
+            seqs.append((prompt[start:end], self.kv.pages_for(rid), start))
+        toks = self.runner.prefill(seqs, sampling=self._rows([p[0] for p in prefill]))
+        for (rid, start, end, last), tok in zip(prefill, toks):
+            self.batcher.prefill_advanced(rid, end)
+            if last:
+                events.append(self._accept(rid, tok, stamp()))
+
+    def _run_continuous(self, prefill, decode, now) -> list[TokenEvent]:
+        """One step of the continuous pipeline: prefill chunks as usual, then every group of decoding sequences that is not
+        on the device is launched (PipelineStage.launch: the host does not wait), then the tokens of the oldest launch
+        are accepted. A sequence belongs to one group from its first decode step to its last (the least loaded group
+        when it starts). With one group per stage the launches of the other groups keep every stage busy while one
+        group's tokens travel back, so the pipeline is drained only by a prefill chunk or when sequences run out."""
+        events: list[TokenEvent] = []
+        t_begin = time.perf_counter()
+        stamp = lambda: now + int((time.perf_counter() - t_begin) * 1000)   # noqa: E731
+        if prefill:
+            self._run_prefill(prefill, stamp, events)
+            started = {p[0] for p in prefill if p[3]}
+            decode = list(decode) + [ev.request_id for ev in events if ev.request_id in started and not ev.is_final]
+        flying = {g for g, _, _ in self._flights}
+        for rid in decode:
+            if rid not in self._grp_of:
+                g = min(range(self._groups), key=lambda i: (self._grp_load[i], i))
+                self._grp_of[rid] = g
+                self._grp_load[g] += 1
+        for g in range(self._groups):
+            if g in flying:
+                continue
+            ids = [rid for rid in decode if self._grp_of[rid] == g]
+            if not ids:
+                continue
+            bk = self.runner.bucket(len(ids), slot=g)
+            rows = self._rows(ids)
+            self.runner.stage_decode_inputs(bk, self.batcher, ids, sampling=rows)
+            self.runner.pp_launch(bk, sampling=rows is not None)
+            self._flights.append((g, bk, ids))
+        if self._flights:
+            g, bk, ids = self._flights.pop(0)
+            out = self.runner.pp_collect(bk)
+            fin, counts = self.batcher.accept_tokens(ids, out.data_ptr(), stamp(), self.cfg.eos_token)
+            toks = out[:len(ids)].tolist()
+            for rid, tok, f, n in zip(ids, toks, fin, counts):
+                if f:
+                    self._finish(rid, n)
+                events.append(TokenEvent(rid, tok, bool(f)))
+        return events
+
+    def _drop_flights(self) -> None:
+        """Wait for every launch that is still on the device and forget its result (the step failed, or the engine is being
+        torn down): the next launch of a group must not find its buffers in use."""
+        flights, self._flights = self._flights, []
+        for _, bk, _ in flights:
+            try:
+                self.runner.pp_collect(bk)
+            except Exception:       # noqa: BLE001  (the results are being thrown away)
+                pass
+        self._grp_of.clear()
+        self._grp_load = [0] * self._groups
+
     def _run(self, prefill, decode, now) -> list[TokenEvent]:
+        if self._groups > 1:
+            return self._run_continuous(prefill, decode, now)
         events: list[TokenEvent] = []
         t_begin = time.perf_counter()
         # a token's time stamp is the step's clock plus the time the step has taken so far, so that TTFT and TPOT
         # include the step that produced the token
         stamp = lambda: now + int((time.perf_counter() - t_begin) * 1000)
         if prefill:
-            seqs = []
-            for rid, start, end, last in prefill:
-                prompt = self.batcher.prompt(rid)
-                seqs.append((prompt[start:end], self.kv.pages_for(rid), start))
-            toks = self.runner.prefill(seqs, sampling=self._rows([p[0] for p in prefill]))
-            for (rid, start, end, last), tok in zip(prefill, toks):
-                self.batcher.prefill_advanced(rid, end)
-                if last:
-                    events.append(self._accept(rid, tok, stamp()))
+            self._run_prefill(prefill, stamp, events)
         pre, self._pre = self._pre, None
         if pre is not None and pre[1] != list(decode):
             self.runner.decode_wait(pre[0])     # the plan changed under it (requests were dropped): its result is not used
@@ -361,6 +430,9 @@ class Engine:
         self.batcher.retire(rid)
         self._sampling.pop(rid, None)
         self._dp_release(rid)
+        g = self._grp_of.pop(rid, None)
+        if g is not None:
+            self._grp_load[g] -= 1
 
     # ---- helpers ------------------------------------------------------------------------------------------------
     @property

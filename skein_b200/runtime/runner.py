@@ -115,11 +115,15 @@ class ModelRunner:
         self.last_wait_ns = 0      # running total of the device-side peer-wait counter, as of the last synchronised step
 
     # ---- decode -----------------------------------------------------------------------------------
-    def bucket(self, n: int) -> _Bucket:
+    def bucket(self, n: int, slot: int | None = None) -> _Bucket:
+        """The staging buffers (and captured graphs) of batches of up to bucket_for(n) rows. `slot` asks for a set of its
+        own: steps of different groups of sequences that are on the device at the same time must not share buffers."""
         B = bucket_for(n)
-        bk = self.buckets.get(B)
+        key = B if slot is None else (B, slot)
+        bk = self.buckets.get(key)
         if bk is None:
-            bk = self.buckets[B] = _Bucket(B, self.max_blocks, self.device)
+            bk = self.buckets[key] = _Bucket(B, self.max_blocks, self.device)
+            bk.slot = slot
         return bk
 
     def _decode_body(self, bk: _Bucket, feedback: bool, sampling: bool = False):
@@ -253,6 +257,53 @@ class ModelRunner:
                 ops.workspace().check_status()
             lo, hi = int(bk.host_out[bk.B + 2]), int(bk.host_out[bk.B + 3])      # a 64-bit total in two words
             self.last_wait_ns = ((hi & 0xFFFFFFFF) << 32) | (lo & 0xFFFFFFFF)
+        return bk.host_out[:bk.B]
+
+    # ---- pipeline parallelism with several groups of sequences in flight -------------------------------------------------
+    def _finish_flight(self, bk: _Bucket, toks) -> None:
+        """Device-to-host copy of a flight's tokens and of the device status, followed by the event the host waits for."""
+        bk.dev_out[:bk.B].copy_(toks)
+        if self.device.type == "cuda":
+            bk.dev_out[bk.B:].copy_(ops.workspace().status)
+        bk.host_out.copy_(bk.dev_out, non_blocking=True)
+        if self.device.type == "cuda":
+            if getattr(bk, "done", None) is None:
+                bk.done = torch.cuda.Event()
+            bk.done.record()
+
+    def pp_launch(self, bk: _Bucket, sampling: bool = False) -> None:
+        """Host-to-device copy of the staged inputs and this stage's share of the step, enqueued without waiting for the
+        step's tokens (PipelineStage.launch). The last stage, which has the tokens as soon as its compute ends, enqueues
+        their copy to the host right behind it; the other stages do that in pp_collect, on a side stream, so that the
+        copy does not wait for the steps of other groups that were enqueued in between."""
+        bk.dev_in.copy_(bk.host_in, non_blocking=True)
+        tok, pos, lens, bt = bk.views(bk.dev_in)
+        inp = BatchInputs(token_ids=tok, positions=pos, block_table=bt, seq_lens=lens, ctx_hint=self.ctx_hint)
+        smp = None
+        if sampling:
+            t, k, p, seeds = bk.sampling_views(bk.dev_in)
+            smp = SamplingInputs(t, k, p, seeds, pos)
+        bk.flight = self.dec.launch(inp, smp, ("group", bk.slot, bk.B, sampling))
+        if self.dec.last:
+            self._finish_flight(bk, bk.flight.tokens)
+
+    def pp_collect(self, bk: _Bucket):
+        """Waits for the tokens of a step enqueued by pp_launch; returns the host result view."""
+        if self.dec.last:
+            self.dec.collect(bk.flight)         # the sends of the tokens left long ago; this only retires their handles
+        else:
+            if self.device.type == "cuda":
+                if getattr(self, "_fb_stream", None) is None:
+                    self._fb_stream = torch.cuda.Stream(device=self.device)
+                with torch.cuda.stream(self._fb_stream):
+                    self._finish_flight(bk, self.dec.collect(bk.flight))
+            else:
+                self._finish_flight(bk, self.dec.collect(bk.flight))
+        bk.flight = None
+        if self.device.type == "cuda":
+            bk.done.synchronize()
+            if int(bk.host_out[bk.B]) != 0:
+                ops.workspace().check_status()
         return bk.host_out[:bk.B]
 
     def decode_loop_step(self, bk: _Bucket):

@@ -47,6 +47,7 @@ _FIELDS = {
     "gemm_autogrid": ("SKEIN_GEMM_AUTOGRID", _bool, None),
     "pack_moe": ("SKEIN_PACK_MOE", _bool, None),
     "pdl": ("SKEIN_PDL", _bool, None),
+    "pp_continuous": ("SKEIN_PP_CONTINUOUS", _bool, None),
     "tune_cache": ("SKEIN_TUNE_CACHE", str, None),
     "grid_barrier_ms": ("SKEIN_GRID_BARRIER_MS", int, None),
     "gemm_wait_ms": ("SKEIN_GEMM_WAIT_MS", int, None),
@@ -68,6 +69,7 @@ class RuntimeConfig:
     gemm_autogrid: bool = True     # whole tiles per CTA when that wastes little
     pack_moe: bool = True          # tile-packed expert weights
     pdl: bool = False              # programmatic dependent launch between the per-layer kernels
+    pp_continuous: bool = False    # pipeline parallelism: one group of sequences per stage in flight across engine steps
     tune_cache: str = ""           # kernel-configuration cache to load ("" = the artifact's own, if any)
     grid_barrier_ms: int = 2000    # budget of the grid-wide arrival counter in the fused reduce + router kernel
     gemm_wait_ms: int = 2000       # budget of the GEMM's pipeline waits and of its wait for the other pieces of a split tile

@@ -152,7 +152,7 @@ def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
     sock.close()
     p = subprocess.Popen([*cli, "serve", "--artifact", art, "--gpus", "0,1", "--port", str(port), "--max-seq-len", "128",
                           "--rendezvous", str(tmp_path / "rdv_http")], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
-                         cwd=ROOT, env=env)
+                         cwd=ROOT, env={**env, "SKEIN_PP_CONTINUOUS": "1"})     # one group of sequences per stage kept in flight
     try:
         up = False
         for _ in range(600):
@@ -179,6 +179,8 @@ def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
         assert rb.returncode == 0, rb.stderr[-2000:]
         bj = json.loads(rb.stdout.strip().splitlines()[-1])
         assert bj["requests_ok"] == 3 and bj["requests_failed"] == 0 and bj["ttft_p50_ms"] > 0 and bj["throughput_tok_s"] > 0
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10) as h:
+            assert "skein_pipeline_groups_in_flight_max 1" in h.read().decode()
         p.send_signal(signal.SIGTERM)
         out, err = p.communicate(timeout=90)
     finally:

@@ -3,21 +3,26 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 from skein_b200.parallel import launcher
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def test_two_stage_pipeline_matches_single_stage(tmp_path):
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_stages_match_single_stage(tmp_path, stages):
+    """Stage-by-stage steps, the micro-batched pipelined decode and the serving engine with one group of sequences per
+    stage in flight, each against the single-stage model."""
     procs = []
-    for l in launcher.plan_launch([0, 1], str(tmp_path / "rdv")):
+    for l in launcher.plan_launch(list(range(stages)), str(tmp_path / "rdv")):
         _, env = launcher.build_command(l, [])
         env["CUDA_VISIBLE_DEVICES"] = ""
         procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "workers", "pp_worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(o[1][-2000:] for o in outs)
-    assert "PP_WORKER_OK" in outs[0][0]
+    assert "PP_WORKER_OK" in outs[0][0] and "PP_CONTINUOUS_OK" in outs[0][0]
 
 
 def test_lock_step_control_agrees_on_a_failure_across_two_cpu_ranks(tmp_path):
