@@ -114,12 +114,32 @@ def main():
         assert eng.idle and not eng._flights and not eng._grp_of and sum(eng._grp_load) == 0
         return [out[i] for i in sorted(out)], most
 
+    def near_tie(prompt, want_seq, got_seq, tol=0.05):
+        """True when the two generations part at a step where the single-stage model, given the common prefix, scores the
+        two tokens within `tol` of each other (bf16 spacing at these logits is 0.016). The groups of the continuous engine
+        are smaller batches than the single-stage engine's, so on GPUs the GEMMs round differently and such a step may
+        go either way; on CPU the arithmetic does not depend on the batch and the generations are equal."""
+        i = next(j for j, (a_, b_) in enumerate(zip(want_seq, got_seq)) if a_ != b_)
+        ref = Decoder(cfg, full if dev.type == "cpu" else shard_model(full, cfg, mc.ParallelLayout(), dev), num_pages=16, page_size=16, max_pos=128)
+        _, lg = ModelRunner(ref, max_blocks_per_seq=4, use_graphs=False).prefill([(prompt + want_seq[:i], [1, 2, 3, 4], 0)], want_logits=True)
+        row = lg[-1].float().flatten()
+        return abs(float(row[want_seq[i]]) - float(row[got_seq[i]])) <= tol and float(row.max()) - float(row[got_seq[i]]) <= tol
+
     got_c, most = serve(stage, True)
     assert most == world - 1 or world == 1, most       # a step launches every idle group and collects one: pp - 1 stay in flight
     assert [len(x) for x in got_c] == [m for _, m in reqs + late]
     if rank == 0:
         want_c, _ = serve(Decoder(cfg, full, num_pages=32, page_size=16, max_pos=128), False)
-        assert got_c == want_c, (got_c, want_c)
+        prompts_c = [p_ for p_, _ in reqs + late]
+        diff = [i for i, (a_, b_) in enumerate(zip(got_c, want_c)) if a_ != b_]
+        if use_cuda:
+            assert len(diff) <= 2 and all(near_tie(prompts_c[i], want_c[i], got_c[i]) for i in diff), (got_c, want_c)
+        else:
+            assert not diff, (got_c, want_c)
+        # the excuse itself: the runner-up of a close step passes, an arbitrary token does not
+        close = [255, 131, 131, 131, 131, 457]      # parts from the single-stage generation where 457 and 131 score 2.359 / 2.344
+        if not use_cuda and want_c[0][:3] == [255, 131, 457]:
+            assert near_tie(prompts_c[0], want_c[0], close) and not near_tie(prompts_c[0], want_c[0], [255, 131, 7, 0, 0, 0])
         print("PP_CONTINUOUS_OK world", world)
     dist.barrier()
     dist.destroy_process_group()
