@@ -22,7 +22,7 @@ def test_pipeline_stages_match_single_stage(tmp_path, stages):
                                       stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(o[1][-2000:] for o in outs)
-    assert "PP_WORKER_OK" in outs[0][0] and "PP_CONTINUOUS_OK" in outs[0][0]
+    assert "PP_WORKER_OK" in outs[0][0] and "PP_CONTINUOUS_OK" in outs[0][0] and "PP_CONTINUOUS_FAILURE_OK" in outs[0][0]
 
 
 def test_lock_step_control_agrees_on_a_failure_across_two_cpu_ranks(tmp_path):

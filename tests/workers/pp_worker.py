@@ -141,6 +141,31 @@ def main():
         if not use_cuda and want_c[0][:3] == [255, 131, 457]:
             assert near_tie(prompts_c[0], want_c[0], close) and not near_tie(prompts_c[0], want_c[0], [255, 131, 7, 0, 0, 0])
         print("PP_CONTINUOUS_OK world", world)
+
+    # a step that fails (on every stage: the lock-step control plane makes a failure of one rank a failure of all) while
+    # groups are on the device: their launches are waited for and dropped, the requests end with an error, and the
+    # engine serves the next request as if nothing had happened
+    for kv in dec.kv:
+        kv.zero_()
+    eng = Engine(stage, EngineConfig(max_batch=8, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False, pp_continuous=True))
+    for p_, m in reqs[:4]:
+        eng.submit(p_, 8)
+
+    def boom(step):
+        if step == 3:
+            raise RuntimeError("injected")
+    eng.failure_injector = boom
+    errs, n_steps = [], 0
+    while not eng.idle and n_steps < 50:
+        errs += [ev for ev in eng.step() if ev.error is not None]
+        n_steps += 1
+    assert len(errs) == 4 and not eng._flights and not eng._grp_of, (errs, n_steps)
+    eng.failure_injector = None
+    rid, _ = eng.submit(reqs[2][0], 9)
+    after = eng.run_until_done()[rid]
+    if rank == 0 and not use_cuda:
+        assert after == want_c[2], (after, want_c[2])
+        print("PP_CONTINUOUS_FAILURE_OK world", world)
     dist.barrier()
     dist.destroy_process_group()
 
