@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--burst-only", action="store_true",
                     help="run only the burst replay (after the multi-rank self-check): --batch is the number of sequences "
                          "served at a time, --prompt / --gen cap the trace's prompt and output lengths and size the KV pool")
+    ap.add_argument("--pp-continuous", action="store_true",
+                    help="with --pp: the end-to-end engine keeps one group of sequences per stage in flight across steps "
+                         "instead of draining the pipeline at the end of every step")
     ap.add_argument("--replicated-attention", action="store_true",
                     help="expert parallelism: every rank runs attention for all sequences (the comparison arm) instead of "
                          "each rank attending over its own slice with token dispatch between the ranks")
@@ -453,7 +456,8 @@ def run_pipeline(args, emit_json):
         for kv in dec.kv:
             kv.zero_()
         ecfg = EngineConfig(max_batch=B, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=False, max_prefill_tokens=8192,
-                            interleave_prefill_tokens=0)
+                            interleave_prefill_tokens=0, pp_continuous=args.pp_continuous)
+        stage.feedback_group = fb_group
         ctl = SharedControl(f"/dev/shm/skein_bench_ctl_{os.environ.get('MASTER_PORT', '0')}", rank, world, control_group, wait_s=300)
         eng = Engine(stage, ecfg)
         for s_ in range(B):
@@ -470,20 +474,25 @@ def run_pipeline(args, emit_json):
                 raise RuntimeError("an engine step failed: " + str([e.error for e in evs if e.error][:1]))
             return evs
 
+        # continuous mode: a step accepts the tokens of one of the pp groups of sequences, so pp steps make one token per sequence
+        per_tok = npp if args.pp_continuous else 1
         n_dec = 0
-        while n_dec < W:
+        while n_dec < W * per_tok:
             evs = one_step()
-            if len(evs) == B and all(not e.is_final for e in evs):
+            if len(evs) == B // per_tok and all(not e.is_final for e in evs):
                 n_dec += 1
         barrier()
         t_a = time.perf_counter()
-        for _ in range(K):
-            one_step()
+        n_tok = 0
+        for _ in range(K * per_tok):
+            n_tok += sum(1 for e in one_step() if e.error is None)
         torch.cuda.synchronize()
         wall = max_over_ranks(time.perf_counter() - t_a)
-        bk = eng.runner.bucket(B)
-        e2e = {"value": round(B * K / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": bk.h2d_bytes, "d2h_bytes_per_step": bk.d2h_bytes,
-               "path": "Engine.step over PipelineStage (pp micro-batches per step, per-stage CUDA graphs); lock-step control page"}
+        bk = eng.runner.bucket(B // per_tok, slot=0 if args.pp_continuous else None)
+        e2e = {"value": round(n_tok / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": bk.h2d_bytes * per_tok,
+               "d2h_bytes_per_step": bk.d2h_bytes * per_tok,
+               "path": ("Engine.step over PipelineStage, one group of sequences per stage kept in flight across steps" if args.pp_continuous
+                        else "Engine.step over PipelineStage (pp micro-batches per step, per-stage CUDA graphs)") + "; lock-step control page"}
         ctl.close()
     if rank == 0:
         emit_json({
