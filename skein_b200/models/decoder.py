@@ -255,8 +255,8 @@ class Decoder:
             return False
         per = B // ways
         # the sampled tokens of a slice are gathered 16 bytes at a time; the fused reduce + router needs one CTA per row
-        return (per % 4 == 0 and ops.can_fuse_route(per, k, device) and B * k <= 2048
-                and (self.comm_moe is None or self.comm_moe.dispatch_fits(per, k)))
+        fits = getattr(self.comm_moe, "dispatch_fits", None)      # CPU rank communicators carry no dispatch buffers
+        return (per % 4 == 0 and ops.can_fuse_route(per, k, device) and B * k <= 2048 and (fits is None or fits(per, k)))
 
     def dp_rows_limit(self, device=None) -> int:
         """Largest power-of-two number of rows per rank that dp_rows_ok accepts (0: none does)."""
