@@ -49,8 +49,21 @@ inline Graph import_model(const Json& cfg) {
   if (m.num_attention_heads % m.num_kv_heads) throw ImportError("num_attention_heads must be a multiple of num_key_value_heads (GQA)");
   m.rope_theta = cfg.has("rope_theta") ? cfg.at("rope_theta").as_double() : 1e4;
   m.rms_norm_eps = cfg.has("rms_norm_eps") ? cfg.at("rms_norm_eps").as_double() : 1e-5;
-  if (const Json* sw = cfg.find("sliding_window"); sw && !sw->is_null()) m.sliding_window = (size_t)sw->as_int();
+  if (const Json* sw = cfg.find("sliding_window"); sw && !sw->is_null()) {
+    const Json* use = cfg.find("use_sliding_window");
+    // Qwen2 lists a window but applies it only with use_sliding_window. Where a window applies it becomes the position limit:
+    // the kernels attend over the whole context, the same function up to that length.
+    if (arch != "Qwen2ForCausalLM" || (use && !use->is_null() && use->as_bool())) {
+      m.sliding_window = (size_t)sw->as_int();
+      if (*m.sliding_window > 0 && *m.sliding_window < m.max_position) m.max_position = *m.sliding_window;
+    }
+  }
   m.tied_embeddings = cfg.has("tie_word_embeddings") && cfg.at("tie_word_embeddings").as_bool();
+  // Qwen2 adds a bias to the q / k / v projections (none on o_proj). The Llama-style `attention_bias` switch adds one to
+  // o_proj as well, which the runtime does not carry.
+  m.qkv_bias = arch == "Qwen2ForCausalLM";
+  if (const Json* ab = cfg.find("attention_bias"); ab && !ab->is_null() && ab->as_bool() && !m.qkv_bias)
+    throw ImportError("attention_bias = true (biases on q, k, v and o_proj) is not supported for " + arch);
   if (moe) {
     m.num_experts = cfg_usize(cfg, "num_local_experts");
     m.top_k = cfg_usize(cfg, "num_experts_per_tok");
@@ -85,6 +98,11 @@ inline Graph import_model(const Json& cfg) {
     a.params.push_back({pre + "self_attn.k_proj.weight", {KV, H}, Dtype::Bf16});
     a.params.push_back({pre + "self_attn.v_proj.weight", {KV, H}, Dtype::Bf16});
     a.params.push_back({pre + "self_attn.o_proj.weight", {H, QO}, Dtype::Bf16});
+    if (m.qkv_bias) {
+      a.params.push_back({pre + "self_attn.q_proj.bias", {QO}, Dtype::Bf16});
+      a.params.push_back({pre + "self_attn.k_proj.bias", {KV}, Dtype::Bf16});
+      a.params.push_back({pre + "self_attn.v_proj.bias", {KV}, Dtype::Bf16});
+    }
     Layer& n2 = add(LayerKind::RmsNorm, b, "post_attention_layernorm");
     n2.hidden = H; n2.eps = m.rms_norm_eps;
     n2.params.push_back({pre + "post_attention_layernorm.weight", {H}, Dtype::Bf16});

@@ -83,6 +83,7 @@ struct ModelMeta {
   std::optional<size_t> num_experts, top_k, sliding_window;
   double rope_theta = 1e4, rms_norm_eps = 1e-5;
   bool tied_embeddings = false;
+  bool qkv_bias = false;       // the q / k / v projections carry a bias vector each (Qwen2)
 
   Json to_json() const {
     Json j = Json::object();
@@ -93,6 +94,7 @@ struct ModelMeta {
         .set("top_k", opt(top_k)).set("intermediate", intermediate).set("rope_theta", rope_theta)
         .set("rms_norm_eps", rms_norm_eps).set("sliding_window", opt(sliding_window))
         .set("tied_embeddings", tied_embeddings);
+    if (qkv_bias) j.set("qkv_bias", true);      // written only when set: plans of models without biases keep their hash
     return j;
   }
   static ModelMeta from_json(const Json& j) {
@@ -109,6 +111,7 @@ struct ModelMeta {
     m.num_experts = opt("num_experts"); m.top_k = opt("top_k"); m.intermediate = j.at("intermediate").as_int();
     m.rope_theta = j.at("rope_theta").as_double(); m.rms_norm_eps = j.at("rms_norm_eps").as_double();
     m.sliding_window = opt("sliding_window"); m.tied_embeddings = j.at("tied_embeddings").as_bool();
+    if (const Json* qb = j.find("qkv_bias"); qb && !qb->is_null()) m.qkv_bias = qb->as_bool();
     return m;
   }
   bool is_moe() const { return num_experts && *num_experts > 0; }

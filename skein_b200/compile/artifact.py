@@ -102,6 +102,9 @@ def build_artifact(plan_json: str, config_json: str, out_root: str | Path, sourc
     """Lower the plan, shard (and quantise) the weights, write the artifact directory. Returns its path."""
     plan = json.loads(plan_json)
     core.plan_validate(plan_json)
+    if json.loads(config_json).get("tie_word_embeddings") and plan["parallelism"]["pp"] > 1:
+        # the output projection reads the embedding table, which the lowering places on the first stage only
+        raise ArtifactError("tied input / output embeddings are not supported with pipeline parallelism")
     h = core.plan_hash(plan_json)
     root = Path(out_root) / h
     tmp = Path(out_root) / (h + ".partial")
@@ -155,6 +158,10 @@ def _full_shape(cfg: ModelConfig, name: str):
         return (cfg.vocab_size, H)
     if name.endswith("layernorm.weight") or name == "model.norm.weight":
         return (H,)
+    if name.endswith("q_proj.bias"):
+        return (cfg.num_heads * D,)
+    if name.endswith("k_proj.bias") or name.endswith("v_proj.bias"):
+        return (cfg.num_kv_heads * D,)
     if "q_proj" in name:
         return (cfg.num_heads * D, H)
     if "k_proj" in name or "v_proj" in name:
@@ -287,13 +294,17 @@ class Artifact:
                     w13 = torch.cat([get(pre + "mlp.gate_proj.weight"), get(pre + "mlp.up_proj.weight")], dim=0).contiguous()
                     w2 = get(pre + "mlp.down_proj.weight").contiguous()
                     router = None
+                bqkv = (torch.cat([get(pre + f"self_attn.{p}_proj.bias") for p in "qkv"]).contiguous() if cfg.qkv_bias else None)
                 layers.append(LayerWeights(attn_norm=get(pre + "input_layernorm.weight"), wqkv=wqkv,
                                            wo=get(pre + "self_attn.o_proj.weight").contiguous(),
-                                           ffn_norm=get(pre + "post_attention_layernorm.weight"), router=router, w13=w13, w2=w2))
+                                           ffn_norm=get(pre + "post_attention_layernorm.weight"), router=router, w13=w13, w2=w2,
+                                           bqkv=bqkv))
             first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
-            return ModelWeights(embed=get("model.embed_tokens.weight") if first else None, layers=layers,
-                                final_norm=get("model.norm.weight") if last else None,
-                                lm_head=get("lm_head.weight") if last else None)
+            embed = get("model.embed_tokens.weight") if first else None
+            # tied embeddings: the output projection is the embedding table (under tensor parallelism both are split by
+            # vocabulary rows the same way, so a rank's table shard is its shard of the output projection)
+            lm_head = (embed if cfg.tie_word_embeddings else get("lm_head.weight")) if last else None
+            return ModelWeights(embed=embed, layers=layers, final_norm=get("model.norm.weight") if last else None, lm_head=lm_head)
 
 
 def verify_shape_compatibility(old: Artifact, new: Artifact) -> None:

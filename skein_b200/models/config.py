@@ -36,6 +36,7 @@ class ModelConfig:
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
     name: str = "mixtral-8x7b"
+    qkv_bias: bool = False        # the q / k / v projections carry a bias each (Qwen2)
 
     @property
     def is_moe(self) -> bool:
@@ -52,6 +53,8 @@ class ModelConfig:
     def param_count(self) -> int:
         H, I, D = self.hidden_size, self.intermediate_size, self.head_dim
         attn = H * (self.num_heads * D) * 2 + H * (self.num_kv_heads * D) * 2
+        if self.qkv_bias:
+            attn += (self.num_heads + 2 * self.num_kv_heads) * D
         ffn = 3 * H * I * max(self.num_experts, 1) + (H * self.num_experts if self.is_moe else 0)
         per_block = attn + ffn + 2 * H
         emb = self.vocab_size * H
@@ -85,7 +88,16 @@ class ModelConfig:
             top_k=int(d.get("num_experts_per_tok", 0)) if arch in MOE_ARCHS else 0,
             max_position_embeddings=int(d.get("max_position_embeddings", 8192)),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            name=name or d.get("_name_or_path") or d.get("model_type", "model"))
+            name=name or d.get("_name_or_path") or d.get("model_type", "model"),
+            qkv_bias=arch == "Qwen2ForCausalLM")
+        # Sliding-window attention (Mistral v0.1; Qwen2 only with use_sliding_window): the attention kernels attend over the
+        # whole context, which is the same function as long as a sequence is no longer than the window, so the window
+        # becomes the position limit and longer requests are refused instead of being answered differently.
+        sw = d.get("sliding_window")
+        if sw and (arch != "Qwen2ForCausalLM" or d.get("use_sliding_window")) and int(sw) < cfg.max_position_embeddings:
+            cfg.max_position_embeddings = int(sw)
+        if d.get("attention_bias") and not cfg.qkv_bias:
+            raise ImportError_(f"attention_bias = true (biases on q, k, v and o_proj) is not supported for {arch}")
         cfg.validate()
         return cfg
 

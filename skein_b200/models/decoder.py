@@ -41,6 +41,7 @@ class LayerWeights:
     w2: torch.Tensor                   # MoE: [E_local, H, I / tp];                     dense: [H, I / tp]
     # block-scaled fp8 copies (present when the plan's dtype map selects fp8 for this block)
     fp8: dict = field(default_factory=dict)
+    bqkv: torch.Tensor | None = None   # [(Hq + 2 Hkv) / tp * D] bias of the fused q / k / v projection (Qwen2), else None
 
 
 @dataclass
@@ -87,12 +88,17 @@ def random_weights(cfg: ModelConfig, lay: ParallelLayout, device, seed: int = 0,
             router, w13, w2 = None, rnd(2 * sh["I"], H), rnd(H, sh["I"])
         layers.append(LayerWeights(
             attn_norm=torch.ones(H, dtype=dtype, device=device), wqkv=rnd((sh["Hq"] + 2 * sh["Hkv"]) * D, H),
-            wo=rnd(H, sh["Hq"] * D), ffn_norm=torch.ones(H, dtype=dtype, device=device), router=router, w13=w13, w2=w2))
+            wo=rnd(H, sh["Hq"] * D), ffn_norm=torch.ones(H, dtype=dtype, device=device), router=router, w13=w13, w2=w2,
+            bqkv=rnd((sh["Hq"] + 2 * sh["Hkv"]) * D) if cfg.qkv_bias else None))
     first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
-    return ModelWeights(
-        embed=rnd(sh["V_local"] if (shard_embed and lay.tp > 1) else cfg.vocab_size, H) if first else None, layers=layers,
-        final_norm=torch.ones(H, dtype=dtype, device=device) if last else None,
-        lm_head=rnd(sh["V_local"], H) if last else None)
+    embed = rnd(sh["V_local"] if (shard_embed and lay.tp > 1) else cfg.vocab_size, H) if first else None
+    if cfg.tie_word_embeddings and first and last:      # the output projection is (this rank's rows of) the embedding table
+        v0 = 0 if embed.shape[0] == sh["V_local"] else lay.tp_rank * sh["V_local"]
+        lm_head = embed[v0:v0 + sh["V_local"]]
+    else:
+        lm_head = rnd(sh["V_local"], H) if last else None
+    return ModelWeights(embed=embed, layers=layers, final_norm=torch.ones(H, dtype=dtype, device=device) if last else None,
+                        lm_head=lm_head)
 
 
 def quantize_blocks(weights: ModelWeights, blocks, names=("wqkv", "wo", "w13", "w2"), drop_bf16: bool = True) -> None:
@@ -309,7 +315,10 @@ class Decoder:
             st.sp = True
 
     def _op_qkv_proj(self, st, li):
-        st.qkv = self._col_linear(st.normed, self.w.layers[li], "wqkv")
+        lw = self.w.layers[li]
+        st.qkv = self._col_linear(st.normed, lw, "wqkv")
+        if lw.bqkv is not None:
+            st.qkv += lw.bqkv       # Qwen2: one elementwise pass over [tokens, (Hq + 2 Hkv) D]; the GEMM epilogue carries no bias
 
     def _rope_fused(self, st, li) -> bool:
         inp = st.inp

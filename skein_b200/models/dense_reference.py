@@ -42,6 +42,8 @@ def forward_full(cfg: ModelConfig, w: ModelWeights, token_ids: torch.Tensor, cap
     for lw in w.layers:
         h = _rms(x, lw.attn_norm, cfg.rms_norm_eps)
         qkv = h @ lw.wqkv.float().t()
+        if getattr(lw, "bqkv", None) is not None:
+            qkv = qkv + lw.bqkv.float()
         q = _rope(qkv[:, :Hq * D].view(T, Hq, D), pos, cfg.rope_theta)
         k = _rope(qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D), pos, cfg.rope_theta)
         v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)

@@ -27,6 +27,10 @@ def shard_layer(lw: LayerWeights, cfg: ModelConfig, lay: ParallelLayout) -> Laye
     k = _rows(lw.wqkv, Hq * D + r * sh["Hkv"] * D, sh["Hkv"] * D)
     v = _rows(lw.wqkv, (Hq + Hkv) * D + r * sh["Hkv"] * D, sh["Hkv"] * D)
     wqkv = torch.cat([q, k, v], dim=0).contiguous()
+    bqkv = None
+    if lw.bqkv is not None:       # the bias rows follow their weight rows
+        bqkv = torch.cat([_rows(lw.bqkv, r * sh["Hq"] * D, sh["Hq"] * D), _rows(lw.bqkv, Hq * D + r * sh["Hkv"] * D, sh["Hkv"] * D),
+                          _rows(lw.bqkv, (Hq + Hkv) * D + r * sh["Hkv"] * D, sh["Hkv"] * D)]).contiguous()
     wo = lw.wo[:, r * sh["Hq"] * D:(r + 1) * sh["Hq"] * D].contiguous()
     Il = sh["I"]
     if cfg.is_moe:
@@ -39,7 +43,7 @@ def shard_layer(lw: LayerWeights, cfg: ModelConfig, lay: ParallelLayout) -> Laye
         w13 = torch.cat([lw.w13[r * Il:(r + 1) * Il], lw.w13[I + r * Il:I + (r + 1) * Il]], dim=0).contiguous()
         w2 = lw.w2[:, r * Il:(r + 1) * Il].contiguous()
         router = None
-    return LayerWeights(attn_norm=lw.attn_norm, wqkv=wqkv, wo=wo, ffn_norm=lw.ffn_norm, router=router, w13=w13, w2=w2)
+    return LayerWeights(attn_norm=lw.attn_norm, wqkv=wqkv, wo=wo, ffn_norm=lw.ffn_norm, router=router, w13=w13, w2=w2, bqkv=bqkv)
 
 
 def shard_model(full: ModelWeights, cfg: ModelConfig, lay: ParallelLayout, device=None, shard_embed: bool = False) -> ModelWeights:
@@ -57,7 +61,7 @@ def shard_model(full: ModelWeights, cfg: ModelConfig, lay: ParallelLayout, devic
     for i in stage:
         s = shard_layer(full.layers[i], cfg, lay)
         layers.append(LayerWeights(**{k: mv(getattr(s, k)) for k in
-                                      ("attn_norm", "wqkv", "wo", "ffn_norm", "router", "w13", "w2")}))
+                                      ("attn_norm", "wqkv", "wo", "ffn_norm", "router", "w13", "w2", "bqkv")}))
     v0 = lay.tp_rank * sh["V_local"]
     lm = full.lm_head[v0:v0 + sh["V_local"]].contiguous() if last else None
     emb = full.embed

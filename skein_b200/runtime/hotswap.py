@@ -44,7 +44,7 @@ def mount_weights(engine, artifact_path, rank: int) -> None:
     fresh = new.load_weights(rank, inner.device)
     with torch.no_grad():
         for old_l, new_l in zip(inner.w.layers, fresh.layers):
-            for name in ("attn_norm", "wqkv", "wo", "ffn_norm", "router", "w13", "w2"):
+            for name in ("attn_norm", "wqkv", "wo", "ffn_norm", "router", "w13", "w2", "bqkv"):
                 _copy_into(getattr(old_l, name), getattr(new_l, name))
             if set(old_l.fp8) != set(new_l.fp8):
                 raise HotSwapError("the artifacts quantise different projections of a block")

@@ -1,4 +1,5 @@
-"""The runtime's decoder against HuggingFace `transformers` on a tiny random Mixtral and a tiny random Llama (CPU).
+"""The runtime's decoder against HuggingFace `transformers` on tiny random models of every supported family (CPU):
+Mixtral, Llama, Mistral, Qwen2 (q / k / v biases) and a Llama with tied input / output embeddings.
 
 The checkpoint is written by transformers, compiled into an artifact by this framework's own pipeline (HF tensor
 names, expert stacking, q/k/v fusion), and both sides run the same prompts. This is the one oracle that is not
@@ -29,18 +30,29 @@ def _hf_model(kind):
     if kind == "mixtral":
         cfg = transformers.MixtralConfig(num_local_experts=4, num_experts_per_tok=2, rope_theta=1e6, **common)
         m = transformers.MixtralForCausalLM(cfg)
+    elif kind == "qwen2":        # q / k / v projections carry biases
+        cfg = transformers.Qwen2Config(rope_theta=1e6, use_sliding_window=False, **{k: v for k, v in common.items() if k != "head_dim"},)
+        m = transformers.Qwen2ForCausalLM(cfg)
+    elif kind == "mistral":
+        cfg = transformers.MistralConfig(rope_theta=1e4, sliding_window=None, **common)
+        m = transformers.MistralForCausalLM(cfg)
+    elif kind == "llama-tied":   # the output projection is the embedding table
+        cfg = transformers.LlamaConfig(rope_theta=5e5, **{**common, "tie_word_embeddings": True})
+        m = transformers.LlamaForCausalLM(cfg)
     else:
         cfg = transformers.LlamaConfig(rope_theta=5e5, **common)
         m = transformers.LlamaForCausalLM(cfg)
     with torch.no_grad():
-        for p in m.parameters():      # larger than the default init so that attention and routing matter; bf16-exact
+        for name, p in m.named_parameters():      # larger than the default init so that attention and routing matter; bf16-exact
             if p.dim() > 1:
                 p.normal_(0.0, 0.06)
+            elif "bias" in name:
+                p.normal_(0.0, 0.5)
             p.copy_(p.to(torch.bfloat16).float())
     return m.eval()
 
 
-@pytest.mark.parametrize("kind", ["mixtral", "llama"])
+@pytest.mark.parametrize("kind", ["mixtral", "llama", "mistral", "qwen2", "llama-tied"])
 def test_decoder_matches_huggingface_transformers(kind, tmp_path):
     hf = _hf_model(kind)
     ckpt = tmp_path / "ckpt"

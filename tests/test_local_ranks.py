@@ -6,13 +6,14 @@ Mirrors crates/skein_emit/tests/op_numerics.rs:299,371 (TP shards sum to the ful
 crates/skein_runtime/src/distributed/barrier_collective.rs:179-220, rank_executor.rs:443-552,
 segment_runner.rs:1698-1791 (two-rank pipeline on CPU threads).
 """
+import dataclasses
 import time
 
 import pytest
 import torch
 
 from skein_b200.models import config as mc
-from skein_b200.models.decoder import Decoder, random_weights
+from skein_b200.models.decoder import Decoder, ModelWeights, random_weights
 from skein_b200.models.sharding import shard_model
 from skein_b200.parallel.local import CommError, run_ranks
 from skein_b200.runtime.runner import ModelRunner
@@ -32,13 +33,18 @@ def _generate(dec, prompts, tables, steps=3):
 
 @pytest.mark.parametrize("tp,cfg", [(2, mc.tiny_mixtral(heads=4, kv_heads=2)), (4, mc.tiny_mixtral(heads=8, kv_heads=4, inter=1024)),
                                     (8, mc.tiny_mixtral(heads=16, kv_heads=8, inter=2048)),
-                                    (2, mc.tiny_llama())], ids=["mixtral-tp2", "mixtral-tp4", "mixtral-tp8", "llama-tp2"])
+                                    (2, mc.tiny_llama()), (2, dataclasses.replace(mc.tiny_llama(), architecture="Qwen2ForCausalLM", qkv_bias=True))],
+                         ids=["mixtral-tp2", "mixtral-tp4", "mixtral-tp8", "llama-tp2", "qwen2-tp2-qkv-bias"])
 def test_tp_shards_reproduce_the_unsharded_model(tp, cfg):
     torch.manual_seed(0)
     full = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=5, std=0.05)
     prompts = torch.randint(0, cfg.vocab_size, (2, 19)).tolist()
     tables = [[1, 2, 3, 4], [5, 6, 7, 8]]
     want, want_lg = _generate(Decoder(cfg, full, num_pages=16, page_size=16, max_pos=128), prompts, tables)
+    if cfg.qkv_bias:        # the biases matter: without them the model samples other tokens
+        assert full.layers[0].bqkv is not None
+        bare = ModelWeights(full.embed, [dataclasses.replace(l, bqkv=None) for l in full.layers], full.final_norm, full.lm_head)
+        assert _generate(Decoder(cfg, bare, num_pages=16, page_size=16, max_pos=128), prompts, tables)[0] != want
 
     def rank_fn(r, comm):
         lay = mc.ParallelLayout(tp=tp, rank=r)
