@@ -47,7 +47,23 @@ inline Graph import_model(const Json& cfg) {
     m.head_dim = m.hidden / m.num_attention_heads;
   }
   if (m.num_attention_heads % m.num_kv_heads) throw ImportError("num_attention_heads must be a multiple of num_key_value_heads (GQA)");
-  m.rope_theta = cfg.has("rope_theta") ? cfg.at("rope_theta").as_double() : 1e4;
+  // newer checkpoints nest theta and the frequency-scaling scheme in `rope_parameters`
+  const Json* rp = cfg.find("rope_parameters");
+  if (rp && (rp->is_null() || !rp->is_object())) rp = nullptr;
+  m.rope_theta = cfg.has("rope_theta") && !cfg.at("rope_theta").is_null() ? cfg.at("rope_theta").as_double()
+                 : (rp && rp->has("rope_theta") ? rp->at("rope_theta").as_double() : 1e4);
+  {
+    const Json* sc = cfg.find("rope_scaling");
+    if (!sc || sc->is_null()) sc = rp;
+    if (sc && sc->is_object()) {
+      std::string kind = "default";
+      if (const Json* t = sc->find("rope_type"); t && !t->is_null()) kind = t->as_string();
+      else if (const Json* t2 = sc->find("type"); t2 && !t2->is_null()) kind = t2->as_string();
+      if (kind != "default" && kind != "linear" && kind != "llama3")
+        throw ImportError("rope scaling `" + kind + "` is not supported (plain, linear and llama3 are)");
+    }
+  }
+  if (const Json* mb = cfg.find("mlp_bias"); mb && !mb->is_null() && mb->as_bool()) throw ImportError("mlp_bias = true is not supported");
   m.rms_norm_eps = cfg.has("rms_norm_eps") ? cfg.at("rms_norm_eps").as_double() : 1e-5;
   if (const Json* sw = cfg.find("sliding_window"); sw && !sw->is_null()) {
     const Json* use = cfg.find("use_sliding_window");

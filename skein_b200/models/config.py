@@ -37,6 +37,7 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     name: str = "mixtral-8x7b"
     qkv_bias: bool = False        # the q / k / v projections carry a bias each (Qwen2)
+    rope_scaling: dict | None = None   # the checkpoint's RoPE frequency scaling ("linear" or "llama3"), None = plain RoPE
 
     @property
     def is_moe(self) -> bool:
@@ -79,17 +80,31 @@ class ModelConfig:
         hd = d.get("head_dim") or (H // nh)
         if d.get("head_dim") is None and H % nh != 0:
             raise ImportError_("hidden_size is not divisible by num_attention_heads and head_dim is absent")
+        # newer checkpoints nest theta and the scaling scheme in `rope_parameters`; older ones have `rope_theta` and
+        # `rope_scaling` at the top level
+        rp = d.get("rope_parameters") or {}
+        theta = d.get("rope_theta", rp.get("rope_theta", 1e4))
+        scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k != "rope_theta"} if rp else None)
+        kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
+        if kind == "default":
+            scaling = None
+        elif kind not in ("linear", "llama3"):
+            raise ImportError_(f"rope scaling {kind!r} is not supported (plain, linear and llama3 are)")
+        if float(d.get("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0)) or 1.0) != 1.0:
+            raise ImportError_("partial rotary embeddings are not supported")
+        if d.get("mlp_bias"):
+            raise ImportError_("mlp_bias = true is not supported")
         cfg = ModelConfig(
             architecture=arch, hidden_size=H, intermediate_size=int(d["intermediate_size"]),
             num_layers=int(d["num_hidden_layers"]), num_heads=nh,
             num_kv_heads=int(d.get("num_key_value_heads", nh)), head_dim=int(hd), vocab_size=int(d["vocab_size"]),
-            rms_norm_eps=float(d.get("rms_norm_eps", 1e-5)), rope_theta=float(d.get("rope_theta", 1e4)),
+            rms_norm_eps=float(d.get("rms_norm_eps", 1e-5)), rope_theta=float(theta),
             num_experts=int(d.get("num_local_experts", 0)) if arch in MOE_ARCHS else 0,
             top_k=int(d.get("num_experts_per_tok", 0)) if arch in MOE_ARCHS else 0,
             max_position_embeddings=int(d.get("max_position_embeddings", 8192)),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             name=name or d.get("_name_or_path") or d.get("model_type", "model"),
-            qkv_bias=arch == "Qwen2ForCausalLM")
+            qkv_bias=arch == "Qwen2ForCausalLM", rope_scaling=dict(scaling) if scaling else None)
         # Sliding-window attention (Mistral v0.1; Qwen2 only with use_sliding_window): the attention kernels attend over the
         # whole context, which is the same function as long as a sequence is no longer than the window, so the window
         # becomes the position limit and longer requests are refused instead of being answered differently.
@@ -110,6 +125,8 @@ class ModelConfig:
              "hidden_act": "silu"}
         if self.is_moe:
             d.update(num_local_experts=self.num_experts, num_experts_per_tok=self.top_k)
+        if self.rope_scaling:
+            d["rope_scaling"] = dict(self.rope_scaling)
         return d
 
     @staticmethod

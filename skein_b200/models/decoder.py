@@ -162,7 +162,7 @@ class Decoder:
         dev = (weights.embed if weights.embed is not None else weights.layers[0].attn_norm).device
         self.device = dev
         self.max_pos = max_pos or cfg.max_position_embeddings
-        self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev)
+        self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev, cfg.rope_scaling)
         self.num_pages = num_pages
         if kv_pools is not None:
             want = (num_pages, 2, self.sh["Hkv"], page_size, cfg.head_dim)

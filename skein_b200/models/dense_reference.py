@@ -11,6 +11,7 @@ import math
 
 import torch
 
+from ..ops.reference import rope_inv_freq
 from .config import ModelConfig
 from .decoder import ModelWeights
 
@@ -20,11 +21,11 @@ def _rms(x, g, eps):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)) * g.float()
 
 
-def _rope(x, pos, theta):
+def _rope(x, pos, theta, scaling=None):
     # x: [T, heads, D]
     D = x.shape[-1]
     half = D // 2
-    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64, device=x.device) * 2.0 / D))
+    inv = rope_inv_freq(D, theta, scaling).to(x.device)
     ang = pos.double().unsqueeze(1) * inv.unsqueeze(0)
     cos, sin = ang.cos().float().unsqueeze(1), ang.sin().float().unsqueeze(1)
     x0, x1 = x[..., :half], x[..., half:]
@@ -44,8 +45,8 @@ def forward_full(cfg: ModelConfig, w: ModelWeights, token_ids: torch.Tensor, cap
         qkv = h @ lw.wqkv.float().t()
         if getattr(lw, "bqkv", None) is not None:
             qkv = qkv + lw.bqkv.float()
-        q = _rope(qkv[:, :Hq * D].view(T, Hq, D), pos, cfg.rope_theta)
-        k = _rope(qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D), pos, cfg.rope_theta)
+        q = _rope(qkv[:, :Hq * D].view(T, Hq, D), pos, cfg.rope_theta, cfg.rope_scaling)
+        k = _rope(qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D), pos, cfg.rope_theta, cfg.rope_scaling)
         v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
         G = Hq // Hkv
         k = k.repeat_interleave(G, dim=1)

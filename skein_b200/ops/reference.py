@@ -73,10 +73,33 @@ def reduce_residual_rmsnorm(residual, partial, gamma, eps, row_idx=None, row_w=N
     return res_out, normed.to(dt)
 
 
-def rope_cos_sin_table(max_pos: int, head_dim: int, theta: float, device=None):
-    """[max_pos, head_dim/2, 2] fp32 (cos, sin), the table the RoPE kernel reads."""
+def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
+    """The head_dim / 2 rotation frequencies (float64), with the checkpoint's frequency scaling applied: none, "linear"
+    (every frequency divided by `factor`) or "llama3" (Llama 3.1 and later: wavelengths beyond the original context
+    are stretched by `factor`, short ones kept, the band in between blended). Other schemes are refused by the importer."""
     half = head_dim // 2
-    inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
+    if kind == "default":
+        return inv
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor
+    if kind == "llama3":
+        lo, hi = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        orig = float(scaling["original_max_position_embeddings"])
+        wavelen = 2.0 * math.pi / inv
+        smooth = (orig / wavelen - lo) / (hi - lo)
+        blended = (1.0 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > orig / lo, inv / factor, inv)
+        medium = ~(wavelen < orig / hi) & ~(wavelen > orig / lo)
+        return torch.where(medium, blended, out)
+    raise ValueError(f"rope scaling {kind!r} is not supported")
+
+
+def rope_cos_sin_table(max_pos: int, head_dim: int, theta: float, device=None, scaling: dict | None = None):
+    """[max_pos, head_dim/2, 2] fp32 (cos, sin), the table the RoPE kernel reads."""
+    inv_freq = rope_inv_freq(head_dim, theta, scaling)
     ang = torch.arange(max_pos, dtype=torch.float64).unsqueeze(1) * inv_freq.unsqueeze(0)
     tab = torch.stack([ang.cos(), ang.sin()], dim=-1).to(torch.float32)
     return tab.to(device) if device is not None else tab

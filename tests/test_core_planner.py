@@ -67,12 +67,45 @@ def test_importer_layer_order_and_names():
     (lambda c: c.update(num_key_value_heads=5), "multiple"),
     (lambda c: c.update(num_experts_per_tok=9), "num_experts_per_tok"),
     (lambda c: c.pop("hidden_size"), "hidden_size"),
+    (lambda c: c.update(rope_scaling={"rope_type": "yarn", "factor": 4.0}), "rope scaling"),
+    (lambda c: c.update(rope_parameters={"rope_type": "dynamic", "factor": 2.0, "rope_theta": 1e6}), "rope scaling"),
+    (lambda c: c.update(architectures=["LlamaForCausalLM"], attention_bias=True), "attention_bias"),
+    (lambda c: c.update(architectures=["LlamaForCausalLM"], mlp_bias=True), "mlp_bias"),
 ])
 def test_importer_rejections(mutate, msg):
+    """What the runtime would compute differently from the checkpoint's own modelling code is refused, by the C++ importer
+    and by its Python mirror alike, instead of being served wrong."""
+    from skein_b200.models.config import ModelConfig
     c = json.loads(CFG)
     mutate(c)
     with pytest.raises(Exception, match=msg):
         core.import_model(json.dumps(c))
+    with pytest.raises(Exception, match=msg):
+        ModelConfig.from_hf_dict(c)
+
+
+def test_importers_agree_on_family_details():
+    from skein_b200.models.config import ModelConfig
+    base = json.loads(LLAMA)
+    # Qwen2: q / k / v biases are parameters; its listed window applies only with use_sliding_window
+    q = dict(base, architectures=["Qwen2ForCausalLM"], sliding_window=4096, use_sliding_window=False, max_position_embeddings=32768)
+    g = json.loads(core.import_model(json.dumps(q)))
+    names = [p["name"] for l in g["layers"] for p in l["params"]]
+    assert "model.layers.0.self_attn.q_proj.bias" in names and "model.layers.0.self_attn.o_proj.bias" not in names
+    assert g["meta"]["qkv_bias"] is True and g["meta"]["max_position"] == 32768
+    cq = ModelConfig.from_hf_dict(q)
+    assert cq.qkv_bias and cq.max_position_embeddings == 32768 and cq.param_count() == core.model_param_count(json.dumps(q))
+    assert "qkv_bias" not in json.loads(core.import_model(LLAMA))["meta"]          # plans of bias-free models keep their hash
+    # a window that applies becomes the position limit (Mistral v0.1)
+    m = dict(base, architectures=["MistralForCausalLM"], sliding_window=4096, max_position_embeddings=32768)
+    assert json.loads(core.model_meta(json.dumps(m)))["max_position"] == 4096 and ModelConfig.from_hf_dict(m).max_position_embeddings == 4096
+    # theta nested in rope_parameters (recent checkpoints), llama3 scaling accepted
+    n = {k: v for k, v in base.items() if k != "rope_theta"}
+    n["rope_parameters"] = {"rope_theta": 5e5, "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192}
+    assert json.loads(core.model_meta(json.dumps(n)))["rope_theta"] == 5e5
+    cn = ModelConfig.from_hf_dict(n)
+    assert cn.rope_theta == 5e5 and cn.rope_scaling["rope_type"] == "llama3" and cn.to_hf_dict()["rope_scaling"]["factor"] == 8.0
 
 
 def test_plan_round_trip_and_hash_stability():

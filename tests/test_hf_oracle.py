@@ -36,6 +36,14 @@ def _hf_model(kind):
     elif kind == "mistral":
         cfg = transformers.MistralConfig(rope_theta=1e4, sliding_window=None, **common)
         m = transformers.MistralForCausalLM(cfg)
+    elif kind == "llama-rope-llama3":      # Llama 3.1-style frequency scaling
+        cfg = transformers.LlamaConfig(rope_theta=5e5, rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                                     "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
+                                       **common)
+        m = transformers.LlamaForCausalLM(cfg)
+    elif kind == "llama-rope-linear":
+        cfg = transformers.LlamaConfig(rope_theta=5e5, rope_scaling={"rope_type": "linear", "factor": 4.0}, **common)
+        m = transformers.LlamaForCausalLM(cfg)
     elif kind == "llama-tied":   # the output projection is the embedding table
         cfg = transformers.LlamaConfig(rope_theta=5e5, **{**common, "tie_word_embeddings": True})
         m = transformers.LlamaForCausalLM(cfg)
@@ -52,17 +60,15 @@ def _hf_model(kind):
     return m.eval()
 
 
-@pytest.mark.parametrize("kind", ["mixtral", "llama", "mistral", "qwen2", "llama-tied"])
+@pytest.mark.parametrize("kind", ["mixtral", "llama", "mistral", "qwen2", "llama-tied", "llama-rope-llama3", "llama-rope-linear"])
 def test_decoder_matches_huggingface_transformers(kind, tmp_path):
     hf = _hf_model(kind)
     ckpt = tmp_path / "ckpt"
     hf.save_pretrained(ckpt, safe_serialization=True)
     cfg_json = (ckpt / "config.json").read_text()
-    d = json.loads(cfg_json)
-    if "rope_theta" not in d:          # newer transformers nest it
-        d["rope_theta"] = d["rope_parameters"]["rope_theta"]
-        cfg_json = json.dumps(d)
-    cfg = ModelConfig.from_hf_dict(json.loads(cfg_json))
+    d = json.loads(cfg_json)      # as transformers wrote it: recent versions nest theta and the scaling in `rope_parameters`
+    cfg = ModelConfig.from_hf_dict(d)
+    assert (cfg.rope_scaling is not None) == ("rope" in kind) and cfg.rope_theta == (1e6 if kind in ("mixtral", "qwen2") else 1e4 if kind == "mistral" else 5e5)
     plan = core.extract_plan(cfg_json, *INPUTS, {"force_batch": 4}, [["bf16", "bf16", "bf16"]])["plan_json"]
     art = Artifact(build_artifact(plan, cfg_json, tmp_path / "art", WeightSource(cfg, str(ckpt))))
     ours = parity.ArtifactForward(art, "cpu")
