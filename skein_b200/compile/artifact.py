@@ -67,6 +67,8 @@ class WeightSource:
             return _random_param(name, shape, self.seed, self.std)
         from safetensors import safe_open
 
+        if self._index is not None and name not in self._index:
+            raise ArtifactError(f"checkpoint has no tensor `{name}`")
         f = self._index[name] if self._index is not None else self._single
         if f not in self._files:
             self._files[f] = safe_open(str(f), framework="pt")
