@@ -161,6 +161,9 @@ class Decoder:
         self.page_size = page_size
         dev = (weights.embed if weights.embed is not None else weights.layers[0].attn_norm).device
         self.device = dev
+        if dev.type == "cuda" and cfg.head_dim != 128:
+            # say so when the model is set up, not in the middle of the first request
+            raise ValueError(f"the attention kernels are built for head size 128; this model has {cfg.head_dim}")
         self.max_pos = max_pos or cfg.max_position_embeddings
         self.cos_sin = ref.rope_cos_sin_table(self.max_pos, cfg.head_dim, cfg.rope_theta, dev, cfg.rope_scaling)
         self.num_pages = num_pages
