@@ -121,6 +121,8 @@ def cmd_serve(args, emit) -> int:
         argv.append("--enable-hot-swap")
     if not args.cuda_graphs:
         argv.append("--no-cuda-graphs")
+    if getattr(args, "ignore_eos", False):
+        argv.append("--ignore-eos")
     if args.speculative_draft:
         argv += ["--speculative-draft", args.speculative_draft, "--speculative-k", str(args.speculative_k)]
     for flag, val in (("--workload", args.workload), ("--cost", args.cost), ("--prompt", args.prompt), ("--demo-prompts", args.demo_prompts)):

@@ -94,6 +94,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--top-k", type=int, default=0)
     s.add_argument("--top-p", type=float, default=1.0)
     s.add_argument("--seed", type=int, default=0)
+    s.add_argument("--ignore-eos", action="store_true",
+                   help="generate max_tokens tokens even when the model emits its end-of-sequence token (benchmarks)")
     s.add_argument("--speculative-draft", default=None, help="artifact of a smaller draft model: speculative decoding in the generation job")
     s.add_argument("--speculative-k", type=int, default=4, help="draft tokens proposed per verification step")
     s.add_argument("--max-batch", type=int, default=0)

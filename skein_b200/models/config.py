@@ -37,6 +37,7 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     name: str = "mixtral-8x7b"
     qkv_bias: bool = False        # the q / k / v projections carry a bias each (Qwen2)
+    eos_token_id: int = -1        # token that ends a generation (-1: none known)
     rope_scaling: dict | None = None   # the checkpoint's RoPE frequency scaling ("linear" or "llama3"), None = plain RoPE
 
     @property
@@ -105,6 +106,10 @@ class ModelConfig:
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             name=name or d.get("_name_or_path") or d.get("model_type", "model"),
             qkv_bias=arch == "Qwen2ForCausalLM", rope_scaling=dict(scaling) if scaling else None)
+        eos = d.get("eos_token_id")
+        if isinstance(eos, (list, tuple)):      # several end tokens: the engine stops on one, the first listed
+            eos = eos[0] if eos else None
+        cfg.eos_token_id = int(eos) if eos is not None else -1
         # Sliding-window attention (Mistral v0.1; Qwen2 only with use_sliding_window): the attention kernels attend over the
         # whole context, which is the same function as long as a sequence is no longer than the window, so the window
         # becomes the position limit and longer requests are refused instead of being answered differently.

@@ -80,6 +80,10 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
                         use_graphs=(device.type == "cuda" and art.plan["execution"]["cuda_graphs"]["enable"] and fused
                                     and pp_info is None and not getattr(args, "no_cuda_graphs", False)))
     ecfg.warm_graphs = ecfg.use_graphs      # every batch bucket is captured while the server starts, not under load
+    # a checkpoint that ships its tokenizer is a real model: its generations end at the model's end-of-sequence token
+    # (an artifact without one is driven with byte tokens and random weights, where no token means "stop")
+    if art.tokenizer_path() is not None and not getattr(args, "ignore_eos", False):
+        ecfg.eos_token = art.cfg.eos_token_id
     # pipeline parallelism: one group of sequences per stage kept in flight across engine steps instead of a pipeline
     # drained at the end of every step
     ecfg.pp_continuous = pp_info is not None and os.environ.get("SKEIN_PP_CONTINUOUS", "0") == "1"
@@ -274,6 +278,7 @@ def parse(argv=None):
     ap.add_argument("--bytes-per-token", type=int, default=0)
     ap.add_argument("--enable-hot-swap", action="store_true")
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)

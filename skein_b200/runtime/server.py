@@ -2,7 +2,7 @@
 
     POST /v1/completions   {"prompt": str | [int], "max_tokens": int, "stream": bool,
                             "temperature": float, "top_k": int, "top_p": float, "seed": int}   (sampling optional)
-        stream=false -> {"id", "tokens", "text", "finish_reason"}
+        stream=false -> {"id", "tokens", "text", "finish_reason"}   ("stop": the model's end-of-sequence token, else "length")
         stream=true  -> text/event-stream with `event: token` / data {"id", "token", "text", "is_final"}
         429 when admission rejects the request, 400 on a malformed body
     GET /metrics           Prometheus text of the engine's instruments
@@ -80,7 +80,9 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer, hotswap=None, artifact
                 break
         if err:
             return web.json_response({"id": rid, "error": {"kind": "step_failed", "message": err}}, status=503)
-        return web.json_response({"id": rid, "tokens": toks, "text": tokenizer.decode(toks), "finish_reason": "length"})
+        eos = driver.engine.cfg.eos_token
+        reason = "stop" if (eos >= 0 and toks and toks[-1] == eos) else "length"
+        return web.json_response({"id": rid, "tokens": toks, "text": tokenizer.decode(toks), "finish_reason": reason})
 
     async def metrics(_):
         return web.Response(text=driver.engine.metrics.render(), content_type="text/plain")

@@ -85,6 +85,50 @@ def test_http_completions_stream_metrics_and_errors(tmp_path):
         driver.stop()
 
 
+def test_generation_ends_at_the_models_end_of_sequence_token(tmp_path):
+    """`eos_token_id` of the checkpoint's config ends a generation (finish_reason "stop") when the artifact ships the
+    model's tokenizer; an artifact without one (byte tokens, random weights) has no such token, and --ignore-eos
+    switches it off."""
+    from aiohttp.test_utils import TestClient, TestServer
+    from tokenizers import Tokenizer as HFTokenizer
+    from tokenizers.models import WordLevel
+
+    from skein_b200.compile.artifact import WeightSource
+    from skein_b200.models.config import ModelConfig
+    from skein_b200.parallel import worker
+
+    art = make_artifact(tmp_path / "plain")
+    free = make_engine(art).generate([[5, 6, 7]], 5)[0]
+    cfg_eos = json.dumps({**json.loads(TINY), "eos_token_id": [free[2], 299]})          # several end tokens: the first counts
+    assert ModelConfig.from_hf_dict(json.loads(cfg_eos)).eos_token_id == free[2] and ModelConfig.from_hf_dict(json.loads(TINY)).eos_token_id == -1
+    tok_file = tmp_path / "tokenizer.json"
+    HFTokenizer(WordLevel({f"t{i}": i for i in range(300)}, unk_token="t0")).save(str(tok_file))
+    plan = core.extract_plan(cfg_eos, *INPUTS, {"force_batch": 4}, [["bf16", "bf16", "bf16"]])["plan_json"]
+    c = ModelConfig.from_hf_dict(json.loads(cfg_eos))
+    with_tok = Artifact(build_artifact(plan, cfg_eos, tmp_path / "tok", WeightSource(c, seed=0, std=0.05), tokenizer_json=tok_file))
+    no_tok = Artifact(build_artifact(plan, cfg_eos, tmp_path / "notok", WeightSource(c, seed=0, std=0.05)))
+    dev = torch.device("cpu")
+    args = lambda a, *extra: worker.parse(["--artifact", str(a.path), "--cpu", "--max-seq-len", "256", *extra])  # noqa: E731
+    eng = worker.build_engine(with_tok, 0, dev, None, args(with_tok))
+    assert eng.cfg.eos_token == free[2]
+    assert worker.build_engine(no_tok, 0, dev, None, args(no_tok)).cfg.eos_token == -1
+    assert worker.build_engine(with_tok, 0, dev, None, args(with_tok, "--ignore-eos")).cfg.eos_token == -1
+    assert eng.generate([[5, 6, 7]], 5)[0] == free[:3]                                  # ends with the end token, which is delivered
+    driver = EngineDriver(eng).start()
+
+    async def scenario():
+        async with TestClient(TestServer(build_app(driver, Tokenizer(300)))) as cl:
+            body = await (await cl.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 5})).json()
+            assert body["tokens"] == free[:3] and body["finish_reason"] == "stop"
+            body = await (await cl.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 2})).json()
+            assert body["tokens"] == free[:2] and body["finish_reason"] == "length"
+
+    try:
+        asyncio.run(asyncio.wait_for(scenario(), 120))
+    finally:
+        driver.stop()
+
+
 def test_hot_swap_reject_drain_and_timeout(tmp_path):
     a = make_artifact(tmp_path / "a", seed=0)
     b = make_artifact(tmp_path / "b", seed=1, batch=8)           # same shapes, other weights and batch policy
