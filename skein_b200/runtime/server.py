@@ -3,7 +3,7 @@
     POST /v1/completions   {"prompt": str | [int], "max_tokens": int, "stream": bool,
                             "temperature": float, "top_k": int, "top_p": float, "seed": int}   (sampling optional)
         stream=false -> {"id", "tokens", "text", "finish_reason"}   ("stop": the model's end-of-sequence token, else "length")
-        stream=true  -> text/event-stream with `event: token` / data {"id", "token", "text", "is_final"}
+        stream=true  -> text/event-stream with `event: token` / data {"id", "token", "text", "is_final"[, "finish_reason"]}
         429 when admission rejects the request, 400 on a malformed body
     GET /metrics           Prometheus text of the engine's instruments
     POST /admin/hotswap    {"artifact": path} (only with hot swap enabled): verify, drain, mount on every rank
@@ -64,6 +64,9 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer, hotswap=None, artifact
                            "is_final": ev.is_final}
                 if ev.error:
                     payload["error"] = ev.error
+                elif ev.is_final:
+                    eos = driver.engine.cfg.eos_token
+                    payload["finish_reason"] = "stop" if (eos >= 0 and ev.token == eos) else "length"
                 await resp.write(f"event: token\ndata: {json.dumps(payload)}\n\n".encode())
                 if ev.is_final:
                     break

@@ -122,6 +122,9 @@ def test_generation_ends_at_the_models_end_of_sequence_token(tmp_path):
             assert body["tokens"] == free[:3] and body["finish_reason"] == "stop"
             body = await (await cl.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 2})).json()
             assert body["tokens"] == free[:2] and body["finish_reason"] == "length"
+            r = await cl.post("/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 5, "stream": True})
+            events = [json.loads(l[6:]) for l in (await r.text()).splitlines() if l.startswith("data: ")]
+            assert [e["token"] for e in events] == free[:3] and events[-1]["finish_reason"] == "stop" and "finish_reason" not in events[0]
 
     try:
         asyncio.run(asyncio.wait_for(scenario(), 120))
