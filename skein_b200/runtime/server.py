@@ -22,7 +22,7 @@ import threading
 
 from .driver import EngineDriver
 from .engine import Engine, SamplingParams
-from .tokenizer import Tokenizer
+from .tokenizer import IncrementalDecoder, Tokenizer
 
 __all__ = ["EngineDriver", "build_app", "serve", "serve_metrics_only"]
 
@@ -58,9 +58,10 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer, hotswap=None, artifact
         if stream:
             resp = web.StreamResponse(headers={"Content-Type": "text/event-stream", "Cache-Control": "no-cache"})
             await resp.prepare(request)
+            pieces = IncrementalDecoder(tokenizer)
             while True:
                 ev = await next_event(q)
-                payload = {"id": rid, "token": ev.token, "text": tokenizer.decode([ev.token]) if ev.token >= 0 else "",
+                payload = {"id": rid, "token": ev.token, "text": pieces.push(ev.token) if ev.token >= 0 else "",
                            "is_final": ev.is_final}
                 if ev.error:
                     payload["error"] = ev.error

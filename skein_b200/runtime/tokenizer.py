@@ -30,3 +30,25 @@ class Tokenizer:
         if self._tok is not None:
             return self._tok.decode(list(ids))
         return bytes(i % 256 for i in ids).decode("utf-8", errors="replace")
+
+
+class IncrementalDecoder:
+    """Text of a token stream, piece by piece. Decoding tokens one at a time loses what only shows between tokens (the
+    space a sentencepiece token carries in front, a character whose bytes are spread over several tokens), so each piece
+    is the difference between two decodes of a short window: the tokens since the last emitted piece with and without
+    the new ones. A piece that would end in the middle of a character is held back until the character is complete."""
+
+    def __init__(self, tokenizer: Tokenizer):
+        self.tok = tokenizer
+        self.ids: list[int] = []
+        self.prefix_off = 0      # start of the decode window
+        self.read_off = 0        # tokens before this index have been emitted
+
+    def push(self, token: int) -> str:
+        self.ids.append(int(token))
+        before = self.tok.decode(self.ids[self.prefix_off:self.read_off])
+        now = self.tok.decode(self.ids[self.prefix_off:])
+        if len(now) > len(before) and not now.endswith("\ufffd"):
+            self.prefix_off, self.read_off = self.read_off, len(self.ids)
+            return now[len(before):]
+        return ""

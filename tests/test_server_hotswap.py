@@ -48,6 +48,26 @@ def test_tokenizer_fallback():
     assert Tokenizer(50).encode("hi") == [104 % 50, 105 % 50]
 
 
+def test_streamed_text_is_decoded_incrementally(tmp_path):
+    """The pieces of a stream add up to the decode of the whole: the space in front of a sentencepiece token and a
+    character spread over several byte tokens are not lost."""
+    from tokenizers import Tokenizer as HFTokenizer
+    from tokenizers import decoders
+    from tokenizers.models import WordLevel
+
+    from skein_b200.runtime.tokenizer import IncrementalDecoder
+    hf = HFTokenizer(WordLevel({"\u2581hello": 0, "\u2581wor": 1, "ld": 2, "<unk>": 3}, unk_token="<unk>"))
+    hf.decoder = decoders.Metaspace()
+    f = tmp_path / "tokenizer.json"
+    hf.save(str(f))
+    t = Tokenizer(4, f)
+    assert t.decode([1]) == "wor"                                # one token at a time the space is gone
+    d = IncrementalDecoder(t)
+    assert [d.push(i) for i in (0, 1, 2, 0)] == ["hello", " wor", "ld", " hello"]
+    fb = IncrementalDecoder(Tokenizer(300))                       # byte tokens: "h", then the two bytes of e-acute, then "!"
+    assert [fb.push(b) for b in "h\u00e9!".encode()] == ["h", "", "\u00e9", "!"]
+
+
 def test_http_completions_stream_metrics_and_errors(tmp_path):
     from aiohttp.test_utils import TestClient, TestServer
 
