@@ -42,6 +42,39 @@ def default_parity_prompts(cfg: ModelConfig, n: int, length: int = 24, seed: int
     return [torch.randint(0, cfg.vocab_size, (length,), generator=g).tolist() for _ in range(n)]
 
 
+def estimate_runtime(plan_json: str, config_json: str, cluster_toml: str, constants_toml: str) -> dict:
+    """The batcher's latency estimator for this plan on this cluster, taken from the placement cost model instead of the
+    constants file's machine-independent defaults: the decode step at batch 1, the exponent of the power law through the
+    steps at batch 1 and at the plan's batch, and the prefill time per prompt token (2 FLOPs per active parameter at the
+    measured GEMM rate, divided among the tensor-parallel ranks). The admission rule (predicted TPOT against the SLO) is only
+    as good as these numbers: with the defaults (8 ms x batch^0.7) a B200 that steps 64 sequences in 17 ms is predicted to need
+    147 ms and admits a fifth of what it can serve."""
+    import math
+    import re
+    plan = json.loads(plan_json)
+    B = int(plan["batching"]["max_batch"])
+
+    def step_us(batch):
+        p = json.loads(plan_json)
+        p["batching"]["max_batch"] = batch
+        return float(core.cost_breakdown(json.dumps(p), config_json, cluster_toml, constants_toml, 0)["total"])
+    c1 = step_us(1)
+    exponent = 0.7
+    if B > 1:
+        exponent = min(1.0, max(0.0, math.log(max(step_us(B), c1) / c1) / math.log(B)))
+    cfg = ModelConfig.from_hf_dict(json.loads(config_json))
+    consts = json.loads(core.cost_constants_json(constants_toml))
+    m = re.search(r'device_kind\s*=\s*"([^"]+)"', cluster_toml)
+    kind = m.group(1) if m else "b200"
+    peak = consts["peak_tflops"].get(kind, {}).get("bf16", 1000.0) * consts["efficiency"]["gemm"].get("bf16", 0.7)
+    H, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    active = cfg.num_layers * (2 * H * D * (cfg.num_heads + cfg.num_kv_heads) + 3 * H * I * (cfg.top_k if cfg.is_moe else 1)) + cfg.vocab_size * H
+    tp = max(1, int(plan["parallelism"]["tp"]))
+    prefill_us = 2.0 * active / (peak * 1e12) * 1e6 / tp
+    return {"per_token_decode_us_at_b1": round(c1, 1), "batch_scaling_exponent": round(exponent, 4),
+            "prefill_per_token_us": round(prefill_us, 3), "source": "placement cost model"}
+
+
 def compile_model(config_json: str, cluster_toml: str, trace_jsonl: str, drift_toml: str, constants_toml: str, out_root,
                   weights: str | None = None, options: dict | None = None, n_parity_prompts: int = 8, prompts=None,
                   enforce_parity: bool = False, max_replans: int = 2, parity_device: str = "cpu", seed: int = 0,
@@ -94,5 +127,6 @@ def compile_model(config_json: str, cluster_toml: str, trace_jsonl: str, drift_t
         from ..calibrate import autotune_decode_gemms
         autotune_decode_gemms(cfg, int(plan["parallelism"]["tp"]), int(plan["batching"]["max_batch"]),
                               art_dir / "cache" / "kernel_configs.json", seed=seed, budget=search_budget)
+    (art_dir / "runtime_estimator.json").write_text(json.dumps(estimate_runtime(plan_json, config_json, cluster_toml, constants_toml)))
     update_latest_symlink(out_root, art_dir)
     return CompileResult(art_dir, plan, report, replans, drift_toml)

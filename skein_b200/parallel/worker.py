@@ -96,6 +96,13 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
         lens = [json.loads(l).get("prompt_tokens") for l in text.splitlines()[1:] if l.strip()]
         ecfg.drift_baseline = tuple(int(x) for x in lens if x)
         ecfg.drift_threshold_kl = float(w.get("recompile_drift_threshold_kl", ecfg.drift_threshold_kl))
+    est = art.path / "runtime_estimator.json"
+    if est.exists() and not args.cost:
+        # the latency estimator that `compile` derived from the cost model for this plan and cluster
+        c = json.loads(est.read_text())
+        ecfg.decode_us_at_b1 = c.get("per_token_decode_us_at_b1", ecfg.decode_us_at_b1)
+        ecfg.batch_exponent = c.get("batch_scaling_exponent", ecfg.batch_exponent)
+        ecfg.prefill_per_token_us = c.get("prefill_per_token_us", ecfg.prefill_per_token_us)
     if args.cost:
         from .. import core
         c = json.loads(core.cost_constants_json(open(args.cost).read())).get("runtime_estimator", {})

@@ -140,6 +140,25 @@ def test_compile_end_to_end_with_replan_and_latest(tmp_path):
         assert f"model.layers.{fp8_layer}.self_attn.q_proj.weight.scale" in sf.keys()
     # real fp8 block-scaled weights pass the gate on this model
     assert r.report.passed, r.report.to_json()
+    # the batcher's latency estimator of this plan comes out of the cost model and the serving engine takes it from the
+    # artifact (a --cost file given to `serve` still wins)
+    from skein_b200.compile.pipeline import estimate_runtime
+    from skein_b200.parallel import worker
+    est = json.loads((r.artifact_dir / "runtime_estimator.json").read_text())
+    assert est["per_token_decode_us_at_b1"] > 0 and 0.0 <= est["batch_scaling_exponent"] <= 1.0 and est["prefill_per_token_us"] > 0
+    eng = worker.build_engine(art, 0, torch.device("cpu"), None, worker.parse(["--artifact", str(r.artifact_dir), "--cpu", "--max-seq-len", "128"]))
+    assert eng.cfg.decode_us_at_b1 == est["per_token_decode_us_at_b1"] and eng.cfg.batch_exponent == est["batch_scaling_exponent"]
+    cost_file = tmp_path / "cost.toml"
+    cost_file.write_text(CONST)
+    eng2 = worker.build_engine(art, 0, torch.device("cpu"), None,
+                               worker.parse(["--artifact", str(r.artifact_dir), "--cpu", "--max-seq-len", "128", "--cost", str(cost_file)]))
+    assert eng2.cfg.decode_us_at_b1 == 8000.0
+    # Mixtral-8x7B on 8 B200s: the estimate reproduces the measured 64-sequence step (4.44 ms) where the defaults say 147 ms
+    mix = (ROOT / "configs/mixtral_8x7b_config.json").read_text()
+    plan8 = core.extract_plan(mix, cluster(8), TRACE, (ROOT / "models/mixtral_8x7b_drift.toml").read_text(), CONST,
+                              {"force_tp": 8, "force_pp": 1, "force_ep": 1, "force_batch": 64})["plan_json"]
+    e8 = estimate_runtime(plan8, mix, cluster(8), CONST)
+    assert 3.5 < e8["per_token_decode_us_at_b1"] * 64 ** e8["batch_scaling_exponent"] / 1e3 < 5.5
     # enforce + impossible tolerance -> failure is raised after re-plans that push the drift table up
     strict = const.replace("fp8_e4m3 = 5.0e-3", "fp8_e4m3 = 1.0e-12")
     r2 = compile_model(TINY, tiny_mem, trace, DRIFT, strict, tmp_path / "b", options={"force_batch": 2}, n_parity_prompts=1, seed=1, max_replans=3)
