@@ -279,34 +279,33 @@ class Artifact:
 
     def _assemble(self, get, lay: ParallelLayout) -> ModelWeights:
         cfg = self.cfg
-        if True:
-            layers = []
-            e_local = cfg.num_experts // lay.ep if cfg.is_moe else 0
-            e0 = lay.ep_rank * e_local
-            for b in lay.stage_layers(cfg.num_layers):
-                pre = f"model.layers.{b}."
-                wqkv = torch.cat([get(pre + f"self_attn.{p}_proj.weight") for p in "qkv"], dim=0).contiguous()
-                if cfg.is_moe:
-                    w13 = torch.stack([torch.cat([get(pre + f"block_sparse_moe.experts.{e}.w1.weight"),
-                                                  get(pre + f"block_sparse_moe.experts.{e}.w3.weight")], dim=0)
-                                       for e in range(e0, e0 + e_local)]).contiguous()
-                    w2 = torch.stack([get(pre + f"block_sparse_moe.experts.{e}.w2.weight") for e in range(e0, e0 + e_local)]).contiguous()
-                    router = get(pre + "block_sparse_moe.gate.weight")
-                else:
-                    w13 = torch.cat([get(pre + "mlp.gate_proj.weight"), get(pre + "mlp.up_proj.weight")], dim=0).contiguous()
-                    w2 = get(pre + "mlp.down_proj.weight").contiguous()
-                    router = None
-                bqkv = (torch.cat([get(pre + f"self_attn.{p}_proj.bias") for p in "qkv"]).contiguous() if cfg.qkv_bias else None)
-                layers.append(LayerWeights(attn_norm=get(pre + "input_layernorm.weight"), wqkv=wqkv,
-                                           wo=get(pre + "self_attn.o_proj.weight").contiguous(),
-                                           ffn_norm=get(pre + "post_attention_layernorm.weight"), router=router, w13=w13, w2=w2,
-                                           bqkv=bqkv))
-            first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
-            embed = get("model.embed_tokens.weight") if first else None
-            # tied embeddings: the output projection is the embedding table (under tensor parallelism both are split by
-            # vocabulary rows the same way, so a rank's table shard is its shard of the output projection)
-            lm_head = (embed if cfg.tie_word_embeddings else get("lm_head.weight")) if last else None
-            return ModelWeights(embed=embed, layers=layers, final_norm=get("model.norm.weight") if last else None, lm_head=lm_head)
+        layers = []
+        e_local = cfg.num_experts // lay.ep if cfg.is_moe else 0
+        e0 = lay.ep_rank * e_local
+        for b in lay.stage_layers(cfg.num_layers):
+            pre = f"model.layers.{b}."
+            wqkv = torch.cat([get(pre + f"self_attn.{p}_proj.weight") for p in "qkv"], dim=0).contiguous()
+            if cfg.is_moe:
+                w13 = torch.stack([torch.cat([get(pre + f"block_sparse_moe.experts.{e}.w1.weight"),
+                                              get(pre + f"block_sparse_moe.experts.{e}.w3.weight")], dim=0)
+                                   for e in range(e0, e0 + e_local)]).contiguous()
+                w2 = torch.stack([get(pre + f"block_sparse_moe.experts.{e}.w2.weight") for e in range(e0, e0 + e_local)]).contiguous()
+                router = get(pre + "block_sparse_moe.gate.weight")
+            else:
+                w13 = torch.cat([get(pre + "mlp.gate_proj.weight"), get(pre + "mlp.up_proj.weight")], dim=0).contiguous()
+                w2 = get(pre + "mlp.down_proj.weight").contiguous()
+                router = None
+            bqkv = (torch.cat([get(pre + f"self_attn.{p}_proj.bias") for p in "qkv"]).contiguous() if cfg.qkv_bias else None)
+            layers.append(LayerWeights(attn_norm=get(pre + "input_layernorm.weight"), wqkv=wqkv,
+                                       wo=get(pre + "self_attn.o_proj.weight").contiguous(),
+                                       ffn_norm=get(pre + "post_attention_layernorm.weight"), router=router, w13=w13, w2=w2,
+                                       bqkv=bqkv))
+        first, last = lay.pp_rank == 0, lay.pp_rank == lay.pp - 1
+        embed = get("model.embed_tokens.weight") if first else None
+        # tied embeddings: the output projection is the embedding table (under tensor parallelism both are split by
+        # vocabulary rows the same way, so a rank's table shard is its shard of the output projection)
+        lm_head = (embed if cfg.tie_word_embeddings else get("lm_head.weight")) if last else None
+        return ModelWeights(embed=embed, layers=layers, final_norm=get("model.norm.weight") if last else None, lm_head=lm_head)
 
 
 def verify_shape_compatibility(old: Artifact, new: Artifact) -> None:
