@@ -8,7 +8,7 @@ import torch
 
 from skein_b200.models import config as mc
 from skein_b200.models.decoder import Decoder, random_weights
-from skein_b200.runtime.engine import Engine, EngineConfig
+from skein_b200.runtime.engine import Engine, EngineConfig, SamplingParams
 
 
 def _decoder(device="cpu", seed=0, pages=96, cfg=None):
@@ -324,3 +324,38 @@ def test_engine_gpu_long_context_8192_token_prompt():
                                         max_prefill_tokens=16384)).generate(prompts, 4)
     assert got[1] == want[1], (got[1], want[1])
     assert got[0][0] == want[0][0] and sum(a == b for a, b in zip(got[0], want[0])) >= 3, (got[0], want[0])
+
+
+def test_random_arrivals_with_end_tokens_sampling_and_shared_prefixes_leak_no_pages():
+    """A few hundred steps of requests that arrive at random, share prompt prefixes, are prefilled in chunks, sample or
+    not, and end at their length limit or at the end-of-sequence token: no sequence continues after its end token,
+    every request ends, and every page is back in the pool."""
+    import random
+    cfg = mc.tiny_mixtral(layers=2, hidden=128, inter=256, heads=4, kv_heads=2, experts=4, vocab=64)
+    w = random_weights(cfg, mc.ParallelLayout(), "cpu", seed=3, std=0.2)
+    eng = Engine(Decoder(cfg, w, num_pages=128, page_size=16, max_pos=128),
+                 EngineConfig(max_batch=8, tpot_ms=1e9, ttft_ms=1e9, use_graphs=False, prefix_cache=True, chunk_tokens=16, eos_token=7))
+    rnd = random.Random(0)
+    shared = [rnd.randrange(64) for _ in range(40)]
+    done, finals, submitted, limits = {}, {}, 0, {}
+    for _ in range(3000):
+        if submitted < 60 and rnd.random() < 0.4:
+            p = shared[:rnd.choice([0, 16, 32])] + [rnd.randrange(64) for _ in range(rnd.randrange(1, 30))]
+            sp = SamplingParams(temperature=0.8, top_k=8, seed=submitted) if rnd.random() < 0.5 else None
+            n = rnd.randrange(1, 20)
+            rid, d = eng.submit(p, n, sampling=sp)
+            if d.kind != "reject":
+                submitted += 1
+                limits[rid] = n
+        elif submitted >= 60 and eng.idle:
+            break
+        for ev in eng.step():
+            assert ev.error is None and ev.request_id not in finals
+            done.setdefault(ev.request_id, []).append(ev.token)
+            if ev.is_final:
+                finals[ev.request_id] = ev.token
+    assert eng.idle and set(finals) == set(limits) and len(finals) == 60
+    for rid, toks in done.items():
+        assert 7 not in toks[:-1] and len(toks) <= limits[rid] and (toks[-1] == 7 or len(toks) == limits[rid])
+    assert any(t == 7 for t in finals.values()) and any(t != 7 for t in finals.values())
+    assert eng.kv.in_use_pages == 0
