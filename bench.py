@@ -143,6 +143,34 @@ def step_roofline(cfg, tp, ep, B, ctx, fp8_experts, ms_per_step, n_gpus, dp=1):
 
 
 
+def cost_model_prediction(cfg, tp, ep, B, ctx, fp8_experts, n_gpus):
+    """What the placement cost model (csrc/core/cost.hpp with cluster/cost_constants.toml, the numbers the planner ranks plans
+    by) says this decode step takes, so that every run shows the model beside the measurement. None when the inputs of
+    the model are not at hand (a GPU count without a cluster file)."""
+    try:
+        import re
+
+        from skein_b200 import core
+        root = os.path.dirname(os.path.abspath(__file__))
+        cluster = open(os.path.join(root, "cluster", f"b200_{n_gpus}x.toml")).read()
+        const = re.sub(r"decode_kv_tokens\s*=\s*\d+", f"decode_kv_tokens = {int(ctx)}", open(os.path.join(root, "cluster", "cost_constants.toml")).read())
+        cfg_json = json.dumps(cfg.to_hf_dict())
+        meta = json.loads(core.model_meta(cfg_json))
+        # the model's dtype map is per block: expert weights in e4m3 are the bulk of a block's bytes
+        wd = "fp8_e4m3" if fp8_experts else "bf16"
+        plan = {"parallelism": {"tp": tp, "pp": 1, "ep": ep}, "kv": {"layout": {"kind": "paged", "page_size": 16}, "kv_sharded": True},
+                "batching": {"kind": "continuous", "max_batch": B},
+                "dtype_map": {"per_layer": [{"weight": wd, "activation": "bf16", "kv_cache": "bf16"}] * meta["num_layers"]},
+                "execution": {"cuda_graphs": {"enable": True, "capture_classes": [{"batch_size": 1 << i, "kv_class": 0} for i in range(4)]},
+                              "spec_decode": {"enable": False, "draft": None}, "prefix_cache": {"enable": True, "reuse_policy": "lru_by_last_access"}},
+                "disaggregation": None, "model_meta": meta}
+        b = core.cost_breakdown(json.dumps(plan), cfg_json, cluster, const, 0)
+        return {"predicted_ms_per_step": round(b["total"] / 1e3, 3), "streaming_us": round(b["compute"]), "collectives_us": round(b["comm"]),
+                "per_kernel_us": round(b["launch"]), "kernels": int(b["kernels"])}
+    except Exception as e:      # noqa: BLE001  (the prediction is a side note of the benchmark line, never its failure)
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
 class ClockSampler:
     """SM clock and throttle reasons of one GPU, sampled DURING the timed region: NVML reads from a thread every
     10 ms (read-only queries), or `nvidia-smi -lms 100` when NVML cannot be loaded."""
@@ -859,6 +887,7 @@ def main():
                        "repeats": R, "ms_per_k_steps_all_repeats": [round(x, 3) for x in all_ms]},
             "roofline": step_roofline(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, ms / K, world,
                                       dp=ep if dec.dp_attention else 1),
+            "cost_model": cost_model_prediction(cfg, tp, ep, B, P + (W + K // 2), args.fp8_experts, world),
             "prefill_ms": round(prefill_ms, 1), "prefill_first_pass_ms": round(prefill_cold_ms, 1), "prefill_repeatable": prefill_repeatable,
             "prefill_tokens_per_s": round(B * P / prefill_ms * 1e3, 1),
             "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2),
