@@ -351,6 +351,7 @@ def bench_over_http(args, emit) -> int:
            "requests_ok": stats["ok"], "requests_rejected": stats["rejected"], "requests_failed": stats["failed"],
            "ttft_p50_ms": None if ttft_p50 is None else round(ttft_p50, 2), "ttft_p95_ms": None if ttft_p95 is None else round(ttft_p95, 2),
            "tpot_p99_ms": None if tpot_p99 is None else round(tpot_p99, 3), "wall_s": round(wall, 2), "baseline": args.baseline}
+    out = _select_metrics(args, out)
     emit(args, out, "\n".join(f"{k:20s} {v}" for k, v in out.items()))
     return 0
 
@@ -389,6 +390,17 @@ def bench_op_profile(args, emit) -> int:
     return 0
 
 
+_BENCH_METRIC_KEYS = {"throughput": ("throughput_tok_s",), "goodput": ("goodput_req_s",), "drift_compliance": ("drift_compliance",)}
+
+
+def _select_metrics(args, out: dict) -> dict:
+    """--metrics throughput,goodput,drift_compliance: the headline figures to report; counts, latencies and the wall time
+    always come along. An unknown name is an error before anything runs (cmd_bench checks it first)."""
+    want = [m.strip() for m in str(getattr(args, "metrics", "") or "").split(",") if m.strip()]
+    drop = {k for name, keys in _BENCH_METRIC_KEYS.items() if name not in want for k in keys}
+    return {k: v for k, v in out.items() if k not in drop}
+
+
 def cmd_bench(args, emit) -> int:
     """Replay a trace (arrival times honoured, scaled by --time-scale) against a single-process engine, or with --url
     against a running server over HTTP."""
@@ -396,6 +408,9 @@ def cmd_bench(args, emit) -> int:
 
     if getattr(args, "collectives", False):
         return bench_collectives(emit, args)
+    unknown = [m.strip() for m in str(getattr(args, "metrics", "") or "").split(",") if m.strip() and m.strip() not in _BENCH_METRIC_KEYS]
+    if unknown:
+        raise ValueError(f"--metrics: unknown metric(s) {unknown}; known: {sorted(_BENCH_METRIC_KEYS)}")
     if getattr(args, "synth", None):
         # the synthetic workloads of the planner tests and of the serving benchmarks, as a trace file
         n, seed = int(args.synth_requests), int(args.synth_seed)
@@ -461,5 +476,6 @@ def cmd_bench(args, emit) -> int:
     out = {"throughput_tok_s": round(done_tokens / wall, 2), "goodput_req_s": round(good / wall, 3), "drift_compliance": drift_ok,
            "requests_ok": ok, "requests_rejected": rejected, "ttft_p50_ms": ttft_p50, "tpot_p99_ms": tpot_p99, "wall_s": round(wall, 2),
            "baseline": args.baseline}
+    out = _select_metrics(args, out)
     emit(args, out, "\n".join(f"{k:20s} {v}" for k, v in out.items()))
     return 0

@@ -115,6 +115,14 @@ def test_compile_verify_serve_job_cpu(tmp_path, capsys):
                  "--time-scale", "1000"]) == 0
     b = json.loads(capsys.readouterr().out)
     assert b["requests_ok"] + b["requests_rejected"] == 2 and b["drift_compliance"] is True
+    assert "throughput_tok_s" in b and "goodput_req_s" in b
+    # --metrics chooses the headline figures; an unknown name is refused
+    assert main(["--output", "json", "bench", "--artifact", art, "--workload", str(ROOT / "cluster/sample_trace.jsonl"), "--max-requests", "1",
+                 "--time-scale", "1000", "--metrics", "throughput"]) == 0
+    b1 = json.loads(capsys.readouterr().out)
+    assert "throughput_tok_s" in b1 and "goodput_req_s" not in b1 and "drift_compliance" not in b1 and "requests_ok" in b1
+    assert main(["--output", "json", "bench", "--artifact", art, "--workload", str(ROOT / "cluster/sample_trace.jsonl"), "--metrics", "latency"]) != 0
+    assert "unknown metric" in capsys.readouterr().err
 
 
 def test_pipeline_artifact_served_by_two_cpu_rank_processes(tmp_path):
