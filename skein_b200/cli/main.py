@@ -36,7 +36,10 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument("--trace", required=True, help="workload trace JSONL (first line: SLO)")
         p.add_argument("--drift", required=True, help="drift table TOML")
         p.add_argument("--cost", required=True, help="cost constants TOML")
-        p.add_argument("--objective", default=os.environ.get("SKEIN_OBJECTIVE", "latency"), choices=["latency", "throughput"])
+        p.add_argument("--objective", default=os.environ.get("SKEIN_OBJECTIVE", "throughput"), choices=["latency", "throughput"],
+                       help="throughput (default): least time per generated token among the plans whose decode step meets the "
+                            "trace's TPOT SLO, which picks the largest batch that fits; latency: the shortest decode step, "
+                            "the reference's objective, which picks batch 1")
 
     e = sub.add_parser("extract", help="search placement + per-layer dtypes, write plan.json")
     planner_inputs(e)
