@@ -169,10 +169,9 @@ def run_rank(args) -> int:
             # the published buffers hold the partials of one prefill chunk (its expert-sorted rows for a MoE model)
             rows = max(512, 8192 * max(1, art.cfg.top_k if art.cfg.is_moe else 1))
             if tp > 1:
-                # tensor-parallel groups of 8 sum their partials inside the NVSwitch unless told otherwise (measured 4.46
-                # against 4.74 ms per Mixtral-8x7B step; no gain at 2 and 4 ranks, where it stays off)
-                mm = True if (tp >= 8 and "SKEIN_MULTIMEM" not in os.environ) else None
-                comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size, fused_rows=rows, multimem=mm)
+                # in-switch reduction (6 % of a step at 8 ranks) stays opt-in for a server (SKEIN_MULTIMEM=1): a rank that dies
+                # while its heap is bound to a multicast object takes its peers' GPUs with it, and a server must survive a rank
+                comm = TPComm(tp_group, device, hidden=art.cfg.hidden_size, fused_rows=rows)
             if ep > 1:
                 comm_moe = TPComm(stage_group, device, hidden=art.cfg.hidden_size, fused_rows=rows)
         elif tp > 1 or ep > 1:
