@@ -70,7 +70,7 @@ def estimate_runtime(plan_json: str, config_json: str, cluster_toml: str, consta
     H, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
     active = cfg.num_layers * (2 * H * D * (cfg.num_heads + cfg.num_kv_heads) + 3 * H * I * (cfg.top_k if cfg.is_moe else 1)) + cfg.vocab_size * H
     tp = max(1, int(plan["parallelism"]["tp"]))
-    prefill_us = 2.0 * active / (peak * 1e12) * 1e6 / tp
+    prefill_us = 2.0 * active / (peak * 1e12) * 1e6 / tp + float(consts.get("runtime_estimator", {}).get("prefill_overhead_us_per_token", 0.0))
     return {"per_token_decode_us_at_b1": round(c1, 1), "batch_scaling_exponent": round(exponent, 4),
             "prefill_per_token_us": round(prefill_us, 3), "source": "placement cost model"}
 

@@ -48,6 +48,17 @@ def size_kv_pool(art: Artifact, lay, device, total_kv_bytes: int, page_size: int
     return max(8, int((free - reserve_frac * total) // page_bytes))
 
 
+def prefill_slice_for_slo(tpot_ms: float, decode_us_at_b1: float, batch_exponent: float, max_batch: int, prefill_per_token_us: float,
+                          max_prefill_tokens: int) -> int:
+    """Prompt tokens a step may carry while other sequences decode, so that the step (the decode of a full batch plus the
+    slice) stays within the TPOT target: what is left of the target after the estimated decode step, divided by the
+    estimated prefill time per token, in multiples of 256 tokens between 256 and the engine's prefill limit."""
+    step_ms = decode_us_at_b1 * max(1, max_batch) ** batch_exponent / 1e3
+    room_us = max(0.0, tpot_ms - step_ms) * 1e3
+    n = int(room_us / max(prefill_per_token_us, 1e-3)) // 256 * 256
+    return max(256, min(int(max_prefill_tokens), n))
+
+
 def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp_info=None) -> Engine:
     lay = art.layout(rank)
     art.check_lowering(rank)
@@ -103,6 +114,9 @@ def build_engine(art: Artifact, rank: int, device, comm, args, comm_moe=None, pp
         ecfg.decode_us_at_b1 = c.get("per_token_decode_us_at_b1", ecfg.decode_us_at_b1)
         ecfg.batch_exponent = c.get("batch_scaling_exponent", ecfg.batch_exponent)
         ecfg.prefill_per_token_us = c.get("prefill_per_token_us", ecfg.prefill_per_token_us)
+        if args.workload:
+            ecfg.interleave_prefill_tokens = prefill_slice_for_slo(ecfg.tpot_ms, ecfg.decode_us_at_b1, ecfg.batch_exponent, ecfg.max_batch,
+                                                                   ecfg.prefill_per_token_us, ecfg.max_prefill_tokens)
     if args.cost:
         from .. import core
         c = json.loads(core.cost_constants_json(open(args.cost).read())).get("runtime_estimator", {})

@@ -159,6 +159,18 @@ def test_compile_end_to_end_with_replan_and_latest(tmp_path):
                               {"force_tp": 8, "force_pp": 1, "force_ep": 1, "force_batch": 64})["plan_json"]
     e8 = estimate_runtime(plan8, mix, cluster(8), CONST)
     assert 3.5 < e8["per_token_decode_us_at_b1"] * 64 ** e8["batch_scaling_exponent"] / 1e3 < 5.5
+    assert 8.0 < e8["prefill_per_token_us"] < 10.5                         # measured 9.3 us per prompt token at TP=8
+    # with a workload's TPOT target the prompt slice that rides with a decode step is what the target leaves room for
+    assert worker.prefill_slice_for_slo(50.0, 5349.0, 0.3032, 64, 26.5, 8192) == 1024     # 1 GPU: 18.9 ms step, 31 ms left at 26.5 us / token
+    assert worker.prefill_slice_for_slo(50.0, e8["per_token_decode_us_at_b1"], e8["batch_scaling_exponent"], 64, e8["prefill_per_token_us"], 8192) >= 4096
+    assert worker.prefill_slice_for_slo(10.0, 5349.0, 0.3032, 64, 26.5, 8192) == 256      # no room: the smallest slice
+    assert worker.prefill_slice_for_slo(1e9, 5349.0, 0.3032, 64, 26.5, 8192) == 8192      # no target: the engine's limit
+    trace_file = tmp_path / "trace.jsonl"
+    trace_file.write_text(TRACE)
+    eng3 = worker.build_engine(art, 0, torch.device("cpu"), None,
+                               worker.parse(["--artifact", str(r.artifact_dir), "--cpu", "--max-seq-len", "128", "--workload", str(trace_file)]))
+    assert eng3.cfg.tpot_ms == 50 and eng3.cfg.interleave_prefill_tokens == worker.prefill_slice_for_slo(
+        50.0, est["per_token_decode_us_at_b1"], est["batch_scaling_exponent"], eng3.cfg.max_batch, est["prefill_per_token_us"], eng3.cfg.max_prefill_tokens)
     # enforce + impossible tolerance -> failure is raised after re-plans that push the drift table up
     strict = const.replace("fp8_e4m3 = 5.0e-3", "fp8_e4m3 = 1.0e-12")
     r2 = compile_model(TINY, tiny_mem, trace, DRIFT, strict, tmp_path / "b", options={"force_batch": 2}, n_parity_prompts=1, seed=1, max_replans=3)
