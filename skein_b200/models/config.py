@@ -8,7 +8,7 @@ dense Llama-style block is a Mixtral block with a plain SwiGLU MLP instead of ro
 from __future__ import annotations
 
 import json
-from dataclasses import dataclass, field, asdict
+from dataclasses import asdict, dataclass
 from pathlib import Path
 
 MOE_ARCHS = {"MixtralForCausalLM"}

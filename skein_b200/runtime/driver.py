@@ -20,7 +20,6 @@ from __future__ import annotations
 import mmap
 import os
 import queue
-import struct
 import threading
 import time
 
