@@ -309,6 +309,19 @@ inline ExtractResult extract_plan(const Graph& ir, const Cluster& cl, const Work
   bool have = false;
   double best_score = 0;
   std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, bool>, std::optional<std::vector<PerLayerDtype>>> memo;
+  // throughput objective: the prompt length that 95 % of the trace's requests stay below; its prefill has to fit the TTFT target
+  uint32_t p95_prompt = 0;
+  if (opt.objective_throughput && !wl.requests.empty()) {
+    std::vector<uint64_t> lens;
+    for (auto& r : wl.requests) lens.push_back(r.prompt_tokens);
+    std::sort(lens.begin(), lens.end());
+    p95_prompt = (uint32_t)lens[std::min(lens.size() - 1, (size_t)(0.95 * (double)lens.size()))];
+  }
+  // kept in case no plan meets both targets (a plan that misses a target is still better than none): the best plan by the
+  // objective among those that meet the TPOT target but not the TTFT one, else the plan with the shortest step
+  ExtractResult fallback, fallback_tpot;
+  bool have_fallback = false, have_fallback_tpot = false;
+  double fallback_tpot_score = 0;
   for (auto& g : enumerate_global_configs(cl, ir, opt)) {
     ++res.counters.raw;
     if ((opt.force_tp && g.parallelism.tp != *opt.force_tp) || (opt.force_pp && g.parallelism.pp != *opt.force_pp) ||
@@ -334,10 +347,33 @@ inline ExtractResult extract_plan(const Graph& ir, const Cluster& cl, const Work
     ++res.counters.scored;
     double score = total;
     if (opt.objective_throughput) {
+      if (!have_fallback || total < fallback.cost_us) { fallback.plan = plan; fallback.cost_us = total; have_fallback = true; }
       if (total / 1000.0 > wl.slo.tpot_p95_ms) continue;
+      const double tput_score = total / (double)g.batch.max_batch;
+      if (!have_fallback_tpot || tput_score < fallback_tpot_score) {
+        fallback_tpot.plan = plan; fallback_tpot.cost_us = total; fallback_tpot_score = tput_score; have_fallback_tpot = true;
+      }
+      if (p95_prompt > 0) {
+        // one sequence of that length through every stage in turn (tensor- and expert-parallel ranks of a stage work side by side)
+        const Placement pl = Placement::from_plan(plan);
+        Plan one = plan;
+        one.batching.max_batch = 1;
+        const WorkloadCtx pw{1, p95_prompt, p95_prompt};
+        std::vector<double> stage_us(std::max(1u, plan.parallelism.pp), 0.0);
+        for (size_t d = 0; d < cl.num_devices(); ++d)
+          if (pl.holds(d)) stage_us[pl.stage_of(d)] = std::max(stage_us[pl.stage_of(d)], cm.compute_on_device(one, ir, cl, pw, d));
+        double prefill_us = 0;
+        for (double t : stage_us) prefill_us += t;
+        if (prefill_us / 1000.0 > wl.slo.ttft_p95_ms) continue;
+      }
       score = total / (double)g.batch.max_batch;
     }
     if (!have || score < best_score) { res.plan = plan; res.cost_us = total; best_score = score; have = true; }
+  }
+  if (!have && have_fallback_tpot) {
+    res.plan = fallback_tpot.plan; res.cost_us = fallback_tpot.cost_us; have = true;
+  } else if (!have && have_fallback) {
+    res.plan = fallback.plan; res.cost_us = fallback.cost_us; have = true;
   }
   if (!have) {
     const auto& c = res.counters;

@@ -310,6 +310,29 @@ def test_enumeration_and_constraints():
     assert core.reject_reason(CFG, tiny_mem, REF_CONST, 2, 1, 1, 16, True) == "global_memory"
 
 
+def test_throughput_objective_respects_both_latency_targets():
+    """The throughput objective keeps plans whose decode step meets the TPOT target and whose prefill of the trace's
+    95th-percentile prompt meets the TTFT target; long prompts therefore need more tensor-parallel ranks. When nothing meets
+    both, the best plan that meets the TPOT target is returned, and when nothing meets that either, the shortest step."""
+    def trace(prompt, ttft, tpot=50):
+        hdr = {"slo": {"ttft_p95_ms": ttft, "tpot_p95_ms": tpot, "max_accuracy_drift": 0.01, "recompile_drift_threshold_kl": 0.05}}
+        return json.dumps(hdr) + "\n" + "".join(json.dumps({"prompt_tokens": prompt, "output_tokens": 64, "arrival_ms": 10 * i}) + "\n" for i in range(20))
+
+    def pick(n, prompt, ttft, tpot=50):
+        r = core.extract_plan(CFG, (ROOT / f"cluster/b200_{n}x.toml").read_text(), trace(prompt, ttft, tpot), DRIFT, CONST, {"objective": "throughput"})
+        p = json.loads(r["plan_json"])
+        return p["parallelism"]["tp"], p["batching"]["max_batch"]
+    assert pick(4, 2000, 300) == (4, 64)
+    # 32k-token prompts at about 20 us per token and rank: 650 ms on one rank, within 300 ms only on four
+    assert pick(4, 32000, 300) == (4, 64) and pick(2, 32000, 400)[0] == 2
+    # one GPU cannot meet 300 ms for such prompts: the plan that meets the TPOT target is kept, not a batch of one
+    assert pick(1, 32000, 300) == (1, 64)
+    # a TPOT target below any step: the shortest step
+    assert pick(1, 2000, 300, tpot=1) == (1, 1)
+    # on 8 GPUs a prompt-heavy trace with a tight TTFT keeps tensor parallelism at 8 where a lax one could choose fewer ranks' worth
+    assert pick(8, 32000, 150)[0] == 8
+
+
 def test_dtype_dp_behaviour():
     dp = lambda mem, drift: core.layer_dtype_dp(CFG, H100_2, REF_CONST, DRIFT, 2, 1, 1, 16, True, mem, drift)
     cost, dm = dp(70 * 10**9, 1e-9)                               # tight drift: everything stays bf16
