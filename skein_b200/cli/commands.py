@@ -38,10 +38,13 @@ def cmd_extract(args, emit) -> int:
         r = core.extract_plan(*ins, _search_options(args))
     Path(args.out).write_text(r["plan_json"])
     plan = json.loads(r["plan_json"])
-    report = {"plan_path": str(args.out), "content_hash": r["content_hash"], "cost_us": r["cost_us"], "search": json.loads(r["counters_json"]),
+    tok_s = plan["batching"]["max_batch"] / max(r["cost_us"], 1e-9) * 1e6      # every sequence of a full batch gains a token per step
+    report = {"plan_path": str(args.out), "content_hash": r["content_hash"], "cost_us": r["cost_us"], "predicted_tokens_per_s": round(tok_s, 1),
+              "objective": getattr(args, "objective", "throughput"), "search": json.loads(r["counters_json"]),
               "summary": _plan_summary(plan), "wall_s": round(time.time() - t0, 3)}
     s = report["summary"]
-    emit(args, report, f"plan written to {args.out}\n  hash        {r['content_hash']}\n  cost        {r['cost_us']:.1f} us per decode step\n"
+    emit(args, report, f"plan written to {args.out}\n  hash        {r['content_hash']}\n  cost        {r['cost_us']:.1f} us per decode step"
+                       f" ({tok_s:.0f} tokens/s at a full batch; objective: {report['objective']})\n"
                        f"  placement   tp={s['parallelism']['tp']} pp={s['parallelism']['pp']} ep={s['parallelism']['ep']}\n"
                        f"  batching    {s['batching']}\n  kv          {s['kv']}\n  dtypes      {s['dtype_histogram']}\n"
                        f"  search      {report['search']}")
