@@ -59,9 +59,10 @@ def estimate_runtime(plan_json: str, config_json: str, cluster_toml: str, consta
         p["batching"]["max_batch"] = batch
         return float(core.cost_breakdown(json.dumps(p), config_json, cluster_toml, constants_toml, 0)["total"])
     c1 = step_us(1)
-    exponent = 0.7
-    if B > 1:
-        exponent = min(1.0, max(0.0, math.log(max(step_us(B), c1) / c1) / math.log(B)))
+    # through the steps at batch 1 and at the plan's batch, or at 64 for a plan of fewer sequences (a server may be started
+    # with a larger --max-batch than the plan's)
+    Bref = max(B, 64)
+    exponent = min(1.0, max(0.0, math.log(max(step_us(Bref), c1) / c1) / math.log(Bref)))
     cfg = ModelConfig.from_hf_dict(json.loads(config_json))
     consts = json.loads(core.cost_constants_json(constants_toml))
     m = re.search(r'device_kind\s*=\s*"([^"]+)"', cluster_toml)
