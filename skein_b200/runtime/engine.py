@@ -272,7 +272,10 @@ class Engine:
         on the device is launched (PipelineStage.launch: the host does not wait), then the tokens of the oldest launch
         are accepted. A sequence belongs to one group from its first decode step to its last (the least loaded group
         when it starts). With one group per stage the launches of the other groups keep every stage busy while one
-        group's tokens travel back, so the pipeline is drained only by a prefill chunk or when sequences run out."""
+        group's tokens travel back, so the pipeline is drained only by a prefill chunk or when sequences run out.
+        Counterpart of the reference's continuous pipelined loops (run_continuous_pipelined and run_continuous_pipelined_mb,
+        crates/skein_runtime/src/distributed/gpu_rank.rs:1293, 1566; two stages and equal-length rows there, any number of
+        stages and ragged sequences here)."""
         events: list[TokenEvent] = []
         t_begin = time.perf_counter()
         stamp = lambda: now + int((time.perf_counter() - t_begin) * 1000)   # noqa: E731
