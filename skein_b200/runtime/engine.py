@@ -116,7 +116,8 @@ class Engine:
         self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
         self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
         if c.warm_graphs:
-            self.runner.capture_buckets(max_batch)
+            # data-parallel attention: a step has at least 4 rows per rank, whatever the number of sequences
+            self.runner.capture_buckets(max(max_batch, 4 * self._dp) if self._dp > 1 else max_batch)
         self.metrics = metrics or core.MetricsRegistry()
         self.clock = clock or (lambda: int(time.monotonic() * 1000))
         self._next_id = 1
