@@ -48,6 +48,20 @@ def test_mixtral_param_count_matches_known_value():
     assert core.model_param_count(CFG) == 46_702_792_704
 
 
+def test_shipped_configs_have_their_known_parameter_counts_and_plan():
+    from skein_b200.models.config import ModelConfig
+    known = {"mixtral_8x7b": 46_702_792_704, "llama3_70b": 70_553_706_496, "qwen2_5_7b": 7_615_616_512, "mistral_7b": 7_248_023_552}
+    for name, n in known.items():
+        cfg = (ROOT / f"configs/{name}_config.json").read_text()
+        assert core.model_param_count(cfg) == n == ModelConfig.from_file(ROOT / f"configs/{name}_config.json").param_count(), name
+        r = core.extract_plan(cfg, (ROOT / "cluster/b200_4x.toml").read_text(), TRACE, (ROOT / f"models/{name}_drift.toml").read_text(), CONST,
+                              {"objective": "throughput"})
+        par = json.loads(r["plan_json"])["parallelism"]
+        assert par["tp"] * par["pp"] * par["ep"] <= 4 and r["cost_us"] > 0
+    q = ModelConfig.from_file(ROOT / "configs/qwen2_5_7b_config.json")
+    assert q.qkv_bias and q.eos_token_id == 151645 and q.head_dim == 128 and q.max_position_embeddings == 32768
+
+
 def test_importer_layer_order_and_names():
     g = json.loads(core.import_model(CFG))
     kinds = [l["kind"]["kind"] for l in g["layers"]]
