@@ -113,6 +113,7 @@ class Engine:
             decode_us_at_b1=c.decode_us_at_b1, batch_exponent=c.batch_exponent,
             prefill_per_token_us=c.prefill_per_token_us, kv=self.kv, max_prefill_tokens=c.max_prefill_tokens,
             interleave_prefill_tokens=c.interleave_prefill_tokens)
+        self.cfg_vocab = int(decoder.cfg.vocab_size)
         self.max_blocks = max(1, (decoder.max_pos + decoder.page_size - 1) // decoder.page_size)
         self.runner = ModelRunner(decoder, self.max_blocks, use_graphs=c.use_graphs)
         if c.warm_graphs:
@@ -156,6 +157,9 @@ class Engine:
         self._next_id = max(self._next_id, rid) + 1
         now = self.clock() if now_ms is None else now_ms
         prompt = [int(t) for t in prompt_ids]
+        if not prompt or min(prompt) < 0 or max(prompt) >= self.cfg_vocab:
+            # an id outside the table reads as a zero row on the device and fails the whole step on the CPU path: refuse it here
+            raise ValueError(f"prompt must be a non-empty list of token ids in [0, {self.cfg_vocab})")
         if len(prompt) + max_new_tokens > self.dec.max_pos:
             self.metrics.record_request(rid, "rejected", 0.0, 0.0, 0, 0)
             raise ValueError(f"prompt + max_new_tokens exceeds the position limit {self.dec.max_pos}")

@@ -43,6 +43,9 @@ def build_app(driver: EngineDriver, tokenizer: Tokenizer, hotswap=None, artifact
             ids = tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
             if not ids or max_tokens < 1:
                 raise ValueError("empty prompt or max_tokens < 1")
+            vocab = driver.engine.cfg_vocab
+            if any(t < 0 or t >= vocab for t in ids):
+                raise ValueError(f"prompt token ids must be in [0, {vocab})")
             sampling = None
             if float(body.get("temperature", 0.0)) > 0.0:
                 sampling = SamplingParams(temperature=float(body["temperature"]), top_k=int(body.get("top_k", 0)),

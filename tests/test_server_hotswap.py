@@ -87,6 +87,9 @@ def test_http_completions_stream_metrics_and_errors(tmp_path):
             assert len(events) == 4 and events[-1]["is_final"] and not events[0]["is_final"] and all("token" in e for e in events)
             assert (await c.post("/v1/completions", json={"max_tokens": 3})).status == 400
             assert (await c.post("/v1/completions", data=b"not json")).status == 400
+            r = await c.post("/v1/completions", json={"prompt": [5, 300, 7], "max_tokens": 2})      # vocabulary is 300
+            assert r.status == 400 and "token ids" in (await r.json())["error"]["message"]
+            assert (await c.post("/v1/completions", json={"prompt": [-1], "max_tokens": 2})).status == 400
             r = await c.post("/v1/completions", json={"prompt": [1] * 250, "max_tokens": 100})
             assert r.status == 429                               # prompt + max_tokens beyond the position limit
             m = await (await c.get("/metrics")).text()
